@@ -1,0 +1,260 @@
+/*
+ * sparseforge_b200 — C ABI of the B200 (sm_100a) SparseLinear hot path.
+ *
+ * Every entry point takes raw device pointers, explicit sizes, dtype enums, scalar
+ * hyper-parameters and a CUDA stream (passed as void*, 0 = legacy default stream).
+ * No torch type crosses this boundary. The caller allocates and owns every buffer,
+ * outputs and scratch included; the library keeps no pointer after a call returns.
+ * All work is enqueued on the given stream; no entry point synchronises the device.
+ *
+ * Return value: 0 on success, a negative sf_status on failure (nothing is launched
+ * after a failed argument check). sf_last_error_string() returns the message of the
+ * last failure on the calling thread.
+ *
+ * Each declaration cites the interface of the SparseForge reference
+ * (liuhanzuo/SparseForge, paths relative to that project) that it stands in for.
+ */
+#ifndef SPARSEFORGE_B200_H
+#define SPARSEFORGE_B200_H
+
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define SF_API __attribute__((visibility("default")))
+#else
+#define SF_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum {
+    SF_OK = 0,
+    SF_ERR_BAD_ARG = -1,      /* null pointer, negative size, unknown enum */
+    SF_ERR_UNSUPPORTED = -2,  /* valid but not implemented (dtype / shape combination) */
+    SF_ERR_ALIGNMENT = -3,    /* pointer or leading dimension not aligned as required */
+    SF_ERR_CUDA = -4,         /* a CUDA runtime / driver call failed */
+    SF_ERR_DEVICE_WAIT = -5   /* a bounded device-side wait ran out (see sf_gemm_status) */
+} sf_status;
+
+typedef enum { SF_F32 = 0, SF_BF16 = 1, SF_I8 = 2 } sf_dtype;
+
+/* Importance metrics of compute_gate_target, legacy/sparse_modeling.py:1041-1079. */
+typedef enum {
+    SF_METRIC_HESSIAN_OBD = 0,   /* (H + 1e-8) * W^2 */
+    SF_METRIC_HESSIAN_RATIO = 1, /* |W| / sqrt(H + 1e-8) */
+    SF_METRIC_MAGNITUDE = 2,     /* |W| */
+    SF_METRIC_HESSIAN = 3,       /* H */
+    SF_METRIC_MOVEMENT = 4       /* |W * grad_ema| / temperature (aux = grad_ema) */
+} sf_metric;
+
+/* Penalty pull inside update_mask, legacy/sparse_modeling.py:1295-1573. */
+typedef enum {
+    SF_PENALTY_NONE = 0,
+    SF_PENALTY_TOPN = 1, /* 'nm_2_4' (:1350-1393) and 'structured_topn' (:1532-1566) */
+    SF_PENALTY_MID = 2   /* 'mid' (:1567-1570) */
+} sf_penalty_mode;
+
+SF_API int sf_version(void);
+SF_API const char* sf_last_error_string(void);
+
+/* Number of doubles of scratch sf_hutch_score needs for `n` weight elements. */
+SF_API int64_t sf_hutch_score_scratch_doubles(int64_t n);
+
+/*
+ * Hutchinson Hessian-diagonal accumulation fused with the importance score and the
+ * layer-wide score statistics.
+ *   replaces: update_hessian_hutchinson elementwise tail, legacy/utils.py:804-868
+ *             score formulas, legacy/sparse_modeling.py:1041-1079
+ *             mean / population std of the score, legacy/sparse_modeling.py:1084-1088
+ *   if hvp != NULL:  H <- beta*H + (1-beta)*max(hvp*v, 0)      (H fp32, in place)
+ *   score <- metric(W, H)                                      (fp32, raw)
+ *   norm[0] <- mean(score), norm[1] <- std_pop(score) + 1e-6   (fp32, on device)
+ * hvp and W have dtype w_dtype; v has dtype v_dtype (SF_I8 signs or w_dtype).
+ * aux is grad_ema for SF_METRIC_MOVEMENT (w_dtype), else ignored; aux_scalar is the
+ * movement temperature. scratch: sf_hutch_score_scratch_doubles(n) doubles.
+ * n = rows*cols, must be a multiple of 8; buffers 16-byte aligned.
+ */
+SF_API int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const void* W,
+                   int w_dtype, const void* aux, float aux_scalar, float* score,
+                   float* norm, double* scratch, int64_t n, float beta, int metric,
+                   void* stream);
+
+/* Stats written by sf_mask_update_nm24 (8 doubles). */
+enum {
+    SF_MSTAT_FLIPS = 0,       /* sum xor(hard(prev mask), hard(new mask)), :1659-1661 */
+    SF_MSTAT_SUM_M = 1,       /* sum m */
+    SF_MSTAT_SUM_M1M = 2,     /* sum m(1-m)  (mid_penalty numerator, legacy/utils.py:913) */
+    SF_MSTAT_SUM_TOP2 = 3,    /* sum of the two largest m per group (nm_2_4_tile_stats) */
+    SF_MSTAT_SUM_BOT2 = 4,    /* sum of the two smallest m per group */
+    SF_MSTAT_COUNT_LT_HALF = 5, /* count m < 0.5 (sparsity_penalty threshold path) */
+    SF_MSTAT_COUNT = 8
+};
+
+/*
+ * One structured (N:M = 2:4) soft-mask update with everything that depends on the new
+ * mask, in one pass over the layer.
+ *   replaces: SparseLinear.update_mask, legacy/sparse_modeling.py:1242-1666, with
+ *             compute_gate_target structured branch :1084-1088, :1164-1185,
+ *             beta mixing :1199-1225, penalty :1350-1393 / :1532-1570, binarize push
+ *             :1575-1590, EMA :1593, flip count :1659-1661;
+ *             effective mask of SparseLinear.forward :759-771 and the weight*mask of
+ *             FusedMaskedLinearSTE.forward :74-81; _hard_mask_from_soft :720-735.
+ *   s  = (score - norm[0]) / norm[1]   (rounded to bf16 first when score_bf16 != 0)
+ *   G  = sigmoid((s - tau_g)/(T + 1e-8)), tau_g = 2nd largest s of the group of 4
+ *        (or the exact 0/1 top-2 indicator when structured_exact != 0)
+ *   G  = (1-beta_s) G + beta_s top2(s)                      if beta_s > 0
+ *   G  = clamp(G - pen*(mask - top2(G)), 0, 1)              SF_PENALTY_TOPN, pen != 0
+ *   G  = clamp(G - pen*(1 - 2 mask), 0, 1)                  SF_PENALTY_MID,  pen != 0
+ *   G  = G*(1-d) if G<0.5, G*(1+d) if G>0.5                 if d != 0
+ *   mask <- clamp(mask*(1-a) + a*G, 0, 1)                   (fp32, in place)
+ *   hard = top2(mask); M_eff = hx*mask + (1-hx)*hard (hx >= 1: mask itself)
+ *   wm   <- W * cast(M_eff)   (w_dtype, optional)           meta <- 2:4 metadata of hard
+ * Ties inside a group go to the lower column index everywhere.
+ * meta: one byte per two groups, row-major [rows, cols/8]: low nibble = group 2j, high
+ * nibble = group 2j+1; nibble = i0 | (i1 << 2) with i0 < i1 the kept column offsets.
+ * stats: SF_MSTAT_COUNT doubles, overwritten. cols % 8 == 0.
+ */
+SF_API int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W,
+                        int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows,
+                        int64_t cols, float temperature, float mask_lr, float pen,
+                        int penalty_mode, float beta_s, float binarize_decay, float hx,
+                        int structured_exact, int score_bf16, void* stream);
+
+/*
+ * Hard top-2-of-4 projection along the input dimension.
+ *   replaces: SparseLinear._hard_mask_from_soft 'nm_2_4' :578-603 and 'structured'
+ *             :720-735, legacy/sparse_modeling.py; the inline copy at
+ *             legacy/main_llama.py:2610-2661.
+ * soft: [rows, cols] of dtype in_dtype with row stride ld_soft (elements). hard (optional)
+ * gets 0/1 in out_dtype with row stride ld_hard; columns beyond (cols/4)*4 are 1.
+ * meta (optional) as in sf_mask_update_nm24 with row stride ceil(cols/8) bytes.
+ */
+SF_API int sf_project_nm24(const void* soft, int in_dtype, int64_t ld_soft, void* hard, int out_dtype,
+                    int64_t ld_hard, uint8_t* meta, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * Effective masked weight without a mask update.
+ *   replaces: SparseLinear.forward :759-771 + FusedMaskedLinearSTE.forward :74-81,
+ *             legacy/sparse_modeling.py (there recomputed on every forward call).
+ *   wm <- W * cast(hx*mask + (1-hx)*top2(mask));  finalized != 0 or hx >= 1: W * cast(mask).
+ *   scale != 1 multiplies wm afterwards (weight_scaling, :777-784).
+ */
+SF_API int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm, uint8_t* meta,
+                        int64_t rows, int64_t cols, float hx, int finalized, float scale,
+                        void* stream);
+
+/*
+ * Mask-aware AdamW step for one parameter tensor.
+ *   replaces: AdamW.step, legacy/adamw.py:65-176 (order of operations as there):
+ *   p *= 1 - lr*wd;  g += decay * p * (1 - mask)  (mask != NULL);
+ *   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  denom = sqrt(v)/sqrt(bc2) + eps;
+ *   p -= (lr/bc1) m/denom;  p -= lr*l1*sign(p)/denom  (l1 > 0, mask != NULL).
+ * bc1 = 1 - b1^step and bc2 = 1 - b2^step are computed by the caller.
+ * p, g, m, v share dtype w_dtype (state dtype = weight dtype, adamw.py:123-125);
+ * mask is fp32. If wm != NULL the new effective masked weight is also written:
+ * wm <- p * cast(hx*mask + (1-hx)*top2(mask)) (cols % 8 == 0 then; rows*cols = n).
+ */
+SF_API int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype,
+                    int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                    float decay, float bc1, float bc2, float adaptive_l1, void* wm, float hx,
+                    int64_t cols, void* stream);
+
+/*
+ * Mask reductions for one layer (no mask update).
+ *   replaces: mid_penalty legacy/utils.py:875-938, sparsity_penalty :941-1025,
+ *             nm_2_4_tile_stats :1028-1234 (the per-layer sums; the caller combines layers).
+ * stats as SF_MSTAT_* (FLIPS is left 0). cols % 4 == 0.
+ */
+SF_API int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, void* stream);
+
+/*
+ * Masked dense GEMMs (tcgen05 / TMEM / TMA, bf16 operands, fp32 accumulation).
+ *   replaces: FusedMaskedLinearSTE.forward matmul, legacy/sparse_modeling.py:83-87,
+ *             and .backward :105-129.
+ * Operands are row-major 2-D; T = tokens. wm is the pre-masked weight [out, in].
+ *   fwd  : y[T,out]  = alpha * x[T,in] . wm[out,in]^T  (+ bias[out])
+ *   dgrad: dx[T,in]  = dy[T,out] . wm[out,in]
+ *   wgrad: dw[out,in]= dy[T,out]^T . x[T,in]                      (no mask: STE)
+ * dtype: SF_BF16 (tensor cores) or SF_F32 (fp32 FMA path, used for fp32 parity cases).
+ * status (optional, device int32[4]): set non-zero if a bounded device-side wait ran
+ * out; the output is then undefined. in, out, T multiples of 8; 16-byte aligned.
+ */
+SF_API int sf_masked_gemm_fwd(const void* x, const void* wm, const void* bias, void* y, int64_t T,
+                       int64_t in, int64_t out, float alpha, int dtype, int32_t* status,
+                       void* stream);
+SF_API int sf_masked_gemm_dgrad(const void* dy, const void* wm, void* dx, int64_t T, int64_t in,
+                         int64_t out, int dtype, int32_t* status, void* stream);
+SF_API int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int64_t in,
+                         int64_t out, int dtype, int32_t* status, void* stream);
+
+/*
+ * Bias gradient: db[out] = sum_t dy[t, out].
+ *   replaces: grad_out_2d.sum(dim=0), legacy/sparse_modeling.py:127-129.
+ * db is fp32 and is overwritten.
+ */
+SF_API int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t out, void* stream);
+
+/*
+ * Hard-2:4 compressed weights.
+ *   replaces: the finalisation bake-in mask.copy_(hard); weight.mul_(mask),
+ *             legacy/main_llama.py:2552-2563, and optimize_sparse_model_for_inference,
+ *             legacy/eval_wiki_ppl.py:548-651 (the reference keeps the zeros dense; it has
+ *             no compressed format).
+ * values[out, in/2] (bf16): the two kept elements of each group of 4, in column order.
+ * meta as in sf_mask_update_nm24. The kept set is top2 of `soft` (fp32, e.g. |W| or the
+ * soft mask) with ties to the lower index.
+ */
+SF_API int sf_sparse24_compress(const void* W, const float* soft, void* values, uint8_t* meta,
+                         int64_t out, int64_t in, void* stream);
+/* Inverse of sf_sparse24_compress: dense[out,in] = W * hard (bf16). */
+SF_API int sf_sparse24_decompress(const void* values, const uint8_t* meta, void* dense, int64_t out,
+                           int64_t in, void* stream);
+
+/* Bytes of the tensor-core ordered metadata buffer sf_sparse24_pack_meta writes. */
+SF_API int64_t sf_sparse24_meta_tc_bytes(int64_t out, int64_t in);
+/* Reorders logical metadata into the order the sparse tensor-core GEMM loads. */
+SF_API int sf_sparse24_pack_meta(const uint8_t* meta, uint8_t* meta_tc, int64_t out, int64_t in,
+                          void* stream);
+/*
+ * y[T,out] = x[T,in] . decompress(values, meta)^T  (+ bias) on the sparse tensor cores
+ * (tcgen05.mma.sp, kind::f16). Same semantics as sf_masked_gemm_fwd with a binary 2:4
+ * mask (legacy/sparse_modeling.py:72-93 after finalisation).
+ */
+SF_API int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, const void* bias,
+                     void* y, int64_t T, int64_t in, int64_t out, int32_t* status, void* stream);
+
+/*
+ * Block-sparse-16 (block-CSR) weights.
+ *   replaces: convert_to_block_sparse, legacy/triton_block_sparse.py:46-103 (same layout:
+ *             blocks[nnz,16,16], row_ptr[out/16+1] int32, col_idx[nnz] int32; a block is
+ *             kept iff sum|w*mask| > 0), built on the device instead of a Python loop.
+ * Call with blocks == NULL to count: row_ptr is filled and *nnz_out (device int32) is set;
+ * then call again with blocks/col_idx sized for nnz.
+ */
+SF_API int sf_bsr16_build(const void* W, const void* mask, int dtype, int mask_dtype, void* blocks,
+                   int32_t* row_ptr, int32_t* col_idx, int32_t* nnz_out, int64_t out, int64_t in,
+                   void* stream);
+/*
+ * Block-sparse-16 products.
+ *   replaces: block_sparse_matmul_v2_kernel, legacy/triton_block_sparse.py:224-284 (fwd);
+ *             dgrad / wgrad have no reference kernel: they are the dense STE backward of
+ *             legacy/sparse_modeling.py:105-125 restricted to the kept blocks.
+ *   fwd  : y[T,out]  = x[T,in] . Wbsr^T (+ bias)
+ *   dgrad: dx[T,in]  = dy[T,out] . Wbsr
+ *   wgrad: dblocks[nnz,16,16] = (dy^T . x) at the kept blocks
+ */
+SF_API int sf_bsr16_fwd(const void* x, const void* blocks, const int32_t* row_ptr, const int32_t* col_idx,
+                 const void* bias, void* y, int64_t T, int64_t in, int64_t out, int dtype,
+                 void* stream);
+SF_API int sf_bsr16_dgrad(const void* dy, const void* blocks, const int32_t* row_ptr,
+                   const int32_t* col_idx, void* dx, int64_t T, int64_t in, int64_t out, int dtype,
+                   void* stream);
+SF_API int sf_bsr16_wgrad(const void* dy, const void* x, const int32_t* row_ptr, const int32_t* col_idx,
+                   void* dblocks, int64_t T, int64_t in, int64_t out, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPARSEFORGE_B200_H */

@@ -1,0 +1,323 @@
+"""CPU oracle for the SparseLinear hot path.  TEST INFRASTRUCTURE ONLY.
+
+A restatement, in plain torch-CPU tensor code, of the algorithms of the SparseForge
+reference (liuhanzuo/SparseForge; citations are ``file:line`` inside that project). Only
+``tests/``, ``__graft_entry__.smoke()`` and the CPU-baseline leg of ``bench.py`` may import
+this module, and only as the checker; nothing in ``sparseforge_b200/`` imports it.
+
+Parity status: the reference ships no tests or golden vectors, so the oracle is pinned
+against outputs of the reference itself: ``tests/golden/make_golden.py`` imports the
+reference (torch 2.11 CPU), runs it on seeded inputs with ``torch.topk`` made tie-stable
+(lower index wins, as the specification of this path requires) and stores its inputs,
+intermediates and outputs; ``tests/test_oracle_golden.py`` replays them through this module.
+
+The arithmetic lives in PyTorch ATen (a dependency of the reference, ``requirements.txt:2``
+``torch>=2.1.0``); rounding points below follow what ATen does for the dtype mix used
+(bf16 weights and gradients, fp32 mask / Hessian / score).
+"""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+
+# --------------------------------------------------------------------------------------
+# top-N of M with the tie rule "lower index wins"
+# --------------------------------------------------------------------------------------
+def stable_topk_indices(x: torch.Tensor, k: int) -> torch.Tensor:
+    """Indices of the k largest entries along the last dim; equal values keep index order.
+
+    Stands in for ``torch.topk(..., largest=True).indices`` (used at
+    legacy/sparse_modeling.py:597, 732, 1172, 1213, 1380, 1559), whose tie order is
+    unspecified. NaN sorts as the largest value, as in torch.
+    """
+    return torch.sort(x, dim=-1, descending=True, stable=True).indices[..., :k]
+
+
+def topn_indicator(x2d: torch.Tensor, n: int = 2, m: int = 4, dtype=None) -> torch.Tensor:
+    """0/1 tensor marking the top-n of every group of m along the last dim (cols % m == 0)."""
+    rows, cols = x2d.shape
+    g = x2d.detach().float().view(rows, cols // m, m)
+    idx = stable_topk_indices(g, n)
+    out = torch.zeros_like(g, dtype=dtype or x2d.dtype)
+    out.scatter_(-1, idx, 1.0)
+    return out.view(rows, cols)
+
+
+def hard_mask_from_soft(soft: torch.Tensor, mode: str = "structured", n: int = 2, m: int = 4) -> torch.Tensor:
+    """legacy/sparse_modeling.py:510-735, modes 'structured' (:720-735), 'nm_2_4' (:578-603),
+    'unstructured' (:526-527), 'none' (:523-524)."""
+    if mode == "none":
+        return torch.ones_like(soft)
+    if mode == "unstructured" or soft.dim() != 2:
+        return (soft > 0.5).to(soft.dtype)
+    rows, cols = soft.shape
+    if mode == "structured":
+        if cols % m != 0:
+            raise ValueError(f"in_features ({cols}) must be divisible by M ({m}).")
+        return topn_indicator(soft, n, m)
+    if mode == "nm_2_4":
+        full = (cols // 4) * 4
+        hard = torch.ones_like(soft)
+        if full > 0:
+            hard[:, :full] = topn_indicator(soft[:, :full].contiguous(), 2, 4)
+        return hard
+    raise ValueError(f"Invalid hard mask_type: {mode}")
+
+
+def meta_from_hard(hard: torch.Tensor) -> torch.Tensor:
+    """Logical 2:4 metadata of a 0/1 mask: per group nibble i0 | (i1 << 2) (i0 < i1 kept column
+    offsets), two groups per byte (low nibble first), rows of ceil(cols/8) bytes. Groups of
+    the ragged tail (beyond (cols//4)*4) get nibble 0. The reference has no metadata format;
+    this is the canonical form the CUDA path is compared with."""
+    rows, cols = hard.shape
+    groups = cols // 4
+    h = (hard[:, : groups * 4] > 0.5).view(rows, groups, 4).to(torch.int64)
+    pos = torch.arange(4).view(1, 1, 4)
+    big = torch.where(h > 0, pos, torch.full_like(pos, 99).expand_as(h))
+    i0 = big.min(dim=-1).values
+    small = torch.where(h > 0, pos, torch.full_like(pos, -1).expand_as(h))
+    i1 = small.max(dim=-1).values
+    nib = (i0 | (i1 << 2)).to(torch.uint8)
+    bytes_per_row = (cols + 7) // 8
+    padded = torch.zeros(rows, bytes_per_row * 2, dtype=torch.uint8)
+    padded[:, :groups] = nib
+    return (padded[:, 0::2] | (padded[:, 1::2] << 4)).contiguous()
+
+
+# --------------------------------------------------------------------------------------
+# Hutchinson accumulation and scores
+# --------------------------------------------------------------------------------------
+def hutchinson_accumulate(H: torch.Tensor, hvp: torch.Tensor, v: torch.Tensor, beta: float) -> torch.Tensor:
+    """legacy/utils.py:804-868 (non-FSDP branch, world size 1): H <- beta H + (1-beta) clamp(hvp*v, 0)."""
+    d = torch.clamp((hvp * v.to(hvp.dtype)).detach(), min=0.0)
+    return H.clone().mul_(beta).add_(d, alpha=1 - beta)
+
+
+def importance_score(W, metric="hessian_obd", H=None, grad_ema=None, temperature=1.0):
+    """legacy/sparse_modeling.py:1041-1079."""
+    eps = 1e-8
+    if metric == "magnitude":
+        return W.abs()
+    if metric == "movement":
+        return (W * grad_ema).abs() / max(float(temperature), eps)
+    if metric == "hessian_obd":
+        return (H + eps) * (W * W)
+    if metric == "hessian_ratio":
+        return W.abs() / torch.sqrt(H + eps)
+    if metric == "hessian":
+        return H
+    raise ValueError(metric)
+
+
+def score_norm_stats(scores: torch.Tensor):
+    """mean and population std + 1e-6 of the fp32 scores, legacy/sparse_modeling.py:1085-1087."""
+    s = scores.float()
+    return s.mean(), s.std(unbiased=False) + 1e-6
+
+
+def normalize_scores(scores: torch.Tensor) -> torch.Tensor:
+    """legacy/sparse_modeling.py:1084-1088."""
+    mu, sigma = score_norm_stats(scores)
+    return ((scores.float() - mu) / sigma).to(scores.dtype)
+
+
+# --------------------------------------------------------------------------------------
+# gate target and mask update (structured N:M = 2:4)
+# --------------------------------------------------------------------------------------
+def gate_target_structured(scores_norm, temperature, *, exact=False, beta_s=0.0, n=2, m=4):
+    """legacy/sparse_modeling.py:1164-1185 (+ beta mixing :1199-1225)."""
+    rows, cols = scores_norm.shape
+    s = scores_norm.float().view(rows, cols // m, m)
+    idx = stable_topk_indices(s, n)
+    tau = torch.gather(s, -1, idx[..., n - 1 : n])
+    Tt = torch.tensor(float(temperature), dtype=torch.float32)
+    if exact:
+        G = torch.zeros_like(s, dtype=scores_norm.dtype)
+        G.scatter_(-1, idx, 1.0)
+        G = G.view(rows, cols)
+    else:
+        G = torch.sigmoid((s - tau) / (Tt + 1e-8)).view(rows, cols).to(scores_norm.dtype)
+    if beta_s > 0.0:
+        target = topn_indicator(scores_norm, n, m, dtype=G.dtype)
+        G = ((1.0 - beta_s) * G.float() + beta_s * target.float()).to(G.dtype)
+    return G
+
+
+def mask_update(mask, G, *, mask_lr, lambda_mid=0.0, pen_lr=None, penalty_mode="mid", binarize_decay=0.0,
+                n=2, m=4):
+    """legacy/sparse_modeling.py:1288-1593 for the structured / nm_2_4 / mid penalty modes.
+    Returns the new mask."""
+    a = float(mask_lr)
+    pen_lr = a if pen_lr is None else float(pen_lr)
+    if float(lambda_mid) != 0.0:
+        if penalty_mode in ("structured_topn", "nm_2_4"):
+            target = topn_indicator(G, n, m, dtype=G.dtype)
+            G = G - (pen_lr * float(lambda_mid)) * (mask.to(G.dtype) - target)
+        elif penalty_mode == "mid":
+            G = G - (pen_lr * float(lambda_mid)) * (1.0 - 2.0 * mask).to(G.dtype)
+        else:
+            raise ValueError(penalty_mode)
+        G = G.clamp(0.0, 1.0)
+    d = float(binarize_decay)
+    if d != 0.0:
+        G = G.clone()
+        lt, gt = G < 0.5, G > 0.5
+        G[lt] = G[lt] * (1.0 - d)
+        G[gt] = G[gt] * (1.0 + d)
+    return mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0)
+
+
+def hardening_x(step, start, duration):
+    """legacy/sparse_modeling.py:1603-1619."""
+    if duration <= 0:
+        return 0.0 if (step >= start and start > 0) else 1.0
+    if step < start:
+        return 1.0
+    if step >= start + duration:
+        return 0.0
+    return max(0.0, min(1.0, 1.0 - float(step - start) / float(max(1, duration))))
+
+
+def temperature_at(step, temp_init, temp_decay, temp_min, period=1):
+    """legacy/sparse_modeling.py:932-942 (non block-sparse)."""
+    updates = step // max(1, int(period))
+    return float(max(float(temp_min), float(temp_init) * (float(temp_decay) ** updates)))
+
+
+def flip_count(prev_mask, new_mask, mode="structured"):
+    """legacy/sparse_modeling.py:1659-1661."""
+    hp = hard_mask_from_soft(prev_mask, mode) > 0.5
+    hn = hard_mask_from_soft(new_mask, mode) > 0.5
+    return int((hp ^ hn).sum().item())
+
+
+def effective_mask(mask, hx, mode="structured", finalized=False):
+    """legacy/sparse_modeling.py:745-771."""
+    if hx >= 1.0 - 1e-6 or finalized:
+        return mask
+    return (hx * mask) + ((1.0 - hx) * hard_mask_from_soft(mask, mode))
+
+
+def masked_weight(W, eff_mask, scale=1.0):
+    """legacy/sparse_modeling.py:74-81."""
+    w = W * eff_mask.to(W.dtype)
+    return w * scale if scale != 1.0 else w
+
+
+def mask_stats(mask):
+    """Per-layer sums behind mid_penalty (legacy/utils.py:913), nm_2_4_tile_stats (:1028-1234, sorted
+    groups: top-2 / bottom-2 sums) and the threshold path of sparsity_penalty (:1003)."""
+    rows, cols = mask.shape
+    m64 = mask.double()
+    g = torch.sort(m64.view(rows, cols // 4, 4), dim=-1, descending=True).values
+    return {
+        "sum_m": float(m64.sum()),
+        "sum_m1m": float((m64 * (1 - m64)).sum()),
+        "sum_top2": float(g[..., :2].sum()),
+        "sum_bot2": float(g[..., 2:].sum()),
+        "count_lt_half": float((mask < 0.5).sum()),
+    }
+
+
+# --------------------------------------------------------------------------------------
+# masked linear forward / backward
+# --------------------------------------------------------------------------------------
+def linear_forward(x, W, eff_mask, bias=None, scale=1.0):
+    """legacy/sparse_modeling.py:72-93."""
+    w = masked_weight(W, eff_mask, scale)
+    x2 = x.reshape(-1, x.shape[-1])
+    y = x2.matmul(w.t())
+    if bias is not None:
+        y = y + bias
+    return y.view(*x.shape[:-1], W.shape[0])
+
+
+def linear_backward(x, W, eff_mask, dy, has_bias=False):
+    """legacy/sparse_modeling.py:96-132 (decay = 0): returns (dx, dW, db)."""
+    cd = dy.dtype
+    dy2 = dy.reshape(-1, dy.shape[-1])
+    x2 = x.reshape(-1, x.shape[-1]).to(cd)
+    w = W.to(cd) * eff_mask.to(cd)
+    dx = dy2.matmul(w).view_as(x)
+    dW = dy2.t().matmul(x2)
+    db = dy2.sum(dim=0) if has_bias else None
+    return dx, dW, db
+
+
+# --------------------------------------------------------------------------------------
+# mask-aware AdamW
+# --------------------------------------------------------------------------------------
+def adamw_step(p, g, m, v, *, step, lr, betas, eps, weight_decay, mask=None, decay=0.0, adaptive_l1=0.0):
+    """legacy/adamw.py:79-174 for one tensor. `step` is the 1-based step number after the
+    increment at :146. Returns (p, m, v) as new tensors."""
+    p, m, v = p.clone(), m.clone(), v.clone()
+    beta1, beta2 = betas
+    p.mul_(1 - lr * weight_decay)
+    grad = g
+    if mask is not None:
+        grad = grad.add(p * (1 - mask), alpha=decay)
+    bc1 = 1 - beta1 ** step
+    bc2 = 1 - beta2 ** step
+    m.mul_(beta1).add_(grad, alpha=1 - beta1)
+    v.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
+    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    p.addcdiv_(m, denom, value=-(lr / bc1))
+    if adaptive_l1 > 0.0 and p.dim() >= 2 and mask is not None:
+        p.add_(adaptive_l1 * torch.sign(p) / denom, alpha=-lr)
+    return p, m, v
+
+
+# --------------------------------------------------------------------------------------
+# hard-2:4 compression and block-sparse-16 layout
+# --------------------------------------------------------------------------------------
+def sparse24_compress(W, soft):
+    """Kept values [out, in/2] (column order) and packed metadata of top2(soft); semantics of the
+    finalisation bake-in legacy/main_llama.py:2552-2563 (weight.mul_(hard))."""
+    hard = topn_indicator(soft.float(), 2, 4, dtype=torch.float32)
+    rows, cols = W.shape
+    keep = hard.view(rows, cols // 4, 4) > 0.5
+    idx = torch.sort(keep.to(torch.int8), dim=-1, descending=True, stable=True).indices[..., :2]
+    idx = torch.sort(idx, dim=-1).values
+    vals = torch.gather(W.view(rows, cols // 4, 4), -1, idx).reshape(rows, cols // 2)
+    return vals, meta_from_hard(hard), hard
+
+
+def block16_keep_mask(W, density=0.5, bs=16):
+    """0/1 mask keeping the round(density * #blocks) 16x16 blocks of largest Frobenius norm (same
+    ordering as the block RMS of legacy/sparse_modeling.py:686-710 applied to |W|); ties go to
+    the lower flat block index."""
+    out, inn = W.shape
+    ob, ib = out // bs, inn // bs
+    tiles = W.float().view(ob, bs, ib, bs).permute(0, 2, 1, 3).reshape(ob * ib, bs * bs)
+    score = (tiles ** 2).sum(dim=-1)
+    k = int(round(density * ob * ib))
+    order = torch.sort(score, descending=True, stable=True).indices[:k]
+    keep = torch.zeros(ob * ib, dtype=torch.bool)
+    keep[order] = True
+    return keep.view(ob, 1, ib, 1).expand(ob, bs, ib, bs).reshape(out, inn).to(W.dtype)
+
+
+def bsr16_convert(W, mask, bs=16):
+    """legacy/triton_block_sparse.py:46-103: (blocks[nnz,16,16], row_ptr int32, col_idx int32)."""
+    out, inn = W.shape
+    ob, ib = out // bs, inn // bs
+    blocked = (W * mask).view(ob, bs, ib, bs).permute(0, 2, 1, 3)
+    nz = blocked.abs().float().sum(dim=(-1, -2)) > 0
+    row_ptr = torch.zeros(ob + 1, dtype=torch.int32)
+    row_ptr[1:] = torch.cumsum(nz.sum(dim=1), 0).to(torch.int32)
+    rows_i, cols_i = torch.nonzero(nz, as_tuple=True)
+    blocks = blocked[rows_i, cols_i].contiguous()
+    if blocks.shape[0] == 0:
+        blocks = torch.zeros(1, bs, bs, dtype=W.dtype)
+    return blocks, row_ptr, cols_i.to(torch.int32)
+
+
+def to_numpy(t: torch.Tensor) -> np.ndarray:
+    """bf16 tensors are stored as their raw uint16 bits."""
+    t = t.detach().cpu().contiguous()
+    if t.dtype == torch.bfloat16:
+        return t.view(torch.int16).numpy().view(np.uint16)
+    return t.numpy()

@@ -1,0 +1,85 @@
+"""ctypes binding of ``libsparseforge_b200.so`` (declared in ``include/sparseforge_b200.h``).
+
+There is no CPU or eager fallback: if the shared library is missing, loading fails with an
+error that says how to build it, and every op in this package fails with it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_double, c_float, c_int, c_int32, c_int64, c_uint8, c_void_p, POINTER
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "lib", "libsparseforge_b200.so")
+
+SF_F32, SF_BF16, SF_I8 = 0, 1, 2
+METRICS = {"hessian_obd": 0, "hessian_ratio": 1, "magnitude": 2, "hessian": 3, "movement": 4}
+PENALTY_NONE, PENALTY_TOPN, PENALTY_MID = 0, 1, 2
+MSTAT_FLIPS, MSTAT_SUM_M, MSTAT_SUM_M1M, MSTAT_SUM_TOP2, MSTAT_SUM_BOT2, MSTAT_COUNT_LT_HALF = range(6)
+MSTAT_COUNT = 8
+
+_P = c_void_p
+_SIGNATURES = {
+    "sf_version": (c_int, []),
+    "sf_last_error_string": (c_char_p, []),
+    "sf_hutch_score_scratch_doubles": (c_int64, [c_int64]),
+    "sf_hutch_score": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_float, _P, _P, _P, c_int64, c_float, c_int, _P]),
+    "sf_mask_update_nm24": (c_int, [_P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_float, c_float, c_float,
+                                    c_int, c_float, c_float, c_float, c_int, c_int, _P]),
+    "sf_project_nm24": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int64, c_int64, _P]),
+    "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_float, c_int, c_float, _P]),
+    "sf_adamw_masked": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_float, c_float, c_float, c_float, c_float,
+                                c_float, c_float, c_float, c_float, _P, c_float, c_int64, _P]),
+    "sf_mask_stats": (c_int, [_P, _P, c_int64, c_int64, _P]),
+    "sf_masked_gemm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_float, c_int, _P, _P]),
+    "sf_masked_gemm_dgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_masked_gemm_wgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_bias_grad": (c_int, [_P, c_int, _P, c_int64, c_int64, _P]),
+    "sf_sparse24_compress": (c_int, [_P, _P, _P, _P, c_int64, c_int64, _P]),
+    "sf_sparse24_decompress": (c_int, [_P, _P, _P, c_int64, c_int64, _P]),
+    "sf_sparse24_meta_tc_bytes": (c_int64, [c_int64, c_int64]),
+    "sf_sparse24_pack_meta": (c_int, [_P, _P, c_int64, c_int64, _P]),
+    "sf_sparse24_gemm": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P]),
+    "sf_bsr16_build": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int64, c_int64, _P]),
+    "sf_bsr16_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
+    "sf_bsr16_dgrad": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
+    "sf_bsr16_wgrad": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
+}
+
+_lib = None
+
+
+def declared_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded shared library. Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"sparseforge_b200: {LIB_PATH} is missing. Build it with "
+                "`python -m sparseforge_b200.build` (needs nvcc). There is no fallback path."
+            )
+        h = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            try:
+                fn = getattr(h, name)
+            except AttributeError:
+                continue  # reported by callers of missing(); ops using it fail on call
+            fn.restype = res
+            fn.argtypes = args
+        _lib = h
+    return _lib
+
+
+def missing_symbols() -> list[str]:
+    h = lib()
+    return [n for n in _SIGNATURES if not hasattr(h, n)]
+
+
+def check(rc: int, what: str = "") -> None:
+    if rc != 0:
+        msg = lib().sf_last_error_string()
+        raise RuntimeError(f"sparseforge_b200 {what} failed ({rc}): {msg.decode() if msg else ''}")

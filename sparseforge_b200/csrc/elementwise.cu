@@ -1,0 +1,779 @@
+// HBM-bound passes of the SparseLinear hot path: Hutchinson accumulate + score,
+// 2:4 soft-mask update + hard projection + masked-weight emit, mask-aware AdamW,
+// mask statistics, bias gradient. Each thread owns 8 consecutive elements (two 2:4
+// groups) and moves them with 16-byte streaming accesses; grids are sized from the
+// SM count and walk the tensor with a grid-stride loop.
+#include "common.cuh"
+
+namespace sf {
+
+static thread_local char g_err[512];
+char* last_error_buffer() { return g_err; }
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count() {
+    static thread_local int cached_dev = -1;
+    static thread_local int cached = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+    if (dev != cached_dev) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+        cached = n;
+        cached_dev = dev;
+    }
+    return cached;
+}
+
+constexpr int kThreads = 256;
+constexpr int kMaxPartialBlocks = 2048;
+
+// Blocks for a grid-stride pass over `chunks` 8-element chunks: a multiple of the SM count.
+static inline int grid_for(int64_t chunks, int blocks_per_sm) {
+    int64_t need = (chunks + kThreads - 1) / kThreads;
+    int64_t cap = (int64_t)sm_count() * blocks_per_sm;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+// ---------------------------------------------------------------------------------------
+// Hutchinson accumulate + score + partial sums
+// ---------------------------------------------------------------------------------------
+template <typename TV>
+__device__ __forceinline__ void load_signs(const TV* p, float (&x)[8]);
+template <>
+__device__ __forceinline__ void load_signs<int8_t>(const int8_t* p, float (&x)[8]) {
+    uint2 a = ld_stream8(p);
+    uint32_t w[2] = {a.x, a.y};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = (float)(int8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xff);
+}
+template <>
+__device__ __forceinline__ void load_signs<float>(const float* p, float (&x)[8]) {
+    Vec8<float>::load(p, x);
+}
+template <>
+__device__ __forceinline__ void load_signs<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[8]) {
+    Vec8<__nv_bfloat16>::load(p, x);
+}
+
+template <typename TW, typename TV, int METRIC, bool ACCUM>
+__global__ void __launch_bounds__(kThreads)
+hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* __restrict__ H,
+                   const TW* __restrict__ W, const TW* __restrict__ aux, float aux_scalar,
+                   float* __restrict__ score, double* __restrict__ partials, int64_t chunks,
+                   float beta, float one_minus_beta) {
+    double acc_s = 0.0, acc_s2 = 0.0;
+    const float eps = 1e-8f;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
+         c += (int64_t)gridDim.x * kThreads) {
+        const int64_t e = c * 8;
+        float w[8], h[8], s[8];
+        Vec8<TW>::load(W + e, w);
+        constexpr bool NEED_H = (METRIC == SF_METRIC_HESSIAN_OBD || METRIC == SF_METRIC_HESSIAN_RATIO ||
+                                 METRIC == SF_METRIC_HESSIAN) || ACCUM;
+        if (NEED_H) Vec8<float>::load(H + e, h);
+        if (ACCUM) {
+            float hv[8], sg[8];
+            Vec8<TW>::load(hvp + e, hv);
+            load_signs<TV>(v + e, sg);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                // diag_est = clamp(hvp*v, min=0) in the weight dtype; H.mul_(beta).add_(d, alpha=1-beta)
+                float d = fmaxf(Vec8<TW>::round(__fmul_rn(hv[i], sg[i])), 0.0f);
+                h[i] = __fmaf_rn(one_minus_beta, d, __fmul_rn(h[i], beta));
+            }
+            Vec8<float>::store(H + e, h);
+        }
+        if (METRIC == SF_METRIC_MOVEMENT) {
+            float g[8];
+            Vec8<TW>::load(aux + e, g);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                s[i] = Vec8<TW>::round(__fdiv_rn(fabsf(Vec8<TW>::round(__fmul_rn(w[i], g[i]))), aux_scalar));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                if (METRIC == SF_METRIC_HESSIAN_OBD) {
+                    float w2 = Vec8<TW>::round(__fmul_rn(w[i], w[i]));
+                    s[i] = __fmul_rn(__fadd_rn(h[i], eps), w2);
+                } else if (METRIC == SF_METRIC_HESSIAN_RATIO) {
+                    s[i] = __fdiv_rn(fabsf(w[i]), __fsqrt_rn(__fadd_rn(h[i], eps)));
+                } else if (METRIC == SF_METRIC_HESSIAN) {
+                    s[i] = h[i];
+                } else {
+                    s[i] = fabsf(w[i]);
+                }
+            }
+        }
+        Vec8<float>::store(score + e, s);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            acc_s += (double)s[i];
+            acc_s2 += (double)s[i] * (double)s[i];
+        }
+    }
+    __shared__ double red[2][kThreads / 32];
+    acc_s = warp_sum(acc_s);
+    acc_s2 = warp_sum(acc_s2);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { red[0][wid] = acc_s; red[1][wid] = acc_s2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double a = 0.0, b = 0.0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) { a += red[0][i]; b += red[1][i]; }
+        partials[2 * blockIdx.x] = a;
+        partials[2 * blockIdx.x + 1] = b;
+    }
+}
+
+// One block folds the per-block partial sums in a fixed order (deterministic) and writes
+// mean and population std + 1e-6 as fp32.
+__global__ void __launch_bounds__(kThreads)
+score_norm_finalize_kernel(const double* __restrict__ partials, int nblocks, double n,
+                           float* __restrict__ norm) {
+    __shared__ double red[2][kThreads];
+    double a = 0.0, b = 0.0;
+    for (int i = threadIdx.x; i < nblocks; i += kThreads) { a += partials[2 * i]; b += partials[2 * i + 1]; }
+    red[0][threadIdx.x] = a;
+    red[1][threadIdx.x] = b;
+    __syncthreads();
+    for (int s = kThreads / 2; s > 0; s >>= 1) {
+        if (threadIdx.x < s) {
+            red[0][threadIdx.x] += red[0][threadIdx.x + s];
+            red[1][threadIdx.x] += red[1][threadIdx.x + s];
+        }
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) {
+        double mean = red[0][0] / n;
+        double var = red[1][0] / n - mean * mean;
+        if (var < 0.0) var = 0.0;
+        norm[0] = (float)mean;
+        norm[1] = __fadd_rn((float)sqrt(var), 1e-6f);
+    }
+}
+
+template <typename TW, typename TV, bool ACCUM>
+static int launch_hutch_score(int metric, const void* hvp, const void* v, float* H, const void* W,
+                              const void* aux, float aux_scalar, float* score, double* scratch,
+                              int64_t chunks, float beta, int grid, cudaStream_t st) {
+    const float omb = (float)(1.0 - (double)beta);
+#define SF_LAUNCH_HS(M)                                                                          \
+    hutch_score_kernel<TW, TV, M, ACCUM><<<grid, kThreads, 0, st>>>(                            \
+        (const TW*)hvp, (const TV*)v, H, (const TW*)W, (const TW*)aux, aux_scalar, score, scratch, \
+        chunks, beta, omb)
+    switch (metric) {
+        case SF_METRIC_HESSIAN_OBD: SF_LAUNCH_HS(SF_METRIC_HESSIAN_OBD); break;
+        case SF_METRIC_HESSIAN_RATIO: SF_LAUNCH_HS(SF_METRIC_HESSIAN_RATIO); break;
+        case SF_METRIC_MAGNITUDE: SF_LAUNCH_HS(SF_METRIC_MAGNITUDE); break;
+        case SF_METRIC_HESSIAN: SF_LAUNCH_HS(SF_METRIC_HESSIAN); break;
+        case SF_METRIC_MOVEMENT: SF_LAUNCH_HS(SF_METRIC_MOVEMENT); break;
+        default: return fail(SF_ERR_BAD_ARG, "sf_hutch_score: unknown metric %d", metric);
+    }
+#undef SF_LAUNCH_HS
+    return SF_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// 2:4 soft-mask update + projection + masked weight + metadata + stats
+// ---------------------------------------------------------------------------------------
+struct MaskUpdateParams {
+    float inv_temp_den;  // T + 1e-8 (fp32)
+    float a, one_minus_a;
+    float pen;
+    int penalty_mode;
+    float beta_s, one_minus_beta_s;
+    float bin_lo, bin_hi;  // 1-d, 1+d
+    int binarize;
+    float hx, one_minus_hx;
+    int soft_only;  // hx >= 1 - 1e-6: effective mask = soft mask
+    int structured_exact;
+    int score_bf16;
+};
+
+__device__ __forceinline__ float sigmoidf_acc(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
+
+__device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
+    if (P.soft_only) return m;
+    return __fadd_rn(__fmul_rn(P.hx, m), kept ? P.one_minus_hx : 0.0f);
+}
+
+struct GroupStats {
+    float sum_m = 0.f, sum_m1m = 0.f, sum_top2 = 0.f, sum_bot2 = 0.f;
+    int flips = 0, lt_half = 0;
+};
+
+__device__ __forceinline__ void block_reduce_stats(const GroupStats& g, double* __restrict__ stats) {
+    __shared__ double red[6][kThreads / 32];
+    double v[6] = {(double)g.flips, (double)g.sum_m, (double)g.sum_m1m,
+                   (double)g.sum_top2, (double)g.sum_bot2, (double)g.lt_half};
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int k = 0; k < 6; ++k) {
+        v[k] = warp_sum(v[k]);
+        if (lane == 0) red[k][wid] = v[k];
+    }
+    __syncthreads();
+    if (threadIdx.x < 6) {
+        double a = 0.0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) a += red[threadIdx.x][i];
+        atomicAdd(&stats[threadIdx.x], a);
+    }
+}
+
+template <typename TW, bool EMIT_WM, bool EMIT_META>
+__global__ void __launch_bounds__(kThreads)
+mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict__ norm,
+                        float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm,
+                        uint8_t* __restrict__ meta, double* __restrict__ stats, int64_t chunks,
+                        MaskUpdateParams P) {
+    const float mu = norm[0], sigma = norm[1];
+    GroupStats gs;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
+         c += (int64_t)gridDim.x * kThreads) {
+        const int64_t e = c * 8;
+        float sc[8], m[8], w[8], out_w[8];
+        Vec8<float>::load(score + e, sc);
+        Vec8<float>::load(mask + e, m);
+        if (EMIT_WM) Vec8<TW>::load(W + e, w);
+        uint32_t meta_byte = 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            float s[4], G[4], mp[4], mn[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                s[i] = __fdiv_rn(__fsub_rn(sc[4 * g + i], mu), sigma);
+                if (P.score_bf16) s[i] = bf16_round(s[i]);
+                mp[i] = m[4 * g + i];
+            }
+            int r[4];
+            rank4(s, r);
+            float tau = s[0];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) if (r[i] == 1) tau = s[i];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float gi;
+                if (P.structured_exact) gi = r[i] < 2 ? 1.0f : 0.0f;
+                else {
+                    gi = sigmoidf_acc(__fdiv_rn(__fsub_rn(s[i], tau), P.inv_temp_den));
+                    if (P.score_bf16) gi = bf16_round(gi);
+                }
+                if (P.beta_s > 0.0f) {
+                    float t = r[i] < 2 ? P.beta_s : 0.0f;
+                    gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), t);
+                    if (P.score_bf16) gi = bf16_round(gi);
+                }
+                G[i] = gi;
+            }
+            if (P.pen != 0.0f) {
+                if (P.penalty_mode == SF_PENALTY_TOPN) {
+                    uint32_t kg = top2_keep(G);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float delta = __fsub_rn(mp[i], ((kg >> i) & 1u) ? 1.0f : 0.0f);
+                        G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, delta));
+                    }
+                } else if (P.penalty_mode == SF_PENALTY_MID) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float pg = __fsub_rn(1.0f, __fmul_rn(2.0f, mp[i]));
+                        G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, pg));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < 4; ++i) G[i] = fminf(fmaxf(G[i], 0.0f), 1.0f);
+            }
+            if (P.binarize) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    if (G[i] < 0.5f) G[i] = __fmul_rn(G[i], P.bin_lo);
+                    else if (G[i] > 0.5f) G[i] = __fmul_rn(G[i], P.bin_hi);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = __fmaf_rn(P.a, G[i], __fmul_rn(mp[i], P.one_minus_a));
+                mn[i] = fminf(fmaxf(v, 0.0f), 1.0f);
+                m[4 * g + i] = mn[i];
+            }
+            const uint32_t kp = top2_keep(mp);
+            int rn[4];
+            rank4(mn, rn);
+            uint32_t kn = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) kn |= (rn[i] < 2 ? 1u : 0u) << i;
+            gs.flips += __popc(kp ^ kn);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                gs.sum_m += mn[i];
+                gs.sum_m1m += mn[i] * (1.0f - mn[i]);
+                if (rn[i] < 2) gs.sum_top2 += mn[i]; else gs.sum_bot2 += mn[i];
+                gs.lt_half += mn[i] < 0.5f ? 1 : 0;
+                if (EMIT_WM) {
+                    float eff = Vec8<TW>::round(effective_mask_value(mn[i], (kn >> i) & 1u, P));
+                    out_w[4 * g + i] = __fmul_rn(w[4 * g + i], eff);
+                }
+            }
+            meta_byte |= nibble_of_keep(kn) << (4 * g);
+        }
+        Vec8<float>::store(mask + e, m);
+        if (EMIT_WM) Vec8<TW>::store(wm + e, out_w);
+        if (EMIT_META) meta[c] = (uint8_t)meta_byte;
+    }
+    block_reduce_stats(gs, stats);
+}
+
+// ---------------------------------------------------------------------------------------
+// hard projection (generic strides and tails)
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__device__ __forceinline__ float load_scalar(const T* p);
+template <>
+__device__ __forceinline__ float load_scalar<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float load_scalar<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T>
+__device__ __forceinline__ void store_scalar(T* p, float v);
+template <>
+__device__ __forceinline__ void store_scalar<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void store_scalar<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// One thread per 8 columns of one row. FAST: full chunks, 16-byte aligned rows.
+template <typename TI, typename TO, bool FAST>
+__global__ void __launch_bounds__(kThreads)
+project_nm24_kernel(const TI* __restrict__ soft, int64_t ld_soft, TO* __restrict__ hard,
+                    int64_t ld_hard, uint8_t* __restrict__ meta, int64_t rows, int64_t cols,
+                    int64_t chunks_per_row) {
+    const int64_t total = rows * chunks_per_row;
+    const int64_t full_cols = (cols / 4) * 4;
+    for (int64_t t = (int64_t)blockIdx.x * kThreads + threadIdx.x; t < total;
+         t += (int64_t)gridDim.x * kThreads) {
+        const int64_t row = t / chunks_per_row, ch = t - row * chunks_per_row;
+        const int64_t col0 = ch * 8;
+        float x[8], h[8];
+        if (FAST) {
+            Vec8<TI>::load(soft + row * ld_soft + col0, x);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                x[i] = (col0 + i < cols) ? load_scalar<TI>(soft + row * ld_soft + col0 + i) : 0.0f;
+        }
+        uint32_t mb = 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            float s[4] = {x[4 * g], x[4 * g + 1], x[4 * g + 2], x[4 * g + 3]};
+            const bool in_core = FAST || (col0 + 4 * g + 4 <= full_cols);
+            uint32_t k = in_core ? top2_keep(s) : 0xFu;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) h[4 * g + i] = ((k >> i) & 1u) ? 1.0f : 0.0f;
+            if (in_core) mb |= nibble_of_keep(k) << (4 * g);
+        }
+        if (hard != nullptr) {
+            if (FAST) {
+                Vec8<TO>::store(hard + row * ld_hard + col0, h);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    if (col0 + i < cols) store_scalar<TO>(hard + row * ld_hard + col0 + i, h[i]);
+            }
+        }
+        if (meta != nullptr) meta[row * chunks_per_row + ch] = (uint8_t)mb;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// effective masked weight (no mask update)
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void __launch_bounds__(kThreads)
+effective_weight_kernel(const TW* __restrict__ W, const float* __restrict__ mask, TW* __restrict__ wm,
+                        uint8_t* __restrict__ meta, int64_t chunks, MaskUpdateParams P, float scale) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
+         c += (int64_t)gridDim.x * kThreads) {
+        const int64_t e = c * 8;
+        float w[8], m[8], o[8];
+        Vec8<TW>::load(W + e, w);
+        Vec8<float>::load(mask + e, m);
+        uint32_t mb = 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            float s[4] = {m[4 * g], m[4 * g + 1], m[4 * g + 2], m[4 * g + 3]};
+            uint32_t k = top2_keep(s);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float eff = Vec8<TW>::round(effective_mask_value(s[i], (k >> i) & 1u, P));
+                float v = Vec8<TW>::round(__fmul_rn(w[4 * g + i], eff));
+                o[4 * g + i] = scale != 1.0f ? __fmul_rn(v, scale) : v;
+            }
+            mb |= nibble_of_keep(k) << (4 * g);
+        }
+        Vec8<TW>::store(wm + e, o);
+        if (meta != nullptr) meta[c] = (uint8_t)mb;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// mask-aware AdamW
+// ---------------------------------------------------------------------------------------
+struct AdamParams {
+    float c_wd;       // 1 - lr*wd
+    float decay;
+    float beta1, one_minus_beta1, beta2, one_minus_beta2;
+    float sqrt_bc2, eps, step_size, lr, l1;
+    int has_mask;
+};
+
+template <typename TW, bool EMIT_WM>
+__global__ void __launch_bounds__(kThreads)
+adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* __restrict__ mask,
+                    TW* __restrict__ m, TW* __restrict__ v, TW* __restrict__ wm, int64_t chunks,
+                    AdamParams A, MaskUpdateParams P) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
+         c += (int64_t)gridDim.x * kThreads) {
+        const int64_t e = c * 8;
+        float pw[8], gr[8], mk[8], em[8], ev[8], o[8];
+        Vec8<TW>::load(p + e, pw);
+        Vec8<TW>::load(g + e, gr);
+        Vec8<TW>::load(m + e, em);
+        Vec8<TW>::load(v + e, ev);
+        if (A.has_mask) Vec8<float>::load(mask + e, mk);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float p1 = Vec8<TW>::round(__fmul_rn(pw[i], A.c_wd));
+            float g1 = gr[i];
+            if (A.has_mask)
+                g1 = __fmaf_rn(A.decay, __fmul_rn(p1, __fsub_rn(1.0f, mk[i])), g1);
+            float m1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta1, g1, Vec8<TW>::round(__fmul_rn(em[i], A.beta1))));
+            float v1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta2, __fmul_rn(g1, g1),
+                                                 Vec8<TW>::round(__fmul_rn(ev[i], A.beta2))));
+            float denom = Vec8<TW>::round(__fdiv_rn(Vec8<TW>::round(__fsqrt_rn(v1)), A.sqrt_bc2));
+            denom = Vec8<TW>::round(__fadd_rn(denom, A.eps));
+            float p2 = Vec8<TW>::round(__fsub_rn(p1, __fmul_rn(A.step_size, __fdiv_rn(m1, denom))));
+            if (A.l1 > 0.0f && A.has_mask) {
+                float sgn = (p2 > 0.0f) ? 1.0f : ((p2 < 0.0f) ? -1.0f : 0.0f);
+                float term = Vec8<TW>::round(__fdiv_rn(Vec8<TW>::round(__fmul_rn(A.l1, sgn)), denom));
+                p2 = Vec8<TW>::round(__fsub_rn(p2, __fmul_rn(A.lr, term)));
+            }
+            pw[i] = p2; em[i] = m1; ev[i] = v1;
+        }
+        Vec8<TW>::store(p + e, pw);
+        Vec8<TW>::store(m + e, em);
+        Vec8<TW>::store(v + e, ev);
+        if (EMIT_WM) {
+#pragma unroll
+            for (int g2 = 0; g2 < 2; ++g2) {
+                float s[4] = {mk[4 * g2], mk[4 * g2 + 1], mk[4 * g2 + 2], mk[4 * g2 + 3]};
+                uint32_t k = P.soft_only ? 0u : top2_keep(s);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float eff = Vec8<TW>::round(effective_mask_value(s[i], (k >> i) & 1u, P));
+                    o[4 * g2 + i] = __fmul_rn(pw[4 * g2 + i], eff);
+                }
+            }
+            Vec8<TW>::store(wm + e, o);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// mask statistics
+// ---------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+mask_stats_kernel(const float* __restrict__ mask, double* __restrict__ stats, int64_t groups) {
+    GroupStats gs;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < groups;
+         c += (int64_t)gridDim.x * kThreads) {
+        uint4 a = ld_stream16(mask + c * 4);
+        float s[4] = {__uint_as_float(a.x), __uint_as_float(a.y), __uint_as_float(a.z), __uint_as_float(a.w)};
+        int r[4];
+        rank4(s, r);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            gs.sum_m += s[i];
+            gs.sum_m1m += s[i] * (1.0f - s[i]);
+            if (r[i] < 2) gs.sum_top2 += s[i]; else gs.sum_bot2 += s[i];
+            gs.lt_half += s[i] < 0.5f ? 1 : 0;
+        }
+    }
+    block_reduce_stats(gs, stats);
+}
+
+// ---------------------------------------------------------------------------------------
+// bias gradient: column sums of dy[T, out]
+// ---------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+bias_grad_kernel(const T* __restrict__ dy, float* __restrict__ db, int64_t rows, int64_t cols,
+                 int64_t rows_per_block) {
+    // block = 32 columns x 8 row lanes
+    const int cx = threadIdx.x & 31, ry = threadIdx.x >> 5;
+    const int64_t col = (int64_t)blockIdx.x * 32 + cx;
+    const int64_t r0 = (int64_t)blockIdx.y * rows_per_block;
+    int64_t r1 = r0 + rows_per_block;
+    if (r1 > rows) r1 = rows;
+    float acc = 0.0f;
+    if (col < cols)
+        for (int64_t r = r0 + ry; r < r1; r += 8) acc += load_scalar<T>(dy + r * cols + col);
+    __shared__ float red[8][33];
+    red[ry][cx] = acc;
+    __syncthreads();
+    if (ry == 0 && col < cols) {
+        float s = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) s += red[i][cx];
+        atomicAdd(&db[col], s);
+    }
+}
+
+}  // namespace sf
+
+using namespace sf;
+
+extern "C" {
+
+int sf_version(void) { return 100; }
+
+const char* sf_last_error_string(void) { return sf::last_error_buffer(); }
+
+int64_t sf_hutch_score_scratch_doubles(int64_t n) {
+    (void)n;
+    return 2 * (int64_t)kMaxPartialBlocks;
+}
+
+int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const void* W, int w_dtype,
+                   const void* aux, float aux_scalar, float* score, float* norm, double* scratch,
+                   int64_t n, float beta, int metric, void* stream) {
+    SF_CHECK_ARG(W && score && norm && scratch, "sf_hutch_score: W, score, norm and scratch must be non-null");
+    SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_hutch_score: n=%lld must be a positive multiple of 8", (long long)n);
+    SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_hutch_score: w_dtype must be SF_F32 or SF_BF16");
+    const bool accum = hvp != nullptr;
+    if (accum) {
+        SF_CHECK_ARG(v != nullptr && H != nullptr, "sf_hutch_score: hvp given without v or H");
+        SF_CHECK_ARG(v_dtype == SF_I8 || v_dtype == w_dtype, "sf_hutch_score: v_dtype must be SF_I8 or w_dtype");
+    }
+    const bool need_h = metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO ||
+                        metric == SF_METRIC_HESSIAN;
+    SF_CHECK_ARG(!need_h || H != nullptr, "sf_hutch_score: metric %d needs H", metric);
+    SF_CHECK_ARG(metric != SF_METRIC_MOVEMENT || aux != nullptr, "sf_hutch_score: movement metric needs aux=grad_ema");
+    if (!(aligned16(W) && aligned16(score) && aligned16(H) && aligned16(hvp) && aligned16(aux)) ||
+        (reinterpret_cast<uintptr_t>(v) & 7u))
+        return fail(SF_ERR_ALIGNMENT, "sf_hutch_score: buffers must be 16-byte aligned (v: 8-byte)");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t chunks = n / 8;
+    int grid = grid_for(chunks, 8);
+    if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;
+    if (metric == SF_METRIC_MOVEMENT && aux_scalar < 1e-8f) aux_scalar = 1e-8f;
+    int rc = SF_OK;
+#define SF_HS(TW, TV, ACC) \
+    rc = launch_hutch_score<TW, TV, ACC>(metric, hvp, v, H, W, aux, aux_scalar, score, scratch, chunks, beta, grid, st)
+    if (w_dtype == SF_F32) {
+        if (!accum) SF_HS(float, float, false);
+        else if (v_dtype == SF_I8) SF_HS(float, int8_t, true);
+        else SF_HS(float, float, true);
+    } else {
+        if (!accum) SF_HS(__nv_bfloat16, __nv_bfloat16, false);
+        else if (v_dtype == SF_I8) SF_HS(__nv_bfloat16, int8_t, true);
+        else SF_HS(__nv_bfloat16, __nv_bfloat16, true);
+    }
+#undef SF_HS
+    if (rc != SF_OK) return rc;
+    score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+static MaskUpdateParams make_mask_params(float temperature, float mask_lr, float pen, int penalty_mode,
+                                         float beta_s, float binarize_decay, float hx, int structured_exact,
+                                         int score_bf16) {
+    MaskUpdateParams P;
+    P.inv_temp_den = temperature + 1e-8f;
+    P.a = mask_lr;
+    P.one_minus_a = (float)(1.0 - (double)mask_lr);
+    P.pen = pen;
+    P.penalty_mode = penalty_mode;
+    P.beta_s = beta_s;
+    P.one_minus_beta_s = (float)(1.0 - (double)beta_s);
+    P.bin_lo = (float)(1.0 - (double)binarize_decay);
+    P.bin_hi = (float)(1.0 + (double)binarize_decay);
+    P.binarize = binarize_decay != 0.0f;
+    P.hx = hx;
+    P.one_minus_hx = (float)(1.0 - (double)hx);
+    P.soft_only = hx >= 1.0f - 1e-6f;
+    P.structured_exact = structured_exact;
+    P.score_bf16 = score_bf16;
+    return P;
+}
+
+int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W, int w_dtype,
+                        void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
+                        float temperature, float mask_lr, float pen, int penalty_mode, float beta_s,
+                        float binarize_decay, float hx, int structured_exact, int score_bf16,
+                        void* stream) {
+    SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm24: score, norm, mask, stats must be non-null");
+    SF_CHECK_ARG(rows > 0 && cols > 0, "sf_mask_update_nm24: rows=%lld cols=%lld must be positive",
+                 (long long)rows, (long long)cols);
+    SF_CHECK_ARG(cols % 8 == 0, "sf_mask_update_nm24: cols=%lld must be a multiple of 8 (2:4 groups, packed metadata)",
+                 (long long)cols);
+    SF_CHECK_ARG(penalty_mode >= SF_PENALTY_NONE && penalty_mode <= SF_PENALTY_MID,
+                 "sf_mask_update_nm24: unknown penalty_mode %d", penalty_mode);
+    SF_CHECK_ARG((wm == nullptr) || (W != nullptr), "sf_mask_update_nm24: wm requested without W");
+    SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_mask_update_nm24: w_dtype must be SF_F32 or SF_BF16");
+    if (!(aligned16(score) && aligned16(mask) && aligned16(W) && aligned16(wm)))
+        return fail(SF_ERR_ALIGNMENT, "sf_mask_update_nm24: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    MaskUpdateParams P = make_mask_params(temperature, mask_lr, pen, penalty_mode, beta_s, binarize_decay,
+                                          hx, structured_exact, score_bf16);
+    const int64_t chunks = rows * cols / 8;
+    const int grid = grid_for(chunks, 8);
+    SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
+#define SF_MU(TW, EW, EM)                                                             \
+    mask_update_nm24_kernel<TW, EW, EM><<<grid, kThreads, 0, st>>>(                   \
+        score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P)
+#define SF_MU_T(TW)                                       \
+    do {                                                  \
+        if (wm && meta) SF_MU(TW, true, true);            \
+        else if (wm) SF_MU(TW, true, false);              \
+        else if (meta) SF_MU(TW, false, true);            \
+        else SF_MU(TW, false, false);                     \
+    } while (0)
+    if (w_dtype == SF_F32) SF_MU_T(float); else SF_MU_T(__nv_bfloat16);
+#undef SF_MU_T
+#undef SF_MU
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_project_nm24(const void* soft, int in_dtype, int64_t ld_soft, void* hard, int out_dtype,
+                    int64_t ld_hard, uint8_t* meta, int64_t rows, int64_t cols, void* stream) {
+    SF_CHECK_ARG(soft != nullptr, "sf_project_nm24: soft must be non-null");
+    SF_CHECK_ARG(hard != nullptr || meta != nullptr, "sf_project_nm24: nothing to write (hard and meta both null)");
+    SF_CHECK_ARG(rows >= 0 && cols >= 0, "sf_project_nm24: negative shape");
+    SF_CHECK_ARG(ld_soft >= cols && (hard == nullptr || ld_hard >= cols), "sf_project_nm24: row stride smaller than cols");
+    SF_CHECK_ARG(in_dtype == SF_F32 || in_dtype == SF_BF16, "sf_project_nm24: in_dtype must be SF_F32 or SF_BF16");
+    SF_CHECK_ARG(hard == nullptr || out_dtype == SF_F32 || out_dtype == SF_BF16,
+                 "sf_project_nm24: out_dtype must be SF_F32 or SF_BF16");
+    if (rows == 0 || cols == 0) return SF_OK;
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t cpr = (cols + 7) / 8;
+    const bool fast = (cols % 8 == 0) && (ld_soft % 8 == 0) && aligned16(soft) &&
+                      (hard == nullptr || ((ld_hard % 8 == 0) && aligned16(hard)));
+    const int grid = grid_for(rows * cpr, 8);
+#define SF_PJ(TI, TO, F) \
+    project_nm24_kernel<TI, TO, F><<<grid, kThreads, 0, st>>>((const TI*)soft, ld_soft, (TO*)hard, ld_hard, meta, rows, cols, cpr)
+#define SF_PJ_F(TI, TO) do { if (fast) SF_PJ(TI, TO, true); else SF_PJ(TI, TO, false); } while (0)
+    const int od = hard ? out_dtype : SF_F32;
+    if (in_dtype == SF_F32 && od == SF_F32) SF_PJ_F(float, float);
+    else if (in_dtype == SF_F32) SF_PJ_F(float, __nv_bfloat16);
+    else if (od == SF_F32) SF_PJ_F(__nv_bfloat16, float);
+    else SF_PJ_F(__nv_bfloat16, __nv_bfloat16);
+#undef SF_PJ_F
+#undef SF_PJ
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm, uint8_t* meta,
+                        int64_t rows, int64_t cols, float hx, int finalized, float scale, void* stream) {
+    SF_CHECK_ARG(W && mask && wm, "sf_effective_weight: W, mask, wm must be non-null");
+    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0, "sf_effective_weight: cols=%lld must be a positive multiple of 8",
+                 (long long)cols);
+    SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_effective_weight: w_dtype must be SF_F32 or SF_BF16");
+    if (!(aligned16(W) && aligned16(mask) && aligned16(wm)))
+        return fail(SF_ERR_ALIGNMENT, "sf_effective_weight: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    MaskUpdateParams P = make_mask_params(1.0f, 0.0f, 0.0f, 0, 0.0f, 0.0f, finalized ? 1.0f : hx, 0, 0);
+    const int64_t chunks = rows * cols / 8;
+    const int grid = grid_for(chunks, 8);
+    if (w_dtype == SF_F32)
+        effective_weight_kernel<float><<<grid, kThreads, 0, st>>>((const float*)W, mask, (float*)wm, meta, chunks, P, scale);
+    else
+        effective_weight_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)W, mask,
+                                                                          (__nv_bfloat16*)wm, meta, chunks, P, scale);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
+                    float lr, float beta1, float beta2, float eps, float weight_decay, float decay,
+                    float bc1, float bc2, float adaptive_l1, void* wm, float hx, int64_t cols,
+                    void* stream) {
+    SF_CHECK_ARG(p && g && m && v, "sf_adamw_masked: p, g, m, v must be non-null");
+    SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_adamw_masked: n=%lld must be a positive multiple of 8", (long long)n);
+    SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_adamw_masked: w_dtype must be SF_F32 or SF_BF16");
+    SF_CHECK_ARG(bc1 > 0.0f && bc2 > 0.0f, "sf_adamw_masked: bias corrections must be positive (step >= 1)");
+    if (wm != nullptr) {
+        SF_CHECK_ARG(mask != nullptr, "sf_adamw_masked: wm requested without mask");
+        SF_CHECK_ARG(cols > 0 && cols % 8 == 0 && n % cols == 0,
+                     "sf_adamw_masked: wm needs cols=%lld a multiple of 8 dividing n", (long long)cols);
+    }
+    if (!(aligned16(p) && aligned16(g) && aligned16(m) && aligned16(v) && aligned16(mask) && aligned16(wm)))
+        return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    AdamParams A;
+    A.c_wd = (float)(1.0 - (double)lr * (double)weight_decay);
+    A.decay = decay;
+    A.beta1 = beta1; A.one_minus_beta1 = (float)(1.0 - (double)beta1);
+    A.beta2 = beta2; A.one_minus_beta2 = (float)(1.0 - (double)beta2);
+    A.sqrt_bc2 = (float)sqrt((double)bc2);
+    A.eps = eps;
+    A.step_size = (float)((double)lr / (double)bc1);
+    A.lr = lr;
+    A.l1 = adaptive_l1;
+    A.has_mask = mask != nullptr;
+    MaskUpdateParams P = make_mask_params(1.0f, 0.0f, 0.0f, 0, 0.0f, 0.0f, hx, 0, 0);
+    const int64_t chunks = n / 8;
+    const int grid = grid_for(chunks, 8);
+#define SF_AD(TW, EW) \
+    adamw_masked_kernel<TW, EW><<<grid, kThreads, 0, st>>>((TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P)
+    if (w_dtype == SF_F32) { if (wm) SF_AD(float, true); else SF_AD(float, false); }
+    else { if (wm) SF_AD(__nv_bfloat16, true); else SF_AD(__nv_bfloat16, false); }
+#undef SF_AD
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, void* stream) {
+    SF_CHECK_ARG(mask && stats, "sf_mask_stats: mask and stats must be non-null");
+    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 4 == 0, "sf_mask_stats: cols=%lld must be a positive multiple of 4",
+                 (long long)cols);
+    if (!aligned16(mask)) return fail(SF_ERR_ALIGNMENT, "sf_mask_stats: mask must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
+    const int64_t groups = rows * cols / 4;
+    mask_stats_kernel<<<grid_for(groups, 8), kThreads, 0, st>>>(mask, stats, groups);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t out, void* stream) {
+    SF_CHECK_ARG(dy && db, "sf_bias_grad: dy and db must be non-null");
+    SF_CHECK_ARG(T > 0 && out > 0, "sf_bias_grad: T and out must be positive");
+    SF_CHECK_ARG(dtype == SF_F32 || dtype == SF_BF16, "sf_bias_grad: dtype must be SF_F32 or SF_BF16");
+    cudaStream_t st = (cudaStream_t)stream;
+    SF_CHECK_CUDA(cudaMemsetAsync(db, 0, out * sizeof(float), st));
+    const int64_t col_blocks = (out + 31) / 32;
+    int64_t row_blocks = ((int64_t)sm_count() * 8 + col_blocks - 1) / col_blocks;
+    if (row_blocks < 1) row_blocks = 1;
+    if (row_blocks > (T + 7) / 8) row_blocks = (T + 7) / 8;
+    const int64_t rpb = (T + row_blocks - 1) / row_blocks;
+    dim3 grid((unsigned)col_blocks, (unsigned)row_blocks);
+    if (dtype == SF_F32) bias_grad_kernel<float><<<grid, kThreads, 0, st>>>((const float*)dy, db, T, out, rpb);
+    else bias_grad_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)dy, db, T, out, rpb);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,402 @@
+// Masked dense GEMMs of SparseLinear on the 5th-generation tensor cores.
+//
+// One persistent, warp-specialised kernel computes D[M,N] = A[M,K] . B[N,K]^T in bf16 with
+// fp32 accumulation in tensor memory (TMEM). Each operand is either K-major (K contiguous
+// in memory) or MN-major (the M / N index contiguous), selected by template parameters, so
+// the three products of the layer run without any transposed copy:
+//   forward : y  = x  . wm^T   A = x  [T,in]   K-major,   B = wm [out,in]  K-major
+//   dgrad   : dx = dy . wm     A = dy [T,out]  K-major,   B = wm [out,in]  MN-major (N = in)
+//   wgrad   : dw = dy^T . x    A = dy [T,out]  MN-major,  B = x  [T,in]    MN-major
+//
+// CTA = 6 warps: warp 0 issues TMA loads (128-byte swizzled tiles into a 4-stage ring),
+// warp 1 issues tcgen05.mma (128 x 256 x 16 per instruction, four per 64-deep stage) and
+// owns the TMEM allocation (2 accumulators x 256 columns), warps 2-5 drain an accumulator
+// with tcgen05.ld, convert to bf16 and store, while the MMA warp already fills the other
+// accumulator. Tiles are handed out round-robin to min(#tiles, #SMs) CTAs.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets status[0] and the CTA leaves
+// through the common teardown (TMEM is always released).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace sf {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int MN_BOX_BYTES = 64 * BK * 2;  // one 64(MN) x 64(K) box of an MN-major operand
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+
+enum { WAIT_PRODUCER = 1, WAIT_MMA_FULL = 2, WAIT_MMA_TMEM = 3, WAIT_EPILOGUE = 4 };
+
+struct GemmSmemTail {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int A_MN, int B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                         __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
+                         float alpha, int M, int N, int K, int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    GemmSmemTail* tail = reinterpret_cast<GemmSmemTail*>(base_ptr + STAGES * STAGE_BYTES);
+    volatile int* abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[a]), 4);
+        }
+        tail->abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ------------------------------ TMA producer ------------------------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, WAIT_PRODUCER);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = ptx::smem_u32(&tail->full[stage]);
+                    const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+                    const int k0 = kb * BK;
+                    ptx::mbar_arrive_expect_tx(bar, STAGE_BYTES);
+                    if (A_MN) {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) ptx::tma_load_2d(sa + j * MN_BOX_BYTES, &tmA, bar, m0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d(sa, &tmA, bar, k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < BN / 64; ++j) ptx::tma_load_2d(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d(sb, &tmB, bar, k0, n0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) {
+            // Give copies that are still in flight time to land before shared memory is released.
+            for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        }
+    } else if (warp == 1) {
+        // ------------------------------ MMA issuer ------------------------------
+        constexpr uint32_t idesc = ptx::make_idesc_bf16(BM, BN, A_MN, B_MN, 0);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, WAIT_MMA_TMEM);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, WAIT_MMA_FULL);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        // K-major: 16 elements = 32 bytes inside the 128-byte swizzled row.
+                        // MN-major: 16 K-rows of 128 bytes.
+                        const uint64_t adesc = A_MN ? ptx::make_smem_desc(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024, 2)
+                                                    : ptx::make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
+                        const uint64_t bdesc = B_MN ? ptx::make_smem_desc(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024, 2)
+                                                    : ptx::make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
+                        ptx::mma_f16_ss(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::mma_commit(ptx::smem_u32(&tail->empty[stage]));
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) break;
+            if (lane == 0) ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[acc]));
+            __syncwarp();
+        }
+    } else {
+        // ------------------------------ epilogue ------------------------------
+        const int q = warp & 3;  // TMEM lanes [32q, 32q+32) belong to warps with warp % 4 == q
+        bool ok = true;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, WAIT_EPILOGUE);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
+            const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                ptx::tmem_ld_wait();
+                if (row < M) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int col = n0 + c * 32 + j * 8;
+                        if (col < N) {
+                            uint32_t pk[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                float v0 = __uint_as_float(r[j * 8 + 2 * i]) * alpha;
+                                float v1 = __uint_as_float(r[j * 8 + 2 * i + 1]) * alpha;
+                                if (bias != nullptr) {
+                                    v0 += __bfloat162float(bias[col + 2 * i]);
+                                    v1 += __bfloat162float(bias[col + 2 * i + 1]);
+                                }
+                                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+                            }
+                            *reinterpret_cast<uint4*>(drow + c * 32 + j * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[acc]));
+        }
+    }
+
+    // ------------------------------ teardown ------------------------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// fp32 FMA GEMM for the fp32 parity cases: C[m,n] = alpha * sum_k A(m,k) B(n,k) (+ bias[n]).
+// Operands are addressed through element strides, so one kernel covers the three products.
+// ---------------------------------------------------------------------------------------
+constexpr int FT = 64, FK = 16;
+
+__global__ void __launch_bounds__(256)
+gemm_f32_fma_kernel(const float* __restrict__ A, int64_t sAm, int64_t sAk, const float* __restrict__ B,
+                    int64_t sBn, int64_t sBk, float* __restrict__ C, int64_t ldC, const float* __restrict__ bias,
+                    float alpha, int M, int N, int K) {
+    __shared__ float As[FK][FT + 1];
+    __shared__ float Bs[FK][FT + 1];
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    const int m0 = blockIdx.y * FT, n0 = blockIdx.x * FT;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += FK) {
+        for (int i = threadIdx.x; i < FT * FK; i += 256) {
+            // Pick the index order that walks the contiguous dimension of each operand.
+            int ma, ka, nb, kb;
+            if (sAk == 1) { ka = i % FK; ma = i / FK; } else { ma = i % FT; ka = i / FT; }
+            if (sBk == 1) { kb = i % FK; nb = i / FK; } else { nb = i % FT; kb = i / FT; }
+            As[ka][ma] = (m0 + ma < M && k0 + ka < K) ? A[(int64_t)(m0 + ma) * sAm + (int64_t)(k0 + ka) * sAk] : 0.0f;
+            Bs[kb][nb] = (n0 + nb < N && k0 + kb < K) ? B[(int64_t)(n0 + nb) * sBn + (int64_t)(k0 + kb) * sBk] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < FK; ++k) {
+            float a[4], b[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) { a[i] = As[k][ty * 4 + i]; b[i] = Bs[k][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx * 4 + j;
+            if (n < N) C[(int64_t)m * ldC + n] = acc[i][j] * alpha + (bias ? bias[n] : 0.0f);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Tensor map over a row-major bf16 matrix [outer, inner] with a 128-byte-swizzled box of
+// 64 inner elements x box_outer rows.
+int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t ld,
+                         int box_outer) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return SF_OK;
+}
+
+// D[M,N] = alpha * A . B^T (+bias). a_mn / b_mn: operand stored with its M / N index contiguous
+// (as [K, M] / [K, N] row-major with leading dimension lda / ldb), else as [M, K] / [N, K].
+template <int A_MN, int B_MN>
+static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldD,
+                       const void* bias, float alpha, int64_t M, int64_t N, int64_t K, int32_t* status,
+                       cudaStream_t st) {
+    CUtensorMap tmA, tmB;
+    int rc;
+    if (A_MN) rc = make_bf16_tensor_map(&tmA, A, M, K, lda, 64);
+    else rc = make_bf16_tensor_map(&tmA, A, K, M, lda, BM);
+    if (rc) return rc;
+    if (B_MN) rc = make_bf16_tensor_map(&tmB, B, N, K, ldb, 64);
+    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, BN);
+    if (rc) return rc;
+    auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        SF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
+        configured_dev = dev;
+    }
+    const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD, (const __nv_bfloat16*)bias,
+                                                      alpha, (int)M, (int)N, (int)K, status);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+static int launch_f32(const float* A, int64_t sAm, int64_t sAk, const float* B, int64_t sBn, int64_t sBk, float* C,
+                      int64_t ldC, const float* bias, float alpha, int64_t M, int64_t N, int64_t K,
+                      cudaStream_t st) {
+    dim3 grid((unsigned)((N + FT - 1) / FT), (unsigned)((M + FT - 1) / FT));
+    gemm_f32_fma_kernel<<<grid, 256, 0, st>>>(A, sAm, sAk, B, sBn, sBk, C, ldC, bias, alpha, (int)M, (int)N, (int)K);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+static int check_gemm_args(const char* who, const void* a, const void* b, const void* d, int64_t T, int64_t in,
+                           int64_t out, int dtype) {
+    if (!a || !b || !d) return fail(SF_ERR_BAD_ARG, "%s: operand pointers must be non-null", who);
+    if (T <= 0 || in <= 0 || out <= 0) return fail(SF_ERR_BAD_ARG, "%s: T, in, out must be positive", who);
+    if (dtype != SF_F32 && dtype != SF_BF16) return fail(SF_ERR_BAD_ARG, "%s: dtype must be SF_F32 or SF_BF16", who);
+    if (T > 0x7fffffff || in > 0x7fffffff || out > 0x7fffffff)
+        return fail(SF_ERR_UNSUPPORTED, "%s: dimension beyond 2^31-1", who);
+    if (dtype == SF_BF16) {
+        if ((T % 8) || (in % 8) || (out % 8))
+            return fail(SF_ERR_UNSUPPORTED, "%s: bf16 path needs T, in, out multiples of 8 (16-byte rows), got %lld %lld %lld",
+                        who, (long long)T, (long long)in, (long long)out);
+        if (!aligned16(a) || !aligned16(b) || !aligned16(d))
+            return fail(SF_ERR_ALIGNMENT, "%s: operands must be 16-byte aligned", who);
+    }
+    return SF_OK;
+}
+
+}  // namespace sf
+
+using namespace sf;
+
+extern "C" {
+
+int sf_masked_gemm_fwd(const void* x, const void* wm, const void* bias, void* y, int64_t T, int64_t in, int64_t out,
+                       float alpha, int dtype, int32_t* status, void* stream) {
+    int rc = check_gemm_args("sf_masked_gemm_fwd", x, wm, y, T, in, out, dtype);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (dtype == SF_F32)
+        return launch_f32((const float*)x, in, 1, (const float*)wm, in, 1, (float*)y, out, (const float*)bias, alpha, T, out, in, st);
+    return launch_bf16<0, 0>(x, in, wm, in, y, out, bias, alpha, T, out, in, status, st);
+}
+
+int sf_masked_gemm_dgrad(const void* dy, const void* wm, void* dx, int64_t T, int64_t in, int64_t out, int dtype,
+                         int32_t* status, void* stream) {
+    int rc = check_gemm_args("sf_masked_gemm_dgrad", dy, wm, dx, T, in, out, dtype);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // dx[t, i] = sum_o dy[t, o] wm[o, i]: B(n = i, k = o) = wm[o*in + i]
+    if (dtype == SF_F32)
+        return launch_f32((const float*)dy, out, 1, (const float*)wm, 1, in, (float*)dx, in, nullptr, 1.0f, T, in, out, st);
+    return launch_bf16<0, 1>(dy, out, wm, in, dx, in, nullptr, 1.0f, T, in, out, status, st);
+}
+
+int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int64_t in, int64_t out, int dtype,
+                         int32_t* status, void* stream) {
+    int rc = check_gemm_args("sf_masked_gemm_wgrad", dy, x, dw, T, in, out, dtype);
+    if (rc) return rc;
+    cudaStream_t st = (cudaStream_t)stream;
+    // dw[o, i] = sum_t dy[t, o] x[t, i]: A(m = o, k = t) = dy[t*out + o], B(n = i, k = t) = x[t*in + i]
+    if (dtype == SF_F32)
+        return launch_f32((const float*)dy, 1, out, (const float*)x, 1, in, (float*)dw, in, nullptr, 1.0f, out, in, T, st);
+    return launch_bf16<1, 1>(dy, out, x, in, dw, in, nullptr, 1.0f, out, in, T, status, st);
+}
+
+}  // extern "C"

@@ -1,0 +1,190 @@
+"""Tensor-level wrappers around the C ABI: each function validates its torch tensors, takes
+their device pointers and enqueues one library call on the current CUDA stream.
+
+torch is used here for device memory and streams only; the arithmetic is in the library.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import SF_BF16, SF_F32, SF_I8, check, lib
+
+_DT = {torch.float32: SF_F32, torch.bfloat16: SF_BF16, torch.int8: SF_I8}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise TypeError(f"sparseforge_b200: unsupported dtype {t.dtype} (float32 / bfloat16 only)") from None
+
+
+def _p(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _cuda(*ts: Optional[torch.Tensor]) -> None:
+    for t in ts:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("sparseforge_b200: tensors must live on a CUDA device (there is no CPU path)")
+        if not t.is_contiguous():
+            raise RuntimeError("sparseforge_b200: tensors must be contiguous")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def hutch_score_scratch(device) -> torch.Tensor:
+    return torch.empty(int(lib().sf_hutch_score_scratch_doubles(0)), dtype=torch.float64, device=device)
+
+
+def hutch_score(W, H, score, norm, scratch, *, hvp=None, v=None, aux=None, aux_scalar=1.0, beta=0.99,
+                metric="hessian_obd") -> None:
+    """H <- beta H + (1-beta) max(hvp*v, 0) (when hvp is given); score <- metric(W, H); norm <- (mean, std+1e-6)."""
+    _cuda(W, H, score, norm, scratch, hvp, v, aux)
+    if score.dtype != torch.float32 or norm.dtype != torch.float32 or (H is not None and H.dtype != torch.float32):
+        raise TypeError("hutch_score: H, score and norm must be float32")
+    if hvp is not None and (hvp.dtype != W.dtype or hvp.numel() != W.numel()):
+        raise TypeError("hutch_score: hvp must match W in dtype and size")
+    if v is not None and v.dtype not in (torch.int8, W.dtype):
+        raise TypeError("hutch_score: v must be int8 signs or have W's dtype")
+    check(lib().sf_hutch_score(_p(hvp), _p(v), _dt(v) if v is not None else SF_I8, _p(H), _p(W), _dt(W), _p(aux),
+                               float(aux_scalar), _p(score), _p(norm), _p(scratch), W.numel(), float(beta),
+                               _lib.METRICS[metric], _stream()), "sf_hutch_score")
+
+
+def mask_update_nm24(score, norm, mask, stats, *, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
+                     pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
+                     structured_exact=False, score_bf16=False) -> None:
+    _cuda(score, norm, mask, stats, W, wm, meta)
+    if mask.dim() != 2:
+        raise ValueError("mask_update_nm24: mask must be 2-D [out, in]")
+    if mask.dtype != torch.float32 or score.dtype != torch.float32 or stats.dtype != torch.float64:
+        raise TypeError("mask_update_nm24: mask/score float32, stats float64")
+    if wm is not None and (W is None or wm.dtype != W.dtype):
+        raise TypeError("mask_update_nm24: wm needs W of the same dtype")
+    rows, cols = mask.shape
+    check(lib().sf_mask_update_nm24(_p(score), _p(norm), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
+                                    _p(wm), _p(meta), _p(stats), rows, cols, float(temperature), float(mask_lr),
+                                    float(pen), int(penalty_mode), float(beta_s), float(binarize_decay), float(hx),
+                                    int(bool(structured_exact)), int(bool(score_bf16)), _stream()),
+          "sf_mask_update_nm24")
+
+
+def project_nm24(soft, *, out_dtype=None, want_hard=True, want_meta=False):
+    """Hard top-2-of-4 projection of a 2-D soft mask. Returns (hard or None, meta or None)."""
+    if soft.dim() != 2:
+        raise ValueError("project_nm24: soft must be 2-D")
+    if not soft.is_cuda:
+        raise RuntimeError("sparseforge_b200: tensors must live on a CUDA device (there is no CPU path)")
+    if soft.stride(1) != 1 and soft.numel() > 0:
+        soft = soft.contiguous()
+    rows, cols = soft.shape
+    out_dtype = out_dtype or soft.dtype
+    hard = torch.empty((rows, cols), dtype=out_dtype, device=soft.device) if want_hard else None
+    meta = torch.zeros((rows, (cols + 7) // 8), dtype=torch.uint8, device=soft.device) if want_meta else None
+    if rows == 0 or cols == 0:
+        return hard, meta
+    check(lib().sf_project_nm24(_p(soft), _dt(soft), soft.stride(0), _p(hard), _DT[out_dtype], cols, _p(meta),
+                                rows, cols, _stream()), "sf_project_nm24")
+    return hard, meta
+
+
+def effective_weight(W, mask, wm, *, meta=None, hx=1.0, finalized=False, scale=1.0) -> None:
+    _cuda(W, mask, wm, meta)
+    if mask.dtype != torch.float32:
+        raise TypeError("effective_weight: mask must be float32")
+    rows, cols = W.shape
+    check(lib().sf_effective_weight(_p(W), _dt(W), _p(mask), _p(wm), _p(meta), rows, cols, float(hx),
+                                    int(bool(finalized)), float(scale), _stream()), "sf_effective_weight")
+
+
+def adamw_masked(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, decay, step, adaptive_l1=0.0,
+                 wm=None, hx=1.0) -> None:
+    _cuda(p, g, m, v, mask, wm)
+    if not (p.dtype == g.dtype == m.dtype == v.dtype):
+        raise TypeError("adamw_masked: p, g, m, v must share a dtype")
+    if mask is not None and mask.dtype != torch.float32:
+        raise TypeError("adamw_masked: mask must be float32")
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    cols = p.shape[-1] if p.dim() >= 2 else 0
+    check(lib().sf_adamw_masked(_p(p), _p(g), _p(mask), _p(m), _p(v), _dt(p), p.numel(), float(lr), float(beta1),
+                                float(beta2), float(eps), float(weight_decay), float(decay), float(bc1), float(bc2),
+                                float(adaptive_l1), _p(wm), float(hx), cols, _stream()), "sf_adamw_masked")
+
+
+def mask_stats(mask, stats) -> None:
+    _cuda(mask, stats)
+    rows, cols = mask.shape
+    check(lib().sf_mask_stats(_p(mask), _p(stats), rows, cols, _stream()), "sf_mask_stats")
+
+
+def _gemm_dtype(*ts) -> int:
+    d = ts[0].dtype
+    for t in ts:
+        if t.dtype != d:
+            raise TypeError(f"masked GEMM: operand dtypes differ ({[str(x.dtype) for x in ts]})")
+    return _dt(ts[0])
+
+
+def gemm_fwd(x2d, wm, bias=None, alpha=1.0, status=None):
+    """y[T,out] = alpha * x2d[T,in] @ wm[out,in]^T (+ bias)."""
+    _cuda(x2d, wm, bias, status)
+    T, k = x2d.shape
+    out, k2 = wm.shape
+    if k != k2:
+        raise ValueError(f"gemm_fwd: x has {k} features, weight has {k2}")
+    dt = _gemm_dtype(x2d, wm) if bias is None else _gemm_dtype(x2d, wm, bias)
+    y = torch.empty((T, out), dtype=x2d.dtype, device=x2d.device)
+    if T == 0:
+        return y
+    check(lib().sf_masked_gemm_fwd(_p(x2d), _p(wm), _p(bias), _p(y), T, k, out, float(alpha), dt, _p(status),
+                                   _stream()), "sf_masked_gemm_fwd")
+    return y
+
+
+def gemm_dgrad(dy2d, wm, status=None):
+    """dx[T,in] = dy2d[T,out] @ wm[out,in]."""
+    _cuda(dy2d, wm, status)
+    T, out = dy2d.shape
+    out2, k = wm.shape
+    if out != out2:
+        raise ValueError(f"gemm_dgrad: dy has {out} features, weight has {out2} rows")
+    dt = _gemm_dtype(dy2d, wm)
+    dx = torch.empty((T, k), dtype=dy2d.dtype, device=dy2d.device)
+    if T == 0:
+        return dx
+    check(lib().sf_masked_gemm_dgrad(_p(dy2d), _p(wm), _p(dx), T, k, out, dt, _p(status), _stream()),
+          "sf_masked_gemm_dgrad")
+    return dx
+
+
+def gemm_wgrad(dy2d, x2d, status=None):
+    """dw[out,in] = dy2d[T,out]^T @ x2d[T,in]."""
+    _cuda(dy2d, x2d, status)
+    T, out = dy2d.shape
+    T2, k = x2d.shape
+    if T != T2:
+        raise ValueError(f"gemm_wgrad: dy has {T} rows, x has {T2}")
+    dt = _gemm_dtype(dy2d, x2d)
+    if T == 0:
+        return torch.zeros((out, k), dtype=dy2d.dtype, device=dy2d.device)
+    dw = torch.empty((out, k), dtype=dy2d.dtype, device=dy2d.device)
+    check(lib().sf_masked_gemm_wgrad(_p(dy2d), _p(x2d), _p(dw), T, k, out, dt, _p(status), _stream()),
+          "sf_masked_gemm_wgrad")
+    return dw
+
+
+def bias_grad(dy2d):
+    _cuda(dy2d)
+    T, out = dy2d.shape
+    db = torch.empty(out, dtype=torch.float32, device=dy2d.device)
+    check(lib().sf_bias_grad(_p(dy2d), _dt(dy2d), _p(db), T, out, _stream()), "sf_bias_grad")
+    return db

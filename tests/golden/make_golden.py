@@ -1,0 +1,266 @@
+"""Generates the golden fixtures in this directory by RUNNING THE REFERENCE ITSELF.
+
+Run where the SparseForge reference is available (it is imported, unmodified, from
+``$SPARSEFORGE_REFERENCE/legacy``, default ``/root/reference/legacy``):
+
+    WANDB_MODE=disabled python tests/golden/make_golden.py
+
+The reference runs on torch CPU with ``torch.topk`` replaced by a tie-stable version (equal
+values: lower index first), the tie rule this path is specified with; ``ties.npz`` also
+records how many 2:4 groups the stock ``torch.topk`` decides differently and how many groups
+hold an exact 2nd/3rd tie. Every fixture stores inputs, intermediates and outputs, so each
+stage can be replayed on its own. bf16 tensors are stored as raw uint16 bits under keys
+ending in ``__bf16``. Nothing here is needed at test time except the ``.npz`` files.
+"""
+from __future__ import annotations
+
+import collections
+import os
+import sys
+
+os.environ.setdefault("WANDB_MODE", "disabled")
+import numpy as np
+import torch
+
+REF = os.environ.get("SPARSEFORGE_REFERENCE", "/root/reference")
+sys.path.insert(0, os.path.join(REF, "legacy"))
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+_orig_topk = torch.topk
+_TopK = collections.namedtuple("topk", ["values", "indices"])
+
+
+def stable_topk(x, k, dim=-1, largest=True, sorted=True):  # noqa: A002
+    assert largest
+    s = torch.sort(x, dim=dim, descending=True, stable=True)
+    sl = [slice(None)] * x.dim()
+    sl[dim] = slice(0, k)
+    return _TopK(s.values[tuple(sl)], s.indices[tuple(sl)])
+
+
+torch.topk = stable_topk
+import adamw as ref_adamw  # noqa: E402
+import sparse_modeling as ref_sm  # noqa: E402
+import triton_block_sparse as ref_bs  # noqa: E402
+import utils as ref_utils  # noqa: E402
+
+
+def put(d, name, t):
+    if isinstance(t, torch.Tensor):
+        t = t.detach().cpu().contiguous().clone()
+        if t.dtype == torch.bfloat16:
+            d[name + "__bf16"] = t.view(torch.int16).numpy().view(np.uint16)
+        else:
+            d[name] = t.numpy()
+    else:
+        d[name] = np.asarray(t)
+
+
+def save(name, d):
+    d["torch_version"] = np.asarray(torch.__version__)
+    np.savez_compressed(os.path.join(HERE, name + ".npz"), **d)
+    print(name, {k: getattr(v, "shape", None) for k, v in d.items() if k != "torch_version"})
+
+
+def rademacher(shape, seed, dtype):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randint(0, 2, shape, generator=g, dtype=torch.int8).float() * 2 - 1).to(dtype)
+
+
+def make_layer(out_f, in_f, W, dtype, **cfg_kw):
+    cfg = ref_sm.SparseLinearConfig(**cfg_kw)
+    layer = ref_sm.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False)
+    layer = layer.to(dtype)
+    layer.weight.data.copy_(W.to(dtype))
+    layer.initialize()
+    # fp32 mask / Hessian next to (possibly bf16) weights, the dtype mix of the LLaMA-shaped runs
+    layer.mask.data = layer.mask.data.float()
+    layer.hessian_diag.data = layer.hessian_diag.data.float()
+    layer.sync_weight()
+    return layer
+
+
+def hutchinson_once(layer, X, dY, v, d, tag):
+    """One update_hessian_hutchinson call with an injected probe; records hvp and H."""
+    T = X.shape[0] * X.shape[1]
+
+    def loss_fn():
+        Y = layer(X)
+        return (torch.nn.functional.gelu(Y.float()) * dY.float()).sum() / T
+
+    # the same double backward the reference performs, only to record hvp
+    loss = loss_fn()
+    (g,) = torch.autograd.grad(loss, [layer.weight], create_graph=True, retain_graph=True)
+    (hvp,) = torch.autograd.grad((g * v).sum(), [layer.weight], retain_graph=False)
+    put(d, f"hvp_{tag}", hvp)
+    ref_utils._rademacher_like = lambda t: v.clone()
+    ref_utils.update_hessian_hutchinson(layer, loss_fn())
+    put(d, f"H_{tag}", layer.hessian_diag.data)
+
+
+def case_chain(name, out_f, in_f, batch, seq, dtype, steps, cfg_kw, lambda_mid=0.0, seed=0):
+    """Score -> mask update -> projection -> masked fwd/bwd -> AdamW, `steps` times."""
+    torch.manual_seed(seed)
+    W = torch.randn(out_f, in_f) * 0.02
+    X = torch.randn(batch, seq, in_f).to(dtype)
+    dY = torch.randn(batch, seq, out_f).to(dtype)
+    d = {}
+    put(d, "W0", W.to(dtype)); put(d, "X", X); put(d, "dY", dY)
+    layer = make_layer(out_f, in_f, W, dtype, **cfg_kw)
+    opt = ref_adamw.AdamW([layer.weight], lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    d["n_steps"] = np.asarray(steps)
+    d["lambda_mid"] = np.asarray(lambda_mid)
+    probe = 0
+    for t in range(steps):
+        Xr = X.clone().requires_grad_(True)
+        # forward / backward with the current mask and hardening state
+        put(d, f"s{t}_hx_fwd", float(layer.hardening_x))
+        put(d, f"s{t}_mask_fwd", layer.mask.data)
+        put(d, f"s{t}_W_fwd", layer.weight.data)
+        layer.weight.grad = None
+        Y = layer(Xr)
+        Y.backward(dY)
+        put(d, f"s{t}_Y", Y); put(d, f"s{t}_dX", Xr.grad); put(d, f"s{t}_dW", layer.weight.grad)
+        # Hutchinson probes (one per step; the first step takes four, as in the fp32 config)
+        for _ in range(4 if t == 0 else 1):
+            v = rademacher((out_f, in_f), 1 + probe, dtype)
+            put(d, f"v_{probe}", v.to(torch.int8))
+            hutchinson_once(layer, X, dY, v, d, str(probe))
+            probe += 1
+        d[f"s{t}_probes_end"] = np.asarray(probe)
+        # optimizer
+        opt.step(decay=2e-4)
+        st = opt.state[layer.weight]
+        put(d, f"s{t}_W_opt", layer.weight.data); put(d, f"s{t}_m", st["exp_avg"]); put(d, f"s{t}_v", st["exp_avg_sq"])
+        # mask update
+        put(d, f"s{t}_T", layer._temperature(t))
+        G = layer.compute_gate_target(t)
+        put(d, f"s{t}_G", G)
+        raw = (layer.hessian_diag.data + 1e-8) * (layer.weight.data * layer.weight.data)
+        put(d, f"s{t}_score_raw", raw)
+        ref_utils.calculate_model_mask(layer, step=t, lambda_mid=lambda_mid)
+        put(d, f"s{t}_mask", layer.mask.data)
+        put(d, f"s{t}_hx", float(layer.hardening_x))
+        put(d, f"s{t}_flips", int(layer.weight.flipped_mask))
+        put(d, f"s{t}_hard", layer._hard_mask_from_soft(layer.mask.data))
+        put(d, f"s{t}_mid_sum", float((layer.mask.data.double() * (1 - layer.mask.data.double())).sum()))
+    save(name, d)
+
+
+def case_penalty():
+    """update_mask with the penalty pulls, binarize push and beta mixing switched on."""
+    torch.manual_seed(7)
+    out_f, in_f = 40, 64
+    d = {}
+    variants = [
+        ("topn", dict(mask_penalty_mode="structured_topn"), 0.7, 0.0),
+        ("nm24", dict(mask_penalty_mode="nm_2_4", hard_mask_type="nm_2_4"), 0.4, 0.0),
+        ("mid", dict(mask_penalty_mode="mid"), 0.9, 0.0),
+        ("bin", dict(mask_penalty_mode="structured_topn", mask_binarize_decay=0.05), 0.3, 0.0),
+        ("beta", dict(mask_penalty_mode="mid", beta_structural_start=0, beta_structural_end=10), 0.0, 0.0),
+        ("exact", dict(structured_exact=True), 0.0, 0.0),
+        ("lowT", dict(temp_init=0.01, temp_min=0.01, mask_penalty_mode="structured_topn"), 0.5, 0.0),
+    ]
+    d["variants"] = np.asarray([v[0] for v in variants])
+    for tag, kw, lam, _ in variants:
+        W = torch.randn(out_f, in_f) * 0.02
+        layer = make_layer(out_f, in_f, W, torch.float32, mask_type="structured", mask_metric="hessian_obd",
+                           mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.2, mask_penalty_lr=0.15,
+                           mask_hardening_start=2, mask_hardening_duration=8, **kw)
+        layer.mask.data = torch.rand(out_f, in_f)
+        layer.hessian_diag.data = torch.rand(out_f, in_f) + 0.1
+        step = 4
+        put(d, f"{tag}_W", W); put(d, f"{tag}_H", layer.hessian_diag.data); put(d, f"{tag}_mask0", layer.mask.data)
+        put(d, f"{tag}_lambda", lam); put(d, f"{tag}_step", step)
+        put(d, f"{tag}_T", layer._temperature(step)); put(d, f"{tag}_beta_s", layer._beta_structural(step))
+        put(d, f"{tag}_G", layer.compute_gate_target(step))
+        layer.update_mask(step, lambda_mid=lam)
+        put(d, f"{tag}_mask1", layer.mask.data); put(d, f"{tag}_hx", float(layer.hardening_x))
+        put(d, f"{tag}_flips", int(layer.weight.flipped_mask))
+    save("penalty", d)
+
+
+def case_ties():
+    """Hard projection on inputs full of ties, plus the disagreement count of the stock topk."""
+    torch.manual_seed(11)
+    d = {}
+    cfg = dict(mask_type="structured", mask_metric="magnitude")
+    layer = make_layer(8, 16, torch.randn(8, 16), torch.float32, **cfg)
+    inputs = {
+        "ones": torch.ones(24, 32),
+        "bf16q": torch.rand(64, 128).to(torch.bfloat16).float(),
+        "coarse": (torch.randint(0, 4, (48, 64)).float() / 4.0),
+        "rand": torch.rand(64, 64),
+        "special": torch.tensor([[0.0, -0.0, 0.0, -0.0, 1.0, 1.0, 0.5, 1.0],
+                                 [0.5, 0.5, 0.5, 0.7, 2.0, 1.0, 1.0, 1.0]]),
+    }
+    d["names"] = np.asarray(list(inputs))
+    for k, soft in inputs.items():
+        put(d, f"{k}_soft", soft)
+        put(d, f"{k}_hard", layer._hard_mask_from_soft(soft))
+        torch.topk = _orig_topk
+        stock = layer._hard_mask_from_soft(soft)
+        torch.topk = stable_topk
+        g = soft.view(soft.shape[0], -1, 4)
+        srt = torch.sort(g, dim=-1, descending=True).values
+        tie_groups = int((srt[..., 1] == srt[..., 2]).sum())
+        diff_groups = int(((stock != layer._hard_mask_from_soft(soft)).view(soft.shape[0], -1, 4).any(-1)).sum())
+        d[f"{k}_tie_groups"] = np.asarray(tie_groups)
+        d[f"{k}_stock_topk_diff_groups"] = np.asarray(diff_groups)
+    # nm_2_4 projection keeps a ragged tail (in % 4 != 0) at 1
+    layer.hard_mask_type = "nm_2_4"
+    tail = torch.rand(12, 30)
+    put(d, "tail_soft", tail); put(d, "tail_hard", layer._hard_mask_from_soft(tail))
+    save("ties", d)
+
+
+def case_adamw():
+    torch.manual_seed(5)
+    d = {}
+    for tag, dtype, l1 in (("f32", torch.float32, 0.0), ("bf16", torch.bfloat16, 0.0), ("l1", torch.float32, 0.02)):
+        p = torch.nn.Parameter((torch.randn(32, 64) * 0.02).to(dtype))
+        p.mask = torch.rand(32, 64)
+        opt = ref_adamw.AdamW([p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, adaptive_l1_decay=l1)
+        put(d, f"{tag}_p0", p.data); put(d, f"{tag}_mask", p.mask)
+        for t in range(3):
+            g = (torch.randn(32, 64) * 0.1).to(dtype)
+            p.grad = g.clone()
+            opt.step(decay=5e-4 * (t + 1))
+            st = opt.state[p]
+            put(d, f"{tag}_g{t}", g); put(d, f"{tag}_p{t + 1}", p.data)
+            put(d, f"{tag}_m{t + 1}", st["exp_avg"]); put(d, f"{tag}_v{t + 1}", st["exp_avg_sq"])
+    save("adamw", d)
+
+
+def case_block_sparse():
+    torch.manual_seed(3)
+    out_f, in_f, T = 64, 96, 24
+    W = torch.randn(out_f, in_f) * 0.02
+    ob, ib = out_f // 16, in_f // 16
+    score = (W.view(ob, 16, ib, 16).permute(0, 2, 1, 3).reshape(ob * ib, 256) ** 2).sum(-1)
+    keep = torch.zeros(ob * ib, dtype=torch.bool)
+    keep[torch.sort(score, descending=True, stable=True).indices[: (ob * ib) // 2]] = True
+    mask = keep.view(ob, 1, ib, 1).expand(ob, 16, ib, 16).reshape(out_f, in_f).float()
+    blocks, row_ptr, col_idx = ref_bs.convert_to_block_sparse(W, mask, 16)
+    layer = ref_bs.BlockSparseLinear(blocks, row_ptr, col_idx, in_f, out_f, None, 16)
+    X = torch.randn(T, in_f)
+    d = {}
+    put(d, "W", W); put(d, "mask", mask); put(d, "blocks", blocks); put(d, "row_ptr", row_ptr)
+    put(d, "col_idx", col_idx); put(d, "X", X); put(d, "Y", layer._torch_forward(X))
+    save("block_sparse", d)
+
+
+if __name__ == "__main__":
+    base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
+                sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
+    # scaled-down copy of the fp32 GPT-2-MLP case (temperature 1, no hardening before the update)
+    case_chain("chain_f32", 96, 64, 2, 20, torch.float32, 1,
+               dict(base, temp_init=1.0, mask_hardening_start=1000, mask_hardening_duration=10000))
+    # scaled-down copy of the bf16 LLaMA-shaped tempering run: temperature 1.0 -> 0.05, hardening from step 1
+    case_chain("chain_bf16", 64, 128, 2, 32, torch.bfloat16, 4,
+               dict(base, temp_init=1.0, temp_min=0.05, temp_decay=0.05 ** (1.0 / 9.0), mask_hardening_start=1,
+                    mask_hardening_duration=3, mask_penalty_mode="structured_topn"), lambda_mid=0.25, seed=100)
+    case_penalty()
+    case_ties()
+    case_adamw()
+    case_block_sparse()

@@ -1,0 +1,156 @@
+"""Pins the CPU oracle against outputs of the reference itself (tests/golden/*.npz).
+
+Each stage of the oracle is fed the reference's own inputs for that stage and must reproduce
+the reference's output: bit-exact for hard masks, flip counts and block-CSR indices, and to
+fp32 / bf16 rounding for floats (the same torch CPU ops are used, so most are bit-exact too).
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import sparselinear_oracle as O
+from tests.golden_io import Golden, rel_err
+
+F32_TOL = 1e-5
+BF16_TOL = 1e-2
+
+
+def test_ties_projection_bit_exact():
+    g = Golden("ties")
+    for name in g["names"]:
+        soft, hard = g[f"{name}_soft"], g[f"{name}_hard"]
+        assert torch.equal(O.hard_mask_from_soft(soft, "structured"), hard), name
+        # the stock topk only ever differs inside groups holding an exact 2nd/3rd tie
+        assert g.scalar(f"{name}_stock_topk_diff_groups") <= g.scalar(f"{name}_tie_groups")
+    assert g.scalar("ones_stock_topk_diff_groups") > 0  # the tie rule matters
+    assert torch.equal(O.hard_mask_from_soft(g["tail_soft"], "nm_2_4"), g["tail_hard"])
+    assert bool((g["tail_hard"][:, 28:] == 1).all())
+    with pytest.raises(ValueError):
+        O.hard_mask_from_soft(g["tail_soft"], "structured")
+
+
+def test_metadata_round_trip():
+    g = Golden("ties")
+    for name in g["names"]:
+        hard = g[f"{name}_hard"]
+        meta = O.meta_from_hard(hard)
+        rows, cols = hard.shape
+        assert meta.shape == (rows, (cols + 7) // 8)
+        nib = torch.stack([meta & 0xF, meta >> 4], dim=-1).view(rows, -1)[:, : cols // 4].long()
+        i0, i1 = nib & 3, nib >> 2
+        assert bool((i0 < i1).all())
+        rebuilt = torch.zeros(rows, cols // 4, 4)
+        rebuilt.scatter_(-1, i0.unsqueeze(-1), 1.0)
+        rebuilt.scatter_(-1, i1.unsqueeze(-1), 1.0)
+        assert torch.equal(rebuilt.view(rows, cols), hard)
+
+
+@pytest.mark.parametrize("case,tol", [("chain_f32", F32_TOL), ("chain_bf16", BF16_TOL)])
+def test_chain_stages(case, tol):
+    g = Golden(case)
+    W = g["W0"]
+    H = torch.ones(W.shape)
+    probe = 0
+    m = torch.zeros_like(W)
+    v = torch.zeros_like(W)
+    mask = torch.ones(W.shape)
+    X, dY = g["X"], g["dY"]
+    lam = g.scalar("lambda_mid")
+    for t in range(g.scalar("n_steps")):
+        hx = g.scalar(f"s{t}_hx_fwd")
+        assert torch.equal(mask, g[f"s{t}_mask_fwd"])
+        # masked forward / backward
+        eff = O.effective_mask(mask, hx)
+        Y = O.linear_forward(X, W, eff)
+        dx, dW, _ = O.linear_backward(X, W, eff, dY)
+        assert rel_err(Y, g[f"s{t}_Y"]) <= tol
+        assert rel_err(dx, g[f"s{t}_dX"]) <= tol
+        assert rel_err(dW, g[f"s{t}_dW"]) <= tol
+        # Hutchinson accumulation from the reference's hvp
+        while probe < g.scalar(f"s{t}_probes_end"):
+            H = O.hutchinson_accumulate(H, g[f"hvp_{probe}"], g[f"v_{probe}"].float(), 0.99)
+            assert rel_err(H, g[f"H_{probe}"]) <= F32_TOL
+            H = g[f"H_{probe}"].clone()
+            probe += 1
+        # AdamW on the reference's gradient
+        W, m, v = O.adamw_step(W, g[f"s{t}_dW"], m, v, step=t + 1, lr=1e-4, betas=(0.9, 0.95), eps=1e-8,
+                               weight_decay=0.1, mask=mask, decay=2e-4)
+        assert rel_err(W, g[f"s{t}_W_opt"]) <= tol
+        assert rel_err(m, g[f"s{t}_m"]) <= tol
+        assert rel_err(v, g[f"s{t}_v"]) <= tol
+        W, m, v = g[f"s{t}_W_opt"].clone(), g[f"s{t}_m"].clone(), g[f"s{t}_v"].clone()
+        # score -> gate -> mask update -> projection
+        raw = O.importance_score(W, "hessian_obd", H=H)
+        assert rel_err(raw, g[f"s{t}_score_raw"]) <= F32_TOL
+        G = O.gate_target_structured(O.normalize_scores(raw), g.scalar(f"s{t}_T"))
+        assert rel_err(G, g[f"s{t}_G"]) <= F32_TOL
+        new_mask = O.mask_update(mask, g[f"s{t}_G"], mask_lr=0.1, lambda_mid=lam, penalty_mode="structured_topn")
+        assert rel_err(new_mask, g[f"s{t}_mask"]) <= F32_TOL
+        assert O.flip_count(mask, g[f"s{t}_mask"]) == g.scalar(f"s{t}_flips")
+        mask = g[f"s{t}_mask"].clone()
+        assert torch.equal(O.hard_mask_from_soft(mask), g[f"s{t}_hard"])
+        assert math.isclose(O.mask_stats(mask)["sum_m1m"], g.scalar(f"s{t}_mid_sum"), rel_tol=1e-9, abs_tol=1e-9)
+
+
+def test_chain_bf16_schedule():
+    g = Golden("chain_bf16")
+    decay = 0.05 ** (1.0 / 9.0)
+    for t in range(g.scalar("n_steps")):
+        assert math.isclose(O.temperature_at(t, 1.0, decay, 0.05), g.scalar(f"s{t}_T"), rel_tol=1e-12)
+        assert math.isclose(O.hardening_x(t, 1, 3), g.scalar(f"s{t}_hx"), rel_tol=1e-12, abs_tol=1e-12)
+
+
+def test_penalty_variants():
+    g = Golden("penalty")
+    modes = {"topn": "structured_topn", "nm24": "nm_2_4", "mid": "mid", "bin": "structured_topn", "beta": "mid",
+             "exact": "mid", "lowT": "structured_topn"}
+    for tag in g["variants"]:
+        W, H, mask0 = g[f"{tag}_W"], g[f"{tag}_H"], g[f"{tag}_mask0"]
+        s = O.normalize_scores(O.importance_score(W, "hessian_obd", H=H))
+        G = O.gate_target_structured(s, g.scalar(f"{tag}_T"), exact=(tag == "exact"), beta_s=g.scalar(f"{tag}_beta_s"))
+        assert rel_err(G, g[f"{tag}_G"]) <= F32_TOL, tag
+        new = O.mask_update(mask0, g[f"{tag}_G"], mask_lr=0.2, lambda_mid=g.scalar(f"{tag}_lambda"), pen_lr=0.15,
+                            penalty_mode=modes[tag], binarize_decay=0.05 if tag == "bin" else 0.0)
+        assert rel_err(new, g[f"{tag}_mask1"]) <= F32_TOL, tag
+        mode = "nm_2_4" if tag == "nm24" else "structured"
+        assert O.flip_count(mask0, g[f"{tag}_mask1"], mode) == g.scalar(f"{tag}_flips"), tag
+        assert math.isclose(O.hardening_x(g.scalar(f"{tag}_step"), 2, 8), g.scalar(f"{tag}_hx"), rel_tol=1e-12)
+
+
+@pytest.mark.parametrize("tag,tol,l1", [("f32", F32_TOL, 0.0), ("bf16", BF16_TOL, 0.0), ("l1", F32_TOL, 0.02)])
+def test_adamw(tag, tol, l1):
+    g = Golden("adamw")
+    p = g[f"{tag}_p0"]
+    m = torch.zeros_like(p)
+    v = torch.zeros_like(p)
+    for t in range(3):
+        p, m, v = O.adamw_step(p, g[f"{tag}_g{t}"], m, v, step=t + 1, lr=1e-3, betas=(0.9, 0.95), eps=1e-8,
+                               weight_decay=0.1, mask=g[f"{tag}_mask"], decay=5e-4 * (t + 1), adaptive_l1=l1)
+        assert rel_err(p, g[f"{tag}_p{t + 1}"]) <= tol
+        assert rel_err(m, g[f"{tag}_m{t + 1}"]) <= tol
+        assert rel_err(v, g[f"{tag}_v{t + 1}"]) <= tol
+
+
+def test_block_sparse_layout():
+    g = Golden("block_sparse")
+    W = g["W"]
+    assert torch.equal(O.block16_keep_mask(W, 0.5), g["mask"])
+    blocks, row_ptr, col_idx = O.bsr16_convert(W, g["mask"])
+    assert torch.equal(blocks, g["blocks"])
+    assert torch.equal(row_ptr, g["row_ptr"]) and torch.equal(col_idx, g["col_idx"])
+    Y = g["X"].matmul((W * g["mask"]).t())
+    assert rel_err(Y, g["Y"]) <= F32_TOL
+
+
+def test_sparse24_compress_round_trip():
+    torch.manual_seed(0)
+    W = torch.randn(16, 64)
+    vals, meta, hard = O.sparse24_compress(W, W.abs())
+    assert torch.equal(hard, O.hard_mask_from_soft(W.abs()))
+    nib = torch.stack([meta & 0xF, meta >> 4], dim=-1).view(16, -1).long()
+    idx = torch.stack([nib & 3, nib >> 2], dim=-1)
+    dense = torch.zeros(16, 16, 4)
+    dense.scatter_(-1, idx, vals.view(16, 16, 2))
+    assert torch.equal(dense.view(16, 64), W * hard)
