@@ -1,0 +1,375 @@
+"""Benchmark of the SparseLinear hot path on the LLaMA-2-7B layer set.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload ("llama2-7b-layerset-tempering"): the seven linear shapes of one LLaMA-2-7B decoder
+layer (q/k/v/o [4096,4096], gate/up [11008,4096], down [4096,11008]) in bf16 with fp32 mask,
+Hessian diagonal and score; activations [4,2048,in] (T = 8192 tokens). One step is one full
+soft-mask tempering step of every matrix: masked forward GEMM, dgrad and wgrad GEMMs, Hutchinson
+accumulate + |W|^2 H score, mask-aware AdamW, and the 2:4 soft-mask update with hard projection,
+metadata and masked-weight emit, at a temperature annealed 1.0 -> 0.05 over 10 steps. Inputs are
+seeded synthetic tensors with the shapes and N(0,0.02) / N(0,1) distributions of that model; the
+Hessian-vector product fed to the Hutchinson kernel is a resident synthetic tensor (the parity tests
+run the real double backward through the same three GEMM kernels).
+
+`value` = algorithmic fwd+bwd GEMM FLOPs of the layer set (6*T*in*out per matrix) divided by the
+whole step time, so the score / mask / optimizer passes count against it. With N GPUs the weights
+are row-sharded (out/N rows per rank), the forward output is all-gathered and the input gradient
+reduce-scattered over NCCL; the total work is fixed (strong scaling).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+SHAPES = [("q", 4096, 4096), ("k", 4096, 4096), ("v", 4096, 4096), ("o", 4096, 4096),
+          ("gate", 11008, 4096), ("up", 11008, 4096), ("down", 4096, 11008)]
+T_TOKENS = 8192
+METRIC = "SparseLinear fwd+bwd TFLOP/s (LLaMA-2-7B layer set, full tempering step)"
+UNIT = "TFLOP/s"
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+# algorithmic bytes per weight element at these dtypes (bf16 W/g/m/v/hvp, int8 probe, fp32 mask/H/score)
+BYTES_SCORE, BYTES_MASK, BYTES_ADAMW = 17.0, 16.125, 18.0
+
+
+def layer_flops(T, rows, cols):
+    return 6.0 * T * rows * cols
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d}, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                if out:
+                    self.rows.append([c.strip() for c in out.split(",")])
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def start(self):
+        self._t = threading.Thread(target=self._run, daemon=True)
+        self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join(timeout=6)
+        sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, c in zip(names, r[3:7]) if c.lower().startswith("active")})
+        mx = max((float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()), default=None)
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------------
+# the product arm
+# ---------------------------------------------------------------------------------------------
+class Matrix:
+    """One row shard of one SparseLinear weight with all its state resident in HBM."""
+
+    def __init__(self, name, rows, cols, seed, dev):
+        from sparseforge_b200 import ops
+
+        g = torch.Generator(device=dev).manual_seed(seed)
+        bf = torch.bfloat16
+        self.name, self.rows, self.cols = name, rows, cols
+        self.W = (torch.randn(rows, cols, device=dev, generator=g) * 0.02).to(bf)
+        self.mask = torch.ones(rows, cols, device=dev)
+        self.H = torch.ones(rows, cols, device=dev)
+        self.m = torch.zeros(rows, cols, device=dev, dtype=bf)
+        self.v = torch.zeros(rows, cols, device=dev, dtype=bf)
+        self.hvp = (torch.randn(rows, cols, device=dev, generator=g) * 1e-3).to(bf)
+        self.probe = (torch.randint(0, 2, (rows, cols), device=dev, generator=g, dtype=torch.int8) * 2 - 1)
+        self.score = torch.empty(rows, cols, device=dev)
+        self.norm = torch.zeros(2, device=dev)
+        self.scratch = ops.hutch_score_scratch(dev)
+        self.stats = torch.zeros(8, dtype=torch.float64, device=dev)
+        self.wm = torch.empty_like(self.W)
+        self.meta = torch.zeros(rows, cols // 8, dtype=torch.uint8, device=dev)
+        ops.effective_weight(self.W, self.mask, self.wm, meta=self.meta, hx=1.0)
+
+
+class Timers:
+    def __init__(self):
+        self.pairs = {}
+
+    def region(self, key):
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        self.pairs.setdefault(key, []).append((s, e))
+        return s, e
+
+    def totals_ms(self):
+        return {k: sum(s.elapsed_time(e) for s, e in v) for k, v in self.pairs.items()}
+
+    def counts(self):
+        return {k: len(v) for k, v in self.pairs.items()}
+
+
+def run_ours(args):
+    import torch.distributed as dist
+
+    from sparseforge_b200 import _lib, ops
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    _lib.lib()  # fail loudly if the CUDA library is missing
+    T = T_TOKENS
+    bf = torch.bfloat16
+    mats = [Matrix(n, r // world, c, 100 + i, dev) for i, (n, r, c) in enumerate(SHAPES)]
+    # activations: the same on every rank (seeded), one buffer per distinct width
+    gx = torch.Generator(device=dev).manual_seed(7)
+    widths = sorted({c for _, _, c in SHAPES} | {r for _, r, _ in SHAPES})
+    X = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
+    dYfull = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
+    host_X = host_dY = None
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    decay_t = 0.05 ** (1.0 / 9.0)
+    launches = 0
+
+    def step(it, timers=None, e2e=False):
+        nonlocal launches
+        temp = max(0.05, decay_t ** (it % 10))
+        hx = max(0.0, min(1.0, 1.0 - ((it % 10) - 1) / 9.0)) if (it % 10) >= 1 else 1.0
+        for mt in mats:
+            x = X[mt.cols]
+            if e2e:
+                x.copy_(host_X[mt.cols], non_blocking=True)
+                dYfull[mt.rows * world].copy_(host_dY[mt.rows * world], non_blocking=True)
+            dy_full = dYfull[mt.rows * world]
+            dy = dy_full if world == 1 else dy_full[:, rank * mt.rows:(rank + 1) * mt.rows].contiguous()
+
+            def timed(key, fn):
+                nonlocal launches
+                if timers is None:
+                    out = fn()
+                else:
+                    s, e = timers.region(key)
+                    s.record()
+                    out = fn()
+                    e.record()
+                launches += 1
+                return out
+
+            y = timed("gemm", lambda: ops.gemm_fwd(x, mt.wm, status=status))
+            if world > 1:
+                yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
+                dist.all_gather_into_tensor(yg, y)
+            dx = timed("gemm", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
+            if world > 1:
+                dxs = torch.empty(T // world, mt.cols, dtype=bf, device=dev)
+                dist.reduce_scatter_tensor(dxs, dx)
+            dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
+            timed("score", lambda: ops.hutch_score(mt.W, mt.H, mt.score, mt.norm, mt.scratch, hvp=mt.hvp, v=mt.probe,
+                                                   beta=0.99))
+            launches += 1  # the one-block statistics kernel behind the score pass
+            timed("adamw", lambda: ops.adamw_masked(mt.W, dw, mt.m, mt.v, mask=mt.mask, lr=1e-4, beta1=0.9, beta2=0.95,
+                                                    eps=1e-8, weight_decay=0.1, decay=2e-4, step=it + 1))
+            timed("mask", lambda: ops.mask_update_nm24(mt.score, mt.norm, mt.mask, mt.stats, W=mt.W, wm=mt.wm,
+                                                       meta=mt.meta, temperature=temp, mask_lr=0.1, hx=hx))
+        if e2e:
+            return torch.stack([mt.stats for mt in mats]).to("cpu", non_blocking=False)
+        return None
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for it in range(args.warmup):
+        step(it)
+    barrier()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    timers = Timers()
+    launches = 0
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for it in range(args.steps):
+        step(args.warmup + it, timers)
+    t1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    total_ms = t0.elapsed_time(t1)
+    launches_timed = launches
+    if int(status[0].item()) != 0:
+        raise RuntimeError(f"a device-side wait ran out inside a GEMM (code {int(status[0])}); the numbers are void")
+    part = timers.totals_ms()
+
+    # end to end: the same step fed from pinned host buffers, stats read back every step
+    host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in SHAPES}}
+    host_dY = {w: dYfull[w].cpu().pin_memory() for w in {r for _, r, _ in SHAPES}}
+    h2d = sum((T * c + T * r) * 2 for _, r, c in SHAPES)
+    d2h = len(SHAPES) * 8 * 8
+    step(0, e2e=True)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for it in range(args.steps):
+        step(args.warmup + it, e2e=True)
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+
+    times = torch.tensor([total_ms, e2e_ms, part.get("gemm", 0.0), part.get("score", 0.0), part.get("adamw", 0.0),
+                          part.get("mask", 0.0)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, gemm_ms, score_ms, adamw_ms, mask_ms = [float(x) for x in times.cpu()]
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks, peak_src = load_peaks()
+    flops_step = sum(layer_flops(T, r, c) for _, r, c in SHAPES)
+    elems_rank = sum(r * c for _, r, c in SHAPES) / world
+    ms_per_step = total_ms / args.steps
+    value = flops_step / (ms_per_step * 1e-3) / 1e12
+    gemm_tflops = (flops_step / world) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
+    gbs = lambda b, ms: (elems_rank * b * args.steps) / (ms * 1e-3) / 1e9 if ms > 0 else None  # noqa: E731
+    out = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "llama2-7b-layerset-tempering", "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
+                   "tokens": T, "row_sharded_over": world, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
+        "clocks": clocks,
+        "e2e": {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2), "unit": UNIT,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches_timed,
+        "roofline": {"bound": "tensor", "achieved": round(gemm_tflops, 1) if gemm_tflops else None,
+                     "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
+                     "frac": round(gemm_tflops / peaks["bf16_tflops_sustained"], 4) if gemm_tflops else None,
+                     "traffic": None, "peak_source": peak_src + " (sustained bf16 GEMM)",
+                     "kernel": "gemm_bf16_tcgen05_kernel (fwd, dgrad, wgrad: 21 launches per step)"},
+        "passes": {
+            "score_gbs": gbs(BYTES_SCORE, score_ms), "adamw_gbs": gbs(BYTES_ADAMW, adamw_ms),
+            "mask_update_gbs": gbs(BYTES_MASK, mask_ms), "hbm_peak_gbs": peaks["hbm_gbs"],
+            "gemm_ms_per_step": gemm_ms / args.steps, "score_ms_per_step": score_ms / args.steps,
+            "adamw_ms_per_step": adamw_ms / args.steps, "mask_ms_per_step": mask_ms / args.steps,
+        },
+    }
+    for k in ("score_gbs", "adamw_gbs", "mask_update_gbs"):
+        if out["passes"][k]:
+            out["passes"][k.replace("_gbs", "_frac")] = round(out["passes"][k] / peaks["hbm_gbs"], 4)
+            out["passes"][k] = round(out["passes"][k], 1)
+    if world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_port_sample(sample_tokens=1024)
+    print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# the CPU arm: the oracle port of the reference's PyTorch path on the host cores
+# ---------------------------------------------------------------------------------------------
+def cpu_port_step(W, mask, H, m, v, X, dY, hvp, probe, it):
+    """One tempering step of one matrix with the oracle (torch CPU ops in the reference's order)."""
+    from oracle import sparselinear_oracle as O
+
+    temp = max(0.05, (0.05 ** (1.0 / 9.0)) ** (it % 10))
+    eff = O.effective_mask(mask, 1.0)
+    O.linear_forward(X, W, eff)
+    _, dW, _ = O.linear_backward(X, W, eff, dY)
+    H = O.hutchinson_accumulate(H, hvp, probe, 0.99)
+    W, m, v = O.adamw_step(W, dW, m, v, step=it + 1, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1,
+                           mask=mask, decay=2e-4)
+    G = O.gate_target_structured(O.normalize_scores(O.importance_score(W, "hessian_obd", H=H)), temp)
+    new_mask = O.mask_update(mask, G, mask_lr=0.1)
+    O.flip_count(mask, new_mask)
+    return W, new_mask, H, m, v
+
+
+def cpu_port_sample(sample_tokens=1024, rows=4096, cols=4096, repeats=2):
+    """Times the oracle on one q-shaped matrix with `sample_tokens` of the 8192 tokens; the
+    throughput is in the bench's unit (fwd+bwd GEMM FLOPs over the whole step time)."""
+    torch.manual_seed(100)
+    bf = torch.bfloat16
+    W = (torch.randn(rows, cols) * 0.02).to(bf)
+    mask, H = torch.ones(rows, cols), torch.ones(rows, cols)
+    m, v = torch.zeros(rows, cols, dtype=bf), torch.zeros(rows, cols, dtype=bf)
+    X, dY = torch.randn(sample_tokens, cols).to(bf), torch.randn(sample_tokens, rows).to(bf)
+    hvp = (torch.randn(rows, cols) * 1e-3).to(bf)
+    probe = (torch.randint(0, 2, (rows, cols), dtype=torch.int8) * 2 - 1).to(bf)
+    best = None
+    for it in range(repeats + 1):
+        t0 = time.perf_counter()
+        W, mask, H, m, v = cpu_port_step(W, mask, H, m, v, X, dY, hvp, probe, it)
+        dt = time.perf_counter() - t0
+        if it > 0:
+            best = dt if best is None else min(best, dt)
+    return {"value": round(layer_flops(sample_tokens, rows, cols) / best / 1e12, 4), "unit": UNIT,
+            "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"one [4096,4096] matrix, {sample_tokens} of 8192 tokens, full tempering step, best of {repeats}",
+            "seconds_per_sample_step": round(best, 3)}
+
+
+def run_reference(args):
+    """The reference's own algorithm on the host cores (oracle port: the reference is Python on
+    torch and is not present on the GPU box; its arithmetic is restated op for op in oracle/)."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    res = cpu_port_sample(sample_tokens=512, repeats=max(1, min(args.steps, 3)))
+    out = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+           "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["seconds_per_sample_step"] * 1e3,
+           "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+           "config": {"workload": "llama2-7b-layerset-tempering", "sample": res["sample"]},
+           "cpu_baseline": res, "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
+                                        "d2h_bytes_per_step": 0}}
+    print(json.dumps(out), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -77,8 +77,8 @@ SF_API int64_t sf_hutch_score_scratch_doubles(int64_t n);
  * n = rows*cols, must be a multiple of 8; buffers 16-byte aligned.
  */
 SF_API int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const void* W,
-                   int w_dtype, const void* aux, float aux_scalar, float* score,
-                   float* norm, double* scratch, int64_t n, float beta, int metric,
+                   int w_dtype, const void* aux, double aux_scalar, float* score,
+                   float* norm, double* scratch, int64_t n, double beta, int metric,
                    void* stream);
 
 /* Stats written by sf_mask_update_nm24 (8 doubles). */
@@ -118,8 +118,8 @@ enum {
  */
 SF_API int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W,
                         int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows,
-                        int64_t cols, float temperature, float mask_lr, float pen,
-                        int penalty_mode, float beta_s, float binarize_decay, float hx,
+                        int64_t cols, double temperature, double mask_lr, double pen,
+                        int penalty_mode, double beta_s, double binarize_decay, double hx,
                         int structured_exact, int score_bf16, void* stream);
 
 /*
@@ -142,7 +142,7 @@ SF_API int sf_project_nm24(const void* soft, int in_dtype, int64_t ld_soft, void
  *   scale != 1 multiplies wm afterwards (weight_scaling, :777-784).
  */
 SF_API int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm, uint8_t* meta,
-                        int64_t rows, int64_t cols, float hx, int finalized, float scale,
+                        int64_t rows, int64_t cols, double hx, int finalized, double scale,
                         void* stream);
 
 /*
@@ -151,14 +151,16 @@ SF_API int sf_effective_weight(const void* W, int w_dtype, const float* mask, vo
  *   p *= 1 - lr*wd;  g += decay * p * (1 - mask)  (mask != NULL);
  *   m = b1 m + (1-b1) g;  v = b2 v + (1-b2) g^2;  denom = sqrt(v)/sqrt(bc2) + eps;
  *   p -= (lr/bc1) m/denom;  p -= lr*l1*sign(p)/denom  (l1 > 0, mask != NULL).
- * bc1 = 1 - b1^step and bc2 = 1 - b2^step are computed by the caller.
+ * bc1 = 1 - b1^step and bc2 = 1 - b2^step are computed by the caller. Hyper-parameters are
+ * doubles, as the Python floats of the reference are; each is rounded to fp32 where the
+ * reference's tensor op rounds it (1 - lr*wd, 1 - b1, lr/bc1, sqrt(bc2) are formed in double).
  * p, g, m, v share dtype w_dtype (state dtype = weight dtype, adamw.py:123-125);
  * mask is fp32. If wm != NULL the new effective masked weight is also written:
  * wm <- p * cast(hx*mask + (1-hx)*top2(mask)) (cols % 8 == 0 then; rows*cols = n).
  */
 SF_API int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype,
-                    int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
-                    float decay, float bc1, float bc2, float adaptive_l1, void* wm, float hx,
+                    int64_t n, double lr, double beta1, double beta2, double eps, double weight_decay,
+                    double decay, double bc1, double bc2, double adaptive_l1, void* wm, double hx,
                     int64_t cols, void* stream);
 
 /*

@@ -23,13 +23,13 @@ _SIGNATURES = {
     "sf_version": (c_int, []),
     "sf_last_error_string": (c_char_p, []),
     "sf_hutch_score_scratch_doubles": (c_int64, [c_int64]),
-    "sf_hutch_score": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_float, _P, _P, _P, c_int64, c_float, c_int, _P]),
-    "sf_mask_update_nm24": (c_int, [_P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_float, c_float, c_float,
-                                    c_int, c_float, c_float, c_float, c_int, c_int, _P]),
+    "sf_hutch_score": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_double, _P, _P, _P, c_int64, c_double, c_int, _P]),
+    "sf_mask_update_nm24": (c_int, [_P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_double, c_double,
+                                    c_int, c_double, c_double, c_double, c_int, c_int, _P]),
     "sf_project_nm24": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int64, c_int64, _P]),
-    "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_float, c_int, c_float, _P]),
-    "sf_adamw_masked": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_float, c_float, c_float, c_float, c_float,
-                                c_float, c_float, c_float, c_float, _P, c_float, c_int64, _P]),
+    "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_int, c_double, _P]),
+    "sf_adamw_masked": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_double, c_double, c_double, c_double, c_double,
+                                c_double, c_double, c_double, c_double, _P, c_double, c_int64, _P]),
     "sf_mask_stats": (c_int, [_P, _P, c_int64, c_int64, _P]),
     "sf_masked_gemm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_float, c_int, _P, _P]),
     "sf_masked_gemm_dgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),

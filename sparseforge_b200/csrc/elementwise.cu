@@ -166,8 +166,9 @@ score_norm_finalize_kernel(const double* __restrict__ partials, int nblocks, dou
 template <typename TW, typename TV, bool ACCUM>
 static int launch_hutch_score(int metric, const void* hvp, const void* v, float* H, const void* W,
                               const void* aux, float aux_scalar, float* score, double* scratch,
-                              int64_t chunks, float beta, int grid, cudaStream_t st) {
-    const float omb = (float)(1.0 - (double)beta);
+                              int64_t chunks, double beta_d, int grid, cudaStream_t st) {
+    const float beta = (float)beta_d;
+    const float omb = (float)(1.0 - beta_d);
 #define SF_LAUNCH_HS(M)                                                                          \
     hutch_score_kernel<TW, TV, M, ACCUM><<<grid, kThreads, 0, st>>>(                            \
         (const TW*)hvp, (const TV*)v, H, (const TW*)W, (const TW*)aux, aux_scalar, score, scratch, \
@@ -554,8 +555,10 @@ int64_t sf_hutch_score_scratch_doubles(int64_t n) {
 }
 
 int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const void* W, int w_dtype,
-                   const void* aux, float aux_scalar, float* score, float* norm, double* scratch,
-                   int64_t n, float beta, int metric, void* stream) {
+                   const void* aux, double aux_scalar_d, float* score, float* norm, double* scratch,
+                   int64_t n, double beta_d, int metric, void* stream) {
+    float aux_scalar = (float)aux_scalar_d;
+    const float beta = (float)beta_d;
     SF_CHECK_ARG(W && score && norm && scratch, "sf_hutch_score: W, score, norm and scratch must be non-null");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_hutch_score: n=%lld must be a positive multiple of 8", (long long)n);
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_hutch_score: w_dtype must be SF_F32 or SF_BF16");
@@ -578,7 +581,7 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
     if (metric == SF_METRIC_MOVEMENT && aux_scalar < 1e-8f) aux_scalar = 1e-8f;
     int rc = SF_OK;
 #define SF_HS(TW, TV, ACC) \
-    rc = launch_hutch_score<TW, TV, ACC>(metric, hvp, v, H, W, aux, aux_scalar, score, scratch, chunks, beta, grid, st)
+    rc = launch_hutch_score<TW, TV, ACC>(metric, hvp, v, H, W, aux, aux_scalar, score, scratch, chunks, beta_d, grid, st)
     if (w_dtype == SF_F32) {
         if (!accum) SF_HS(float, float, false);
         else if (v_dtype == SF_I8) SF_HS(float, int8_t, true);
@@ -595,23 +598,23 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
     return SF_OK;
 }
 
-static MaskUpdateParams make_mask_params(float temperature, float mask_lr, float pen, int penalty_mode,
-                                         float beta_s, float binarize_decay, float hx, int structured_exact,
+static MaskUpdateParams make_mask_params(double temperature, double mask_lr, double pen, int penalty_mode,
+                                         double beta_s, double binarize_decay, double hx, int structured_exact,
                                          int score_bf16) {
     MaskUpdateParams P;
-    P.inv_temp_den = temperature + 1e-8f;
-    P.a = mask_lr;
-    P.one_minus_a = (float)(1.0 - (double)mask_lr);
-    P.pen = pen;
+    P.inv_temp_den = (float)temperature + 1e-8f;
+    P.a = (float)mask_lr;
+    P.one_minus_a = (float)(1.0 - mask_lr);
+    P.pen = (float)pen;
     P.penalty_mode = penalty_mode;
-    P.beta_s = beta_s;
-    P.one_minus_beta_s = (float)(1.0 - (double)beta_s);
-    P.bin_lo = (float)(1.0 - (double)binarize_decay);
-    P.bin_hi = (float)(1.0 + (double)binarize_decay);
-    P.binarize = binarize_decay != 0.0f;
-    P.hx = hx;
-    P.one_minus_hx = (float)(1.0 - (double)hx);
-    P.soft_only = hx >= 1.0f - 1e-6f;
+    P.beta_s = (float)beta_s;
+    P.one_minus_beta_s = (float)(1.0 - beta_s);
+    P.bin_lo = (float)(1.0 - binarize_decay);
+    P.bin_hi = (float)(1.0 + binarize_decay);
+    P.binarize = binarize_decay != 0.0;
+    P.hx = (float)hx;
+    P.one_minus_hx = (float)(1.0 - hx);
+    P.soft_only = hx >= 1.0 - 1e-6;
     P.structured_exact = structured_exact;
     P.score_bf16 = score_bf16;
     return P;
@@ -619,8 +622,8 @@ static MaskUpdateParams make_mask_params(float temperature, float mask_lr, float
 
 int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W, int w_dtype,
                         void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
-                        float temperature, float mask_lr, float pen, int penalty_mode, float beta_s,
-                        float binarize_decay, float hx, int structured_exact, int score_bf16,
+                        double temperature, double mask_lr, double pen, int penalty_mode, double beta_s,
+                        double binarize_decay, double hx, int structured_exact, int score_bf16,
                         void* stream) {
     SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm24: score, norm, mask, stats must be non-null");
     SF_CHECK_ARG(rows > 0 && cols > 0, "sf_mask_update_nm24: rows=%lld cols=%lld must be positive",
@@ -686,7 +689,8 @@ int sf_project_nm24(const void* soft, int in_dtype, int64_t ld_soft, void* hard,
 }
 
 int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm, uint8_t* meta,
-                        int64_t rows, int64_t cols, float hx, int finalized, float scale, void* stream) {
+                        int64_t rows, int64_t cols, double hx, int finalized, double scale_d, void* stream) {
+    const float scale = (float)scale_d;
     SF_CHECK_ARG(W && mask && wm, "sf_effective_weight: W, mask, wm must be non-null");
     SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0, "sf_effective_weight: cols=%lld must be a positive multiple of 8",
                  (long long)cols);
@@ -694,7 +698,7 @@ int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm,
     if (!(aligned16(W) && aligned16(mask) && aligned16(wm)))
         return fail(SF_ERR_ALIGNMENT, "sf_effective_weight: buffers must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    MaskUpdateParams P = make_mask_params(1.0f, 0.0f, 0.0f, 0, 0.0f, 0.0f, finalized ? 1.0f : hx, 0, 0);
+    MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, finalized ? 1.0 : hx, 0, 0);
     const int64_t chunks = rows * cols / 8;
     const int grid = grid_for(chunks, 8);
     if (w_dtype == SF_F32)
@@ -707,13 +711,13 @@ int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm,
 }
 
 int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
-                    float lr, float beta1, float beta2, float eps, float weight_decay, float decay,
-                    float bc1, float bc2, float adaptive_l1, void* wm, float hx, int64_t cols,
+                    double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
+                    double bc1, double bc2, double adaptive_l1, void* wm, double hx, int64_t cols,
                     void* stream) {
     SF_CHECK_ARG(p && g && m && v, "sf_adamw_masked: p, g, m, v must be non-null");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_adamw_masked: n=%lld must be a positive multiple of 8", (long long)n);
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_adamw_masked: w_dtype must be SF_F32 or SF_BF16");
-    SF_CHECK_ARG(bc1 > 0.0f && bc2 > 0.0f, "sf_adamw_masked: bias corrections must be positive (step >= 1)");
+    SF_CHECK_ARG(bc1 > 0.0 && bc2 > 0.0, "sf_adamw_masked: bias corrections must be positive (step >= 1)");
     if (wm != nullptr) {
         SF_CHECK_ARG(mask != nullptr, "sf_adamw_masked: wm requested without mask");
         SF_CHECK_ARG(cols > 0 && cols % 8 == 0 && n % cols == 0,
@@ -723,17 +727,17 @@ int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v,
         return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked: buffers must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     AdamParams A;
-    A.c_wd = (float)(1.0 - (double)lr * (double)weight_decay);
-    A.decay = decay;
-    A.beta1 = beta1; A.one_minus_beta1 = (float)(1.0 - (double)beta1);
-    A.beta2 = beta2; A.one_minus_beta2 = (float)(1.0 - (double)beta2);
-    A.sqrt_bc2 = (float)sqrt((double)bc2);
-    A.eps = eps;
-    A.step_size = (float)((double)lr / (double)bc1);
-    A.lr = lr;
-    A.l1 = adaptive_l1;
+    A.c_wd = (float)(1.0 - lr * weight_decay);
+    A.decay = (float)decay;
+    A.beta1 = (float)beta1; A.one_minus_beta1 = (float)(1.0 - beta1);
+    A.beta2 = (float)beta2; A.one_minus_beta2 = (float)(1.0 - beta2);
+    A.sqrt_bc2 = (float)sqrt(bc2);
+    A.eps = (float)eps;
+    A.step_size = (float)(lr / bc1);
+    A.lr = (float)lr;
+    A.l1 = (float)adaptive_l1;
     A.has_mask = mask != nullptr;
-    MaskUpdateParams P = make_mask_params(1.0f, 0.0f, 0.0f, 0, 0.0f, 0.0f, hx, 0, 0);
+    MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, hx, 0, 0);
     const int64_t chunks = n / 8;
     const int grid = grid_for(chunks, 8);
 #define SF_AD(TW, EW) \

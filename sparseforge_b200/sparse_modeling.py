@@ -1,0 +1,651 @@
+"""SparseLinear and its autograd functions on the B200 kernels.
+
+Host-side mirror of the reference's ``legacy/sparse_modeling.py`` interface (same class and
+method names, argument meaning and error behaviour) for the structured 2:4 path:
+
+* ``SparseLinearConfig``  — legacy/sparse_modeling.py:136-239 (same fields and defaults)
+* ``STE`` / ``SRSTE``      — :23-53
+* ``FusedMaskedLinearSTE`` — :56-132 (``apply(x, weight, bias, mask, decay, scale_factor)``)
+* ``SparseLinear``         — :242-1666
+
+What differs by design: the masked weight ``W * M_eff`` is materialised once per change of
+weight or mask (by the mask-update and AdamW kernels) instead of twice per step; the mask
+update is one fused kernel that also emits 2:4 metadata, the flip count and the mask sums;
+all three products run on tcgen05 kernels and stay differentiable to second order, which the
+Hutchinson estimator needs. Tensors must live on a CUDA device; there is no CPU path.
+"""
+from __future__ import annotations
+
+import weakref
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from . import _lib, ops
+
+
+@dataclass
+class SparseLinearConfig:
+    """Field-for-field the reference's dataclass (legacy/sparse_modeling.py:136-239)."""
+
+    change_mask: bool = True
+    mode: str = "sparse_forward"  # "sparse_forward" | "dense_forward"
+    mask_type: str = "structured"  # "structured" | "unstructured" | "none"
+    mask_metric: str = "hessian_obd"  # magnitude | movement | hessian_obd | hessian_ratio | hessian | wanda
+    sparsity_ratio: float = 0.5
+    N: int = 2
+    M: int = 4
+    beta: float = 0.99
+    score_ema_beta: float = 0.99
+    mask_update_period: int = 10
+    mask_update_switch_step: int = 0
+    mask_update_period_before: Optional[int] = None
+    mask_update_period_after: Optional[int] = None
+    mask_lr: float = 0.10
+    mask_penalty_lr: float = None
+    mask_penalty_mode: str = "mid"
+    temp_init: float = 1.0
+    temp_min: float = 0.05
+    temp_decay: float = 0.97
+    mask_binarize_decay: float = 0
+    mask_hardening_start: int = 1000
+    mask_hardening_duration: int = 10000
+    sparsity_warmup_steps: int = 100
+    tau_sample_size: int = 262144
+    temperature: float = 1.0
+    freeze_low: float = 0.0
+    freeze_high: float = 1.0
+    SLoRB: bool = False
+    SLoRB_k: int = 64
+    SLoRB_init_type: str = "mean"
+    trainable_projection: bool = False
+    structured_exact: bool = False
+    hard_mask_type: str = "match"
+    beta_structural_start: int = 0
+    beta_structural_end: int = 0
+    gradient_checkpointing: bool = False
+    srste_decay: float = 0.0
+    glu_joint_mask: bool = False
+    weight_scaling: bool = False
+
+
+# ----------------------------------------------------------------------------------------
+# differentiable GEMM primitives (closed under differentiation, so any order works)
+# ----------------------------------------------------------------------------------------
+class _MatmulNT(torch.autograd.Function):
+    """a[M,K] @ b[N,K]^T on the forward-product kernel."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return ops.gemm_fwd(a.contiguous(), b.contiguous())
+
+    @staticmethod
+    def backward(ctx, gy):
+        a, b = ctx.saved_tensors
+        ga = _MatmulNN.apply(gy, b) if ctx.needs_input_grad[0] else None
+        gb = _MatmulTN.apply(gy, a) if ctx.needs_input_grad[1] else None
+        return ga, gb
+
+
+class _MatmulNN(torch.autograd.Function):
+    """a[M,K] @ b[K,N] on the dgrad kernel."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return ops.gemm_dgrad(a.contiguous(), b.contiguous())
+
+    @staticmethod
+    def backward(ctx, gy):
+        a, b = ctx.saved_tensors
+        ga = _MatmulNT.apply(gy, b) if ctx.needs_input_grad[0] else None
+        gb = _MatmulTN.apply(a, gy) if ctx.needs_input_grad[1] else None
+        return ga, gb
+
+
+class _MatmulTN(torch.autograd.Function):
+    """a[K,M]^T @ b[K,N] on the wgrad kernel."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        ctx.save_for_backward(a, b)
+        return ops.gemm_wgrad(a.contiguous(), b.contiguous())
+
+    @staticmethod
+    def backward(ctx, gy):
+        a, b = ctx.saved_tensors
+        ga = _MatmulNT.apply(b, gy) if ctx.needs_input_grad[0] else None
+        gb = _MatmulNN.apply(a, gy) if ctx.needs_input_grad[1] else None
+        return ga, gb
+
+
+class _MaskedWeight(torch.autograd.Function):
+    """weight * cast(M_eff) with its true gradient g * cast(M_eff) (no gradient to the mask).
+
+    Stands for ``weight_cast * mask_for_grad`` in the reference's backward
+    (legacy/sparse_modeling.py:113), which is built from differentiable ops there.
+    """
+
+    @staticmethod
+    def forward(ctx, weight, mask, hx, finalized, wm_cached):
+        ctx.save_for_backward(mask)
+        ctx.hx, ctx.finalized = hx, finalized
+        if wm_cached is not None:
+            return wm_cached.view_as(wm_cached)
+        wm = torch.empty_like(weight)
+        ops.effective_weight(weight.detach().contiguous(), mask, wm, hx=hx, finalized=finalized)
+        return wm
+
+    @staticmethod
+    def backward(ctx, g):
+        (mask,) = ctx.saved_tensors
+        out = torch.empty_like(g)
+        ops.effective_weight(g.contiguous(), mask, out, hx=ctx.hx, finalized=ctx.finalized)
+        return out, None, None, None, None
+
+
+class STE(torch.autograd.Function):
+    """Forward weight * mask; backward passes the gradient to the dense weight
+    (legacy/sparse_modeling.py:23-35)."""
+
+    @staticmethod
+    def forward(ctx, weight, mask):
+        return weight * mask
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        return grad_output, None
+
+
+class SRSTE(torch.autograd.Function):
+    """STE plus decay * weight where mask < 0.5 (legacy/sparse_modeling.py:38-53)."""
+
+    @staticmethod
+    def forward(ctx, weight, mask, decay):
+        ctx.save_for_backward(weight)
+        ctx.mask, ctx.decay = mask, decay
+        return weight * mask
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        (weight,) = ctx.saved_tensors
+        return grad_output + ctx.decay * weight * (ctx.mask < 0.5).to(weight.dtype), None, None
+
+
+def _as_f32_mask(mask: torch.Tensor) -> torch.Tensor:
+    return mask if mask.dtype == torch.float32 else mask.float()
+
+
+class FusedMaskedLinearSTE(torch.autograd.Function):
+    """Masked linear with a straight-through weight gradient.
+
+    ``apply(x, weight, bias, mask, decay, scale_factor=1.0)`` as in the reference
+    (legacy/sparse_modeling.py:72-132): ``mask`` is the effective mask. Two extra trailing
+    arguments are used by ``SparseLinear``: a cached masked weight and (hx, finalized), in which
+    case ``mask`` is the soft mask and the effective mask is formed inside the kernels.
+    The backward pass is made of differentiable functions, so ``create_graph=True`` works.
+    """
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, mask, decay, scale_factor=1.0, wm_cached=None, hx=1.0, finalized=True):
+        if not x.is_cuda:
+            raise RuntimeError("FusedMaskedLinearSTE: tensors must live on a CUDA device (there is no CPU path)")
+        cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else weight.dtype
+        mask32 = _as_f32_mask(mask.detach())
+        if wm_cached is None:
+            wm = torch.empty_like(weight)
+            ops.effective_weight(weight.detach().contiguous(), mask32.contiguous(), wm, hx=hx, finalized=finalized)
+        else:
+            wm = wm_cached
+        x2 = x.reshape(-1, x.shape[-1])
+        y2 = ops.gemm_fwd(x2.to(cd).contiguous(), wm.to(cd), None if bias is None else bias.to(cd).contiguous(),
+                          alpha=float(scale_factor))
+        ctx.save_for_backward(x, weight, mask32)
+        ctx.has_bias = bias is not None
+        ctx.decay = float(decay)
+        ctx.hx, ctx.finalized = float(hx), bool(finalized)
+        ctx.wm = wm if wm.dtype == cd else None
+        return y2.view(*x.shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, weight, mask32 = ctx.saved_tensors
+        cd = grad_out.dtype
+        gy = grad_out.reshape(-1, grad_out.shape[-1])
+        x2 = x.reshape(-1, x.shape[-1]).to(cd)
+        grad_x = grad_w = grad_b = None
+        if ctx.needs_input_grad[0]:
+            w = _MaskedWeight.apply(weight.to(cd), mask32, ctx.hx, ctx.finalized, ctx.wm)
+            grad_x = _MatmulNN.apply(gy, w).view_as(x)
+        if ctx.needs_input_grad[1]:
+            grad_w = _MatmulTN.apply(gy, x2)
+            if ctx.decay != 0.0:
+                eff_lt = (_effective_mask_tensor(mask32, ctx.hx, ctx.finalized) < 0.5).to(cd)
+                grad_w = grad_w + ctx.decay * weight.to(cd) * eff_lt
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            grad_b = gy.sum(dim=0) if torch.is_grad_enabled() else ops.bias_grad(gy.contiguous()).to(cd)
+        return grad_x, grad_w, grad_b, None, None, None, None, None, None
+
+
+def _effective_mask_tensor(mask32, hx, finalized):
+    """hx * mask + (1 - hx) * top2(mask) as a tensor (legacy/sparse_modeling.py:759-771)."""
+    if finalized or hx >= 1.0 - 1e-6:
+        return mask32
+    hard, _ = ops.project_nm24(mask32)
+    return (hx * mask32) + ((1.0 - hx) * hard)
+
+
+# ----------------------------------------------------------------------------------------
+# SparseLinear
+# ----------------------------------------------------------------------------------------
+_SUPPORTED_METRICS = ("magnitude", "movement", "hessian_obd", "hessian_ratio", "hessian")
+
+
+class SparseLinear(nn.Linear):
+    """``nn.Linear`` with a continuous 2:4 mask driven by no-grad dynamics
+    (legacy/sparse_modeling.py:242-1666).
+
+    State-dict keys match the reference: ``weight bias mask grad_ema hessian_diag
+    frozen_mask_flags scaler_row`` (1-element placeholders where unused). ``mask`` and
+    ``hessian_diag`` are kept in float32 whatever the weight dtype.
+    """
+
+    def __init__(self, in_features, out_features, sparselinear_config=None, bias=True, **kwargs):
+        super().__init__(in_features, out_features, bias=bias, **kwargs)
+        assert sparselinear_config is not None
+        cfg = sparselinear_config
+        self.cfg = cfg
+        self.mode = cfg.mode
+        self.change_mask = cfg.change_mask
+        self.mask_type = cfg.mask_type
+        self.mask_metric = cfg.mask_metric
+        self.sparsity_ratio = cfg.sparsity_ratio
+        self.N, self.M = cfg.N, cfg.M
+        dev = self.weight.device
+
+        def frozen(shape, fill=0.0, dtype=torch.float32):
+            return nn.Parameter(torch.full(shape, fill, device=dev, dtype=dtype), requires_grad=False)
+
+        self.mask = frozen((out_features, in_features), 1.0)
+        if cfg.change_mask and cfg.mask_metric == "movement":
+            self.grad_ema = frozen((out_features, in_features), dtype=self.weight.dtype)
+        else:
+            self.grad_ema = frozen((1,), dtype=self.weight.dtype)
+            self._grad_ema_placeholder = True
+        if cfg.change_mask and (cfg.mask_metric in ("hessian_obd", "hessian_ratio", "hessian")
+                                or getattr(cfg, "enable_hutchinson", False)):
+            self.hessian_diag = frozen((out_features, in_features))
+        else:
+            self.hessian_diag = frozen((1,))
+            self._hessian_diag_placeholder = True
+        if cfg.change_mask and (cfg.freeze_low > 0.0 or cfg.freeze_high < 1.0):
+            raise NotImplementedError("freeze_low / freeze_high bands are not part of the 2:4 kernel path")
+        self.frozen_mask_flags = frozen((1,), dtype=self.weight.dtype)
+        self._frozen_mask_flags_placeholder = True
+        if cfg.mask_metric == "wanda":
+            raise NotImplementedError("mask_metric='wanda' (calibration scaler) is not part of the 2:4 kernel path")
+        self.scaler_row = frozen((1,), dtype=self.weight.dtype)
+        self._scaler_row_placeholder = True
+        self.nsamples = 0
+
+        self.weight.mask = self.mask
+        self.weight.flipped_mask = 0
+        self.weight.init_flipped_mask = 0
+        self.weight.param_count = self.weight.numel()
+        self.weight._sf_owner = weakref.ref(self)
+        self.srste_decay = cfg.srste_decay
+        self.mask_penalty_lr = float(cfg.mask_penalty_lr) if cfg.mask_penalty_lr is not None else float(cfg.mask_lr)
+        self.hard_mask_type = str(getattr(cfg, "hard_mask_type", "match") or "match")
+        self.hardening_x = 1.0
+        self.SLoRB = cfg.SLoRB
+        if self.SLoRB:
+            raise NotImplementedError("SLoRB bypass is outside this path")
+        # device-side caches (not part of the state dict)
+        self._wm = None          # W * cast(M_eff) in the weight dtype
+        self._wm_key = None      # what the cache was built from
+        self._meta = None        # packed 2:4 metadata of top2(mask)
+        self._score = None
+        self._norm = None
+        self._stats = None
+        self._scratch = None
+        self.last_mask_stats = None  # device float64[8] written by the last update_mask
+
+    # -- helpers -------------------------------------------------------------------------
+    def _is_placeholder(self, name: str) -> bool:
+        return getattr(self, f"_{name}_placeholder", False)
+
+    def _resolved_hard_type(self) -> str:
+        return self.mask_type if self.hard_mask_type == "match" else self.hard_mask_type
+
+    def _buffers_ready(self):
+        dev = self.weight.device
+        if self._score is None or self._score.device != dev or self._score.shape != self.weight.shape:
+            self._score = torch.empty(self.weight.shape, dtype=torch.float32, device=dev)
+            self._norm = torch.zeros(2, dtype=torch.float32, device=dev)
+            self._stats = torch.zeros(_lib.MSTAT_COUNT, dtype=torch.float64, device=dev)
+            self._scratch = ops.hutch_score_scratch(dev)
+            self._meta = torch.zeros((self.out_features, (self.in_features + 7) // 8), dtype=torch.uint8, device=dev)
+            self._wm = torch.empty_like(self.weight.data)
+            self._wm_key = None
+
+    def _check_2to4(self):
+        if int(self.N) != 2 or int(self.M) != 4:
+            raise NotImplementedError(f"N:M = {self.N}:{self.M}: only 2:4 is implemented")
+        if self.in_features % 8 != 0:
+            raise ValueError(f"in_features ({self.in_features}) must be a multiple of 8 for the 2:4 kernels")
+
+    @torch.no_grad()
+    def initialize(self):
+        """legacy/sparse_modeling.py:410-439."""
+        self.mask.fill_(1.0)
+        if not self._is_placeholder("grad_ema"):
+            self.grad_ema.zero_()
+        if not self._is_placeholder("hessian_diag"):
+            self.hessian_diag.fill_(1.0 if self.mask_metric == "hessian_obd" else 0.0)
+        self.sync_weight()
+        self.invalidate_masked_weight()
+
+    @torch.no_grad()
+    def sync_weight(self):
+        """legacy/sparse_modeling.py:441-458."""
+        self.weight.mask = self.mask
+        self.weight._sf_owner = weakref.ref(self)
+        self.weight.flipped_mask = int(getattr(self.weight, "flipped_mask", 0))
+        self.weight.init_flipped_mask = int(getattr(self.weight, "init_flipped_mask", 0))
+        self.weight.param_count = int(getattr(self.weight, "param_count", self.weight.numel()))
+
+    def _blockify_tensor(self, tensor):
+        if self.hard_mask_type in ("block_sparse16", "block_sparse32"):
+            raise NotImplementedError("block-sparse soft masks are outside the 2:4 kernel path")
+        return tensor
+
+    # -- hard projection -----------------------------------------------------------------
+    @torch.no_grad()
+    def _hard_mask_from_soft(self, soft_mask: torch.Tensor) -> torch.Tensor:
+        """legacy/sparse_modeling.py:510-735 for 'none', 'unstructured', 'structured', 'nm_2_4'."""
+        mt = self._resolved_hard_type()
+        if mt == "none":
+            return torch.ones_like(soft_mask)
+        if mt == "unstructured" or soft_mask.dim() != 2:
+            return (soft_mask > 0.5).to(dtype=soft_mask.dtype)
+        if mt == "nm_2_4":
+            return ops.project_nm24(soft_mask)[0]
+        if mt != "structured":
+            raise ValueError(f"Invalid hard mask_type: {mt}")
+        if int(self.N) != 2 or int(self.M) != 4:
+            raise NotImplementedError(f"N:M = {self.N}:{self.M}: only 2:4 is implemented")
+        if soft_mask.shape[1] % 4 != 0:
+            raise ValueError(f"in_features ({soft_mask.shape[1]}) must be divisible by M ({self.M}).")
+        return ops.project_nm24(soft_mask)[0]
+
+    @torch.no_grad()
+    def metadata(self) -> torch.Tensor:
+        """Packed 2:4 metadata of top2(mask) ([out, in/8] uint8), as left by the last mask update
+        or masked-weight refresh."""
+        self.masked_weight()
+        return self._meta
+
+    # -- masked weight cache ---------------------------------------------------------------
+    def invalidate_masked_weight(self):
+        """Call after changing ``weight`` or ``mask`` outside ``update_mask`` / the AdamW of this package."""
+        self._wm_key = None
+
+    def _adamw_emit_target(self):
+        """(wm buffer, hx) the AdamW kernel should write the new masked weight with."""
+        self._check_2to4()
+        self._buffers_ready()
+        fin = bool(getattr(self, "_hardening_finalized", False))
+        return self._wm, (1.0 if fin else float(self.hardening_x))
+
+    def _adamw_emitted(self):
+        self._wm_key = self._current_key()
+        self.weight._sf_wm_stale = False
+        self.weight._sf_managed = True
+
+    def _current_key(self):
+        fin = bool(getattr(self, "_hardening_finalized", False))
+        return (self.weight.data_ptr(), self.weight._version, self.mask.data_ptr(), self.mask._version,
+                float(self.hardening_x), fin, self.weight.dtype)
+
+    @torch.no_grad()
+    def masked_weight(self) -> torch.Tensor:
+        """W * cast(M_eff). Rebuilt on every call unless this package's AdamW manages the weight (it
+        and ``update_mask`` then rewrite the cache whenever they change weight or mask); under a
+        managed weight, code that edits ``weight.data`` or ``mask.data`` itself must call
+        ``invalidate_masked_weight()``."""
+        self._check_2to4()
+        self._buffers_ready()
+        key = self._current_key()
+        managed = getattr(self.weight, "_sf_managed", False)  # set by this package's AdamW
+        if (not managed) or self._wm_key != key or getattr(self.weight, "_sf_wm_stale", True):
+            ops.effective_weight(self.weight.data, self.mask.data, self._wm, meta=self._meta,
+                                 hx=float(self.hardening_x), finalized=key[5])
+            self._wm_key = key
+            self.weight._sf_wm_stale = False
+        return self._wm
+
+    # -- forward -----------------------------------------------------------------------------
+    def _compute_weight_scale_factor(self) -> float:
+        """legacy/sparse_modeling.py:799-827."""
+        mt = self._resolved_hard_type()
+        if mt == "none":
+            return 1.0
+        if mt == "structured":
+            n, m = int(self.N), int(self.M)
+            return 1.0 if (n <= 0 or m <= 0 or n >= m) else float(m) / float(n)
+        if mt == "nm_2_4":
+            return 2.0
+        sr = float(self.sparsity_ratio)
+        return 1.0 if (sr <= 0.0 or sr >= 1.0) else 1.0 / (1.0 - sr)
+
+    def forward(self, x):
+        """legacy/sparse_modeling.py:737-796."""
+        if self.mode == "dense_forward" or self.mask_type == "none":
+            ones = torch.ones_like(self.mask.data)
+            return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)
+        if self.mode != "sparse_forward":
+            raise ValueError(f"Invalid mode: {self.mode}")
+        if self._resolved_hard_type() not in ("structured", "nm_2_4"):
+            raise NotImplementedError(f"hard mask type {self._resolved_hard_type()!r} is outside the 2:4 kernel path")
+        hx = float(getattr(self, "hardening_x", 1.0))
+        finalized = bool(getattr(self, "_hardening_finalized", False))
+        scale = 1.0
+        if getattr(self.cfg, "weight_scaling", False) and hx < 1.0 - 1e-6:
+            scale = 1.0 + (1.0 - hx) * (self._compute_weight_scale_factor() - 1.0)
+        wm = self.masked_weight()
+        return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized)
+
+    # -- grad / hessian EMA ----------------------------------------------------------------
+    @torch.no_grad()
+    def update_grad_hessian_ema(self, update_hessian_with_grad2: bool = True):
+        """legacy/sparse_modeling.py:901-922 (including its early return for every metric but movement)."""
+        if self._is_placeholder("grad_ema") or self.weight.grad is None:
+            return
+        g = self.weight.grad.detach()
+        if g.shape != self.grad_ema.shape:
+            if g.numel() != self.grad_ema.numel():
+                return
+            g = g.view_as(self.grad_ema)
+        b = float(self.cfg.beta)
+        self.grad_ema.mul_(b).add_(g, alpha=1 - b)
+        if update_hessian_with_grad2 and not self._is_placeholder("hessian_diag"):
+            self.hessian_diag.mul_(b).add_((g * g).float(), alpha=1 - b)
+
+    def update_importance_ema(self):
+        pass
+
+    @torch.no_grad()
+    def accumulate_hutchinson(self, hvp: torch.Tensor, v: torch.Tensor, beta: Optional[float] = None):
+        """H <- beta H + (1-beta) max(hvp * v, 0), fused with the score of the current weights
+        (elementwise tail of update_hessian_hutchinson, legacy/utils.py:804-868)."""
+        if self._is_placeholder("hessian_diag"):
+            return
+        self._buffers_ready()
+        ops.hutch_score(self.weight.data, self.hessian_diag.data, self._score, self._norm, self._scratch,
+                        hvp=hvp.contiguous(), v=v.contiguous(), beta=float(self.cfg.beta if beta is None else beta),
+                        metric=self.mask_metric if self.mask_metric in _SUPPORTED_METRICS else "hessian_obd")
+
+    # -- schedules (host scalars) --------------------------------------------------------------
+    def _mask_update_period(self, step: int) -> int:
+        """legacy/sparse_modeling.py:944-952."""
+        base = int(getattr(self.cfg, "mask_update_period", 10))
+        sw = int(getattr(self.cfg, "mask_update_switch_step", 0) or 0)
+        before = getattr(self.cfg, "mask_update_period_before", None)
+        after = getattr(self.cfg, "mask_update_period_after", None)
+        if sw > 0 and before is not None and after is not None:
+            return int(before) if step < sw else int(after)
+        return base
+
+    def _temperature(self, step: int) -> float:
+        """legacy/sparse_modeling.py:932-942."""
+        k = max(1, int(self._mask_update_period(step)))
+        t = float(self.cfg.temp_init) * (float(self.cfg.temp_decay) ** (step // k))
+        return float(max(float(self.cfg.temp_min), t))
+
+    def _effective_sparsity(self, step: int) -> float:
+        """legacy/sparse_modeling.py:954-964."""
+        warm = int(self.cfg.sparsity_warmup_steps)
+        if warm <= 0:
+            return float(self.sparsity_ratio)
+        return float(self.sparsity_ratio * min(1.0, max(0.0, step / max(1, warm))))
+
+    def _beta_structural(self, step: int) -> float:
+        """legacy/sparse_modeling.py:966-985."""
+        start = int(getattr(self.cfg, "beta_structural_start", 0))
+        end = int(getattr(self.cfg, "beta_structural_end", 0))
+        if end <= start or step < start:
+            return 0.0
+        if step >= end:
+            return 1.0
+        t = float(step - start) / float(end - start)
+        return float(3.0 * t * t - 2.0 * t * t * t)
+
+    def _next_hardening_x(self, step: int) -> float:
+        """legacy/sparse_modeling.py:1603-1619."""
+        start = int(getattr(self.cfg, "mask_hardening_start", 0))
+        duration = int(getattr(self.cfg, "mask_hardening_duration", 0))
+        if duration <= 0:
+            return 0.0 if (step >= start and start > 0) else 1.0
+        if step < start:
+            return 1.0
+        if step >= start + duration:
+            return 0.0
+        return max(0.0, min(1.0, 1.0 - float(step - start) / float(max(1, duration))))
+
+    # -- score and gate ---------------------------------------------------------------------
+    @torch.no_grad()
+    def _refresh_score(self):
+        """Raw score of the current weights and its mean / std, without touching the Hessian."""
+        self._buffers_ready()
+        metric = self.mask_metric
+        if metric not in _SUPPORTED_METRICS:
+            metric = "magnitude"
+        H = None if self._is_placeholder("hessian_diag") else self.hessian_diag.data
+        if H is None and metric in ("hessian_obd", "hessian_ratio", "hessian"):
+            metric = "magnitude"
+        aux = None
+        if metric == "movement":
+            if self._is_placeholder("grad_ema"):
+                metric = "magnitude"
+            else:
+                aux = self.grad_ema.data
+        ops.hutch_score(self.weight.data, H, self._score, self._norm, self._scratch, aux=aux,
+                        aux_scalar=float(self.cfg.temperature), metric=metric)
+
+    def _score_is_bf16(self) -> bool:
+        # the reference's score has dtype promote(weight, hessian): bf16 only when no fp32 Hessian enters
+        return self.weight.dtype == torch.bfloat16 and self.mask_metric in ("magnitude", "movement")
+
+    @torch.no_grad()
+    def compute_gate_target(self, step: int) -> torch.Tensor:
+        """Soft gate G of legacy/sparse_modeling.py:1018-1239 (structured branch), as a tensor.
+        Runs the fused update kernel on a copy of the mask with mask_lr = 1 and no penalty, which
+        leaves exactly G in the copy."""
+        if (not self.change_mask) or (self.mask_type == "none"):
+            return torch.ones_like(self.mask)
+        if self.mask_type != "structured":
+            raise NotImplementedError("only mask_type='structured' is implemented on this path")
+        self._check_2to4()
+        self._refresh_score()
+        G = torch.zeros_like(self.mask.data)
+        stats = torch.zeros(_lib.MSTAT_COUNT, dtype=torch.float64, device=G.device)
+        ops.mask_update_nm24(self._score, self._norm, G, stats, temperature=self._temperature(step), mask_lr=1.0,
+                             beta_s=self._beta_structural(step),
+                             structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
+                             score_bf16=self._score_is_bf16())
+        return G
+
+    # -- periodic mask update ---------------------------------------------------------------
+    @torch.no_grad()
+    def update_mask(self, step: int, lambda_mid: float = 0.0, score_ready: bool = False):
+        """legacy/sparse_modeling.py:1242-1666. One kernel: gate, penalty, EMA, hard projection,
+        effective masked weight, metadata, flip count and mask sums. ``score_ready=True`` reuses
+        the score left by ``accumulate_hutchinson`` in this step (weights unchanged since)."""
+        if self.mask.numel() == 0:
+            return
+        if self.mask.dim() != 2 or self.weight.shape != self.mask.shape:
+            return
+        if (not self.change_mask) or (self.mask_type == "none"):
+            self.weight.flipped_mask = 0
+            self.weight.init_flipped_mask = 0
+            return
+        if step < int(self.cfg.sparsity_warmup_steps):
+            return
+        if step % max(1, int(self._mask_update_period(step))) != 0:
+            return
+        if self.mask_type != "structured":
+            raise NotImplementedError("only mask_type='structured' is implemented on this path")
+        self._check_2to4()
+        if not score_ready:
+            self._refresh_score()
+        lam = 0.0 if lambda_mid is None else float(lambda_mid)
+        mode = str(getattr(self.cfg, "mask_penalty_mode", "mid") or "mid")
+        if lam != 0.0 and mode not in ("mid", "structured_topn", "nm_2_4"):
+            raise NotImplementedError(f"mask_penalty_mode={mode!r} is outside the 2:4 kernel path")
+        pmode = _lib.PENALTY_MID if mode == "mid" else _lib.PENALTY_TOPN
+        hx_new = self._next_hardening_x(step)
+        ops.mask_update_nm24(self._score, self._norm, self.mask.data, self._stats, W=self.weight.data, wm=self._wm,
+                             meta=self._meta, temperature=self._temperature(step), mask_lr=float(self.cfg.mask_lr),
+                             pen=float(self.mask_penalty_lr) * lam, penalty_mode=pmode if lam != 0.0 else 0,
+                             beta_s=self._beta_structural(step),
+                             binarize_decay=float(getattr(self.cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
+                             structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
+                             score_bf16=self._score_is_bf16())
+        self.hardening_x = hx_new
+        self.last_mask_stats = self._stats
+        self._wm_key = self._current_key()
+        self.weight._sf_wm_stale = False
+        # The flip count stays on the device; reading the attribute costs one synchronisation.
+        self.weight.flipped_mask = _LazyInt(self._stats, _lib.MSTAT_FLIPS)
+        self.weight.init_flipped_mask = 0
+        self.weight.mask = self.mask
+
+
+class _LazyInt:
+    """Integer that lives in a device tensor until somebody looks at it."""
+
+    __slots__ = ("_t", "_i", "_v")
+
+    def __init__(self, t, i):
+        self._t, self._i, self._v = t.clone(), i, None
+
+    def __int__(self):
+        if self._v is None:
+            self._v = int(self._t[self._i].item())
+        return self._v
+
+    __index__ = __int__
+
+    def __repr__(self):
+        return str(int(self))
+
+    def __eq__(self, other):
+        return int(self) == int(other)
+
+    def __add__(self, other):
+        return int(self) + int(other)
+
+    __radd__ = __add__

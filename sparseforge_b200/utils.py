@@ -1,0 +1,239 @@
+"""Model-level drivers of the mask / Hessian path.
+
+Host-side mirror of the functions the reference training loop imports from ``legacy/utils.py``
+(``legacy/main_llama.py:32-50``) that belong to the SparseLinear hot path. Each walks the model's
+``SparseLinear`` modules and calls their kernels; layer-wide scalars stay on the device until the
+caller reads them. Evaluation, calibration and logging helpers of that file are not part of this
+path.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.distributed as dist
+
+from . import _lib, ops
+from .sparse_modeling import SparseLinear
+
+
+def get_raw_model(model):
+    """Innermost student / base model (legacy/utils.py:59-88)."""
+    if hasattr(model, "_fsdp_wrapped_module"):
+        inner = model._fsdp_wrapped_module
+        if hasattr(inner, "student"):
+            student = inner.student
+            return getattr(student, "_fsdp_wrapped_module", student)
+        return inner
+    if hasattr(model, "module"):
+        return model.module.student if hasattr(model.module, "student") else model.module
+    if hasattr(model, "student"):
+        student = model.student
+        return getattr(student, "_fsdp_wrapped_module", student)
+    return model
+
+
+def _sparse_modules(model):
+    return [m for _, m in get_raw_model(model).named_modules() if isinstance(m, SparseLinear)]
+
+
+@torch.no_grad()
+def set_model_mode(model, mode: str):
+    """legacy/utils.py:91-95."""
+    for m in _sparse_modules(model):
+        m.mode = mode
+
+
+@torch.no_grad()
+def sync_weight(model, device=None):
+    """legacy/utils.py:99-106."""
+    if device is not None:
+        model = model.to(device)
+    for m in _sparse_modules(model):
+        m.sync_weight()
+        m.invalidate_masked_weight()
+
+
+@torch.no_grad()
+def initialize_model(model):
+    """legacy/utils.py:110-116."""
+    for m in _sparse_modules(model):
+        m.initialize()
+
+
+@torch.no_grad()
+def update_model_grad_ema(model, update_hessian_with_grad2: bool = True):
+    """legacy/utils.py:122-134."""
+    for m in _sparse_modules(model):
+        m.update_grad_hessian_ema(update_hessian_with_grad2=update_hessian_with_grad2)
+
+
+@torch.no_grad()
+def update_mask_penalty_lr(model, step: int, max_steps: int, penalty_lr_min: float, penalty_lr_max: float,
+                           schedule: str = "linear"):
+    """legacy/utils.py:141-180."""
+    if schedule == "linear":
+        cur = penalty_lr_min + (penalty_lr_max - penalty_lr_min) * min(1.0, step / max(1, max_steps))
+    elif schedule == "cosine":
+        f = 0.5 * (1.0 - math.cos(math.pi * min(1.0, step / max(1, max_steps))))
+        cur = penalty_lr_min + (penalty_lr_max - penalty_lr_min) * f
+    else:
+        cur = penalty_lr_max
+    for m in _sparse_modules(model):
+        m.mask_penalty_lr = cur
+    return cur
+
+
+@torch.no_grad()
+def calculate_model_mask(model, step=0, lambda_mid: float = 0.0):
+    """legacy/utils.py:183-310. The mask update of a layer is local to its rows, so no parameter is
+    gathered first (the reference summons every FSDP parameter here)."""
+    for m in _sparse_modules(model):
+        if getattr(m.cfg, "glu_joint_mask", False):
+            raise NotImplementedError("glu_joint_mask is outside the structured 2:4 kernel path")
+        m.update_mask(step, lambda_mid=lambda_mid)
+
+
+@torch.no_grad()
+def calculate_flip_rate(model):
+    """legacy/utils.py:691-704."""
+    flipped = init_flipped = total = 0
+    for m in _sparse_modules(model):
+        flipped += int(getattr(m.weight, "flipped_mask", 0))
+        init_flipped += int(getattr(m.weight, "init_flipped_mask", 0))
+        total += int(getattr(m.weight, "param_count", m.weight.numel()))
+    return flipped, flipped / max(total, 1), init_flipped, init_flipped / max(total, 1)
+
+
+def _rademacher_like(t: torch.Tensor) -> torch.Tensor:
+    """+-1 probe in the dtype of ``t`` (legacy/utils.py:710-711)."""
+    return (torch.randint_like(t, low=0, high=2, dtype=torch.int8).float() * 2 - 1).to(dtype=t.dtype, device=t.device)
+
+
+def update_hessian_hutchinson(model, loss):
+    """Hutchinson estimate diag(H) ~ E[(Hv) * v] for every SparseLinear weight
+    (legacy/utils.py:714-868). The two autograd passes run through the differentiable tcgen05
+    products; the accumulation, clamp and EMA are one fused kernel per layer, which also leaves
+    the layer's importance score ready for the next mask update."""
+    owners = _sparse_modules(model)
+    if not owners:
+        return
+    params = [m.weight for m in owners]
+    try:
+        grads = torch.autograd.grad(loss, params, create_graph=True, retain_graph=True, allow_unused=True)
+        dot, vs = None, []
+        for g, p in zip(grads, params):
+            if g is None:
+                vs.append(None)
+                continue
+            v = _rademacher_like(p)
+            vs.append(v)
+            term = (g * v).sum()
+            dot = term if dot is None else dot + term
+        hvps = [None] * len(params) if dot is None else torch.autograd.grad(dot, params, retain_graph=True,
+                                                                              allow_unused=True)
+    except RuntimeError as e:
+        raise RuntimeError(f"[Hutchinson] Double-backward failed: {e}") from e
+    world = dist.get_world_size() if (dist.is_available() and dist.is_initialized()) else 1
+    for m, hvp, v in zip(owners, hvps, vs):
+        if hvp is None or v is None or m._is_placeholder("hessian_diag"):
+            continue
+        if world > 1 and hvp.shape == m.hessian_diag.shape and not getattr(m, "_row_sharded", False):
+            # data-parallel replicas average clamp(hvp*v, 0) (legacy/utils.py:860-865); the clamp
+            # commutes with nothing, so it is applied before the reduction as there.
+            d = torch.clamp((hvp * v).detach(), min=0.0)
+            dist.all_reduce(d, op=dist.ReduceOp.SUM)
+            d.div_(world)
+            m.accumulate_hutchinson(d, torch.ones_like(v))
+        else:
+            m.accumulate_hutchinson(hvp.detach(), v)
+
+
+def _layer_stats(m: SparseLinear) -> torch.Tensor:
+    stats = torch.zeros(_lib.MSTAT_COUNT, dtype=torch.float64, device=m.mask.device)
+    ops.mask_stats(m.mask.data, stats)
+    return stats
+
+
+def _all_reduce(t: torch.Tensor) -> torch.Tensor:
+    if dist.is_available() and dist.is_initialized():
+        dist.all_reduce(t, op=dist.ReduceOp.SUM)
+    return t
+
+
+@torch.no_grad()
+def mid_penalty(model, lambda_mid: float = 0.0):
+    """lambda * mean(m (1 - m)) over every mask (legacy/utils.py:875-938)."""
+    mods = [m for m in _sparse_modules(model) if m.mask.numel() > 0]
+    device = mods[0].mask.device if mods else torch.device("cuda")
+    if lambda_mid <= 0 or not mods:
+        return torch.tensor(0.0, device=device)
+    acc = torch.zeros(2, dtype=torch.float64, device=device)
+    for m in mods:
+        s = _layer_stats(m)
+        if not bool(torch.isfinite(s[_lib.MSTAT_SUM_M1M])):
+            continue
+        acc[0] += s[_lib.MSTAT_SUM_M1M]
+        acc[1] += float(m.mask.numel())
+    _all_reduce(acc)
+    if float(acc[1]) <= 0:
+        return torch.tensor(0.0, device=device)
+    res = lambda_mid * acc[0] / acc[1]
+    return res.to(torch.float32) if bool(torch.isfinite(res)) else torch.tensor(0.0, device=device)
+
+
+@torch.no_grad()
+def sparsity_penalty(model, target_sparsity: float = 0.5, alpha: float = 0.0):
+    """Global hard sparsity and alpha * (sparsity - target)^2 (legacy/utils.py:941-1025); structured
+    2-D masks count (M-N)/M analytically as there."""
+    mods = [m for m in _sparse_modules(model) if m.mask.numel() > 0]
+    device = mods[0].mask.device if mods else torch.device("cuda")
+    acc = torch.zeros(2, dtype=torch.float64, device=device)
+    for m in mods:
+        mk = m.mask.detach()
+        if getattr(m, "mask_type", "unstructured") == "structured" and mk.dim() == 2 and mk.shape[1] % int(m.M) == 0:
+            acc[0] += float(mk.shape[0] * (mk.shape[1] // int(m.M)) * (int(m.M) - int(m.N)))
+        else:
+            acc[0] += (mk < 0.5).double().sum()
+        acc[1] += float(mk.numel())
+    _all_reduce(acc)
+    cur = float(acc[0] / acc[1]) if float(acc[1]) > 0 else 0.0
+    pen = torch.tensor(float(alpha * (cur - float(target_sparsity)) ** 2) if alpha != 0.0 else 0.0, device=device)
+    return pen, cur
+
+
+@torch.no_grad()
+def nm_2_4_tile_stats(model, debug=False):
+    """Average of the two largest / two smallest mask values per group of 4
+    (legacy/utils.py:1028-1234)."""
+    mods = [m for m in _sparse_modules(model) if m.mask.dim() == 2 and m.mask.shape[1] % 4 == 0 and m.mask.numel() > 0]
+    zero = {"top2_avg": 0.0, "bot2_avg": 0.0, "top2_gap": 0.0, "bot2_gap": 0.0, "total_gap": 0.0}
+    if not mods:
+        return zero
+    acc = torch.zeros(3, dtype=torch.float64, device=mods[0].mask.device)
+    for m in mods:
+        s = _layer_stats(m)
+        acc[0] += s[_lib.MSTAT_SUM_TOP2]
+        acc[1] += s[_lib.MSTAT_SUM_BOT2]
+        acc[2] += float(m.mask.numel() // 4)
+    _all_reduce(acc)
+    tiles = float(acc[2])
+    if tiles <= 0:
+        return zero
+    top2, bot2 = float(acc[0]) / (tiles * 2), float(acc[1]) / (tiles * 2)
+    return {"top2_avg": top2, "bot2_avg": bot2, "top2_gap": 1.0 - top2, "bot2_gap": bot2,
+            "total_gap": (1.0 - top2) + bot2}
+
+
+@torch.no_grad()
+def finalize_hard_masks(model):
+    """End-of-training bake-in (legacy/main_llama.py:2552-2563): mask <- top2(mask), weight *= mask,
+    mask updates off, forward uses the mask as is."""
+    for m in _sparse_modules(model):
+        hard = m._hard_mask_from_soft(m.mask.data)
+        m.mask.data.copy_(hard)
+        m.weight.data.mul_(m.mask.data.to(m.weight.dtype))
+        m.change_mask = False
+        m._hardening_finalized = True
+        m.hardening_x = 0.0
+        m.invalidate_masked_weight()

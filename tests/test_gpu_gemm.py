@@ -1,0 +1,191 @@
+"""GPU parity of the masked GEMMs (tcgen05 bf16 path and fp32 FMA path) and of the module-level
+chain against the reference-generated fixtures. The reference for a GEMM is the fp32 product of the
+same (already rounded) inputs; tolerance 1e-2 for bf16 results, 1e-5 for fp32, relative to the
+largest reference magnitude."""
+import pytest
+import torch
+
+from oracle import sparselinear_oracle as O
+from tests.golden_io import Golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 1e-2
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from sparseforge_b200 import ops as _ops
+
+    return _ops
+
+
+def ref_products(x, w, dy):
+    """fp64 products of the given tensors, computed on the GPU by torch (the checker only)."""
+    xd, wd, dyd = x.double(), w.double(), dy.double()
+    return xd @ wd.t(), dyd @ wd, dyd.t() @ xd
+
+
+def check_status(status):
+    assert int(status[0]) == 0, f"a device-side wait ran out, code {int(status[0])}"
+
+
+# ragged sizes exercise partial tiles in M, N and K; the last rows are LLaMA-2-7B layer shapes
+BF16_SHAPES = [
+    (128, 64, 256),
+    (8, 8, 8),
+    (136, 72, 264),
+    (1000, 200, 520),
+    (256, 4096, 512),
+    (2048, 1024, 1280),
+    (8192, 4096, 4096),
+    (8192, 4096, 11008),
+    (8192, 11008, 4096),
+]
+
+
+@pytest.mark.parametrize("T,k,n", BF16_SHAPES)
+def test_bf16_products(ops, T, k, n):
+    torch.manual_seed(T + k + n)
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
+    dy = torch.randn(T, n, device=DEV).to(torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    y = ops.gemm_fwd(x, w, status=status)
+    dx = ops.gemm_dgrad(dy, w, status=status)
+    dw = ops.gemm_wgrad(dy, x, status=status)
+    torch.cuda.synchronize()
+    check_status(status)
+    if T * k * n <= 2048 * 1024 * 1280:
+        ry, rdx, rdw = ref_products(x, w, dy)
+    else:
+        ry, rdx, rdw = (x.float() @ w.float().t()), (dy.float() @ w.float()), (dy.float().t() @ x.float())
+    assert rel_err(y, ry) <= BF16_TOL
+    assert rel_err(dx, rdx) <= BF16_TOL
+    assert rel_err(dw, rdw) <= BF16_TOL
+
+
+def test_bf16_bias_and_scale(ops):
+    torch.manual_seed(0)
+    x = torch.randn(200, 128, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(320, 128, device=DEV) * 0.05).to(torch.bfloat16)
+    b = torch.randn(320, device=DEV).to(torch.bfloat16)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    y = ops.gemm_fwd(x, w, bias=b, alpha=1.5, status=status)
+    check_status(status)
+    assert rel_err(y, 1.5 * (x.double() @ w.double().t()) + b.double()) <= BF16_TOL
+
+
+def test_bf16_linearity_at_full_size(ops):
+    """A size-independent property at the LLaMA gate/up shape: products are linear in x."""
+    torch.manual_seed(1)
+    T, k, n = 8192, 4096, 11008
+    x1 = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
+    y1 = ops.gemm_fwd(x1, w).float()
+    y2 = ops.gemm_fwd((x1.float() * 2).to(torch.bfloat16), w).float()  # exact doubling in bf16
+    assert rel_err(y2, 2 * y1) <= BF16_TOL
+    # row permutation of x permutes rows of y exactly
+    perm = torch.randperm(T, device=DEV)
+    yp = ops.gemm_fwd(x1[perm].contiguous(), w)
+    assert torch.equal(yp.float(), y1[perm])
+
+
+@pytest.mark.parametrize("T,k,n", [(40, 64, 96), (100, 72, 50), (8192, 768, 3072)])
+def test_f32_products(ops, T, k, n):
+    torch.manual_seed(T)
+    x = torch.randn(T, k, device=DEV)
+    w = torch.randn(n, k, device=DEV) * 0.02
+    dy = torch.randn(T, n, device=DEV)
+    ry, rdx, rdw = ref_products(x, w, dy)
+    assert rel_err(ops.gemm_fwd(x, w), ry) <= F32_TOL
+    assert rel_err(ops.gemm_dgrad(dy, w), rdx) <= F32_TOL
+    assert rel_err(ops.gemm_wgrad(dy, x), rdw) <= F32_TOL
+
+
+def test_bias_grad(ops):
+    torch.manual_seed(3)
+    for dtype, tol in ((torch.float32, F32_TOL), (torch.bfloat16, 1e-4)):
+        dy = torch.randn(1000, 328, device=DEV).to(dtype)
+        assert rel_err(ops.bias_grad(dy), dy.double().sum(0)) <= tol
+
+
+# ---------------------------------------------------------------------------------------
+# module-level chain against the reference run (same sequence as tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case,dtype,tol,steps_cfg", [
+    ("chain_f32", torch.float32, F32_TOL, dict(temp_init=1.0, mask_hardening_start=1000, mask_hardening_duration=10000)),
+    ("chain_bf16", torch.bfloat16, BF16_TOL, dict(temp_init=1.0, temp_min=0.05, temp_decay=0.05 ** (1.0 / 9.0),
+                                                   mask_hardening_start=1, mask_hardening_duration=3,
+                                                   mask_penalty_mode="structured_topn")),
+])
+def test_sparse_linear_chain(case, dtype, tol, steps_cfg):
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden(case)
+    W0, X, dY = g["W0"], g["X"].to(DEV), g["dY"].to(DEV)
+    out_f, in_f = W0.shape
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
+                                sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99, **steps_cfg)
+    layer = sf.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False).to(DEV).to(dtype)
+    layer.mask.data = layer.mask.data.float()
+    layer.hessian_diag.data = layer.hessian_diag.data.float()
+    layer.weight.data.copy_(W0.to(DEV))
+    layer.initialize()
+    opt = sf.AdamW([layer.weight], lr=1e-4, betas=(0.9, 0.95), weight_decay=0.1)
+    lam = g.scalar("lambda_mid")
+    T = X.shape[0] * X.shape[1]
+    probe = 0
+    # Float outputs are compared at the tolerance; whatever the next stage consumes is then reset
+    # to the reference's value so that each step checks one stage at a time.
+    for t in range(g.scalar("n_steps")):
+        assert layer.hardening_x == pytest.approx(g.scalar(f"s{t}_hx_fwd"))
+        Xr = X.clone().requires_grad_(True)
+        layer.weight.grad = None
+        Y = layer(Xr)
+        Y.backward(dY)
+        assert rel_err(Y.float(), g[f"s{t}_Y"].float()) <= tol
+        assert rel_err(Xr.grad.float(), g[f"s{t}_dX"].float()) <= tol
+        assert rel_err(layer.weight.grad.float(), g[f"s{t}_dW"].float()) <= tol
+        while probe < g.scalar(f"s{t}_probes_end"):
+            v = g[f"v_{probe}"].to(DEV).to(dtype)
+            U._rademacher_like = lambda tt, v=v: v.clone()
+            loss = (torch.nn.functional.gelu(layer(X).float()) * dY.float()).sum() / T
+            U.update_hessian_hutchinson(layer, loss)
+            # hvp comes out of second-order products of bf16/fp32 GEMMs: compare H, which the
+            # reference forms from it
+            assert rel_err(layer.hessian_diag.data, g[f"H_{probe}"]) <= (1e-4 if dtype == torch.float32 else tol)
+            layer.hessian_diag.data.copy_(g[f"H_{probe}"].to(DEV))
+            probe += 1
+        layer.weight.grad = g[f"s{t}_dW"].to(DEV)
+        opt.step(decay=2e-4)
+        st = opt.state[layer.weight]
+        assert rel_err(layer.weight.data.float(), g[f"s{t}_W_opt"].float()) <= tol
+        assert rel_err(st["exp_avg"].float(), g[f"s{t}_m"].float()) <= tol
+        assert rel_err(st["exp_avg_sq"].float(), g[f"s{t}_v"].float()) <= tol
+        layer.weight.data.copy_(g[f"s{t}_W_opt"].to(DEV))
+        st["exp_avg"].copy_(g[f"s{t}_m"].to(DEV)); st["exp_avg_sq"].copy_(g[f"s{t}_v"].to(DEV))
+        assert layer._temperature(t) == pytest.approx(g.scalar(f"s{t}_T"), rel=1e-12)
+        G = layer.compute_gate_target(t)
+        assert rel_err(G, g[f"s{t}_G"]) <= F32_TOL
+        prev = layer.mask.data.clone()
+        U.calculate_model_mask(layer, step=t, lambda_mid=lam)
+        assert rel_err(layer.mask.data, g[f"s{t}_mask"]) <= F32_TOL
+        assert layer.hardening_x == pytest.approx(g.scalar(f"s{t}_hx"))
+        assert int(layer.weight.flipped_mask) == O.flip_count(prev.cpu(), layer.mask.data.cpu())
+        layer.mask.data.copy_(g[f"s{t}_mask"].to(DEV))
+        layer.invalidate_masked_weight()
+        hard = layer._hard_mask_from_soft(layer.mask.data)
+        assert torch.equal(hard.cpu(), g[f"s{t}_hard"])
+        pen = U.mid_penalty(layer, 1.0)
+        assert float(pen) * layer.mask.numel() == pytest.approx(g.scalar(f"s{t}_mid_sum"), rel=1e-5)
+    flipped, ratio, _, _ = U.calculate_flip_rate(layer)
+    assert 0 <= ratio <= 1
+    _, cur = U.sparsity_penalty(layer, 0.5, 1.0)
+    assert cur == pytest.approx(0.5)
+    stats = U.nm_2_4_tile_stats(layer)
+    want = O.mask_stats(layer.mask.data.cpu())
+    assert stats["top2_avg"] == pytest.approx(want["sum_top2"] / (layer.mask.numel() / 2), rel=1e-5)

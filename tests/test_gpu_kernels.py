@@ -1,0 +1,282 @@
+"""GPU parity of every kernel against the CPU oracle and the reference-generated fixtures.
+
+All calls go through the C ABI (``sparseforge_b200.ops`` is a pointer-passing wrapper).
+Bars: bit-exact for hard masks, metadata and flip counts; 1e-5 (fp32) / 1e-2 (bf16) relative to
+the largest reference magnitude for scores, soft masks, GEMM outputs and optimizer state.
+"""
+import pytest
+import torch
+
+from oracle import sparselinear_oracle as O
+from tests.golden_io import Golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+F32_TOL = 1e-5
+BF16_TOL = 1e-2
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from sparseforge_b200 import ops as _ops
+
+    return _ops
+
+
+def dev(t):
+    return t.to(DEV).contiguous()
+
+
+def unpack_meta(meta, cols):
+    """[rows, cols/8] packed bytes -> 0/1 mask [rows, cols]."""
+    meta = meta.cpu()
+    rows = meta.shape[0]
+    nib = torch.stack([meta & 0xF, meta >> 4], dim=-1).view(rows, -1)[:, : cols // 4].long()
+    out = torch.zeros(rows, cols // 4, 4)
+    out.scatter_(-1, (nib & 3).unsqueeze(-1), 1.0)
+    out.scatter_(-1, (nib >> 2).unsqueeze(-1), 1.0)
+    return out.view(rows, cols)
+
+
+# ---------------------------------------------------------------------------------------
+# hard projection
+# ---------------------------------------------------------------------------------------
+def test_project_ties_bit_exact(ops):
+    g = Golden("ties")
+    for name in g["names"]:
+        soft, want = g[f"{name}_soft"], g[f"{name}_hard"]
+        hard, meta = ops.project_nm24(dev(soft), want_meta=True)
+        assert torch.equal(hard.cpu(), want), name
+        assert torch.equal(meta.cpu(), O.meta_from_hard(want)), name
+        assert torch.equal(unpack_meta(meta, soft.shape[1]), want), name
+        hb, _ = ops.project_nm24(dev(soft), out_dtype=torch.bfloat16)
+        assert torch.equal(hb.float().cpu(), want), name
+
+
+def test_project_ragged_tail_and_strides(ops):
+    g = Golden("ties")
+    soft, want = g["tail_soft"], g["tail_hard"]
+    hard, meta = ops.project_nm24(dev(soft), want_meta=True)
+    assert torch.equal(hard.cpu(), want)
+    assert torch.equal(meta.cpu(), O.meta_from_hard(want))
+    # a column slice of a wider tensor (row stride != cols)
+    wide = torch.rand(16, 96)
+    view = dev(wide)[:, 8:72]
+    h2, _ = ops.project_nm24(view)
+    assert torch.equal(h2.cpu(), O.hard_mask_from_soft(wide[:, 8:72].contiguous()))
+    # empty inputs
+    h3, m3 = ops.project_nm24(torch.empty(0, 64, device=DEV), want_meta=True)
+    assert h3.shape == (0, 64) and m3.shape == (0, 8)
+
+
+def test_project_nan_and_bf16_input(ops):
+    x = torch.tensor([[float("nan"), 1.0, 2.0, 3.0, 1.0, float("nan"), float("nan"), 0.0]])
+    hard, _ = ops.project_nm24(dev(x))
+    assert torch.equal(hard.cpu(), O.hard_mask_from_soft(x))
+    xb = torch.rand(32, 64).to(torch.bfloat16)
+    hb, _ = ops.project_nm24(dev(xb))
+    assert torch.equal(hb.float().cpu(), O.hard_mask_from_soft(xb.float()))
+
+
+@pytest.mark.parametrize("shape", [(4096, 4096), (11008, 4096), (4096, 11008)])
+def test_project_llama_shapes_properties(ops, shape):
+    torch.manual_seed(100)
+    w = (torch.randn(shape) * 0.02).abs()
+    hard, meta = ops.project_nm24(dev(w), want_meta=True)
+    # exactly two kept per group, idempotent, metadata decodes to the mask, equal to the oracle
+    assert bool((hard.view(shape[0], -1, 4).sum(-1) == 2).all())
+    again, _ = ops.project_nm24(hard)
+    assert torch.equal(again, hard)
+    assert torch.equal(unpack_meta(meta, shape[1]), hard.cpu())
+    assert torch.equal(hard.cpu(), O.hard_mask_from_soft(w))
+
+
+# ---------------------------------------------------------------------------------------
+# Hutchinson accumulate + score
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("case", ["chain_f32", "chain_bf16"])
+def test_hutch_score_chain(ops, case):
+    g = Golden(case)
+    probe = 0
+    H = torch.ones(g["W0"].shape)
+    for t in range(g.scalar("n_steps")):
+        W = g[f"s{t}_W_fwd"]
+        while probe < g.scalar(f"s{t}_probes_end"):
+            Hd = dev(H)
+            score = torch.empty(W.shape, dtype=torch.float32, device=DEV)
+            norm = torch.zeros(2, dtype=torch.float32, device=DEV)
+            scratch = ops.hutch_score_scratch(DEV)
+            # int8 probe and weight-dtype probe must agree
+            ops.hutch_score(dev(W), Hd, score, norm, scratch, hvp=dev(g[f"hvp_{probe}"]), v=dev(g[f"v_{probe}"]), beta=0.99)
+            Hd2 = dev(H)
+            ops.hutch_score(dev(W), Hd2, score, norm, scratch, hvp=dev(g[f"hvp_{probe}"]),
+                            v=dev(g[f"v_{probe}"].to(W.dtype)), beta=0.99)
+            assert torch.equal(Hd, Hd2)
+            assert rel_err(Hd, g[f"H_{probe}"]) <= F32_TOL
+            want = O.importance_score(W, "hessian_obd", H=g[f"H_{probe}"])
+            assert rel_err(score, want) <= F32_TOL
+            mu, sigma = O.score_norm_stats(want)
+            assert abs(float(norm[0]) - float(mu)) <= F32_TOL * abs(float(mu))
+            assert abs(float(norm[1]) - float(sigma)) <= F32_TOL * abs(float(sigma))
+            H = g[f"H_{probe}"].clone()
+            probe += 1
+
+
+@pytest.mark.parametrize("metric", ["hessian_obd", "hessian_ratio", "magnitude", "hessian", "movement"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_score_metrics(ops, metric, dtype):
+    torch.manual_seed(1)
+    W = (torch.randn(64, 128) * 0.02).to(dtype)
+    H = torch.rand(64, 128) + 0.05
+    ge = (torch.randn(64, 128) * 0.01).to(dtype)
+    score = torch.empty(W.shape, dtype=torch.float32, device=DEV)
+    norm = torch.zeros(2, dtype=torch.float32, device=DEV)
+    ops.hutch_score(dev(W), dev(H), score, norm, ops.hutch_score_scratch(DEV), aux=dev(ge), aux_scalar=0.7, metric=metric)
+    want = O.importance_score(W, metric, H=H, grad_ema=ge, temperature=0.7)
+    tol = F32_TOL if (dtype == torch.float32 or metric in ("hessian",)) else BF16_TOL
+    assert rel_err(score, want.float()) <= tol
+    mu, sigma = O.score_norm_stats(score.cpu())
+    assert abs(float(norm[0]) - float(mu)) <= 1e-5 * abs(float(mu)) + 1e-12
+    assert abs(float(norm[1]) - float(sigma)) <= 1e-5 * abs(float(sigma))
+
+
+# ---------------------------------------------------------------------------------------
+# mask update
+# ---------------------------------------------------------------------------------------
+def run_mask_update(ops, W, H, mask0, *, T, mask_lr, pen, pmode, beta_s=0.0, bin_d=0.0, hx=1.0, exact=False):
+    Wd, Hd = dev(W), dev(H)
+    score = torch.empty(W.shape, dtype=torch.float32, device=DEV)
+    norm = torch.zeros(2, dtype=torch.float32, device=DEV)
+    ops.hutch_score(Wd, Hd, score, norm, ops.hutch_score_scratch(DEV))
+    mask = dev(mask0)
+    stats = torch.zeros(8, dtype=torch.float64, device=DEV)
+    wm = torch.empty_like(Wd)
+    meta = torch.zeros(W.shape[0], W.shape[1] // 8, dtype=torch.uint8, device=DEV)
+    ops.mask_update_nm24(score, norm, mask, stats, W=Wd, wm=wm, meta=meta, temperature=T, mask_lr=mask_lr, pen=pen,
+                         penalty_mode=pmode, beta_s=beta_s, binarize_decay=bin_d, hx=hx, structured_exact=exact)
+    return mask.cpu(), stats.cpu(), wm.cpu(), meta.cpu()
+
+
+@pytest.mark.parametrize("case,tol", [("chain_f32", F32_TOL), ("chain_bf16", BF16_TOL)])
+def test_mask_update_chain(ops, case, tol):
+    from sparseforge_b200 import _lib
+
+    g = Golden(case)
+    lam = g.scalar("lambda_mid")
+    for t in range(g.scalar("n_steps")):
+        W, H = g[f"s{t}_W_opt"], g[f"H_{g.scalar(f's{t}_probes_end') - 1}"]
+        mask0 = g[f"s{t}_mask_fwd"]
+        hx = g.scalar(f"s{t}_hx")
+        mask, stats, wm, meta = run_mask_update(ops, W, H, mask0, T=g.scalar(f"s{t}_T"), mask_lr=0.1, pen=0.1 * lam,
+                                                pmode=_lib.PENALTY_TOPN if lam else 0, hx=hx)
+        want = g[f"s{t}_mask"]
+        assert rel_err(mask, want) <= F32_TOL
+        hard_now = O.hard_mask_from_soft(mask)
+        # flips and metadata are exact functions of the masks the kernel itself produced
+        assert int(stats[_lib.MSTAT_FLIPS]) == O.flip_count(mask0, mask)
+        assert torch.equal(unpack_meta(meta, W.shape[1]), hard_now)
+        # and they agree with the reference wherever the reference's mask has no near-tie
+        if torch.equal(hard_now, g[f"s{t}_hard"]):
+            assert int(stats[_lib.MSTAT_FLIPS]) == g.scalar(f"s{t}_flips")
+        assert (hard_now != g[f"s{t}_hard"]).float().mean() <= 1e-3
+        st = O.mask_stats(mask)
+        assert abs(float(stats[_lib.MSTAT_SUM_M]) - st["sum_m"]) <= 1e-5 * st["sum_m"]
+        assert abs(float(stats[_lib.MSTAT_SUM_M1M]) - st["sum_m1m"]) <= 1e-5 * st["sum_m1m"] + 1e-9
+        assert abs(float(stats[_lib.MSTAT_SUM_TOP2]) - st["sum_top2"]) <= 1e-5 * st["sum_top2"]
+        assert abs(float(stats[_lib.MSTAT_SUM_BOT2]) - st["sum_bot2"]) <= 1e-5 * st["sum_bot2"] + 1e-9
+        assert float(stats[_lib.MSTAT_COUNT_LT_HALF]) == st["count_lt_half"]
+        want_wm = O.masked_weight(W, O.effective_mask(mask, hx))
+        assert rel_err(wm.float(), want_wm.float()) <= tol
+
+
+def test_mask_update_penalty_variants(ops):
+    from sparseforge_b200 import _lib
+
+    g = Golden("penalty")
+    pm = {"topn": 1, "nm24": 1, "mid": 2, "bin": 1, "beta": 2, "exact": 2, "lowT": 1}
+    for tag in g["variants"]:
+        lam = g.scalar(f"{tag}_lambda")
+        mask, stats, wm, meta = run_mask_update(
+            ops, g[f"{tag}_W"], g[f"{tag}_H"], g[f"{tag}_mask0"], T=g.scalar(f"{tag}_T"), mask_lr=0.2, pen=0.15 * lam,
+            pmode=pm[tag] if lam else 0, beta_s=g.scalar(f"{tag}_beta_s"), bin_d=0.05 if tag == "bin" else 0.0,
+            hx=g.scalar(f"{tag}_hx"), exact=(tag == "exact"))
+        assert rel_err(mask, g[f"{tag}_mask1"]) <= F32_TOL, tag
+        assert int(stats[_lib.MSTAT_FLIPS]) == O.flip_count(g[f"{tag}_mask0"], mask), tag
+        if torch.equal(O.hard_mask_from_soft(mask), O.hard_mask_from_soft(g[f"{tag}_mask1"])):
+            assert int(stats[_lib.MSTAT_FLIPS]) == g.scalar(f"{tag}_flips"), tag
+
+
+def test_gate_from_update_kernel(ops):
+    """mask_lr = 1 on a zero mask leaves exactly the gate G."""
+    g = Golden("penalty")
+    for tag in ("topn", "beta", "exact", "lowT"):
+        mask, _, _, _ = run_mask_update(ops, g[f"{tag}_W"], g[f"{tag}_H"], torch.zeros(g[f"{tag}_W"].shape),
+                                        T=g.scalar(f"{tag}_T"), mask_lr=1.0, pen=0.0, pmode=0,
+                                        beta_s=g.scalar(f"{tag}_beta_s"), exact=(tag == "exact"))
+        assert rel_err(mask, g[f"{tag}_G"]) <= F32_TOL, tag
+
+
+def test_effective_weight(ops):
+    torch.manual_seed(2)
+    for dtype, tol in ((torch.float32, F32_TOL), (torch.bfloat16, BF16_TOL)):
+        W = (torch.randn(48, 64) * 0.02).to(dtype)
+        mask = torch.rand(48, 64)
+        for hx, fin in ((1.0, False), (0.4, False), (0.0, False), (0.3, True)):
+            wm = torch.empty_like(dev(W))
+            meta = torch.zeros(48, 8, dtype=torch.uint8, device=DEV)
+            ops.effective_weight(dev(W), dev(mask), wm, meta=meta, hx=hx, finalized=fin)
+            want = O.masked_weight(W, O.effective_mask(mask, hx, finalized=fin))
+            assert rel_err(wm.float(), want.float()) <= tol
+            assert torch.equal(unpack_meta(meta, 64), O.hard_mask_from_soft(mask))
+
+
+# ---------------------------------------------------------------------------------------
+# AdamW
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("tag,tol,l1", [("f32", F32_TOL, 0.0), ("bf16", BF16_TOL, 0.0), ("l1", F32_TOL, 0.02)])
+def test_adamw_golden(ops, tag, tol, l1):
+    g = Golden("adamw")
+    p = dev(g[f"{tag}_p0"])
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    mask = dev(g[f"{tag}_mask"])
+    for t in range(3):
+        wm = torch.empty_like(p)
+        ops.adamw_masked(p, dev(g[f"{tag}_g{t}"]), m, v, mask=mask, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8,
+                         weight_decay=0.1, decay=5e-4 * (t + 1), step=t + 1, adaptive_l1=l1, wm=wm, hx=0.5)
+        assert rel_err(p.float(), g[f"{tag}_p{t + 1}"].float()) <= tol
+        assert rel_err(m.float(), g[f"{tag}_m{t + 1}"].float()) <= tol
+        assert rel_err(v.float(), g[f"{tag}_v{t + 1}"].float()) <= tol
+        want_wm = O.masked_weight(p.cpu(), O.effective_mask(mask.cpu(), 0.5))
+        assert rel_err(wm.float(), want_wm.float()) <= tol
+
+
+def test_adamw_no_mask(ops):
+    torch.manual_seed(4)
+    p0, g0 = torch.randn(1024) * 0.1, torch.randn(1024) * 0.01
+    p = dev(p0)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    ops.adamw_masked(p, dev(g0), m, v, lr=1e-3, beta1=0.9, beta2=0.999, eps=1e-8, weight_decay=0.01, decay=0.0, step=1)
+    wp, wm_, wv = O.adamw_step(p0, g0, torch.zeros(1024), torch.zeros(1024), step=1, lr=1e-3, betas=(0.9, 0.999),
+                               eps=1e-8, weight_decay=0.01)
+    assert rel_err(p, wp) <= F32_TOL and rel_err(m, wm_) <= F32_TOL and rel_err(v, wv) <= F32_TOL
+
+
+# ---------------------------------------------------------------------------------------
+# argument checks: bad calls are refused on the host, nothing is launched
+# ---------------------------------------------------------------------------------------
+def test_bad_arguments_are_refused(ops):
+    with pytest.raises(RuntimeError):
+        ops.project_nm24(torch.rand(8, 8))  # CPU tensor
+    score = torch.zeros(8, 12, device=DEV)
+    with pytest.raises(RuntimeError, match="multiple of 8"):
+        ops.mask_update_nm24(score, torch.zeros(2, device=DEV), torch.ones(8, 12, device=DEV),
+                             torch.zeros(8, dtype=torch.float64, device=DEV))
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        ops.gemm_fwd(torch.zeros(8, 12, device=DEV, dtype=torch.bfloat16), torch.zeros(16, 12, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        ops.gemm_fwd(torch.zeros(8, 16, device=DEV), torch.zeros(16, 24, device=DEV))
+    with pytest.raises(TypeError):
+        ops.gemm_fwd(torch.zeros(8, 16, device=DEV), torch.zeros(16, 16, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(TypeError):
+        ops.project_nm24(torch.zeros(8, 8, device=DEV, dtype=torch.float16))
