@@ -81,6 +81,35 @@ SF_API int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H,
                    float* norm, double* scratch, int64_t n, double beta, int metric,
                    void* stream);
 
+/*
+ * sf_hutch_score without a scratch argument: the partial sums go to an array that is part
+ * of the library image. This entry point has no counterpart in the reference. It is for
+ * callers that are not allowed to allocate device memory at the point where they need the
+ * score, for example a hook that runs in the middle of a training step while a caching
+ * allocator owns all free memory and a cudaMalloc would stall or fail, code that must not
+ * cause the implicit device synchronisation of cudaMalloc / cudaFree, or a process that runs
+ * under a fixed device-memory budget. The call allocates nothing, on the device or through
+ * any library. Inputs and outputs are still the caller's buffers, as in sf_hutch_score.
+ *
+ * Limits and rules:
+ *  - The array is 4096 doubles (32 KiB), resident on every GPU that loads the library until
+ *    the process ends. It holds the partial sums of at most 2048 thread blocks of 32768
+ *    elements, so n may not exceed SF_HUTCH_SCORE_STATIC_MAX_N (67,108,864 elements; the
+ *    largest LLaMA-2-7B matrix has 45,088,768). A larger n returns SF_ERR_UNSUPPORTED and
+ *    launches nothing; use sf_hutch_score with your own scratch then.
+ *  - The first call on each device looks up the array's device address (once per device,
+ *    with that device current). Make that first call outside any CUDA stream capture.
+ *  - All calls on one device share the array. It still holds the previous call's partial
+ *    sums when the next call starts; that is harmless because each call overwrites every
+ *    slot it later reads, and nothing needs to start at zero. Two calls that run on the GPU
+ *    at the same time (different streams) would overwrite each other's sums: serialise them.
+ */
+#define SF_HUTCH_SCORE_STATIC_MAX_N ((int64_t)67108864)
+SF_API int64_t sf_hutch_score_static_max_n(void);
+SF_API int sf_hutch_score_static(const void* hvp, const void* v, int v_dtype, float* H, const void* W,
+                                 int w_dtype, const void* aux, double aux_scalar, float* score,
+                                 float* norm, int64_t n, double beta, int metric, void* stream);
+
 /* Stats written by sf_mask_update_nm24 (8 doubles). */
 enum {
     SF_MSTAT_FLIPS = 0,       /* sum xor(hard(prev mask), hard(new mask)), :1659-1661 */

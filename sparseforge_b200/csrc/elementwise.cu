@@ -3,6 +3,8 @@
 // mask statistics, bias gradient. Each thread owns 8 consecutive elements (two 2:4
 // groups) and moves them with 16-byte streaming accesses; grids are sized from the
 // SM count and walk the tensor with a grid-stride loop.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace sf {
@@ -778,6 +780,63 @@ int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t out, v
     else bias_grad_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)dy, db, T, out, rpb);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// sf_hutch_score_static: the same pass with the partial-sum scratch held inside the library
+// ---------------------------------------------------------------------------------------
+// For callers that may not allocate device memory where they need the score: a hook in the
+// middle of a training step while a caching allocator holds all free memory, code that must
+// avoid the device-wide synchronisation that cudaMalloc and cudaFree imply, a process with a
+// fixed device-memory budget. The scratch of the score pass lives in the file-scope array
+// below instead of a caller buffer: 32 KiB on every GPU that loads the library, held until
+// the process exits. The entry point itself allocates nothing.
+namespace sf {
+constexpr int64_t kStaticScratchDoubles = 2 * (int64_t)kMaxPartialBlocks;
+static __device__ __align__(256) double g_static_score_scratch[kStaticScratchDoubles];
+
+constexpr int kMaxDevices = 64;
+static double* g_static_scratch_ptr[kMaxDevices];  // device address of the array, per device
+static std::mutex g_static_scratch_mu;
+
+// Device address of g_static_score_scratch on the current device. In host code the name of a
+// __device__ array is only a handle; the address a kernel can use comes from the runtime.
+static int static_scratch_address(double** out) {
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return fail(SF_ERR_UNSUPPORTED, "sf_hutch_score_static: device index %d beyond %d", dev, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        SF_CHECK_CUDA(cudaGetSymbolAddress(&p, g_static_score_scratch));
+        g_static_scratch_ptr[dev] = static_cast<double*>(p);
+    }
+    *out = g_static_scratch_ptr[dev];
+    return SF_OK;
+}
+}  // namespace sf
+
+extern "C" {
+
+int64_t sf_hutch_score_static_max_n(void) { return SF_HUTCH_SCORE_STATIC_MAX_N; }
+
+int sf_hutch_score_static(const void* hvp, const void* v, int v_dtype, float* H, const void* W, int w_dtype,
+                          const void* aux, double aux_scalar, float* score, float* norm, int64_t n, double beta,
+                          int metric, void* stream) {
+    if (n > SF_HUTCH_SCORE_STATIC_MAX_N)
+        return sf::fail(SF_ERR_UNSUPPORTED,
+                        "sf_hutch_score_static: n=%lld exceeds the built-in scratch limit of %lld elements; "
+                        "use sf_hutch_score with caller-provided scratch",
+                        (long long)n, (long long)SF_HUTCH_SCORE_STATIC_MAX_N);
+    double* scratch = nullptr;
+    int rc = sf::static_scratch_address(&scratch);
+    if (rc != SF_OK) return rc;
+    // Every partial-sum slot the kernels read is written earlier in the same call, so nothing
+    // has to be cleared between calls; calls that overlap on the GPU would mix their partials.
+    return sf_hutch_score(hvp, v, v_dtype, H, W, w_dtype, aux, aux_scalar, score, norm, scratch, n, beta, metric,
+                          stream);
 }
 
 }  // extern "C"
