@@ -267,6 +267,11 @@ SF_API int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* me
 SF_API int sf_bsr16_build(const void* W, const void* mask, int dtype, int mask_dtype, void* blocks,
                    int32_t* row_ptr, int32_t* col_idx, int32_t* nnz_out, int64_t out, int64_t in,
                    void* stream);
+/* Scatters the kept blocks into a dense row-major [out,in] matrix (zeros elsewhere); the
+ * device-side counterpart of the rebuild loop in BlockSparseLinear._torch_forward,
+ * legacy/triton_block_sparse.py:435-462. */
+SF_API int sf_bsr16_to_dense(const void* blocks, const int32_t* row_ptr, const int32_t* col_idx, void* dense,
+                             int64_t in, int64_t out, int dtype, void* stream);
 /*
  * Block-sparse-16 products.
  *   replaces: block_sparse_matmul_v2_kernel, legacy/triton_block_sparse.py:224-284 (fwd);
@@ -275,15 +280,18 @@ SF_API int sf_bsr16_build(const void* W, const void* mask, int dtype, int mask_d
  *   fwd  : y[T,out]  = x[T,in] . Wbsr^T (+ bias)
  *   dgrad: dx[T,in]  = dy[T,out] . Wbsr
  *   wgrad: dblocks[nnz,16,16] = (dy^T . x) at the kept blocks
+ * workspace: out*in elements of `dtype`, caller-owned, overwritten (the products run on the
+ * dense tensor-core tiles through it). status as in sf_masked_gemm_fwd.
  */
 SF_API int sf_bsr16_fwd(const void* x, const void* blocks, const int32_t* row_ptr, const int32_t* col_idx,
-                 const void* bias, void* y, int64_t T, int64_t in, int64_t out, int dtype,
-                 void* stream);
-SF_API int sf_bsr16_dgrad(const void* dy, const void* blocks, const int32_t* row_ptr,
-                   const int32_t* col_idx, void* dx, int64_t T, int64_t in, int64_t out, int dtype,
-                   void* stream);
+                        const void* bias, void* y, void* workspace, int64_t T, int64_t in, int64_t out,
+                        int dtype, int32_t* status, void* stream);
+SF_API int sf_bsr16_dgrad(const void* dy, const void* blocks, const int32_t* row_ptr, const int32_t* col_idx,
+                          void* dx, void* workspace, int64_t T, int64_t in, int64_t out, int dtype,
+                          int32_t* status, void* stream);
 SF_API int sf_bsr16_wgrad(const void* dy, const void* x, const int32_t* row_ptr, const int32_t* col_idx,
-                   void* dblocks, int64_t T, int64_t in, int64_t out, int dtype, void* stream);
+                          void* dblocks, void* workspace, int64_t T, int64_t in, int64_t out, int dtype,
+                          int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

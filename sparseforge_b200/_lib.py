@@ -43,9 +43,10 @@ _SIGNATURES = {
     "sf_sparse24_pack_meta": (c_int, [_P, _P, c_int64, c_int64, _P]),
     "sf_sparse24_gemm": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P]),
     "sf_bsr16_build": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int64, c_int64, _P]),
-    "sf_bsr16_fwd": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
-    "sf_bsr16_dgrad": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
-    "sf_bsr16_wgrad": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P]),
+    "sf_bsr16_to_dense": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, _P]),
+    "sf_bsr16_fwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_bsr16_dgrad": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_bsr16_wgrad": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
 }
 
 _lib = None

@@ -1,0 +1,386 @@
+// Hard-2:4 compressed weights and their GEMM on the sparse tensor cores.
+//
+// Storage: values[out, in/2] (the two kept bf16 of every group of four, in column order) and
+// logical metadata (one nibble per group, i0 | i1 << 2; see sparseforge_b200.h). For the GEMM the
+// metadata is reordered once into "tensor-core order": tiles of 128 rows x 128 logical columns,
+// 2048 contiguous bytes each, laid out so that one tcgen05.cp.128x128b moves a tile from shared
+// memory into 4 TMEM columns in exactly the lane / bit positions tcgen05.mma.sp reads:
+//   row m = m0 + 8 m1 + 16 m2 (m0 < 8, m1 < 2, m2 < 8), logical column k = k0 + 16 k1 + 32 k2
+//   byte offset in the tile = 256 m2 + 128 k1 + 16 m0 + 4 k2 + 2 m1 + (k0 >> 3)
+// i.e. TMEM lane 16 m2 + 8 k1 + m0, column k2, bits [16 m1, 16 m1 + 16) hold the four nibbles of
+// row m, columns [32 k2 + 16 k1, +16).
+//
+// GEMM: y[T,out] = x[T,in] . Wc^T computed as D[out-tile 128, token-tile BN] so that the sparse
+// operand is the MMA's A operand. One CTA = TMA producer warp, MMA warp (tcgen05.cp of the
+// metadata + four tcgen05.mma.sp 128 x BN x 32 per 128-deep stage), four epilogue warps that
+// write the transposed accumulator to y. Token tile BN is picked from T (16 ... 128).
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+namespace sf {
+
+int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t ld, int box_outer);
+
+constexpr int kThreadsE = 256;
+
+static inline int grid_for_e(int64_t items) {
+    int64_t need = (items + kThreadsE - 1) / kThreadsE;
+    int64_t cap = (int64_t)sm_count() * 8;
+    if (need < 1) need = 1;
+    return (int)(need < cap ? need : cap);
+}
+
+// ------------------------------------------------------------------------------------------
+// compress / decompress / metadata reorder
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreadsE)
+sparse24_compress_kernel(const __nv_bfloat16* __restrict__ W, const float* __restrict__ soft,
+                         __nv_bfloat16* __restrict__ values, uint8_t* __restrict__ meta, int64_t chunks) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreadsE + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreadsE) {
+        const uint4 wraw = ld_stream16(W + c * 8);
+        const uint16_t* wh = reinterpret_cast<const uint16_t*>(&wraw);
+        float s[8];
+        Vec8<float>::load(soft + c * 8, s);
+        uint16_t out[4];
+        uint32_t mb = 0;
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            float x[4] = {s[4 * g], s[4 * g + 1], s[4 * g + 2], s[4 * g + 3]};
+            const uint32_t k = top2_keep(x);
+            const uint32_t i0 = __ffs(k) - 1, i1 = 31 - __clz(k);
+            out[2 * g] = wh[4 * g + i0];
+            out[2 * g + 1] = wh[4 * g + i1];
+            mb |= (i0 | (i1 << 2)) << (4 * g);
+        }
+        st_stream8(values + c * 4, make_uint2(out[0] | ((uint32_t)out[1] << 16), out[2] | ((uint32_t)out[3] << 16)));
+        meta[c] = (uint8_t)mb;
+    }
+}
+
+__global__ void __launch_bounds__(kThreadsE)
+sparse24_decompress_kernel(const __nv_bfloat16* __restrict__ values, const uint8_t* __restrict__ meta,
+                           __nv_bfloat16* __restrict__ dense, int64_t chunks) {
+    for (int64_t c = (int64_t)blockIdx.x * kThreadsE + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreadsE) {
+        const uint2 v = ld_stream8(values + c * 4);
+        const uint16_t vals[4] = {(uint16_t)(v.x & 0xffff), (uint16_t)(v.x >> 16), (uint16_t)(v.y & 0xffff), (uint16_t)(v.y >> 16)};
+        const uint32_t mb = meta[c];
+        uint16_t o[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+            const uint32_t nib = (mb >> (4 * g)) & 0xF;
+            o[4 * g + (nib & 3)] = vals[2 * g];
+            o[4 * g + (nib >> 2)] = vals[2 * g + 1];
+        }
+        st_stream16(dense + c * 8, make_uint4(o[0] | ((uint32_t)o[1] << 16), o[2] | ((uint32_t)o[3] << 16),
+                                              o[4] | ((uint32_t)o[5] << 16), o[6] | ((uint32_t)o[7] << 16)));
+    }
+}
+
+// One thread per 16-bit unit of the tensor-core ordered buffer.
+__global__ void __launch_bounds__(kThreadsE)
+sparse24_pack_meta_kernel(const uint8_t* __restrict__ meta, uint16_t* __restrict__ meta_tc, int64_t out, int64_t in,
+                          int64_t k_tiles, int64_t units) {
+    const int64_t row_bytes = in / 8;
+    for (int64_t u = (int64_t)blockIdx.x * kThreadsE + threadIdx.x; u < units; u += (int64_t)gridDim.x * kThreadsE) {
+        const int64_t tile = u >> 10;           // 1024 units of 2 bytes per tile
+        const int w = (int)(u & 1023);          // unit index inside the tile = byte offset / 2
+        const int m2 = w >> 7, k1 = (w >> 6) & 1, m0 = (w >> 3) & 7, k2 = (w >> 1) & 3, m1 = w & 1;
+        const int64_t mt = tile / k_tiles, kt = tile - mt * k_tiles;
+        const int64_t row = mt * 128 + m0 + 8 * m1 + 16 * m2;
+        const int64_t byte = kt * 16 + k2 * 4 + k1 * 2;  // logical metadata byte of column 128 kt + 32 k2 + 16 k1
+        uint16_t v = 0;
+        if (row < out && byte + 1 < row_bytes + 1) {
+            const uint8_t b0 = byte < row_bytes ? meta[row * row_bytes + byte] : 0;
+            const uint8_t b1 = byte + 1 < row_bytes ? meta[row * row_bytes + byte + 1] : 0;
+            v = (uint16_t)b0 | ((uint16_t)b1 << 8);
+        }
+        meta_tc[u] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// sparse tensor-core GEMM
+// ------------------------------------------------------------------------------------------
+constexpr int SP_BM = 128, SP_BK = 128 /* logical */, SP_THREADS = 192;
+constexpr int SP_A_BYTES = SP_BM * (SP_BK / 2) * 2;  // 16 KiB of compressed values
+constexpr int SP_META_BYTES = 2048;
+
+template <int BN> struct SpCfg {
+    static constexpr int STAGES = BN >= 128 ? 4 : (BN == 64 ? 6 : 8);
+    static constexpr int B_BOX_BYTES = BN * 128;              // 64 logical columns of BN token rows
+    static constexpr int STAGE_BYTES = SP_A_BYTES + 2 * B_BOX_BYTES + SP_META_BYTES;
+    static constexpr int META_COL0 = 2 * BN;                  // TMEM columns after the two accumulators
+    static constexpr int TMEM_NEED = 2 * BN + 4 * STAGES;
+    static constexpr int TMEM_COLS = TMEM_NEED <= 64 ? 64 : (TMEM_NEED <= 128 ? 128 : (TMEM_NEED <= 256 ? 256 : 512));
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+};
+
+template <int STAGES>
+struct SpSmemTail {
+    uint64_t full[STAGES];
+    uint64_t empty[STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_dst), "l"(gsrc), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+template <int BN>
+__global__ void __launch_bounds__(SP_THREADS, 1)
+sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                     const uint8_t* __restrict__ meta_tc, __nv_bfloat16* __restrict__ Y,
+                     const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status) {
+    using C = SpCfg<BN>;
+    constexpr int STAGES = C::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    auto* tail = reinterpret_cast<SpSmemTail<STAGES>*>(base_ptr + STAGES * C::STAGE_BYTES);
+    volatile int* abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (out + SP_BM - 1) / SP_BM, tiles_n = (T + BN - 1) / BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int num_kb = (in + SP_BK - 1) / SP_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[a]), 4);
+        }
+        tail->abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_u32(&tail->tmem_base), C::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+            const int mt = tile % tiles_m, nt = tile / tiles_m;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 11);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t bar = ptx::smem_u32(&tail->full[stage]);
+                    const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + SP_A_BYTES;
+                    const uint32_t sm = sb + 2 * C::B_BOX_BYTES;
+                    ptx::mbar_arrive_expect_tx(bar, C::STAGE_BYTES);
+                    ptx::tma_load_2d(sa, &tmA, bar, kb * (SP_BK / 2), mt * SP_BM);
+                    ptx::tma_load_2d(sb, &tmB, bar, kb * SP_BK, nt * BN);
+                    ptx::tma_load_2d(sb + C::B_BOX_BYTES, &tmB, bar, kb * SP_BK + 64, nt * BN);
+                    bulk_load_1d(sm, meta_tc + ((int64_t)mt * num_kb + kb) * SP_META_BYTES, SP_META_BYTES, bar);
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    } else if (warp == 1) {
+        constexpr uint32_t idesc = ptx::make_idesc_bf16(SP_BM, BN, 0, 0, 1);
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 13);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 12);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                if (lane == 0) {
+                    const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + SP_A_BYTES;
+                    const uint32_t sm = sb + 2 * C::B_BOX_BYTES;
+                    const uint32_t tmem_e = tmem_base + (uint32_t)(C::META_COL0 + 4 * stage);
+                    // metadata tile: 128 rows of 16 bytes, 8-row groups 128 bytes apart, no swizzle
+                    ptx::tmem_cp_128x128b(tmem_e, ptx::make_smem_desc(sm, 16, 128, 0));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const uint64_t adesc = ptx::make_smem_desc(sa + k * 32, 16, 1024, 2);
+                        const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * C::B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
+                        ptx::mma_f16_ss_sp(tmem_d, adesc, bdesc, tmem_e + (uint32_t)(k & ~1), idesc | (uint32_t)(k & 1),
+                                           (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::mma_commit(ptx::smem_u32(&tail->empty[stage]));
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+            if (!ok) break;
+            if (lane == 0) ptx::mma_commit(ptx::smem_u32(&tail->tmem_full[acc]));
+            __syncwarp();
+        }
+    } else {
+        const int q = warp & 3;
+        bool ok = true;
+        int t = 0;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+            const int mt = tile % tiles_m, nt = tile / tiles_m;
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 14);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int o = mt * SP_BM + q * 32 + lane;  // output feature of this thread
+            const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
+            const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+            constexpr int CH = BN >= 32 ? 32 : 16;
+#pragma unroll 1
+            for (int c = 0; c < BN / CH; ++c) {
+                uint32_t r[32];
+                if (CH == 32) ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * CH), r);
+                else tmem_ld_32x32b_x16(taddr + (uint32_t)(c * CH), r);
+                ptx::tmem_ld_wait();
+                if (o < out) {
+#pragma unroll
+                    for (int j = 0; j < CH; ++j) {
+                        const int tok = nt * BN + c * CH + j;
+                        if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[acc]));
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+}
+
+template <int BN>
+static int launch_sparse(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
+                         int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st) {
+    using C = SpCfg<BN>;
+    CUtensorMap tmA, tmB;
+    int rc = make_bf16_tensor_map(&tmA, values, in / 2, out, in / 2, SP_BM);
+    if (rc) return rc;
+    rc = make_bf16_tensor_map(&tmB, x, in, T, in, BN);
+    if (rc) return rc;
+    auto kern = sparse24_gemm_kernel<BN>;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        SF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
+        configured_dev = dev;
+    }
+    const int64_t tiles = ((out + SP_BM - 1) / SP_BM) * ((T + BN - 1) / BN);
+    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    kern<<<grid, SP_THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, meta_tc, (__nv_bfloat16*)y, (const __nv_bfloat16*)bias,
+                                                  (int)out, (int)T, (int)in, status);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+}  // namespace sf
+
+using namespace sf;
+
+extern "C" {
+
+int sf_sparse24_compress(const void* W, const float* soft, void* values, uint8_t* meta, int64_t out, int64_t in,
+                         void* stream) {
+    SF_CHECK_ARG(W && soft && values && meta, "sf_sparse24_compress: W, soft, values, meta must be non-null");
+    SF_CHECK_ARG(out > 0 && in > 0 && in % 8 == 0, "sf_sparse24_compress: in=%lld must be a positive multiple of 8", (long long)in);
+    if (!(aligned16(W) && aligned16(soft)) || (reinterpret_cast<uintptr_t>(values) & 7u))
+        return fail(SF_ERR_ALIGNMENT, "sf_sparse24_compress: W, soft must be 16-byte and values 8-byte aligned");
+    const int64_t chunks = out * in / 8;
+    sparse24_compress_kernel<<<grid_for_e(chunks), kThreadsE, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)W, soft, (__nv_bfloat16*)values, meta, chunks);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_sparse24_decompress(const void* values, const uint8_t* meta, void* dense, int64_t out, int64_t in, void* stream) {
+    SF_CHECK_ARG(values && meta && dense, "sf_sparse24_decompress: values, meta, dense must be non-null");
+    SF_CHECK_ARG(out > 0 && in > 0 && in % 8 == 0, "sf_sparse24_decompress: in=%lld must be a positive multiple of 8", (long long)in);
+    if (!aligned16(dense) || (reinterpret_cast<uintptr_t>(values) & 7u))
+        return fail(SF_ERR_ALIGNMENT, "sf_sparse24_decompress: dense must be 16-byte and values 8-byte aligned");
+    const int64_t chunks = out * in / 8;
+    sparse24_decompress_kernel<<<grid_for_e(chunks), kThreadsE, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)values, meta, (__nv_bfloat16*)dense, chunks);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int64_t sf_sparse24_meta_tc_bytes(int64_t out, int64_t in) {
+    if (out <= 0 || in <= 0) return 0;
+    return ((out + 127) / 128) * ((in + 127) / 128) * (int64_t)SP_META_BYTES;
+}
+
+int sf_sparse24_pack_meta(const uint8_t* meta, uint8_t* meta_tc, int64_t out, int64_t in, void* stream) {
+    SF_CHECK_ARG(meta && meta_tc, "sf_sparse24_pack_meta: meta and meta_tc must be non-null");
+    SF_CHECK_ARG(out > 0 && in > 0 && in % 8 == 0, "sf_sparse24_pack_meta: in=%lld must be a positive multiple of 8", (long long)in);
+    if (!aligned16(meta_tc)) return fail(SF_ERR_ALIGNMENT, "sf_sparse24_pack_meta: meta_tc must be 16-byte aligned");
+    const int64_t k_tiles = (in + 127) / 128;
+    const int64_t units = sf_sparse24_meta_tc_bytes(out, in) / 2;
+    sparse24_pack_meta_kernel<<<grid_for_e(units), kThreadsE, 0, (cudaStream_t)stream>>>(
+        meta, (uint16_t*)meta_tc, out, in, k_tiles, units);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y, int64_t T,
+                     int64_t in, int64_t out, int32_t* status, void* stream) {
+    SF_CHECK_ARG(x && values && meta_tc && y, "sf_sparse24_gemm: x, values, meta_tc, y must be non-null");
+    SF_CHECK_ARG(T > 0 && in > 0 && out > 0, "sf_sparse24_gemm: T, in, out must be positive");
+    if (in % 16 != 0)
+        return fail(SF_ERR_UNSUPPORTED, "sf_sparse24_gemm: in=%lld must be a multiple of 16 (16-byte rows of compressed values)", (long long)in);
+    if (T > 0x7fffffff || in > 0x7fffffff || out > 0x7fffffff)
+        return fail(SF_ERR_UNSUPPORTED, "sf_sparse24_gemm: dimension beyond 2^31-1");
+    if (!(aligned16(x) && aligned16(values) && aligned16(meta_tc)))
+        return fail(SF_ERR_ALIGNMENT, "sf_sparse24_gemm: x, values, meta_tc must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
+}
+
+}  // extern "C"

@@ -188,3 +188,120 @@ def bias_grad(dy2d):
     db = torch.empty(out, dtype=torch.float32, device=dy2d.device)
     check(lib().sf_bias_grad(_p(dy2d), _dt(dy2d), _p(db), T, out, _stream()), "sf_bias_grad")
     return db
+
+
+# ----------------------------------------------------------------------------------------
+# hard-2:4 compressed weights
+# ----------------------------------------------------------------------------------------
+def sparse24_compress(W, soft):
+    """(values[out,in/2] bf16, meta[out,in/8] uint8) of W pruned to top2(soft) per group of 4."""
+    _cuda(W, soft)
+    if W.dtype != torch.bfloat16 or soft.dtype != torch.float32:
+        raise TypeError("sparse24_compress: W bfloat16, soft float32")
+    out, k = W.shape
+    values = torch.empty((out, k // 2), dtype=torch.bfloat16, device=W.device)
+    meta = torch.empty((out, k // 8), dtype=torch.uint8, device=W.device)
+    check(lib().sf_sparse24_compress(_p(W), _p(soft), _p(values), _p(meta), out, k, _stream()), "sf_sparse24_compress")
+    return values, meta
+
+
+def sparse24_decompress(values, meta):
+    _cuda(values, meta)
+    out, half = values.shape
+    dense = torch.empty((out, half * 2), dtype=torch.bfloat16, device=values.device)
+    check(lib().sf_sparse24_decompress(_p(values), _p(meta), _p(dense), out, half * 2, _stream()), "sf_sparse24_decompress")
+    return dense
+
+
+def sparse24_pack_meta(meta, out, k):
+    """Logical metadata -> the order the sparse tensor-core GEMM loads."""
+    _cuda(meta)
+    n = int(lib().sf_sparse24_meta_tc_bytes(out, k))
+    meta_tc = torch.empty(n, dtype=torch.uint8, device=meta.device)
+    check(lib().sf_sparse24_pack_meta(_p(meta), _p(meta_tc), out, k, _stream()), "sf_sparse24_pack_meta")
+    return meta_tc
+
+
+def sparse24_gemm(x2d, values, meta_tc, bias=None, status=None):
+    """y[T,out] = x2d[T,in] @ decompress(values, meta)^T (+ bias) on the sparse tensor cores."""
+    _cuda(x2d, values, meta_tc, bias, status)
+    if x2d.dtype != torch.bfloat16 or values.dtype != torch.bfloat16:
+        raise TypeError("sparse24_gemm: bfloat16 only")
+    T, k = x2d.shape
+    out = values.shape[0]
+    if values.shape[1] * 2 != k:
+        raise ValueError(f"sparse24_gemm: x has {k} features, compressed weight has {values.shape[1] * 2}")
+    y = torch.empty((T, out), dtype=torch.bfloat16, device=x2d.device)
+    if T == 0:
+        return y
+    check(lib().sf_sparse24_gemm(_p(x2d), _p(values), _p(meta_tc), _p(bias), _p(y), T, k, out, _p(status), _stream()),
+          "sf_sparse24_gemm")
+    return y
+
+
+# ----------------------------------------------------------------------------------------
+# block-sparse-16
+# ----------------------------------------------------------------------------------------
+def bsr16_build(W, mask=None):
+    """(blocks[nnz,16,16], row_ptr int32, col_idx int32) of W*mask; a block is kept iff sum|W*mask| > 0."""
+    _cuda(W, mask)
+    out, k = W.shape
+    row_ptr = torch.zeros(out // 16 + 1, dtype=torch.int32, device=W.device)
+    nnz_t = torch.zeros(1, dtype=torch.int32, device=W.device)
+    md = _dt(mask) if mask is not None else SF_F32
+    check(lib().sf_bsr16_build(_p(W), _p(mask), _dt(W), md, None, _p(row_ptr), None, _p(nnz_t), out, k, _stream()),
+          "sf_bsr16_build")
+    nnz = int(nnz_t.item())
+    blocks = torch.zeros((max(nnz, 1), 16, 16), dtype=W.dtype, device=W.device)
+    col_idx = torch.zeros(nnz, dtype=torch.int32, device=W.device)
+    if nnz > 0:
+        check(lib().sf_bsr16_build(_p(W), _p(mask), _dt(W), md, _p(blocks), _p(row_ptr), _p(col_idx), None, out, k,
+                                   _stream()), "sf_bsr16_build")
+    return blocks, row_ptr, col_idx
+
+
+def bsr16_to_dense(blocks, row_ptr, col_idx, out, k):
+    _cuda(blocks, row_ptr, col_idx)
+    dense = torch.empty((out, k), dtype=blocks.dtype, device=blocks.device)
+    if col_idx.numel() == 0:
+        return dense.zero_()
+    check(lib().sf_bsr16_to_dense(_p(blocks), _p(row_ptr), _p(col_idx), _p(dense), k, out, _dt(blocks), _stream()),
+          "sf_bsr16_to_dense")
+    return dense
+
+
+def _bsr_ws(workspace, out, k, like):
+    if workspace is None:
+        workspace = torch.empty((out, k), dtype=like.dtype, device=like.device)
+    return workspace
+
+
+def bsr16_fwd(x2d, blocks, row_ptr, col_idx, out, bias=None, workspace=None, status=None):
+    _cuda(x2d, blocks, row_ptr, col_idx, bias, workspace, status)
+    T, k = x2d.shape
+    ws = _bsr_ws(workspace, out, k, x2d)
+    y = torch.empty((T, out), dtype=x2d.dtype, device=x2d.device)
+    check(lib().sf_bsr16_fwd(_p(x2d), _p(blocks), _p(row_ptr), _p(col_idx), _p(bias), _p(y), _p(ws), T, k, out,
+                             _gemm_dtype(x2d, blocks), _p(status), _stream()), "sf_bsr16_fwd")
+    return y
+
+
+def bsr16_dgrad(dy2d, blocks, row_ptr, col_idx, k, workspace=None, status=None):
+    _cuda(dy2d, blocks, row_ptr, col_idx, workspace, status)
+    T, out = dy2d.shape
+    ws = _bsr_ws(workspace, out, k, dy2d)
+    dx = torch.empty((T, k), dtype=dy2d.dtype, device=dy2d.device)
+    check(lib().sf_bsr16_dgrad(_p(dy2d), _p(blocks), _p(row_ptr), _p(col_idx), _p(dx), _p(ws), T, k, out,
+                               _gemm_dtype(dy2d, blocks), _p(status), _stream()), "sf_bsr16_dgrad")
+    return dx
+
+
+def bsr16_wgrad(dy2d, x2d, row_ptr, col_idx, workspace=None, status=None):
+    _cuda(dy2d, x2d, row_ptr, col_idx, workspace, status)
+    T, out = dy2d.shape
+    k = x2d.shape[1]
+    ws = _bsr_ws(workspace, out, k, x2d)
+    dblocks = torch.zeros((max(col_idx.numel(), 1), 16, 16), dtype=x2d.dtype, device=x2d.device)
+    check(lib().sf_bsr16_wgrad(_p(dy2d), _p(x2d), _p(row_ptr), _p(col_idx), _p(dblocks), _p(ws), T, k, out,
+                               _gemm_dtype(dy2d, x2d), _p(status), _stream()), "sf_bsr16_wgrad")
+    return dblocks

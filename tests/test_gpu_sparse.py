@@ -1,0 +1,150 @@
+"""GPU parity of the hard-2:4 compressed path and the block-sparse-16 path.
+
+The reference has neither a compressed format nor a block-sparse backward; their semantics are the
+dense masked products with the binary mask (legacy/main_llama.py:2552-2563,
+legacy/sparse_modeling.py:72-132), which is what the oracle computes. Compressed values, metadata
+and block-CSR indices are compared bit-exactly; GEMM outputs at 1e-2 (bf16) relative to the largest
+reference magnitude.
+"""
+import pytest
+import torch
+
+from oracle import sparselinear_oracle as O
+from tests.golden_io import Golden, rel_err
+
+pytestmark = pytest.mark.gpu
+
+BF16_TOL = 1e-2
+DEV = "cuda"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from sparseforge_b200 import ops as _ops
+
+    return _ops
+
+
+def test_compress_round_trip_bit_exact(ops):
+    torch.manual_seed(0)
+    for shape in ((16, 64), (130, 256), (4096, 4096)):
+        W = (torch.randn(shape) * 0.02).to(torch.bfloat16)
+        vals, meta = ops.sparse24_compress(W.to(DEV), W.float().abs().to(DEV))
+        ovals, ometa, ohard = O.sparse24_compress(W, W.float().abs())
+        assert torch.equal(vals.cpu().view(torch.int16), ovals.view(torch.int16))
+        assert torch.equal(meta.cpu(), ometa)
+        dense = ops.sparse24_decompress(vals, meta)
+        assert torch.equal(dense.cpu().float(), (W * ohard.to(torch.bfloat16)).float())  # +-0 compare equal
+
+
+def test_compress_ties_lower_index(ops):
+    W = torch.ones(8, 32).to(torch.bfloat16)
+    vals, meta = ops.sparse24_compress(W.to(DEV), torch.ones(8, 32, device=DEV))
+    assert bool((meta.cpu() == 0x44).all())  # columns 0 and 1 of every group: nibble 0 | 1 << 2
+
+
+def test_pack_meta_is_the_documented_permutation(ops):
+    torch.manual_seed(1)
+    out, k = 256, 384
+    meta = torch.randint(0, 256, (out, k // 8), dtype=torch.uint8)
+    tc = ops.sparse24_pack_meta(meta.to(DEV), out, k).cpu()
+    assert tc.numel() == (out // 128) * (k // 128) * 2048
+    k_tiles = k // 128
+    for (row, col) in [(0, 0), (7, 16), (8, 31), (137, 200), (255, 383), (128, 128), (100, 96)]:
+        mt, m = divmod(row, 128)
+        kt, kk = divmod(col, 128)
+        m0, m1, m2 = m % 8, (m // 8) % 2, m // 16
+        k0, k1, k2 = kk % 16, (kk // 16) % 2, kk // 32
+        off = (mt * k_tiles + kt) * 2048 + 256 * m2 + 128 * k1 + 16 * m0 + 4 * k2 + 2 * m1 + (k0 >> 3)
+        assert int(tc[off]) == int(meta[row, col // 8]), (row, col)
+
+
+SPARSE_SHAPES = [
+    (1, 128, 128), (16, 256, 128), (17, 384, 256), (128, 512, 384), (100, 272, 200), (1024, 1024, 512),
+    (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 11008), (1024, 11008, 4096), (8192, 4096, 4096),
+]
+
+
+@pytest.mark.parametrize("T,k,n", SPARSE_SHAPES)
+def test_sparse24_gemm(ops, T, k, n):
+    torch.manual_seed(T + k + n)
+    W = (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    vals, meta = ops.sparse24_compress(W, W.float().abs())
+    meta_tc = ops.sparse24_pack_meta(meta, n, k)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    y = ops.sparse24_gemm(x, vals, meta_tc, status=status)
+    torch.cuda.synchronize()
+    assert int(status[0]) == 0, f"a device-side wait ran out, code {int(status[0])}"
+    wd = ops.sparse24_decompress(vals, meta)
+    ref = x.float() @ wd.float().t()
+    assert rel_err(y, ref) <= BF16_TOL
+    # and it agrees with the dense masked GEMM on the same pruned weight
+    if T % 8 == 0:
+        assert rel_err(y, ops.gemm_fwd(x, wd).float()) <= BF16_TOL
+
+
+def test_sparse24_gemm_bias(ops):
+    torch.manual_seed(5)
+    T, k, n = 40, 256, 136
+    W = (torch.randn(n, k, device=DEV) * 0.05).to(torch.bfloat16)
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    b = torch.randn(n, device=DEV).to(torch.bfloat16)
+    vals, meta = ops.sparse24_compress(W, W.float().abs())
+    y = ops.sparse24_gemm(x, vals, ops.sparse24_pack_meta(meta, n, k), bias=b)
+    ref = x.float() @ ops.sparse24_decompress(vals, meta).float().t() + b.float()
+    assert rel_err(y, ref) <= BF16_TOL
+
+
+# ---------------------------------------------------------------------------------------
+# block-sparse-16
+# ---------------------------------------------------------------------------------------
+def test_bsr16_build_matches_reference_fixture(ops):
+    g = Golden("block_sparse")
+    blocks, row_ptr, col_idx = ops.bsr16_build(g["W"].to(DEV), g["mask"].to(DEV))
+    assert torch.equal(row_ptr.cpu(), g["row_ptr"]) and torch.equal(col_idx.cpu(), g["col_idx"])
+    assert torch.equal(blocks.cpu(), g["blocks"])
+    y = ops.bsr16_fwd(g["X"].to(DEV), blocks, row_ptr, col_idx, g["W"].shape[0])
+    assert rel_err(y, g["Y"]) <= 1e-5
+
+
+@pytest.mark.parametrize("shape,T", [((64, 96), 24), ((256, 512), 200), ((11008, 4096), 2048)])
+def test_bsr16_products(ops, shape, T):
+    torch.manual_seed(shape[0])
+    out, k = shape
+    W = (torch.randn(out, k) * 0.02).to(torch.bfloat16)
+    mask = O.block16_keep_mask(W.float(), 0.5).to(torch.bfloat16)
+    blocks, row_ptr, col_idx = ops.bsr16_build(W.to(DEV), mask.to(DEV))
+    ob, orp, oci = O.bsr16_convert(W, mask)
+    assert torch.equal(row_ptr.cpu(), orp) and torch.equal(col_idx.cpu(), oci)
+    assert torch.equal(blocks.cpu().float(), ob.float())
+    assert int(row_ptr[-1]) == round(0.5 * (out // 16) * (k // 16))
+    dense = ops.bsr16_to_dense(blocks, row_ptr, col_idx, out, k)
+    assert torch.equal(dense.cpu().float(), (W * mask).float())
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    dy = torch.randn(T, out, device=DEV).to(torch.bfloat16)
+    wd = dense.float()
+    assert rel_err(ops.bsr16_fwd(x, blocks, row_ptr, col_idx, out), x.float() @ wd.t()) <= BF16_TOL
+    assert rel_err(ops.bsr16_dgrad(dy, blocks, row_ptr, col_idx, k), dy.float() @ wd) <= BF16_TOL
+    dblocks = ops.bsr16_wgrad(dy, x, row_ptr, col_idx)
+    full = (dy.float().t() @ x.float())
+    got_dense = ops.bsr16_to_dense(dblocks, row_ptr, col_idx, out, k).float()
+    assert rel_err(got_dense, full * mask.to(DEV).float()) <= BF16_TOL
+
+
+def test_block_sparse_linear_module(ops):
+    from sparseforge_b200.block_sparse import BlockSparseLinear, get_sparsity_info
+
+    torch.manual_seed(9)
+    W = (torch.randn(128, 256, device=DEV) * 0.02).to(torch.bfloat16)
+    mask = O.block16_keep_mask(W.float().cpu(), 0.5).to(DEV).to(torch.bfloat16)
+    layer = BlockSparseLinear.from_dense(W, mask)
+    info = get_sparsity_info(layer.block_row_indices, 256 // 16)
+    assert info["block_sparsity"] == pytest.approx(0.5)
+    x = torch.randn(2, 24, 256, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    layer.sparse_blocks.requires_grad_(True)
+    y = layer(x)
+    y.float().sum().backward()
+    assert rel_err(y.reshape(48, 128), x.detach().float().reshape(48, 256) @ (W * mask).float().t()) <= BF16_TOL
+    assert rel_err(x.grad.reshape(48, 256), torch.ones(48, 128, device=DEV) @ (W * mask).float()) <= BF16_TOL
+    assert layer.sparse_blocks.grad.shape == layer.sparse_blocks.shape
