@@ -151,10 +151,11 @@ def run_ours(args):
     _lib.lib()  # fail loudly if the CUDA library is missing
     T = T_TOKENS
     bf = torch.bfloat16
-    mats = [Matrix(n, r // world, c, 100 + i, dev) for i, (n, r, c) in enumerate(SHAPES)]
+    shapes = [s for s in SHAPES if (not args.only or s[0] in args.only.split(","))]
+    mats = [Matrix(n, r // world, c, 100 + i, dev) for i, (n, r, c) in enumerate(SHAPES) if (n, r, c) in shapes]
     # activations: the same on every rank (seeded), one buffer per distinct width
     gx = torch.Generator(device=dev).manual_seed(7)
-    widths = sorted({c for _, _, c in SHAPES} | {r for _, r, _ in SHAPES})
+    widths = sorted({c for _, _, c in shapes} | {r for _, r, _ in shapes})
     X = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
     dYfull = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
     host_X = host_dY = None
@@ -233,19 +234,21 @@ def run_ours(args):
     part = timers.totals_ms()
 
     # end to end: the same step fed from pinned host buffers, stats read back every step
-    host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in SHAPES}}
-    host_dY = {w: dYfull[w].cpu().pin_memory() for w in {r for _, r, _ in SHAPES}}
-    h2d = sum((T * c + T * r) * 2 for _, r, c in SHAPES)
-    d2h = len(SHAPES) * 8 * 8
-    step(0, e2e=True)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for it in range(args.steps):
-        step(args.warmup + it, e2e=True)
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
+    h2d = sum((T * c + T * r) * 2 for _, r, c in shapes)
+    d2h = len(shapes) * 8 * 8
+    e2e_ms = float("nan")
+    if not args.no_e2e:
+        host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in shapes}}
+        host_dY = {w: dYfull[w].cpu().pin_memory() for w in {r for _, r, _ in shapes}}
+        step(0, e2e=True)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for it in range(args.steps):
+            step(args.warmup + it, e2e=True)
+        e1.record()
+        barrier()
+        e2e_ms = e0.elapsed_time(e1)
 
     times = torch.tensor([total_ms, e2e_ms, part.get("gemm", 0.0), part.get("score", 0.0), part.get("adamw", 0.0),
                           part.get("mask", 0.0)], dtype=torch.float64, device=dev)
@@ -258,8 +261,8 @@ def run_ours(args):
         return
 
     peaks, peak_src = load_peaks()
-    flops_step = sum(layer_flops(T, r, c) for _, r, c in SHAPES)
-    elems_rank = sum(r * c for _, r, c in SHAPES) / world
+    flops_step = sum(layer_flops(T, r, c) for _, r, c in shapes)
+    elems_rank = sum(r * c for _, r, c in shapes) / world
     ms_per_step = total_ms / args.steps
     value = flops_step / (ms_per_step * 1e-3) / 1e12
     gemm_tflops = (flops_step / world) * args.steps / (gemm_ms * 1e-3) / 1e12 if gemm_ms > 0 else None
@@ -268,17 +271,18 @@ def run_ours(args):
         "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "llama2-7b-layerset-tempering", "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
+        "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
+                   "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
         "clocks": clocks,
-        "e2e": {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2), "unit": UNIT,
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "e2e": None if args.no_e2e else {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2),
+                                         "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_timed,
         "roofline": {"bound": "tensor", "achieved": round(gemm_tflops, 1) if gemm_tflops else None,
                      "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": round(gemm_tflops / peaks["bf16_tflops_sustained"], 4) if gemm_tflops else None,
                      "traffic": None, "peak_source": peak_src + " (sustained bf16 GEMM)",
-                     "kernel": "gemm_bf16_tcgen05_kernel (fwd, dgrad, wgrad: 21 launches per step)"},
+                     "kernel": f"gemm_bf16_tcgen05_kernel (fwd, dgrad, wgrad: {3 * len(shapes)} launches per step)"},
         "passes": {
             "score_gbs": gbs(BYTES_SCORE, score_ms), "adamw_gbs": gbs(BYTES_ADAMW, adamw_ms),
             "mask_update_gbs": gbs(BYTES_MASK, mask_ms), "hbm_peak_gbs": peaks["hbm_gbs"],
@@ -363,6 +367,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
+                                               "workload for profiler captures; the JSON line then names it")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":

@@ -71,7 +71,7 @@ SF_API int64_t sf_hutch_score_scratch_doubles(int64_t n);
  *   if hvp != NULL:  H <- beta*H + (1-beta)*max(hvp*v, 0)      (H fp32, in place)
  *   score <- metric(W, H)                                      (fp32, raw)
  *   norm[0] <- mean(score), norm[1] <- std_pop(score) + 1e-6   (fp32, on device)
- * hvp and W have dtype w_dtype; v has dtype v_dtype (SF_I8 signs or w_dtype).
+ * hvp and W have dtype w_dtype; v has dtype v_dtype (SF_I8 holding +1 / -1 only, or w_dtype).
  * aux is grad_ema for SF_METRIC_MOVEMENT (w_dtype), else ignored; aux_scalar is the
  * movement temperature. scratch: sf_hutch_score_scratch_doubles(n) doubles.
  * n = rows*cols, must be a multiple of 8; buffers 16-byte aligned.

@@ -81,6 +81,48 @@ __device__ __forceinline__ uint32_t top2_keep(const float (&x)[4]) {
     return k;
 }
 
+// ---- cheap arithmetic for the HBM-bound passes ------------------------------------------
+// The passes must stay under ~60 instructions per element to keep up with HBM, so division,
+// square root and exp use the 1-2 ulp hardware approximations (relative error < 5e-7, far
+// inside the 1e-5 parity bar) instead of the IEEE-exact sequences.
+__device__ __forceinline__ float fast_rcp(float x) {
+    float r;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float fast_sqrt(float x) {
+    float r;
+    asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+__device__ __forceinline__ float fast_ex2(float x) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+    return r;
+}
+// Round-to-nearest-even to bf16 precision with integer ops (keeps the conversion pipe free).
+__device__ __forceinline__ float bf16_round_int(float x) {
+    uint32_t u = __float_as_uint(x);
+    u = (u + 0x7fffu + ((u >> 16) & 1u)) & 0xffff0000u;
+    return __uint_as_float(u);
+}
+
+// Stable top-2 of a group of four without NaN handling: six comparisons, "a >= b" lets the
+// lower index win a tie. rank[i] as in rank4 for NaN-free input.
+__device__ __forceinline__ void rank4_fast(const float (&x)[4], int (&rank)[4]) {
+    const int c01 = x[0] >= x[1], c02 = x[0] >= x[2], c03 = x[0] >= x[3];
+    const int c12 = x[1] >= x[2], c13 = x[1] >= x[3], c23 = x[2] >= x[3];
+    rank[0] = 3 - c01 - c02 - c03;
+    rank[1] = c01 + 2 - c12 - c13;
+    rank[2] = c02 + c12 + 1 - c23;
+    rank[3] = c03 + c13 + c23;
+}
+__device__ __forceinline__ uint32_t top2_keep_fast(const float (&x)[4]) {
+    int r[4];
+    rank4_fast(x, r);
+    return (r[0] < 2 ? 1u : 0u) | (r[1] < 2 ? 2u : 0u) | (r[2] < 2 ? 4u : 0u) | (r[3] < 2 ? 8u : 0u);
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -147,7 +189,100 @@ struct Vec8<__nv_bfloat16> {
         }
         st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
     }
-    static __device__ __forceinline__ float round(float x) { return bf16_round(x); }
+    static __device__ __forceinline__ float round(float x) { return bf16_round_int(x); }
 };
+
+
+// ---- warp-span decomposition of the streaming passes ------------------------------------
+// A warp walks the tensor in spans of 256 consecutive elements. Lane l owns two 2:4 groups of
+// the span: elements [4l, 4l+4) and [128+4l, 128+4l+4). Every warp-wide access is then one
+// contiguous run (512 B for fp32, 256 B for bf16, 128 B for int8): full sectors, no sector is
+// touched by two instructions. x[0..3] is the first group, x[4..7] the second.
+struct SpanPos {
+    int64_t a, b;  // element index of the lane's first / second group
+    bool va, vb;   // the group lies inside the tensor (n is a multiple of 8)
+};
+__device__ __forceinline__ SpanPos span_pos(int64_t span, int lane, int64_t n) {
+    SpanPos p;
+    p.a = span * 256 + 4 * lane;
+    p.b = p.a + 128;
+    p.va = p.a + 4 <= n;
+    p.vb = p.b + 4 <= n;
+    return p;
+}
+#define SF_SPAN_LOOP(span, n)                                                                   \
+    for (int64_t span = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5),           \
+                 _spans = ((n) + 255) / 256, _step = (int64_t)gridDim.x * (blockDim.x >> 5);    \
+         span < _spans; span += _step)
+
+template <typename T>
+struct Span8;
+template <>
+struct Span8<float> {
+    static __device__ __forceinline__ void load(const float* p, const SpanPos& s, float (&x)[8]) {
+        uint4 a = s.va ? ld_stream16(p + s.a) : make_uint4(0, 0, 0, 0);
+        uint4 b = s.vb ? ld_stream16(p + s.b) : make_uint4(0, 0, 0, 0);
+        x[0] = __uint_as_float(a.x); x[1] = __uint_as_float(a.y);
+        x[2] = __uint_as_float(a.z); x[3] = __uint_as_float(a.w);
+        x[4] = __uint_as_float(b.x); x[5] = __uint_as_float(b.y);
+        x[6] = __uint_as_float(b.z); x[7] = __uint_as_float(b.w);
+    }
+    static __device__ __forceinline__ void store(float* p, const SpanPos& s, const float (&x)[8]) {
+        if (s.va) st_stream16(p + s.a, make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]),
+                                                   __float_as_uint(x[2]), __float_as_uint(x[3])));
+        if (s.vb) st_stream16(p + s.b, make_uint4(__float_as_uint(x[4]), __float_as_uint(x[5]),
+                                                   __float_as_uint(x[6]), __float_as_uint(x[7])));
+    }
+    static __device__ __forceinline__ float round(float x) { return x; }
+};
+template <>
+struct Span8<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, const SpanPos& s, float (&x)[8]) {
+        uint2 a = s.va ? ld_stream8(p + s.a) : make_uint2(0, 0);
+        uint2 b = s.vb ? ld_stream8(p + s.b) : make_uint2(0, 0);
+        const uint32_t w[4] = {a.x, a.y, b.x, b.y};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[2 * i] = __uint_as_float(w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const SpanPos& s, const float (&x)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        if (s.va) st_stream8(p + s.a, make_uint2(w[0], w[1]));
+        if (s.vb) st_stream8(p + s.b, make_uint2(w[2], w[3]));
+    }
+    static __device__ __forceinline__ float round(float x) { return bf16_round_int(x); }
+};
+// +1 / -1 probes stored as int8: the float is built from the sign bit.
+template <>
+struct Span8<int8_t> {
+    static __device__ __forceinline__ void load(const int8_t* p, const SpanPos& s, float (&x)[8]) {
+        const uint32_t a = s.va ? __ldcs(reinterpret_cast<const uint32_t*>(p + s.a)) : 0u;
+        const uint32_t b = s.vb ? __ldcs(reinterpret_cast<const uint32_t*>(p + s.b)) : 0u;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[i] = __uint_as_float(0x3f800000u | (((a >> (8 * i)) & 0x80u) << 24));
+            x[4 + i] = __uint_as_float(0x3f800000u | (((b >> (8 * i)) & 0x80u) << 24));
+        }
+    }
+};
+// Packed 2:4 metadata of a span: byte j of the tensor holds groups 2j (low nibble) and 2j+1.
+// Lanes 2j and 2j+1 hold those two groups; the even lane writes the byte of the first halves,
+// the odd lane the byte of the second halves. Must be called by the whole warp.
+__device__ __forceinline__ void store_meta_span(uint8_t* meta, const SpanPos& s, uint32_t nib_a, uint32_t nib_b) {
+    const uint32_t pa = __shfl_xor_sync(0xffffffffu, nib_a, 1);
+    const uint32_t pb = __shfl_xor_sync(0xffffffffu, nib_b, 1);
+    if (((threadIdx.x & 1) == 0)) {
+        if (s.va) meta[s.a >> 3] = (uint8_t)(nib_a | (pa << 4));
+    } else {
+        if (s.vb) meta[s.b >> 3] = (uint8_t)(pb | (nib_b << 4));
+    }
+}
 
 }  // namespace sf

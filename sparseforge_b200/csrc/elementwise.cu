@@ -4,6 +4,7 @@
 // groups) and moves them with 16-byte streaming accesses; grids are sized from the
 // SM count and walk the tensor with a grid-stride loop.
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 
@@ -46,27 +47,29 @@ static inline int grid_for(int64_t chunks, int blocks_per_sm) {
     return (int)(need < cap ? need : cap);
 }
 
+// Grid of exactly one resident wave of `kernel` (SMs x blocks that fit per SM), so the
+// grid-stride loop gives every block the same share and there is no partial last wave.
+static int grid_one_wave(const void* kernel, int64_t chunks) {
+    static std::mutex mu;
+    static std::unordered_map<const void*, int> cache;
+    int per_sm = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(kernel);
+        if (it != cache.end()) per_sm = it->second;
+    }
+    if (per_sm == 0) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, 0) != cudaSuccess || per_sm <= 0)
+            per_sm = 4;
+        std::lock_guard<std::mutex> lock(mu);
+        cache[kernel] = per_sm;
+    }
+    return grid_for(chunks, per_sm);
+}
+
 // ---------------------------------------------------------------------------------------
 // Hutchinson accumulate + score + partial sums
 // ---------------------------------------------------------------------------------------
-template <typename TV>
-__device__ __forceinline__ void load_signs(const TV* p, float (&x)[8]);
-template <>
-__device__ __forceinline__ void load_signs<int8_t>(const int8_t* p, float (&x)[8]) {
-    uint2 a = ld_stream8(p);
-    uint32_t w[2] = {a.x, a.y};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) x[i] = (float)(int8_t)((w[i >> 2] >> (8 * (i & 3))) & 0xff);
-}
-template <>
-__device__ __forceinline__ void load_signs<float>(const float* p, float (&x)[8]) {
-    Vec8<float>::load(p, x);
-}
-template <>
-__device__ __forceinline__ void load_signs<__nv_bfloat16>(const __nv_bfloat16* p, float (&x)[8]) {
-    Vec8<__nv_bfloat16>::load(p, x);
-}
-
 template <typename TW, typename TV, int METRIC, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
 hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* __restrict__ H,
@@ -75,29 +78,29 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
                    float beta, float one_minus_beta) {
     double acc_s = 0.0, acc_s2 = 0.0;
     const float eps = 1e-8f;
-    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
-         c += (int64_t)gridDim.x * kThreads) {
-        const int64_t e = c * 8;
+    const int64_t n = chunks * 8;
+    SF_SPAN_LOOP(span, n) {
+        const SpanPos pos = span_pos(span, threadIdx.x & 31, n);
         float w[8], h[8], s[8];
-        Vec8<TW>::load(W + e, w);
+        Span8<TW>::load(W, pos, w);
         constexpr bool NEED_H = (METRIC == SF_METRIC_HESSIAN_OBD || METRIC == SF_METRIC_HESSIAN_RATIO ||
                                  METRIC == SF_METRIC_HESSIAN) || ACCUM;
-        if (NEED_H) Vec8<float>::load(H + e, h);
+        if (NEED_H) Span8<float>::load(H, pos, h);
         if (ACCUM) {
             float hv[8], sg[8];
-            Vec8<TW>::load(hvp + e, hv);
-            load_signs<TV>(v + e, sg);
+            Span8<TW>::load(hvp, pos, hv);
+            Span8<TV>::load(v, pos, sg);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 // diag_est = clamp(hvp*v, min=0) in the weight dtype; H.mul_(beta).add_(d, alpha=1-beta)
                 float d = fmaxf(Vec8<TW>::round(__fmul_rn(hv[i], sg[i])), 0.0f);
                 h[i] = __fmaf_rn(one_minus_beta, d, __fmul_rn(h[i], beta));
             }
-            Vec8<float>::store(H + e, h);
+            Span8<float>::store(H, pos, h);
         }
         if (METRIC == SF_METRIC_MOVEMENT) {
             float g[8];
-            Vec8<TW>::load(aux + e, g);
+            Span8<TW>::load(aux, pos, g);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
                 s[i] = Vec8<TW>::round(__fdiv_rn(fabsf(Vec8<TW>::round(__fmul_rn(w[i], g[i]))), aux_scalar));
@@ -116,12 +119,16 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
                 }
             }
         }
-        Vec8<float>::store(score + e, s);
+        Span8<float>::store(score, pos, s);
+        // eight values are summed in fp32, the running totals are kept in fp64
+        float ps = 0.0f, ps2 = 0.0f;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            acc_s += (double)s[i];
-            acc_s2 += (double)s[i] * (double)s[i];
+            ps += s[i];
+            ps2 = fmaf(s[i], s[i], ps2);
         }
+        acc_s += (double)ps;
+        acc_s2 += (double)ps2;
     }
     __shared__ double red[2][kThreads / 32];
     acc_s = warp_sum(acc_s);
@@ -168,13 +175,17 @@ score_norm_finalize_kernel(const double* __restrict__ partials, int nblocks, dou
 template <typename TW, typename TV, bool ACCUM>
 static int launch_hutch_score(int metric, const void* hvp, const void* v, float* H, const void* W,
                               const void* aux, float aux_scalar, float* score, double* scratch,
-                              int64_t chunks, double beta_d, int grid, cudaStream_t st) {
+                              int64_t chunks, double beta_d, int& grid, cudaStream_t st) {
     const float beta = (float)beta_d;
     const float omb = (float)(1.0 - beta_d);
 #define SF_LAUNCH_HS(M)                                                                          \
-    hutch_score_kernel<TW, TV, M, ACCUM><<<grid, kThreads, 0, st>>>(                            \
-        (const TW*)hvp, (const TV*)v, H, (const TW*)W, (const TW*)aux, aux_scalar, score, scratch, \
-        chunks, beta, omb)
+    do {                                                                                         \
+        auto kern = hutch_score_kernel<TW, TV, M, ACCUM>;                                        \
+        grid = grid_one_wave((const void*)kern, chunks);                                         \
+        if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;                                  \
+        kern<<<grid, kThreads, 0, st>>>((const TW*)hvp, (const TV*)v, H, (const TW*)W, (const TW*)aux, aux_scalar, \
+                                        score, scratch, chunks, beta, omb);                      \
+    } while (0)
     switch (metric) {
         case SF_METRIC_HESSIAN_OBD: SF_LAUNCH_HS(SF_METRIC_HESSIAN_OBD); break;
         case SF_METRIC_HESSIAN_RATIO: SF_LAUNCH_HS(SF_METRIC_HESSIAN_RATIO); break;
@@ -191,7 +202,7 @@ static int launch_hutch_score(int metric, const void* hvp, const void* v, float*
 // 2:4 soft-mask update + projection + masked weight + metadata + stats
 // ---------------------------------------------------------------------------------------
 struct MaskUpdateParams {
-    float inv_temp_den;  // T + 1e-8 (fp32)
+    float neg_log2e_over_t;  // -log2(e) / (T + 1e-8)
     float a, one_minus_a;
     float pen;
     int penalty_mode;
@@ -203,8 +214,6 @@ struct MaskUpdateParams {
     int structured_exact;
     int score_bf16;
 };
-
-__device__ __forceinline__ float sigmoidf_acc(float x) { return __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-x))); }
 
 __device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
     if (P.soft_only) return m;
@@ -241,7 +250,10 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
                         float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm,
                         uint8_t* __restrict__ meta, double* __restrict__ stats, int64_t chunks,
                         MaskUpdateParams P) {
-    const float mu = norm[0], sigma = norm[1];
+    // The gate needs (s_i - tau) / (sigma (T + 1e-8)) only, so the mean cancels unless the
+    // normalised score has to be rounded to bf16 first.
+    const float mu = norm[0];
+    const float inv_sigma = __fdiv_rn(1.0f, norm[1]);
     GroupStats gs;
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
          c += (int64_t)gridDim.x * kThreads) {
@@ -256,33 +268,32 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
             float s[4], G[4], mp[4], mn[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                s[i] = __fdiv_rn(__fsub_rn(sc[4 * g + i], mu), sigma);
-                if (P.score_bf16) s[i] = bf16_round(s[i]);
+                s[i] = __fmul_rn(__fsub_rn(sc[4 * g + i], mu), inv_sigma);
+                if (P.score_bf16) s[i] = bf16_round_int(s[i]);
                 mp[i] = m[4 * g + i];
             }
             int r[4];
-            rank4(s, r);
-            float tau = s[0];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) if (r[i] == 1) tau = s[i];
+            rank4_fast(s, r);
+            const float tau = r[0] == 1 ? s[0] : (r[1] == 1 ? s[1] : (r[2] == 1 ? s[2] : s[3]));
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float gi;
                 if (P.structured_exact) gi = r[i] < 2 ? 1.0f : 0.0f;
                 else {
-                    gi = sigmoidf_acc(__fdiv_rn(__fsub_rn(s[i], tau), P.inv_temp_den));
-                    if (P.score_bf16) gi = bf16_round(gi);
+                    // sigmoid(z) = 1 / (1 + 2^(-z log2 e)), z = (s_i - tau) / (T + 1e-8)
+                    gi = fast_rcp(1.0f + fast_ex2(__fmul_rn(__fsub_rn(s[i], tau), P.neg_log2e_over_t)));
+                    if (P.score_bf16) gi = bf16_round_int(gi);
                 }
                 if (P.beta_s > 0.0f) {
                     float t = r[i] < 2 ? P.beta_s : 0.0f;
                     gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), t);
-                    if (P.score_bf16) gi = bf16_round(gi);
+                    if (P.score_bf16) gi = bf16_round_int(gi);
                 }
                 G[i] = gi;
             }
             if (P.pen != 0.0f) {
                 if (P.penalty_mode == SF_PENALTY_TOPN) {
-                    uint32_t kg = top2_keep(G);
+                    const uint32_t kg = top2_keep_fast(G);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         float delta = __fsub_rn(mp[i], ((kg >> i) & 1u) ? 1.0f : 0.0f);
@@ -311,21 +322,20 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
                 mn[i] = fminf(fmaxf(v, 0.0f), 1.0f);
                 m[4 * g + i] = mn[i];
             }
-            const uint32_t kp = top2_keep(mp);
-            int rn[4];
-            rank4(mn, rn);
-            uint32_t kn = 0;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) kn |= (rn[i] < 2 ? 1u : 0u) << i;
+            const uint32_t kp = top2_keep_fast(mp);
+            const uint32_t kn = top2_keep_fast(mn);
             gs.flips += __popc(kp ^ kn);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                gs.sum_m += mn[i];
-                gs.sum_m1m += mn[i] * (1.0f - mn[i]);
-                if (rn[i] < 2) gs.sum_top2 += mn[i]; else gs.sum_bot2 += mn[i];
+                const bool top = (kn >> i) & 1u;
+                const float mv = mn[i];
+                gs.sum_m += mv;
+                gs.sum_m1m += __fmaf_rn(-mv, mv, mv);
+                gs.sum_top2 += top ? mv : 0.0f;
+                gs.sum_bot2 += top ? 0.0f : mv;
                 gs.lt_half += mn[i] < 0.5f ? 1 : 0;
                 if (EMIT_WM) {
-                    float eff = Vec8<TW>::round(effective_mask_value(mn[i], (kn >> i) & 1u, P));
+                    float eff = Vec8<TW>::round(effective_mask_value(mn[i], top, P));
                     out_w[4 * g + i] = __fmul_rn(w[4 * g + i], eff);
                 }
             }
@@ -414,7 +424,7 @@ effective_weight_kernel(const TW* __restrict__ W, const float* __restrict__ mask
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
             float s[4] = {m[4 * g], m[4 * g + 1], m[4 * g + 2], m[4 * g + 3]};
-            uint32_t k = top2_keep(s);
+            uint32_t k = top2_keep_fast(s);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float eff = Vec8<TW>::round(effective_mask_value(s[i], (k >> i) & 1u, P));
@@ -435,7 +445,7 @@ struct AdamParams {
     float c_wd;       // 1 - lr*wd
     float decay;
     float beta1, one_minus_beta1, beta2, one_minus_beta2;
-    float sqrt_bc2, eps, step_size, lr, l1;
+    float inv_sqrt_bc2, eps, step_size, lr, l1;
     int has_mask;
 };
 
@@ -462,12 +472,13 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
             float m1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta1, g1, Vec8<TW>::round(__fmul_rn(em[i], A.beta1))));
             float v1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta2, __fmul_rn(g1, g1),
                                                  Vec8<TW>::round(__fmul_rn(ev[i], A.beta2))));
-            float denom = Vec8<TW>::round(__fdiv_rn(Vec8<TW>::round(__fsqrt_rn(v1)), A.sqrt_bc2));
+            float denom = Vec8<TW>::round(__fmul_rn(Vec8<TW>::round(fast_sqrt(v1)), A.inv_sqrt_bc2));
             denom = Vec8<TW>::round(__fadd_rn(denom, A.eps));
-            float p2 = Vec8<TW>::round(__fsub_rn(p1, __fmul_rn(A.step_size, __fdiv_rn(m1, denom))));
+            const float inv_denom = fast_rcp(denom);
+            float p2 = Vec8<TW>::round(__fsub_rn(p1, __fmul_rn(A.step_size, __fmul_rn(m1, inv_denom))));
             if (A.l1 > 0.0f && A.has_mask) {
                 float sgn = (p2 > 0.0f) ? 1.0f : ((p2 < 0.0f) ? -1.0f : 0.0f);
-                float term = Vec8<TW>::round(__fdiv_rn(Vec8<TW>::round(__fmul_rn(A.l1, sgn)), denom));
+                float term = Vec8<TW>::round(__fmul_rn(Vec8<TW>::round(__fmul_rn(A.l1, sgn)), inv_denom));
                 p2 = Vec8<TW>::round(__fsub_rn(p2, __fmul_rn(A.lr, term)));
             }
             pw[i] = p2; em[i] = m1; ev[i] = v1;
@@ -479,7 +490,7 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
 #pragma unroll
             for (int g2 = 0; g2 < 2; ++g2) {
                 float s[4] = {mk[4 * g2], mk[4 * g2 + 1], mk[4 * g2 + 2], mk[4 * g2 + 3]};
-                uint32_t k = P.soft_only ? 0u : top2_keep(s);
+                uint32_t k = P.soft_only ? 0u : top2_keep_fast(s);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float eff = Vec8<TW>::round(effective_mask_value(s[i], (k >> i) & 1u, P));
@@ -604,7 +615,7 @@ static MaskUpdateParams make_mask_params(double temperature, double mask_lr, dou
                                          double beta_s, double binarize_decay, double hx, int structured_exact,
                                          int score_bf16) {
     MaskUpdateParams P;
-    P.inv_temp_den = (float)temperature + 1e-8f;
+    P.neg_log2e_over_t = (float)(-1.4426950408889634 / (double)((float)temperature + 1e-8f));
     P.a = (float)mask_lr;
     P.one_minus_a = (float)(1.0 - mask_lr);
     P.pen = (float)pen;
@@ -642,11 +653,13 @@ int sf_mask_update_nm24(const float* score, const float* norm, float* mask, cons
     MaskUpdateParams P = make_mask_params(temperature, mask_lr, pen, penalty_mode, beta_s, binarize_decay,
                                           hx, structured_exact, score_bf16);
     const int64_t chunks = rows * cols / 8;
-    const int grid = grid_for(chunks, 8);
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
-#define SF_MU(TW, EW, EM)                                                             \
-    mask_update_nm24_kernel<TW, EW, EM><<<grid, kThreads, 0, st>>>(                   \
-        score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P)
+#define SF_MU(TW, EW, EM)                                                                        \
+    do {                                                                                         \
+        auto kern = mask_update_nm24_kernel<TW, EW, EM>;                                         \
+        kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
+            score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);                   \
+    } while (0)
 #define SF_MU_T(TW)                                       \
     do {                                                  \
         if (wm && meta) SF_MU(TW, true, true);            \
@@ -702,7 +715,8 @@ int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm,
     cudaStream_t st = (cudaStream_t)stream;
     MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, finalized ? 1.0 : hx, 0, 0);
     const int64_t chunks = rows * cols / 8;
-    const int grid = grid_for(chunks, 8);
+    const int grid = w_dtype == SF_F32 ? grid_one_wave((const void*)effective_weight_kernel<float>, chunks)
+                                       : grid_one_wave((const void*)effective_weight_kernel<__nv_bfloat16>, chunks);
     if (w_dtype == SF_F32)
         effective_weight_kernel<float><<<grid, kThreads, 0, st>>>((const float*)W, mask, (float*)wm, meta, chunks, P, scale);
     else
@@ -733,7 +747,7 @@ int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v,
     A.decay = (float)decay;
     A.beta1 = (float)beta1; A.one_minus_beta1 = (float)(1.0 - beta1);
     A.beta2 = (float)beta2; A.one_minus_beta2 = (float)(1.0 - beta2);
-    A.sqrt_bc2 = (float)sqrt(bc2);
+    A.inv_sqrt_bc2 = (float)(1.0 / sqrt(bc2));
     A.eps = (float)eps;
     A.step_size = (float)(lr / bc1);
     A.lr = (float)lr;
@@ -741,9 +755,12 @@ int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v,
     A.has_mask = mask != nullptr;
     MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, hx, 0, 0);
     const int64_t chunks = n / 8;
-    const int grid = grid_for(chunks, 8);
-#define SF_AD(TW, EW) \
-    adamw_masked_kernel<TW, EW><<<grid, kThreads, 0, st>>>((TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P)
+#define SF_AD(TW, EW)                                                                            \
+    do {                                                                                         \
+        auto kern = adamw_masked_kernel<TW, EW>;                                                 \
+        kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
+            (TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P);                  \
+    } while (0)
     if (w_dtype == SF_F32) { if (wm) SF_AD(float, true); else SF_AD(float, false); }
     else { if (wm) SF_AD(__nv_bfloat16, true); else SF_AD(__nv_bfloat16, false); }
 #undef SF_AD

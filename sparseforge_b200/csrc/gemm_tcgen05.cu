@@ -36,6 +36,19 @@ constexpr int GEMM_SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /* alignment slack *
 
 enum { WAIT_PRODUCER = 1, WAIT_MMA_FULL = 2, WAIT_MMA_TMEM = 3, WAIT_EPILOGUE = 4 };
 
+// Tile order: groups of RASTER_GROUP_M tile rows, walked column by column inside a group, so the
+// ~148 tiles in flight cover a near-square patch of the output and share operand panels in L2.
+constexpr int RASTER_GROUP_M = 16;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    const int per_group = RASTER_GROUP_M * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * RASTER_GROUP_M;
+    const int gm = min(RASTER_GROUP_M, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    tm = first_m + r % gm;
+    tn = r / gm;
+}
+
 struct GemmSmemTail {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
@@ -93,7 +106,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, WAIT_PRODUCER);
                 if (!ok) break;
@@ -168,7 +183,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
         bool ok = true;
         int t = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
-            const int m0 = (tile / tiles_n) * BM, n0 = (tile % tiles_n) * BN;
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * BM, n0 = tn * BN;
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, WAIT_EPILOGUE);

@@ -143,6 +143,18 @@ __device__ __forceinline__ void tmem_ld_32x32b_x16(uint32_t taddr, uint32_t (&r)
         : "memory");
 }
 
+// Same near-square patch order as the dense GEMM: groups of 16 weight-row tiles.
+__device__ __forceinline__ void sp_tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+    constexpr int G = 16;
+    const int per_group = G * tiles_n;
+    const int g = tile / per_group;
+    const int first_m = g * G;
+    const int gm = min(G, tiles_m - first_m);
+    const int r = tile - g * per_group;
+    tm = first_m + r % gm;
+    tn = r / gm;
+}
+
 template <int BN>
 __global__ void __launch_bounds__(SP_THREADS, 1)
 sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -192,7 +204,8 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t phase = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-            const int mt = tile % tiles_m, nt = tile / tiles_m;
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 11);
                 if (!ok) break;
@@ -255,7 +268,8 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         bool ok = true;
         int t = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
-            const int mt = tile % tiles_m, nt = tile / tiles_m;
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 14);

@@ -280,3 +280,49 @@ def test_bad_arguments_are_refused(ops):
         ops.gemm_fwd(torch.zeros(8, 16, device=DEV), torch.zeros(16, 16, device=DEV, dtype=torch.bfloat16))
     with pytest.raises(TypeError):
         ops.project_nm24(torch.zeros(8, 8, device=DEV, dtype=torch.float16))
+
+
+# ---------------------------------------------------------------------------------------
+# sizes that do not fill the last 256-element warp span
+# ---------------------------------------------------------------------------------------
+@pytest.mark.parametrize("shape", [(24, 40), (3, 8), (33, 72)])
+def test_ragged_sizes_against_oracle(ops, shape):
+    from sparseforge_b200 import _lib
+
+    torch.manual_seed(shape[0] * 100 + shape[1])
+    rows, cols = shape
+    W = torch.randn(rows, cols) * 0.02
+    H0 = torch.rand(rows, cols) + 0.1
+    hvp = torch.randn(rows, cols) * 0.01
+    v = (torch.randint(0, 2, (rows, cols), dtype=torch.int8) * 2 - 1)
+    mask0 = torch.rand(rows, cols)
+    Hd = dev(H0)
+    score = torch.full((rows, cols), -7.0, device=DEV)
+    norm = torch.zeros(2, device=DEV)
+    ops.hutch_score(dev(W), Hd, score, norm, ops.hutch_score_scratch(DEV), hvp=dev(hvp), v=dev(v), beta=0.9)
+    H1 = O.hutchinson_accumulate(H0, hvp, v.float(), 0.9)
+    want = O.importance_score(W, "hessian_obd", H=H1)
+    assert rel_err(Hd, H1) <= F32_TOL and rel_err(score, want) <= F32_TOL
+    mu, sigma = O.score_norm_stats(want)
+    assert abs(float(norm[0]) - float(mu)) <= F32_TOL * abs(float(mu))
+    assert abs(float(norm[1]) - float(sigma)) <= F32_TOL * abs(float(sigma))
+    mask, stats, wm, meta = run_mask_update(ops, W, H1, mask0, T=0.3, mask_lr=0.25, pen=0.05, pmode=_lib.PENALTY_TOPN, hx=0.5)
+    G = O.gate_target_structured(O.normalize_scores(want), 0.3)
+    want_mask = O.mask_update(mask0, G, mask_lr=0.25, lambda_mid=1.0, pen_lr=0.05, penalty_mode="structured_topn")
+    assert rel_err(mask, want_mask) <= F32_TOL
+    assert int(stats[_lib.MSTAT_FLIPS]) == O.flip_count(mask0, mask)
+    st = O.mask_stats(mask)
+    assert abs(float(stats[_lib.MSTAT_SUM_M]) - st["sum_m"]) <= 1e-5 * st["sum_m"]
+    assert float(stats[_lib.MSTAT_COUNT_LT_HALF]) == st["count_lt_half"]
+    assert torch.equal(unpack_meta(meta, cols), O.hard_mask_from_soft(mask))
+    assert rel_err(wm, O.masked_weight(W, O.effective_mask(mask, 0.5))) <= F32_TOL
+    p = dev(W)
+    m, vv = torch.zeros_like(p), torch.zeros_like(p)
+    g = torch.randn(rows, cols) * 0.1
+    wm2 = torch.empty_like(p)
+    ops.adamw_masked(p, dev(g), m, vv, mask=dev(mask0), lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                     decay=1e-3, step=1, wm=wm2, hx=0.25)
+    wp, wm_, wv = O.adamw_step(W, g, torch.zeros(rows, cols), torch.zeros(rows, cols), step=1, lr=1e-3, betas=(0.9, 0.95),
+                               eps=1e-8, weight_decay=0.1, mask=mask0, decay=1e-3)
+    assert rel_err(p, wp) <= F32_TOL and rel_err(m, wm_) <= F32_TOL and rel_err(vv, wv) <= F32_TOL
+    assert rel_err(wm2, O.masked_weight(wp, O.effective_mask(mask0, 0.25))) <= F32_TOL
