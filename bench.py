@@ -163,16 +163,37 @@ def run_ours(args):
     decay_t = 0.05 ** (1.0 / 9.0)
     launches = 0
 
+    # end-to-end leg: two staging buffers per operand, filled from pinned host memory on a copy stream
+    copy_stream = torch.cuda.Stream(device=dev)
+    stage_free = [torch.cuda.Event(), torch.cuda.Event()]
+    stage_x = stage_dy = None
+
+    def prefetch(j):
+        mt, b = mats[j], j % 2
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(stage_free[b])
+            xs = stage_x[b][: T * mt.cols].view(T, mt.cols)
+            dys = stage_dy[b][: T * mt.rows * world].view(T, mt.rows * world)
+            xs.copy_(host_X[mt.cols], non_blocking=True)
+            dys.copy_(host_dY[mt.rows * world], non_blocking=True)
+            ready = torch.cuda.Event()
+            ready.record(copy_stream)
+        return xs, dys, ready
+
     def step(it, timers=None, e2e=False):
         nonlocal launches
         temp = max(0.05, decay_t ** (it % 10))
         hx = max(0.0, min(1.0, 1.0 - ((it % 10) - 1) / 9.0)) if (it % 10) >= 1 else 1.0
-        for mt in mats:
-            x = X[mt.cols]
+        pending = prefetch(0) if e2e else None
+        for i, mt in enumerate(mats):
             if e2e:
-                x.copy_(host_X[mt.cols], non_blocking=True)
-                dYfull[mt.rows * world].copy_(host_dY[mt.rows * world], non_blocking=True)
-            dy_full = dYfull[mt.rows * world]
+                # inputs of this matrix arrive from pinned host memory on the copy stream while the
+                # previous matrix computes; the next matrix's copy is queued before this one's kernels
+                x, dy_full, ready = pending
+                pending = prefetch(i + 1) if i + 1 < len(mats) else None
+                torch.cuda.current_stream().wait_event(ready)
+            else:
+                x, dy_full = X[mt.cols], dYfull[mt.rows * world]
             dy = dy_full if world == 1 else dy_full[:, rank * mt.rows:(rank + 1) * mt.rows].contiguous()
 
             def timed(key, fn):
@@ -203,6 +224,8 @@ def run_ours(args):
                                                     eps=1e-8, weight_decay=0.1, decay=2e-4, step=it + 1))
             timed("mask", lambda: ops.mask_update_nm24(mt.score, mt.norm, mt.mask, mt.stats, W=mt.W, wm=mt.wm,
                                                        meta=mt.meta, temperature=temp, mask_lr=0.1, hx=hx))
+            if e2e:
+                stage_free[i % 2].record()
         if e2e:
             return torch.stack([mt.stats for mt in mats]).to("cpu", non_blocking=False)
         return None
@@ -240,6 +263,11 @@ def run_ours(args):
     if not args.no_e2e:
         host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in shapes}}
         host_dY = {w: dYfull[w].cpu().pin_memory() for w in {r for _, r, _ in shapes}}
+        wmax = max(widths)
+        stage_x = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
+        stage_dy = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
+        for ev in stage_free:
+            ev.record()
         step(0, e2e=True)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)

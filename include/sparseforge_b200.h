@@ -75,11 +75,21 @@ SF_API int64_t sf_hutch_score_scratch_doubles(int64_t n);
  * aux is grad_ema for SF_METRIC_MOVEMENT (w_dtype), else ignored; aux_scalar is the
  * movement temperature. scratch: sf_hutch_score_scratch_doubles(n) doubles.
  * n = rows*cols, must be a multiple of 8; buffers 16-byte aligned.
+ * On return scratch[0] and scratch[1] hold sum(score) and sum(score^2) of this call, for
+ * callers that hold one shard of a layer and combine the sums across shards.
  */
 SF_API int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const void* W,
                    int w_dtype, const void* aux, double aux_scalar, float* score,
                    float* norm, double* scratch, int64_t n, double beta, int metric,
                    void* stream);
+
+/*
+ * norm <- (mean, std_pop + 1e-6) from sums[0] = sum(score), sums[1] = sum(score^2) over n
+ * elements (device pointers). Used after the sums of the row shards of one layer have been
+ * added up across ranks; the same arithmetic as the tail of sf_hutch_score
+ * (legacy/sparse_modeling.py:1085-1087 over the whole layer).
+ */
+SF_API int sf_score_norm_from_sums(const double* sums, double n, float* norm, void* stream);
 
 /*
  * sf_hutch_score without a scratch argument: the partial sums go to an array that is part

@@ -148,7 +148,7 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
 // One block folds the per-block partial sums in a fixed order (deterministic) and writes
 // mean and population std + 1e-6 as fp32.
 __global__ void __launch_bounds__(kThreads)
-score_norm_finalize_kernel(const double* __restrict__ partials, int nblocks, double n,
+score_norm_finalize_kernel(double* __restrict__ partials, int nblocks, double n,
                            float* __restrict__ norm) {
     __shared__ double red[2][kThreads];
     double a = 0.0, b = 0.0;
@@ -166,6 +166,19 @@ score_norm_finalize_kernel(const double* __restrict__ partials, int nblocks, dou
     if (threadIdx.x == 0) {
         double mean = red[0][0] / n;
         double var = red[1][0] / n - mean * mean;
+        if (var < 0.0) var = 0.0;
+        norm[0] = (float)mean;
+        norm[1] = __fadd_rn((float)sqrt(var), 1e-6f);
+        // the raw sums stay available to callers that combine several shards of one layer
+        partials[0] = red[0][0];
+        partials[1] = red[1][0];
+    }
+}
+
+__global__ void score_norm_from_sums_kernel(const double* __restrict__ sums, double n, float* __restrict__ norm) {
+    if (threadIdx.x == 0 && blockIdx.x == 0) {
+        double mean = sums[0] / n;
+        double var = sums[1] / n - mean * mean;
         if (var < 0.0) var = 0.0;
         norm[0] = (float)mean;
         norm[1] = __fadd_rn((float)sqrt(var), 1e-6f);
@@ -607,6 +620,14 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
 #undef SF_HS
     if (rc != SF_OK) return rc;
     score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_score_norm_from_sums(const double* sums, double n, float* norm, void* stream) {
+    SF_CHECK_ARG(sums && norm, "sf_score_norm_from_sums: sums and norm must be non-null");
+    SF_CHECK_ARG(n > 0, "sf_score_norm_from_sums: n must be positive");
+    score_norm_from_sums_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(sums, n, norm);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }

@@ -305,3 +305,9 @@ def bsr16_wgrad(dy2d, x2d, row_ptr, col_idx, workspace=None, status=None):
     check(lib().sf_bsr16_wgrad(_p(dy2d), _p(x2d), _p(row_ptr), _p(col_idx), _p(dblocks), _p(ws), T, k, out,
                                _gemm_dtype(dy2d, x2d), _p(status), _stream()), "sf_bsr16_wgrad")
     return dblocks
+
+
+def score_norm_from_sums(sums, n, norm) -> None:
+    """norm <- (mean, std + 1e-6) from device sums (sum s, sum s^2) over n elements."""
+    _cuda(sums, norm)
+    check(lib().sf_score_norm_from_sums(_p(sums), float(n), _p(norm), _stream()), "sf_score_norm_from_sums")

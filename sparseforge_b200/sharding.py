@@ -1,0 +1,125 @@
+"""Row sharding of a SparseLinear layer over the GPUs of one box.
+
+Rows of the weight (``out_features``) are split evenly over the ranks of a process group. 2:4 groups
+run along ``in_features``, so the soft mask, hard projection, metadata, Hessian diagonal, Adam state
+and the weight gradient of a shard are local to its rank. What crosses ranks:
+
+* forward: the output columns of the shards are all-gathered;
+* backward: the partial input gradients of the shards are summed (all-reduce);
+* mask update: the score normalisation is layer-wide (legacy/sparse_modeling.py:1084-1088), so
+  sum(score), sum(score^2) of the shards are all-reduced before mean / std are formed.
+
+The reference shards the same layer through FSDP flat parameters and gathers every parameter for a
+mask update (legacy/utils.py:246-251); here nothing but the three items above is exchanged.
+The collectives go through ``torch.distributed`` (NCCL on GPUs; the functions below are
+backend-agnostic and are exercised with gloo in the CPU tests).
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+
+def shard_bounds(out_features: int, world: int, rank: int, multiple: int = 16) -> Tuple[int, int]:
+    """[start, stop) rows of ``rank``. Every shard has out_features / world rows, a multiple of
+    ``multiple`` (16 keeps block-16 tiles and 16-byte rows whole)."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} for world size {world}")
+    if out_features % world != 0 or (out_features // world) % multiple != 0:
+        raise ValueError(f"out_features={out_features} cannot be split into {world} shards of a multiple of {multiple} rows")
+    rows = out_features // world
+    return rank * rows, (rank + 1) * rows
+
+
+def combine_score_sums(sums: torch.Tensor, n_local: int, group=None) -> Tuple[torch.Tensor, int]:
+    """All-reduce (sum s, sum s^2) of the shards of one layer; returns the layer-wide sums and count."""
+    world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+    if world > 1:
+        dist.all_reduce(sums, op=dist.ReduceOp.SUM, group=group)
+    return sums, n_local * world
+
+
+class _GatherColumns(torch.autograd.Function):
+    """[T, rows] per rank -> [T, rows * world]; backward keeps the rank's own column block."""
+
+    @staticmethod
+    def forward(ctx, y_local, group):
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        ctx.rank, ctx.rows = rank, y_local.shape[-1]
+        flat = torch.empty(world * y_local.numel(), dtype=y_local.dtype, device=y_local.device)
+        dist.all_gather_into_tensor(flat, y_local.contiguous().view(-1), group=group)
+        parts = flat.view((world,) + tuple(y_local.shape))
+        # parts[r] holds the columns of rank r: move the rank axis next to the column axis
+        return parts.movedim(0, -2).reshape(*y_local.shape[:-1], world * y_local.shape[-1])
+
+    @staticmethod
+    def backward(ctx, gy):
+        r, n = ctx.rank, ctx.rows
+        return gy[..., r * n:(r + 1) * n].contiguous(), None
+
+
+class _SumInputGrad(torch.autograd.Function):
+    """Identity in forward; backward sums the partial input gradients of the shards."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, gx):
+        gx = gx.contiguous()
+        dist.all_reduce(gx, op=dist.ReduceOp.SUM, group=ctx.group)
+        return gx, None
+
+
+def gather_columns(y_local: torch.Tensor, group=None) -> torch.Tensor:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return y_local
+    return _GatherColumns.apply(y_local, group)
+
+
+def sum_input_grad(x: torch.Tensor, group=None) -> torch.Tensor:
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size(group) == 1:
+        return x
+    return _SumInputGrad.apply(x, group)
+
+
+class RowShardedLinear(nn.Module):
+    """Wraps the shard of a linear layer held by this rank (any module mapping [..., in] to
+    [..., out / world], e.g. a ``SparseLinear`` built with ``out_features // world`` rows)."""
+
+    def __init__(self, shard: nn.Module, group=None):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+        if hasattr(shard, "_row_shard_group"):
+            shard._row_shard_group = group
+            shard._row_sharded = True
+
+    def forward(self, x):
+        return gather_columns(self.shard(sum_input_grad(x, self.group)), self.group)
+
+
+def shard_sparse_linear(full_weight: torch.Tensor, config, bias: Optional[torch.Tensor] = None, group=None,
+                        device=None, dtype=None) -> RowShardedLinear:
+    """Builds this rank's ``SparseLinear`` shard from the full weight and wraps it."""
+    from .sparse_modeling import SparseLinear
+
+    world = dist.get_world_size(group) if (dist.is_available() and dist.is_initialized()) else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    out_f, in_f = full_weight.shape
+    lo, hi = shard_bounds(out_f, world, rank)
+    layer = SparseLinear(in_f, hi - lo, sparselinear_config=config, bias=bias is not None)
+    layer = layer.to(device=device or full_weight.device, dtype=dtype or full_weight.dtype)
+    layer.mask.data = layer.mask.data.float()
+    layer.hessian_diag.data = layer.hessian_diag.data.float()
+    with torch.no_grad():
+        layer.weight.copy_(full_weight[lo:hi])
+        if bias is not None:
+            layer.bias.copy_(bias[lo:hi])
+    layer.initialize()
+    return RowShardedLinear(layer, group)

@@ -312,6 +312,8 @@ class SparseLinear(nn.Linear):
         self._stats = None
         self._scratch = None
         self.last_mask_stats = None  # device float64[8] written by the last update_mask
+        self._row_shard_group = None  # set by sharding.RowShardedLinear when this is one shard of a layer
+        self._row_sharded = False
 
     # -- helpers -------------------------------------------------------------------------
     def _is_placeholder(self, name: str) -> bool:
@@ -487,6 +489,7 @@ class SparseLinear(nn.Linear):
         ops.hutch_score(self.weight.data, self.hessian_diag.data, self._score, self._norm, self._scratch,
                         hvp=hvp.contiguous(), v=v.contiguous(), beta=float(self.cfg.beta if beta is None else beta),
                         metric=self.mask_metric if self.mask_metric in _SUPPORTED_METRICS else "hessian_obd")
+        self._combine_shard_norm()
 
     # -- schedules (host scalars) --------------------------------------------------------------
     def _mask_update_period(self, step: int) -> int:
@@ -554,6 +557,17 @@ class SparseLinear(nn.Linear):
                 aux = self.grad_ema.data
         ops.hutch_score(self.weight.data, H, self._score, self._norm, self._scratch, aux=aux,
                         aux_scalar=float(self.cfg.temperature), metric=metric)
+        self._combine_shard_norm()
+
+    def _combine_shard_norm(self):
+        """Score mean / std are taken over the whole layer: when this module is one row shard, add up
+        the shards' sums before forming them."""
+        if not self._row_sharded:
+            return
+        from .sharding import combine_score_sums
+
+        sums, n = combine_score_sums(self._scratch[:2], self.weight.numel(), self._row_shard_group)
+        ops.score_norm_from_sums(sums, n, self._norm)
 
     def _score_is_bf16(self) -> bool:
         # the reference's score has dtype promote(weight, hessian): bf16 only when no fp32 Hessian enters

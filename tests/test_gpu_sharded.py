@@ -1,0 +1,83 @@
+"""Row-sharded SparseLinear on two GPUs (NCCL) against the same layer unsharded on one GPU.
+Skipped on a box with a single GPU. A rank leaves only after its last collective has completed."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import sparseforge_b200 as sf
+        from sparseforge_b200 import utils as U
+        from sparseforge_b200.sharding import shard_bounds, shard_sparse_linear
+
+        torch.manual_seed(0)
+        out_f, in_f, T = 512, 256, 256
+        bf = torch.bfloat16
+        W = (torch.randn(out_f, in_f) * 0.02).to(bf).to(dev)
+        X = torch.randn(2, T // 2, in_f).to(bf).to(dev)
+        dY = torch.randn(2, T // 2, out_f).to(bf).to(dev)
+        cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", mask_update_period=1,
+                                    sparsity_warmup_steps=0, mask_lr=0.1, mask_hardening_start=0, mask_hardening_duration=4)
+        full = sf.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False).to(dev).to(bf)
+        full.weight.data.copy_(W)
+        full.initialize()
+        sharded = shard_sparse_linear(W, cfg)
+        lo, hi = shard_bounds(out_f, world, rank)
+
+        def rel(a, b):
+            return float((a.double() - b.double()).abs().max()) / max(float(b.double().abs().max()), 1e-30)
+
+        ok = True
+        for step in range(2):
+            U.calculate_model_mask(full, step=step)
+            U.calculate_model_mask(sharded, step=step)
+            ok = ok and rel(sharded.shard.mask.data, full.mask.data[lo:hi]) <= 1e-5
+            ok = ok and sharded.shard.hardening_x == full.hardening_x
+            x1 = X.clone().requires_grad_(True)
+            x2 = X.clone().requires_grad_(True)
+            y1, y2 = full(x1), sharded(x2)
+            y1.backward(dY)
+            y2.backward(dY)
+            ok = ok and rel(y2, y1) <= 1e-2 and rel(x2.grad, x1.grad) <= 1e-2
+            ok = ok and rel(sharded.shard.weight.grad, full.weight.grad[lo:hi]) <= 1e-2
+        flips = torch.tensor([int(sharded.shard.weight.flipped_mask)], device=dev)
+        dist.all_reduce(flips)
+        ok = ok and abs(int(flips) - int(full.weight.flipped_mask)) <= 2
+        torch.cuda.synchronize()
+        dist.barrier()
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sharded_layer_matches_unsharded_on_two_gpus():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=300)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert dict(q.get(timeout=10) for _ in range(world)) == {0: True, 1: True}

@@ -1,0 +1,147 @@
+"""CPU-side checks: the C-ABI library loads and exports every symbol the header declares, host
+schedules and shard arithmetic match the reference formulas, and the product refuses CPU tensors
+(there is no fallback path)."""
+import math
+import os
+import re
+
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def header_symbols():
+    text = open(os.path.join(ROOT, "include", "sparseforge_b200.h")).read()
+    return sorted(set(re.findall(r"SF_API\s+[\w\s\*]+?\b(sf_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from sparseforge_b200 import _lib
+
+    lib = _lib.lib()
+    declared = header_symbols()
+    assert len(declared) >= 25
+    missing = [n for n in declared if not hasattr(lib, n)]
+    assert not missing, missing
+    # the ctypes table covers the header, nothing more, nothing less
+    assert sorted(_lib.declared_symbols()) == declared
+    assert lib.sf_version() >= 100
+    assert int(lib.sf_hutch_score_scratch_doubles(1 << 20)) == 4096
+    assert int(lib.sf_sparse24_meta_tc_bytes(256, 384)) == 2 * 3 * 2048
+
+
+def test_argument_errors_come_back_as_codes_without_a_gpu():
+    from sparseforge_b200 import _lib
+
+    lib = _lib.lib()
+    # null pointers / bad sizes are refused on the host before anything touches a device
+    assert lib.sf_project_nm24(None, 0, 8, None, 0, 8, None, 4, 8, None) == -1
+    assert b"soft must be non-null" in lib.sf_last_error_string()
+    assert lib.sf_masked_gemm_fwd(1 << 12, 1 << 12, None, 1 << 12, 8, 12, 8, 1.0, 1, None, None) == -2
+    assert b"multiples of 8" in lib.sf_last_error_string()
+    assert lib.sf_sparse24_gemm(16, 16, 16, None, 16, 8, 24, 8, None, None) == -2
+    assert lib.sf_bsr16_build(16, None, 1, 1, None, 16, None, None, 24, 32, None) == -1
+
+
+def test_ops_refuse_cpu_tensors():
+    from sparseforge_b200 import ops
+    import sparseforge_b200 as sf
+
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.project_nm24(torch.rand(4, 8))
+    with pytest.raises(RuntimeError, match="CUDA"):
+        ops.gemm_fwd(torch.zeros(8, 8), torch.zeros(8, 8))
+    layer = sf.SparseLinear(16, 16, sparselinear_config=sf.SparseLinearConfig(), bias=False)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        layer(torch.zeros(2, 16))
+    p = torch.nn.Parameter(torch.zeros(8, 8))
+    p.grad = torch.zeros(8, 8)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        sf.AdamW([p]).step()
+
+
+def test_config_fields_match_the_reference_dataclass():
+    import dataclasses
+
+    import sparseforge_b200 as sf
+
+    want = ["change_mask", "mode", "mask_type", "mask_metric", "sparsity_ratio", "N", "M", "beta", "score_ema_beta",
+            "mask_update_period", "mask_update_switch_step", "mask_update_period_before", "mask_update_period_after",
+            "mask_lr", "mask_penalty_lr", "mask_penalty_mode", "temp_init", "temp_min", "temp_decay",
+            "mask_binarize_decay", "mask_hardening_start", "mask_hardening_duration", "sparsity_warmup_steps",
+            "tau_sample_size", "temperature", "freeze_low", "freeze_high", "SLoRB", "SLoRB_k", "SLoRB_init_type",
+            "trainable_projection", "structured_exact", "hard_mask_type", "beta_structural_start",
+            "beta_structural_end", "gradient_checkpointing", "srste_decay", "glu_joint_mask", "weight_scaling"]
+    assert [f.name for f in dataclasses.fields(sf.SparseLinearConfig)] == want
+    cfg = sf.SparseLinearConfig()
+    assert (cfg.mask_lr, cfg.temp_decay, cfg.mask_update_period, cfg.sparsity_warmup_steps) == (0.10, 0.97, 10, 100)
+
+
+def test_host_schedules_match_reference_formulas():
+    import sparseforge_b200 as sf
+    from oracle import sparselinear_oracle as O
+
+    cfg = sf.SparseLinearConfig(temp_init=1.0, temp_min=0.05, temp_decay=0.7, mask_update_period=3,
+                                mask_hardening_start=5, mask_hardening_duration=10, sparsity_warmup_steps=20,
+                                beta_structural_start=4, beta_structural_end=12)
+    layer = sf.SparseLinear(16, 8, sparselinear_config=cfg, bias=False)
+    for step in (0, 1, 2, 3, 7, 30, 100):
+        assert layer._temperature(step) == pytest.approx(O.temperature_at(step, 1.0, 0.7, 0.05, period=3), rel=1e-12)
+        assert layer._next_hardening_x(step) == pytest.approx(O.hardening_x(step, 5, 10), abs=1e-12)
+    assert layer._effective_sparsity(10) == pytest.approx(0.25)
+    assert layer._beta_structural(3) == 0.0 and layer._beta_structural(12) == 1.0
+    t = (8 - 4) / 8
+    assert layer._beta_structural(8) == pytest.approx(3 * t * t - 2 * t ** 3)
+    cfg2 = sf.SparseLinearConfig(mask_update_switch_step=10, mask_update_period_before=2, mask_update_period_after=5)
+    l2 = sf.SparseLinear(16, 8, sparselinear_config=cfg2, bias=False)
+    assert (l2._mask_update_period(9), l2._mask_update_period(10)) == (2, 5)
+    # state-dict keys of the reference layer
+    assert set(layer.state_dict()) == {"weight", "mask", "grad_ema", "hessian_diag", "frozen_mask_flags", "scaler_row"}
+    assert layer.mask.dtype == torch.float32 and layer.grad_ema.numel() == 1 and layer._is_placeholder("grad_ema")
+
+
+def test_unsupported_configurations_raise():
+    import sparseforge_b200 as sf
+
+    with pytest.raises(NotImplementedError):
+        sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(mask_metric="wanda"))
+    with pytest.raises(NotImplementedError):
+        sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(freeze_low=0.1))
+    with pytest.raises(NotImplementedError):
+        sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(SLoRB=True))
+    with pytest.raises(NotImplementedError):
+        sf.AdamW([torch.nn.Parameter(torch.zeros(2))], amsgrad=True)
+    with pytest.raises(ValueError):
+        sf.AdamW([torch.nn.Parameter(torch.zeros(2))], lr=-1.0)
+
+
+def test_shard_bounds():
+    from sparseforge_b200.sharding import shard_bounds
+
+    for out in (4096, 11008):
+        for world in (1, 2, 4, 8):
+            spans = [shard_bounds(out, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == out
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            assert all((hi - lo) % 16 == 0 for lo, hi in spans)
+    with pytest.raises(ValueError):
+        shard_bounds(11008, 3, 0)
+    with pytest.raises(ValueError):
+        shard_bounds(4096, 4, 4)
+
+
+def test_get_raw_model_unwraps():
+    from sparseforge_b200 import utils as U
+
+    class Box(torch.nn.Module):
+        def __init__(self, inner, attr):
+            super().__init__()
+            setattr(self, attr, inner)
+
+    core = torch.nn.Linear(2, 2)
+    assert U.get_raw_model(core) is core
+    assert U.get_raw_model(Box(core, "module")) is core
+    assert U.get_raw_model(Box(core, "student")) is core
+    assert U.get_raw_model(Box(Box(core, "student"), "module")) is core
+    assert math.isclose(U.update_mask_penalty_lr(core, 5, 10, 0.0, 1.0, "linear"), 0.5)

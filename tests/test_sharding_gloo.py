@@ -1,0 +1,73 @@
+"""Row-sharding collectives on CPU ranks (gloo, world size 2): gathering output columns, summing
+partial input gradients and combining the score sums must reproduce the unsharded layer."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sparseforge_b200.sharding import RowShardedLinear, combine_score_sums, shard_bounds
+
+        torch.manual_seed(0)  # identical "full" tensors on every rank
+        out_f, in_f, T = 64, 48, 10
+        W = torch.randn(out_f, in_f, dtype=torch.float64)
+        X = torch.randn(2, T // 2, in_f, dtype=torch.float64)
+        dY = torch.randn(2, T // 2, out_f, dtype=torch.float64)
+        lo, hi = shard_bounds(out_f, world, rank)
+        shard = torch.nn.Linear(in_f, hi - lo, bias=False, dtype=torch.float64)  # stand-in for the local shard
+        with torch.no_grad():
+            shard.weight.copy_(W[lo:hi])
+        layer = RowShardedLinear(shard)
+        x = X.clone().requires_grad_(True)
+        y = layer(x)
+        y.backward(dY)
+        ref_x = X.clone().requires_grad_(True)
+        ref_y = ref_x @ W.t()
+        ref_y.backward(dY)
+        ok = torch.allclose(y, ref_y) and torch.allclose(x.grad, ref_x.grad)
+        ok = ok and torch.allclose(shard.weight.grad, (dY.reshape(T, out_f).t() @ X.reshape(T, in_f))[lo:hi])
+        # layer-wide score statistics from per-shard sums
+        score = (W * W)[lo:hi]
+        sums = torch.stack([score.sum(), (score * score).sum()])
+        sums, n = combine_score_sums(sums, score.numel())
+        mean = sums[0] / n
+        std = (sums[1] / n - mean * mean).sqrt()
+        full = W * W
+        ok = ok and n == full.numel() and torch.allclose(mean, full.mean()) and torch.allclose(std, full.std(unbiased=False))
+        out_q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_row_sharded_layer_matches_unsharded_on_two_gloo_ranks():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=180)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    results = dict(q.get(timeout=10) for _ in range(world))
+    assert results == {0: True, 1: True}
+
+
+def test_single_process_is_a_no_op():
+    from sparseforge_b200.sharding import gather_columns, sum_input_grad
+
+    x = torch.randn(3, 4)
+    assert gather_columns(x) is x and sum_input_grad(x) is x
