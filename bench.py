@@ -209,13 +209,15 @@ def run_ours(args):
                 return out
 
             y = timed("gemm", lambda: ops.gemm_fwd(x, mt.wm, status=status))
+            works = []
             if world > 1:
+                # the collectives run on NCCL's own stream and overlap the next products
                 yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
-                dist.all_gather_into_tensor(yg, y)
+                works.append(dist.all_gather_into_tensor(yg, y, async_op=True))
             dx = timed("gemm", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
             if world > 1:
                 dxs = torch.empty(T // world, mt.cols, dtype=bf, device=dev)
-                dist.reduce_scatter_tensor(dxs, dx)
+                works.append(dist.reduce_scatter_tensor(dxs, dx, async_op=True))
             dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
             timed("score", lambda: ops.hutch_score(mt.W, mt.H, mt.score, mt.norm, mt.scratch, hvp=mt.hvp, v=mt.probe,
                                                    beta=0.99))
@@ -224,6 +226,8 @@ def run_ours(args):
                                                     eps=1e-8, weight_decay=0.1, decay=2e-4, step=it + 1))
             timed("mask", lambda: ops.mask_update_nm24(mt.score, mt.norm, mt.mask, mt.stats, W=mt.W, wm=mt.wm,
                                                        meta=mt.meta, temperature=temp, mask_lr=0.1, hx=hx))
+            for wk in works:
+                wk.wait()
             if e2e:
                 stage_free[i % 2].record()
         if e2e:

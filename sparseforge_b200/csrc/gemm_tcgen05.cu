@@ -309,6 +309,10 @@ static EncodeTiledFn encode_tiled_fn() {
 // 64 inner elements x box_outer rows.
 int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t ld,
                          int box_outer) {
+    // The encode call goes straight to the driver and needs a context current on this thread. A
+    // thread that has not made a runtime call yet (e.g. an autograd worker on device 0) has none:
+    // a no-op runtime call binds the primary context of the current device first.
+    SF_CHECK_CUDA(cudaFree(nullptr));
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};

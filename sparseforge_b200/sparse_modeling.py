@@ -316,6 +316,20 @@ class SparseLinear(nn.Linear):
         self._row_sharded = False
 
     # -- helpers -------------------------------------------------------------------------
+    def _apply(self, fn, recurse=True):
+        """``.to(dtype)`` / ``.half()`` / ``.bfloat16()`` convert the weight; the soft mask and the
+        Hessian diagonal stay float32 (the kernels read them as such), moved to the new device."""
+        keep = {n: getattr(self, n).data for n in ("mask", "hessian_diag") if not self._is_placeholder(n)}
+        out = super()._apply(fn, recurse) if recurse is not True else super()._apply(fn)
+        for n, old in keep.items():
+            prm = getattr(self, n)
+            if prm.dtype != torch.float32:
+                prm.data = old.to(device=prm.device, dtype=torch.float32)
+        self.weight.mask = self.mask
+        self.weight._sf_owner = weakref.ref(self)
+        self._wm_key = None
+        return out
+
     def _is_placeholder(self, name: str) -> bool:
         return getattr(self, f"_{name}_placeholder", False)
 

@@ -189,3 +189,26 @@ def test_sparse_linear_chain(case, dtype, tol, steps_cfg):
     stats = U.nm_2_4_tile_stats(layer)
     want = O.mask_stats(layer.mask.data.cpu())
     assert stats["top2_avg"] == pytest.approx(want["sum_top2"] / (layer.mask.numel() / 2), rel=1e-5)
+
+
+def test_gemm_from_a_fresh_thread(ops):
+    """The tensor-core GEMM is callable as the first CUDA action of a new host thread (autograd runs
+    backward passes on such threads)."""
+    import threading
+
+    x = torch.randn(64, 64, device=DEV).to(torch.bfloat16)
+    w = torch.randn(64, 64, device=DEV).to(torch.bfloat16)
+    out = {}
+
+    def run():
+        try:
+            out["y"] = ops.gemm_dgrad(x, w)
+            torch.cuda.synchronize()
+        except Exception as e:  # surfaced below
+            out["err"] = e
+
+    t = threading.Thread(target=run)
+    t.start()
+    t.join()
+    assert "err" not in out, out.get("err")
+    assert rel_err(out["y"], x.float() @ w.float()) <= BF16_TOL
