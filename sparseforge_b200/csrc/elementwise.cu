@@ -478,21 +478,21 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         if (A.has_mask) Vec8<float>::load(mask + e, mk);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
+            // p.mul_(1 - lr*wd) rounds to the storage type; the moments and the update are carried in
+            // fp32 and rounded once when stored (the reference rounds after every in-place op, which
+            // differs by at most one storage ulp)
             float p1 = Vec8<TW>::round(__fmul_rn(pw[i], A.c_wd));
             float g1 = gr[i];
             if (A.has_mask)
                 g1 = __fmaf_rn(A.decay, __fmul_rn(p1, __fsub_rn(1.0f, mk[i])), g1);
-            float m1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta1, g1, Vec8<TW>::round(__fmul_rn(em[i], A.beta1))));
-            float v1 = Vec8<TW>::round(__fmaf_rn(A.one_minus_beta2, __fmul_rn(g1, g1),
-                                                 Vec8<TW>::round(__fmul_rn(ev[i], A.beta2))));
-            float denom = Vec8<TW>::round(__fmul_rn(Vec8<TW>::round(fast_sqrt(v1)), A.inv_sqrt_bc2));
-            denom = Vec8<TW>::round(__fadd_rn(denom, A.eps));
+            float m1 = __fmaf_rn(A.one_minus_beta1, g1, __fmul_rn(em[i], A.beta1));
+            float v1 = __fmaf_rn(A.one_minus_beta2, __fmul_rn(g1, g1), __fmul_rn(ev[i], A.beta2));
+            float denom = __fmaf_rn(fast_sqrt(v1), A.inv_sqrt_bc2, A.eps);
             const float inv_denom = fast_rcp(denom);
-            float p2 = Vec8<TW>::round(__fsub_rn(p1, __fmul_rn(A.step_size, __fmul_rn(m1, inv_denom))));
+            float p2 = __fsub_rn(p1, __fmul_rn(A.step_size, __fmul_rn(m1, inv_denom)));
             if (A.l1 > 0.0f && A.has_mask) {
                 float sgn = (p2 > 0.0f) ? 1.0f : ((p2 < 0.0f) ? -1.0f : 0.0f);
-                float term = Vec8<TW>::round(__fmul_rn(Vec8<TW>::round(__fmul_rn(A.l1, sgn)), inv_denom));
-                p2 = Vec8<TW>::round(__fsub_rn(p2, __fmul_rn(A.lr, term)));
+                p2 = __fsub_rn(p2, __fmul_rn(A.lr, __fmul_rn(__fmul_rn(A.l1, sgn), inv_denom)));
             }
             pw[i] = p2; em[i] = m1; ev[i] = v1;
         }
@@ -507,7 +507,7 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     float eff = Vec8<TW>::round(effective_mask_value(s[i], (k >> i) & 1u, P));
-                    o[4 * g2 + i] = __fmul_rn(pw[4 * g2 + i], eff);
+                    o[4 * g2 + i] = __fmul_rn(Vec8<TW>::round(pw[4 * g2 + i]), eff);  // the weight as stored
                 }
             }
             Vec8<TW>::store(wm + e, o);
