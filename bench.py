@@ -392,6 +392,60 @@ def run_reference(args):
     print(json.dumps(out), flush=True)
 
 
+def run_sparse24(args):
+    """Hard-2:4 compressed inference GEMM against the dense masked GEMM on the same pruned weight
+    (BASELINE config 3): three distinct LLaMA-2-7B weight shapes x activation rows 1 ... 8192."""
+    from sparseforge_b200 import ops
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    bf = torch.bfloat16
+    shapes = [s for s in (("q", 4096, 4096), ("gate", 11008, 4096), ("down", 4096, 11008))
+              if (not args.only or s[0] in args.only.split(","))]
+    rows_sweep = [int(r) for r in args.rows.split(",")]
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+
+    def timeit(fn, iters):
+        for _ in range(max(3, args.warmup)):
+            fn()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        return s.elapsed_time(e) / iters
+
+    cases = []
+    for i, (name, out_f, in_f) in enumerate(shapes):
+        g = torch.Generator(device=dev).manual_seed(100 + i)
+        W = (torch.randn(out_f, in_f, device=dev, generator=g) * 0.02).to(bf)
+        vals, meta = ops.sparse24_compress(W, W.float().abs())
+        meta_tc = ops.sparse24_pack_meta(meta, out_f, in_f)
+        wd = ops.sparse24_decompress(vals, meta)
+        for T in rows_sweep:
+            x = torch.randn(T, in_f, device=dev, generator=g).to(bf)
+            xd = x if T % 8 == 0 else torch.cat([x, torch.zeros(8 - T % 8, in_f, device=dev, dtype=bf)])
+            ts = timeit(lambda: ops.sparse24_gemm(x, vals, meta_tc, status=status), args.steps)
+            td = timeit(lambda: ops.gemm_fwd(xd, wd, status=status), args.steps)
+            flops = 2.0 * T * in_f * out_f
+            bytes_s = in_f * out_f + in_f * out_f / 8 + 2.0 * T * (in_f + out_f)
+            cases.append({"shape": name, "rows": T, "sparse_us": round(ts * 1e3, 1), "dense_us": round(td * 1e3, 1),
+                          "sparse_tflops": round(flops / ts / 1e9, 1), "speedup_vs_dense": round(td / ts, 3),
+                          "sparse_gbs": round(bytes_s / ts / 1e6, 1)})
+    if int(status[0].item()) != 0:
+        raise RuntimeError("a device-side wait ran out inside a GEMM; the numbers are void")
+    big = [c for c in cases if c["rows"] >= 8192]
+    print(json.dumps({"metric": "hard-2:4 compressed GEMM, dense-equivalent TFLOP/s and speed-up over the dense masked GEMM",
+                      "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+                      "config": {"workload": "llama2-7b-sparse24-inference", "timing": "CUDA events around back-to-back "
+                                 "launches from Python; rows <= 128 are bounded by host launch overhead"},
+                      "value": round(sum(c["sparse_tflops"] for c in big) / max(1, len(big)), 1),
+                      "speedup_rows_8192": round(sum(c["speedup_vs_dense"] for c in big) / max(1, len(big)), 3),
+                      "cases": cases}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -402,7 +456,12 @@ def main():
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")
+    ap.add_argument("--workload", default="tempering", choices=["tempering", "sparse24"],
+                    help="tempering = the headline layer-set step; sparse24 = compressed inference GEMM sweep")
+    ap.add_argument("--rows", default="1,16,128,1024,8192", help="activation rows of the sparse24 sweep")
     args = ap.parse_args()
+    if args.workload == "sparse24":
+        return run_sparse24(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)

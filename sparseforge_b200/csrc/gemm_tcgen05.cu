@@ -326,6 +326,23 @@ int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64
     return SF_OK;
 }
 
+// Tensor map over a byte matrix [rows, 16] (rows of 16 bytes, no swizzle) with a box of box_rows rows:
+// the tensor-core ordered 2:4 metadata, one 2048-byte tile = 128 such rows.
+int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows) {
+    SF_CHECK_CUDA(cudaFree(nullptr));
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+    cuuint64_t dims[2] = {16, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {16};
+    cuuint32_t box[2] = {16, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled (metadata) failed with CUresult %d", (int)r);
+    return SF_OK;
+}
+
 // D[M,N] = alpha * A . B^T (+bias). a_mn / b_mn: operand stored with its M / N index contiguous
 // (as [K, M] / [K, N] row-major with leading dimension lda / ldb), else as [M, K] / [N, K].
 template <int A_MN, int B_MN>

@@ -307,6 +307,219 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// CTA-pair variant for large token counts
+// ------------------------------------------------------------------------------------------
+// At 2x the MMA rate the 1-CTA kernel is bound by the L2 -> SM operand traffic (the activation
+// tile is 2/3 of each stage). Here a cluster of two CTAs computes a 256 (weight rows) x 224
+// (tokens) tile with tcgen05 .cta_group::2: each CTA loads its own 128 weight rows (values +
+// metadata) but only half of the activation rows, and the leader's MMAs read both halves. Per
+// dense-equivalent FLOP that halves the operand bytes. Barriers: each CTA has its own `empty`
+// ring (released by a multicast commit of the leader), the leader's `full` ring counts the
+// bytes of both CTAs, accumulator hand-over uses the leader's `tmem_empty` (8 epilogue warps)
+// and a multicast `tmem_full`.
+constexpr int P2_BN = 224, P2_BNH = P2_BN / 2, P2_STAGES = 4;
+constexpr int P2_B_BOX_BYTES = P2_BNH * 128;  // 112 token rows x 64 logical columns
+constexpr int P2_STAGE_BYTES = SP_A_BYTES + 2 * P2_B_BOX_BYTES + SP_META_BYTES;  // 47104
+constexpr int P2_META_COL0 = 2 * P2_BN;       // 448
+constexpr int P2_TMEM_COLS = 512;
+constexpr int P2_SMEM_BYTES = P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SP_THREADS, 1)
+sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                          const __grid_constant__ CUtensorMap tmE, __nv_bfloat16* __restrict__ Y,
+                          const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status) {
+    constexpr int STAGES = P2_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    auto* tail = reinterpret_cast<SpSmemTail<STAGES>*>(base_ptr + STAGES * P2_STAGE_BYTES);
+    volatile int* abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = ptx::cluster_ctarank();  // 0 = leader
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (out + 255) / 256, tiles_n = (T + P2_BN - 1) / P2_BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int num_kb = (in + SP_BK - 1) / SP_BK;
+    const int meta_tiles_m = (out + 127) / 128;  // 128-row metadata tiles per K tile column
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[a]), 8);  // 4 epilogue warps of each CTA
+        }
+        tail->abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&tail->tmem_base), P2_TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmE);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();  // barriers of both CTAs are initialised before anything remote happens
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
+            const int m0 = mt * 256 + (int)cta * 128;    // this CTA's weight rows
+            const int n0 = nt * P2_BN + (int)cta * P2_BNH;  // this CTA's half of the token rows
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 21);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t local_bar = ptx::smem_u32(&tail->full[stage]);
+                    const uint32_t leader_bar = ptx::map_to_cta(local_bar, 0);
+                    const uint32_t sa = base + stage * P2_STAGE_BYTES, sb = sa + SP_A_BYTES;
+                    const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * P2_STAGE_BYTES);
+                    ptx::tma_load_2d_pair(sa, &tmA, leader_bar, kb * (SP_BK / 2), m0);
+                    ptx::tma_load_2d_pair(sb, &tmB, leader_bar, kb * SP_BK, n0);
+                    ptx::tma_load_2d_pair(sb + P2_B_BOX_BYTES, &tmB, leader_bar, kb * SP_BK + 64, n0);
+                    // metadata tile (m0 / 128, kb): 128 rows of 16 bytes
+                    ptx::tma_load_2d_pair(sm, &tmE, leader_bar, 0, ((m0 >> 7) * num_kb + kb) * 128);
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+        (void)meta_tiles_m;
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (cta == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(256, P2_BN, 0, 0, 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int t = 0;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+                const int acc = t & 1;
+                const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 23);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * P2_BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 22);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = base + stage * P2_STAGE_BYTES, sb = sa + SP_A_BYTES;
+                        const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
+                        const uint32_t tmem_e = tmem_base + (uint32_t)(P2_META_COL0 + 4 * stage);
+                        ptx::tmem_cp_128x128b_pair(tmem_e, ptx::make_smem_desc(sm, 16, 128, 0));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const uint64_t adesc = ptx::make_smem_desc(sa + k * 32, 16, 1024, 2);
+                            const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * P2_B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
+                            ptx::mma_f16_ss_sp_pair(tmem_d, adesc, bdesc, tmem_e + (uint32_t)(k & ~1), idesc | (uint32_t)(k & 1),
+                                                    (kb | k) != 0 ? 1u : 0u);
+                        }
+                        ptx::mma_commit_pair(ptx::smem_u32(&tail->empty[stage]), (uint16_t)3);
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if (lane == 0) ptx::mma_commit_pair(ptx::smem_u32(&tail->tmem_full[acc]), (uint16_t)3);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): 128 weight rows x 224 tokens each ----------------
+        const int q = warp & 3;
+        const uint32_t leader_empty0 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[0]), 0);
+        const uint32_t leader_empty1 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[1]), 0);
+        bool ok = true;
+        int t = 0;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 24);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int o = mt * 256 + (int)cta * 128 + q * 32 + lane;
+            const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
+            const uint32_t taddr = tmem_base + (uint32_t)(acc * P2_BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < P2_BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                ptx::tmem_ld_wait();
+                if (o < out) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = nt * P2_BN + c * 32 + j;
+                        if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+        }
+    }
+
+    // ---------------- teardown: nobody leaves while the peer may still touch this CTA ----------------
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, P2_TMEM_COLS);
+    }
+}
+
+int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows);
+
+static int launch_sparse_pair(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
+                              int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st) {
+    CUtensorMap tmA, tmB, tmE;
+    int rc = make_bf16_tensor_map(&tmA, values, in / 2, out, in / 2, SP_BM);
+    if (rc) return rc;
+    rc = make_bf16_tensor_map(&tmB, x, in, T, in, P2_BNH);
+    if (rc) return rc;
+    const int64_t meta_rows = sf_sparse24_meta_tc_bytes(out, in) / 16;
+    rc = make_meta_tensor_map(&tmE, meta_tc, meta_rows, 128);
+    if (rc) return rc;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES));
+        configured_dev = dev;
+    }
+    const int64_t tiles = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
+    const int64_t max_pairs = sm_count() / 2;
+    const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+    sparse24_gemm_pair_kernel<<<2 * pairs, SP_THREADS, P2_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
+                                                                            (const __nv_bfloat16*)bias, (int)out, (int)T,
+                                                                            (int)in, status);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
 template <int BN>
 static int launch_sparse(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
                          int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st) {
@@ -394,7 +607,8 @@ int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, 
     if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st);
     if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st);
     if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st);
-    return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    if (T <= 128) return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    return launch_sparse_pair(x, values, meta_tc, bias, y, T, in, out, status, st);
 }
 
 }  // extern "C"
