@@ -18,6 +18,7 @@
 // through the common teardown (TMEM is always released).
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -47,6 +48,31 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     const int r = tile - g * per_group;
     tm = first_m + r % gm;
     tn = r / gm;
+}
+
+// 32 consecutive fp32 accumulators of one output row -> bf16, scaled, biased, stored as four
+// 16-byte vectors (columns beyond N are dropped; N is a multiple of 8).
+__device__ __forceinline__ void store_row_chunk(const uint32_t (&r)[32], __nv_bfloat16* dst, int col0, int N, float alpha,
+                                                const __nv_bfloat16* __restrict__ bias) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const int col = col0 + j * 8;
+        if (col < N) {
+            uint32_t pk[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v0 = __uint_as_float(r[j * 8 + 2 * i]) * alpha;
+                float v1 = __uint_as_float(r[j * 8 + 2 * i + 1]) * alpha;
+                if (bias != nullptr) {
+                    v0 += __bfloat162float(bias[col + 2 * i]);
+                    v1 += __bfloat162float(bias[col + 2 * i + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                pk[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+            *reinterpret_cast<uint4*>(dst + j * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+    }
 }
 
 struct GemmSmemTail {
@@ -199,27 +225,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
                 ptx::tmem_ld_wait();
-                if (row < M) {
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const int col = n0 + c * 32 + j * 8;
-                        if (col < N) {
-                            uint32_t pk[4];
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) {
-                                float v0 = __uint_as_float(r[j * 8 + 2 * i]) * alpha;
-                                float v1 = __uint_as_float(r[j * 8 + 2 * i + 1]) * alpha;
-                                if (bias != nullptr) {
-                                    v0 += __bfloat162float(bias[col + 2 * i]);
-                                    v1 += __bfloat162float(bias[col + 2 * i + 1]);
-                                }
-                                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
-                                pk[i] = *reinterpret_cast<uint32_t*>(&h);
-                            }
-                            *reinterpret_cast<uint4*>(drow + c * 32 + j * 8) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
-                        }
-                    }
-                }
+                if (row < M) store_row_chunk(r, drow + c * 32, n0 + c * 32, N, alpha, bias);
             }
             ptx::tc_fence_before();
             __syncwarp();
@@ -233,6 +239,189 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (warp == 1) {
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 .cta_group::2): a cluster of two CTAs computes a 256 x 256 tile.
+// Each CTA loads its own 128 rows of A but only 128 of the 256 rows of B; the leader's MMAs
+// read both halves. A stage shrinks from 48 KiB to 32 KiB for the same FLOPs, so the ring
+// holds 6 stages and the L2 -> SM operand traffic per FLOP drops by a third. Barrier protocol:
+// `full` lives in the leader and counts the bytes of both CTAs, `empty` and `tmem_full` are
+// released in both CTAs by multicast commits, `tmem_empty` of the leader collects the eight
+// epilogue warps of the pair.
+// ---------------------------------------------------------------------------------------
+constexpr int PAIR_STAGES = 6;
+constexpr int PAIR_BNH = BN / 2;                       // B rows loaded by each CTA
+constexpr int PAIR_B_BYTES = PAIR_BNH * BK * 2;        // 16 KiB
+constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
+constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
+
+struct PairSmemTail {
+    uint64_t full[PAIR_STAGES];
+    uint64_t empty[PAIR_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    int abort_flag;
+};
+
+template <int A_MN, int B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
+                      float alpha, int M, int N, int K, int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    PairSmemTail* tail = reinterpret_cast<PairSmemTail*>(base_ptr + PAIR_STAGES * PAIR_STAGE_BYTES);
+    volatile int* abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = ptx::cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int num_kb = (K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[a]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[a]), 8);
+        }
+        tail->abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&tail->tmem_base), TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * 2 * BM + (int)cta * BM;       // this CTA's rows of A / D
+            const int n0 = tn * BN + (int)cta * PAIR_BNH;     // this CTA's half of the B rows
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 31);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t local_bar = ptx::smem_u32(&tail->full[stage]);
+                    const uint32_t bar = ptx::map_to_cta(local_bar, 0);
+                    const uint32_t sa = base + stage * PAIR_STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+                    const int k0 = kb * BK;
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * PAIR_STAGE_BYTES);
+                    if (A_MN) {
+#pragma unroll
+                        for (int j = 0; j < BM / 64; ++j) ptx::tma_load_2d_pair(sa + j * MN_BOX_BYTES, &tmA, bar, m0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d_pair(sa, &tmA, bar, k0, m0);
+                    }
+                    if (B_MN) {
+#pragma unroll
+                        for (int j = 0; j < PAIR_BNH / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
+                    } else {
+                        ptx::tma_load_2d_pair(sb, &tmB, bar, k0, n0);
+                    }
+                }
+                __syncwarp();
+                if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    } else if (warp == 1) {
+        if (cta == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int t = 0;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+                const int acc = t & 1;
+                const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 33);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 32);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = base + stage * PAIR_STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint64_t adesc = A_MN ? ptx::make_smem_desc(sa + k * (UMMA_K * 128), MN_BOX_BYTES, 1024, 2)
+                                                        : ptx::make_smem_desc(sa + k * (UMMA_K * 2), 16, 1024, 2);
+                            const uint64_t bdesc = B_MN ? ptx::make_smem_desc(sb + k * (UMMA_K * 128), MN_BOX_BYTES, 1024, 2)
+                                                        : ptx::make_smem_desc(sb + k * (UMMA_K * 2), 16, 1024, 2);
+                            ptx::mma_f16_ss_pair(tmem_d, adesc, bdesc, idesc, (kb | k) != 0 ? 1u : 0u);
+                        }
+                        ptx::mma_commit_pair(ptx::smem_u32(&tail->empty[stage]), (uint16_t)3);
+                    }
+                    __syncwarp();
+                    if (++stage == PAIR_STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if (lane == 0) ptx::mma_commit_pair(ptx::smem_u32(&tail->tmem_full[acc]), (uint16_t)3);
+                __syncwarp();
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const uint32_t leader_empty0 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[0]), 0);
+        const uint32_t leader_empty1 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[1]), 0);
+        bool ok = true;
+        int t = 0;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+            int tm, tn;
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN;
+            const int acc = t & 1;
+            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 34);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int row = m0 + q * 32 + lane;
+            __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
+            const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                ptx::tmem_ld_wait();
+                if (row < M) store_row_chunk(r, drow + c * 32, n0 + c * 32, N, alpha, bias);
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
     }
 }
 
@@ -345,6 +534,16 @@ int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int bo
 
 // D[M,N] = alpha * A . B^T (+bias). a_mn / b_mn: operand stored with its M / N index contiguous
 // (as [K, M] / [K, N] row-major with leading dimension lda / ldb), else as [M, K] / [N, K].
+// The CTA-pair kernel serves every problem with more than one 128-row tile; setting
+// SF_GEMM_SINGLE_CTA=1 in the environment keeps the 1-CTA kernel (for A/B measurements).
+static bool use_pair_kernel() {
+    static const bool v = [] {
+        const char* e = getenv("SF_GEMM_SINGLE_CTA");
+        return !(e && e[0] == '1');
+    }();
+    return v;
+}
+
 template <int A_MN, int B_MN>
 static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldD,
                        const void* bias, float alpha, int64_t M, int64_t N, int64_t K, int32_t* status,
@@ -354,13 +553,29 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (A_MN) rc = make_bf16_tensor_map(&tmA, A, M, K, lda, 64);
     else rc = make_bf16_tensor_map(&tmA, A, K, M, lda, BM);
     if (rc) return rc;
+    const bool pair = M > BM && use_pair_kernel();
     if (B_MN) rc = make_bf16_tensor_map(&tmB, B, N, K, ldb, 64);
-    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, BN);
+    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_BNH : BN);
     if (rc) return rc;
-    auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
-    static thread_local int configured_dev = -1;
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (M > BM && use_pair_kernel()) {
+        auto pk = gemm_bf16_pair_kernel<A_MN, B_MN>;
+        static thread_local int pair_dev = -1;
+        if (pair_dev != dev) {
+            SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
+            pair_dev = dev;
+        }
+        const int64_t ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+        const int64_t max_pairs = sm_count() / 2;
+        const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
+        pk<<<2 * pairs, GEMM_THREADS, PAIR_SMEM_BYTES, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD, (const __nv_bfloat16*)bias,
+                                                             alpha, (int)M, (int)N, (int)K, status);
+        SF_CHECK_CUDA(cudaGetLastError());
+        return SF_OK;
+    }
+    auto kern = gemm_bf16_tcgen05_kernel<A_MN, B_MN>;
+    static thread_local int configured_dev = -1;
     if (configured_dev != dev) {
         SF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, GEMM_SMEM_BYTES));
         configured_dev = dev;

@@ -608,6 +608,14 @@ int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, 
     if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st);
     if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st);
     if (T <= 128) return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    // Pick the tiling that wastes fewer tile slots in its last wave; a CTA-pair tile does the same
+    // work with about 1.3x less operand traffic, so it wins unless its wave fill is much worse.
+    const int64_t sms = sm_count();
+    const int64_t t1 = ((out + SP_BM - 1) / SP_BM) * ((T + 127) / 128), s1 = sms;
+    const int64_t t2 = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN), s2 = sms / 2;
+    const double fill1 = (double)t1 / (double)(((t1 + s1 - 1) / s1) * s1);
+    const double fill2 = (double)t2 / (double)(((t2 + s2 - 1) / s2) * s2);
+    if (fill1 > 1.3 * fill2) return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
     return launch_sparse_pair(x, values, meta_tc, bias, y, T, in, out, status, st);
 }
 
