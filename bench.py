@@ -327,7 +327,7 @@ def run_ours(args):
             out["passes"][k.replace("_gbs", "_frac")] = round(out["passes"][k] / peaks["hbm_gbs"], 4)
             out["passes"][k] = round(out["passes"][k], 1)
     if world == 1 and not args.no_cpu_baseline:
-        out["cpu_baseline"] = cpu_port_sample(sample_tokens=1024)
+        out["cpu_baseline"] = cpu_port_sample(repeats=3)
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -353,9 +353,10 @@ def cpu_port_step(W, mask, H, m, v, X, dY, hvp, probe, it):
     return W, new_mask, H, m, v
 
 
-def cpu_port_sample(sample_tokens=1024, rows=4096, cols=4096, repeats=2):
-    """Times the oracle on one q-shaped matrix with `sample_tokens` of the 8192 tokens; the
-    throughput is in the bench's unit (fwd+bwd GEMM FLOPs over the whole step time)."""
+def cpu_port_sample(sample_tokens=T_TOKENS, rows=4096, cols=4096, repeats=2):
+    """Times the oracle on one complete q-shaped matrix with all 8192 tokens (the ratio of GEMM
+    work to per-weight work is that of the full workload); the throughput is in the bench's unit
+    (fwd+bwd GEMM FLOPs over the whole step time)."""
     torch.manual_seed(100)
     bf = torch.bfloat16
     W = (torch.randn(rows, cols) * 0.02).to(bf)
@@ -373,7 +374,8 @@ def cpu_port_sample(sample_tokens=1024, rows=4096, cols=4096, repeats=2):
             best = dt if best is None else min(best, dt)
     return {"value": round(layer_flops(sample_tokens, rows, cols) / best / 1e12, 4), "unit": UNIT,
             "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"one [4096,4096] matrix, {sample_tokens} of 8192 tokens, full tempering step, best of {repeats}",
+            "sample": f"one [{rows},{cols}] matrix of the seven, all {sample_tokens} tokens, full tempering step, "
+                      f"best of {repeats}",
             "seconds_per_sample_step": round(best, 3)}
 
 
@@ -382,11 +384,13 @@ def run_reference(args):
     torch and is not present on the GPU box; its arithmetic is restated op for op in oracle/)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    res = cpu_port_sample(sample_tokens=512, repeats=max(1, min(args.steps, 3)))
+    res = cpu_port_sample(repeats=max(1, min(args.steps, 5)))
     out = {"impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
            "steps": args.steps, "warmup": args.warmup, "ms_per_step": res["seconds_per_sample_step"] * 1e3,
            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-           "config": {"workload": "llama2-7b-layerset-tempering", "sample": res["sample"]},
+           "config": {"workload": "llama2-7b-layerset-tempering",
+                      "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]", "tokens": T_TOKENS,
+                      "row_sharded_over": 1, "sample": res["sample"]},
            "cpu_baseline": res, "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0,
                                         "d2h_bytes_per_step": 0}}
     print(json.dumps(out), flush=True)
