@@ -154,3 +154,22 @@ def test_sparse24_compress_round_trip():
     dense = torch.zeros(16, 16, 4)
     dense.scatter_(-1, idx, vals.view(16, 16, 2))
     assert torch.equal(dense.view(16, 64), W * hard)
+
+
+def test_c_oracle_matches_reference_fixtures_and_python_oracle():
+    """The C restatement of the projection (oracle/nm24_oracle.c) against the reference's outputs."""
+    from oracle import nm24_c
+
+    g = Golden("ties")
+    for name in list(g["names"]) + ["tail"]:
+        soft, want = g[f"{name}_soft"], g[f"{name}_hard"]
+        hard, meta = nm24_c.project(soft.numpy())
+        assert np.array_equal(hard, want.numpy()), name
+        assert np.array_equal(meta, O.meta_from_hard(want).numpy()), name
+    x = np.array([[np.nan, 1.0, 2.0, 3.0, 1.0, np.nan, np.nan, 0.0]], dtype=np.float32)
+    assert np.array_equal(nm24_c.project(x)[0], O.hard_mask_from_soft(torch.from_numpy(x)).numpy())
+    torch.manual_seed(3)
+    big = torch.rand(256, 1024)
+    hard, meta = nm24_c.project(big.numpy())
+    assert np.array_equal(hard, O.hard_mask_from_soft(big).numpy())
+    assert np.array_equal(meta, O.meta_from_hard(O.hard_mask_from_soft(big)).numpy())
