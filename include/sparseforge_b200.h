@@ -142,7 +142,10 @@ enum {
  *             FusedMaskedLinearSTE.forward :74-81; _hard_mask_from_soft :720-735.
  *   s  = (score - norm[0]) / norm[1]   (rounded to bf16 first when score_bf16 != 0)
  *   G  = sigmoid((s - tau_g)/(T + 1e-8)), tau_g = 2nd largest s of the group of 4
- *        (or the exact 0/1 top-2 indicator when structured_exact != 0)
+ *        (or the exact 0/1 top-2 indicator when structured_exact != 0);
+ *        with tau != NULL (device scalar, normalised-score units) the gate is the unstructured
+ *        one of :1099-1162, G = sigmoid((s - *tau)/(T + 1e-8)), tau being the sampled quantile
+ *        of _tau_unstructured :987-1015; everything after the gate is unchanged
  *   G  = (1-beta_s) G + beta_s top2(s)                      if beta_s > 0
  *   G  = clamp(G - pen*(mask - top2(G)), 0, 1)              SF_PENALTY_TOPN, pen != 0
  *   G  = clamp(G - pen*(1 - 2 mask), 0, 1)                  SF_PENALTY_MID,  pen != 0
@@ -155,8 +158,8 @@ enum {
  * nibble = group 2j+1; nibble = i0 | (i1 << 2) with i0 < i1 the kept column offsets.
  * stats: SF_MSTAT_COUNT doubles, overwritten. cols % 8 == 0.
  */
-SF_API int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W,
-                        int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows,
+SF_API int sf_mask_update_nm24(const float* score, const float* norm, const float* tau, float* mask,
+                        const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows,
                         int64_t cols, double temperature, double mask_lr, double pen,
                         int penalty_mode, double beta_s, double binarize_decay, double hx,
                         int structured_exact, int score_bf16, void* stream);

@@ -146,6 +146,27 @@ def gate_target_structured(scores_norm, temperature, *, exact=False, beta_s=0.0,
     return G
 
 
+def tau_unstructured(scores_norm, sparsity, tau_sample_size=262144, sample_idx=None):
+    """legacy/sparse_modeling.py:987-1015 (single process): quantile of a random sample of the
+    normalised scores. The sample positions are an input here (the reference draws them with
+    torch.randint on the tensor's device)."""
+    flat = scores_norm.flatten()
+    n = flat.numel()
+    m = int(tau_sample_size) if tau_sample_size is not None else n
+    sample = flat[sample_idx] if (m > 0 and n > m) else flat
+    return torch.quantile(sample.float(), q=float(sparsity))
+
+
+def gate_target_unstructured(scores_norm, tau, temperature, *, beta_s=0.0, n=2, m=4):
+    """legacy/sparse_modeling.py:1099-1162 (non block-sparse branch, :1162) + beta mixing :1199-1225."""
+    Tt = torch.tensor(float(temperature), dtype=torch.float32)
+    G = torch.sigmoid((scores_norm.float() - tau) / (Tt + 1e-8)).to(scores_norm.dtype)
+    if beta_s > 0.0:
+        target = topn_indicator(scores_norm, n, m, dtype=G.dtype)
+        G = ((1.0 - beta_s) * G.float() + beta_s * target.float()).to(G.dtype)
+    return G
+
+
 def mask_update(mask, G, *, mask_lr, lambda_mid=0.0, pen_lr=None, penalty_mode="mid", binarize_decay=0.0,
                 n=2, m=4):
     """legacy/sparse_modeling.py:1288-1593 for the structured / nm_2_4 / mid penalty modes.

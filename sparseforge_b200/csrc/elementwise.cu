@@ -226,6 +226,7 @@ struct MaskUpdateParams {
     int soft_only;  // hx >= 1 - 1e-6: effective mask = soft mask
     int structured_exact;
     int score_bf16;
+    const float* tau;  // unstructured gate: threshold in normalised-score units (device); null = 2:4 gate
 };
 
 __device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
@@ -267,6 +268,8 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
     // normalised score has to be rounded to bf16 first.
     const float mu = norm[0];
     const float inv_sigma = __fdiv_rn(1.0f, norm[1]);
+    const bool unstructured = P.tau != nullptr;
+    const float tau_global = unstructured ? *P.tau : 0.0f;
     GroupStats gs;
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
          c += (int64_t)gridDim.x * kThreads) {
@@ -287,11 +290,11 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
             }
             int r[4];
             rank4_fast(s, r);
-            const float tau = r[0] == 1 ? s[0] : (r[1] == 1 ? s[1] : (r[2] == 1 ? s[2] : s[3]));
+            const float tau = unstructured ? tau_global : (r[0] == 1 ? s[0] : (r[1] == 1 ? s[1] : (r[2] == 1 ? s[2] : s[3])));
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float gi;
-                if (P.structured_exact) gi = r[i] < 2 ? 1.0f : 0.0f;
+                if (P.structured_exact && !unstructured) gi = r[i] < 2 ? 1.0f : 0.0f;
                 else {
                     // sigmoid(z) = 1 / (1 + 2^(-z log2 e)), z = (s_i - tau) / (T + 1e-8)
                     gi = fast_rcp(1.0f + fast_ex2(__fmul_rn(__fsub_rn(s[i], tau), P.neg_log2e_over_t)));
@@ -651,11 +654,12 @@ static MaskUpdateParams make_mask_params(double temperature, double mask_lr, dou
     P.soft_only = hx >= 1.0 - 1e-6;
     P.structured_exact = structured_exact;
     P.score_bf16 = score_bf16;
+    P.tau = nullptr;
     return P;
 }
 
-int sf_mask_update_nm24(const float* score, const float* norm, float* mask, const void* W, int w_dtype,
-                        void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
+int sf_mask_update_nm24(const float* score, const float* norm, const float* tau, float* mask, const void* W,
+                        int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
                         double temperature, double mask_lr, double pen, int penalty_mode, double beta_s,
                         double binarize_decay, double hx, int structured_exact, int score_bf16,
                         void* stream) {
@@ -673,6 +677,7 @@ int sf_mask_update_nm24(const float* score, const float* norm, float* mask, cons
     cudaStream_t st = (cudaStream_t)stream;
     MaskUpdateParams P = make_mask_params(temperature, mask_lr, pen, penalty_mode, beta_s, binarize_decay,
                                           hx, structured_exact, score_bf16);
+    P.tau = tau;
     const int64_t chunks = rows * cols / 8;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
 #define SF_MU(TW, EW, EM)                                                                        \

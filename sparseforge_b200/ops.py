@@ -59,10 +59,12 @@ def hutch_score(W, H, score, norm, scratch, *, hvp=None, v=None, aux=None, aux_s
                                _lib.METRICS[metric], _stream()), "sf_hutch_score")
 
 
-def mask_update_nm24(score, norm, mask, stats, *, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
+def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
                      pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
                      structured_exact=False, score_bf16=False) -> None:
-    _cuda(score, norm, mask, stats, W, wm, meta)
+    _cuda(score, norm, mask, stats, W, wm, meta, tau)
+    if tau is not None and tau.dtype != torch.float32:
+        raise TypeError("mask_update_nm24: tau must be a float32 device scalar")
     if mask.dim() != 2:
         raise ValueError("mask_update_nm24: mask must be 2-D [out, in]")
     if mask.dtype != torch.float32 or score.dtype != torch.float32 or stats.dtype != torch.float64:
@@ -70,7 +72,7 @@ def mask_update_nm24(score, norm, mask, stats, *, W=None, wm=None, meta=None, te
     if wm is not None and (W is None or wm.dtype != W.dtype):
         raise TypeError("mask_update_nm24: wm needs W of the same dtype")
     rows, cols = mask.shape
-    check(lib().sf_mask_update_nm24(_p(score), _p(norm), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
+    check(lib().sf_mask_update_nm24(_p(score), _p(norm), _p(tau), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
                                     _p(wm), _p(meta), _p(stats), rows, cols, float(temperature), float(mask_lr),
                                     float(pen), int(penalty_mode), float(beta_s), float(binarize_decay), float(hx),
                                     int(bool(structured_exact)), int(bool(score_bf16)), _stream()),

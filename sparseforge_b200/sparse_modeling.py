@@ -589,22 +589,65 @@ class SparseLinear(nn.Linear):
 
     @torch.no_grad()
     def compute_gate_target(self, step: int) -> torch.Tensor:
-        """Soft gate G of legacy/sparse_modeling.py:1018-1239 (structured branch), as a tensor.
-        Runs the fused update kernel on a copy of the mask with mask_lr = 1 and no penalty, which
-        leaves exactly G in the copy."""
+        """Soft gate G of legacy/sparse_modeling.py:1018-1239 (structured and unstructured branches),
+        as a tensor. Runs the fused update kernel on a copy of the mask with mask_lr = 1 and no
+        penalty, which leaves exactly G in the copy."""
         if (not self.change_mask) or (self.mask_type == "none"):
             return torch.ones_like(self.mask)
-        if self.mask_type != "structured":
-            raise NotImplementedError("only mask_type='structured' is implemented on this path")
+        self._check_mask_modes()
         self._check_2to4()
         self._refresh_score()
         G = torch.zeros_like(self.mask.data)
         stats = torch.zeros(_lib.MSTAT_COUNT, dtype=torch.float64, device=G.device)
-        ops.mask_update_nm24(self._score, self._norm, G, stats, temperature=self._temperature(step), mask_lr=1.0,
+        ops.mask_update_nm24(self._score, self._norm, G, stats, tau=self._gate_tau(step),
+                             temperature=self._temperature(step), mask_lr=1.0,
                              beta_s=self._beta_structural(step),
                              structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
                              score_bf16=self._score_is_bf16())
         return G
+
+    def _check_mask_modes(self):
+        """Gate / projection combinations the 2:4 kernels cover."""
+        if self.mask_type not in ("structured", "unstructured"):
+            raise ValueError(f"Invalid mask_type: {self.mask_type}")
+        if self._resolved_hard_type() not in ("structured", "nm_2_4"):
+            raise NotImplementedError(
+                f"hard mask type {self._resolved_hard_type()!r} with mask_type={self.mask_type!r} is outside the 2:4 "
+                "kernel path (use hard_mask_type='nm_2_4' or mask_type='structured')")
+
+    @torch.no_grad()
+    def _tau_unstructured(self, scores: torch.Tensor, sparsity: float, sample_idx: Optional[torch.Tensor] = None):
+        """Quantile threshold of legacy/sparse_modeling.py:987-1015 on a random sample of the scores,
+        averaged over data-parallel replicas (not over the row shards of one layer: each shard samples
+        its own rows, as each FSDP rank does in the reference)."""
+        flat = scores.flatten()
+        n = flat.numel()
+        m = int(self.cfg.tau_sample_size) if self.cfg.tau_sample_size is not None else n
+        if m > 0 and n > m:
+            idx = sample_idx if sample_idx is not None else torch.randint(0, n, (m,), device=flat.device)
+            sample = flat[idx]
+        else:
+            sample = flat
+        tau = torch.quantile(sample.float(), q=float(sparsity))
+        if getattr(self, "_in_summon_context", False):
+            return tau
+        import torch.distributed as dist
+
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+            t = tau.clone()
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+            tau = t / dist.get_world_size()
+        return tau
+
+    def _gate_tau(self, step: int):
+        """Device scalar with the unstructured gate's threshold in normalised-score units, or None for
+        the structured gate. The quantile of the raw score sample is mapped through the same affine
+        normalisation as the scores (a quantile commutes with it)."""
+        if self.mask_type != "unstructured":
+            return None
+        tau_raw = self._tau_unstructured(self._score, self._effective_sparsity(step),
+                                         getattr(self, "_tau_sample_idx", None))
+        return ((tau_raw - self._norm[0]) / self._norm[1]).to(torch.float32).reshape(1).contiguous()
 
     # -- periodic mask update ---------------------------------------------------------------
     @torch.no_grad()
@@ -624,8 +667,7 @@ class SparseLinear(nn.Linear):
             return
         if step % max(1, int(self._mask_update_period(step))) != 0:
             return
-        if self.mask_type != "structured":
-            raise NotImplementedError("only mask_type='structured' is implemented on this path")
+        self._check_mask_modes()
         self._check_2to4()
         if not score_ready:
             self._refresh_score()
@@ -635,7 +677,8 @@ class SparseLinear(nn.Linear):
             raise NotImplementedError(f"mask_penalty_mode={mode!r} is outside the 2:4 kernel path")
         pmode = _lib.PENALTY_MID if mode == "mid" else _lib.PENALTY_TOPN
         hx_new = self._next_hardening_x(step)
-        ops.mask_update_nm24(self._score, self._norm, self.mask.data, self._stats, W=self.weight.data, wm=self._wm,
+        ops.mask_update_nm24(self._score, self._norm, self.mask.data, self._stats, tau=self._gate_tau(step),
+                             W=self.weight.data, wm=self._wm,
                              meta=self._meta, temperature=self._temperature(step), mask_lr=float(self.cfg.mask_lr),
                              pen=float(self.mask_penalty_lr) * lam, penalty_mode=pmode if lam != 0.0 else 0,
                              beta_s=self._beta_structural(step),

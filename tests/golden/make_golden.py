@@ -98,7 +98,10 @@ def hutchinson_once(layer, X, dY, v, d, tag):
     put(d, f"H_{tag}", layer.hessian_diag.data)
 
 
-def case_chain(name, out_f, in_f, batch, seq, dtype, steps, cfg_kw, lambda_mid=0.0, seed=0):
+_orig_randint = torch.randint
+
+
+def case_chain(name, out_f, in_f, batch, seq, dtype, steps, cfg_kw, lambda_mid=0.0, seed=0, tau_idx_seed=None):
     """Score -> mask update -> projection -> masked fwd/bwd -> AdamW, `steps` times."""
     torch.manual_seed(seed)
     W = torch.randn(out_f, in_f) * 0.02
@@ -134,11 +137,21 @@ def case_chain(name, out_f, in_f, batch, seq, dtype, steps, cfg_kw, lambda_mid=0
         put(d, f"s{t}_W_opt", layer.weight.data); put(d, f"s{t}_m", st["exp_avg"]); put(d, f"s{t}_v", st["exp_avg_sq"])
         # mask update
         put(d, f"s{t}_T", layer._temperature(t))
+        if tau_idx_seed is not None:
+            # the unstructured gate samples score positions with torch.randint: inject recorded ones
+            gi = torch.Generator().manual_seed(tau_idx_seed + t)
+            idx = _orig_randint(0, out_f * in_f, (int(layer.cfg.tau_sample_size),), generator=gi)
+            put(d, f"s{t}_tau_idx", idx)
+            torch.randint = lambda *a, **k: idx.clone()
         G = layer.compute_gate_target(t)
         put(d, f"s{t}_G", G)
-        raw = (layer.hessian_diag.data + 1e-8) * (layer.weight.data * layer.weight.data)
+        if layer.mask_metric == "hessian_ratio":
+            raw = layer.weight.data.abs() / torch.sqrt(layer.hessian_diag.data + 1e-8)
+        else:
+            raw = (layer.hessian_diag.data + 1e-8) * (layer.weight.data * layer.weight.data)
         put(d, f"s{t}_score_raw", raw)
         ref_utils.calculate_model_mask(layer, step=t, lambda_mid=lambda_mid)
+        torch.randint = _orig_randint
         put(d, f"s{t}_mask", layer.mask.data)
         put(d, f"s{t}_hx", float(layer.hardening_x))
         put(d, f"s{t}_flips", int(layer.weight.flipped_mask))
@@ -260,6 +273,14 @@ if __name__ == "__main__":
     case_chain("chain_bf16", 64, 128, 2, 32, torch.bfloat16, 4,
                dict(base, temp_init=1.0, temp_min=0.05, temp_decay=0.05 ** (1.0 / 9.0), mask_hardening_start=1,
                     mask_hardening_duration=3, mask_penalty_mode="structured_topn"), lambda_mid=0.25, seed=100)
+    # the launcher's default recipe (train_llama.sh:223-262): unstructured gate from a sampled quantile,
+    # nm_2_4 projection and penalty, |W| / sqrt(H) score
+    case_chain("chain_paper", 64, 128, 2, 32, torch.bfloat16, 3,
+               dict(mask_type="unstructured", hard_mask_type="nm_2_4", mask_metric="hessian_ratio", N=2, M=4,
+                    mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.1, beta=0.98, temp_init=1.0, temp_min=0.05,
+                    temp_decay=0.5, mask_hardening_start=1, mask_hardening_duration=2, mask_penalty_lr=0.1,
+                    mask_penalty_mode="nm_2_4", tau_sample_size=1024, sparsity_ratio=0.5),
+               lambda_mid=0.1, seed=200, tau_idx_seed=900)
     case_penalty()
     case_ties()
     case_adamw()

@@ -212,3 +212,49 @@ def test_gemm_from_a_fresh_thread(ops):
     t.join()
     assert "err" not in out, out.get("err")
     assert rel_err(out["y"], x.float() @ w.float()) <= BF16_TOL
+
+
+def test_paper_recipe_mask_path():
+    """The launcher's default recipe (unstructured gate from a sampled quantile, nm_2_4 projection and
+    penalty, |W|/sqrt(H) score) against the reference run: every stage is fed the reference's inputs."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("chain_paper")
+    W0 = g["W0"]
+    out_f, in_f = W0.shape
+    cfg = sf.SparseLinearConfig(mask_type="unstructured", hard_mask_type="nm_2_4", mask_metric="hessian_ratio", N=2, M=4,
+                                mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.1, beta=0.98, temp_init=1.0,
+                                temp_min=0.05, temp_decay=0.5, mask_hardening_start=1, mask_hardening_duration=2,
+                                mask_penalty_lr=0.1, mask_penalty_mode="nm_2_4", tau_sample_size=1024, sparsity_ratio=0.5)
+    layer = sf.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False).to(DEV).to(torch.bfloat16)
+    layer.initialize()
+    lam = g.scalar("lambda_mid")
+    X, dY = g["X"].to(DEV), g["dY"].to(DEV)
+    for t in range(g.scalar("n_steps")):
+        # forward / backward with the reference's weight, mask and hardening state
+        layer.weight.data.copy_(g[f"s{t}_W_fwd"].to(DEV))
+        layer.mask.data.copy_(g[f"s{t}_mask_fwd"].to(DEV))
+        layer.hardening_x = g.scalar(f"s{t}_hx_fwd")
+        layer.invalidate_masked_weight()
+        Xr = X.clone().requires_grad_(True)
+        layer.weight.grad = None
+        Y = layer(Xr)
+        Y.backward(dY)
+        assert rel_err(Y.float(), g[f"s{t}_Y"].float()) <= BF16_TOL
+        assert rel_err(Xr.grad.float(), g[f"s{t}_dX"].float()) <= BF16_TOL
+        assert rel_err(layer.weight.grad.float(), g[f"s{t}_dW"].float()) <= BF16_TOL
+        # mask update from the reference's post-optimizer weight and Hessian
+        layer.weight.data.copy_(g[f"s{t}_W_opt"].to(DEV))
+        layer.hessian_diag.data.copy_(g[f"H_{g.scalar(f's{t}_probes_end') - 1}"].to(DEV))
+        layer._tau_sample_idx = g[f"s{t}_tau_idx"].to(DEV)
+        assert layer._temperature(t) == pytest.approx(g.scalar(f"s{t}_T"), rel=1e-12)
+        G = layer.compute_gate_target(t)
+        assert rel_err(G, g[f"s{t}_G"]) <= F32_TOL
+        prev = layer.mask.data.clone()
+        U.calculate_model_mask(layer, step=t, lambda_mid=lam)
+        assert rel_err(layer.mask.data, g[f"s{t}_mask"]) <= F32_TOL
+        assert layer.hardening_x == pytest.approx(g.scalar(f"s{t}_hx"))
+        assert int(layer.weight.flipped_mask) == O.flip_count(prev.cpu(), layer.mask.data.cpu(), "nm_2_4")
+        layer.mask.data.copy_(g[f"s{t}_mask"].to(DEV))
+        assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"s{t}_hard"])

@@ -94,6 +94,30 @@ def test_chain_stages(case, tol):
         assert math.isclose(O.mask_stats(mask)["sum_m1m"], g.scalar(f"s{t}_mid_sum"), rel_tol=1e-9, abs_tol=1e-9)
 
 
+def test_chain_paper_recipe():
+    """Unstructured gate from a sampled quantile + nm_2_4 penalty and projection + |W|/sqrt(H) score."""
+    g = Golden("chain_paper")
+    lam = g.scalar("lambda_mid")
+    mask = torch.ones(g["W0"].shape)
+    for t in range(g.scalar("n_steps")):
+        assert torch.equal(mask, g[f"s{t}_mask_fwd"])
+        hx = g.scalar(f"s{t}_hx_fwd")
+        eff = O.effective_mask(mask, hx, mode="nm_2_4")
+        assert rel_err(O.linear_forward(g["X"], g[f"s{t}_W_fwd"], eff), g[f"s{t}_Y"]) <= BF16_TOL
+        W, H = g[f"s{t}_W_opt"], g[f"H_{g.scalar(f's{t}_probes_end') - 1}"]
+        raw = O.importance_score(W, "hessian_ratio", H=H)
+        assert rel_err(raw, g[f"s{t}_score_raw"]) <= F32_TOL
+        s = O.normalize_scores(raw)
+        tau = O.tau_unstructured(s, 0.5, 1024, g[f"s{t}_tau_idx"])
+        G = O.gate_target_unstructured(s, tau, g.scalar(f"s{t}_T"))
+        assert rel_err(G, g[f"s{t}_G"]) <= F32_TOL
+        new_mask = O.mask_update(mask, g[f"s{t}_G"], mask_lr=0.1, lambda_mid=lam, pen_lr=0.1, penalty_mode="nm_2_4")
+        assert rel_err(new_mask, g[f"s{t}_mask"]) <= F32_TOL
+        assert O.flip_count(mask, g[f"s{t}_mask"], "nm_2_4") == g.scalar(f"s{t}_flips")
+        mask = g[f"s{t}_mask"].clone()
+        assert torch.equal(O.hard_mask_from_soft(mask, "nm_2_4"), g[f"s{t}_hard"])
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
