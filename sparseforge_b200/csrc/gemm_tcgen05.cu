@@ -481,6 +481,28 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+typedef CUresult (*CtxGetCurrentFn)(CUcontext*);
+
+// Driver calls need a context current on the calling thread. A thread that has made no runtime
+// call yet (an autograd worker on device 0) has none; a no-op runtime call binds the primary
+// context of the current device. Checked through the driver so that nothing but the two queries
+// runs on threads that are already set up (cudaFree is not allowed during stream capture).
+static int ensure_context() {
+    static CtxGetCurrentFn get_current = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuCtxGetCurrent", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            get_current = reinterpret_cast<CtxGetCurrentFn>(p);
+    });
+    CUcontext ctx = nullptr;
+    if (get_current && get_current(&ctx) == CUDA_SUCCESS && ctx != nullptr) return SF_OK;
+    SF_CHECK_CUDA(cudaFree(nullptr));
+    return SF_OK;
+}
+
 static EncodeTiledFn encode_tiled_fn() {
     static EncodeTiledFn fn = nullptr;
     static std::once_flag once;
@@ -498,10 +520,7 @@ static EncodeTiledFn encode_tiled_fn() {
 // 64 inner elements x box_outer rows.
 int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t ld,
                          int box_outer) {
-    // The encode call goes straight to the driver and needs a context current on this thread. A
-    // thread that has not made a runtime call yet (e.g. an autograd worker on device 0) has none:
-    // a no-op runtime call binds the primary context of the current device first.
-    SF_CHECK_CUDA(cudaFree(nullptr));
+    if (int rc = ensure_context()) return rc;
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
@@ -518,7 +537,7 @@ int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64
 // Tensor map over a byte matrix [rows, 16] (rows of 16 bytes, no swizzle) with a box of box_rows rows:
 // the tensor-core ordered 2:4 metadata, one 2048-byte tile = 128 such rows.
 int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows) {
-    SF_CHECK_CUDA(cudaFree(nullptr));
+    if (int rc = ensure_context()) return rc;
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     cuuint64_t dims[2] = {16, (cuuint64_t)rows};
