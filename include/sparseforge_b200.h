@@ -206,6 +206,27 @@ SF_API int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, v
                     int64_t cols, void* stream);
 
 /*
+ * The same AdamW step, followed in the same pass by the importance score of the UPDATED weight.
+ *   replaces: AdamW.step legacy/adamw.py:65-176 followed by SparseLinear.update_mask's score
+ *             refresh, legacy/sparse_modeling.py:1041-1088 (the training loop steps the optimizer,
+ *             then update_mask scores the new weight: main.py's sparse step). One read of p, g,
+ *             m, v, mask, H instead of the optimizer pass plus a score pass over W and H.
+ * score[n] (fp32) <- metric(p_new as stored, H); norm[0..1] <- mean and population std + 1e-6 of
+ * score; scratch as for sf_hutch_score (scratch[0..1] hold sum and sum of squares on return).
+ * metric is one of SF_METRIC_HESSIAN_OBD, _HESSIAN_RATIO, _MAGNITUDE, _HESSIAN; H (fp32) may be NULL
+ * for _MAGNITUDE. hvp != NULL also folds this step's Hutchinson sample into H first
+ * (H <- beta_h H + (1-beta_h) max(hvp*probe, 0), arguments as for sf_hutch_score; the reference
+ * does it after backward and before the optimizer step, main.py's Hutchinson block); hvp = NULL
+ * leaves H untouched. Results equal sf_hutch_score(score = NULL) + sf_adamw_masked +
+ * sf_hutch_score(hvp = NULL), bit for bit in H, p, m, v and score.
+ */
+SF_API int sf_adamw_masked_score(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype,
+                          int64_t n, double lr, double beta1, double beta2, double eps, double weight_decay,
+                          double decay, double bc1, double bc2, double adaptive_l1, const void* hvp,
+                          const void* probe, int v_dtype, double beta_h, float* H, float* score, float* norm,
+                          double* scratch, int metric, void* stream);
+
+/*
  * Mask reductions for one layer (no mask update).
  *   replaces: mid_penalty legacy/utils.py:875-938, sparsity_penalty :941-1025,
  *             nm_2_4_tile_stats :1028-1234 (the per-layer sums; the caller combines layers).

@@ -272,6 +272,18 @@ struct Span8<int8_t> {
         }
     }
 };
+// Eight +-1 probe signs held as int8 in one 8-byte load (only the sign bit is read).
+template <>
+struct Vec8<int8_t> {
+    static __device__ __forceinline__ void load(const int8_t* p, float (&x)[8]) {
+        const uint2 r = __ldcs(reinterpret_cast<const uint2*>(p));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[i] = __uint_as_float(0x3f800000u | (((r.x >> (8 * i)) & 0x80u) << 24));
+            x[4 + i] = __uint_as_float(0x3f800000u | (((r.y >> (8 * i)) & 0x80u) << 24));
+        }
+    }
+};
 // Packed 2:4 metadata of a span: byte j of the tensor holds groups 2j (low nibble) and 2j+1.
 // Lanes 2j and 2j+1 hold those two groups; the even lane writes the byte of the first halves,
 // the odd lane the byte of the second halves. Must be called by the whole warp.

@@ -70,6 +70,8 @@ static int grid_one_wave(const void* kernel, int64_t chunks) {
 // ---------------------------------------------------------------------------------------
 // Hutchinson accumulate + score + partial sums
 // ---------------------------------------------------------------------------------------
+constexpr int kMetricNone = -1;
+
 template <typename TW, typename TV, int METRIC, bool ACCUM>
 __global__ void __launch_bounds__(kThreads)
 hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* __restrict__ H,
@@ -81,8 +83,9 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
     const int64_t n = chunks * 8;
     SF_SPAN_LOOP(span, n) {
         const SpanPos pos = span_pos(span, threadIdx.x & 31, n);
+        constexpr bool SCORE = METRIC != kMetricNone;  // kMetricNone: update H only
         float w[8], h[8], s[8];
-        Span8<TW>::load(W, pos, w);
+        if (SCORE) Span8<TW>::load(W, pos, w);
         constexpr bool NEED_H = (METRIC == SF_METRIC_HESSIAN_OBD || METRIC == SF_METRIC_HESSIAN_RATIO ||
                                  METRIC == SF_METRIC_HESSIAN) || ACCUM;
         if (NEED_H) Span8<float>::load(H, pos, h);
@@ -98,6 +101,7 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
             }
             Span8<float>::store(H, pos, h);
         }
+        if (!SCORE) continue;
         if (METRIC == SF_METRIC_MOVEMENT) {
             float g[8];
             Span8<TW>::load(aux, pos, g);
@@ -130,6 +134,7 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
         acc_s += (double)ps;
         acc_s2 += (double)ps2;
     }
+    if (METRIC == kMetricNone) return;
     __shared__ double red[2][kThreads / 32];
     acc_s = warp_sum(acc_s);
     acc_s2 = warp_sum(acc_s2);
@@ -199,7 +204,8 @@ static int launch_hutch_score(int metric, const void* hvp, const void* v, float*
         kern<<<grid, kThreads, 0, st>>>((const TW*)hvp, (const TV*)v, H, (const TW*)W, (const TW*)aux, aux_scalar, \
                                         score, scratch, chunks, beta, omb);                      \
     } while (0)
-    switch (metric) {
+    switch (score == nullptr ? kMetricNone : metric) {
+        case kMetricNone: SF_LAUNCH_HS(kMetricNone); break;
         case SF_METRIC_HESSIAN_OBD: SF_LAUNCH_HS(SF_METRIC_HESSIAN_OBD); break;
         case SF_METRIC_HESSIAN_RATIO: SF_LAUNCH_HS(SF_METRIC_HESSIAN_RATIO); break;
         case SF_METRIC_MAGNITUDE: SF_LAUNCH_HS(SF_METRIC_MAGNITUDE); break;
@@ -465,11 +471,23 @@ struct AdamParams {
     int has_mask;
 };
 
-template <typename TW, bool EMIT_WM>
+template <typename TW>
+struct HutchArgs {
+    const TW* hvp;          // NULL: H is read only
+    const int8_t* probe_i8; // exactly one of the two probes is set when hvp is
+    const TW* probe_w;
+    float beta, one_minus_beta;
+};
+
+// SCORE: also writes the importance score of the updated (stored) weight and this block's partial
+// sums of score and score^2, so the mask update that follows needs no separate score pass.
+template <typename TW, bool EMIT_WM, bool SCORE>
 __global__ void __launch_bounds__(kThreads)
 adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* __restrict__ mask,
                     TW* __restrict__ m, TW* __restrict__ v, TW* __restrict__ wm, int64_t chunks,
-                    AdamParams A, MaskUpdateParams P) {
+                    AdamParams A, MaskUpdateParams P, float* __restrict__ H, float* __restrict__ score,
+                    double* __restrict__ partials, int metric, HutchArgs<TW> hu) {
+    double acc_s = 0.0, acc_s2 = 0.0;
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
          c += (int64_t)gridDim.x * kThreads) {
         const int64_t e = c * 8;
@@ -502,6 +520,38 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         Vec8<TW>::store(p + e, pw);
         Vec8<TW>::store(m + e, em);
         Vec8<TW>::store(v + e, ev);
+        if (SCORE) {
+            float h[8], sc[8];
+            if (metric != SF_METRIC_MAGNITUDE || hu.hvp != nullptr) Vec8<float>::load(H + e, h);
+            if (hu.hvp != nullptr) {
+                // the Hutchinson sample of this step is folded into H before the score reads it
+                float hv[8], sg[8];
+                Vec8<TW>::load(hu.hvp + e, hv);
+                if (hu.probe_i8) Vec8<int8_t>::load(hu.probe_i8 + e, sg); else Vec8<TW>::load(hu.probe_w + e, sg);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float d = fmaxf(Vec8<TW>::round(__fmul_rn(hv[i], sg[i])), 0.0f);
+                    h[i] = __fmaf_rn(hu.one_minus_beta, d, __fmul_rn(h[i], hu.beta));
+                }
+                Vec8<float>::store(H + e, h);
+            }
+            float ps = 0.0f, ps2 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float w = Vec8<TW>::round(pw[i]);  // the weight as stored
+                float sv;
+                if (metric == SF_METRIC_HESSIAN_OBD) sv = __fmul_rn(__fadd_rn(h[i], 1e-8f), Vec8<TW>::round(__fmul_rn(w, w)));
+                else if (metric == SF_METRIC_HESSIAN_RATIO) sv = __fdiv_rn(fabsf(w), __fsqrt_rn(__fadd_rn(h[i], 1e-8f)));
+                else if (metric == SF_METRIC_HESSIAN) sv = h[i];
+                else sv = fabsf(w);
+                sc[i] = sv;
+                ps += sv;
+                ps2 = fmaf(sv, sv, ps2);
+            }
+            Vec8<float>::store(score + e, sc);
+            acc_s += (double)ps;
+            acc_s2 += (double)ps2;
+        }
         if (EMIT_WM) {
 #pragma unroll
             for (int g2 = 0; g2 < 2; ++g2) {
@@ -514,6 +564,21 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
                 }
             }
             Vec8<TW>::store(wm + e, o);
+        }
+    }
+    if (SCORE) {
+        __shared__ double red[2][kThreads / 32];
+        acc_s = warp_sum(acc_s);
+        acc_s2 = warp_sum(acc_s2);
+        const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+        if (lane == 0) { red[0][wid] = acc_s; red[1][wid] = acc_s2; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            double a = 0.0, b = 0.0;
+#pragma unroll
+            for (int i = 0; i < kThreads / 32; ++i) { a += red[0][i]; b += red[1][i]; }
+            partials[2 * blockIdx.x] = a;
+            partials[2 * blockIdx.x + 1] = b;
         }
     }
 }
@@ -588,7 +653,9 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
                    int64_t n, double beta_d, int metric, void* stream) {
     float aux_scalar = (float)aux_scalar_d;
     const float beta = (float)beta_d;
-    SF_CHECK_ARG(W && score && norm && scratch, "sf_hutch_score: W, score, norm and scratch must be non-null");
+    SF_CHECK_ARG(W != nullptr || score == nullptr, "sf_hutch_score: W must be non-null");
+    SF_CHECK_ARG(score == nullptr ? hvp != nullptr : (norm && scratch),
+                 "sf_hutch_score: give score, norm and scratch, or score = NULL with hvp to update H only");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_hutch_score: n=%lld must be a positive multiple of 8", (long long)n);
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_hutch_score: w_dtype must be SF_F32 or SF_BF16");
     const bool accum = hvp != nullptr;
@@ -596,10 +663,10 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
         SF_CHECK_ARG(v != nullptr && H != nullptr, "sf_hutch_score: hvp given without v or H");
         SF_CHECK_ARG(v_dtype == SF_I8 || v_dtype == w_dtype, "sf_hutch_score: v_dtype must be SF_I8 or w_dtype");
     }
-    const bool need_h = metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO ||
-                        metric == SF_METRIC_HESSIAN;
+    const bool need_h = score != nullptr && (metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO ||
+                                             metric == SF_METRIC_HESSIAN);
     SF_CHECK_ARG(!need_h || H != nullptr, "sf_hutch_score: metric %d needs H", metric);
-    SF_CHECK_ARG(metric != SF_METRIC_MOVEMENT || aux != nullptr, "sf_hutch_score: movement metric needs aux=grad_ema");
+    SF_CHECK_ARG(score == nullptr || metric != SF_METRIC_MOVEMENT || aux != nullptr, "sf_hutch_score: movement metric needs aux=grad_ema");
     if (!(aligned16(W) && aligned16(score) && aligned16(H) && aligned16(hvp) && aligned16(aux)) ||
         (reinterpret_cast<uintptr_t>(v) & 7u))
         return fail(SF_ERR_ALIGNMENT, "sf_hutch_score: buffers must be 16-byte aligned (v: 8-byte)");
@@ -622,6 +689,8 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
     }
 #undef SF_HS
     if (rc != SF_OK) return rc;
+    SF_CHECK_CUDA(cudaGetLastError());
+    if (score == nullptr) return SF_OK;
     score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
@@ -752,10 +821,11 @@ int sf_effective_weight(const void* W, int w_dtype, const float* mask, void* wm,
     return SF_OK;
 }
 
-int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
-                    double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
-                    double bc1, double bc2, double adaptive_l1, void* wm, double hx, int64_t cols,
-                    void* stream) {
+static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
+                      double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
+                      double bc1, double bc2, double adaptive_l1, void* wm, double hx, int64_t cols,
+                      float* H, float* score, float* norm, double* scratch, int metric, const void* hvp,
+                      const void* probe, int v_dtype, double beta_h, void* stream) {
     SF_CHECK_ARG(p && g && m && v, "sf_adamw_masked: p, g, m, v must be non-null");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_adamw_masked: n=%lld must be a positive multiple of 8", (long long)n);
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_adamw_masked: w_dtype must be SF_F32 or SF_BF16");
@@ -781,17 +851,62 @@ int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v,
     A.has_mask = mask != nullptr;
     MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, hx, 0, 0);
     const int64_t chunks = n / 8;
-#define SF_AD(TW, EW)                                                                            \
+    int grid = 0;
+#define SF_AD(TW, EW, SC)                                                                        \
     do {                                                                                         \
-        auto kern = adamw_masked_kernel<TW, EW>;                                                 \
-        kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
-            (TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P);                  \
+        auto kern = adamw_masked_kernel<TW, EW, SC>;                                             \
+        grid = grid_one_wave((const void*)kern, chunks);                                         \
+        if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;                                  \
+        HutchArgs<TW> hu;                                                                        \
+        hu.hvp = (const TW*)hvp;                                                                 \
+        hu.probe_i8 = (hvp && v_dtype == SF_I8) ? (const int8_t*)probe : nullptr;                \
+        hu.probe_w = (hvp && v_dtype != SF_I8) ? (const TW*)probe : nullptr;                     \
+        hu.beta = (float)beta_h;                                                                 \
+        hu.one_minus_beta = (float)(1.0 - beta_h);                                               \
+        kern<<<grid, kThreads, 0, st>>>((TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P, H, score, \
+                                        scratch, metric, hu);                                    \
     } while (0)
-    if (w_dtype == SF_F32) { if (wm) SF_AD(float, true); else SF_AD(float, false); }
-    else { if (wm) SF_AD(__nv_bfloat16, true); else SF_AD(__nv_bfloat16, false); }
+    if (score != nullptr) {
+        if (w_dtype == SF_F32) SF_AD(float, false, true); else SF_AD(__nv_bfloat16, false, true);
+    } else if (w_dtype == SF_F32) { if (wm) SF_AD(float, true, false); else SF_AD(float, false, false); }
+    else { if (wm) SF_AD(__nv_bfloat16, true, false); else SF_AD(__nv_bfloat16, false, false); }
 #undef SF_AD
     SF_CHECK_CUDA(cudaGetLastError());
+    if (score != nullptr) {
+        score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+        SF_CHECK_CUDA(cudaGetLastError());
+    }
     return SF_OK;
+}
+
+int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
+                    double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
+                    double bc1, double bc2, double adaptive_l1, void* wm, double hx, int64_t cols,
+                    void* stream) {
+    return adamw_impl(p, g, mask, m, v, w_dtype, n, lr, beta1, beta2, eps, weight_decay, decay, bc1, bc2, adaptive_l1,
+                      wm, hx, cols, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.0, stream);
+}
+
+int sf_adamw_masked_score(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,
+                          double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
+                          double bc1, double bc2, double adaptive_l1, const void* hvp, const void* probe,
+                          int v_dtype, double beta_h, float* H, float* score, float* norm, double* scratch,
+                          int metric, void* stream) {
+    if (hvp != nullptr) {
+        SF_CHECK_ARG(probe != nullptr && H != nullptr, "sf_adamw_masked_score: hvp given without probe or H");
+        SF_CHECK_ARG(v_dtype == SF_I8 || v_dtype == w_dtype, "sf_adamw_masked_score: v_dtype must be SF_I8 or w_dtype");
+        if (!aligned16(hvp) || (reinterpret_cast<uintptr_t>(probe) & 7u))
+            return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked_score: hvp must be 16-byte, probe 8-byte aligned");
+    }
+    SF_CHECK_ARG(score && norm && scratch, "sf_adamw_masked_score: score, norm, scratch must be non-null");
+    SF_CHECK_ARG(metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO || metric == SF_METRIC_MAGNITUDE ||
+                     metric == SF_METRIC_HESSIAN,
+                 "sf_adamw_masked_score: metric %d is not available fused (use sf_hutch_score)", metric);
+    SF_CHECK_ARG(metric == SF_METRIC_MAGNITUDE || H != nullptr, "sf_adamw_masked_score: metric %d needs H", metric);
+    if (!(aligned16(H) && aligned16(score)))
+        return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked_score: buffers must be 16-byte aligned");
+    return adamw_impl(p, g, mask, m, v, w_dtype, n, lr, beta1, beta2, eps, weight_decay, decay, bc1, bc2, adaptive_l1,
+                      nullptr, 1.0, 0, H, score, norm, scratch, metric, hvp, probe, v_dtype, beta_h, stream);
 }
 
 int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, void* stream) {

@@ -59,6 +59,17 @@ def hutch_score(W, H, score, norm, scratch, *, hvp=None, v=None, aux=None, aux_s
                                _lib.METRICS[metric], _stream()), "sf_hutch_score")
 
 
+def hutch_accumulate(H, hvp, v, *, beta=0.99) -> None:
+    """H <- beta H + (1-beta) max(hvp*v, 0) only: the score is left to a later pass (adamw_masked_score)."""
+    _cuda(H, hvp, v)
+    if H.dtype != torch.float32 or H.numel() != hvp.numel():
+        raise TypeError("hutch_accumulate: H must be float32 with hvp's size")
+    if v.dtype not in (torch.int8, hvp.dtype):
+        raise TypeError("hutch_accumulate: v must be int8 signs or have hvp's dtype")
+    check(lib().sf_hutch_score(_p(hvp), _p(v), _dt(v), _p(H), None, _dt(hvp), None, 1.0, None, None, None,
+                               hvp.numel(), float(beta), _lib.METRICS["hessian_obd"], _stream()), "sf_hutch_score")
+
+
 def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
                      pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
                      structured_exact=False, score_bf16=False) -> None:
@@ -120,6 +131,32 @@ def adamw_masked(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, 
     check(lib().sf_adamw_masked(_p(p), _p(g), _p(mask), _p(m), _p(v), _dt(p), p.numel(), float(lr), float(beta1),
                                 float(beta2), float(eps), float(weight_decay), float(decay), float(bc1), float(bc2),
                                 float(adaptive_l1), _p(wm), float(hx), cols, _stream()), "sf_adamw_masked")
+
+
+def adamw_masked_score(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, decay, step, adaptive_l1=0.0,
+                       H=None, score, norm, scratch, metric: str, hvp=None, probe=None, beta_h=0.99) -> None:
+    """AdamW step and, in the same pass, the importance score of the updated weight with its mean/std.
+    With hvp and probe the Hutchinson sample is folded into H first (as hutch_accumulate does)."""
+    _cuda(p, g, m, v, mask, H, score, norm, scratch, hvp, probe)
+    if hvp is not None:
+        if probe is None or H is None or hvp.dtype != p.dtype or hvp.numel() != p.numel():
+            raise TypeError("adamw_masked_score: hvp needs probe and H, and p's dtype and size")
+        if probe.dtype not in (torch.int8, p.dtype):
+            raise TypeError("adamw_masked_score: probe must be int8 signs or have p's dtype")
+    if not (p.dtype == g.dtype == m.dtype == v.dtype):
+        raise TypeError("adamw_masked_score: p, g, m, v must share a dtype")
+    if mask is not None and mask.dtype != torch.float32:
+        raise TypeError("adamw_masked_score: mask must be float32")
+    if score.dtype != torch.float32 or (H is not None and H.dtype != torch.float32):
+        raise TypeError("adamw_masked_score: H and score must be float32")
+    bc1 = 1.0 - beta1 ** step
+    bc2 = 1.0 - beta2 ** step
+    check(lib().sf_adamw_masked_score(_p(p), _p(g), _p(mask), _p(m), _p(v), _dt(p), p.numel(), float(lr), float(beta1),
+                                      float(beta2), float(eps), float(weight_decay), float(decay), float(bc1),
+                                      float(bc2), float(adaptive_l1), _p(hvp), _p(probe),
+                                      _dt(probe) if probe is not None else SF_I8, float(beta_h), _p(H), _p(score),
+                                      _p(norm), _p(scratch),
+                                      _lib.METRICS[metric], _stream()), "sf_adamw_masked_score")
 
 
 def mask_stats(mask, stats) -> None:

@@ -262,6 +262,54 @@ def test_adamw_no_mask(ops):
     assert rel_err(p, wp) <= F32_TOL and rel_err(m, wm_) <= F32_TOL and rel_err(v, wv) <= F32_TOL
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("metric", ["hessian_obd", "hessian_ratio", "magnitude", "hessian"])
+def test_adamw_with_score_equals_separate_calls(ops, dtype, metric):
+    """The fused optimizer+score pass and the H-only accumulation give, bit for bit, what the
+    separate calls give: H update, AdamW step, then the score of the new weight."""
+    torch.manual_seed(11)
+    rows, cols = 96, 264  # 25344 elements: not a multiple of a 256-element span
+    p0 = (torch.randn(rows, cols) * 0.05).to(dtype)
+    g0 = (torch.randn(rows, cols) * 0.01).to(dtype)
+    hvp = (torch.randn(rows, cols) * 0.1).to(dtype)
+    sign = (torch.randint(0, 2, (rows, cols)) * 2 - 1).to(torch.int8)
+    mask = torch.rand(rows, cols)
+    H0 = torch.rand(rows, cols) * 1e-3
+    kw = dict(lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, decay=2e-4, step=3, adaptive_l1=1e-5)
+
+    # separate calls
+    pa, ma, va, Ha = dev(p0), dev(torch.full_like(p0, 1e-3)), dev(torch.full_like(p0, 1e-5)), dev(H0)
+    sa, na, scr = torch.empty(rows, cols, device=DEV), torch.empty(2, device=DEV), ops.hutch_score_scratch(DEV)
+    ops.hutch_score(pa, Ha, sa, na, scr, hvp=dev(hvp), v=dev(sign), beta=0.98, metric=metric)
+    ops.adamw_masked(pa, dev(g0), ma, va, mask=dev(mask), **kw)
+    ops.hutch_score(pa, Ha, sa, na, scr, metric=metric)
+    sums_a = scr[:2].clone()
+
+    # H only, then optimizer + score in one pass
+    pb, mb, vb, Hb = dev(p0), dev(torch.full_like(p0, 1e-3)), dev(torch.full_like(p0, 1e-5)), dev(H0)
+    sb, nb, scr2 = torch.empty(rows, cols, device=DEV), torch.empty(2, device=DEV), ops.hutch_score_scratch(DEV)
+    ops.hutch_accumulate(Hb, dev(hvp), dev(sign), beta=0.98)
+    ops.adamw_masked_score(pb, dev(g0), mb, vb, mask=dev(mask), H=Hb, score=sb, norm=nb, scratch=scr2,
+                           metric=metric, **kw)
+    assert torch.equal(Ha, Hb)
+    assert torch.equal(pa, pb) and torch.equal(ma, mb) and torch.equal(va, vb)
+    assert torch.equal(sa, sb)
+    # all three in one pass (the probe once as int8 signs, once in the weight dtype)
+    for probe in (dev(sign), dev(sign.to(dtype))):
+        pc, mc, vc, Hc = dev(p0), dev(torch.full_like(p0, 1e-3)), dev(torch.full_like(p0, 1e-5)), dev(H0)
+        sc_, nc = torch.empty(rows, cols, device=DEV), torch.empty(2, device=DEV)
+        ops.adamw_masked_score(pc, dev(g0), mc, vc, mask=dev(mask), H=Hc, score=sc_, norm=nc, scratch=scr2,
+                               metric=metric, hvp=dev(hvp), probe=probe, beta_h=0.98, **kw)
+        assert torch.equal(Ha, Hc) and torch.equal(pa, pc) and torch.equal(ma, mc) and torch.equal(va, vc)
+        assert torch.equal(sa, sc_) and torch.allclose(na, nc, rtol=1e-6, atol=0)
+    # eight values at a time are summed in fp32, and the two kernels group the eight differently
+    assert torch.allclose(sums_a, scr2[:2], rtol=1e-6, atol=0)
+    assert torch.allclose(na, nb, rtol=1e-6, atol=0)
+    # and against the oracle's score of the new weight
+    want = O.importance_score(pb.cpu(), metric, H=Hb.cpu())
+    assert rel_err(sb, want.float()) <= (F32_TOL if dtype == torch.float32 else BF16_TOL)
+
+
 # ---------------------------------------------------------------------------------------
 # argument checks: bad calls are refused on the host, nothing is launched
 # ---------------------------------------------------------------------------------------
