@@ -123,6 +123,38 @@ __device__ __forceinline__ uint32_t top2_keep_fast(const float (&x)[4]) {
     return (r[0] < 2 ? 1u : 0u) | (r[1] < 2 ? 2u : 0u) | (r[2] < 2 ? 4u : 0u) | (r[3] < 2 ? 8u : 0u);
 }
 
+// The same stable top-2 as lane masks: keep[i] is all ones if column i is kept, else zero.
+// b_ij = (x_i >= x_j) says "i beats j" (the lower index wins a tie); column i is kept when at
+// most one other column beats it, which is a majority vote over three of the six comparisons.
+__device__ __forceinline__ uint32_t set_ge(float a, float b) {
+    uint32_t d;
+    asm("set.ge.u32.f32 %0, %1, %2;" : "=r"(d) : "f"(a), "f"(b));
+    return d;
+}
+__device__ __forceinline__ uint32_t maj3(uint32_t a, uint32_t b, uint32_t c) { return (a & b) | (a & c) | (b & c); }
+__device__ __forceinline__ void top2_keep_masks(const float (&x)[4], uint32_t (&keep)[4]) {
+    const uint32_t b01 = set_ge(x[0], x[1]), b02 = set_ge(x[0], x[2]), b03 = set_ge(x[0], x[3]);
+    const uint32_t b12 = set_ge(x[1], x[2]), b13 = set_ge(x[1], x[3]), b23 = set_ge(x[2], x[3]);
+    keep[0] = maj3(b01, b02, b03);
+    keep[1] = maj3(~b01, b12, b13);
+    keep[2] = maj3(~b02, ~b12, b23);
+    keep[3] = maj3(~b03, ~b13, ~b23);
+}
+__device__ __forceinline__ uint32_t keep_bits(const uint32_t (&keep)[4]) {
+    return (keep[0] & 1u) | (keep[1] & 2u) | (keep[2] & 4u) | (keep[3] & 8u);
+}
+// Second largest of four values (the 2:4 group threshold), seven min/max.
+__device__ __forceinline__ float second_largest4(const float (&x)[4]) {
+    const float lo1 = fminf(x[0], x[1]), hi1 = fmaxf(x[0], x[1]);
+    const float lo2 = fminf(x[2], x[3]), hi2 = fmaxf(x[2], x[3]);
+    return fmaxf(fminf(hi1, hi2), fmaxf(lo1, lo2));
+}
+// Metadata nibble from keep bits with exactly two set: keep >> 1 is unique per pattern (1..6).
+__device__ __forceinline__ uint32_t nibble_of_keep_lut(uint32_t keep) {
+    constexpr uint32_t lut = (4u << 4) | (8u << 8) | (9u << 12) | (12u << 16) | (13u << 20) | (14u << 24);
+    return (lut >> ((keep & 0xEu) << 1)) & 0xFu;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -168,6 +200,19 @@ struct Vec8<float> {
     }
     // Rounding a value to the storage type and back (identity for fp32).
     static __device__ __forceinline__ float round(float x) { return x; }
+    // Raw storage of 8 elements, and p <- raw * round(f) element by element.
+    struct Raw { uint4 a, b; };
+    static __device__ __forceinline__ Raw load_raw(const float* p) { return Raw{ld_stream16(p), ld_stream16(p + 4)}; }
+    static __device__ __forceinline__ void store_product(float* p, const Raw& r, const float (&f)[8]) {
+        st_stream16(p, make_uint4(__float_as_uint(__fmul_rn(__uint_as_float(r.a.x), f[0])),
+                                  __float_as_uint(__fmul_rn(__uint_as_float(r.a.y), f[1])),
+                                  __float_as_uint(__fmul_rn(__uint_as_float(r.a.z), f[2])),
+                                  __float_as_uint(__fmul_rn(__uint_as_float(r.a.w), f[3]))));
+        st_stream16(p + 4, make_uint4(__float_as_uint(__fmul_rn(__uint_as_float(r.b.x), f[4])),
+                                      __float_as_uint(__fmul_rn(__uint_as_float(r.b.y), f[5])),
+                                      __float_as_uint(__fmul_rn(__uint_as_float(r.b.z), f[6])),
+                                      __float_as_uint(__fmul_rn(__uint_as_float(r.b.w), f[7]))));
+    }
 };
 template <>
 struct Vec8<__nv_bfloat16> {
@@ -190,6 +235,21 @@ struct Vec8<__nv_bfloat16> {
         st_stream16(p, make_uint4(w[0], w[1], w[2], w[3]));
     }
     static __device__ __forceinline__ float round(float x) { return bf16_round_int(x); }
+    // Raw storage of 8 elements, and p <- raw * round(f): the factors are packed to bf16 pairs and
+    // multiplied pairwise (one rounding of the exact product, as a bf16 tensor multiply does).
+    struct Raw { uint4 a; };
+    static __device__ __forceinline__ Raw load_raw(const __nv_bfloat16* p) { return Raw{ld_stream16(p)}; }
+    static __device__ __forceinline__ void store_product(__nv_bfloat16* p, const Raw& r, const float (&f)[8]) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+        uint32_t o[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 e = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            const __nv_bfloat162 prod = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]), e);
+            o[i] = *reinterpret_cast<const uint32_t*>(&prod);
+        }
+        st_stream16(p, make_uint4(o[0], o[1], o[2], o[3]));
+    }
 };
 
 

@@ -264,61 +264,70 @@ __device__ __forceinline__ void block_reduce_stats(const GroupStats& g, double* 
     }
 }
 
-template <typename TW, bool EMIT_WM, bool EMIT_META>
+// PLAIN: no bf16 score rounding, no exact gate, no beta mixing, no penalty, no binarise push
+// (the tempering recipe of the benchmark); the general instantiation tests those at run time.
+template <typename TW, bool EMIT_WM, bool EMIT_META, bool PLAIN>
 __global__ void __launch_bounds__(kThreads)
 mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict__ norm,
                         float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm,
                         uint8_t* __restrict__ meta, double* __restrict__ stats, int64_t chunks,
                         MaskUpdateParams P) {
-    // The gate needs (s_i - tau) / (sigma (T + 1e-8)) only, so the mean cancels unless the
-    // normalised score has to be rounded to bf16 first.
     const float mu = norm[0];
     const float inv_sigma = __fdiv_rn(1.0f, norm[1]);
     const bool unstructured = P.tau != nullptr;
     const float tau_global = unstructured ? *P.tau : 0.0f;
+    const bool score_bf16 = !PLAIN && P.score_bf16;
+    const bool exact = !PLAIN && P.structured_exact && !unstructured;
+    const bool mix = !PLAIN && P.beta_s > 0.0f;
+    const bool penalty = !PLAIN && P.pen != 0.0f;
+    const bool binarize = !PLAIN && P.binarize;
+    const uint32_t omhx_bits = P.soft_only ? 0u : __float_as_uint(P.one_minus_hx);
+    const float hx = P.soft_only ? 1.0f : P.hx;
     GroupStats gs;
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks;
          c += (int64_t)gridDim.x * kThreads) {
         const int64_t e = c * 8;
-        float sc[8], m[8], w[8], out_w[8];
+        float sc[8], m[8], eff[8];
+        typename Vec8<TW>::Raw wraw;
         Vec8<float>::load(score + e, sc);
         Vec8<float>::load(mask + e, m);
-        if (EMIT_WM) Vec8<TW>::load(W + e, w);
-        uint32_t meta_byte = 0;
+        if (EMIT_WM) wraw = Vec8<TW>::load_raw(W + e);
+        uint32_t kp8 = 0, kn8 = 0;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
             float s[4], G[4], mp[4], mn[4];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 s[i] = __fmul_rn(__fsub_rn(sc[4 * g + i], mu), inv_sigma);
-                if (P.score_bf16) s[i] = bf16_round_int(s[i]);
+                if (score_bf16) s[i] = bf16_round_int(s[i]);
                 mp[i] = m[4 * g + i];
             }
-            int r[4];
-            rank4_fast(s, r);
-            const float tau = unstructured ? tau_global : (r[0] == 1 ? s[0] : (r[1] == 1 ? s[1] : (r[2] == 1 ? s[2] : s[3])));
+            const float tau = unstructured ? tau_global : second_largest4(s);
+            uint32_t ks[4] = {0u, 0u, 0u, 0u};
+            if (exact || mix) top2_keep_masks(s, ks);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 float gi;
-                if (P.structured_exact && !unstructured) gi = r[i] < 2 ? 1.0f : 0.0f;
+                if (exact) gi = __uint_as_float(ks[i] & 0x3f800000u);
                 else {
                     // sigmoid(z) = 1 / (1 + 2^(-z log2 e)), z = (s_i - tau) / (T + 1e-8)
                     gi = fast_rcp(1.0f + fast_ex2(__fmul_rn(__fsub_rn(s[i], tau), P.neg_log2e_over_t)));
-                    if (P.score_bf16) gi = bf16_round_int(gi);
+                    if (score_bf16) gi = bf16_round_int(gi);
                 }
-                if (P.beta_s > 0.0f) {
-                    float t = r[i] < 2 ? P.beta_s : 0.0f;
+                if (mix) {
+                    const float t = __uint_as_float(ks[i] & __float_as_uint(P.beta_s));
                     gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), t);
-                    if (P.score_bf16) gi = bf16_round_int(gi);
+                    if (score_bf16) gi = bf16_round_int(gi);
                 }
                 G[i] = gi;
             }
-            if (P.pen != 0.0f) {
+            if (penalty) {
                 if (P.penalty_mode == SF_PENALTY_TOPN) {
-                    const uint32_t kg = top2_keep_fast(G);
+                    uint32_t kg[4];
+                    top2_keep_masks(G, kg);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        float delta = __fsub_rn(mp[i], ((kg >> i) & 1u) ? 1.0f : 0.0f);
+                        float delta = __fsub_rn(mp[i], __uint_as_float(kg[i] & 0x3f800000u));
                         G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, delta));
                     }
                 } else if (P.penalty_mode == SF_PENALTY_MID) {
@@ -331,7 +340,7 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
 #pragma unroll
                 for (int i = 0; i < 4; ++i) G[i] = fminf(fmaxf(G[i], 0.0f), 1.0f);
             }
-            if (P.binarize) {
+            if (binarize) {
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     if (G[i] < 0.5f) G[i] = __fmul_rn(G[i], P.bin_lo);
@@ -340,33 +349,32 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
             }
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                float v = __fmaf_rn(P.a, G[i], __fmul_rn(mp[i], P.one_minus_a));
-                mn[i] = fminf(fmaxf(v, 0.0f), 1.0f);
+                // clamp((1-a) mask + a G, 0, 1): the clamp rides on the multiply-add
+                mn[i] = __saturatef(__fmaf_rn(P.a, G[i], __fmul_rn(mp[i], P.one_minus_a)));
                 m[4 * g + i] = mn[i];
             }
-            const uint32_t kp = top2_keep_fast(mp);
-            const uint32_t kn = top2_keep_fast(mn);
-            gs.flips += __popc(kp ^ kn);
+            uint32_t kp[4], kn[4];
+            top2_keep_masks(mp, kp);
+            top2_keep_masks(mn, kn);
+            kp8 |= keep_bits(kp) << (4 * g);
+            kn8 |= keep_bits(kn) << (4 * g);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const bool top = (kn >> i) & 1u;
                 const float mv = mn[i];
                 gs.sum_m += mv;
                 gs.sum_m1m += __fmaf_rn(-mv, mv, mv);
-                gs.sum_top2 += top ? mv : 0.0f;
-                gs.sum_bot2 += top ? 0.0f : mv;
-                gs.lt_half += mn[i] < 0.5f ? 1 : 0;
-                if (EMIT_WM) {
-                    float eff = Vec8<TW>::round(effective_mask_value(mn[i], top, P));
-                    out_w[4 * g + i] = __fmul_rn(w[4 * g + i], eff);
-                }
+                gs.sum_top2 += __uint_as_float(kn[i] & __float_as_uint(mv));
+                gs.lt_half += mv < 0.5f ? 1 : 0;
+                // hx * mask + (1 - hx) * hard, two roundings as the reference's tensor expression
+                if (EMIT_WM) eff[4 * g + i] = __fadd_rn(__fmul_rn(hx, mv), __uint_as_float(kn[i] & omhx_bits));
             }
-            meta_byte |= nibble_of_keep(kn) << (4 * g);
         }
+        gs.flips += __popc(kp8 ^ kn8);
         Vec8<float>::store(mask + e, m);
-        if (EMIT_WM) Vec8<TW>::store(wm + e, out_w);
-        if (EMIT_META) meta[c] = (uint8_t)meta_byte;
+        if (EMIT_WM) Vec8<TW>::store_product(wm + e, wraw, eff);
+        if (EMIT_META) meta[c] = (uint8_t)(nibble_of_keep_lut(kn8 & 0xFu) | (nibble_of_keep_lut(kn8 >> 4) << 4));
     }
+    gs.sum_bot2 = gs.sum_m - gs.sum_top2;
     block_reduce_stats(gs, stats);
 }
 
@@ -749,11 +757,16 @@ int sf_mask_update_nm24(const float* score, const float* norm, const float* tau,
     P.tau = tau;
     const int64_t chunks = rows * cols / 8;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
-#define SF_MU(TW, EW, EM)                                                                        \
+    const bool plain = !score_bf16 && !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0;
+#define SF_MU_K(TW, EW, EM, PL)                                                                  \
     do {                                                                                         \
-        auto kern = mask_update_nm24_kernel<TW, EW, EM>;                                         \
+        auto kern = mask_update_nm24_kernel<TW, EW, EM, PL>;                                     \
         kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
             score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);                   \
+    } while (0)
+#define SF_MU(TW, EW, EM)                                                                        \
+    do {                                                                                         \
+        if (plain) SF_MU_K(TW, EW, EM, true); else SF_MU_K(TW, EW, EM, false);                   \
     } while (0)
 #define SF_MU_T(TW)                                       \
     do {                                                  \
@@ -764,6 +777,7 @@ int sf_mask_update_nm24(const float* score, const float* norm, const float* tau,
     } while (0)
     if (w_dtype == SF_F32) SF_MU_T(float); else SF_MU_T(__nv_bfloat16);
 #undef SF_MU_T
+#undef SF_MU_K
 #undef SF_MU
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
