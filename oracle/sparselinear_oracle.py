@@ -271,6 +271,49 @@ def linear_backward(x, W, eff_mask, dy, has_bias=False):
 # --------------------------------------------------------------------------------------
 # mask-aware AdamW
 # --------------------------------------------------------------------------------------
+class MaskedLinearSTE(torch.autograd.Function):
+    """Masked linear with a straight-through weight gradient, made of differentiable torch ops so
+    that a second backward pass (Hutchinson) runs through it: legacy/sparse_modeling.py:72-132.
+    ``eff_mask`` is the effective mask of the step (no gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, W, b, eff_mask):
+        ctx.save_for_backward(x, W, eff_mask)
+        ctx.has_bias = b is not None
+        return torch.nn.functional.linear(x, W * eff_mask.to(W.dtype), b)
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, W, M = ctx.saved_tensors
+        gy2 = gy.reshape(-1, gy.shape[-1])
+        gx = gy.matmul(W * M.to(W.dtype))                      # :112-115
+        gW = gy2.t().matmul(x.reshape(-1, x.shape[-1]))        # :117-125, no mask (straight-through)
+        gb = gy2.sum(0) if ctx.has_bias else None              # :127-129
+        return gx, gW, gb, None
+
+
+def hutchinson_hvps(loss, weights, probes):
+    """hvp_i = d<g, v>/dW_i with g = dloss/dW (graph kept): legacy/utils.py:760-790."""
+    grads = torch.autograd.grad(loss, weights, create_graph=True, retain_graph=True)
+    dot = sum((g * v).sum() for g, v in zip(grads, probes))
+    return torch.autograd.grad(dot, weights, retain_graph=True)
+
+
+def mid_penalty_value(masks, lambda_mid):
+    """lambda * sum(m (1 - m)) / count over all layers: legacy/utils.py:875-938."""
+    if lambda_mid <= 0:
+        return 0.0
+    tot = sum(float((m.double() * (1 - m.double())).sum()) for m in masks)
+    return lambda_mid * tot / sum(m.numel() for m in masks)
+
+
+def clip_grad_norm(grads, max_norm):
+    """torch.nn.utils.clip_grad_norm_ (2-norm over all gradients; coefficient clamped to 1)."""
+    total = torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(g) for g in grads]))
+    coef = torch.clamp(max_norm / (total + 1e-6), max=1.0)
+    return [g * coef for g in grads], float(total)
+
+
 def adamw_step(p, g, m, v, *, step, lr, betas, eps, weight_decay, mask=None, decay=0.0, adaptive_l1=0.0):
     """legacy/adamw.py:79-174 for one tensor. `step` is the 1-based step number after the
     increment at :146. Returns (p, m, v) as new tensors."""

@@ -457,8 +457,43 @@ class SparseLinear(nn.Linear):
         sr = float(self.sparsity_ratio)
         return 1.0 if (sr <= 0.0 or sr >= 1.0) else 1.0 / (1.0 - sr)
 
+    # -- inference on the sparse tensor cores ---------------------------------------------------
+    @torch.no_grad()
+    def compress_for_inference(self):
+        """Bakes weight * top2(mask) into the compressed 2:4 form the sparse tensor cores read
+        (values [out, in/2] bf16 + metadata) and switches ``mode`` to ``"sparse24_forward"``.
+        The reference's inference bake-in multiplies the hard mask into a dense weight and runs a
+        dense GEMM (legacy/eval_wiki_ppl.py:548-651); this is the same function with half the
+        weight bytes and half the tensor-core work. Forward only; the dense weight is kept."""
+        self._check_2to4()
+        if self.weight.dtype != torch.bfloat16:
+            raise TypeError("compress_for_inference: the sparse tensor-core GEMM is bfloat16 only")
+        if self.in_features % 16 != 0:
+            raise ValueError(f"compress_for_inference: in_features ({self.in_features}) must be a multiple of 16")
+        values, meta = ops.sparse24_compress(self.weight.data.contiguous(), self.mask.data.float().contiguous())
+        self._sp_values = values
+        self._sp_meta = meta
+        self._sp_meta_tc = ops.sparse24_pack_meta(meta, self.out_features, self.in_features)
+        self._sp_status = torch.zeros(4, dtype=torch.int32, device=self.weight.device)
+        self.mode = "sparse24_forward"
+        self._inference_optimized = True
+        return self
+
+    def _sparse24_forward(self, x):
+        if torch.is_grad_enabled() and (x.requires_grad or self.weight.requires_grad and self.training):
+            raise RuntimeError("mode 'sparse24_forward' is inference only; call it under torch.no_grad() / eval()")
+        if getattr(self, "_sp_values", None) is None:
+            raise RuntimeError("mode 'sparse24_forward' without compressed buffers: call compress_for_inference()")
+        x2d = x.reshape(-1, self.in_features)
+        if x2d.dtype != torch.bfloat16:
+            x2d = x2d.to(torch.bfloat16)
+        y = ops.sparse24_gemm(x2d.contiguous(), self._sp_values, self._sp_meta_tc, bias=self.bias, status=self._sp_status)
+        return y.view(*x.shape[:-1], self.out_features).to(x.dtype)
+
     def forward(self, x):
         """legacy/sparse_modeling.py:737-796."""
+        if self.mode == "sparse24_forward":
+            return self._sparse24_forward(x)
         if self.mode == "dense_forward" or self.mask_type == "none":
             ones = torch.ones_like(self.mask.data)
             return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)

@@ -237,3 +237,41 @@ def finalize_hard_masks(model):
         m._hardening_finalized = True
         m.hardening_x = 0.0
         m.invalidate_masked_weight()
+
+
+@torch.no_grad()
+def optimize_sparse_model_for_inference(model, use_slorb: bool = False, compressed: bool = False):
+    """Inference bake-in (legacy/eval_wiki_ppl.py:548-651): every SparseLinear gets its HARD mask
+    multiplied into the weight once and then runs ``dense_forward`` (a layer whose finalized
+    weight already carries the zeros is not multiplied twice). With ``use_slorb`` the layer stays
+    in ``sparse_forward`` and only its mask is made binary, as in the reference.
+    ``compressed=True`` goes one step further than the reference: bf16 layers are stored in the
+    2:4 compressed form and run on the sparse tensor cores (``SparseLinear.compress_for_inference``)."""
+    optimized = total = 0
+    for m in _sparse_modules(get_raw_model(model)):
+        total += 1
+        soft = m.mask.data
+        binary = bool(torch.all((soft == 0) | (soft == 1)).item())
+        hard = soft if binary else m._hard_mask_from_soft(soft)
+        hard_w = hard.to(m.weight.dtype)
+        can_dense = not use_slorb
+        already = False
+        if can_dense and getattr(m, "_hardening_finalized", False):
+            wz = float((m.weight.data == 0).float().mean())
+            mz = float((hard_w == 0).float().mean())
+            already = wz >= mz - 1e-4
+        if not already:
+            if can_dense:
+                m.weight.data.mul_(hard_w)
+            else:
+                m.mask.data.copy_(hard.to(m.mask.dtype))
+        if can_dense:
+            if compressed and m.weight.dtype == torch.bfloat16 and m.in_features % 16 == 0:
+                m.mask.data.copy_(hard.to(m.mask.dtype))
+                m.compress_for_inference()
+            else:
+                m.mode = "dense_forward"
+        m._inference_optimized = True
+        m.invalidate_masked_weight()
+        optimized += 1
+    return model

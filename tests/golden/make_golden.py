@@ -15,6 +15,7 @@ ending in ``__bf16``. Nothing here is needed at test time except the ``.npz`` fi
 from __future__ import annotations
 
 import collections
+import json
 import os
 import sys
 
@@ -263,6 +264,101 @@ def case_block_sparse():
     save("block_sparse", d)
 
 
+class TinyMLP(torch.nn.Module):
+    """Two SparseLinear layers around a GELU (the shape of a GPT-2 MLP block, legacy/model.py:95-113)."""
+
+    def __init__(self, linear_cls, cfg, d_in=64, d_hid=128, d_out=64):
+        super().__init__()
+        self.fc1 = linear_cls(d_in, d_hid, sparselinear_config=cfg, bias=True)
+        self.fc2 = linear_cls(d_hid, d_out, sparselinear_config=cfg, bias=False)
+
+    def forward(self, x):
+        return self.fc2(torch.nn.functional.gelu(self.fc1(x)))
+
+
+TRAIN_LOOP_CFG = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
+                      sparsity_warmup_steps=0, mask_lr=0.2, beta=0.9, temp_init=1.0, temp_min=0.05,
+                      temp_decay=0.6, mask_hardening_start=2, mask_hardening_duration=3,
+                      mask_penalty_mode="structured_topn", srste_decay=2e-4)
+TRAIN_LOOP = dict(steps=6, lr=5e-3, betas=(0.9, 0.95), weight_decay=0.1, grad_clip=1.0, lambda_mid_max=0.3,
+                  lambda_mid_warmup=4, decay_ramp=3)
+
+
+def case_train_loop():
+    """Free-running training loop over a two-layer model in the reference's order
+    (legacy/main_llama.py:1997-2211): forward, loss + mid penalty, Hutchinson, backward, clip,
+    grad EMA, GradScaler.step(optimizer, decay=), calculate_model_mask; then the end-of-training
+    bake-in (legacy/main_llama.py:2552-2563) and the state dict a checkpoint would hold."""
+    torch.manual_seed(321)
+    hp = TRAIN_LOOP
+    cfg = ref_sm.SparseLinearConfig(**TRAIN_LOOP_CFG)
+    model = TinyMLP(ref_sm.SparseLinear, cfg)
+    with torch.no_grad():
+        model.fc1.weight.copy_(torch.randn(128, 64) * 0.15)
+        model.fc1.bias.copy_(torch.randn(128) * 0.05)
+        model.fc2.weight.copy_(torch.randn(64, 128) * 0.15)
+    ref_utils.initialize_model(model)
+    d = {}
+    for n, t in model.state_dict().items():
+        put(d, "init/" + n, t)
+    params = [model.fc1.weight, model.fc1.bias, model.fc2.weight]
+    opt = ref_adamw.AdamW(params, lr=hp["lr"], betas=hp["betas"], weight_decay=hp["weight_decay"],
+                          srste_decay=TRAIN_LOOP_CFG["srste_decay"])
+    scaler = torch.amp.GradScaler("cpu", enabled=False)
+    steps = hp["steps"]
+    X = torch.randn(steps, 4, 16, 64)
+    Yt = torch.randn(steps, 4, 16, 64)
+    put(d, "X", X); put(d, "Yt", Yt)
+    for it in range(steps):
+        out = model(X[it])
+        task = torch.nn.functional.mse_loss(out, Yt[it])
+        lam = hp["lambda_mid_max"] * min(1.0, it / hp["lambda_mid_warmup"])
+        loss = task + ref_utils.mid_penalty(model, lam)
+        probes = [rademacher(tuple(w.shape), 5000 + 10 * it + j, torch.float32) for j, w in
+                  enumerate((model.fc1.weight, model.fc2.weight))]
+        for j, v in enumerate(probes):
+            put(d, f"s{it}_probe{j}", v.to(torch.int8))
+        queue = [v.clone() for v in probes]
+        ref_utils._rademacher_like = lambda t, q=queue: q.pop(0)
+        ref_utils.update_hessian_hutchinson(model, loss)
+        scaler.scale(loss).backward()
+        scaler.unscale_(opt)
+        gnorm = torch.nn.utils.clip_grad_norm_(model.parameters(), hp["grad_clip"])
+        ref_utils.update_model_grad_ema(model, update_hessian_with_grad2=False)
+        decay = TRAIN_LOOP_CFG["srste_decay"] * min(1.0, (it + 1) / hp["decay_ramp"])
+        scaler.step(opt, decay=decay)
+        scaler.update()
+        opt.zero_grad(set_to_none=True)
+        ref_utils.calculate_model_mask(model, it, lambda_mid=lam)
+        put(d, f"s{it}_loss", float(loss.detach())); put(d, f"s{it}_task", float(task.detach())); put(d, f"s{it}_gnorm", float(gnorm))
+        put(d, f"s{it}_lambda_mid", lam); put(d, f"s{it}_decay", decay)
+        put(d, f"s{it}_flip", np.asarray(ref_utils.calculate_flip_rate(model), dtype=np.float64))
+        for ln, layer in (("fc1", model.fc1), ("fc2", model.fc2)):
+            put(d, f"s{it}_{ln}_W", layer.weight.data); put(d, f"s{it}_{ln}_mask", layer.mask.data)
+            put(d, f"s{it}_{ln}_H", layer.hessian_diag.data); put(d, f"s{it}_{ln}_hx", float(layer.hardening_x))
+        put(d, f"s{it}_fc1_b", model.fc1.bias.data)
+    # end-of-training bake-in, the non-sharded branch
+    with torch.no_grad():
+        for layer in (model.fc1, model.fc2):
+            hard = layer._hard_mask_from_soft(layer.mask).detach()
+            layer.mask.copy_(hard)
+            layer.weight.mul_(layer.mask)
+            layer.change_mask = False
+            layer._hardening_finalized = True
+        Xe = torch.randn(3, 8, 64)
+        put(d, "eval_X", Xe); put(d, "eval_Y", model(Xe))
+    sd = model.state_dict()
+    d["state_keys"] = np.asarray(list(sd.keys()))
+    for n, t in sd.items():
+        put(d, "final/" + n, t)
+    opt_sd = opt.state_dict()
+    d["opt_state_keys"] = np.asarray(sorted(opt_sd["state"][0].keys()))
+    d["opt_group_keys"] = np.asarray(sorted(k for k in opt_sd["param_groups"][0].keys()))
+    d["cfg_json"] = np.asarray(json.dumps(TRAIN_LOOP_CFG))
+    d["hp_json"] = np.asarray(json.dumps(TRAIN_LOOP))
+    save("train_loop", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -281,6 +377,7 @@ if __name__ == "__main__":
                     temp_decay=0.5, mask_hardening_start=1, mask_hardening_duration=2, mask_penalty_lr=0.1,
                     mask_penalty_mode="nm_2_4", tau_sample_size=1024, sparsity_ratio=0.5),
                lambda_mid=0.1, seed=200, tau_idx_seed=900)
+    case_train_loop()
     case_penalty()
     case_ties()
     case_adamw()

@@ -1,0 +1,159 @@
+"""A free-running training loop over a two-layer model, the end-of-training bake-in, the checkpoint
+state dict and the inference bake-in, against a trajectory recorded from the reference
+(tests/golden/train_loop.npz; generator: tests/golden/make_golden.py, case_train_loop).
+
+The loop is the reference's (legacy/main_llama.py:1997-2211): forward, loss + mid penalty,
+Hutchinson, backward, clip, grad EMA, GradScaler.step(optimizer, decay=), calculate_model_mask.
+Nothing is reset between steps, so the tolerance is that of six accumulated fp32 steps.
+"""
+import json
+
+import pytest
+import torch
+
+from golden_io import Golden, rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+LOOP_TOL = 2e-4  # six free-running fp32 steps through GEMMs with another summation order
+
+
+class TinyMLP(torch.nn.Module):
+    def __init__(self, linear_cls, cfg, d_in=64, d_hid=128, d_out=64):
+        super().__init__()
+        self.fc1 = linear_cls(d_in, d_hid, sparselinear_config=cfg, bias=True)
+        self.fc2 = linear_cls(d_hid, d_out, sparselinear_config=cfg, bias=False)
+
+    def forward(self, x):
+        return self.fc2(torch.nn.functional.gelu(self.fc1(x)))
+
+
+def _build(g, prefix):
+    import sparseforge_b200 as sf
+
+    cfg = sf.SparseLinearConfig(**json.loads(str(g["cfg_json"])))
+    model = TinyMLP(sf.SparseLinear, cfg).to(DEV)
+    sd = {k: g[prefix + k].to(DEV) for k in [str(k) for k in g["state_keys"]]}
+    # the reference's keys, shapes and dtypes load with strict=True
+    missing, unexpected = model.load_state_dict(sd, strict=True)
+    assert not missing and not unexpected
+    assert list(model.state_dict().keys()) == [str(k) for k in g["state_keys"]]
+    for k, v in model.state_dict().items():
+        assert tuple(v.shape) == tuple(g[prefix + k].shape), k
+    return model, cfg
+
+
+def _hard_agreement(a, b):
+    return float((a.cpu() == b.cpu()).float().mean())
+
+
+def test_training_loop_follows_the_reference():
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("train_loop")
+    hp = json.loads(str(g["hp_json"]))
+    cfgd = json.loads(str(g["cfg_json"]))
+    model, _ = _build(g, "init/")
+    U.initialize_model(model)
+    opt = sf.AdamW([model.fc1.weight, model.fc1.bias, model.fc2.weight], lr=hp["lr"], betas=tuple(hp["betas"]),
+                   weight_decay=hp["weight_decay"], srste_decay=cfgd["srste_decay"])
+    scaler = torch.amp.GradScaler("cuda", enabled=False)
+    X, Yt = g["X"].to(DEV), g["Yt"].to(DEV)
+    for it in range(hp["steps"]):
+        out = model(X[it])
+        task = torch.nn.functional.mse_loss(out, Yt[it])
+        lam = hp["lambda_mid_max"] * min(1.0, it / hp["lambda_mid_warmup"])
+        assert lam == pytest.approx(g.scalar(f"s{it}_lambda_mid"))
+        loss = task + U.mid_penalty(model, lam)
+        queue = [g[f"s{it}_probe{j}"].to(DEV).float() for j in range(2)]
+        U._rademacher_like = lambda t, q=queue: q.pop(0)
+        U.update_hessian_hutchinson(model, loss)
+        scaler.scale(loss).backward()
+        scaler.unscale_(opt)
+        gnorm = torch.nn.utils.clip_grad_norm_(model.parameters(), hp["grad_clip"])
+        U.update_model_grad_ema(model, update_hessian_with_grad2=False)
+        decay = cfgd["srste_decay"] * min(1.0, (it + 1) / hp["decay_ramp"])
+        scaler.step(opt, decay=decay)
+        scaler.update()
+        opt.zero_grad(set_to_none=True)
+        U.calculate_model_mask(model, it, lambda_mid=lam)
+
+        assert float(loss.detach()) == pytest.approx(g.scalar(f"s{it}_loss"), rel=LOOP_TOL)
+        assert float(gnorm) == pytest.approx(g.scalar(f"s{it}_gnorm"), rel=LOOP_TOL)
+        for ln, layer in (("fc1", model.fc1), ("fc2", model.fc2)):
+            assert layer.hardening_x == pytest.approx(g.scalar(f"s{it}_{ln}_hx"))
+            assert rel_err(layer.weight.data, g[f"s{it}_{ln}_W"]) <= LOOP_TOL, (it, ln)
+            assert rel_err(layer.hessian_diag.data, g[f"s{it}_{ln}_H"]) <= 5 * LOOP_TOL, (it, ln)
+            assert rel_err(layer.mask.data, g[f"s{it}_{ln}_mask"]) <= 5 * LOOP_TOL, (it, ln)
+        assert rel_err(model.fc1.bias.data, g[f"s{it}_fc1_b"]) <= LOOP_TOL
+        # flips: equal unless a near-tie of the soft mask is decided the other way
+        flipped = U.calculate_flip_rate(model)[0]
+        assert abs(flipped - g[f"s{it}_flip"][0].item()) <= 4, (it, flipped)
+
+    # optimizer state layout a resumed run would read
+    osd = opt.state_dict()
+    assert sorted(osd["state"][0].keys()) == [str(k) for k in g["opt_state_keys"]]
+    assert set(str(k) for k in g["opt_group_keys"]) <= set(osd["param_groups"][0].keys())
+
+    # end-of-training bake-in
+    U.finalize_hard_masks(model)
+    for ln, layer in (("fc1", model.fc1), ("fc2", model.fc2)):
+        assert _hard_agreement(layer.mask.data, g[f"final/{ln}.mask"]) >= 0.999
+        grp = layer.mask.data.view(layer.out_features, -1, 4).sum(-1)
+        assert torch.all(grp == 2)
+        assert torch.all((layer.weight.data == 0) | (layer.mask.data == 1))
+    with torch.no_grad():
+        Ye = model(g["eval_X"].to(DEV))
+    assert rel_err(Ye, g["eval_Y"]) <= 50 * LOOP_TOL  # a flipped near-tie moves one small weight in or out
+
+
+def test_reference_checkpoint_loads_and_bakes_in():
+    """The reference's finalized state dict loads key for key; the loaded model reproduces the
+    reference's output in all three inference forms: masked forward, dense bake-in
+    (legacy/eval_wiki_ppl.py:548-651) and the compressed 2:4 tensor-core form."""
+    from sparseforge_b200 import utils as U
+
+    g = Golden("train_loop")
+    Xe, want = g["eval_X"].to(DEV), g["eval_Y"]
+
+    def load():
+        model, _ = _build(g, "final/")
+        for m in model.modules():
+            if hasattr(m, "hardening_x"):  # what the reference's loader sets (eval_wiki_ppl.py:828-831)
+                m.hardening_x = 0.0
+                m._hardening_finalized = True
+        return model.eval()
+
+    model = load()
+    with torch.no_grad():
+        assert rel_err(model(Xe), want) <= 1e-5
+    W_before = model.fc1.weight.data.clone()
+    U.optimize_sparse_model_for_inference(model)
+    assert model.fc1.mode == "dense_forward" and model.fc2.mode == "dense_forward"
+    assert torch.equal(model.fc1.weight.data, W_before)  # the finalized weight is not masked twice
+    with torch.no_grad():
+        assert rel_err(model(Xe), want) <= 1e-5
+
+    # a checkpoint saved before the bake-in (soft masks, unmasked weights) gets the hard mask once
+    soft, _ = _build(g, "init/")
+    soft.fc1.mask.data.copy_(g["s3_fc1_mask"].to(DEV))
+    soft.fc1.weight.data.copy_(g["s3_fc1_W"].to(DEV))
+    hard = soft.fc1._hard_mask_from_soft(soft.fc1.mask.data)
+    U.optimize_sparse_model_for_inference(soft)
+    assert torch.equal(soft.fc1.weight.data, g["s3_fc1_W"].to(DEV) * hard)
+
+    # compressed form: bf16 weights on the sparse tensor cores
+    model16 = load().to(torch.bfloat16)
+    with torch.no_grad():
+        dense16 = model16(Xe.to(torch.bfloat16)).float()
+    U.optimize_sparse_model_for_inference(model16, compressed=True)
+    assert model16.fc1.mode == "sparse24_forward" and model16.fc2.mode == "sparse24_forward"
+    assert model16.fc1._sp_values.shape == (128, 32) and model16.fc1._sp_values.dtype == torch.bfloat16
+    with torch.no_grad():
+        sparse16 = model16(Xe.to(torch.bfloat16)).float()
+    assert rel_err(sparse16, dense16) <= 1e-2
+    assert rel_err(sparse16, want) <= 2e-2
+    with pytest.raises(RuntimeError):
+        model16.train()
+        model16(Xe.to(torch.bfloat16).requires_grad_(True))

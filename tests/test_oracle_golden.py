@@ -118,6 +118,64 @@ def test_chain_paper_recipe():
         assert torch.equal(O.hard_mask_from_soft(mask, "nm_2_4"), g[f"s{t}_hard"])
 
 
+def test_training_loop_replay():
+    """The oracle, free running, follows the reference's two-layer training loop step for step
+    (forward, mid penalty, Hutchinson double backward, clip, AdamW with SR-STE decay, mask update
+    with the top-N penalty pull, hardening) and ends in the same finalized state."""
+    import json
+
+    g = Golden("train_loop")
+    hp, cfg = json.loads(str(g["hp_json"])), json.loads(str(g["cfg_json"]))
+    W = {"fc1": g["init/fc1.weight"].clone(), "fc2": g["init/fc2.weight"].clone()}
+    b1 = g["init/fc1.bias"].clone()
+    mask = {k: torch.ones(W[k].shape) for k in W}
+    H = {k: torch.ones(W[k].shape) for k in W}
+    hx = {k: 1.0 for k in W}
+    st = {k: (torch.zeros_like(t), torch.zeros_like(t)) for k, t in (("fc1", W["fc1"]), ("b1", b1), ("fc2", W["fc2"]))}
+    tol = 1e-5
+    for it in range(hp["steps"]):
+        w1, w2, bb = W["fc1"].clone().requires_grad_(True), W["fc2"].clone().requires_grad_(True), b1.clone().requires_grad_(True)
+        h = O.MaskedLinearSTE.apply(g["X"][it], w1, bb, O.effective_mask(mask["fc1"], hx["fc1"]))
+        out = O.MaskedLinearSTE.apply(torch.nn.functional.gelu(h), w2, None, O.effective_mask(mask["fc2"], hx["fc2"]))
+        lam = hp["lambda_mid_max"] * min(1.0, it / hp["lambda_mid_warmup"])
+        loss = torch.nn.functional.mse_loss(out, g["Yt"][it]) + O.mid_penalty_value(list(mask.values()), lam)
+        assert math.isclose(float(loss.detach()), g.scalar(f"s{it}_loss"), rel_tol=tol)
+        probes = [g[f"s{it}_probe{j}"].float() for j in range(2)]
+        hvps = O.hutchinson_hvps(loss, [w1, w2], probes)
+        for k, hv, pv in zip(("fc1", "fc2"), hvps, probes):
+            H[k] = O.hutchinson_accumulate(H[k], hv.detach(), pv, cfg["beta"])
+            assert rel_err(H[k], g[f"s{it}_{k}_H"]) <= tol
+        grads = torch.autograd.grad(loss, [w1, bb, w2])
+        grads, gnorm = O.clip_grad_norm(list(grads), hp["grad_clip"])
+        assert math.isclose(gnorm, g.scalar(f"s{it}_gnorm"), rel_tol=tol)
+        decay = cfg["srste_decay"] * min(1.0, (it + 1) / hp["decay_ramp"])
+        kw = dict(step=it + 1, lr=hp["lr"], betas=tuple(hp["betas"]), eps=1e-8, weight_decay=hp["weight_decay"])
+        W["fc1"], *st["fc1"] = O.adamw_step(W["fc1"], grads[0], *st["fc1"], mask=mask["fc1"], decay=decay, **kw)
+        b1, *st["b1"] = O.adamw_step(b1, grads[1], *st["b1"], **kw)
+        W["fc2"], *st["fc2"] = O.adamw_step(W["fc2"], grads[2], *st["fc2"], mask=mask["fc2"], decay=decay, **kw)
+        assert rel_err(b1, g[f"s{it}_fc1_b"]) <= tol
+        flips = 0
+        for k in ("fc1", "fc2"):
+            assert rel_err(W[k], g[f"s{it}_{k}_W"]) <= tol
+            T = O.temperature_at(it, cfg["temp_init"], cfg["temp_decay"], cfg["temp_min"])
+            G = O.gate_target_structured(O.normalize_scores(O.importance_score(W[k], "hessian_obd", H=H[k])), T)
+            new = O.mask_update(mask[k], G, mask_lr=cfg["mask_lr"], lambda_mid=lam, penalty_mode="structured_topn")
+            assert rel_err(new, g[f"s{it}_{k}_mask"]) <= tol
+            flips += O.flip_count(mask[k], new)
+            mask[k] = new
+            hx[k] = O.hardening_x(it, cfg["mask_hardening_start"], cfg["mask_hardening_duration"])
+            assert math.isclose(hx[k], g.scalar(f"s{it}_{k}_hx"), abs_tol=1e-12)
+        assert flips == int(g[f"s{it}_flip"][0])
+    # bake-in: mask <- top2(mask), weight *= mask (legacy/main_llama.py:2552-2563)
+    for k in ("fc1", "fc2"):
+        hard = O.hard_mask_from_soft(mask[k])
+        assert torch.equal(hard, g[f"final/{k}.mask"])
+        assert rel_err(W[k] * hard, g[f"final/{k}.weight"]) <= tol
+    h = O.linear_forward(g["eval_X"], g["final/fc1.weight"], g["final/fc1.mask"], bias=g["final/fc1.bias"])
+    Ye = O.linear_forward(torch.nn.functional.gelu(h), g["final/fc2.weight"], g["final/fc2.mask"])
+    assert rel_err(Ye, g["eval_Y"]) <= tol
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
