@@ -159,7 +159,36 @@ def run_ours(args):
     widths = sorted({c for _, _, c in shapes} | {r for _, r, _ in shapes})
     X = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
     dYfull = {w: torch.randn(T, w, device=dev, generator=gx).to(bf) for w in widths}
+    # a rank's upstream gradient is the column block of its own rows (what a split layer receives)
+    dYshard = {}
+    if world > 1:
+        for mt in mats:
+            dYshard[mt.name] = dYfull[mt.rows * world][:, rank * mt.rows:(rank + 1) * mt.rows].contiguous()
+        del dYfull
+        dYfull = None
     host_X = host_dY = None
+
+    # N > 1: the output all-gather and the input-gradient reduce-scatter are done by the GEMM
+    # epilogues through peer memory (two landing buffers each, alternating by matrix); NCCL only
+    # provides the barrier. --collective nccl keeps the library collectives instead.
+    arena, collective = None, "none"
+    if world > 1:
+        collective = args.collective
+        if collective == "p2p":
+            try:
+                from sparseforge_b200.sharding import PeerArena
+
+                wmax_ = max(widths)
+                buf_bytes = T * wmax_ * 2
+                arena = PeerArena(4 * buf_bytes, dev)
+            except Exception as e:  # no peer mapping on this box: say so and use the library collectives
+                print(f"[bench] peer memory unavailable ({e}); using NCCL collectives", file=sys.stderr, flush=True)
+                collective = "nccl"
+        flags = torch.tensor([1 if collective == "p2p" else 0], device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        if int(flags) == 0 and collective == "p2p":
+            arena.close()
+            arena, collective = None, "nccl"
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     decay_t = 0.05 ** (1.0 / 9.0)
     launches = 0
@@ -174,9 +203,9 @@ def run_ours(args):
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(stage_free[b])
             xs = stage_x[b][: T * mt.cols].view(T, mt.cols)
-            dys = stage_dy[b][: T * mt.rows * world].view(T, mt.rows * world)
+            dys = stage_dy[b][: T * mt.rows].view(T, mt.rows)
             xs.copy_(host_X[mt.cols], non_blocking=True)
-            dys.copy_(host_dY[mt.rows * world], non_blocking=True)
+            dys.copy_(host_dY[mt.name], non_blocking=True)
             ready = torch.cuda.Event()
             ready.record(copy_stream)
         return xs, dys, ready
@@ -190,12 +219,11 @@ def run_ours(args):
             if e2e:
                 # inputs of this matrix arrive from pinned host memory on the copy stream while the
                 # previous matrix computes; the next matrix's copy is queued before this one's kernels
-                x, dy_full, ready = pending
+                x, dy, ready = pending
                 pending = prefetch(i + 1) if i + 1 < len(mats) else None
                 torch.cuda.current_stream().wait_event(ready)
             else:
-                x, dy_full = X[mt.cols], dYfull[mt.rows * world]
-            dy = dy_full if world == 1 else dy_full[:, rank * mt.rows:(rank + 1) * mt.rows].contiguous()
+                x, dy = X[mt.cols], (dYfull[mt.rows] if world == 1 else dYshard[mt.name])
 
             def timed(key, fn):
                 nonlocal launches
@@ -209,17 +237,31 @@ def run_ours(args):
                 launches += 1
                 return out
 
-            y = timed("gemm", lambda: ops.gemm_fwd(x, mt.wm, status=status))
             works = []
-            if world > 1:
-                # the collectives run on NCCL's own stream and overlap the next products
-                yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
-                works.append(dist.all_gather_into_tensor(yg, y, async_op=True))
-            dx = timed("gemm", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
-            if world > 1:
-                dxs = torch.empty(T // world, mt.cols, dtype=bf, device=dev)
-                works.append(dist.reduce_scatter_tensor(dxs, dx, async_op=True))
-            dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
+            if arena is not None:
+                b = i % 2
+                y_off, s_off = b * buf_bytes, (2 + b) * buf_bytes
+                rows_t = T // world
+                timed("gemm", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
+                                                             rank * mt.rows, status=status))
+                timed("gemm", lambda: ops.gemm_dgrad_reducescatter(
+                    dy, mt.wm, arena.ptrs(s_off + rank * rows_t * mt.cols * 2), status=status))
+                # the barrier between ranks runs beside the weight-gradient product
+                arrived = arena.barrier(async_op=True)
+                dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
+                arrived.wait()
+                timed("reduce", lambda: ops.reduce_slots(arena.view(s_off, (world, rows_t, mt.cols), bf)))
+            else:
+                y = timed("gemm", lambda: ops.gemm_fwd(x, mt.wm, status=status))
+                if world > 1:
+                    # the collectives run on NCCL's own stream and overlap the next products
+                    yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
+                    works.append(dist.all_gather_into_tensor(yg, y, async_op=True))
+                dx = timed("gemm", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
+                if world > 1:
+                    dxs = torch.empty(T // world, mt.cols, dtype=bf, device=dev)
+                    works.append(dist.reduce_scatter_tensor(dxs, dx, async_op=True))
+                dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
             # the reference's order: Hutchinson sample into H, optimizer step, score of the NEW weight
             # (one pass over the matrix), then the mask update that consumes score and its statistics
             timed("optim", lambda: ops.adamw_masked_score(
@@ -264,12 +306,12 @@ def run_ours(args):
     part = timers.totals_ms()
 
     # end to end: the same step fed from pinned host buffers, stats read back every step
-    h2d = sum((T * c + T * r) * 2 for _, r, c in shapes)
+    h2d = sum((T * c + T * (r // world)) * 2 for _, r, c in shapes)
     d2h = len(shapes) * 8 * 8
     e2e_ms = float("nan")
     if not args.no_e2e:
         host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in shapes}}
-        host_dY = {w: dYfull[w].cpu().pin_memory() for w in {r for _, r, _ in shapes}}
+        host_dY = {mt.name: (dYfull[mt.rows] if world == 1 else dYshard[mt.name]).cpu().pin_memory() for mt in mats}
         wmax = max(widths)
         stage_x = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
         stage_dy = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
@@ -290,6 +332,8 @@ def run_ours(args):
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms, gemm_ms, optim_ms, mask_ms = [float(x) for x in times.cpu()]
+    if arena is not None:
+        arena.close()
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -308,7 +352,7 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
-                   "tokens": T, "row_sharded_over": world, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
+                   "tokens": T, "row_sharded_over": world, "collective": collective, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
         "clocks": clocks,
         "e2e": None if args.no_e2e else {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2),
                                          "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -468,6 +512,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: exchange through the GEMM epilogues and peer memory (p2p) or NCCL collectives")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")

@@ -262,6 +262,43 @@ SF_API int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t
 SF_API int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t out, void* stream);
 
 /*
+ * Row-sharded layer: the two products whose result has to cross GPUs, with the exchange done by
+ * the GEMM epilogue itself (plain stores into the other GPUs' memory over NVLink) instead of a
+ * collective that re-reads the result afterwards.
+ *   replaces: the all-gather of the layer output and the reduce-scatter of the input gradient that
+ *             FSDP / tensor-parallel wrappers run around a split layer (the reference wraps the
+ *             model in FSDP, legacy/main_llama.py:603-621, and all-reduces through DDP otherwise).
+ * sf_masked_gemm_fwd_allgather: this rank holds rows [col_offset, col_offset + out_local) of the
+ *   weight; y_all[0..n_dest) are the FULL outputs [T, out_total] of every GPU (its own first or
+ *   anywhere), and each tile of this rank's columns is stored into all of them.
+ * sf_masked_gemm_dgrad_reducescatter: rank c owns token rows [c*T/n, (c+1)*T/n) of dX; slots[c] is
+ *   the slot [T/n, in] that rank c keeps for THIS rank's partial sums. After all ranks finished
+ *   (a barrier the caller provides), the owner adds its n slots with sf_reduce_slots.
+ * Both need T > 128 and bf16. Host arrays y_all / slots hold device pointers; peer pointers come from
+ * sf_peer_open. No call waits on another GPU: ordering between ranks is the caller's barrier.
+ */
+SF_API int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias, void* const* y_all,
+                                 int n_dest, int64_t T, int64_t in, int64_t out_local, int64_t out_total,
+                                 int64_t col_offset, float alpha, int dtype, int32_t* status, void* stream);
+SF_API int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks,
+                                       int64_t T, int64_t in, int64_t out_local, int dtype, int32_t* status,
+                                       void* stream);
+/* out[n] <- sum over g of slots[g*n .. g*n + n), fp32 accumulation in slot order. */
+SF_API int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_t n, int dtype, void* stream);
+
+/*
+ * Sharing a device buffer with the other processes of one node (one process per GPU) through CUDA
+ * IPC. sf_peer_export fills `handle` (sf_peer_handle_bytes() bytes) and the offset of `ptr` inside
+ * its allocation; the peer process passes both to sf_peer_open and gets a pointer valid on its own
+ * device, to be released with sf_peer_close(base). The buffer must come from cudaMalloc (PyTorch's
+ * default caching allocator does). No counterpart in the reference, which leaves this to NCCL.
+ */
+SF_API int sf_peer_handle_bytes(void);
+SF_API int sf_peer_export(const void* ptr, void* handle, int64_t* offset);
+SF_API int sf_peer_open(const void* handle, int64_t offset, void** base, void** ptr);
+SF_API int sf_peer_close(void* base);
+
+/*
  * Hard-2:4 compressed weights.
  *   replaces: the finalisation bake-in mask.copy_(hard); weight.mul_(mask),
  *             legacy/main_llama.py:2552-2563, and optimize_sparse_model_for_inference,

@@ -75,6 +75,55 @@ __device__ __forceinline__ void store_row_chunk(const uint32_t (&r)[32], __nv_bf
     }
 }
 
+// The same conversion kept in registers, so that one accumulator chunk can be stored to several
+// destinations (its own memory and peers' memory over NVLink).
+__device__ __forceinline__ void pack_row_chunk(const uint32_t (&r)[32], int col0, float alpha,
+                                               const __nv_bfloat16* __restrict__ bias, int N, uint4 (&pk)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        uint32_t w[4] = {0u, 0u, 0u, 0u};
+        const int col = col0 + j * 8;
+        if (col < N) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v0 = __uint_as_float(r[j * 8 + 2 * i]) * alpha;
+                float v1 = __uint_as_float(r[j * 8 + 2 * i + 1]) * alpha;
+                if (bias != nullptr) {
+                    v0 += __bfloat162float(bias[col + 2 * i]);
+                    v1 += __bfloat162float(bias[col + 2 * i + 1]);
+                }
+                __nv_bfloat162 h = __floats2bfloat162_rn(v0, v1);
+                w[i] = *reinterpret_cast<uint32_t*>(&h);
+            }
+        }
+        pk[j] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+__device__ __forceinline__ void store_packed_chunk(__nv_bfloat16* dst, int col0, int N, const uint4 (&pk)[4]) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+        if (col0 + j * 8 < N) *reinterpret_cast<uint4*>(dst + j * 8) = pk[j];
+}
+
+// Where the epilogue of a row-sharded product writes. DIST_LOCAL: the one output matrix D.
+// DIST_BROADCAST (output all-gather): every tile goes to all `count` destinations, each the full
+// [M, ld] output of one GPU, at column offset col_off (this shard's columns).
+// DIST_SCATTER (input-gradient reduce-scatter): rows [c*rows_per, (c+1)*rows_per) go to ptr[c], the
+// slot GPU c keeps for this GPU's partial sums ([rows_per, ld]); the owner adds the slots up.
+// Peer pointers are plain global addresses mapped through CUDA IPC; the stores cross NVLink.
+constexpr int DIST_LOCAL = 0, DIST_BROADCAST = 1, DIST_SCATTER = 2;
+constexpr int DIST_EPI_ROW_BYTES = 128 + 16;                   // 64 bf16 columns + padding against bank conflicts
+constexpr int DIST_EPI_WARP_BYTES = 32 * DIST_EPI_ROW_BYTES;   // one turn buffer per epilogue warp
+constexpr int DIST_EPI_BYTES = 4 * DIST_EPI_WARP_BYTES;
+constexpr int MAX_PEERS = 8;
+struct PeerOut {
+    __nv_bfloat16* ptr[MAX_PEERS];
+    int64_t ld;
+    int64_t col_off;
+    int count;
+    int rows_per;
+};
+
 struct GemmSmemTail {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
@@ -266,11 +315,11 @@ struct PairSmemTail {
     int abort_flag;
 };
 
-template <int A_MN, int B_MN>
+template <int A_MN, int B_MN, int DIST = DIST_LOCAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
-                      float alpha, int M, int N, int K, int32_t* status) {
+                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -401,19 +450,61 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (!ok) break;
             ptx::tc_fence_after();
             const int row = m0 + q * 32 + lane;
-            __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
             const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
+            if (DIST == DIST_LOCAL) {
+                __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
-                ptx::tmem_ld_wait();
-                if (row < M) store_row_chunk(r, drow + c * 32, n0 + c * 32, N, alpha, bias);
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                    ptx::tmem_ld_wait();
+                    if (row < M) store_row_chunk(r, drow + c * 32, n0 + c * 32, N, alpha, bias);
+                }
+            } else {
+                // Stores that cross NVLink are not merged by the local L2, so the tile is turned in
+                // shared memory first: a thread holds one row, a warp store then covers four rows
+                // x 128 contiguous bytes (8 lanes x 16 B per row) in every destination.
+                uint8_t* ebuf = base_ptr + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * DIST_EPI_WARP_BYTES;
+                const int piece = lane & 7, rsub = lane >> 3;
+#pragma unroll 1
+                for (int c = 0; c < BN / 64; ++c) {
+                    uint32_t r[32];
+                    uint4 pk[4];
+                    __syncwarp();  // the previous chunk has been read out of ebuf
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 64 + h * 32), r);
+                        ptx::tmem_ld_wait();
+                        pack_row_chunk(r, n0 + c * 64 + h * 32, alpha, bias, N, pk);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + (h * 4 + j) * 16) = pk[j];
+                    }
+                    __syncwarp();
+                    const int col = n0 + c * 64 + piece * 8;
+#pragma unroll
+                    for (int rg = 0; rg < 8; ++rg) {
+                        const int rr = rg * 4 + rsub;
+                        const int orow = m0 + q * 32 + rr;
+                        const uint4 v = *reinterpret_cast<const uint4*>(ebuf + rr * DIST_EPI_ROW_BYTES + piece * 16);
+                        if (orow < M && col < N) {
+                            if (DIST == DIST_SCATTER) {
+                                const int owner = min(orow / po.rows_per, po.count - 1);
+                                *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v;
+                            } else {
+                                const int64_t off = (int64_t)orow * po.ld + po.col_off + col;
+                                for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v;
+                            }
+                        }
+                    }
+                }
             }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
         }
+        // stores to other GPUs' memory are made visible system-wide before the kernel ends
+        if (DIST != DIST_LOCAL) __threadfence_system();
     }
 
     ptx::tc_fence_before();
@@ -566,7 +657,7 @@ static bool use_pair_kernel() {
 template <int A_MN, int B_MN>
 static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldD,
                        const void* bias, float alpha, int64_t M, int64_t N, int64_t K, int32_t* status,
-                       cudaStream_t st) {
+                       cudaStream_t st, int dist = DIST_LOCAL, const PeerOut* peers = nullptr) {
     CUtensorMap tmA, tmB;
     int rc;
     if (A_MN) rc = make_bf16_tensor_map(&tmA, A, M, K, lda, 64);
@@ -578,18 +669,30 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (rc) return rc;
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
-    if (M > BM && use_pair_kernel()) {
-        auto pk = gemm_bf16_pair_kernel<A_MN, B_MN>;
-        static thread_local int pair_dev = -1;
-        if (pair_dev != dev) {
-            SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
-            pair_dev = dev;
-        }
+    if (dist != DIST_LOCAL && !pair)
+        return fail(SF_ERR_UNSUPPORTED, "the sharded epilogue needs more than %d rows and the CTA-pair kernel", BM);
+    if (pair) {
         const int64_t ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
         const int64_t max_pairs = sm_count() / 2;
         const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
-        pk<<<2 * pairs, GEMM_THREADS, PAIR_SMEM_BYTES, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD, (const __nv_bfloat16*)bias,
-                                                             alpha, (int)M, (int)N, (int)K, status);
+        const PeerOut none = {};
+#define SF_LAUNCH_PAIR(DISTV, SLOT)                                                                              \
+    do {                                                                                                         \
+        auto pk = gemm_bf16_pair_kernel<A_MN, B_MN, DISTV>;                                                      \
+        static thread_local int pair_dev[3] = {-1, -1, -1};                                                      \
+        const int smem_bytes = PAIR_SMEM_BYTES + (DISTV == DIST_LOCAL ? 0 : DIST_EPI_BYTES);                     \
+        if (pair_dev[SLOT] != dev) {                                                                             \
+            SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));    \
+            pair_dev[SLOT] = dev;                                                                                \
+        }                                                                                                        \
+        pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD,                        \
+                                                             (const __nv_bfloat16*)bias, alpha, (int)M, (int)N,  \
+                                                             (int)K, status, peers ? *peers : none);             \
+    } while (0)
+        if (dist == DIST_BROADCAST) SF_LAUNCH_PAIR(DIST_BROADCAST, 1);
+        else if (dist == DIST_SCATTER) SF_LAUNCH_PAIR(DIST_SCATTER, 2);
+        else SF_LAUNCH_PAIR(DIST_LOCAL, 0);
+#undef SF_LAUNCH_PAIR
         SF_CHECK_CUDA(cudaGetLastError());
         return SF_OK;
     }
@@ -669,6 +772,52 @@ int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int
     if (dtype == SF_F32)
         return launch_f32((const float*)dy, 1, out, (const float*)x, 1, in, (float*)dw, in, nullptr, 1.0f, out, in, T, st);
     return launch_bf16<1, 1>(dy, out, x, in, dw, in, nullptr, 1.0f, out, in, T, status, st);
+}
+
+static int fill_peers(const char* who, void* const* ptrs, int n_peers, PeerOut* po) {
+    if (!ptrs || n_peers < 1 || n_peers > MAX_PEERS)
+        return fail(SF_ERR_BAD_ARG, "%s: 1..%d destination pointers expected, got %d", who, MAX_PEERS, n_peers);
+    *po = PeerOut{};
+    for (int i = 0; i < n_peers; ++i) {
+        if (!ptrs[i] || !aligned16(ptrs[i])) return fail(SF_ERR_ALIGNMENT, "%s: destination %d is null or not 16-byte aligned", who, i);
+        po->ptr[i] = (__nv_bfloat16*)ptrs[i];
+    }
+    po->count = n_peers;
+    return SF_OK;
+}
+
+int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias, void* const* y_all, int n_dest,
+                                 int64_t T, int64_t in, int64_t out_local, int64_t out_total, int64_t col_offset,
+                                 float alpha, int dtype, int32_t* status, void* stream) {
+    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_fwd_allgather: bf16 only");
+    PeerOut po;
+    int rc = fill_peers("sf_masked_gemm_fwd_allgather", y_all, n_dest, &po);
+    if (rc) return rc;
+    rc = check_gemm_args("sf_masked_gemm_fwd_allgather", x, wm, y_all[0], T, in, out_local, dtype);
+    if (rc) return rc;
+    if (col_offset < 0 || col_offset % 8 || out_total % 8 || col_offset + out_local > out_total)
+        return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_fwd_allgather: columns [%lld, %lld) do not fit %lld (multiples of 8)",
+                    (long long)col_offset, (long long)(col_offset + out_local), (long long)out_total);
+    po.ld = out_total;
+    po.col_off = col_offset;
+    return launch_bf16<0, 0>(x, in, wm, in, nullptr, 0, bias, alpha, T, out_local, in, status, (cudaStream_t)stream,
+                             DIST_BROADCAST, &po);
+}
+
+int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks, int64_t T,
+                                       int64_t in, int64_t out_local, int dtype, int32_t* status, void* stream) {
+    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_dgrad_reducescatter: bf16 only");
+    PeerOut po;
+    int rc = fill_peers("sf_masked_gemm_dgrad_reducescatter", slots, n_ranks, &po);
+    if (rc) return rc;
+    rc = check_gemm_args("sf_masked_gemm_dgrad_reducescatter", dy, wm, slots[0], T, in, out_local, dtype);
+    if (rc) return rc;
+    if (T % n_ranks) return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_dgrad_reducescatter: T=%lld is not a multiple of %d ranks",
+                                 (long long)T, n_ranks);
+    po.ld = in;
+    po.rows_per = (int)(T / n_ranks);
+    return launch_bf16<0, 1>(dy, out_local, wm, in, nullptr, 0, nullptr, 1.0f, T, in, out_local, status,
+                             (cudaStream_t)stream, DIST_SCATTER, &po);
 }
 
 }  // extern "C"

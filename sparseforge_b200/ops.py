@@ -279,6 +279,77 @@ def sparse24_gemm(x2d, values, meta_tc, bias=None, status=None):
 
 
 # ----------------------------------------------------------------------------------------
+# row-sharded products whose epilogue delivers the result to the other GPUs
+# ----------------------------------------------------------------------------------------
+def _ptr_array(ptrs):
+    import ctypes
+
+    arr = (ctypes.c_void_p * len(ptrs))(*[int(p) for p in ptrs])
+    return arr
+
+
+def gemm_fwd_allgather(x2d, wm, dest_ptrs, out_total, col_offset, bias=None, alpha=1.0, status=None) -> None:
+    """Columns [col_offset, col_offset + wm.shape[0]) of the layer output, written by the GEMM
+    epilogue into every destination (device pointers to [T, out_total] bf16 buffers, one per GPU)."""
+    _cuda(x2d, wm, bias, status)
+    T, k = x2d.shape
+    out_local, k2 = wm.shape
+    if k != k2:
+        raise ValueError(f"gemm_fwd_allgather: x has {k} features, weight has {k2}")
+    arr = _ptr_array(dest_ptrs)
+    check(lib().sf_masked_gemm_fwd_allgather(_p(x2d), _p(wm), _p(bias), arr, len(dest_ptrs), T, k, out_local,
+                                             int(out_total), int(col_offset), float(alpha), _gemm_dtype(x2d, wm),
+                                             _p(status), _stream()), "sf_masked_gemm_fwd_allgather")
+
+
+def gemm_dgrad_reducescatter(dy2d, wm, slot_ptrs, status=None) -> None:
+    """Partial input gradient of this shard, token rows of rank c written into slot_ptrs[c] (the
+    [T/n, in] slot rank c keeps for this rank). The owner sums its slots with ``reduce_slots``."""
+    _cuda(dy2d, wm, status)
+    T, out_local = dy2d.shape
+    if wm.shape[0] != out_local:
+        raise ValueError(f"gemm_dgrad_reducescatter: dy has {out_local} columns, weight has {wm.shape[0]} rows")
+    arr = _ptr_array(slot_ptrs)
+    check(lib().sf_masked_gemm_dgrad_reducescatter(_p(dy2d), _p(wm), arr, len(slot_ptrs), T, wm.shape[1], out_local,
+                                                   _gemm_dtype(dy2d, wm), _p(status), _stream()),
+          "sf_masked_gemm_dgrad_reducescatter")
+
+
+def reduce_slots(slots, out=None):
+    """Sum over the leading axis of ``slots`` ([G, ...]) in slot order, fp32 accumulation."""
+    _cuda(slots, out)
+    G = slots.shape[0]
+    if out is None:
+        out = torch.empty(slots.shape[1:], dtype=slots.dtype, device=slots.device)
+    check(lib().sf_reduce_slots(_p(slots), _p(out), G, out.numel(), _dt(slots), _stream()), "sf_reduce_slots")
+    return out
+
+
+def peer_export(t: torch.Tensor):
+    """(handle bytes, byte offset) that another process of this node passes to ``peer_open``."""
+    import ctypes
+
+    _cuda(t)
+    buf = ctypes.create_string_buffer(int(lib().sf_peer_handle_bytes()))
+    off = ctypes.c_int64(0)
+    check(lib().sf_peer_export(_p(t), buf, ctypes.byref(off)), "sf_peer_export")
+    return bytes(buf.raw), int(off.value)
+
+
+def peer_open(handle: bytes, offset: int):
+    """Maps a buffer exported by another process; returns (base, pointer) as integers."""
+    import ctypes
+
+    base, ptr = ctypes.c_void_p(0), ctypes.c_void_p(0)
+    check(lib().sf_peer_open(ctypes.c_char_p(handle), int(offset), ctypes.byref(base), ctypes.byref(ptr)), "sf_peer_open")
+    return int(base.value), int(ptr.value)
+
+
+def peer_close(base: int) -> None:
+    check(lib().sf_peer_close(int(base)), "sf_peer_close")
+
+
+# ----------------------------------------------------------------------------------------
 # block-sparse-16
 # ----------------------------------------------------------------------------------------
 def bsr16_build(W, mask=None):

@@ -123,3 +123,58 @@ def shard_sparse_linear(full_weight: torch.Tensor, config, bias: Optional[torch.
             layer.bias.copy_(bias[lo:hi])
     layer.initialize()
     return RowShardedLinear(layer, group)
+
+
+class PeerArena:
+    """One device buffer per rank that every other rank of the node can store into: the landing
+    zone of the sharded GEMM epilogues (``ops.gemm_fwd_allgather`` / ``ops.gemm_dgrad_reducescatter``).
+
+    Each rank allocates ``nbytes``, exports it through CUDA IPC, and opens the buffers of the other
+    ranks; ``ptrs(offset)`` then lists, rank by rank, the address of the same byte offset in every
+    arena (its own memory for its own rank). One export per rank, so a process never opens an
+    allocation twice. ``barrier()`` orders ranks: what a rank stored before its barrier is in the
+    peers' memory once they have passed theirs."""
+
+    def __init__(self, nbytes: int, device, group=None):
+        from . import ops
+
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        handle, off = ops.peer_export(self.buf)
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, (handle, off), group=group)
+        self._bases, self._ptrs = [], []
+        for r, (h, o) in enumerate(gathered):
+            if r == self.rank:
+                self._ptrs.append(self.buf.data_ptr())
+            else:
+                base, ptr = ops.peer_open(h, o)
+                self._bases.append(base)
+                self._ptrs.append(ptr)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def ptrs(self, offset: int = 0):
+        if offset % 16:
+            raise ValueError("PeerArena offsets must be multiples of 16 bytes")
+        return [p + int(offset) for p in self._ptrs]
+
+    def view(self, offset: int, shape, dtype) -> torch.Tensor:
+        n = int(torch.tensor(shape).prod()) * torch.empty((), dtype=dtype).element_size()
+        return self.buf[offset:offset + n].view(dtype).view(*shape)
+
+    def barrier(self, async_op: bool = False):
+        """A one-element all-reduce ordered after the work already queued on the current stream.
+        With ``async_op`` the returned work's ``wait()`` makes the current stream wait for it, so
+        kernels queued in between run beside the barrier."""
+        return dist.all_reduce(self._flag, group=self.group, async_op=async_op)
+
+    def close(self):
+        from . import ops
+
+        torch.cuda.synchronize()
+        dist.barrier(group=self.group)
+        for b in self._bases:
+            ops.peer_close(b)
+        self._bases = []

@@ -258,3 +258,44 @@ def test_paper_recipe_mask_path():
         assert int(layer.weight.flipped_mask) == O.flip_count(prev.cpu(), layer.mask.data.cpu(), "nm_2_4")
         layer.mask.data.copy_(g[f"s{t}_mask"].to(DEV))
         assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"s{t}_hard"])
+
+
+@pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4)])
+def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
+    """The all-gather and reduce-scatter epilogues with every "rank" played in turn on one GPU: the
+    destinations are ordinary buffers of this GPU, so only the addressing is under test."""
+    torch.manual_seed(T + G)
+    bf = torch.bfloat16
+    out_total = out_local * G
+    x = torch.randn(T, in_f, device=DEV).to(bf)
+    wms = [(torch.randn(out_local, in_f, device=DEV) * 0.05).to(bf) for _ in range(G)]
+    dys = [torch.randn(T, out_local, device=DEV).to(bf) for _ in range(G)]
+    bias = [(torch.randn(out_local, device=DEV) * 0.1).to(bf) for _ in range(G)]
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+
+    # output all-gather: every rank's full output buffer ends up with all column blocks
+    y_all = [torch.full((T, out_total), float("nan"), device=DEV, dtype=bf) for _ in range(G)]
+    for r in range(G):
+        ops.gemm_fwd_allgather(x, wms[r], [y.data_ptr() for y in y_all], out_total, r * out_local, bias=bias[r],
+                               alpha=0.5, status=status)
+    want = torch.cat([ops.gemm_fwd(x, wms[r], bias[r], alpha=0.5) for r in range(G)], dim=1)
+    for y in y_all:
+        assert torch.equal(y, want)
+
+    # input-gradient reduce-scatter: slots[c][r] is rank c's slot for rank r's partial sums
+    rows = T // G
+    slots = [torch.full((G, rows, in_f), float("nan"), device=DEV, dtype=bf) for _ in range(G)]
+    for r in range(G):
+        ops.gemm_dgrad_reducescatter(dys[r], wms[r], [slots[c][r].data_ptr() for c in range(G)], status=status)
+    partial = [ops.gemm_dgrad(dys[r], wms[r]) for r in range(G)]
+    for c in range(G):
+        for r in range(G):
+            assert torch.equal(slots[c][r], partial[r][c * rows:(c + 1) * rows])
+        got = ops.reduce_slots(slots[c])
+        ref = sum(p[c * rows:(c + 1) * rows].float() for p in partial)
+        assert rel_err(got.float(), ref) <= 1e-2
+    assert int(status[0]) == 0
+    with pytest.raises(RuntimeError):
+        ops.gemm_fwd_allgather(x[:64], wms[0], [y_all[0].data_ptr()], out_total, 0)  # too few rows for the pair kernel
+    with pytest.raises(RuntimeError):
+        ops.gemm_fwd_allgather(x, wms[0], [y_all[0].data_ptr()], out_total, out_total)  # columns out of range

@@ -63,6 +63,30 @@ def _worker(rank, world, port, q):
             y2.backward(dY)
             ok = ok and rel(y2, y1) <= 1e-2 and rel(x2.grad, x1.grad) <= 1e-2
             ok = ok and rel(sharded.shard.weight.grad, full.weight.grad[lo:hi]) <= 1e-2
+        # the same exchange done by the GEMM epilogues through peer memory instead of NCCL
+        from sparseforge_b200 import ops
+        from sparseforge_b200.sharding import PeerArena
+
+        Tt, in2, out2 = 512, 256, 512
+        ol = out2 // world
+        xs = torch.randn(Tt, in2, generator=torch.Generator().manual_seed(5)).to(bf).to(dev)
+        wfull = (torch.randn(out2, in2, generator=torch.Generator().manual_seed(6)) * 0.05).to(bf).to(dev)
+        dyf = torch.randn(Tt, out2, generator=torch.Generator().manual_seed(7)).to(bf).to(dev)
+        y_bytes, slot_bytes = Tt * out2 * 2, Tt * in2 * 2
+        arena = PeerArena(y_bytes + slot_bytes, dev)
+        try:
+            wl = wfull[rank * ol:(rank + 1) * ol].contiguous()
+            dyl = dyf[:, rank * ol:(rank + 1) * ol].contiguous()
+            rows = Tt // world
+            ops.gemm_fwd_allgather(xs, wl, arena.ptrs(0), out2, rank * ol)
+            ops.gemm_dgrad_reducescatter(dyl, wl, arena.ptrs(y_bytes + rank * rows * in2 * 2))
+            arena.barrier()
+            y_full = arena.view(0, (Tt, out2), bf)
+            dx_mine = ops.reduce_slots(arena.view(y_bytes, (world, rows, in2), bf))
+            ok = ok and rel(y_full, ops.gemm_fwd(xs, wfull)) <= 1e-2
+            ok = ok and rel(dx_mine, ops.gemm_dgrad(dyf, wfull)[rank * rows:(rank + 1) * rows]) <= 1e-2
+        finally:
+            arena.close()
         flips = torch.tensor([int(sharded.shard.weight.flipped_mask)], device=dev)
         dist.all_reduce(flips)
         ok = ok and abs(int(flips) - int(full.weight.flipped_mask)) <= 2
