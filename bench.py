@@ -245,7 +245,7 @@ def run_ours(args):
                 timed("gemm", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
                                                              rank * mt.rows, status=status))
                 timed("gemm", lambda: ops.gemm_dgrad_reducescatter(
-                    dy, mt.wm, arena.ptrs(s_off + rank * rows_t * mt.cols * 2), status=status))
+                    dy, mt.wm, arena.ptrs(s_off + rank * rows_t * mt.cols * 2), rank, status=status))
                 # the barrier between ranks runs beside the weight-gradient product
                 arrived = arena.barrier(async_op=True)
                 dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))

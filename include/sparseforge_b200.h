@@ -272,7 +272,8 @@ SF_API int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t
  *   weight; y_all[0..n_dest) are the FULL outputs [T, out_total] of every GPU (its own first or
  *   anywhere), and each tile of this rank's columns is stored into all of them.
  * sf_masked_gemm_dgrad_reducescatter: rank c owns token rows [c*T/n, (c+1)*T/n) of dX; slots[c] is
- *   the slot [T/n, in] that rank c keeps for THIS rank's partial sums. After all ranks finished
+ *   the slot [T/n, in] that rank c keeps for THIS rank's partial sums (`rank` = this rank's index:
+ *   the tiles are walked owner by owner in turn, starting after it). After all ranks finished
  *   (a barrier the caller provides), the owner adds its n slots with sf_reduce_slots.
  * Both need T > 128 and bf16. Host arrays y_all / slots hold device pointers; peer pointers come from
  * sf_peer_open. No call waits on another GPU: ordering between ranks is the caller's barrier.
@@ -281,8 +282,8 @@ SF_API int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const voi
                                  int n_dest, int64_t T, int64_t in, int64_t out_local, int64_t out_total,
                                  int64_t col_offset, float alpha, int dtype, int32_t* status, void* stream);
 SF_API int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks,
-                                       int64_t T, int64_t in, int64_t out_local, int dtype, int32_t* status,
-                                       void* stream);
+                                       int rank, int64_t T, int64_t in, int64_t out_local, int dtype,
+                                       int32_t* status, void* stream);
 /* out[n] <- sum over g of slots[g*n .. g*n + n), fp32 accumulation in slot order. */
 SF_API int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_t n, int dtype, void* stream);
 

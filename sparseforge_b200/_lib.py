@@ -43,7 +43,7 @@ _SIGNATURES = {
     "sf_bias_grad": (c_int, [_P, c_int, _P, c_int64, c_int64, _P]),
     "sf_masked_gemm_fwd_allgather": (c_int, [_P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                              c_int, _P, _P]),
-    "sf_masked_gemm_dgrad_reducescatter": (c_int, [_P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_masked_gemm_dgrad_reducescatter": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_reduce_slots": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "sf_peer_handle_bytes": (c_int, []),
     "sf_peer_export": (c_int, [_P, _P, _P]),

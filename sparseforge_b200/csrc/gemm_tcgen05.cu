@@ -122,7 +122,18 @@ struct PeerOut {
     int64_t col_off;
     int count;
     int rows_per;
+    int interleave;  // DIST_SCATTER: > 1 walks the tile rows owner by owner in turn (see interleave_rows)
+    int rot;         // ... starting with the owner after this rank
 };
+
+// Tile rows in raster order all belong to one owner for a long stretch, which would send the
+// kernel's whole NVLink traffic in one burst (and every rank to the same GPU at once). Walking
+// them owner by owner in turn, each rank starting at another owner, spreads the stores evenly
+// over the kernel's duration and over the destinations. A bijection when tiles_m % G == 0.
+__device__ __forceinline__ int interleave_rows(int tm, int tiles_m, int G, int rot) {
+    const int owner = (tm % G + rot) % G;
+    return owner * (tiles_m / G) + tm / G;
+}
 
 struct GemmSmemTail {
     uint64_t full[STAGES];
@@ -367,6 +378,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
             const int m0 = tm * 2 * BM + (int)cta * BM;       // this CTA's rows of A / D
             const int n0 = tn * BN + (int)cta * PAIR_BNH;     // this CTA's half of the B rows
             for (int kb = 0; kb < num_kb; ++kb) {
@@ -443,6 +455,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
             int tm, tn;
             tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
             const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN;
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
@@ -466,42 +479,59 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 // x 128 contiguous bytes (8 lanes x 16 B per row) in every destination.
                 uint8_t* ebuf = base_ptr + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * DIST_EPI_WARP_BYTES;
                 const int piece = lane & 7, rsub = lane >> 3;
+                // The accumulator reads of the next 64 columns are in flight while the stores of
+                // this chunk are issued; the accumulator is handed back to the MMA warp as soon as
+                // its last column has been read, before the last stores go out.
+                uint32_t ra[32], rb[32];
+                ptx::tmem_ld_32x32b_x32(taddr, ra);
+                ptx::tmem_ld_32x32b_x32(taddr + 32u, rb);
+                ptx::tmem_ld_wait();
 #pragma unroll 1
                 for (int c = 0; c < BN / 64; ++c) {
-                    uint32_t r[32];
-                    uint4 pk[4];
-                    __syncwarp();  // the previous chunk has been read out of ebuf
+                    uint4 pk[4], v[8];
+                    pack_row_chunk(ra, n0 + c * 64, alpha, bias, N, pk);
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 64 + h * 32), r);
-                        ptx::tmem_ld_wait();
-                        pack_row_chunk(r, n0 + c * 64 + h * 32, alpha, bias, N, pk);
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + j * 16) = pk[j];
+                    pack_row_chunk(rb, n0 + c * 64 + 32, alpha, bias, N, pk);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + (h * 4 + j) * 16) = pk[j];
-                    }
+                    for (int j = 0; j < 4; ++j)
+                        *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + (4 + j) * 16) = pk[j];
                     __syncwarp();
+#pragma unroll
+                    for (int rg = 0; rg < 8; ++rg)
+                        v[rg] = *reinterpret_cast<const uint4*>(ebuf + (rg * 4 + rsub) * DIST_EPI_ROW_BYTES + piece * 16);
+                    __syncwarp();  // ebuf may be overwritten by the next chunk
+                    if (c + 1 < BN / 64) {
+                        ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 64), ra);
+                        ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 64 + 32), rb);
+                    } else {
+                        ptx::tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+                    }
                     const int col = n0 + c * 64 + piece * 8;
 #pragma unroll
                     for (int rg = 0; rg < 8; ++rg) {
-                        const int rr = rg * 4 + rsub;
-                        const int orow = m0 + q * 32 + rr;
-                        const uint4 v = *reinterpret_cast<const uint4*>(ebuf + rr * DIST_EPI_ROW_BYTES + piece * 16);
+                        const int orow = m0 + q * 32 + rg * 4 + rsub;
                         if (orow < M && col < N) {
                             if (DIST == DIST_SCATTER) {
                                 const int owner = min(orow / po.rows_per, po.count - 1);
-                                *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v;
+                                *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v[rg];
                             } else {
                                 const int64_t off = (int64_t)orow * po.ld + po.col_off + col;
-                                for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v;
+                                for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v[rg];
                             }
                         }
                     }
+                    if (c + 1 < BN / 64) ptx::tmem_ld_wait();
                 }
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+            if (DIST == DIST_LOCAL) {
+                ptx::tc_fence_before();
+                __syncwarp();
+                if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
+            }
         }
         // stores to other GPUs' memory are made visible system-wide before the kernel ends
         if (DIST != DIST_LOCAL) __threadfence_system();
@@ -804,8 +834,9 @@ int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias
                              DIST_BROADCAST, &po);
 }
 
-int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks, int64_t T,
-                                       int64_t in, int64_t out_local, int dtype, int32_t* status, void* stream) {
+int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks, int rank,
+                                       int64_t T, int64_t in, int64_t out_local, int dtype, int32_t* status,
+                                       void* stream) {
     if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_dgrad_reducescatter: bf16 only");
     PeerOut po;
     int rc = fill_peers("sf_masked_gemm_dgrad_reducescatter", slots, n_ranks, &po);
@@ -814,8 +845,12 @@ int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* con
     if (rc) return rc;
     if (T % n_ranks) return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_dgrad_reducescatter: T=%lld is not a multiple of %d ranks",
                                  (long long)T, n_ranks);
+    if (rank < 0 || rank >= n_ranks) return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_dgrad_reducescatter: rank %d of %d", rank, n_ranks);
     po.ld = in;
     po.rows_per = (int)(T / n_ranks);
+    // whole 256-row tiles per owner: walk the owners in turn, starting after this rank
+    po.interleave = (T % ((int64_t)2 * BM * n_ranks) == 0) ? n_ranks : 1;
+    po.rot = (rank + 1) % n_ranks;
     return launch_bf16<0, 1>(dy, out_local, wm, in, nullptr, 0, nullptr, 1.0f, T, in, out_local, status,
                              (cudaStream_t)stream, DIST_SCATTER, &po);
 }

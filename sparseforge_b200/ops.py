@@ -302,7 +302,7 @@ def gemm_fwd_allgather(x2d, wm, dest_ptrs, out_total, col_offset, bias=None, alp
                                              _p(status), _stream()), "sf_masked_gemm_fwd_allgather")
 
 
-def gemm_dgrad_reducescatter(dy2d, wm, slot_ptrs, status=None) -> None:
+def gemm_dgrad_reducescatter(dy2d, wm, slot_ptrs, rank, status=None) -> None:
     """Partial input gradient of this shard, token rows of rank c written into slot_ptrs[c] (the
     [T/n, in] slot rank c keeps for this rank). The owner sums its slots with ``reduce_slots``."""
     _cuda(dy2d, wm, status)
@@ -310,7 +310,7 @@ def gemm_dgrad_reducescatter(dy2d, wm, slot_ptrs, status=None) -> None:
     if wm.shape[0] != out_local:
         raise ValueError(f"gemm_dgrad_reducescatter: dy has {out_local} columns, weight has {wm.shape[0]} rows")
     arr = _ptr_array(slot_ptrs)
-    check(lib().sf_masked_gemm_dgrad_reducescatter(_p(dy2d), _p(wm), arr, len(slot_ptrs), T, wm.shape[1], out_local,
+    check(lib().sf_masked_gemm_dgrad_reducescatter(_p(dy2d), _p(wm), arr, len(slot_ptrs), int(rank), T, wm.shape[1], out_local,
                                                    _gemm_dtype(dy2d, wm), _p(status), _stream()),
           "sf_masked_gemm_dgrad_reducescatter")
 

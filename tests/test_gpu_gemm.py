@@ -260,7 +260,7 @@ def test_paper_recipe_mask_path():
         assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"s{t}_hard"])
 
 
-@pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4)])
+@pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4), (2048, 264, 136, 4), (768, 64, 136, 2)])
 def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
     """The all-gather and reduce-scatter epilogues with every "rank" played in turn on one GPU: the
     destinations are ordinary buffers of this GPU, so only the addressing is under test."""
@@ -286,7 +286,7 @@ def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
     rows = T // G
     slots = [torch.full((G, rows, in_f), float("nan"), device=DEV, dtype=bf) for _ in range(G)]
     for r in range(G):
-        ops.gemm_dgrad_reducescatter(dys[r], wms[r], [slots[c][r].data_ptr() for c in range(G)], status=status)
+        ops.gemm_dgrad_reducescatter(dys[r], wms[r], [slots[c][r].data_ptr() for c in range(G)], r, status=status)
     partial = [ops.gemm_dgrad(dys[r], wms[r]) for r in range(G)]
     for c in range(G):
         for r in range(G):

@@ -79,7 +79,7 @@ def _worker(rank, world, port, q):
             dyl = dyf[:, rank * ol:(rank + 1) * ol].contiguous()
             rows = Tt // world
             ops.gemm_fwd_allgather(xs, wl, arena.ptrs(0), out2, rank * ol)
-            ops.gemm_dgrad_reducescatter(dyl, wl, arena.ptrs(y_bytes + rank * rows * in2 * 2))
+            ops.gemm_dgrad_reducescatter(dyl, wl, arena.ptrs(y_bytes + rank * rows * in2 * 2), rank)
             arena.barrier()
             y_full = arena.view(0, (Tt, out2), bf)
             dx_mine = ops.reduce_slots(arena.view(y_bytes, (world, rows, in2), bf))
