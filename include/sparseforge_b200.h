@@ -329,6 +329,22 @@ SF_API int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* me
                      void* y, int64_t T, int64_t in, int64_t out, int32_t* status, void* stream);
 
 /*
+ * The same product for T <= 128 activation rows with the K range of each 128-row weight tile split
+ * over several CTAs, so that a weight matrix with few tiles is streamed by all SMs (a 4096-row
+ * matrix has 32 tiles for 148 SMs). Each K range stores its fp32 partial sums in `workspace`
+ * (sf_sparse24_splitk_workspace_bytes(T, out) bytes, its first 64 KiB ZERO on first use: they hold
+ * the tiles' arrival tickets, which every call leaves at zero again, so the workspace serves the next call
+ * on the same stream). The last range to arrive adds the partial sums in K order, so the result
+ * does not depend on timing; it agrees with sf_sparse24_gemm to fp32 rounding before the bf16
+ * store. splits = 0 picks the factor; T > 128 ignores the workspace and runs sf_sparse24_gemm.
+ * No counterpart in the reference (dense semantics as sf_sparse24_gemm).
+ */
+SF_API int64_t sf_sparse24_splitk_workspace_bytes(int64_t T, int64_t out);
+SF_API int sf_sparse24_gemm_splitk(const void* x, const void* values, const uint8_t* meta_tc, const void* bias,
+                            void* y, int64_t T, int64_t in, int64_t out, void* workspace,
+                            int64_t workspace_bytes, int splits, int32_t* status, void* stream);
+
+/*
  * Block-sparse-16 (block-CSR) weights.
  *   replaces: convert_to_block_sparse, legacy/triton_block_sparse.py:46-103 (same layout:
  *             blocks[nnz,16,16], row_ptr[out/16+1] int32, col_idx[nnz] int32; a block is

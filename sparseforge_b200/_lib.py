@@ -54,6 +54,8 @@ _SIGNATURES = {
     "sf_sparse24_meta_tc_bytes": (c_int64, [c_int64, c_int64]),
     "sf_sparse24_pack_meta": (c_int, [_P, _P, c_int64, c_int64, _P]),
     "sf_sparse24_gemm": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, _P, _P]),
+    "sf_sparse24_splitk_workspace_bytes": (c_int64, [c_int64, c_int64]),
+    "sf_sparse24_gemm_splitk": (c_int, [_P, _P, _P, _P, _P, c_int64, c_int64, c_int64, _P, c_int64, c_int, _P, _P]),
     "sf_bsr16_build": (c_int, [_P, _P, c_int, c_int, _P, _P, _P, _P, c_int64, c_int64, _P]),
     "sf_bsr16_to_dense": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int, _P]),
     "sf_bsr16_fwd": (c_int, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),

@@ -159,7 +159,11 @@ template <int BN>
 __global__ void __launch_bounds__(SP_THREADS, 1)
 sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const uint8_t* __restrict__ meta_tc, __nv_bfloat16* __restrict__ Y,
-                     const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status) {
+                     const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status,
+                     int splits, float* __restrict__ ws, int* __restrict__ counters) {
+    // splits > 1: a work unit is one K range of a tile. Unit s stores its fp32 partial sums into
+    // ws[s][T][out]; the unit that draws the last ticket of the tile adds the partial sums in the
+    // order s = 0, 1, ... (a fixed order, whoever arrives last), writes Y and resets the ticket.
     using C = SpCfg<BN>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -171,8 +175,10 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (out + SP_BM - 1) / SP_BM, tiles_n = (T + BN - 1) / BN;
-    const int total_tiles = tiles_m * tiles_n;
+    const int mn_tiles = tiles_m * tiles_n;
+    const int total_tiles = mn_tiles * splits;  // unit u: tile u % mn_tiles, K range u / mn_tiles
     const int num_kb = (in + SP_BK - 1) / SP_BK;
+    const int kb_per = (num_kb + splits - 1) / splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -205,8 +211,9 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
             int mt, nt;
-            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
-            for (int kb = 0; kb < num_kb; ++kb) {
+            sp_tile_coords(tile % mn_tiles, tiles_m, tiles_n, mt, nt);
+            const int kb0 = (tile / mn_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 11);
                 if (!ok) break;
                 if (lane == 0) {
@@ -237,7 +244,8 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-            for (int kb = 0; kb < num_kb; ++kb) {
+            const int kb0 = (tile / mn_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+            for (int kb = kb0; kb < kb1; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 12);
                 if (!ok) break;
                 ptx::tc_fence_after();
@@ -252,7 +260,7 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                         const uint64_t adesc = ptx::make_smem_desc(sa + k * 32, 16, 1024, 2);
                         const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * C::B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
                         ptx::mma_f16_ss_sp(tmem_d, adesc, bdesc, tmem_e + (uint32_t)(k & ~1), idesc | (uint32_t)(k & 1),
-                                           (kb | k) != 0 ? 1u : 0u);
+                                           (kb != kb0 || k != 0) ? 1u : 0u);
                     }
                     ptx::mma_commit(ptx::smem_u32(&tail->empty[stage]));
                 }
@@ -269,7 +277,8 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int t = 0;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
             int mt, nt;
-            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
+            const int mn = tile % mn_tiles;
+            sp_tile_coords(mn, tiles_m, tiles_n, mt, nt);
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 14);
@@ -286,16 +295,68 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 else tmem_ld_32x32b_x16(taddr + (uint32_t)(c * CH), r);
                 ptx::tmem_ld_wait();
                 if (o < out) {
+                    if (splits > 1) {
+                        // partial sums of unit s: ws[s][o][0..BN), a contiguous run per thread
+                        float4* dst = reinterpret_cast<float4*>(&ws[((int64_t)(tile / mn_tiles) * out + o) * BN + c * CH]);
 #pragma unroll
-                    for (int j = 0; j < CH; ++j) {
-                        const int tok = nt * BN + c * CH + j;
-                        if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                        for (int j = 0; j < CH / 4; ++j)
+                            __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < CH; ++j) {
+                            const int tok = nt * BN + c * CH + j;
+                            if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                        }
                     }
                 }
             }
             ptx::tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&tail->tmem_empty[acc]));
+            if (splits > 1) {
+                // Each warp owns 32 output features of the tile in every unit, so the ticket is per
+                // warp quarter: no barrier between warps. The warp that draws the last ticket sees
+                // the sums of all units (fence before the ticket, fence after it).
+                __threadfence();
+                __syncwarp();
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(&counters[mn * 4 + q], 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket == splits - 1) {
+                    __threadfence();
+                    if (o < out) {
+                        // sixteen tokens at a time, four 16-byte loads per unit in flight
+                        for (int tok0 = 0; tok0 < BN && tok0 < T; tok0 += 16) {
+                            float4 sum[4];
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) sum[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                            for (int sidx = 0; sidx < splits; ++sidx) {
+                                const float4* src = reinterpret_cast<const float4*>(&ws[((int64_t)sidx * out + o) * BN + tok0]);
+                                float4 part[4];
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) part[i] = __ldcg(src + i);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i) {
+                                    sum[i].x += part[i].x; sum[i].y += part[i].y; sum[i].z += part[i].z; sum[i].w += part[i].w;
+                                }
+                            }
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float v[4] = {sum[i].x, sum[i].y, sum[i].z, sum[i].w};
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const int tok = tok0 + 4 * i + e;
+                                    if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(v[e] + b);
+                                }
+                            }
+                        }
+                    }
+                    __syncwarp();
+                    if (lane == 0) counters[mn * 4 + q] = 0;
+                }
+            }
         }
     }
 
@@ -520,9 +581,29 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
     return SF_OK;
 }
 
+constexpr int SP_MAX_SPLITS = 8;
+// The arrival tickets sit at the head of the workspace in a region of fixed size, so that a
+// workspace reused for another matrix never has partial sums where tickets are expected.
+constexpr int64_t SP_TICKET_BYTES = 64 * 1024;
+static int64_t sp_ticket_bytes(int64_t) { return SP_TICKET_BYTES; }
+
+// Split-K factor for a product with few tiles: as many K ranges as fit in one wave of CTAs, at
+// least four K blocks each (measured on 4096-row matrices: 12.7 -> 8.6 us at 16 rows, K = 4096;
+// 38 -> 13 us at 16 rows and 44 -> 35 us at 128 rows, K = 11008; 17.5 -> 31 us at 128 rows, K = 4096). A matrix that already fills more than half of the SMs is not split
+// (it streams its weights at several TB/s as it is).
+static int choose_splits(int64_t tiles, int64_t num_kb, int64_t T) {
+    // beyond 32 rows the final sum over the partial results costs more than a short K loop saves
+    if (T > 32 && num_kb < 64) return 1;
+    int64_t s = sm_count() / (tiles > 0 ? tiles : 1);
+    if (s > SP_MAX_SPLITS) s = SP_MAX_SPLITS;
+    if (s > num_kb / 4) s = num_kb / 4;
+    return s < 2 ? 1 : (int)s;
+}
+
 template <int BN>
 static int launch_sparse(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
-                         int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st) {
+                         int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st, int splits = 1,
+                         float* ws = nullptr, int* counters = nullptr) {
     using C = SpCfg<BN>;
     CUtensorMap tmA, tmB;
     int rc = make_bf16_tensor_map(&tmA, values, in / 2, out, in / 2, SP_BM);
@@ -537,10 +618,10 @@ static int launch_sparse(const void* x, const void* values, const uint8_t* meta_
         SF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured_dev = dev;
     }
-    const int64_t tiles = ((out + SP_BM - 1) / SP_BM) * ((T + BN - 1) / BN);
+    const int64_t tiles = ((out + SP_BM - 1) / SP_BM) * ((T + BN - 1) / BN) * splits;
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     kern<<<grid, SP_THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, meta_tc, (__nv_bfloat16*)y, (const __nv_bfloat16*)bias,
-                                                  (int)out, (int)T, (int)in, status);
+                                                  (int)out, (int)T, (int)in, status, splits, ws, counters);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
@@ -593,8 +674,39 @@ int sf_sparse24_pack_meta(const uint8_t* meta, uint8_t* meta_tc, int64_t out, in
     return SF_OK;
 }
 
+int64_t sf_sparse24_splitk_workspace_bytes(int64_t T, int64_t out) {
+    if (T <= 0 || out <= 0 || T > 128) return 0;
+    // the tickets, then fp32 partial sums [splits][out][token tile of up to 128]
+    return sp_ticket_bytes(out) + (int64_t)SP_MAX_SPLITS * out * 128 * (int64_t)sizeof(float);
+}
+
+static int sparse24_gemm_impl(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
+                              int64_t T, int64_t in, int64_t out, void* workspace, int64_t workspace_bytes, int splits,
+                              int32_t* status, void* stream);
+
 int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y, int64_t T,
                      int64_t in, int64_t out, int32_t* status, void* stream) {
+    return sparse24_gemm_impl(x, values, meta_tc, bias, y, T, in, out, nullptr, 0, 1, status, stream);
+}
+
+int sf_sparse24_gemm_splitk(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
+                            int64_t T, int64_t in, int64_t out, void* workspace, int64_t workspace_bytes, int splits,
+                            int32_t* status, void* stream) {
+    SF_CHECK_ARG(splits >= 0 && splits <= SP_MAX_SPLITS, "sf_sparse24_gemm_splitk: splits must be 0 (choose) .. %d", SP_MAX_SPLITS);
+    if (T <= 128) {
+        SF_CHECK_ARG(((out + SP_BM - 1) / SP_BM) * 16 <= SP_TICKET_BYTES, "sf_sparse24_gemm_splitk: out=%lld has more tiles than tickets", (long long)out);
+        SF_CHECK_ARG(workspace != nullptr && aligned16(workspace), "sf_sparse24_gemm_splitk: workspace must be non-null and 16-byte aligned");
+        SF_CHECK_ARG(workspace_bytes >= sf_sparse24_splitk_workspace_bytes(T, out),
+                     "sf_sparse24_gemm_splitk: workspace of %lld bytes, %lld needed", (long long)workspace_bytes,
+                     (long long)sf_sparse24_splitk_workspace_bytes(T, out));
+    }
+    return sparse24_gemm_impl(x, values, meta_tc, bias, y, T, in, out, workspace, workspace_bytes, splits, status, stream);
+}
+
+static int sparse24_gemm_impl(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
+                              int64_t T, int64_t in, int64_t out, void* workspace, int64_t workspace_bytes, int splits,
+                              int32_t* status, void* stream) {
+    (void)workspace_bytes;
     SF_CHECK_ARG(x && values && meta_tc && y, "sf_sparse24_gemm: x, values, meta_tc, y must be non-null");
     SF_CHECK_ARG(T > 0 && in > 0 && out > 0, "sf_sparse24_gemm: T, in, out must be positive");
     if (in % 16 != 0)
@@ -604,10 +716,20 @@ int sf_sparse24_gemm(const void* x, const void* values, const uint8_t* meta_tc, 
     if (!(aligned16(x) && aligned16(values) && aligned16(meta_tc)))
         return fail(SF_ERR_ALIGNMENT, "sf_sparse24_gemm: x, values, meta_tc must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
-    if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st);
-    if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st);
-    if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st);
-    if (T <= 128) return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st);
+    if (T <= 128) {
+        const int64_t tiles_m = (out + SP_BM - 1) / SP_BM, num_kb = (in + SP_BK - 1) / SP_BK;
+        int S = 1;
+        if (workspace != nullptr) S = splits > 0 ? splits : choose_splits(tiles_m, num_kb, T);
+        if (S > num_kb) S = (int)num_kb;
+        // every unit needs at least one K block: (S - 1) * ceil(num_kb / S) < num_kb
+        while (S > 1 && (int64_t)(S - 1) * ((num_kb + S - 1) / S) >= num_kb) --S;
+        int* cnt = S > 1 ? (int*)workspace : nullptr;
+        float* ws = S > 1 ? (float*)((char*)workspace + sp_ticket_bytes(out)) : nullptr;
+        if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
+        if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
+        if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
+        return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
+    }
     // Pick the tiling that wastes fewer tile slots in its last wave; a CTA-pair tile does the same
     // work with about 1.3x less operand traffic, so it wins unless its wave fill is much worse.
     const int64_t sms = sm_count();

@@ -261,8 +261,22 @@ def sparse24_pack_meta(meta, out, k):
     return meta_tc
 
 
-def sparse24_gemm(x2d, values, meta_tc, bias=None, status=None):
-    """y[T,out] = x2d[T,in] @ decompress(values, meta)^T (+ bias) on the sparse tensor cores."""
+_SPLITK_WS = {}  # (device index, stream) -> zeroed workspace, left zeroed by every call
+
+
+def _splitk_workspace(device, nbytes):
+    key = (device.index, _stream())
+    ws = _SPLITK_WS.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _SPLITK_WS[key] = ws
+    return ws
+
+
+def sparse24_gemm(x2d, values, meta_tc, bias=None, status=None, splits=0):
+    """y[T,out] = x2d[T,in] @ decompress(values, meta)^T (+ bias) on the sparse tensor cores.
+    Up to 128 rows the K range of each weight tile is split over CTAs (``splits``: 0 = choose,
+    1 = off) with fp32 partial sums in a cached, self-cleaning workspace."""
     _cuda(x2d, values, meta_tc, bias, status)
     if x2d.dtype != torch.bfloat16 or values.dtype != torch.bfloat16:
         raise TypeError("sparse24_gemm: bfloat16 only")
@@ -272,6 +286,12 @@ def sparse24_gemm(x2d, values, meta_tc, bias=None, status=None):
         raise ValueError(f"sparse24_gemm: x has {k} features, compressed weight has {values.shape[1] * 2}")
     y = torch.empty((T, out), dtype=torch.bfloat16, device=x2d.device)
     if T == 0:
+        return y
+    if T <= 128 and splits != 1:
+        need = int(lib().sf_sparse24_splitk_workspace_bytes(T, out))
+        ws = _splitk_workspace(x2d.device, need)
+        check(lib().sf_sparse24_gemm_splitk(_p(x2d), _p(values), _p(meta_tc), _p(bias), _p(y), T, k, out, _p(ws),
+                                            ws.numel(), int(splits), _p(status), _stream()), "sf_sparse24_gemm_splitk")
         return y
     check(lib().sf_sparse24_gemm(_p(x2d), _p(values), _p(meta_tc), _p(bias), _p(y), T, k, out, _p(status), _stream()),
           "sf_sparse24_gemm")

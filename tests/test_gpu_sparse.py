@@ -96,6 +96,34 @@ def test_sparse24_gemm_bias(ops):
     assert rel_err(y, ref) <= BF16_TOL
 
 
+@pytest.mark.parametrize("T,k,n", [(1, 1024, 256), (16, 1152, 136), (100, 2048, 384), (128, 4096, 4096), (8, 11008, 4096)])
+@pytest.mark.parametrize("splits", [0, 2, 3, 5, 8])
+def test_sparse24_gemm_split_k(ops, T, k, n, splits):
+    """K ranges of a weight tile computed by several CTAs and summed in the fp32 workspace give the
+    unsplit result to fp32 rounding, with bias, and leave the workspace clean for the next call."""
+    torch.manual_seed(T + k + n)
+    W = (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    b = torch.randn(n, device=DEV).to(torch.bfloat16)
+    vals, meta = ops.sparse24_compress(W, W.float().abs())
+    meta_tc = ops.sparse24_pack_meta(meta, n, k)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    y1 = ops.sparse24_gemm(x, vals, meta_tc, bias=b, status=status, splits=1)
+    ref = x.float() @ ops.sparse24_decompress(vals, meta).float().t() + b.float()
+    for _ in range(3):  # the same workspace three times in a row
+        ys = ops.sparse24_gemm(x, vals, meta_tc, bias=b, status=status, splits=splits)
+        assert rel_err(ys, ref) <= BF16_TOL
+        # one bf16 ulp at most against the unsplit kernel (fp32 sums in another order)
+        assert float((ys.float() - y1.float()).abs().max()) <= 2.0 ** -7 * float(y1.float().abs().max())
+        if _ == 0:
+            first = ys.clone()
+        assert torch.equal(ys, first)  # the partial sums are added in K order, whoever arrives last
+    assert int(status[0]) == 0
+    # the arrival tickets at the head of the workspace are back at zero
+    ws = ops._SPLITK_WS[(torch.cuda.current_device(), torch.cuda.current_stream().cuda_stream)]
+    assert int(ws[: 64 * 1024].count_nonzero()) == 0
+
+
 # ---------------------------------------------------------------------------------------
 # block-sparse-16
 # ---------------------------------------------------------------------------------------
