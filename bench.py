@@ -42,6 +42,9 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 # algorithmic bytes per weight element at these dtypes (bf16 W/g/m/v/hvp, int8 probe, fp32 mask/H/score)
 # optimizer pass: W,m,v read+written (12), g (2), hvp (2), probe (1), mask (4), H read+written (8), score written (4)
 BYTES_OPTIM, BYTES_MASK = 33.0, 16.125
+# DRAM bytes (read + write) of one GEMM launch from the ncu capture of the q-shaped matrix
+# (mean of forward, dgrad, wgrad: 259.2 MB for 274.88 GFLOP), scaled to a launch by its FLOPs
+GEMM_TRAFFIC_PER_GFLOP = 259.2e6 / 274.88
 
 
 def layer_flops(T, rows, cols):
@@ -360,7 +363,9 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "achieved": round(gemm_tflops, 1) if gemm_tflops else None,
                      "peak": peaks["bf16_tflops_sustained"], "unit": "TFLOP/s",
                      "frac": round(gemm_tflops / peaks["bf16_tflops_sustained"], 4) if gemm_tflops else None,
-                     "traffic": None, "peak_source": peak_src + " (sustained bf16 GEMM)",
+                     "traffic": round(GEMM_TRAFFIC_PER_GFLOP * flops_step / world / (3 * len(shapes)) / 1e9),
+                     "traffic_source": "ncu capture of the q-shaped launches, scaled by FLOPs per launch (bytes)",
+                     "peak_source": peak_src + " (sustained bf16 GEMM)",
                      "kernel": f"gemm_bf16_pair_kernel (fwd, dgrad, wgrad: {3 * len(shapes)} launches per step)"},
         "passes": {
             "optim_score_gbs": gbs(BYTES_OPTIM, optim_ms),
