@@ -199,15 +199,25 @@ def run_ours(args):
     # end-to-end leg: two staging buffers per operand, filled from pinned host memory on a copy stream
     copy_stream = torch.cuda.Stream(device=dev)
     stage_free = [torch.cuda.Event(), torch.cuda.Event()]
-    stage_x = stage_dy = None
+    step_done = [torch.cuda.Event(), torch.cuda.Event()]
+    stage_xw = stage_dy = None
+    first_use = {}
+    for j_, mt_ in enumerate(mats):
+        first_use.setdefault(mt_.cols, j_)
 
-    def prefetch(j):
-        mt, b = mats[j], j % 2
+    def prefetch(j, it):
+        """Queues the host->device copies of matrix j's inputs on the copy stream. The activation
+        of a width is an input of the step, shared by the matrices of that width (q, k, v, o, gate,
+        up read the same 4096-wide tensor): it is copied once per step, into the buffer of the
+        step's parity; the upstream gradient is per matrix."""
+        mt, b, p = mats[j], j % 2, it % 2
         with torch.cuda.stream(copy_stream):
             copy_stream.wait_event(stage_free[b])
-            xs = stage_x[b][: T * mt.cols].view(T, mt.cols)
+            xs = stage_xw[mt.cols][p]
+            if first_use[mt.cols] == j:
+                copy_stream.wait_event(step_done[p])  # the step before last has finished with this buffer
+                xs.copy_(host_X[mt.cols], non_blocking=True)
             dys = stage_dy[b][: T * mt.rows].view(T, mt.rows)
-            xs.copy_(host_X[mt.cols], non_blocking=True)
             dys.copy_(host_dY[mt.name], non_blocking=True)
             ready = torch.cuda.Event()
             ready.record(copy_stream)
@@ -217,13 +227,13 @@ def run_ours(args):
         nonlocal launches
         temp = max(0.05, decay_t ** (it % 10))
         hx = max(0.0, min(1.0, 1.0 - ((it % 10) - 1) / 9.0)) if (it % 10) >= 1 else 1.0
-        pending = prefetch(0) if e2e else None
+        pending = prefetch(0, it) if e2e else None
         for i, mt in enumerate(mats):
             if e2e:
                 # inputs of this matrix arrive from pinned host memory on the copy stream while the
                 # previous matrix computes; the next matrix's copy is queued before this one's kernels
                 x, dy, ready = pending
-                pending = prefetch(i + 1) if i + 1 < len(mats) else None
+                pending = prefetch(i + 1, it) if i + 1 < len(mats) else None
                 torch.cuda.current_stream().wait_event(ready)
             else:
                 x, dy = X[mt.cols], (dYfull[mt.rows] if world == 1 else dYshard[mt.name])
@@ -279,6 +289,7 @@ def run_ours(args):
             if e2e:
                 stage_free[i % 2].record()
         if e2e:
+            step_done[it % 2].record()
             return torch.stack([mt.stats for mt in mats]).to("cpu", non_blocking=False)
         return None
 
@@ -309,18 +320,19 @@ def run_ours(args):
     part = timers.totals_ms()
 
     # end to end: the same step fed from pinned host buffers, stats read back every step
-    h2d = sum((T * c + T * (r // world)) * 2 for _, r, c in shapes)
+    h2d = sum(T * w * 2 for w in {c for _, _, c in shapes}) + sum(T * (r // world) * 2 for _, r, _ in shapes)
     d2h = len(shapes) * 8 * 8
     e2e_ms = float("nan")
     if not args.no_e2e:
         host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in shapes}}
         host_dY = {mt.name: (dYfull[mt.rows] if world == 1 else dYshard[mt.name]).cpu().pin_memory() for mt in mats}
         wmax = max(widths)
-        stage_x = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
+        stage_xw = {w: [torch.empty(T, w, dtype=bf, device=dev) for _ in range(2)] for w in host_X}
         stage_dy = [torch.empty(T * wmax, dtype=bf, device=dev) for _ in range(2)]
-        for ev in stage_free:
+        for ev in stage_free + step_done:
             ev.record()
         step(0, e2e=True)
+        step(1, e2e=True)
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
