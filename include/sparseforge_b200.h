@@ -165,6 +165,27 @@ SF_API int sf_mask_update_nm24(const float* score, const float* norm, const floa
                         int structured_exact, int score_bf16, void* stream);
 
 /*
+ * Joint mask update of a GLU gate / up pair: both layers are updated from ONE score, the sum of
+ * their importance scores, so that the same positions are pruned in both.
+ *   replaces: _update_glu_joint_mask legacy/utils.py:363-479 with _compute_joint_gate_target
+ *             :536-613 and _apply_mid_penalty_to_gate :616-643.
+ * sf_score_sum: out <- a + b (fp32 scores of the two layers, e.g. written by sf_hutch_score) with
+ *   norm <- (mean, population std + 1e-6) of out; scratch as for sf_hutch_score.
+ * sf_mask_update_nm24_joint: sf_mask_update_nm24 with the penalty pull taken from `pen_mask`
+ *   instead of the mask being updated (the reference forms the penalised gate once, from the
+ *   gate layer's mask, and applies it to both layers); pen_mask = NULL is sf_mask_update_nm24.
+ *   Call it once per layer with the joint score.
+ */
+SF_API int sf_score_sum(const float* a, const float* b, float* out, float* norm, double* scratch, int64_t n,
+                 void* stream);
+SF_API int sf_mask_update_nm24_joint(const float* score, const float* norm, const float* tau,
+                              const float* pen_mask, float* mask, const void* W, int w_dtype, void* wm,
+                              uint8_t* meta, double* stats, int64_t rows, int64_t cols, double temperature,
+                              double mask_lr, double pen, int penalty_mode, double beta_s,
+                              double binarize_decay, double hx, int structured_exact, int score_bf16,
+                              void* stream);
+
+/*
  * Hard top-2-of-4 projection along the input dimension.
  *   replaces: SparseLinear._hard_mask_from_soft 'nm_2_4' :578-603 and 'structured'
  *             :720-735, legacy/sparse_modeling.py; the inline copy at

@@ -191,6 +191,42 @@ def mask_update(mask, G, *, mask_lr, lambda_mid=0.0, pen_lr=None, penalty_mode="
     return mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0)
 
 
+def glu_joint_update(gate_score, up_score, gate_mask, up_mask, *, temperature, mask_lr, lambda_mid=0.0,
+                     pen_lr=None, penalty_mode="mid", binarize_decay=0.0, beta_s=0.0, exact=False):
+    """Joint update of a GLU gate / up pair, legacy/utils.py:363-479: one gate target from the
+    summed raw scores (:407-412, :536-613), the penalty pull taken from the GATE layer's mask
+    (:616-643; modes other than structured_topn / mid only clamp), the binarise push (:423-431),
+    then the same target moves both masks (:434-435). Returns (new gate mask, new up mask)."""
+    joint = gate_score + up_score
+    G = gate_target_structured(normalize_scores(joint).to(gate_mask.dtype), temperature, exact=exact, beta_s=beta_s)
+    a = float(mask_lr)
+    pen_lr = a if pen_lr is None else float(pen_lr)
+    if float(lambda_mid) != 0.0:
+        if penalty_mode == "structured_topn":
+            G = G - (pen_lr * float(lambda_mid)) * (gate_mask.to(G.dtype) - topn_indicator(G, 2, 4, dtype=G.dtype))
+        elif penalty_mode == "mid":
+            G = G - (pen_lr * float(lambda_mid)) * (1.0 - 2.0 * gate_mask).to(G.dtype)
+        G = G.clamp(0.0, 1.0)
+    d = float(binarize_decay)
+    if d != 0.0:
+        G = G.clone()
+        lt, gt = G < 0.5, G > 0.5
+        G[lt] = G[lt] * (1.0 - d)
+        G[gt] = G[gt] * (1.0 + d)
+    return (gate_mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0),
+            up_mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0))
+
+
+def beta_structural(step, start, end):
+    """legacy/sparse_modeling.py:966-985: smooth-step ramp of the structural mixing weight."""
+    if end <= start or step < start:
+        return 0.0
+    if step >= end:
+        return 1.0
+    t = float(step - start) / float(end - start)
+    return float(3.0 * t * t - 2.0 * t * t * t)
+
+
 def hardening_x(step, start, duration):
     """legacy/sparse_modeling.py:1603-1619."""
     if duration <= 0:

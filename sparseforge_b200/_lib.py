@@ -29,6 +29,9 @@ _SIGNATURES = {
     "sf_hutch_score_static": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_double, _P, _P, c_int64, c_double, c_int, _P]),
     "sf_mask_update_nm24": (c_int, [_P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_double, c_double,
                                     c_int, c_double, c_double, c_double, c_int, c_int, _P]),
+    "sf_mask_update_nm24_joint": (c_int, [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_double,
+                                          c_double, c_int, c_double, c_double, c_double, c_int, c_int, _P]),
+    "sf_score_sum": (c_int, [_P, _P, _P, _P, _P, c_int64, _P]),
     "sf_project_nm24": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int64, c_int64, _P]),
     "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_int, c_double, _P]),
     "sf_adamw_masked": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_double, c_double, c_double, c_double, c_double,

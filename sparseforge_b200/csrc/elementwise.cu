@@ -150,6 +150,41 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
     }
 }
 
+// out = a + b (the joint score of a gate / up pair) with this block's partial sums of out and out^2.
+__global__ void __launch_bounds__(kThreads)
+score_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ out,
+                 double* __restrict__ partials, int64_t chunks) {
+    double acc_s = 0.0, acc_s2 = 0.0;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
+        float x[8], y[8];
+        Vec8<float>::load(a + c * 8, x);
+        Vec8<float>::load(b + c * 8, y);
+        float ps = 0.0f, ps2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            x[i] = __fadd_rn(x[i], y[i]);
+            ps += x[i];
+            ps2 = fmaf(x[i], x[i], ps2);
+        }
+        Vec8<float>::store(out + c * 8, x);
+        acc_s += (double)ps;
+        acc_s2 += (double)ps2;
+    }
+    __shared__ double red[2][kThreads / 32];
+    acc_s = warp_sum(acc_s);
+    acc_s2 = warp_sum(acc_s2);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { red[0][wid] = acc_s; red[1][wid] = acc_s2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double sa = 0.0, sb = 0.0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) { sa += red[0][i]; sb += red[1][i]; }
+        partials[2 * blockIdx.x] = sa;
+        partials[2 * blockIdx.x + 1] = sb;
+    }
+}
+
 // One block folds the per-block partial sums in a fixed order (deterministic) and writes
 // mean and population std + 1e-6 as fp32.
 __global__ void __launch_bounds__(kThreads)
@@ -233,6 +268,7 @@ struct MaskUpdateParams {
     int structured_exact;
     int score_bf16;
     const float* tau;  // unstructured gate: threshold in normalised-score units (device); null = 2:4 gate
+    const float* pen_mask;  // mask the penalty pull is taken from (GLU joint update); null = the updated mask
 };
 
 __device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
@@ -322,18 +358,23 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
                 G[i] = gi;
             }
             if (penalty) {
+                float pm[4] = {mp[0], mp[1], mp[2], mp[3]};
+                if (P.pen_mask != nullptr) {
+                    const float4 t = __ldcs(reinterpret_cast<const float4*>(P.pen_mask + e + 4 * g));
+                    pm[0] = t.x; pm[1] = t.y; pm[2] = t.z; pm[3] = t.w;
+                }
                 if (P.penalty_mode == SF_PENALTY_TOPN) {
                     uint32_t kg[4];
                     top2_keep_masks(G, kg);
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        float delta = __fsub_rn(mp[i], __uint_as_float(kg[i] & 0x3f800000u));
+                        float delta = __fsub_rn(pm[i], __uint_as_float(kg[i] & 0x3f800000u));
                         G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, delta));
                     }
                 } else if (P.penalty_mode == SF_PENALTY_MID) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        float pg = __fsub_rn(1.0f, __fmul_rn(2.0f, mp[i]));
+                        float pg = __fsub_rn(1.0f, __fmul_rn(2.0f, pm[i]));
                         G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, pg));
                     }
                 }
@@ -732,14 +773,57 @@ static MaskUpdateParams make_mask_params(double temperature, double mask_lr, dou
     P.structured_exact = structured_exact;
     P.score_bf16 = score_bf16;
     P.tau = nullptr;
+    P.pen_mask = nullptr;
     return P;
 }
+
+static int mask_update_impl(const float* score, const float* norm, const float* tau, const float* pen_mask,
+                            float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats,
+                            int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
+                            int penalty_mode, double beta_s, double binarize_decay, double hx, int structured_exact,
+                            int score_bf16, void* stream);
 
 int sf_mask_update_nm24(const float* score, const float* norm, const float* tau, float* mask, const void* W,
                         int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
                         double temperature, double mask_lr, double pen, int penalty_mode, double beta_s,
                         double binarize_decay, double hx, int structured_exact, int score_bf16,
                         void* stream) {
+    return mask_update_impl(score, norm, tau, nullptr, mask, W, w_dtype, wm, meta, stats, rows, cols, temperature,
+                            mask_lr, pen, penalty_mode, beta_s, binarize_decay, hx, structured_exact, score_bf16, stream);
+}
+
+int sf_mask_update_nm24_joint(const float* score, const float* norm, const float* tau, const float* pen_mask,
+                              float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats,
+                              int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
+                              int penalty_mode, double beta_s, double binarize_decay, double hx,
+                              int structured_exact, int score_bf16, void* stream) {
+    if (pen_mask != nullptr && !aligned16(pen_mask))
+        return fail(SF_ERR_ALIGNMENT, "sf_mask_update_nm24_joint: pen_mask must be 16-byte aligned");
+    return mask_update_impl(score, norm, tau, pen_mask, mask, W, w_dtype, wm, meta, stats, rows, cols, temperature,
+                            mask_lr, pen, penalty_mode, beta_s, binarize_decay, hx, structured_exact, score_bf16, stream);
+}
+
+int sf_score_sum(const float* a, const float* b, float* out, float* norm, double* scratch, int64_t n, void* stream) {
+    SF_CHECK_ARG(a && b && out && norm && scratch, "sf_score_sum: a, b, out, norm, scratch must be non-null");
+    SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_score_sum: n=%lld must be a positive multiple of 8", (long long)n);
+    if (!(aligned16(a) && aligned16(b) && aligned16(out)))
+        return fail(SF_ERR_ALIGNMENT, "sf_score_sum: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t chunks = n / 8;
+    int grid = grid_one_wave((const void*)score_sum_kernel, chunks);
+    if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;
+    score_sum_kernel<<<grid, kThreads, 0, st>>>(a, b, out, scratch, chunks);
+    SF_CHECK_CUDA(cudaGetLastError());
+    score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+static int mask_update_impl(const float* score, const float* norm, const float* tau, const float* pen_mask,
+                            float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats,
+                            int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
+                            int penalty_mode, double beta_s, double binarize_decay, double hx, int structured_exact,
+                            int score_bf16, void* stream) {
     SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm24: score, norm, mask, stats must be non-null");
     SF_CHECK_ARG(rows > 0 && cols > 0, "sf_mask_update_nm24: rows=%lld cols=%lld must be positive",
                  (long long)rows, (long long)cols);
@@ -755,6 +839,7 @@ int sf_mask_update_nm24(const float* score, const float* norm, const float* tau,
     MaskUpdateParams P = make_mask_params(temperature, mask_lr, pen, penalty_mode, beta_s, binarize_decay,
                                           hx, structured_exact, score_bf16);
     P.tau = tau;
+    P.pen_mask = pen_mask;
     const int64_t chunks = rows * cols / 8;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
     const bool plain = !score_bf16 && !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0;

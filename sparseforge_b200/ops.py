@@ -70,10 +70,20 @@ def hutch_accumulate(H, hvp, v, *, beta=0.99) -> None:
                                hvp.numel(), float(beta), _lib.METRICS["hessian_obd"], _stream()), "sf_hutch_score")
 
 
+def score_sum(a, b, out, norm, scratch) -> None:
+    """out <- a + b (fp32 scores of a gate / up pair); norm <- (mean, std + 1e-6) of out."""
+    _cuda(a, b, out, norm, scratch)
+    if not (a.dtype == b.dtype == out.dtype == torch.float32) or a.numel() != b.numel() or a.numel() != out.numel():
+        raise TypeError("score_sum: a, b, out must be float32 tensors of one size")
+    check(lib().sf_score_sum(_p(a), _p(b), _p(out), _p(norm), _p(scratch), a.numel(), _stream()), "sf_score_sum")
+
+
 def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
                      pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
-                     structured_exact=False, score_bf16=False) -> None:
-    _cuda(score, norm, mask, stats, W, wm, meta, tau)
+                     structured_exact=False, score_bf16=False, pen_mask=None) -> None:
+    _cuda(score, norm, mask, stats, W, wm, meta, tau, pen_mask)
+    if pen_mask is not None and (pen_mask.dtype != torch.float32 or pen_mask.shape != mask.shape):
+        raise TypeError("mask_update_nm24: pen_mask must be a float32 tensor of the mask's shape")
     if tau is not None and tau.dtype != torch.float32:
         raise TypeError("mask_update_nm24: tau must be a float32 device scalar")
     if mask.dim() != 2:
@@ -83,6 +93,14 @@ def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, met
     if wm is not None and (W is None or wm.dtype != W.dtype):
         raise TypeError("mask_update_nm24: wm needs W of the same dtype")
     rows, cols = mask.shape
+    if pen_mask is not None:
+        check(lib().sf_mask_update_nm24_joint(_p(score), _p(norm), _p(tau), _p(pen_mask), _p(mask), _p(W),
+                                              _dt(W) if W is not None else SF_F32, _p(wm), _p(meta), _p(stats), rows,
+                                              cols, float(temperature), float(mask_lr), float(pen), int(penalty_mode),
+                                              float(beta_s), float(binarize_decay), float(hx),
+                                              int(bool(structured_exact)), int(bool(score_bf16)), _stream()),
+              "sf_mask_update_nm24_joint")
+        return
     check(lib().sf_mask_update_nm24(_p(score), _p(norm), _p(tau), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
                                     _p(wm), _p(meta), _p(stats), rows, cols, float(temperature), float(mask_lr),
                                     float(pen), int(penalty_mode), float(beta_s), float(binarize_decay), float(hx),

@@ -674,13 +674,13 @@ class SparseLinear(nn.Linear):
             tau = t / dist.get_world_size()
         return tau
 
-    def _gate_tau(self, step: int):
+    def _gate_tau(self, step: int, score: Optional[torch.Tensor] = None):
         """Device scalar with the unstructured gate's threshold in normalised-score units, or None for
         the structured gate. The quantile of the raw score sample is mapped through the same affine
         normalisation as the scores (a quantile commutes with it)."""
         if self.mask_type != "unstructured":
             return None
-        tau_raw = self._tau_unstructured(self._score, self._effective_sparsity(step),
+        tau_raw = self._tau_unstructured(self._score if score is None else score, self._effective_sparsity(step),
                                          getattr(self, "_tau_sample_idx", None))
         return ((tau_raw - self._norm[0]) / self._norm[1]).to(torch.float32).reshape(1).contiguous()
 
@@ -711,15 +711,22 @@ class SparseLinear(nn.Linear):
         if lam != 0.0 and mode not in ("mid", "structured_topn", "nm_2_4"):
             raise NotImplementedError(f"mask_penalty_mode={mode!r} is outside the 2:4 kernel path")
         pmode = _lib.PENALTY_MID if mode == "mid" else _lib.PENALTY_TOPN
-        hx_new = self._next_hardening_x(step)
-        ops.mask_update_nm24(self._score, self._norm, self.mask.data, self._stats, tau=self._gate_tau(step),
-                             W=self.weight.data, wm=self._wm,
-                             meta=self._meta, temperature=self._temperature(step), mask_lr=float(self.cfg.mask_lr),
-                             pen=float(self.mask_penalty_lr) * lam, penalty_mode=pmode if lam != 0.0 else 0,
-                             beta_s=self._beta_structural(step),
-                             binarize_decay=float(getattr(self.cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
-                             structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
-                             score_bf16=self._score_is_bf16())
+        self._launch_mask_update(self._score, self._norm, step, pen=float(self.mask_penalty_lr) * lam,
+                                 pmode=pmode if lam != 0.0 else 0, tau=self._gate_tau(step), owner=self,
+                                 score_bf16=self._score_is_bf16())
+
+    def _launch_mask_update(self, score, norm, step, *, pen, pmode, tau, owner, score_bf16=False, pen_mask=None):
+        """The fused update kernel on this layer's mask with the gate schedule (temperature, mask_lr,
+        beta mixing, binarise push, hardening) of ``owner`` (the layer itself, or the gate layer of a
+        GLU pair updated jointly)."""
+        cfg = owner.cfg
+        hx_new = owner._next_hardening_x(step)
+        ops.mask_update_nm24(score, norm, self.mask.data, self._stats, tau=tau, W=self.weight.data, wm=self._wm,
+                             meta=self._meta, temperature=owner._temperature(step), mask_lr=float(cfg.mask_lr),
+                             pen=pen, penalty_mode=pmode, beta_s=owner._beta_structural(step),
+                             binarize_decay=float(getattr(cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
+                             structured_exact=bool(getattr(cfg, "structured_exact", False)),
+                             score_bf16=score_bf16, pen_mask=pen_mask)
         self.hardening_x = hx_new
         self.last_mask_stats = self._stats
         self._wm_key = self._current_key()

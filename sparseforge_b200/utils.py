@@ -84,14 +84,79 @@ def update_mask_penalty_lr(model, step: int, max_steps: int, penalty_lr_min: flo
     return cur
 
 
+def _identify_glu_pairs(sparse_modules_dict):
+    """{gate name: up name} of the GLU pairs whose gate layer asks for a joint mask
+    (``...mlp.gate_proj`` / ``up_proj`` and ``...mlp.w1`` / ``w3``): legacy/utils.py:313-360."""
+    import re
+
+    pairs = {}
+    for pat, other in ((re.compile(r"(.+\.mlp)\.gate_proj$"), "up_proj"), (re.compile(r"(.+\.mlp)\.w1$"), "w3")):
+        for name, mod in sparse_modules_dict.items():
+            m = pat.match(name)
+            if m and f"{m.group(1)}.{other}" in sparse_modules_dict and getattr(mod.cfg, "glu_joint_mask", False):
+                pairs[name] = f"{m.group(1)}.{other}"
+    return pairs
+
+
+@torch.no_grad()
+def _update_glu_joint_mask(gate, up, step, lambda_mid):
+    """One mask update for a gate / up pair from the SUM of their importance scores
+    (legacy/utils.py:363-479): the gate layer's schedule (temperature, mask_lr, beta mixing,
+    binarise push, hardening) drives both, the penalised target is formed once from the gate
+    layer's mask, and both masks move towards it. Three kernels per pair beyond the two score
+    passes: the joint score with its statistics, and one fused update per layer."""
+    if (not gate.change_mask) or gate.mask_type == "none":
+        for m in (gate, up):
+            m.weight.flipped_mask = 0
+            m.weight.init_flipped_mask = 0
+        return
+    if step < int(gate.cfg.sparsity_warmup_steps):
+        return
+    if step % max(1, int(gate._mask_update_period(step))) != 0:
+        return
+    if gate.mask.shape != up.mask.shape:
+        import warnings
+
+        warnings.warn(f"[GLU Joint] Shape mismatch: gate={tuple(gate.mask.shape)}, up={tuple(up.mask.shape)}. "
+                      "Falling back to independent update.")
+        gate.update_mask(step, lambda_mid=lambda_mid)
+        up.update_mask(step, lambda_mid=lambda_mid)
+        return
+    for m in (gate, up):
+        m._check_mask_modes()
+        m._check_2to4()
+        m._refresh_score()
+    joint = getattr(gate, "_joint_score", None)
+    if joint is None or joint.shape != gate._score.shape or joint.device != gate._score.device:
+        joint = gate._joint_score = torch.empty_like(gate._score)
+    ops.score_sum(gate._score, up._score, joint, gate._norm, gate._scratch)
+    gate._combine_shard_norm()
+    lam = 0.0 if lambda_mid is None else float(lambda_mid)
+    mode = str(getattr(gate.cfg, "mask_penalty_mode", "mid") or "mid")
+    # the joint path knows the top-N pull and the mid pull; any other mode leaves the gate as it is
+    pmode = {"structured_topn": _lib.PENALTY_TOPN, "mid": _lib.PENALTY_MID}.get(mode, 0) if lam != 0.0 else 0
+    pen = float(gate.mask_penalty_lr) * lam if pmode else 0.0
+    tau = gate._gate_tau(step, joint)
+    # `up` first: its penalty pull reads the gate layer's mask as it was before this update
+    up._launch_mask_update(joint, gate._norm, step, pen=pen, pmode=pmode, tau=tau, owner=gate,
+                           pen_mask=gate.mask.data if pmode else None)
+    gate._launch_mask_update(joint, gate._norm, step, pen=pen, pmode=pmode, tau=tau, owner=gate)
+
+
 @torch.no_grad()
 def calculate_model_mask(model, step=0, lambda_mid: float = 0.0):
     """legacy/utils.py:183-310. The mask update of a layer is local to its rows, so no parameter is
-    gathered first (the reference summons every FSDP parameter here)."""
-    for m in _sparse_modules(model):
-        if getattr(m.cfg, "glu_joint_mask", False):
-            raise NotImplementedError("glu_joint_mask is outside the structured 2:4 kernel path")
-        m.update_mask(step, lambda_mid=lambda_mid)
+    gathered first (the reference summons every FSDP parameter here). GLU gate / up pairs whose
+    config sets ``glu_joint_mask`` get one joint update."""
+    named = {n: m for n, m in get_raw_model(model).named_modules() if isinstance(m, SparseLinear)}
+    handled = set()
+    if any(getattr(m.cfg, "glu_joint_mask", False) for m in named.values()):
+        for gname, uname in _identify_glu_pairs(named).items():
+            _update_glu_joint_mask(named[gname], named[uname], step, lambda_mid)
+            handled.update((gname, uname))
+    for n, m in named.items():
+        if n not in handled:
+            m.update_mask(step, lambda_mid=lambda_mid)
 
 
 @torch.no_grad()

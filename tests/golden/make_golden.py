@@ -359,6 +359,63 @@ def case_train_loop():
     save("train_loop", d)
 
 
+class _GLUMLP(torch.nn.Module):
+    def __init__(self, linear_cls, cfg, d=64, h=96):
+        super().__init__()
+        self.gate_proj = linear_cls(d, h, sparselinear_config=cfg, bias=False)
+        self.up_proj = linear_cls(d, h, sparselinear_config=cfg, bias=False)
+        self.down_proj = linear_cls(h, d, sparselinear_config=cfg, bias=False)
+
+
+class TinyGLU(torch.nn.Module):
+    """Module names as in a LLaMA block (``mlp.gate_proj / up_proj / down_proj``), which is what the
+    pair detection keys on (legacy/utils.py:313-360)."""
+
+    def __init__(self, linear_cls, cfg):
+        super().__init__()
+        self.block = torch.nn.Module()
+        self.block.mlp = _GLUMLP(linear_cls, cfg)
+        self.mlp = self.block.mlp
+
+
+GLU_VARIANTS = {
+    "topn": dict(mask_penalty_mode="structured_topn", mask_binarize_decay=0.05, beta_structural_start=0,
+                 beta_structural_end=4),
+    "mid": dict(mask_penalty_mode="mid"),
+    "nm24": dict(mask_penalty_mode="nm_2_4"),
+}
+GLU_BASE = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1, sparsity_warmup_steps=0,
+                mask_lr=0.25, temp_init=0.8, temp_min=0.05, temp_decay=0.7, mask_hardening_start=1,
+                mask_hardening_duration=2, mask_penalty_lr=0.2, glu_joint_mask=True)
+
+
+def case_glu_joint():
+    """calculate_model_mask on a gate / up / down triple with glu_joint_mask: the pair gets one
+    joint update from the summed scores (legacy/utils.py:363-479), down its own."""
+    d = {"variants": np.asarray(list(GLU_VARIANTS)), "base_json": np.asarray(json.dumps(GLU_BASE)),
+         "variants_json": np.asarray(json.dumps(GLU_VARIANTS))}
+    for tag, extra in GLU_VARIANTS.items():
+        torch.manual_seed(11 + len(tag))
+        cfg = ref_sm.SparseLinearConfig(**dict(GLU_BASE, **extra))
+        model = TinyGLU(ref_sm.SparseLinear, cfg)
+        ref_utils.initialize_model(model)
+        with torch.no_grad():
+            for n, m in (("gate", model.mlp.gate_proj), ("up", model.mlp.up_proj), ("down", model.mlp.down_proj)):
+                m.weight.copy_(torch.randn_like(m.weight) * 0.05)
+                m.hessian_diag.copy_(torch.rand_like(m.hessian_diag) + 0.1)
+                m.mask.copy_(torch.rand_like(m.mask))  # gate and up start from different masks
+                put(d, f"{tag}_{n}_W", m.weight.data); put(d, f"{tag}_{n}_H", m.hessian_diag.data)
+                put(d, f"{tag}_{n}_mask0", m.mask.data)
+        for step in range(3):
+            lam = 0.3 * (step + 1) / 3
+            ref_utils.calculate_model_mask(model, step, lambda_mid=lam)
+            put(d, f"{tag}_s{step}_lambda", lam)
+            for n, m in (("gate", model.mlp.gate_proj), ("up", model.mlp.up_proj), ("down", model.mlp.down_proj)):
+                put(d, f"{tag}_s{step}_{n}_mask", m.mask.data); put(d, f"{tag}_s{step}_{n}_hx", float(m.hardening_x))
+                put(d, f"{tag}_s{step}_{n}_flips", int(m.weight.flipped_mask))
+    save("glu_joint", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -378,6 +435,7 @@ if __name__ == "__main__":
                     mask_penalty_mode="nm_2_4", tau_sample_size=1024, sparsity_ratio=0.5),
                lambda_mid=0.1, seed=200, tau_idx_seed=900)
     case_train_loop()
+    case_glu_joint()
     case_penalty()
     case_ties()
     case_adamw()

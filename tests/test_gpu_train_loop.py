@@ -157,3 +157,61 @@ def test_reference_checkpoint_loads_and_bakes_in():
     with pytest.raises(RuntimeError):
         model16.train()
         model16(Xe.to(torch.bfloat16).requires_grad_(True))
+
+
+class _GLUMLP(torch.nn.Module):
+    def __init__(self, linear_cls, cfg, d=64, h=96):
+        super().__init__()
+        self.gate_proj = linear_cls(d, h, sparselinear_config=cfg, bias=False)
+        self.up_proj = linear_cls(d, h, sparselinear_config=cfg, bias=False)
+        self.down_proj = linear_cls(h, d, sparselinear_config=cfg, bias=False)
+
+
+class TinyGLU(torch.nn.Module):
+    def __init__(self, linear_cls, cfg):
+        super().__init__()
+        self.block = torch.nn.Module()
+        self.block.mlp = _GLUMLP(linear_cls, cfg)
+        self.mlp = self.block.mlp
+
+
+@pytest.mark.parametrize("tag", ["topn", "mid", "nm24"])
+def test_glu_joint_mask_follows_the_reference(tag):
+    """calculate_model_mask with glu_joint_mask: gate_proj / up_proj get one update from the summed
+    score (penalty pull from the gate layer's mask), down_proj its own (legacy/utils.py:183-479)."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("glu_joint")
+    cfgd = dict(json.loads(str(g["base_json"])), **json.loads(str(g["variants_json"]))[tag])
+    model = TinyGLU(sf.SparseLinear, sf.SparseLinearConfig(**cfgd)).to(DEV)
+    U.initialize_model(model)
+    layers = {"gate": model.mlp.gate_proj, "up": model.mlp.up_proj, "down": model.mlp.down_proj}
+    for n, m in layers.items():
+        m.weight.data.copy_(g[f"{tag}_{n}_W"].to(DEV))
+        m.hessian_diag.data.copy_(g[f"{tag}_{n}_H"].to(DEV))
+        m.mask.data.copy_(g[f"{tag}_{n}_mask0"].to(DEV))
+        m.invalidate_masked_weight()
+    assert U._identify_glu_pairs({n: m for n, m in model.named_modules() if isinstance(m, sf.SparseLinear)}) == \
+        {"block.mlp.gate_proj": "block.mlp.up_proj"}
+    for step in range(3):
+        prev = {n: m.mask.data.clone() for n, m in layers.items()}
+        U.calculate_model_mask(model, step, lambda_mid=g.scalar(f"{tag}_s{step}_lambda"))
+        for n, m in layers.items():
+            want = g[f"{tag}_s{step}_{n}_mask"]
+            assert rel_err(m.mask.data, want) <= 1e-5, (tag, step, n)
+            assert m.hardening_x == pytest.approx(g.scalar(f"{tag}_s{step}_{n}_hx"))
+            # the kernel's flip count is exact for the mask it produced; the reference's differs only
+            # where a near-tie of the new soft mask is decided the other way
+            hard_prev = m._hard_mask_from_soft(prev[n]) > 0.5
+            hard_now = m._hard_mask_from_soft(m.mask.data) > 0.5
+            assert int(m.weight.flipped_mask) == int((hard_prev ^ hard_now).sum())
+            assert abs(int(m.weight.flipped_mask) - g.scalar(f"{tag}_s{step}_{n}_flips")) <= 4
+            # continue from the reference's mask so that each step checks one update
+            m.mask.data.copy_(want.to(DEV))
+            m.invalidate_masked_weight()
+            # the masked weight written by the update belongs to the mask before the reset; rebuild
+            wm = m.masked_weight()
+            eff = m.mask.data * m.hardening_x + (1 - m.hardening_x) * m._hard_mask_from_soft(m.mask.data) \
+                if m.hardening_x < 1.0 else m.mask.data
+            assert rel_err(wm, m.weight.data * eff) <= 1e-5

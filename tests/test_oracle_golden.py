@@ -176,6 +176,37 @@ def test_training_loop_replay():
     assert rel_err(Ye, g["eval_Y"]) <= tol
 
 
+def test_glu_joint_mask_update():
+    """Gate / up pairs updated from the summed score, the third layer on its own."""
+    import json
+
+    g = Golden("glu_joint")
+    base, variants = json.loads(str(g["base_json"])), json.loads(str(g["variants_json"]))
+    for tag in [str(t) for t in g["variants"]]:
+        cfg = dict(base, **variants[tag])
+        W = {n: g[f"{tag}_{n}_W"] for n in ("gate", "up", "down")}
+        H = {n: g[f"{tag}_{n}_H"] for n in ("gate", "up", "down")}
+        mask = {n: g[f"{tag}_{n}_mask0"].clone() for n in ("gate", "up", "down")}
+        for step in range(3):
+            lam = g.scalar(f"{tag}_s{step}_lambda")
+            T = O.temperature_at(step, cfg["temp_init"], cfg["temp_decay"], cfg["temp_min"])
+            beta_s = O.beta_structural(step, cfg.get("beta_structural_start", 0), cfg.get("beta_structural_end", 0))
+            bd = cfg.get("mask_binarize_decay", 0.0)
+            sc = {n: O.importance_score(W[n], "hessian_obd", H=H[n]) for n in W}
+            new_gate, new_up = O.glu_joint_update(sc["gate"], sc["up"], mask["gate"], mask["up"], temperature=T,
+                                                  mask_lr=cfg["mask_lr"], lambda_mid=lam, pen_lr=cfg["mask_penalty_lr"],
+                                                  penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd, beta_s=beta_s)
+            G = O.gate_target_structured(O.normalize_scores(sc["down"]), T, beta_s=beta_s)
+            new_down = O.mask_update(mask["down"], G, mask_lr=cfg["mask_lr"], lambda_mid=lam, pen_lr=cfg["mask_penalty_lr"],
+                                     penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd)
+            for n, new in (("gate", new_gate), ("up", new_up), ("down", new_down)):
+                assert rel_err(new, g[f"{tag}_s{step}_{n}_mask"]) <= F32_TOL, (tag, step, n)
+                assert O.flip_count(mask[n], g[f"{tag}_s{step}_{n}_mask"]) == g.scalar(f"{tag}_s{step}_{n}_flips")
+                mask[n] = g[f"{tag}_s{step}_{n}_mask"].clone()
+                hx = O.hardening_x(step, cfg["mask_hardening_start"], cfg["mask_hardening_duration"])
+                assert math.isclose(hx, g.scalar(f"{tag}_s{step}_{n}_hx"), abs_tol=1e-12)
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
