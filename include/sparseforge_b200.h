@@ -256,6 +256,21 @@ SF_API int sf_adamw_masked_score(void* p, const void* g, const float* mask, void
 SF_API int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * Logging summary of the soft masks.
+ *   replaces: mask_stats legacy/utils.py:2069-2280 (the per-layer accumulation :2117-2154; the
+ *             caller adds layers up, all-reduces and forms mean / std / entropy / fractions).
+ * sf_mask_summary ADDS to out[0..12): count, sum m, sum m^2, sum of the binary entropy of
+ *   clamp(m, eps, 1-eps) (clamp in fp32, logarithms in fp64, as the reference's tensor ops),
+ *   counts m<0.5, m<0.1, m<0.01, m>0.9, m>0.99, m>0.5, sum of the m<0.5 entries, sum of the m>0.5
+ *   entries. Zero `out` before the first layer.
+ * sf_mask_sample_hist ADDS the histogram of mask[idx[0..take)) over `bins` equal bins of [0, 1]
+ *   (torch.histc) to hist[0..bins): the reference's quantiles come from a random sample per layer.
+ */
+SF_API int sf_mask_summary(const float* mask, int64_t n, double eps, double* out, void* stream);
+SF_API int sf_mask_sample_hist(const float* mask, const int64_t* idx, int64_t take, int bins, double* hist,
+                        void* stream);
+
+/*
  * Masked dense GEMMs (tcgen05 / TMEM / TMA, bf16 operands, fp32 accumulation).
  *   replaces: FusedMaskedLinearSTE.forward matmul, legacy/sparse_modeling.py:83-87,
  *             and .backward :105-129.

@@ -415,6 +415,43 @@ def bsr16_convert(W, mask, bs=16):
     return blocks, row_ptr, cols_i.to(torch.int32)
 
 
+def mask_log_stats(masks, sample_idx, bins=100, eps=1e-8):
+    """legacy/utils.py:2069-2280 for one process and no block-sparse layers: sums in fp64, the
+    entropy of clamp(m, eps, 1 - eps) (the clamp runs in the mask's dtype), quantiles from the
+    histogram of the sampled entries (the sample positions are an input)."""
+    import math
+
+    tot = sum_m = sum_m2 = ent = 0.0
+    cnt = {k: 0.0 for k in ("lt05", "lt01", "lt001", "gt90", "gt99", "gt05")}
+    s_lt = s_gt = 0.0
+    hist = torch.zeros(bins, dtype=torch.float64)
+    for m, idx in zip(masks, sample_idx):
+        md = m.double()
+        tot += m.numel()
+        sum_m += float(md.sum())
+        sum_m2 += float((md * md).sum())
+        mm = m.clamp(eps, 1 - eps).double()
+        ent += float((-(mm * mm.log()) - ((1 - mm) * (1 - mm).log())).sum())
+        cnt["lt05"] += float((m < 0.5).sum()); cnt["lt01"] += float((m < 0.1).sum()); cnt["lt001"] += float((m < 0.01).sum())
+        cnt["gt90"] += float((m > 0.9).sum()); cnt["gt99"] += float((m > 0.99).sum()); cnt["gt05"] += float((m > 0.5).sum())
+        s_lt += float(md[m < 0.5].sum()); s_gt += float(md[m > 0.5].sum())
+        hist += torch.histc(m.reshape(-1)[idx].float(), bins=bins, min=0.0, max=1.0).double()
+    mean = sum_m / tot
+    cdf = hist.cumsum(0) / (hist.sum() + 1e-12)
+
+    def q(p):
+        i = int(torch.searchsorted(cdf, torch.tensor([p], dtype=cdf.dtype)).item())
+        return (max(0, min(bins - 1, i)) + 0.5) / bins
+
+    return {"mask_mean": mean, "mask_std": math.sqrt(max(sum_m2 / tot - mean * mean, 0.0)), "mask_entropy": ent / tot,
+            "mask_hard_sparsity@0.5": cnt["lt05"] / tot, "mask_frac_lt_0.1": cnt["lt01"] / tot,
+            "mask_frac_lt_0.01": cnt["lt001"] / tot, "mask_frac_gt_0.9": cnt["gt90"] / tot,
+            "mask_frac_gt_0.99": cnt["gt99"] / tot, "mask_frac_gt_0.5": cnt["gt05"] / tot,
+            "mask_mean_lt_0.5": s_lt / cnt["lt05"] if cnt["lt05"] > 0 else 0.0,
+            "mask_mean_gt_0.5": s_gt / cnt["gt05"] if cnt["gt05"] > 0 else 0.0,
+            "mask_p10": q(0.10), "mask_p50": q(0.50), "mask_p90": q(0.90)}
+
+
 def to_numpy(t: torch.Tensor) -> np.ndarray:
     """bf16 tensors are stored as their raw uint16 bits."""
     t = t.detach().cpu().contiguous()

@@ -185,6 +185,62 @@ score_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, float
     }
 }
 
+// Summary of one soft mask for logging: twelve sums in fp64 (count, sum m, sum m^2, entropy with
+// the reference's fp32 clamp and fp64 logarithms, counts below 0.5 / 0.1 / 0.01 and above 0.9 /
+// 0.99 / 0.5, sums of the entries below and above 0.5), added to `out` with atomics.
+__global__ void __launch_bounds__(kThreads)
+mask_summary_kernel(const float* __restrict__ mask, int64_t n, float clamp_lo, float clamp_hi, double* __restrict__ out) {
+    double acc[12];
+#pragma unroll
+    for (int i = 0; i < 12; ++i) acc[i] = 0.0;
+    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
+        const float m = __ldcs(mask + i);
+        const double md = (double)m;
+        acc[0] += 1.0;
+        acc[1] += md;
+        acc[2] += md * md;
+        const double mm = (double)fminf(fmaxf(m, clamp_lo), clamp_hi);
+        acc[3] += -(mm * log(mm)) - ((1.0 - mm) * log(1.0 - mm));
+        acc[4] += m < 0.5f ? 1.0 : 0.0;
+        acc[5] += m < 0.1f ? 1.0 : 0.0;
+        acc[6] += m < 0.01f ? 1.0 : 0.0;
+        acc[7] += m > 0.9f ? 1.0 : 0.0;
+        acc[8] += m > 0.99f ? 1.0 : 0.0;
+        acc[9] += m > 0.5f ? 1.0 : 0.0;
+        acc[10] += m < 0.5f ? md : 0.0;
+        acc[11] += m > 0.5f ? md : 0.0;
+    }
+    __shared__ double red[12][kThreads / 32];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+#pragma unroll
+    for (int i = 0; i < 12; ++i) {
+        const double v = warp_sum(acc[i]);
+        if (lane == 0) red[i][wid] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < 12) {
+        double a = 0.0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) a += red[threadIdx.x][i];
+        atomicAdd(&out[threadIdx.x], a);
+    }
+}
+
+// Histogram of mask[idx[j]] over `bins` equal bins of [0, 1] (torch.histc: bin = trunc(x * bins),
+// x = 1 in the last bin, values outside [0, 1] dropped), added to `hist`.
+__global__ void __launch_bounds__(kThreads)
+mask_sample_hist_kernel(const float* __restrict__ mask, const int64_t* __restrict__ idx, int64_t take, int bins,
+                        double* __restrict__ hist) {
+    for (int64_t j = (int64_t)blockIdx.x * kThreads + threadIdx.x; j < take; j += (int64_t)gridDim.x * kThreads) {
+        const float x = mask[idx[j]];
+        if (x >= 0.0f && x <= 1.0f) {
+            int pos = (int)(__fmul_rn(__fdiv_rn(x, 1.0f), (float)bins));
+            if (pos > bins - 1) pos = bins - 1;
+            atomicAdd(&hist[pos], 1.0);
+        }
+    }
+}
+
 // One block folds the per-block partial sums in a fixed order (deterministic) and writes
 // mean and population std + 1e-6 as fp32.
 __global__ void __launch_bounds__(kThreads)
@@ -1017,6 +1073,29 @@ int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, 
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
     const int64_t groups = rows * cols / 4;
     mask_stats_kernel<<<grid_for(groups, 8), kThreads, 0, st>>>(mask, stats, groups);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_mask_summary(const float* mask, int64_t n, double eps, double* out, void* stream) {
+    SF_CHECK_ARG(mask && out, "sf_mask_summary: mask and out must be non-null");
+    SF_CHECK_ARG(n > 0, "sf_mask_summary: n must be positive");
+    // the clamp bounds are formed in fp32 as the tensor op forms them (1 - 1e-8 is 1 in fp32)
+    const float lo = (float)eps, hi = (float)(1.0 - eps);
+    int64_t blocks = (n + kThreads * 16 - 1) / (kThreads * 16);
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    if (blocks < 1) blocks = 1;
+    mask_summary_kernel<<<(int)blocks, kThreads, 0, (cudaStream_t)stream>>>(mask, n, lo, hi, out);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_mask_sample_hist(const float* mask, const int64_t* idx, int64_t take, int bins, double* hist, void* stream) {
+    SF_CHECK_ARG(mask && idx && hist, "sf_mask_sample_hist: mask, idx, hist must be non-null");
+    SF_CHECK_ARG(take > 0 && bins > 0, "sf_mask_sample_hist: take and bins must be positive");
+    int64_t blocks = (take + kThreads - 1) / kThreads;
+    if (blocks > 148 * 4) blocks = 148 * 4;
+    mask_sample_hist_kernel<<<(int)blocks, kThreads, 0, (cudaStream_t)stream>>>(mask, idx, take, bins, hist);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }

@@ -183,6 +183,23 @@ def mask_stats(mask, stats) -> None:
     check(lib().sf_mask_stats(_p(mask), _p(stats), rows, cols, _stream()), "sf_mask_stats")
 
 
+def mask_summary(mask, out, eps=1e-8) -> None:
+    """Adds the twelve logging sums of one soft mask to ``out`` (float64[12])."""
+    _cuda(mask, out)
+    if mask.dtype != torch.float32 or out.dtype != torch.float64 or out.numel() < 12:
+        raise TypeError("mask_summary: mask float32, out float64[12]")
+    check(lib().sf_mask_summary(_p(mask), mask.numel(), float(eps), _p(out), _stream()), "sf_mask_summary")
+
+
+def mask_sample_hist(mask, idx, hist) -> None:
+    """Adds the histogram of mask.flatten()[idx] over len(hist) equal bins of [0, 1] to ``hist`` (float64)."""
+    _cuda(mask, idx, hist)
+    if mask.dtype != torch.float32 or idx.dtype != torch.int64 or hist.dtype != torch.float64:
+        raise TypeError("mask_sample_hist: mask float32, idx int64, hist float64")
+    check(lib().sf_mask_sample_hist(_p(mask), _p(idx), idx.numel(), hist.numel(), _p(hist), _stream()),
+          "sf_mask_sample_hist")
+
+
 def _gemm_dtype(*ts) -> int:
     d = ts[0].dtype
     for t in ts:

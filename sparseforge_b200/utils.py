@@ -291,6 +291,72 @@ def nm_2_4_tile_stats(model, debug=False):
 
 
 @torch.no_grad()
+@torch.no_grad()
+def mask_stats(model, bins: int = 100, eps: float = 1e-8, sample_per_layer: int = 4096):
+    """Global statistics of the continuous masks (legacy/utils.py:2069-2280): mean, std, entropy,
+    fractions below / above thresholds, and p10 / p50 / p90 from a histogram of a random sample of
+    every layer. One read of each mask (one kernel) plus a gather of the sample; the sums are
+    all-reduced, so call it on every rank. The block statistics of the block-sparse modes are not
+    produced (those modes are outside this path)."""
+    mods = [m for m in _sparse_modules(model) if m.mask.numel() > 0]
+    device = mods[0].mask.device if mods else torch.device("cuda")
+    acc = torch.zeros(12, dtype=torch.float64, device=device)
+    hist = torch.zeros(int(bins), dtype=torch.float64, device=device)
+    for m in mods:
+        mk = m.mask.data
+        ops.mask_summary(mk, acc, eps)
+        take = min(mk.numel(), int(sample_per_layer))
+        if take > 0:
+            idx = torch.randint(0, mk.numel(), (take,), device=device)
+            ops.mask_sample_hist(mk, idx.to(torch.int64).contiguous(), hist)
+    _all_reduce(acc)
+    _all_reduce(hist)
+    a = [float(x) for x in acc.cpu()]
+    tot = a[0]
+    if tot <= 0:
+        return {"mask_mean": 1.0, "mask_std": 0.0, "mask_entropy": 0.0, "mask_hard_sparsity@0.5": 0.0,
+                "mask_frac_lt_0.1": 0.0, "mask_frac_lt_0.01": 0.0, "mask_p10": 1.0, "mask_p50": 1.0, "mask_p90": 1.0}
+    mean = a[1] / tot
+    std = math.sqrt(max(a[2] / tot - mean * mean, 0.0))
+    h = hist.cpu()
+
+    def q_from_hist(q):
+        if float(h.sum()) <= 0:
+            return mean
+        cdf = h.cumsum(0) / (h.sum() + 1e-12)
+        i = int(torch.searchsorted(cdf, torch.tensor([q], dtype=cdf.dtype)).item())
+        return float((max(0, min(int(bins) - 1, i)) + 0.5) / int(bins))
+
+    return {
+        "mask_mean": mean, "mask_std": std, "mask_entropy": a[3] / tot, "mask_hard_sparsity@0.5": a[4] / tot,
+        "mask_frac_lt_0.1": a[5] / tot, "mask_frac_lt_0.01": a[6] / tot, "mask_frac_gt_0.9": a[7] / tot,
+        "mask_frac_gt_0.99": a[8] / tot, "mask_frac_gt_0.5": a[9] / tot,
+        "mask_mean_lt_0.5": a[10] / a[4] if a[4] > 0 else 0.0, "mask_mean_gt_0.5": a[11] / a[9] if a[9] > 0 else 0.0,
+        "mask_p10": q_from_hist(0.10), "mask_p50": q_from_hist(0.50), "mask_p90": q_from_hist(0.90),
+    }
+
+
+@torch.no_grad()
+def log_mask_stats(model, step: int, wandb_run=None, prefix: str = "mask/", bins: int = 100,
+                   sample_per_layer: int = 4096):
+    """legacy/utils.py:2283-2340: global mask statistics plus the schedule scalars of the first layer,
+    handed to ``wandb_run.log`` on rank 0. Returns the dictionary (on every rank)."""
+    stats = mask_stats(model, bins=bins, sample_per_layer=sample_per_layer)
+    log = {prefix + k: v for k, v in stats.items()}
+    log["iter"] = step
+    for m in _sparse_modules(model):
+        log[prefix + "beta_structural"] = float(m._beta_structural(step))
+        log[prefix + "hardening_x"] = float(getattr(m, "hardening_x", 1.0))
+        break
+    rank0 = not (dist.is_available() and dist.is_initialized()) or dist.get_rank() == 0
+    if rank0 and wandb_run is not None and hasattr(wandb_run, "log"):
+        try:
+            wandb_run.log(log, step=step)
+        except TypeError:
+            wandb_run.log(log)
+    return log
+
+
 def finalize_hard_masks(model):
     """End-of-training bake-in (legacy/main_llama.py:2552-2563): mask <- top2(mask), weight *= mask,
     mask updates off, forward uses the mask as is."""

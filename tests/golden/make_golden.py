@@ -416,6 +416,35 @@ def case_glu_joint():
     save("glu_joint", d)
 
 
+def case_mask_stats():
+    """mask_stats (legacy/utils.py:2069-2280) of a two-layer model, once with masks strictly inside
+    (0, 1) and once with entries at exactly 0 and 1 (the entropy term is then NaN in the reference:
+    the fp32 clamp bound 1 - 1e-8 is 1)."""
+    torch.manual_seed(77)
+    cfg = ref_sm.SparseLinearConfig(**TRAIN_LOOP_CFG)
+    model = TinyMLP(ref_sm.SparseLinear, cfg)
+    ref_utils.initialize_model(model)
+    d = {}
+    for tag in ("inside", "edges"):
+        with torch.no_grad():
+            for m in (model.fc1, model.fc2):
+                if tag == "inside":
+                    m.mask.copy_(torch.rand_like(m.mask) * 0.98 + 0.01)
+                else:
+                    m.mask.copy_((torch.randn_like(m.mask) * 0.5 + 0.5).clamp(0.0, 1.0))
+        put(d, f"{tag}_fc1_mask", model.fc1.mask.data); put(d, f"{tag}_fc2_mask", model.fc2.mask.data)
+        gi = torch.Generator().manual_seed(5 + len(tag))
+        idxs = [_orig_randint(0, 128 * 64, (512,), generator=gi) for _ in range(2)]
+        put(d, f"{tag}_idx0", idxs[0]); put(d, f"{tag}_idx1", idxs[1])
+        q = [i.clone() for i in idxs]
+        torch.randint = lambda *a, **k: q.pop(0)
+        st = ref_utils.mask_stats(model, bins=100, sample_per_layer=512)
+        torch.randint = _orig_randint
+        d[f"{tag}_keys"] = np.asarray(list(st.keys()))
+        d[f"{tag}_values"] = np.asarray([float(v) for v in st.values()], dtype=np.float64)
+    save("mask_stats", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -436,6 +465,7 @@ if __name__ == "__main__":
                lambda_mid=0.1, seed=200, tau_idx_seed=900)
     case_train_loop()
     case_glu_joint()
+    case_mask_stats()
     case_penalty()
     case_ties()
     case_adamw()

@@ -215,3 +215,37 @@ def test_glu_joint_mask_follows_the_reference(tag):
             eff = m.mask.data * m.hardening_x + (1 - m.hardening_x) * m._hard_mask_from_soft(m.mask.data) \
                 if m.hardening_x < 1.0 else m.mask.data
             assert rel_err(wm, m.weight.data * eff) <= 1e-5
+
+
+@pytest.mark.parametrize("tag", ["inside", "edges"])
+def test_mask_stats_follow_the_reference(tag):
+    """mask_stats / log_mask_stats (legacy/utils.py:2069-2340) with the reference's sample positions."""
+    import math
+
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g, gl = Golden("mask_stats"), Golden("train_loop")
+    model = TinyMLP(sf.SparseLinear, sf.SparseLinearConfig(**json.loads(str(gl["cfg_json"])))).to(DEV)
+    model.fc1.mask.data.copy_(g[f"{tag}_fc1_mask"].to(DEV))
+    model.fc2.mask.data.copy_(g[f"{tag}_fc2_mask"].to(DEV))
+    queue = [g[f"{tag}_idx0"].to(DEV), g[f"{tag}_idx1"].to(DEV)]
+    orig = torch.randint
+    torch.randint = lambda *a, **k: queue.pop(0)
+    try:
+        logged = {}
+
+        class Run:
+            def log(self, d, step=None):
+                logged.update(d)
+
+        out = U.log_mask_stats(model, 7, wandb_run=Run(), sample_per_layer=512)
+    finally:
+        torch.randint = orig
+    assert logged == out and out["iter"] == 7 and out["mask/hardening_x"] == 1.0
+    for k, v in zip(g[f"{tag}_keys"], g[f"{tag}_values"].tolist()):
+        got = out["mask/" + str(k)]
+        if math.isnan(v):
+            assert math.isnan(got), k
+        else:
+            assert got == pytest.approx(v, rel=1e-6, abs=1e-12), k

@@ -207,6 +207,21 @@ def test_glu_joint_mask_update():
                 assert math.isclose(hx, g.scalar(f"{tag}_s{step}_{n}_hx"), abs_tol=1e-12)
 
 
+def _same_stats(got, keys, values, rel):
+    for k, v in zip(keys, values):
+        if math.isnan(v):
+            assert math.isnan(got[str(k)]), k
+        else:
+            assert math.isclose(got[str(k)], float(v), rel_tol=rel, abs_tol=1e-12), (k, got[str(k)], v)
+
+
+def test_mask_log_stats():
+    g = Golden("mask_stats")
+    for tag in ("inside", "edges"):
+        got = O.mask_log_stats([g[f"{tag}_fc1_mask"], g[f"{tag}_fc2_mask"]], [g[f"{tag}_idx0"], g[f"{tag}_idx1"]])
+        _same_stats(got, g[f"{tag}_keys"], g[f"{tag}_values"].tolist(), 1e-12)
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
