@@ -298,6 +298,25 @@ SF_API int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t
 SF_API int sf_bias_grad(const void* dy, int dtype, float* db, int64_t T, int64_t out, void* stream);
 
 /*
+ * Distillation KL loss over the vocabulary, one sweep of both logit tensors per direction.
+ *   replaces: Distill_Model.kl_loss, legacy/sparse_modeling.py:1749-1828 (per chunk: clamp to
+ *             +-max_logit, divide by the temperature, two log_softmax, exp, multiply, sum).
+ * sf_kl_div_fwd: row_kl[r] = sum_v softmax(b)_v (log_softmax(b)_v - log_softmax(a)_v) with
+ *   a = clamp(student[r], +-max_logit) / temperature, b likewise from teacher; lse[2r], lse[2r+1]
+ *   = logsumexp of a and of b (kept for the backward pass). The caller sums the rows chunk by
+ *   chunk (dropping chunks whose sum is not finite, :1802-1821) and scales by temperature^2 / rows.
+ * sf_kl_div_bwd: grad[r, v] = row_scale[r] * (softmax(a)_v - softmax(b)_v) / temperature where
+ *   |student[r, v]| < max_logit, else 0 (the gradient autograd gives the student logits; the
+ *   teacher gets none). row_scale[r] = upstream gradient * temperature^2 / rows, 0 for dropped rows.
+ * student, teacher, grad: [rows, vocab] of `dtype` (SF_F32 / SF_BF16), vocab % 8 == 0.
+ */
+SF_API int sf_kl_div_fwd(const void* student, const void* teacher, int dtype, int64_t rows, int64_t vocab,
+                  double temperature, double max_logit, float* row_kl, float* lse, void* stream);
+SF_API int sf_kl_div_bwd(const void* student, const void* teacher, int dtype, const float* lse,
+                  const float* row_scale, int64_t rows, int64_t vocab, double temperature, double max_logit,
+                  void* grad, void* stream);
+
+/*
  * Row-sharded layer: the two products whose result has to cross GPUs, with the exchange done by
  * the GEMM epilogue itself (plain stores into the other GPUs' memory over NVLink) instead of a
  * collective that re-reads the result afterwards.

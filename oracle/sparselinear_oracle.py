@@ -452,6 +452,28 @@ def mask_log_stats(masks, sample_idx, bins=100, eps=1e-8):
             "mask_p10": q(0.10), "mask_p50": q(0.50), "mask_p90": q(0.90)}
 
 
+def kl_distill_loss(student_logits, teacher_logits, temperature=2.0, max_logit=100.0):
+    """Distill_Model.kl_loss, legacy/sparse_modeling.py:1749-1828, with differentiable torch ops:
+    chunks of 2048 / 512 / 128 token rows by vocabulary size, fp32 log-softmax of the clamped and
+    tempered logits, chunks with a non-finite sum dropped, total * temperature^2 / tokens."""
+    shape = student_logits.shape
+    s2 = student_logits.reshape(-1, shape[-1])
+    t2 = teacher_logits.reshape(-1, shape[-1])
+    rows, vocab = s2.shape
+    chunk = 128 if vocab > 100000 else (512 if vocab > 50000 else 2048)
+    total = torch.zeros((), dtype=torch.float32)
+    for i in range(0, rows, chunk):
+        a = torch.log_softmax(s2[i:i + chunk].float().clamp(-max_logit, max_logit) / temperature, dim=-1)
+        b = torch.log_softmax(t2[i:i + chunk].float().clamp(-max_logit, max_logit) / temperature, dim=-1)
+        if torch.isnan(a).any() or torch.isnan(b).any():
+            continue
+        c = ((b - a) * b.exp()).sum()
+        if torch.isfinite(c):
+            total = total + c
+    kl = (total * (temperature ** 2) / rows).to(student_logits.dtype)
+    return kl if torch.isfinite(kl) else torch.zeros((), dtype=student_logits.dtype)
+
+
 def to_numpy(t: torch.Tensor) -> np.ndarray:
     """bf16 tensors are stored as their raw uint16 bits."""
     t = t.detach().cpu().contiguous()

@@ -8,9 +8,10 @@ from .adamw import AdamW  # noqa: F401
 from .sparse_modeling import (  # noqa: F401
     STE,
     SRSTE,
+    Distill_Model,
     FusedMaskedLinearSTE,
     SparseLinear,
     SparseLinearConfig,
 )
 
-__all__ = ["AdamW", "STE", "SRSTE", "FusedMaskedLinearSTE", "SparseLinear", "SparseLinearConfig"]
+__all__ = ["AdamW", "STE", "SRSTE", "Distill_Model", "FusedMaskedLinearSTE", "SparseLinear", "SparseLinearConfig"]

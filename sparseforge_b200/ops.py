@@ -200,6 +200,28 @@ def mask_sample_hist(mask, idx, hist) -> None:
           "sf_mask_sample_hist")
 
 
+def kl_div_fwd(student2d, teacher2d, temperature=2.0, max_logit=100.0):
+    """(row_kl[rows], lse[rows, 2]) of the distillation KL; see ``sf_kl_div_fwd``."""
+    _cuda(student2d, teacher2d)
+    if student2d.shape != teacher2d.shape or student2d.dtype != teacher2d.dtype:
+        raise TypeError("kl_div_fwd: student and teacher logits must share shape and dtype")
+    rows, vocab = student2d.shape
+    row_kl = torch.empty(rows, dtype=torch.float32, device=student2d.device)
+    lse = torch.empty((rows, 2), dtype=torch.float32, device=student2d.device)
+    check(lib().sf_kl_div_fwd(_p(student2d), _p(teacher2d), _dt(student2d), rows, vocab, float(temperature),
+                              float(max_logit), _p(row_kl), _p(lse), _stream()), "sf_kl_div_fwd")
+    return row_kl, lse
+
+
+def kl_div_bwd(student2d, teacher2d, lse, row_scale, temperature=2.0, max_logit=100.0):
+    _cuda(student2d, teacher2d, lse, row_scale)
+    rows, vocab = student2d.shape
+    grad = torch.empty_like(student2d)
+    check(lib().sf_kl_div_bwd(_p(student2d), _p(teacher2d), _dt(student2d), _p(lse), _p(row_scale), rows, vocab,
+                              float(temperature), float(max_logit), _p(grad), _stream()), "sf_kl_div_bwd")
+    return grad
+
+
 def _gemm_dtype(*ts) -> int:
     d = ts[0].dtype
     for t in ts:

@@ -762,3 +762,91 @@ class _LazyInt:
         return int(self) + int(other)
 
     __radd__ = __add__
+
+
+# ----------------------------------------------------------------------------------------
+# distillation wrapper
+# ----------------------------------------------------------------------------------------
+class _KLDivLoss(torch.autograd.Function):
+    """Scalar distillation KL with the chunk rules of legacy/sparse_modeling.py:1749-1828: rows are
+    summed in chunks of 2048 / 512 / 128 tokens (by vocabulary size), a chunk whose sum is not
+    finite is dropped, the total is scaled by temperature^2 / tokens."""
+
+    @staticmethod
+    def forward(ctx, student_logits, teacher_logits, temperature):
+        shape = student_logits.shape
+        s2 = student_logits.reshape(-1, shape[-1]).contiguous()
+        t2 = teacher_logits.reshape(-1, shape[-1]).to(s2.dtype).contiguous()
+        rows, vocab = s2.shape
+        chunk = 128 if vocab > 100000 else (512 if vocab > 50000 else 2048)
+        row_kl, lse = ops.kl_div_fwd(s2, t2, temperature, 100.0)
+        nchunks = (rows + chunk - 1) // chunk
+        padded = torch.zeros(nchunks * chunk, dtype=torch.float64, device=s2.device)
+        padded[:rows] = row_kl.double()
+        sums = padded.view(nchunks, chunk).sum(1)
+        keep = torch.isfinite(sums)
+        total = torch.where(keep, sums, torch.zeros_like(sums)).sum()
+        kl = (total * (float(temperature) ** 2) / rows).to(student_logits.dtype)
+        ok = torch.isfinite(kl)
+        kl = torch.where(ok, kl, torch.zeros_like(kl))
+        row_keep = (keep & ok).repeat_interleave(chunk)[:rows].to(torch.float32)
+        ctx.save_for_backward(s2, t2, lse, row_keep)
+        ctx.temperature, ctx.shape, ctx.rows = float(temperature), shape, rows
+        return kl
+
+    @staticmethod
+    def backward(ctx, g):
+        s2, t2, lse, row_keep = ctx.saved_tensors
+        scale = row_keep * (g.float() * (ctx.temperature ** 2) / ctx.rows)
+        grad = ops.kl_div_bwd(s2, t2, lse, scale.contiguous(), ctx.temperature, 100.0)
+        return grad.view(ctx.shape), None, None
+
+
+class Distill_Model(torch.nn.Module):
+    """Student / teacher wrapper of the reference (legacy/sparse_modeling.py:1668-1843): the models
+    return ``(logits, loss, hidden_states)``; ``forward`` returns ``(student logits, task loss,
+    layerwise loss or None, KL loss)``. The KL term is one fused kernel per direction."""
+
+    def __init__(self, model, teacher=None, output_hidden_state=False):
+        super().__init__()
+        self.student = model
+        self.teacher = teacher
+        self.student.config.output_hidden_state = output_hidden_state
+        self.teacher.config.output_hidden_state = output_hidden_state
+        self.output_hidden_state = output_hidden_state
+        self.teacher.eval()
+
+    def forward(self, idx, targets=None):
+        if self.teacher is None:
+            student_logits, task_loss, _ = self.student(idx, targets)
+            return student_logits, task_loss, None, torch.tensor(0.0, device=idx.device)
+        student_logits, task_loss, student_hidden = self.student(idx, targets)
+        with torch.no_grad():
+            try:
+                tdev = next(self.teacher.parameters()).device
+            except Exception:
+                tdev = idx.device
+            idx_t = idx.to(tdev) if idx.device != tdev else idx
+            targets_t = None if targets is None else (targets.to(tdev) if targets.device != tdev else targets)
+            teacher_logits, _, teacher_hidden = self.teacher(idx_t, targets_t)
+        if teacher_logits.device != student_logits.device:
+            teacher_logits = teacher_logits.to(device=student_logits.device, dtype=student_logits.dtype)
+        layerwise = None
+        if self.output_hidden_state:
+            if student_hidden is not None and teacher_hidden is not None:
+                if len(teacher_hidden) == len(student_hidden):
+                    teacher_hidden = [t.to(device=student_logits.device, dtype=student_logits.dtype) for t in teacher_hidden]
+                layerwise = self.layerwise_loss(student_hidden, teacher_hidden)
+            else:
+                layerwise = 0.0
+        return student_logits, task_loss, layerwise, self.kl_loss(student_logits, teacher_logits)
+
+    def kl_loss(self, student_logits, teacher_logits, temperature=2):
+        return _KLDivLoss.apply(student_logits, teacher_logits.detach(), float(temperature))
+
+    def layerwise_loss(self, student_hidden_states, teacher_hidden_states):
+        loss = 0.0
+        eps = torch.finfo(torch.bfloat16).eps
+        for s, t in zip(student_hidden_states, teacher_hidden_states):
+            loss = loss + (s - t).pow(2).mean() / (t.pow(2).mean() + eps)
+        return loss

@@ -445,6 +445,29 @@ def case_mask_stats():
     save("mask_stats", d)
 
 
+def case_kl_loss():
+    """Distill_Model.kl_loss (legacy/sparse_modeling.py:1749-1828) and its gradient with respect
+    to the student logits, fp32 and bf16, with a few logits beyond the +-100 clamp and one row made
+    of NaN (its chunk is dropped)."""
+    torch.manual_seed(42)
+    d = {}
+    for tag, dtype, rows, vocab in (("f32", torch.float32, 40, 512), ("bf16", torch.bfloat16, 24, 1024),
+                                    ("chunks", torch.float32, 2100, 16)):
+        s = (torch.randn(2, rows // 2, vocab) * 3.0).to(dtype)
+        t = (torch.randn(2, rows // 2, vocab) * 3.0).to(dtype)
+        s[0, 0, :4] = torch.tensor([150.0, -140.0, 99.0, -99.5]).to(dtype)
+        t[0, 1, :2] = torch.tensor([120.0, -130.0]).to(dtype)
+        if tag == "chunks":
+            s[1, -1, 3] = float("nan")  # the last chunk (rows 2048..2099) is dropped
+        s.requires_grad_(True)
+        # logits come out of a model, i.e. they are not a leaf (the reference clamps in place)
+        kl = ref_sm.Distill_Model.kl_loss(None, s * 1.0, t.clone())
+        (kl * 1.5).backward()
+        put(d, f"{tag}_student", s.detach()); put(d, f"{tag}_teacher", t); put(d, f"{tag}_kl", kl.detach().float())
+        put(d, f"{tag}_grad", s.grad)
+    save("kl_loss", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -466,6 +489,7 @@ if __name__ == "__main__":
     case_train_loop()
     case_glu_joint()
     case_mask_stats()
+    case_kl_loss()
     case_penalty()
     case_ties()
     case_adamw()

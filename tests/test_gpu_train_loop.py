@@ -249,3 +249,32 @@ def test_mask_stats_follow_the_reference(tag):
             assert math.isnan(got), k
         else:
             assert got == pytest.approx(v, rel=1e-6, abs=1e-12), k
+
+
+@pytest.mark.parametrize("tag,tol", [("f32", 1e-5), ("bf16", 1e-2), ("chunks", 1e-5)])
+def test_kl_distillation_loss(tag, tol):
+    """The fused KL kernels against Distill_Model.kl_loss of the reference (loss and the gradient of
+    the student logits; logits beyond the clamp get no gradient; a chunk with NaN is dropped)."""
+    import sparseforge_b200 as sf
+
+    g = Golden("kl_loss")
+    s = g[f"{tag}_student"].to(DEV).requires_grad_(True)
+    t = g[f"{tag}_teacher"].to(DEV)
+    kl = sf.Distill_Model.kl_loss(None, s, t)
+    (kl * 1.5).backward()
+    assert kl.dtype == s.dtype
+    assert rel_err(kl.detach().float(), g[f"{tag}_kl"]) <= tol
+    assert rel_err(s.grad.float(), g[f"{tag}_grad"].float()) <= tol
+    assert not torch.isnan(s.grad).any()
+    # a vocabulary of LLaMA's size: rows against a float64 evaluation on the device
+    if tag == "f32":
+        torch.manual_seed(3)
+        s2 = (torch.randn(64, 32000, device=DEV) * 4).to(torch.bfloat16)
+        t2 = (torch.randn(64, 32000, device=DEV) * 4).to(torch.bfloat16)
+        from sparseforge_b200 import ops
+
+        row_kl, lse = ops.kl_div_fwd(s2, t2, 2.0, 100.0)
+        a = torch.log_softmax(s2.double() / 2, -1)
+        b = torch.log_softmax(t2.double() / 2, -1)
+        assert rel_err(row_kl, ((b - a) * b.exp()).sum(-1)) <= 1e-5
+        assert rel_err(lse[:, 0], torch.logsumexp(s2.double() / 2, -1)) <= 1e-6

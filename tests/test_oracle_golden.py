@@ -222,6 +222,16 @@ def test_mask_log_stats():
         _same_stats(got, g[f"{tag}_keys"], g[f"{tag}_values"].tolist(), 1e-12)
 
 
+@pytest.mark.parametrize("tag,tol", [("f32", 1e-5), ("bf16", BF16_TOL), ("chunks", 1e-5)])
+def test_kl_distill_loss(tag, tol):
+    g = Golden("kl_loss")
+    s = g[f"{tag}_student"].clone().requires_grad_(True)
+    kl = O.kl_distill_loss(s, g[f"{tag}_teacher"])
+    (kl * 1.5).backward()
+    assert rel_err(kl.detach().float(), g[f"{tag}_kl"]) <= tol
+    assert rel_err(s.grad.float(), g[f"{tag}_grad"].float()) <= tol
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
