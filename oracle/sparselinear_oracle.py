@@ -474,6 +474,23 @@ def kl_distill_loss(student_logits, teacher_logits, temperature=2.0, max_logit=1
     return kl if torch.isfinite(kl) else torch.zeros((), dtype=student_logits.dtype)
 
 
+def slorb_init(W, mask, k, init_type="mean"):
+    """(x_proj, SLoRB_Weight) of legacy/sparse_modeling.py:830-872 (block-sum projection; the bypass
+    weight starts from the block mean / sum of the pruned part W (1 - mask))."""
+    n, d = W.shape
+    rows = d // k
+    x_proj = torch.zeros(rows, d, dtype=W.dtype)
+    for r in range(rows):
+        x_proj[r, r * k:(r + 1) * k] = 1
+    pruned = (W * (1.0 - mask)).view(n, rows, k)
+    return x_proj, (pruned.mean(dim=2) if init_type == "mean" else pruned.sum(dim=2))
+
+
+def slorb_bypass(x, x_proj, slorb_weight):
+    """out += (x x_proj^T) SLoRB_Weight^T, legacy/sparse_modeling.py:790-794."""
+    return torch.nn.functional.linear(torch.nn.functional.linear(x, x_proj), slorb_weight)
+
+
 def to_numpy(t: torch.Tensor) -> np.ndarray:
     """bf16 tensors are stored as their raw uint16 bits."""
     t = t.detach().cpu().contiguous()

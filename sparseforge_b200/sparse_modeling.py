@@ -302,7 +302,18 @@ class SparseLinear(nn.Linear):
         self.hardening_x = 1.0
         self.SLoRB = cfg.SLoRB
         if self.SLoRB:
-            raise NotImplementedError("SLoRB bypass is outside this path")
+            # low-rank bypass out += (x x_proj^T) SLoRB_Weight^T; parameters registered here and filled
+            # by init_SLoRB, as the reference does (legacy/sparse_modeling.py:388-408)
+            self.SLoRB_k = cfg.SLoRB_k
+            self.SLoRB_init_type = cfg.SLoRB_init_type
+            self.trainable_projection = cfg.trainable_projection
+            k = int(self.SLoRB_k)
+            assert k > 0, f"SLoRB_k must be > 0 (got {k})"
+            assert in_features % k == 0, f"in_features ({in_features}) must be divisible by SLoRB_k ({k})."
+            self.x_proj = nn.Parameter(torch.zeros(in_features // k, in_features, device=dev, dtype=self.weight.dtype),
+                                       requires_grad=bool(self.trainable_projection))
+            self.SLoRB_Weight = nn.Parameter(torch.zeros(out_features, in_features // k, device=dev,
+                                                         dtype=self.weight.dtype), requires_grad=True)
         # device-side caches (not part of the state dict)
         self._wm = None          # W * cast(M_eff) in the weight dtype
         self._wm_key = None      # what the cache was built from
@@ -507,7 +518,43 @@ class SparseLinear(nn.Linear):
         if getattr(self.cfg, "weight_scaling", False) and hx < 1.0 - 1e-6:
             scale = 1.0 + (1.0 - hx) * (self._compute_weight_scale_factor() - 1.0)
         wm = self.masked_weight()
-        return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized)
+        out = FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized)
+        if self.SLoRB and hasattr(self, "x_proj"):
+            out = out + self._slorb(x)
+        return out
+
+    def _slorb(self, x):
+        """(x x_proj^T) SLoRB_Weight^T, legacy/sparse_modeling.py:790-794, as two products on the
+        tensor-core kernels (differentiable with respect to x, the projection and the weight)."""
+        x2 = x.reshape(-1, x.shape[-1])
+        z = _MatmulNT.apply(x2, self.x_proj.to(x2.dtype))
+        y = _MatmulNT.apply(z, self.SLoRB_Weight.to(x2.dtype))
+        return y.view(*x.shape[:-1], self.out_features)
+
+    @torch.no_grad()
+    def init_SLoRB(self):
+        """legacy/sparse_modeling.py:830-872: x_proj sums blocks of k input features (or is drawn
+        xavier-uniform); SLoRB_Weight starts from the mean / sum over each block of the part of the
+        weight that the mask currently prunes, W (1 - mask)."""
+        n, d = self.weight.shape
+        k = int(self.SLoRB_k)
+        assert d % k == 0, f"in_features ({d}) must be divisible by SLoRB_k ({k})."
+        rows = d // k
+        xp = self.x_proj.data
+        xp.zero_()
+        r = torch.arange(rows, device=xp.device)
+        xp[r[:, None], (r * k)[:, None] + torch.arange(k, device=xp.device)] = 1
+        if self.SLoRB_init_type == "xavier":
+            nn.init.xavier_uniform_(self.x_proj)
+        else:
+            pruned = (self.weight.detach() * (1.0 - self.mask.detach())).view(n, rows, k)
+            if self.SLoRB_init_type == "mean":
+                init = pruned.mean(dim=2)
+            elif self.SLoRB_init_type == "sum":
+                init = pruned.sum(dim=2)
+            else:
+                raise ValueError(f"Invalid SLoRB_init_type: {self.SLoRB_init_type}")
+            self.SLoRB_Weight.data.copy_(init)
 
     # -- grad / hessian EMA ----------------------------------------------------------------
     @torch.no_grad()

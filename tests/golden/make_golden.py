@@ -468,6 +468,39 @@ def case_kl_loss():
     save("kl_loss", d)
 
 
+def case_slorb():
+    """SparseLinear with the SLoRB bypass (legacy/sparse_modeling.py:388-408, 790-794, 830-872):
+    init_SLoRB from a soft mask, then forward / backward with gradients of x, weight, SLoRB_Weight
+    and (trainable) x_proj."""
+    d = {}
+    for tag, init, trainable in (("mean", "mean", False), ("sum", "sum", True)):
+        torch.manual_seed(17 + len(tag) + int(trainable))
+        cfg = ref_sm.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, SLoRB=True, SLoRB_k=8,
+                                        SLoRB_init_type=init, trainable_projection=trainable, mask_hardening_start=1000)
+        layer = ref_sm.SparseLinear(64, 48, sparselinear_config=cfg, bias=True)
+        layer.initialize()
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(48, 64) * 0.1)
+            layer.bias.copy_(torch.randn(48) * 0.1)
+            layer.mask.copy_(torch.rand(48, 64))
+        layer.init_SLoRB()
+        if trainable:
+            with torch.no_grad():
+                layer.x_proj.add_(torch.randn_like(layer.x_proj) * 0.05)
+        x = torch.randn(3, 8, 64, requires_grad=True)
+        dy = torch.randn(3, 8, 48)
+        y = layer(x)
+        y.backward(dy)
+        d[f"{tag}_state_keys"] = np.asarray(list(layer.state_dict().keys()))
+        for n, t in layer.state_dict().items():
+            put(d, f"{tag}/" + n, t)
+        put(d, f"{tag}_x", x.detach()); put(d, f"{tag}_dy", dy); put(d, f"{tag}_y", y.detach())
+        put(d, f"{tag}_dx", x.grad); put(d, f"{tag}_dW", layer.weight.grad); put(d, f"{tag}_dS", layer.SLoRB_Weight.grad)
+        if trainable:
+            put(d, f"{tag}_dP", layer.x_proj.grad)
+    save("slorb", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -490,6 +523,7 @@ if __name__ == "__main__":
     case_glu_joint()
     case_mask_stats()
     case_kl_loss()
+    case_slorb()
     case_penalty()
     case_ties()
     case_adamw()

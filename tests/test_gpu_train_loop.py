@@ -278,3 +278,37 @@ def test_kl_distillation_loss(tag, tol):
         b = torch.log_softmax(t2.double() / 2, -1)
         assert rel_err(row_kl, ((b - a) * b.exp()).sum(-1)) <= 1e-5
         assert rel_err(lse[:, 0], torch.logsumexp(s2.double() / 2, -1)) <= 1e-6
+
+
+@pytest.mark.parametrize("tag,trainable", [("mean", False), ("sum", True)])
+def test_slorb_bypass_follows_the_reference(tag, trainable):
+    """SLoRB low-rank bypass (legacy/sparse_modeling.py:388-408, 790-794, 830-872): state-dict keys,
+    init_SLoRB, forward and all gradients."""
+    import sparseforge_b200 as sf
+
+    g = Golden("slorb")
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, SLoRB=True, SLoRB_k=8,
+                                SLoRB_init_type=tag, trainable_projection=trainable, mask_hardening_start=1000)
+    layer = sf.SparseLinear(64, 48, sparselinear_config=cfg, bias=True).to(DEV)
+    keys = [str(k) for k in g[f"{tag}_state_keys"]]
+    assert list(layer.state_dict().keys()) == keys
+    layer.load_state_dict({k: g[f"{tag}/{k}"].to(DEV) for k in keys}, strict=True)
+    assert layer.x_proj.requires_grad == trainable and layer.SLoRB_Weight.requires_grad
+    if not trainable:
+        # init_SLoRB rebuilds projection and bypass weight from W and the soft mask
+        want_p, want_s = layer.x_proj.data.clone(), layer.SLoRB_Weight.data.clone()
+        layer.x_proj.data.zero_(); layer.SLoRB_Weight.data.zero_()
+        layer.init_SLoRB()
+        assert torch.equal(layer.x_proj.data, want_p)
+        assert rel_err(layer.SLoRB_Weight.data, want_s) <= 1e-5
+    x = g[f"{tag}_x"].to(DEV).requires_grad_(True)
+    y = layer(x)
+    y.backward(g[f"{tag}_dy"].to(DEV))
+    assert rel_err(y, g[f"{tag}_y"]) <= 1e-5
+    assert rel_err(x.grad, g[f"{tag}_dx"]) <= 1e-5
+    assert rel_err(layer.weight.grad, g[f"{tag}_dW"]) <= 1e-5
+    assert rel_err(layer.SLoRB_Weight.grad, g[f"{tag}_dS"]) <= 1e-5
+    if trainable:
+        assert rel_err(layer.x_proj.grad, g[f"{tag}_dP"]) <= 1e-5
+    else:
+        assert layer.x_proj.grad is None

@@ -108,8 +108,9 @@ def test_unsupported_configurations_raise():
         sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(mask_metric="wanda"))
     with pytest.raises(NotImplementedError):
         sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(freeze_low=0.1))
-    with pytest.raises(NotImplementedError):
-        sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(SLoRB=True))
+    slorb = sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(SLoRB=True, SLoRB_k=16))
+    assert tuple(slorb.x_proj.shape) == (4, 64) and tuple(slorb.SLoRB_Weight.shape) == (8, 4)
+    assert list(slorb.state_dict().keys())[-2:] == ["x_proj", "SLoRB_Weight"]
     with pytest.raises(NotImplementedError):
         sf.AdamW([torch.nn.Parameter(torch.zeros(2))], amsgrad=True)
     with pytest.raises(ValueError):

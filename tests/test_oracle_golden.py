@@ -232,6 +232,25 @@ def test_kl_distill_loss(tag, tol):
     assert rel_err(s.grad.float(), g[f"{tag}_grad"].float()) <= tol
 
 
+def test_slorb_bypass():
+    g = Golden("slorb")
+    for tag in ("mean", "sum"):
+        W, mask, b = g[f"{tag}/weight"], g[f"{tag}/mask"], g[f"{tag}/bias"]
+        xp, sw = O.slorb_init(W, mask, 8, tag)
+        assert rel_err(sw, g[f"{tag}/SLoRB_Weight"]) <= F32_TOL
+        if tag == "mean":
+            assert torch.equal(xp, g[f"{tag}/x_proj"])
+        x = g[f"{tag}_x"].clone().requires_grad_(True)
+        w = W.clone().requires_grad_(True)
+        s_w = g[f"{tag}/SLoRB_Weight"].clone().requires_grad_(True)
+        y = O.MaskedLinearSTE.apply(x, w, b, O.effective_mask(mask, 1.0)) + O.slorb_bypass(x, g[f"{tag}/x_proj"], s_w)
+        y.backward(g[f"{tag}_dy"])
+        assert rel_err(y, g[f"{tag}_y"]) <= F32_TOL
+        assert rel_err(x.grad, g[f"{tag}_dx"]) <= F32_TOL
+        assert rel_err(w.grad, g[f"{tag}_dW"]) <= F32_TOL
+        assert rel_err(s_w.grad, g[f"{tag}_dS"]) <= F32_TOL
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
