@@ -40,8 +40,9 @@ METRIC = "SparseLinear fwd+bwd TFLOP/s (LLaMA-2-7B layer set, full tempering ste
 UNIT = "TFLOP/s"
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 # algorithmic bytes per weight element at these dtypes (bf16 W/g/m/v/hvp, int8 probe, fp32 mask/H/score)
-# optimizer pass: W,m,v read+written (12), g (2), hvp (2), probe (1), mask (4), H read+written (8), score written (4)
-BYTES_OPTIM, BYTES_MASK = 33.0, 16.125
+# optimizer pass: W,m,v read+written (12), g (2), hvp (2), probe (1), mask (4), H read+written (8);
+# mask update: H (4), mask read+written (8), W (2), masked weight (2), metadata (0.125)
+BYTES_OPTIM, BYTES_MASK = 29.0, 16.125
 # DRAM bytes (read + write) of one GEMM launch from the ncu capture of the q-shaped matrix
 # (mean of forward, dgrad, wgrad: 259.2 MB for 274.88 GFLOP), scaled to a launch by its FLOPs
 GEMM_TRAFFIC_PER_GFLOP = 259.2e6 / 274.88
@@ -279,11 +280,14 @@ def run_ours(args):
             # (one pass over the matrix), then the mask update that consumes score and its statistics
             timed("optim", lambda: ops.adamw_masked_score(
                 mt.W, dw, mt.m, mt.v, mask=mt.mask, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
-                decay=2e-4, step=it + 1, hvp=mt.hvp, probe=mt.probe, beta_h=0.99, H=mt.H, score=mt.score,
+                decay=2e-4, step=it + 1, hvp=mt.hvp, probe=mt.probe, beta_h=0.99, H=mt.H, score=None,
                 norm=mt.norm, scratch=mt.scratch, metric="hessian_obd"))
             launches += 1  # the one-block statistics kernel behind the score
-            timed("mask", lambda: ops.mask_update_nm24(mt.score, mt.norm, mt.mask, mt.stats, W=mt.W, wm=mt.wm,
-                                                       meta=mt.meta, temperature=temp, mask_lr=0.1, hx=hx))
+            # the mask update forms the score again from W and H (it reads W anyway), so the optimizer
+            # pass above writes no score tensor
+            timed("mask", lambda: ops.mask_update_nm24_from_weight(mt.W, mt.H, mt.norm, mt.mask, mt.stats, mt.wm,
+                                                                   mt.meta, metric="hessian_obd", temperature=temp,
+                                                                   mask_lr=0.1, hx=hx))
             for wk in works:
                 wk.wait()
             if e2e:

@@ -165,6 +165,23 @@ SF_API int sf_mask_update_nm24(const float* score, const float* norm, const floa
                         int structured_exact, int score_bf16, void* stream);
 
 /*
+ * sf_mask_update_nm24 without a score tensor: the score is formed again inside the pass from the
+ * weight and the Hessian diagonal (metric SF_METRIC_HESSIAN_OBD, _HESSIAN_RATIO, _MAGNITUDE or
+ * _HESSIAN; the same arithmetic as sf_hutch_score / sf_adamw_masked_score, so the result equals
+ * the update from their score tensor bit for bit). The pass reads W anyway to write the masked
+ * weight, so the optimizer pass before it need not write the score (score = NULL there) and this
+ * pass reads H instead: 4 bytes per element less traffic per step. norm comes from
+ * sf_adamw_masked_score / sf_hutch_score; wm and meta are required. No bf16 score rounding
+ * (the metrics with a fp32 Hessian never need it).
+ */
+SF_API int sf_mask_update_nm24_from_weight(const void* W, int w_dtype, const float* H, int metric,
+                                    const float* norm, const float* tau, float* mask, void* wm,
+                                    uint8_t* meta, double* stats, int64_t rows, int64_t cols,
+                                    double temperature, double mask_lr, double pen, int penalty_mode,
+                                    double beta_s, double binarize_decay, double hx, int structured_exact,
+                                    void* stream);
+
+/*
  * Joint mask update of a GLU gate / up pair: both layers are updated from ONE score, the sum of
  * their importance scores, so that the same positions are pruned in both.
  *   replaces: _update_glu_joint_mask legacy/utils.py:363-479 with _compute_joint_gate_target
@@ -232,8 +249,8 @@ SF_API int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, v
  *             refresh, legacy/sparse_modeling.py:1041-1088 (the training loop steps the optimizer,
  *             then update_mask scores the new weight: main.py's sparse step). One read of p, g,
  *             m, v, mask, H instead of the optimizer pass plus a score pass over W and H.
- * score[n] (fp32) <- metric(p_new as stored, H); norm[0..1] <- mean and population std + 1e-6 of
- * score; scratch as for sf_hutch_score (scratch[0..1] hold sum and sum of squares on return).
+ * score[n] (fp32) <- metric(p_new as stored, H) (score = NULL: not written, only its statistics
+ * are formed); norm[0..1] <- mean and population std + 1e-6 of score; scratch as for sf_hutch_score (scratch[0..1] hold sum and sum of squares on return).
  * metric is one of SF_METRIC_HESSIAN_OBD, _HESSIAN_RATIO, _MAGNITUDE, _HESSIAN; H (fp32) may be NULL
  * for _MAGNITUDE. hvp != NULL also folds this step's Hutchinson sample into H first
  * (H <- beta_h H + (1-beta_h) max(hvp*probe, 0), arguments as for sf_hutch_score; the reference
@@ -349,6 +366,16 @@ SF_API int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_
  * device, to be released with sf_peer_close(base). The buffer must come from cudaMalloc (PyTorch's
  * default caching allocator does). No counterpart in the reference, which leaves this to NCCL.
  */
+/*
+ * Self-test of the device-side wait limit. Every mbarrier wait in the tensor-core kernels is
+ * bounded (about two seconds); when one runs out the kernel stores a code in the caller's status
+ * word, every role leaves through the common teardown, and the context stays usable. This entry
+ * launches a one-block kernel that waits, with the same routine and a limit of `limit_ms`
+ * milliseconds, on a barrier nobody arrives at: afterwards *status == 99. No counterpart in the
+ * reference (its failure handling is host-side, legacy/main_llama.py:2075-2108).
+ */
+SF_API int sf_selftest_bounded_wait(double limit_ms, int32_t* status, void* stream);
+
 SF_API int sf_peer_handle_bytes(void);
 SF_API int sf_peer_export(const void* ptr, void* handle, int64_t* offset);
 SF_API int sf_peer_open(const void* handle, int64_t offset, void** base, void** ptr);

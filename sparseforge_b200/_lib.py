@@ -31,6 +31,8 @@ _SIGNATURES = {
                                     c_int, c_double, c_double, c_double, c_int, c_int, _P]),
     "sf_mask_update_nm24_joint": (c_int, [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_double,
                                           c_double, c_int, c_double, c_double, c_double, c_int, c_int, _P]),
+    "sf_mask_update_nm24_from_weight": (c_int, [_P, c_int, _P, c_int, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_double,
+                                                c_double, c_double, c_int, c_double, c_double, c_double, c_int, _P]),
     "sf_score_sum": (c_int, [_P, _P, _P, _P, _P, c_int64, _P]),
     "sf_project_nm24": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, _P, c_int64, c_int64, _P]),
     "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_int, c_double, _P]),
@@ -52,6 +54,7 @@ _SIGNATURES = {
                                              c_int, _P, _P]),
     "sf_masked_gemm_dgrad_reducescatter": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_reduce_slots": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
+    "sf_selftest_bounded_wait": (c_int, [c_double, _P, _P]),
     "sf_peer_handle_bytes": (c_int, []),
     "sf_peer_export": (c_int, [_P, _P, _P]),
     "sf_peer_open": (c_int, [_P, c_int64, _P, _P]),

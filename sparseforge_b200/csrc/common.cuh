@@ -203,6 +203,10 @@ struct Vec8<float> {
     // Raw storage of 8 elements, and p <- raw * round(f) element by element.
     struct Raw { uint4 a, b; };
     static __device__ __forceinline__ Raw load_raw(const float* p) { return Raw{ld_stream16(p), ld_stream16(p + 4)}; }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&x)[8]) {
+        x[0] = __uint_as_float(r.a.x); x[1] = __uint_as_float(r.a.y); x[2] = __uint_as_float(r.a.z); x[3] = __uint_as_float(r.a.w);
+        x[4] = __uint_as_float(r.b.x); x[5] = __uint_as_float(r.b.y); x[6] = __uint_as_float(r.b.z); x[7] = __uint_as_float(r.b.w);
+    }
     static __device__ __forceinline__ void store_product(float* p, const Raw& r, const float (&f)[8]) {
         st_stream16(p, make_uint4(__float_as_uint(__fmul_rn(__uint_as_float(r.a.x), f[0])),
                                   __float_as_uint(__fmul_rn(__uint_as_float(r.a.y), f[1])),
@@ -239,6 +243,14 @@ struct Vec8<__nv_bfloat16> {
     // multiplied pairwise (one rounding of the exact product, as a bf16 tensor multiply does).
     struct Raw { uint4 a; };
     static __device__ __forceinline__ Raw load_raw(const __nv_bfloat16* p) { return Raw{ld_stream16(p)}; }
+    static __device__ __forceinline__ void unpack(const Raw& r, float (&x)[8]) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            x[2 * i] = __uint_as_float(w[i] << 16);
+            x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
     static __device__ __forceinline__ void store_product(__nv_bfloat16* p, const Raw& r, const float (&f)[8]) {
         const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
         uint32_t o[4];

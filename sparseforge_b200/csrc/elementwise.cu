@@ -325,6 +325,7 @@ struct MaskUpdateParams {
     int score_bf16;
     const float* tau;  // unstructured gate: threshold in normalised-score units (device); null = 2:4 gate
     const float* pen_mask;  // mask the penalty pull is taken from (GLU joint update); null = the updated mask
+    int metric;             // FROM_W instantiations: which score to form from W and H
 };
 
 __device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
@@ -358,7 +359,9 @@ __device__ __forceinline__ void block_reduce_stats(const GroupStats& g, double* 
 
 // PLAIN: no bf16 score rounding, no exact gate, no beta mixing, no penalty, no binarise push
 // (the tempering recipe of the benchmark); the general instantiation tests those at run time.
-template <typename TW, bool EMIT_WM, bool EMIT_META, bool PLAIN>
+// FROM_W: the score is not read but formed again from the weight and the Hessian diagonal with the
+// arithmetic of the score kernels (so it equals what they would have written); `score` then holds H.
+template <typename TW, bool EMIT_WM, bool EMIT_META, bool PLAIN, bool FROM_W = false>
 __global__ void __launch_bounds__(kThreads)
 mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict__ norm,
                         float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm,
@@ -381,9 +384,20 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
         const int64_t e = c * 8;
         float sc[8], m[8], eff[8];
         typename Vec8<TW>::Raw wraw;
-        Vec8<float>::load(score + e, sc);
+        if (!FROM_W || P.metric != SF_METRIC_MAGNITUDE) Vec8<float>::load(score + e, sc);
         Vec8<float>::load(mask + e, m);
-        if (EMIT_WM) wraw = Vec8<TW>::load_raw(W + e);
+        if (EMIT_WM || FROM_W) wraw = Vec8<TW>::load_raw(W + e);
+        if (FROM_W) {
+            float w[8];
+            Vec8<TW>::unpack(wraw, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const float h = sc[i];
+                if (P.metric == SF_METRIC_HESSIAN_OBD) sc[i] = __fmul_rn(__fadd_rn(h, 1e-8f), Vec8<TW>::round(__fmul_rn(w[i], w[i])));
+                else if (P.metric == SF_METRIC_HESSIAN_RATIO) sc[i] = __fdiv_rn(fabsf(w[i]), __fsqrt_rn(__fadd_rn(h, 1e-8f)));
+                else if (P.metric == SF_METRIC_MAGNITUDE) sc[i] = fabsf(w[i]);
+            }
+        }
         uint32_t kp8 = 0, kn8 = 0;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
@@ -653,7 +667,7 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
                 ps += sv;
                 ps2 = fmaf(sv, sv, ps2);
             }
-            Vec8<float>::store(score + e, sc);
+            if (score != nullptr) Vec8<float>::store(score + e, sc);
             acc_s += (double)ps;
             acc_s2 += (double)ps2;
         }
@@ -830,6 +844,7 @@ static MaskUpdateParams make_mask_params(double temperature, double mask_lr, dou
     P.score_bf16 = score_bf16;
     P.tau = nullptr;
     P.pen_mask = nullptr;
+    P.metric = SF_METRIC_HESSIAN_OBD;
     return P;
 }
 
@@ -871,6 +886,45 @@ int sf_score_sum(const float* a, const float* b, float* out, float* norm, double
     score_sum_kernel<<<grid, kThreads, 0, st>>>(a, b, out, scratch, chunks);
     SF_CHECK_CUDA(cudaGetLastError());
     score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_mask_update_nm24_from_weight(const void* W, int w_dtype, const float* H, int metric, const float* norm,
+                                    const float* tau, float* mask, void* wm, uint8_t* meta, double* stats,
+                                    int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
+                                    int penalty_mode, double beta_s, double binarize_decay, double hx,
+                                    int structured_exact, void* stream) {
+    SF_CHECK_ARG(W && norm && mask && wm && meta && stats,
+                 "sf_mask_update_nm24_from_weight: W, norm, mask, wm, meta, stats must be non-null");
+    SF_CHECK_ARG(metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO || metric == SF_METRIC_MAGNITUDE ||
+                     metric == SF_METRIC_HESSIAN,
+                 "sf_mask_update_nm24_from_weight: metric %d cannot be formed from W and H", metric);
+    SF_CHECK_ARG(metric == SF_METRIC_MAGNITUDE || H != nullptr, "sf_mask_update_nm24_from_weight: metric %d needs H", metric);
+    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0,
+                 "sf_mask_update_nm24_from_weight: cols=%lld must be a positive multiple of 8", (long long)cols);
+    SF_CHECK_ARG(penalty_mode >= SF_PENALTY_NONE && penalty_mode <= SF_PENALTY_MID,
+                 "sf_mask_update_nm24_from_weight: unknown penalty_mode %d", penalty_mode);
+    SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_mask_update_nm24_from_weight: w_dtype must be SF_F32 or SF_BF16");
+    if (!(aligned16(H) && aligned16(mask) && aligned16(W) && aligned16(wm)))
+        return fail(SF_ERR_ALIGNMENT, "sf_mask_update_nm24_from_weight: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    MaskUpdateParams P = make_mask_params(temperature, mask_lr, pen, penalty_mode, beta_s, binarize_decay, hx,
+                                          structured_exact, 0);
+    P.tau = tau;
+    P.metric = metric;
+    const int64_t chunks = rows * cols / 8;
+    SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
+    const bool plain = !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0;
+#define SF_MUW(TW, PL)                                                                           \
+    do {                                                                                         \
+        auto kern = mask_update_nm24_kernel<TW, true, true, PL, true>;                           \
+        kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
+            H, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);                       \
+    } while (0)
+    if (w_dtype == SF_F32) { if (plain) SF_MUW(float, true); else SF_MUW(float, false); }
+    else { if (plain) SF_MUW(__nv_bfloat16, true); else SF_MUW(__nv_bfloat16, false); }
+#undef SF_MUW
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
@@ -1021,13 +1075,13 @@ static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* 
         kern<<<grid, kThreads, 0, st>>>((TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P, H, score, \
                                         scratch, metric, hu);                                    \
     } while (0)
-    if (score != nullptr) {
+    if (norm != nullptr) {
         if (w_dtype == SF_F32) SF_AD(float, false, true); else SF_AD(__nv_bfloat16, false, true);
     } else if (w_dtype == SF_F32) { if (wm) SF_AD(float, true, false); else SF_AD(float, false, false); }
     else { if (wm) SF_AD(__nv_bfloat16, true, false); else SF_AD(__nv_bfloat16, false, false); }
 #undef SF_AD
     SF_CHECK_CUDA(cudaGetLastError());
-    if (score != nullptr) {
+    if (norm != nullptr) {
         score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
         SF_CHECK_CUDA(cudaGetLastError());
     }
@@ -1053,7 +1107,7 @@ int sf_adamw_masked_score(void* p, const void* g, const float* mask, void* m, vo
         if (!aligned16(hvp) || (reinterpret_cast<uintptr_t>(probe) & 7u))
             return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked_score: hvp must be 16-byte, probe 8-byte aligned");
     }
-    SF_CHECK_ARG(score && norm && scratch, "sf_adamw_masked_score: score, norm, scratch must be non-null");
+    SF_CHECK_ARG(norm && scratch, "sf_adamw_masked_score: norm and scratch must be non-null");
     SF_CHECK_ARG(metric == SF_METRIC_HESSIAN_OBD || metric == SF_METRIC_HESSIAN_RATIO || metric == SF_METRIC_MAGNITUDE ||
                      metric == SF_METRIC_HESSIAN,
                  "sf_adamw_masked_score: metric %d is not available fused (use sf_hutch_score)", metric);

@@ -804,6 +804,24 @@ int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int
     return launch_bf16<1, 1>(dy, out, x, in, dw, in, nullptr, 1.0f, out, in, T, status, st);
 }
 
+// The bounded wait every pipeline role of the GEMM kernels uses, exercised on a barrier that nobody
+// arrives at: the wait gives up after `limit_cycles`, records `code` in *status, and the kernel
+// returns normally.
+__global__ void bounded_wait_selftest_kernel(long long limit_cycles, int32_t* status, int code) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(&bar), 1);
+        abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    __syncthreads();
+    volatile int* af = &abort_flag;
+    // two waiters: the first to run out sets the abort flag, the other leaves through it
+    if (threadIdx.x == 0 || threadIdx.x == 32) ptx::mbar_wait_limit(ptx::smem_u32(&bar), 0, af, status, code, limit_cycles);
+    __syncthreads();
+}
+
 static int fill_peers(const char* who, void* const* ptrs, int n_peers, PeerOut* po) {
     if (!ptrs || n_peers < 1 || n_peers > MAX_PEERS)
         return fail(SF_ERR_BAD_ARG, "%s: 1..%d destination pointers expected, got %d", who, MAX_PEERS, n_peers);
@@ -813,6 +831,18 @@ static int fill_peers(const char* who, void* const* ptrs, int n_peers, PeerOut* 
         po->ptr[i] = (__nv_bfloat16*)ptrs[i];
     }
     po->count = n_peers;
+    return SF_OK;
+}
+
+int sf_selftest_bounded_wait(double limit_ms, int32_t* status, void* stream) {
+    SF_CHECK_ARG(status != nullptr, "sf_selftest_bounded_wait: status must be non-null");
+    SF_CHECK_ARG(limit_ms > 0.0 && limit_ms <= 100.0, "sf_selftest_bounded_wait: limit_ms must be in (0, 100]");
+    int dev = 0, khz = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    SF_CHECK_CUDA(cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, dev));
+    const long long cycles = (long long)(limit_ms * (double)khz);
+    bounded_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(cycles, status, 99);
+    SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
 

@@ -48,8 +48,8 @@ constexpr long long kWaitLimitCycles = 4000000000LL;
 // Waits for the phase with the given parity. Returns false if the wait ran out or another
 // role of this CTA already gave up (abort_flag in shared memory); the first to give up
 // stores `code` into *status (global, may be null).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                int32_t* status, int code, long long limit_cycles) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
@@ -57,12 +57,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         for (int i = 0; i < 64; ++i)
             if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > kWaitLimitCycles) {
+        if (clock64() - t0 > limit_cycles) {
             *abort_flag = 1;
             if (status) atomicCAS(status, 0, code);
             return false;
         }
     }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int code) {
+    return mbar_wait_limit(bar, parity, abort_flag, status, code, kWaitLimitCycles);
 }
 
 // ---- TMA -------------------------------------------------------------------------------

@@ -70,6 +70,23 @@ def hutch_accumulate(H, hvp, v, *, beta=0.99) -> None:
                                hvp.numel(), float(beta), _lib.METRICS["hessian_obd"], _stream()), "sf_hutch_score")
 
 
+def mask_update_nm24_from_weight(W, H, norm, mask, stats, wm, meta, *, metric="hessian_obd", tau=None, temperature=1.0,
+                                 mask_lr=0.1, pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0,
+                                 hx=1.0, structured_exact=False) -> None:
+    """``mask_update_nm24`` with the score formed inside the pass from W and H (no score tensor)."""
+    _cuda(W, H, norm, mask, stats, wm, meta, tau)
+    if mask.dtype != torch.float32 or (H is not None and H.dtype != torch.float32) or stats.dtype != torch.float64:
+        raise TypeError("mask_update_nm24_from_weight: mask / H float32, stats float64")
+    if wm.dtype != W.dtype:
+        raise TypeError("mask_update_nm24_from_weight: wm must have W's dtype")
+    rows, cols = mask.shape
+    check(lib().sf_mask_update_nm24_from_weight(_p(W), _dt(W), _p(H), _lib.METRICS[metric], _p(norm), _p(tau), _p(mask),
+                                                _p(wm), _p(meta), _p(stats), rows, cols, float(temperature),
+                                                float(mask_lr), float(pen), int(penalty_mode), float(beta_s),
+                                                float(binarize_decay), float(hx), int(bool(structured_exact)),
+                                                _stream()), "sf_mask_update_nm24_from_weight")
+
+
 def score_sum(a, b, out, norm, scratch) -> None:
     """out <- a + b (fp32 scores of a gate / up pair); norm <- (mean, std + 1e-6) of out."""
     _cuda(a, b, out, norm, scratch)
@@ -152,7 +169,7 @@ def adamw_masked(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, 
 
 
 def adamw_masked_score(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, decay, step, adaptive_l1=0.0,
-                       H=None, score, norm, scratch, metric: str, hvp=None, probe=None, beta_h=0.99) -> None:
+                       H=None, score=None, norm, scratch, metric: str, hvp=None, probe=None, beta_h=0.99) -> None:
     """AdamW step and, in the same pass, the importance score of the updated weight with its mean/std.
     With hvp and probe the Hutchinson sample is folded into H first (as hutch_accumulate does)."""
     _cuda(p, g, m, v, mask, H, score, norm, scratch, hvp, probe)
@@ -165,7 +182,7 @@ def adamw_masked_score(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_d
         raise TypeError("adamw_masked_score: p, g, m, v must share a dtype")
     if mask is not None and mask.dtype != torch.float32:
         raise TypeError("adamw_masked_score: mask must be float32")
-    if score.dtype != torch.float32 or (H is not None and H.dtype != torch.float32):
+    if (score is not None and score.dtype != torch.float32) or (H is not None and H.dtype != torch.float32):
         raise TypeError("adamw_masked_score: H and score must be float32")
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step

@@ -299,3 +299,18 @@ def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
         ops.gemm_fwd_allgather(x[:64], wms[0], [y_all[0].data_ptr()], out_total, 0)  # too few rows for the pair kernel
     with pytest.raises(RuntimeError):
         ops.gemm_fwd_allgather(x, wms[0], [y_all[0].data_ptr()], out_total, out_total)  # columns out of range
+
+
+def test_a_wait_that_runs_out_reports_and_returns(ops):
+    """The bounded wait of the pipeline roles, on a barrier nobody arrives at: the kernel returns,
+    the status word holds the code, and the next product on the same context is correct."""
+    from sparseforge_b200 import _lib
+
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    _lib.check(_lib.lib().sf_selftest_bounded_wait(5.0, status.data_ptr(), torch.cuda.current_stream().cuda_stream),
+               "sf_selftest_bounded_wait")
+    torch.cuda.synchronize()
+    assert int(status[0]) == 99
+    x = torch.randn(256, 64, device=DEV).to(torch.bfloat16)
+    w = torch.randn(128, 64, device=DEV).to(torch.bfloat16)
+    assert rel_err(ops.gemm_fwd(x, w).float(), x.float() @ w.float().t()) <= 1e-2

@@ -310,6 +310,39 @@ def test_adamw_with_score_equals_separate_calls(ops, dtype, metric):
     assert rel_err(sb, want.float()) <= (F32_TOL if dtype == torch.float32 else BF16_TOL)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("metric,extra", [("hessian_obd", {}), ("hessian_ratio", dict(pen=0.03, penalty_mode=2)),
+                                          ("magnitude", dict(beta_s=0.3, binarize_decay=0.05)), ("hessian", {})])
+def test_mask_update_from_weight_equals_update_from_score(ops, dtype, metric, extra):
+    """Forming the score inside the mask update from W and H gives, bit for bit, the update from the
+    score tensor the optimizer pass would have written; that pass then only needs the statistics."""
+    torch.manual_seed(21)
+    rows, cols = 80, 136
+    W = dev((torch.randn(rows, cols) * 0.05).to(dtype))
+    g0 = dev((torch.randn(rows, cols) * 0.01).to(dtype))
+    H = dev(torch.rand(rows, cols) * 1e-2)
+    mask0 = torch.rand(rows, cols)
+    kw = dict(lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, decay=2e-4, step=2)
+    upd = dict(temperature=0.3, mask_lr=0.2, hx=0.4, **extra)
+
+    def run(with_score):
+        p, m, v = W.clone(), torch.zeros_like(W), torch.zeros_like(W)
+        mask, stats = dev(mask0), torch.zeros(8, dtype=torch.float64, device=DEV)
+        norm, scr = torch.empty(2, device=DEV), ops.hutch_score_scratch(DEV)
+        wm, meta = torch.empty_like(p), torch.zeros(rows, cols // 8, dtype=torch.uint8, device=DEV)
+        score = torch.empty(rows, cols, device=DEV) if with_score else None
+        ops.adamw_masked_score(p, g0, m, v, mask=mask, H=H, score=score, norm=norm, scratch=scr, metric=metric, **kw)
+        if with_score:
+            ops.mask_update_nm24(score, norm, mask, stats, W=p, wm=wm, meta=meta, **upd)
+        else:
+            ops.mask_update_nm24_from_weight(p, H, norm, mask, stats, wm, meta, metric=metric, **upd)
+        return p, mask, wm, meta, stats, norm
+
+    a, b = run(True), run(False)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+
+
 # ---------------------------------------------------------------------------------------
 # argument checks: bad calls are refused on the host, nothing is launched
 # ---------------------------------------------------------------------------------------
