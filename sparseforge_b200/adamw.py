@@ -81,6 +81,20 @@ class AdamW(Optimizer):
                 owner = getattr(p, "_sf_owner", None)
                 layer = owner() if owner is not None else None
                 wm, hx = (None, 1.0)
+                fused = layer._optimizer_score_target() if (layer is not None and mask is not None) else None
+                if fused is not None:
+                    # the mask update of this step follows: write the score of the new weight here
+                    # and leave the masked weight to that update
+                    metric, H = fused
+                    ops.adamw_masked_score(p.data, grad.contiguous(), state["exp_avg"], state["exp_avg_sq"],
+                                           mask=mask.data.contiguous(), lr=group["lr"], beta1=beta1, beta2=beta2,
+                                           eps=group["eps"], weight_decay=group["weight_decay"], decay=float(self.decay),
+                                           step=state["step"], adaptive_l1=self.adaptive_l1_decay, H=H,
+                                           score=layer._score, norm=layer._norm, scratch=layer._scratch, metric=metric)
+                    layer._optimizer_wrote_score()
+                    continue
+                if layer is not None:
+                    layer._score_key = None
                 if layer is not None and mask is not None and layer.mode == "sparse_forward" \
                         and layer.mask_type == "structured":
                     wm, hx = layer._adamw_emit_target()

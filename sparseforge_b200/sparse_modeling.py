@@ -325,6 +325,13 @@ class SparseLinear(nn.Linear):
         self.last_mask_stats = None  # device float64[8] written by the last update_mask
         self._row_shard_group = None  # set by sharding.RowShardedLinear when this is one shard of a layer
         self._row_sharded = False
+        # Score fusion with the optimizer: when the last update_mask call predicts that the next step
+        # updates the mask too, this package's AdamW writes the score of the new weight in its own
+        # pass (and leaves the masked weight to the mask update), and the Hutchinson accumulation
+        # only updates H. _score_key records what that score was computed from.
+        self.fuse_score_with_optimizer = True
+        self._fuse_score_next = False
+        self._score_key = None
 
     # -- helpers -------------------------------------------------------------------------
     def _apply(self, fn, recurse=True):
@@ -582,6 +589,12 @@ class SparseLinear(nn.Linear):
         if self._is_placeholder("hessian_diag"):
             return
         self._buffers_ready()
+        self._score_key = None
+        if self._optimizer_score_target() is not None:
+            # the optimizer pass of this step scores the weight it writes: only H is updated here
+            ops.hutch_accumulate(self.hessian_diag.data, hvp.contiguous(), v.contiguous(),
+                                 beta=float(self.cfg.beta if beta is None else beta))
+            return
         ops.hutch_score(self.weight.data, self.hessian_diag.data, self._score, self._norm, self._scratch,
                         hvp=hvp.contiguous(), v=v.contiguous(), beta=float(self.cfg.beta if beta is None else beta),
                         metric=self.mask_metric if self.mask_metric in _SUPPORTED_METRICS else "hessian_obd")
@@ -639,12 +652,10 @@ class SparseLinear(nn.Linear):
     def _refresh_score(self):
         """Raw score of the current weights and its mean / std, without touching the Hessian."""
         self._buffers_ready()
-        metric = self.mask_metric
-        if metric not in _SUPPORTED_METRICS:
-            metric = "magnitude"
-        H = None if self._is_placeholder("hessian_diag") else self.hessian_diag.data
-        if H is None and metric in ("hessian_obd", "hessian_ratio", "hessian"):
-            metric = "magnitude"
+        if self._score_key is not None and self._score_key == self._score_state():
+            return  # written by the optimizer pass of this step; weight and Hessian untouched since
+        self._score_key = None
+        metric, H = self._resolved_metric()
         aux = None
         if metric == "movement":
             if self._is_placeholder("grad_ema"):
@@ -654,6 +665,46 @@ class SparseLinear(nn.Linear):
         ops.hutch_score(self.weight.data, H, self._score, self._norm, self._scratch, aux=aux,
                         aux_scalar=float(self.cfg.temperature), metric=metric)
         self._combine_shard_norm()
+
+    def _resolved_metric(self):
+        """(metric, H) the score is computed with: metrics that lack their tensor fall back to the
+        magnitude, as the reference does (legacy/sparse_modeling.py:1041-1079)."""
+        metric = self.mask_metric
+        if metric not in _SUPPORTED_METRICS:
+            metric = "magnitude"
+        H = None if self._is_placeholder("hessian_diag") else self.hessian_diag.data
+        if H is None and metric in ("hessian_obd", "hessian_ratio", "hessian"):
+            metric = "magnitude"
+        return metric, H
+
+    def _score_state(self):
+        H = None if self._is_placeholder("hessian_diag") else self.hessian_diag
+        return (self.weight.data_ptr(), self.weight._version, 0 if H is None else H.data_ptr(),
+                0 if H is None else H._version, self.mask_metric)
+
+    def _optimizer_score_target(self):
+        """What this package's AdamW needs to write the score in its own pass, or None when the
+        next step is not expected to update the mask (or the metric needs another tensor)."""
+        if not (self.fuse_score_with_optimizer and self._fuse_score_next and self.change_mask):
+            return None
+        metric, H = self._resolved_metric()
+        if metric == "movement" or self.mode != "sparse_forward":
+            return None
+        self._check_2to4()
+        self._buffers_ready()
+        return metric, H
+
+    def _optimizer_wrote_score(self):
+        self._combine_shard_norm()
+        self._score_key = self._score_state()
+        self.weight._sf_wm_stale = True  # the masked weight is rewritten by the mask update that follows
+        self.weight._sf_managed = True
+        self._wm_key = None
+
+    def _predict_mask_update(self, step: int) -> bool:
+        if (not self.change_mask) or self.mask_type == "none" or step < int(self.cfg.sparsity_warmup_steps):
+            return False
+        return step % max(1, int(self._mask_update_period(step))) == 0
 
     def _combine_shard_norm(self):
         """Score mean / std are taken over the whole layer: when this module is one row shard, add up
@@ -775,6 +826,7 @@ class SparseLinear(nn.Linear):
                              structured_exact=bool(getattr(cfg, "structured_exact", False)),
                              score_bf16=score_bf16, pen_mask=pen_mask)
         self.hardening_x = hx_new
+        self._fuse_score_next = self._predict_mask_update(step + 1)
         self.last_mask_stats = self._stats
         self._wm_key = self._current_key()
         self.weight._sf_wm_stale = False

@@ -84,6 +84,26 @@ def update_mask_penalty_lr(model, step: int, max_steps: int, penalty_lr_min: flo
     return cur
 
 
+def all_ranks_ok(ok: bool, device=None) -> bool:
+    """True only if every rank passes True (the ok-flag the reference all-reduces with MIN after
+    steps that may fail on one rank only, legacy/main_llama.py:637-651, 771-788). A rank that caught
+    an exception passes False and every rank learns of it before the next collective."""
+    if not (dist.is_available() and dist.is_initialized()) or dist.get_world_size() == 1:
+        return bool(ok)
+    if device is None:
+        device = torch.device("cuda", torch.cuda.current_device()) if dist.get_backend() == "nccl" else torch.device("cpu")
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    return bool(int(flag.item()))
+
+
+def loss_is_finite_on_all_ranks(loss: torch.Tensor) -> bool:
+    """The training loop's guard (legacy/main_llama.py:2075-2108): if the loss of any rank is not
+    finite, every rank skips backward and the optimizer step, so that the collectives of the
+    sharded step stay matched."""
+    return all_ranks_ok(bool(torch.isfinite(loss.detach()).all().item()), device=loss.device)
+
+
 def _identify_glu_pairs(sparse_modules_dict):
     """{gate name: up name} of the GLU pairs whose gate layer asks for a joint mask
     (``...mlp.gate_proj`` / ``up_proj`` and ``...mlp.w1`` / ``w3``): legacy/utils.py:313-360."""

@@ -312,3 +312,45 @@ def test_slorb_bypass_follows_the_reference(tag, trainable):
         assert rel_err(layer.x_proj.grad, g[f"{tag}_dP"]) <= 1e-5
     else:
         assert layer.x_proj.grad is None
+
+
+def test_score_fusion_with_the_optimizer_changes_nothing():
+    """The module path with the score written by the optimizer pass (and the Hutchinson step
+    updating H only) against the same loop with separate score passes: identical weights, masks,
+    Hessians and flip counts after every step."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("train_loop")
+    hp = json.loads(str(g["hp_json"]))
+    cfgd = json.loads(str(g["cfg_json"]))
+    X, Yt = g["X"].to(DEV), g["Yt"].to(DEV)
+    runs = []
+    for fuse in (False, True):
+        model, _ = _build(g, "init/")
+        U.initialize_model(model)
+        for m in (model.fc1, model.fc2):
+            m.fuse_score_with_optimizer = fuse
+        opt = sf.AdamW([model.fc1.weight, model.fc1.bias, model.fc2.weight], lr=hp["lr"], betas=tuple(hp["betas"]),
+                       weight_decay=hp["weight_decay"], srste_decay=cfgd["srste_decay"])
+        trace = []
+        for it in range(4):
+            loss = torch.nn.functional.mse_loss(model(X[it]), Yt[it]) + U.mid_penalty(model, 0.1)
+            queue = [g[f"s{it}_probe{j}"].to(DEV).float() for j in range(2)]
+            U._rademacher_like = lambda t, q=queue: q.pop(0)
+            U.update_hessian_hutchinson(model, loss)
+            loss.backward()
+            opt.step(decay=1e-4)
+            opt.zero_grad(set_to_none=True)
+            if it == 2:  # a forward between the optimizer and the mask update sees the new weight
+                with torch.no_grad():
+                    trace.append(model(X[it]).clone())
+            U.calculate_model_mask(model, it, lambda_mid=0.1)
+            for m in (model.fc1, model.fc2):
+                trace += [m.weight.data.clone(), m.mask.data.clone(), m.hessian_diag.data.clone(),
+                          torch.tensor(int(m.weight.flipped_mask)), m.masked_weight().clone()]
+        assert model.fc1._fuse_score_next  # every step updates the mask in this recipe
+        runs.append(trace)
+    assert len(runs[0]) == len(runs[1])
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)

@@ -66,6 +66,44 @@ def test_row_sharded_layer_matches_unsharded_on_two_gloo_ranks():
     assert results == {0: True, 1: True}
 
 
+def _guard_worker(rank, world, port, out_q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from sparseforge_b200 import utils as U
+
+        # step 0: every rank is fine; step 1: rank 1 sees a NaN loss; step 2: rank 0's step raises
+        seen = []
+        seen.append(U.loss_is_finite_on_all_ranks(torch.tensor(1.5)))
+        seen.append(U.loss_is_finite_on_all_ranks(torch.tensor(float("nan") if rank == 1 else 2.0)))
+        try:
+            if rank == 0:
+                raise RuntimeError("injected host-side failure")
+            ok = True
+        except RuntimeError:
+            ok = False
+        seen.append(U.all_ranks_ok(ok))
+        seen.append(U.all_ranks_ok(True))  # the group is still usable afterwards
+        out_q.put((rank, seen))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_one_failing_rank_makes_every_rank_skip_the_step():
+    """Failure detection as the reference does it: on the host, through an all-reduced ok-flag."""
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_guard_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    results = dict(q.get(timeout=10) for _ in range(world))
+    assert results == {0: [True, False, False, True], 1: [True, False, False, True]}
+
+
 def test_single_process_is_a_no_op():
     from sparseforge_b200.sharding import gather_columns, sum_input_grad
 
