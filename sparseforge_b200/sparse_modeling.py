@@ -792,6 +792,8 @@ class SparseLinear(nn.Linear):
             return
         if self.mask.dim() != 2 or self.weight.shape != self.mask.shape:
             return
+        # the optimizer pass of the next step writes the score if that step updates the mask
+        self._fuse_score_next = self._predict_mask_update(step + 1)
         if (not self.change_mask) or (self.mask_type == "none"):
             self.weight.flipped_mask = 0
             self.weight.init_flipped_mask = 0

@@ -1,9 +1,9 @@
 """Generates the golden fixtures in this directory by RUNNING THE REFERENCE ITSELF.
 
 Run where the SparseForge reference is available (it is imported, unmodified, from
-``$SPARSEFORGE_REFERENCE/legacy``, default ``/root/reference/legacy``):
+``$SPARSEFORGE_REFERENCE/legacy``):
 
-    WANDB_MODE=disabled python tests/golden/make_golden.py
+    SPARSEFORGE_REFERENCE=<checkout of liuhanzuo/SparseForge> WANDB_MODE=disabled python tests/golden/make_golden.py
 
 The reference runs on torch CPU with ``torch.topk`` replaced by a tie-stable version (equal
 values: lower index first), the tie rule this path is specified with; ``ties.npz`` also
@@ -23,7 +23,9 @@ os.environ.setdefault("WANDB_MODE", "disabled")
 import numpy as np
 import torch
 
-REF = os.environ.get("SPARSEFORGE_REFERENCE", "/root/reference")
+REF = os.environ.get("SPARSEFORGE_REFERENCE")
+if not REF or not os.path.isdir(os.path.join(REF, "legacy")):
+    raise SystemExit("set SPARSEFORGE_REFERENCE to a checkout of the SparseForge reference (the directory holding legacy/)")
 sys.path.insert(0, os.path.join(REF, "legacy"))
 HERE = os.path.dirname(os.path.abspath(__file__))
 
