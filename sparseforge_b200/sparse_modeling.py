@@ -424,8 +424,11 @@ class SparseLinear(nn.Linear):
 
     # -- masked weight cache ---------------------------------------------------------------
     def invalidate_masked_weight(self):
-        """Call after changing ``weight`` or ``mask`` outside ``update_mask`` / the AdamW of this package."""
+        """Call after changing ``weight``, ``mask`` or ``hessian_diag`` through ``.data`` (edits that
+        autograd's version counters do not see) outside ``update_mask`` / the AdamW of this package:
+        drops the cached masked weight and the score the optimizer pass may have left."""
         self._wm_key = None
+        self._score_key = None
 
     def _adamw_emit_target(self):
         """(wm buffer, hx) the AdamW kernel should write the new masked weight with."""

@@ -167,6 +167,7 @@ def test_sparse_linear_chain(case, dtype, tol, steps_cfg):
         assert rel_err(st["exp_avg"].float(), g[f"s{t}_m"].float()) <= tol
         assert rel_err(st["exp_avg_sq"].float(), g[f"s{t}_v"].float()) <= tol
         layer.weight.data.copy_(g[f"s{t}_W_opt"].to(DEV))
+        layer.invalidate_masked_weight()  # a .data edit: the score left by the optimizer pass is stale
         st["exp_avg"].copy_(g[f"s{t}_m"].to(DEV)); st["exp_avg_sq"].copy_(g[f"s{t}_v"].to(DEV))
         assert layer._temperature(t) == pytest.approx(g.scalar(f"s{t}_T"), rel=1e-12)
         G = layer.compute_gate_target(t)
