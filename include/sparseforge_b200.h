@@ -273,6 +273,30 @@ SF_API int sf_adamw_masked_score(void* p, const void* g, const float* mask, void
 SF_API int sf_mask_stats(const float* mask, double* stats, int64_t rows, int64_t cols, void* stream);
 
 /*
+ * Block-granular soft masks (hard_mask_type block_sparse16 / block_sparse32).
+ *   replaces: the block branches of legacy/sparse_modeling.py: gate :1122-1157, _blockify_tensor
+ *             :461-508, penalty :1395-1530, mask blockify :1600, hard projection :607-718.
+ * The layer-wide decisions (quantile of the block scores, top-k blocks) are taken by the caller on
+ * [rows/bs, cols/bs] arrays; these three entries are the passes over the layer itself.
+ * sf_block_sums: sum[b], sumsq[b] (sumsq may be NULL) over every whole bs x bs block of x; with
+ *   norm != NULL over (x - norm[0]) / norm[1] (the normalised score). bs = 16 or 32.
+ * sf_block_mask_update: every element m of a whole block b moves to clamp((1-a) m + a G', 0, 1) with
+ *   G' = gate[b], pulled by clamp(G' - pen (m - target[b]), 0, 1) when pen != 0 and pushed away from
+ *   0.5 by the binarise factor; only new_sum[b], the block sums of the result, are written for
+ *   whole blocks (sf_block_mask_apply re-writes them block-constant); elements beyond the whole
+ *   blocks are updated in place with gate 1 and target 1.
+ * sf_block_mask_apply: inside the whole blocks mask <- value[b] (value = NULL keeps the mask) and
+ *   wm <- W * cast(hx * mask + (1 - hx) * keep[b]) (keep = 1 beyond the whole blocks); wm may be NULL.
+ */
+SF_API int sf_block_sums(const float* x, int64_t rows, int64_t cols, int bs, const float* norm, float* sum,
+                  float* sumsq, void* stream);
+SF_API int sf_block_mask_update(float* mask, int64_t rows, int64_t cols, int bs, const float* gate,
+                         const float* target, double mask_lr, double pen, double binarize_decay,
+                         float* new_sum, void* stream);
+SF_API int sf_block_mask_apply(float* mask, const void* W, int w_dtype, void* wm, int64_t rows, int64_t cols,
+                        int bs, const float* value, const uint8_t* keep, double hx, void* stream);
+
+/*
  * Logging summary of the soft masks.
  *   replaces: mask_stats legacy/utils.py:2069-2280 (the per-layer accumulation :2117-2154; the
  *             caller adds layers up, all-reduces and forms mean / std / entropy / fractions).

@@ -191,6 +191,85 @@ def mask_update(mask, G, *, mask_lr, lambda_mid=0.0, pen_lr=None, penalty_mode="
     return mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0)
 
 
+# --------------------------------------------------------------------------------------
+# block-sparse soft masks (hard_mask_type block_sparse16 / block_sparse32)
+# --------------------------------------------------------------------------------------
+def _block_view(x, bs):
+    rows, cols = x.shape
+    ob, ib = rows // bs, cols // bs
+    return x[: ob * bs, : ib * bs].float().reshape(ob, bs, ib, bs), ob, ib
+
+
+def block_keep(block_values, sparsity_ratio):
+    """0/1 [ob, ib]: the round((1 - sr) * blocks) largest blocks, ties to the lower flat index
+    (legacy/sparse_modeling.py:621-637 with a tie-stable top-k)."""
+    flat = block_values.flatten()
+    total = flat.numel()
+    k = max(0, min(total, int(round((1.0 - float(sparsity_ratio)) * total))))
+    keep = torch.zeros(total)
+    if k > 0:
+        keep[stable_topk_indices(flat, k)] = 1.0
+    return keep.view_as(block_values)
+
+
+def _expand_blocks(block_values, like, bs, fill=1.0):
+    ob, ib = block_values.shape
+    out = torch.full(like.shape, float(fill), dtype=torch.float32)
+    out[: ob * bs, : ib * bs] = block_values.float().repeat_interleave(bs, 0).repeat_interleave(bs, 1)
+    return out
+
+
+def blockify(x, bs):
+    """legacy/sparse_modeling.py:461-508: block means broadcast over each whole block."""
+    tiles, ob, ib = _block_view(x, bs)
+    out = x.clone().float()
+    out[: ob * bs, : ib * bs] = tiles.mean(dim=(1, 3)).repeat_interleave(bs, 0).repeat_interleave(bs, 1)
+    return out.to(x.dtype)
+
+
+def hard_mask_block(soft, bs, sparsity_ratio):
+    """legacy/sparse_modeling.py:607-718: whole blocks kept by the RMS of the soft mask per block; the
+    ragged tail stays 1."""
+    tiles, ob, ib = _block_view(soft, bs)
+    rms = (tiles ** 2).mean(dim=(1, 3)).sqrt()
+    return _expand_blocks(block_keep(rms, sparsity_ratio), soft, bs).to(soft.dtype)
+
+
+def gate_target_block(scores_norm, bs, sparsity, temperature):
+    """legacy/sparse_modeling.py:1122-1157: RMS of the normalised scores per block, threshold at the
+    quantile of the block values, sigmoid at the temperature; 1 in the ragged tail."""
+    tiles, ob, ib = _block_view(scores_norm, bs)
+    rms = (tiles ** 2).mean(dim=(1, 3)).sqrt()
+    tau = torch.quantile(rms.flatten().float(), q=float(sparsity))
+    Tt = torch.tensor(float(temperature), dtype=torch.float32)
+    return _expand_blocks(torch.sigmoid((rms.float() - tau) / (Tt + 1e-8)), scores_norm, bs).to(scores_norm.dtype)
+
+
+def mask_update_block(mask, G, bs, *, mask_lr, sparsity_ratio, lambda_mid=0.0, pen_lr=None, penalty_mode="mid",
+                      binarize_decay=0.0):
+    """legacy/sparse_modeling.py:1395-1530 (block penalty: pull towards the top blocks by the block
+    MEAN of the current mask), :1567-1593 (mid pull, clamp, binarise push, EMA), :1600 (blockify)."""
+    a = float(mask_lr)
+    pen_lr = a if pen_lr is None else float(pen_lr)
+    if float(lambda_mid) != 0.0:
+        if penalty_mode in ("block_sparse16", "block_sparse32"):
+            tiles, ob, ib = _block_view(mask, bs)
+            target = _expand_blocks(block_keep(tiles.mean(dim=(1, 3)), sparsity_ratio), mask, bs)
+            G = G - (pen_lr * float(lambda_mid)) * (mask.to(G.dtype) - target.to(G.dtype))
+        elif penalty_mode == "mid":
+            G = G - (pen_lr * float(lambda_mid)) * (1.0 - 2.0 * mask).to(G.dtype)
+        else:
+            raise ValueError(penalty_mode)
+        G = G.clamp(0.0, 1.0)
+    d = float(binarize_decay)
+    if d != 0.0:
+        G = G.clone()
+        lt, gt = G < 0.5, G > 0.5
+        G[lt] = G[lt] * (1.0 - d)
+        G[gt] = G[gt] * (1.0 + d)
+    return blockify(mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0), bs)
+
+
 def glu_joint_update(gate_score, up_score, gate_mask, up_mask, *, temperature, mask_lr, lambda_mid=0.0,
                      pen_lr=None, penalty_mode="mid", binarize_decay=0.0, beta_s=0.0, exact=False):
     """Joint update of a GLU gate / up pair, legacy/utils.py:363-479: one gate target from the

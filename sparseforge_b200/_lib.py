@@ -42,6 +42,9 @@ _SIGNATURES = {
                                       c_double, c_double, c_double, c_double, c_double, _P, _P, c_int, c_double,
                                       _P, _P, _P, _P, c_int, _P]),
     "sf_mask_stats": (c_int, [_P, _P, c_int64, c_int64, _P]),
+    "sf_block_sums": (c_int, [_P, c_int64, c_int64, c_int, _P, _P, _P, _P]),
+    "sf_block_mask_update": (c_int, [_P, c_int64, c_int64, c_int, _P, _P, c_double, c_double, c_double, _P, _P]),
+    "sf_block_mask_apply": (c_int, [_P, _P, c_int, _P, c_int64, c_int64, c_int, _P, _P, c_double, _P]),
     "sf_mask_summary": (c_int, [_P, c_int64, c_double, _P, _P]),
     "sf_mask_sample_hist": (c_int, [_P, _P, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_float, c_int, _P, _P]),

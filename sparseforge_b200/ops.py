@@ -200,6 +200,38 @@ def mask_stats(mask, stats) -> None:
     check(lib().sf_mask_stats(_p(mask), _p(stats), rows, cols, _stream()), "sf_mask_stats")
 
 
+def block_sums(x, bs, norm=None, want_sq=True):
+    """(sum, sumsq) over every whole bs x bs block of a float32 matrix, each [rows // bs, cols // bs]."""
+    _cuda(x, norm)
+    if x.dtype != torch.float32 or x.dim() != 2:
+        raise TypeError("block_sums: x must be a 2-D float32 tensor")
+    rows, cols = x.shape
+    ob, ib = rows // bs, cols // bs
+    s = torch.empty((ob, ib), dtype=torch.float32, device=x.device)
+    q = torch.empty((ob, ib), dtype=torch.float32, device=x.device) if want_sq else None
+    check(lib().sf_block_sums(_p(x), rows, cols, int(bs), _p(norm), _p(s), _p(q), _stream()), "sf_block_sums")
+    return s, q
+
+
+def block_mask_update(mask, bs, gate, target=None, *, mask_lr, pen=0.0, binarize_decay=0.0):
+    """EMA update of a block-mode soft mask; returns the per-block sums of the updated mask."""
+    _cuda(mask, gate, target)
+    rows, cols = mask.shape
+    new_sum = torch.empty_like(gate)
+    check(lib().sf_block_mask_update(_p(mask), rows, cols, int(bs), _p(gate), _p(target), float(mask_lr), float(pen),
+                                     float(binarize_decay), _p(new_sum), _stream()), "sf_block_mask_update")
+    return new_sum
+
+
+def block_mask_apply(mask, bs, keep, *, value=None, W=None, wm=None, hx=1.0) -> None:
+    _cuda(mask, keep, value, W, wm)
+    if keep.dtype != torch.uint8:
+        raise TypeError("block_mask_apply: keep must be uint8")
+    rows, cols = mask.shape
+    check(lib().sf_block_mask_apply(_p(mask), _p(W), _dt(W) if W is not None else SF_F32, _p(wm), rows, cols, int(bs),
+                                    _p(value), _p(keep), float(hx), _stream()), "sf_block_mask_apply")
+
+
 def mask_summary(mask, out, eps=1e-8) -> None:
     """Adds the twelve logging sums of one soft mask to ``out`` (float64[12])."""
     _cuda(mask, out)

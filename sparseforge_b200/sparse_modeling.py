@@ -354,6 +354,21 @@ class SparseLinear(nn.Linear):
     def _resolved_hard_type(self) -> str:
         return self.mask_type if self.hard_mask_type == "match" else self.hard_mask_type
 
+    def _block_size(self) -> int:
+        """16 / 32 in the block-sparse soft-mask modes, else 0."""
+        return {"block_sparse16": 16, "block_sparse32": 32}.get(self.hard_mask_type, 0)
+
+    def _block_keep(self, block_values: torch.Tensor) -> torch.Tensor:
+        """uint8 [ob, ib]: the round((1 - sparsity_ratio) * blocks) blocks with the largest value, ties
+        to the lower flat index (legacy/sparse_modeling.py:621-637, 671-687)."""
+        flat = block_values.flatten()
+        total = flat.numel()
+        keep_n = max(0, min(total, int(round((1.0 - float(self.sparsity_ratio)) * total))))
+        keep = torch.zeros(total, dtype=torch.uint8, device=flat.device)
+        if keep_n > 0:
+            keep[torch.sort(flat, descending=True, stable=True).indices[:keep_n]] = 1
+        return keep.view_as(block_values)
+
     def _buffers_ready(self):
         dev = self.weight.device
         if self._score is None or self._score.device != dev or self._score.shape != self.weight.shape:
@@ -391,10 +406,17 @@ class SparseLinear(nn.Linear):
         self.weight.init_flipped_mask = int(getattr(self.weight, "init_flipped_mask", 0))
         self.weight.param_count = int(getattr(self.weight, "param_count", self.weight.numel()))
 
+    @torch.no_grad()
     def _blockify_tensor(self, tensor):
-        if self.hard_mask_type in ("block_sparse16", "block_sparse32"):
-            raise NotImplementedError("block-sparse soft masks are outside the 2:4 kernel path")
-        return tensor
+        """Block means broadcast back over each whole block (legacy/sparse_modeling.py:461-508)."""
+        bs = self._block_size()
+        if not bs or tensor.dim() != 2 or tensor.shape[0] < bs or tensor.shape[1] < bs:
+            return tensor
+        out = tensor.float().contiguous().clone()
+        s, _ = ops.block_sums(out, bs, want_sq=False)
+        keep = torch.ones(s.shape, dtype=torch.uint8, device=out.device)
+        ops.block_mask_apply(out, bs, keep, value=(s / float(bs * bs)).contiguous())
+        return out.to(tensor.dtype)
 
     # -- hard projection -----------------------------------------------------------------
     @torch.no_grad()
@@ -407,6 +429,16 @@ class SparseLinear(nn.Linear):
             return (soft_mask > 0.5).to(dtype=soft_mask.dtype)
         if mt == "nm_2_4":
             return ops.project_nm24(soft_mask)[0]
+        if mt in ("block_sparse16", "block_sparse32"):
+            # whole blocks kept by the RMS of the soft mask over the block (:607-718)
+            bs = 16 if mt == "block_sparse16" else 32
+            hard = torch.ones_like(soft_mask, dtype=torch.float32)
+            if soft_mask.shape[0] < bs or soft_mask.shape[1] < bs:
+                return hard.to(soft_mask.dtype)
+            _, sq = ops.block_sums(soft_mask.float().contiguous(), bs)
+            keep = self._block_keep(torch.sqrt(sq / float(bs * bs)))
+            ops.block_mask_apply(hard, bs, keep, value=keep.float().contiguous())
+            return hard.to(soft_mask.dtype)
         if mt != "structured":
             raise ValueError(f"Invalid hard mask_type: {mt}")
         if int(self.N) != 2 or int(self.M) != 4:
@@ -453,6 +485,8 @@ class SparseLinear(nn.Linear):
         and ``update_mask`` then rewrite the cache whenever they change weight or mask); under a
         managed weight, code that edits ``weight.data`` or ``mask.data`` itself must call
         ``invalidate_masked_weight()``."""
+        if self._block_size():
+            return self._masked_weight_block()
         self._check_2to4()
         self._buffers_ready()
         key = self._current_key()
@@ -462,6 +496,21 @@ class SparseLinear(nn.Linear):
                                  hx=float(self.hardening_x), finalized=key[5])
             self._wm_key = key
             self.weight._sf_wm_stale = False
+        return self._wm
+
+    @torch.no_grad()
+    def _masked_weight_block(self) -> torch.Tensor:
+        """W * cast(hx * mask + (1 - hx) * block-hard(mask)) in the block-sparse modes, rebuilt on every
+        call (one pass for the block sums of the mask, one for the product)."""
+        bs = self._block_size()
+        self._buffers_ready()
+        hx = float(self.hardening_x)
+        fin = bool(getattr(self, "_hardening_finalized", False))
+        keep = torch.ones((self.out_features // bs, self.in_features // bs), dtype=torch.uint8, device=self.weight.device)
+        if not fin and hx < 1.0 - 1e-6:
+            _, sq = ops.block_sums(self.mask.data, bs)
+            keep = self._block_keep(torch.sqrt(sq / float(bs * bs)))
+        ops.block_mask_apply(self.mask.data, bs, keep, W=self.weight.data, wm=self._wm, hx=1.0 if fin else hx)
         return self._wm
 
     # -- forward -----------------------------------------------------------------------------
@@ -520,8 +569,8 @@ class SparseLinear(nn.Linear):
             return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)
         if self.mode != "sparse_forward":
             raise ValueError(f"Invalid mode: {self.mode}")
-        if self._resolved_hard_type() not in ("structured", "nm_2_4"):
-            raise NotImplementedError(f"hard mask type {self._resolved_hard_type()!r} is outside the 2:4 kernel path")
+        if self._resolved_hard_type() not in ("structured", "nm_2_4", "block_sparse16", "block_sparse32"):
+            raise NotImplementedError(f"hard mask type {self._resolved_hard_type()!r} is outside the kernel paths")
         hx = float(getattr(self, "hardening_x", 1.0))
         finalized = bool(getattr(self, "_hardening_finalized", False))
         scale = 1.0
@@ -617,7 +666,10 @@ class SparseLinear(nn.Linear):
     def _temperature(self, step: int) -> float:
         """legacy/sparse_modeling.py:932-942."""
         k = max(1, int(self._mask_update_period(step)))
-        t = float(self.cfg.temp_init) * (float(self.cfg.temp_decay) ** (step // k))
+        init = float(self.cfg.temp_init)
+        if self._block_size():
+            init *= float(getattr(self.cfg, "block_sparse_temp_mult", 2.0))
+        t = init * (float(self.cfg.temp_decay) ** (step // k))
         return float(max(float(self.cfg.temp_min), t))
 
     def _effective_sparsity(self, step: int) -> float:
@@ -625,7 +677,10 @@ class SparseLinear(nn.Linear):
         warm = int(self.cfg.sparsity_warmup_steps)
         if warm <= 0:
             return float(self.sparsity_ratio)
-        return float(self.sparsity_ratio * min(1.0, max(0.0, step / max(1, warm))))
+        r = min(1.0, max(0.0, step / max(1, warm)))
+        if self._block_size():
+            r = r * r * r
+        return float(self.sparsity_ratio * r)
 
     def _beta_structural(self, step: int) -> float:
         """legacy/sparse_modeling.py:966-985."""
@@ -731,6 +786,12 @@ class SparseLinear(nn.Linear):
         if (not self.change_mask) or (self.mask_type == "none"):
             return torch.ones_like(self.mask)
         self._check_mask_modes()
+        if self._block_size():
+            bs = self._block_size()
+            G = torch.ones_like(self.mask.data)
+            gate = self._block_gate(step)
+            ops.block_mask_apply(G, bs, torch.ones(gate.shape, dtype=torch.uint8, device=G.device), value=gate)
+            return G
         self._check_2to4()
         self._refresh_score()
         G = torch.zeros_like(self.mask.data)
@@ -746,6 +807,10 @@ class SparseLinear(nn.Linear):
         """Gate / projection combinations the 2:4 kernels cover."""
         if self.mask_type not in ("structured", "unstructured"):
             raise ValueError(f"Invalid mask_type: {self.mask_type}")
+        if self._block_size():
+            if self.mask_type != "unstructured":
+                raise NotImplementedError("block-sparse hard masks are built for mask_type='unstructured' (the block gate)")
+            return
         if self._resolved_hard_type() not in ("structured", "nm_2_4"):
             raise NotImplementedError(
                 f"hard mask type {self._resolved_hard_type()!r} with mask_type={self.mask_type!r} is outside the 2:4 "
@@ -806,6 +871,8 @@ class SparseLinear(nn.Linear):
         if step % max(1, int(self._mask_update_period(step))) != 0:
             return
         self._check_mask_modes()
+        if self._block_size():
+            return self._update_mask_block(step, lambda_mid)
         self._check_2to4()
         if not score_ready:
             self._refresh_score()
@@ -817,6 +884,62 @@ class SparseLinear(nn.Linear):
         self._launch_mask_update(self._score, self._norm, step, pen=float(self.mask_penalty_lr) * lam,
                                  pmode=pmode if lam != 0.0 else 0, tau=self._gate_tau(step), owner=self,
                                  score_bf16=self._score_is_bf16())
+
+    def _block_gate(self, step: int):
+        """Per-block gate of legacy/sparse_modeling.py:1122-1157: RMS of the normalised score over each
+        block, its quantile at the scheduled sparsity as threshold, a sigmoid at the temperature."""
+        bs = self._block_size()
+        self._refresh_score()
+        _, sq = ops.block_sums(self._score, bs, norm=self._norm)
+        rms = torch.sqrt(sq / float(bs * bs))
+        tau = torch.quantile(rms.flatten().float(), q=float(self._effective_sparsity(step)))
+        return torch.sigmoid((rms - tau) / (float(self._temperature(step)) + 1e-8)).contiguous()
+
+    def _update_mask_block(self, step: int, lambda_mid):
+        """update_mask in the block-sparse modes (legacy/sparse_modeling.py:1122-1157, 1395-1530, 1573-1663):
+        block gate, pull towards the top blocks of the current mask, binarise push, EMA, block means
+        written back over each block, hard view = top blocks by block RMS. Three passes over the layer
+        beside the score (block sums of score and of mask, the EMA) and one that rewrites mask and
+        masked weight; quantile and block ranking work on [out/bs, in/bs] arrays."""
+        bs = self._block_size()
+        if self.out_features < bs or self.in_features < bs or self.in_features % 4 != 0:
+            raise NotImplementedError("block-sparse masks need at least one whole block and in_features % 4 == 0")
+        if self._beta_structural(step) > 0.0:
+            raise NotImplementedError("beta_structural mixing is an N:M target; it is not combined with block masks")
+        self._buffers_ready()
+        n = float(bs * bs)
+        gate = self._block_gate(step)
+        prev_sum, prev_sq = ops.block_sums(self.mask.data, bs)
+        keep_prev = self._block_keep(torch.sqrt(prev_sq / n))
+        lam = 0.0 if lambda_mid is None else float(lambda_mid)
+        mode = str(getattr(self.cfg, "mask_penalty_mode", "mid") or "mid")
+        pen, target = 0.0, None
+        if lam != 0.0:
+            scale = float(self.mask_penalty_lr) * lam
+            if mode in ("block_sparse16", "block_sparse32"):
+                if mode != self.hard_mask_type:
+                    raise NotImplementedError("block penalty and block hard mask must use the same block size")
+                # target: the top blocks by the MEAN of the current mask (:1420-1443)
+                pen, target = scale, self._block_keep(prev_sum / n).float().contiguous()
+            elif mode == "mid":
+                # G - s (1 - 2m) = G - (-2s) (m - 1/2)
+                pen, target = -2.0 * scale, torch.full_like(gate, 0.5)
+            else:
+                raise NotImplementedError(f"mask_penalty_mode={mode!r} is not combined with block masks")
+        new_sum = ops.block_mask_update(self.mask.data, bs, gate, target, mask_lr=float(self.cfg.mask_lr), pen=pen,
+                                        binarize_decay=float(getattr(self.cfg, "mask_binarize_decay", 0.0) or 0.0))
+        hx_new = self._next_hardening_x(step)
+        value = (new_sum / n).contiguous()
+        keep_new = self._block_keep(value)  # the mask is block-constant now: its block RMS is the value itself
+        ops.block_mask_apply(self.mask.data, bs, keep_new, value=value, W=self.weight.data, wm=self._wm, hx=hx_new)
+        self.hardening_x = hx_new
+        self._fuse_score_next = False
+        self._stats.zero_()
+        self._stats[_lib.MSTAT_FLIPS] = (keep_prev ^ keep_new).sum().double() * n
+        self.last_mask_stats = self._stats
+        self.weight.flipped_mask = _LazyInt(self._stats, _lib.MSTAT_FLIPS)
+        self.weight.init_flipped_mask = 0
+        self.weight.mask = self.mask
 
     def _launch_mask_update(self, score, norm, step, *, pen, pmode, tau, owner, score_bf16=False, pen_mask=None):
         """The fused update kernel on this layer's mask with the gate schedule (temperature, mask_lr,

@@ -503,6 +503,46 @@ def case_slorb():
     save("slorb", d)
 
 
+BLOCK_CASES = {
+    "bs16": dict(shape=(128, 160), cfg=dict(hard_mask_type="block_sparse16", mask_penalty_mode="block_sparse16",
+                                            mask_binarize_decay=0.05)),
+    "bs32": dict(shape=(128, 160), cfg=dict(hard_mask_type="block_sparse32", mask_penalty_mode="block_sparse32")),
+    "tail": dict(shape=(72, 104), cfg=dict(hard_mask_type="block_sparse16", mask_penalty_mode="mid")),
+}
+BLOCK_BASE = dict(mask_type="unstructured", mask_metric="hessian_obd", sparsity_ratio=0.5, mask_update_period=1,
+                  sparsity_warmup_steps=1, mask_lr=0.3, temp_init=0.5, temp_min=0.05, temp_decay=0.7,
+                  mask_hardening_start=2, mask_hardening_duration=2, mask_penalty_lr=0.2, tau_sample_size=1 << 30)
+
+
+def case_block_masks():
+    """Block-sparse soft masks (hard_mask_type block_sparse16 / 32): block gate, block penalty, EMA,
+    blockified mask, block hard view, masked forward (legacy/sparse_modeling.py:461-508, 607-718,
+    1122-1157, 1395-1530)."""
+    d = {"cases_json": np.asarray(json.dumps(BLOCK_CASES)), "base_json": np.asarray(json.dumps(BLOCK_BASE))}
+    for tag, spec in BLOCK_CASES.items():
+        torch.manual_seed(31 + len(tag))
+        out_f, in_f = spec["shape"]
+        cfg = ref_sm.SparseLinearConfig(**dict(BLOCK_BASE, **spec["cfg"]))
+        layer = ref_sm.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False)
+        layer.initialize()
+        with torch.no_grad():
+            layer.weight.copy_(torch.randn(out_f, in_f) * 0.05)
+            layer.hessian_diag.copy_(torch.rand(out_f, in_f) + 0.05)
+        put(d, f"{tag}_W", layer.weight.data); put(d, f"{tag}_H", layer.hessian_diag.data)
+        x = torch.randn(6, in_f)
+        put(d, f"{tag}_x", x)
+        for step in range(5):
+            lam = 0.25
+            put(d, f"{tag}_s{step}_G", layer.compute_gate_target(step))
+            layer.update_mask(step, lambda_mid=lam)
+            put(d, f"{tag}_s{step}_mask", layer.mask.data); put(d, f"{tag}_s{step}_hx", float(layer.hardening_x))
+            put(d, f"{tag}_s{step}_flips", int(layer.weight.flipped_mask))
+            put(d, f"{tag}_s{step}_hard", layer._hard_mask_from_soft(layer.mask.data))
+            put(d, f"{tag}_s{step}_T", layer._temperature(step)); put(d, f"{tag}_s{step}_sp", layer._effective_sparsity(step))
+            put(d, f"{tag}_s{step}_y", layer(x).detach())
+    save("block_masks", d)
+
+
 if __name__ == "__main__":
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
@@ -526,6 +566,7 @@ if __name__ == "__main__":
     case_mask_stats()
     case_kl_loss()
     case_slorb()
+    case_block_masks()
     case_penalty()
     case_ties()
     case_adamw()

@@ -1,0 +1,50 @@
+"""Block-sparse soft masks (hard_mask_type block_sparse16 / block_sparse32) against a trajectory
+recorded from the reference (tests/golden/block_masks.npz; generator case_block_masks):
+block gate, block penalty / mid pull, binarise push, EMA, blockified mask, block hard view, flip
+counts and the masked forward pass (legacy/sparse_modeling.py:461-508, 607-718, 1122-1157, 1395-1530).
+"""
+import json
+
+import pytest
+import torch
+
+from golden_io import Golden, rel_err
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+@pytest.mark.parametrize("tag", ["bs16", "bs32", "tail"])
+def test_block_sparse_soft_masks_follow_the_reference(tag):
+    import sparseforge_b200 as sf
+
+    g = Golden("block_masks")
+    spec = json.loads(str(g["cases_json"]))[tag]
+    cfg = sf.SparseLinearConfig(**dict(json.loads(str(g["base_json"])), **spec["cfg"]))
+    out_f, in_f = spec["shape"]
+    layer = sf.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False).to(DEV)
+    layer.initialize()
+    layer.weight.data.copy_(g[f"{tag}_W"].to(DEV))
+    layer.hessian_diag.data.copy_(g[f"{tag}_H"].to(DEV))
+    layer.invalidate_masked_weight()
+    x = g[f"{tag}_x"].to(DEV)
+    for step in range(5):
+        assert layer._temperature(step) == pytest.approx(g.scalar(f"{tag}_s{step}_T"), rel=1e-12)
+        assert layer._effective_sparsity(step) == pytest.approx(g.scalar(f"{tag}_s{step}_sp"), rel=1e-12, abs=1e-15)
+        assert rel_err(layer.compute_gate_target(step), g[f"{tag}_s{step}_G"]) <= 1e-5
+        layer.update_mask(step, lambda_mid=0.25)
+        assert rel_err(layer.mask.data, g[f"{tag}_s{step}_mask"]) <= 1e-5, (tag, step)
+        assert layer.hardening_x == pytest.approx(g.scalar(f"{tag}_s{step}_hx"))
+        assert int(layer.weight.flipped_mask) == g.scalar(f"{tag}_s{step}_flips"), (tag, step)
+        assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"{tag}_s{step}_hard"])
+        with torch.no_grad():
+            assert rel_err(layer(x), g[f"{tag}_s{step}_y"]) <= 1e-5
+    # the blockified tensor is block-constant and keeps the ragged tail
+    t = torch.rand(out_f, in_f, device=DEV)
+    b = layer._blockify_tensor(t)
+    bs = 16 if cfg.hard_mask_type == "block_sparse16" else 32
+    ob, ib = out_f // bs, in_f // bs
+    want = t.clone()
+    want[: ob * bs, : ib * bs] = t[: ob * bs, : ib * bs].reshape(ob, bs, ib, bs).mean(dim=(1, 3)) \
+        .repeat_interleave(bs, 0).repeat_interleave(bs, 1)
+    assert rel_err(b, want) <= 1e-6

@@ -124,3 +124,133 @@ def test_sharded_layer_matches_unsharded_on_two_gpus():
         r, v = q.get(timeout=10)
         results[r] = v
     assert results == {0: True, 1: True}, results
+
+
+def _ddp_worker(rank, world, port, q):
+    """Three steps of the training loop under DistributedDataParallel (each rank its half of the
+    batch) against the same steps computed in one process from both halves: gradients averaged,
+    clamp(hvp * v) averaged before the Hessian EMA (legacy/utils.py:860-865), masks identical."""
+    import datetime
+    import json
+    import sys
+    import traceback
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    try:
+        from torch.nn.parallel import DistributedDataParallel as DDP
+
+        sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+        import sparseforge_b200 as sf
+        from golden_io import Golden
+        from sparseforge_b200 import utils as U
+
+        g = Golden("train_loop")
+        hp, cfgd = json.loads(str(g["hp_json"])), json.loads(str(g["cfg_json"]))
+
+        class TinyMLP(torch.nn.Module):
+            def __init__(self):
+                super().__init__()
+                cfg = sf.SparseLinearConfig(**cfgd)
+                self.fc1 = sf.SparseLinear(64, 128, sparselinear_config=cfg, bias=True)
+                self.fc2 = sf.SparseLinear(128, 64, sparselinear_config=cfg, bias=False)
+
+            def forward(self, x):
+                return self.fc2(torch.nn.functional.gelu(self.fc1(x)))
+
+        def make():
+            m = TinyMLP().to(dev)
+            m.load_state_dict({str(k): g["init/" + str(k)].to(dev) for k in g["state_keys"]}, strict=True)
+            U.initialize_model(m)
+            o = sf.AdamW([m.fc1.weight, m.fc1.bias, m.fc2.weight], lr=hp["lr"], betas=tuple(hp["betas"]),
+                         weight_decay=hp["weight_decay"], srste_decay=cfgd["srste_decay"])
+            return m, o
+
+        dist_model, dist_opt = make()
+        ddp = DDP(dist_model, device_ids=[rank])
+        one_model, one_opt = make()
+
+        def rel(a, b):
+            return float((a.double() - b.double()).abs().max()) / max(float(b.double().abs().max()), 1e-30)
+
+        ok = True
+        X, Yt = g["X"].to(dev), g["Yt"].to(dev)
+        mse = torch.nn.functional.mse_loss
+        for it in range(3):
+            lam = 0.1
+            probes = [g[f"s{it}_probe{j}"].to(dev).float() for j in range(2)]
+            halves = [(X[it][2 * r:2 * r + 2], Yt[it][2 * r:2 * r + 2]) for r in range(world)]
+            # distributed: this rank's half
+            xb, yb = halves[rank]
+            loss = mse(ddp(xb), yb) + U.mid_penalty(ddp, lam)
+            queue = [p.clone() for p in probes]
+            U._rademacher_like = lambda t, qq=queue: qq.pop(0)
+            U.update_hessian_hutchinson(ddp, loss)
+            loss.backward()
+            torch.nn.utils.clip_grad_norm_(ddp.parameters(), hp["grad_clip"])
+            dist_opt.step(decay=1e-4)
+            dist_opt.zero_grad(set_to_none=True)
+            U.calculate_model_mask(ddp, it, lambda_mid=lam)
+            # one process: both halves, averaged by hand (run identically on every rank)
+            layers = (one_model.fc1, one_model.fc2)
+            ds = [torch.zeros_like(m.weight.data) for m in layers]
+            losses = []
+            for xh, yh in halves:
+                lh = mse(one_model(xh), yh) + U.mid_penalty(one_model, lam)
+                gr = torch.autograd.grad(lh, [m.weight for m in layers], create_graph=True, retain_graph=True)
+                hv = torch.autograd.grad(sum((a * v).sum() for a, v in zip(gr, probes)), [m.weight for m in layers],
+                                         retain_graph=True)
+                for d, h, v in zip(ds, hv, probes):
+                    d += torch.clamp((h * v).detach(), min=0.0) / world
+                losses.append(lh)
+            for m, d in zip(layers, ds):
+                m.accumulate_hutchinson(d, torch.ones_like(d))
+            (sum(losses) / world).backward()
+            torch.nn.utils.clip_grad_norm_(one_model.parameters(), hp["grad_clip"])
+            one_opt.step(decay=1e-4)
+            one_opt.zero_grad(set_to_none=True)
+            for m in layers:
+                m.update_mask(it, lambda_mid=lam)
+            for a, b in zip((dist_model.fc1, dist_model.fc2), layers):
+                ok = ok and rel(a.weight.data, b.weight.data) <= 1e-4
+                ok = ok and rel(a.hessian_diag.data, b.hessian_diag.data) <= 1e-4
+                ok = ok and rel(a.mask.data, b.mask.data) <= 1e-4
+                ok = ok and abs(int(a.weight.flipped_mask) - int(b.weight.flipped_mask)) <= 2
+            ok = ok and U.loss_is_finite_on_all_ranks(loss)
+        torch.cuda.synchronize()
+        dist.barrier()
+        q.put((rank, bool(ok)))
+    except Exception:
+        msg = traceback.format_exc()
+        print(f"[rank {rank}] {msg}", file=sys.stderr, flush=True)
+        q.put((rank, msg))
+        q.close()
+        q.join_thread()
+        os._exit(1)
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_training_loop_under_ddp_matches_one_process():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_ddp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=150)
+    for p in procs:
+        if p.is_alive():
+            p.kill()
+    results = {}
+    while not q.empty():
+        r, v = q.get(timeout=10)
+        results[r] = v
+    assert results == {0: True, 1: True}, results

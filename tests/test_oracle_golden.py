@@ -251,6 +251,41 @@ def test_slorb_bypass():
         assert rel_err(s_w.grad, g[f"{tag}_dS"]) <= F32_TOL
 
 
+@pytest.mark.parametrize("tag", ["bs16", "bs32", "tail"])
+def test_block_sparse_soft_masks(tag):
+    import json
+
+    g = Golden("block_masks")
+    spec = json.loads(str(g["cases_json"]))[tag]
+    cfg = dict(json.loads(str(g["base_json"])), **spec["cfg"])
+    bs = 16 if cfg["hard_mask_type"] == "block_sparse16" else 32
+    W, H = g[f"{tag}_W"], g[f"{tag}_H"]
+    mask = torch.ones(W.shape)
+    hx = 1.0
+    for step in range(5):
+        T = O.temperature_at(step, cfg["temp_init"] * 2.0, cfg["temp_decay"], cfg["temp_min"])
+        assert math.isclose(T, g.scalar(f"{tag}_s{step}_T"), rel_tol=1e-12)
+        sparsity = cfg["sparsity_ratio"] * min(1.0, step / cfg["sparsity_warmup_steps"]) ** 3
+        assert math.isclose(sparsity, g.scalar(f"{tag}_s{step}_sp"), rel_tol=1e-12, abs_tol=1e-15)
+        s = O.normalize_scores(O.importance_score(W, "hessian_obd", H=H))
+        G = O.blockify(O.gate_target_block(s, bs, sparsity, T), bs)
+        assert rel_err(G, g[f"{tag}_s{step}_G"]) <= F32_TOL
+        if step >= cfg["sparsity_warmup_steps"]:
+            new = O.mask_update_block(mask, G, bs, mask_lr=cfg["mask_lr"], sparsity_ratio=cfg["sparsity_ratio"],
+                                      lambda_mid=0.25, pen_lr=cfg["mask_penalty_lr"], penalty_mode=cfg["mask_penalty_mode"],
+                                      binarize_decay=cfg.get("mask_binarize_decay", 0.0))
+            flips = int(((O.hard_mask_block(mask, bs, 0.5) > 0.5) ^ (O.hard_mask_block(new, bs, 0.5) > 0.5)).sum())
+            assert flips == g.scalar(f"{tag}_s{step}_flips")
+            mask = new
+            hx = O.hardening_x(step, cfg["mask_hardening_start"], cfg["mask_hardening_duration"])
+        assert rel_err(mask, g[f"{tag}_s{step}_mask"]) <= F32_TOL
+        assert math.isclose(hx, g.scalar(f"{tag}_s{step}_hx"), abs_tol=1e-12)
+        hard = O.hard_mask_block(mask, bs, cfg["sparsity_ratio"])
+        assert torch.equal(hard, g[f"{tag}_s{step}_hard"])
+        eff = mask if hx >= 1.0 - 1e-6 else hx * mask + (1.0 - hx) * hard
+        assert rel_err(O.linear_forward(g[f"{tag}_x"], W, eff), g[f"{tag}_s{step}_y"]) <= F32_TOL
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
