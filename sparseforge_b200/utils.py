@@ -316,22 +316,35 @@ def mask_stats(model, bins: int = 100, eps: float = 1e-8, sample_per_layer: int 
     """Global statistics of the continuous masks (legacy/utils.py:2069-2280): mean, std, entropy,
     fractions below / above thresholds, and p10 / p50 / p90 from a histogram of a random sample of
     every layer. One read of each mask (one kernel) plus a gather of the sample; the sums are
-    all-reduced, so call it on every rank. The block statistics of the block-sparse modes are not
-    produced (those modes are outside this path)."""
+    all-reduced, so call it on every rank. Block-sparse layers add the mean mask value of the lower
+    and upper half of their blocks."""
     mods = [m for m in _sparse_modules(model) if m.mask.numel() > 0]
     device = mods[0].mask.device if mods else torch.device("cuda")
     acc = torch.zeros(12, dtype=torch.float64, device=device)
     hist = torch.zeros(int(bins), dtype=torch.float64, device=device)
+    blk = torch.zeros(5, dtype=torch.float64, device=device)  # blocks, lower-half sum / count, upper-half sum / count
     for m in mods:
         mk = m.mask.data
         ops.mask_summary(mk, acc, eps)
+        bs = m._block_size() if hasattr(m, "_block_size") else 0
+        if bs and mk.dim() == 2 and mk.shape[0] >= bs and mk.shape[1] >= bs and mk.shape[1] % 4 == 0:
+            # block-sparse layers: mean mask value of the lower and of the upper half of the blocks (:2155-2188)
+            sums, _ = ops.block_sums(mk, bs, want_sq=False)
+            means = torch.sort((sums / float(bs * bs)).flatten()).values.double()
+            half = means.numel() // 2
+            blk[0] += means.numel()
+            if half > 0:
+                blk[1] += means[:half].sum(); blk[2] += half
+                blk[3] += means[half:].sum(); blk[4] += means.numel() - half
         take = min(mk.numel(), int(sample_per_layer))
         if take > 0:
             idx = torch.randint(0, mk.numel(), (take,), device=device)
             ops.mask_sample_hist(mk, idx.to(torch.int64).contiguous(), hist)
     _all_reduce(acc)
     _all_reduce(hist)
+    _all_reduce(blk)
     a = [float(x) for x in acc.cpu()]
+    bk = [float(x) for x in blk.cpu()]
     tot = a[0]
     if tot <= 0:
         return {"mask_mean": 1.0, "mask_std": 0.0, "mask_entropy": 0.0, "mask_hard_sparsity@0.5": 0.0,
@@ -347,13 +360,19 @@ def mask_stats(model, bins: int = 100, eps: float = 1e-8, sample_per_layer: int 
         i = int(torch.searchsorted(cdf, torch.tensor([q], dtype=cdf.dtype)).item())
         return float((max(0, min(int(bins) - 1, i)) + 0.5) / int(bins))
 
-    return {
+    result = {
         "mask_mean": mean, "mask_std": std, "mask_entropy": a[3] / tot, "mask_hard_sparsity@0.5": a[4] / tot,
         "mask_frac_lt_0.1": a[5] / tot, "mask_frac_lt_0.01": a[6] / tot, "mask_frac_gt_0.9": a[7] / tot,
         "mask_frac_gt_0.99": a[8] / tot, "mask_frac_gt_0.5": a[9] / tot,
         "mask_mean_lt_0.5": a[10] / a[4] if a[4] > 0 else 0.0, "mask_mean_gt_0.5": a[11] / a[9] if a[9] > 0 else 0.0,
         "mask_p10": q_from_hist(0.10), "mask_p50": q_from_hist(0.50), "mask_p90": q_from_hist(0.90),
     }
+    if bk[0] > 0:
+        lower = bk[1] / bk[2] if bk[2] > 0 else 0.0
+        upper = bk[3] / bk[4] if bk[4] > 0 else 0.0
+        result.update({"blk_lower_half_mean": lower, "blk_upper_half_mean": upper, "blk_total_blocks": bk[0],
+                       "blk_separation": upper - lower})
+    return result
 
 
 @torch.no_grad()

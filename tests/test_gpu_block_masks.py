@@ -48,3 +48,22 @@ def test_block_sparse_soft_masks_follow_the_reference(tag):
     want[: ob * bs, : ib * bs] = t[: ob * bs, : ib * bs].reshape(ob, bs, ib, bs).mean(dim=(1, 3)) \
         .repeat_interleave(bs, 0).repeat_interleave(bs, 1)
     assert rel_err(b, want) <= 1e-6
+
+
+def test_mask_stats_block_keys():
+    """mask_stats of a block-sparse layer adds the lower / upper half block means (legacy/utils.py:2155-2188)."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("block_masks")
+    spec = json.loads(str(g["cases_json"]))["bs16"]
+    cfg = sf.SparseLinearConfig(**dict(json.loads(str(g["base_json"])), **spec["cfg"]))
+    layer = sf.SparseLinear(160, 128, sparselinear_config=cfg, bias=False).to(DEV)
+    mask = g["bs16_s3_mask"]
+    layer.mask.data.copy_(mask.to(DEV))
+    st = U.mask_stats(layer, sample_per_layer=256)
+    means = torch.sort(mask.reshape(8, 16, 10, 16).mean(dim=(1, 3)).flatten()).values.double()
+    assert st["blk_total_blocks"] == 80
+    assert st["blk_lower_half_mean"] == pytest.approx(float(means[:40].mean()), rel=1e-6)
+    assert st["blk_upper_half_mean"] == pytest.approx(float(means[40:].mean()), rel=1e-6)
+    assert st["blk_separation"] == pytest.approx(float(means[40:].mean() - means[:40].mean()), rel=1e-5)
