@@ -297,11 +297,32 @@ SF_API int sf_block_mask_apply(float* mask, const void* W, int w_dtype, void* wm
                         int bs, const float* value, const uint8_t* keep, double hx, void* stream);
 
 /*
+ * hard_mask_type 'block16': inside every 16 x 16 tile the keep_k entries with the largest soft-mask
+ * value are kept (ties to the lower row-major position inside the tile).
+ *   replaces: _hard_mask_from_soft 'block16' legacy/sparse_modeling.py:537-574, the 'block16'
+ *             penalty :1298-1348, and for this mode the gate / EMA / flip count / effective mask
+ *             of update_mask and forward (:1099-1162 unstructured gate, :1573-1663, :745-771).
+ * sf_mask_update_tile16: sf_mask_update_nm24 with 16 x 16 tiles in place of groups of four:
+ *   G = sigmoid((s - *tau)/(T + 1e-8)); penalty_mode 1: G = clamp(G - pen (mask - topk_tile(G)), 0, 1),
+ *   2: G = clamp(G - pen (1 - 2 mask), 0, 1); binarise push; mask <- clamp((1-a) mask + a G, 0, 1);
+ *   hard = topk_tile(mask); wm <- W * cast(hx mask + (1-hx) hard) (optional); stats as SF_MSTAT_*
+ *   (the TOP2 / BOT2 slots hold the sums of the kept / dropped entries). One warp per tile, radix
+ *   select of the k-th largest. rows and cols multiples of 16.
+ * sf_project_tile16: hard view (fp32 0/1, optional) and / or masked weight of a soft mask.
+ */
+SF_API int sf_mask_update_tile16(const float* score, const float* norm, const float* tau, float* mask,
+                          const void* W, int w_dtype, void* wm, double* stats, int64_t rows, int64_t cols,
+                          int keep_k, double temperature, double mask_lr, double pen, int penalty_mode,
+                          double binarize_decay, double hx, void* stream);
+SF_API int sf_project_tile16(const float* soft, float* hard, const void* W, int w_dtype, void* wm, int64_t rows,
+                      int64_t cols, int keep_k, double hx, void* stream);
+
+/*
  * Logging summary of the soft masks.
  *   replaces: mask_stats legacy/utils.py:2069-2280 (the per-layer accumulation :2117-2154; the
  *             caller adds layers up, all-reduces and forms mean / std / entropy / fractions).
  * sf_mask_summary ADDS to out[0..12): count, sum m, sum m^2, sum of the binary entropy of
- *   clamp(m, eps, 1-eps) (clamp in fp32, logarithms in fp64, as the reference's tensor ops),
+ *   clamp(m, eps, 1-eps) (clamp in fp32 as the reference's tensor op; fp32 logarithms, fp64 totals),
  *   counts m<0.5, m<0.1, m<0.01, m>0.9, m>0.99, m>0.5, sum of the m<0.5 entries, sum of the m>0.5
  *   entries. Zero `out` before the first layer.
  * sf_mask_sample_hist ADDS the histogram of mask[idx[0..take)) over `bins` equal bins of [0, 1]

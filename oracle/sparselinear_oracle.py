@@ -270,6 +270,50 @@ def mask_update_block(mask, G, bs, *, mask_lr, sparsity_ratio, lambda_mid=0.0, p
     return blockify(mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0), bs)
 
 
+def _tile16_topk(x, keep_k):
+    """0/1 tensor: the keep_k largest entries of every 16 x 16 tile, ties to the lower row-major
+    position inside the tile (legacy/sparse_modeling.py:549-571 with a tie-stable top-k)."""
+    rows, cols = x.shape
+    ob, ib = rows // 16, cols // 16
+    tiles = x.float().reshape(ob, 16, ib, 16).permute(0, 2, 1, 3).reshape(ob, ib, 256)
+    keep = torch.zeros_like(tiles)
+    if keep_k >= 256:
+        keep.fill_(1.0)
+    elif keep_k > 0:
+        keep.scatter_(-1, stable_topk_indices(tiles, keep_k), 1.0)
+    return keep.view(ob, ib, 16, 16).permute(0, 2, 1, 3).reshape(rows, cols)
+
+
+def hard_mask_tile16(soft, sparsity_ratio):
+    """legacy/sparse_modeling.py:537-574 for sizes that are multiples of 16."""
+    keep_k = max(0, min(256, int(round((1.0 - float(sparsity_ratio)) * 256))))
+    return _tile16_topk(soft, keep_k).to(soft.dtype)
+
+
+def mask_update_tile16(mask, G, *, mask_lr, sparsity_ratio, lambda_mid=0.0, pen_lr=None, penalty_mode="block16",
+                       binarize_decay=0.0):
+    """legacy/sparse_modeling.py:1298-1348 ('block16' pull towards the per-tile top-k of the gate),
+    :1567-1593 (mid pull, clamp, binarise push, EMA)."""
+    a = float(mask_lr)
+    pen_lr = a if pen_lr is None else float(pen_lr)
+    if float(lambda_mid) != 0.0:
+        if penalty_mode == "block16":
+            keep_k = max(0, min(256, int(round((1.0 - float(sparsity_ratio)) * 256))))
+            G = G - (pen_lr * float(lambda_mid)) * (mask.to(G.dtype) - _tile16_topk(G, keep_k).to(G.dtype))
+        elif penalty_mode == "mid":
+            G = G - (pen_lr * float(lambda_mid)) * (1.0 - 2.0 * mask).to(G.dtype)
+        else:
+            raise ValueError(penalty_mode)
+        G = G.clamp(0.0, 1.0)
+    d = float(binarize_decay)
+    if d != 0.0:
+        G = G.clone()
+        lt, gt = G < 0.5, G > 0.5
+        G[lt] = G[lt] * (1.0 - d)
+        G[gt] = G[gt] * (1.0 + d)
+    return mask.clone().mul_(1 - a).add_(G, alpha=a).clamp_(0.0, 1.0)
+
+
 def glu_joint_update(gate_score, up_score, gate_mask, up_mask, *, temperature, mask_lr, lambda_mid=0.0,
                      pen_lr=None, penalty_mode="mid", binarize_decay=0.0, beta_s=0.0, exact=False):
     """Joint update of a GLU gate / up pair, legacy/utils.py:363-479: one gate target from the

@@ -134,27 +134,32 @@ block_mask_apply_kernel(float* __restrict__ mask, const TW* __restrict__ W, TW* 
                         int64_t cols, int ob, int ib, const float* __restrict__ value,
                         const uint8_t* __restrict__ keep, float hx, int write_mask) {
     const int64_t total = rows * cols;
+    // cols % 4 == 0 and bs % 4 == 0: four consecutive elements share row, block and tail status
     for (int64_t i = ((int64_t)blockIdx.x * kBlkThreads + threadIdx.x) * 4; i < total;
          i += (int64_t)gridDim.x * kBlkThreads * 4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int64_t idx = i + e;
-            if (idx >= total) break;
-            const int64_t r = idx / cols, c = idx - r * cols;
-            const bool inside = r < (int64_t)ob * BS && c < (int64_t)ib * BS;
-            float m, hard = 1.0f;
-            if (inside) {
-                const int64_t b = (r / BS) * ib + c / BS;
-                m = value != nullptr ? value[b] : mask[idx];
-                hard = keep[b] ? 1.0f : 0.0f;
-                if (write_mask && value != nullptr) mask[idx] = m;
+        const int64_t r = i / cols, c = i - r * cols;
+        const bool inside = r < (int64_t)ob * BS && c < (int64_t)ib * BS;
+        float4 m4;
+        float hard = 1.0f;
+        if (inside) {
+            const int64_t b = (r / BS) * ib + c / BS;
+            hard = keep[b] ? 1.0f : 0.0f;
+            if (value != nullptr) {
+                const float v = value[b];
+                m4 = make_float4(v, v, v, v);
+                if (write_mask) *reinterpret_cast<float4*>(mask + i) = m4;
             } else {
-                m = mask[idx];
+                m4 = *reinterpret_cast<const float4*>(mask + i);
             }
-            if (wm != nullptr) {
-                const float eff = hx >= 1.0f - 1e-6f ? m : __fadd_rn(__fmul_rn(hx, m), __fmul_rn(1.0f - hx, hard));
-                const float w = load_scalar_w(W + idx);
-                store_scalar_w(wm + idx, __fmul_rn(w, Vec8<TW>::round(eff)));
+        } else {
+            m4 = *reinterpret_cast<const float4*>(mask + i);
+        }
+        if (wm != nullptr) {
+            const float m[4] = {m4.x, m4.y, m4.z, m4.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float eff = hx >= 1.0f - 1e-6f ? m[e] : __fadd_rn(__fmul_rn(hx, m[e]), __fmul_rn(1.0f - hx, hard));
+                store_scalar_w(wm + i + e, __fmul_rn(load_scalar_w(W + i + e), Vec8<TW>::round(eff)));
             }
         }
     }
@@ -207,7 +212,8 @@ int sf_block_mask_apply(float* mask, const void* W, int w_dtype, void* wm, int64
                         const float* value, const uint8_t* keep, double hx, void* stream) {
     SF_CHECK_ARG(mask && keep, "sf_block_mask_apply: mask and keep must be non-null");
     SF_CHECK_ARG(bs == 16 || bs == 32, "sf_block_mask_apply: bs must be 16 or 32");
-    SF_CHECK_ARG(rows >= bs && cols >= bs, "sf_block_mask_apply: need at least one whole block");
+    SF_CHECK_ARG(rows >= bs && cols >= bs && cols % 4 == 0, "sf_block_mask_apply: need at least one whole block and cols %% 4 == 0");
+    if (!aligned16(mask)) return fail(SF_ERR_ALIGNMENT, "sf_block_mask_apply: mask must be 16-byte aligned");
     SF_CHECK_ARG((wm == nullptr) || (W != nullptr), "sf_block_mask_apply: wm requested without W");
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_block_mask_apply: w_dtype must be SF_F32 or SF_BF16");
     const int ob = (int)(rows / bs), ib = (int)(cols / bs);

@@ -185,30 +185,40 @@ score_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, float
     }
 }
 
-// Summary of one soft mask for logging: twelve sums in fp64 (count, sum m, sum m^2, entropy with
-// the reference's fp32 clamp and fp64 logarithms, counts below 0.5 / 0.1 / 0.01 and above 0.9 /
-// 0.99 / 0.5, sums of the entries below and above 0.5), added to `out` with atomics.
+// Summary of one soft mask for logging: twelve sums (count, sum m, sum m^2, entropy with the
+// reference's fp32 clamp, counts below 0.5 / 0.1 / 0.01 and above 0.9 / 0.99 / 0.5, sums of the
+// entries below and above 0.5), added to `out` with atomics.
 __global__ void __launch_bounds__(kThreads)
 mask_summary_kernel(const float* __restrict__ mask, int64_t n, float clamp_lo, float clamp_hi, double* __restrict__ out) {
     double acc[12];
 #pragma unroll
     for (int i = 0; i < 12; ++i) acc[i] = 0.0;
-    for (int64_t i = (int64_t)blockIdx.x * kThreads + threadIdx.x; i < n; i += (int64_t)gridDim.x * kThreads) {
-        const float m = __ldcs(mask + i);
-        const double md = (double)m;
-        acc[0] += 1.0;
-        acc[1] += md;
-        acc[2] += md * md;
-        const double mm = (double)fminf(fmaxf(m, clamp_lo), clamp_hi);
-        acc[3] += -(mm * log(mm)) - ((1.0 - mm) * log(1.0 - mm));
-        acc[4] += m < 0.5f ? 1.0 : 0.0;
-        acc[5] += m < 0.1f ? 1.0 : 0.0;
-        acc[6] += m < 0.01f ? 1.0 : 0.0;
-        acc[7] += m > 0.9f ? 1.0 : 0.0;
-        acc[8] += m > 0.99f ? 1.0 : 0.0;
-        acc[9] += m > 0.5f ? 1.0 : 0.0;
-        acc[10] += m < 0.5f ? md : 0.0;
-        acc[11] += m > 0.5f ? md : 0.0;
+    // eight elements at a time are summed in fp32 (entropy with fp32 logarithms: each term is good
+    // to an fp32 ulp, which is what a logging statistic needs), the running totals are fp64
+    for (int64_t i0 = ((int64_t)blockIdx.x * kThreads + threadIdx.x) * 8; i0 < n; i0 += (int64_t)gridDim.x * kThreads * 8) {
+        float p[12];
+#pragma unroll
+        for (int i = 0; i < 12; ++i) p[i] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            if (i0 + e >= n) break;
+            const float m = __ldcs(mask + i0 + e);
+            p[0] += 1.f;
+            p[1] += m;
+            p[2] = fmaf(m, m, p[2]);
+            const float mm = fminf(fmaxf(m, clamp_lo), clamp_hi);
+            p[3] += -(mm * logf(mm)) - ((1.0f - mm) * logf(1.0f - mm));
+            p[4] += m < 0.5f ? 1.f : 0.f;
+            p[5] += m < 0.1f ? 1.f : 0.f;
+            p[6] += m < 0.01f ? 1.f : 0.f;
+            p[7] += m > 0.9f ? 1.f : 0.f;
+            p[8] += m > 0.99f ? 1.f : 0.f;
+            p[9] += m > 0.5f ? 1.f : 0.f;
+            p[10] += m < 0.5f ? m : 0.f;
+            p[11] += m > 0.5f ? m : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 12; ++i) acc[i] += (double)p[i];
     }
     __shared__ double red[12][kThreads / 32];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;

@@ -22,7 +22,14 @@ struct RowAcc {
 
 // clamp that keeps NaN (fminf / fmaxf would return the bound), as the tensor clamp does
 __device__ __forceinline__ float clamp_keep_nan(float x, float lim) {
-    return x != x ? x : fminf(fmaxf(x, -lim), lim);
+    float y;
+    asm("max.NaN.f32 %0, %1, %2;\n\tmin.NaN.f32 %0, %0, %3;" : "=&f"(y) : "f"(x), "f"(-lim), "f"(lim));
+    return y;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 
 __device__ __forceinline__ void acc_init(RowAcc& r) {
@@ -39,6 +46,38 @@ __device__ __forceinline__ void acc_add(RowAcc& r, float a, float b) {
     r.sum_b += e;
     r.wsum = fmaf(e, b - a, r.wsum);
 }
+// Eight logits of each tensor at once: the running maxima move at most once per chunk, so the
+// common case is one subtraction, one ex2 and one addition per logit. Internally the exponent is
+// taken in base 2 (logits scaled by log2 e); max_a / max_b are kept in natural units.
+__device__ __forceinline__ void acc_add8(RowAcc& r, const float (&a)[8], const float (&b)[8], float max_logit,
+                                         float inv_temp) {
+    constexpr float kLog2e = 1.4426950408889634f;
+    float x[8], y[8];
+    float mx = -INFINITY, my = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        x[i] = clamp_keep_nan(a[i], max_logit) * inv_temp;
+        y[i] = clamp_keep_nan(b[i], max_logit) * inv_temp;
+        mx = fmaxf(mx, x[i]);
+        my = fmaxf(my, y[i]);
+    }
+    if (mx > r.max_a) { r.sum_a *= ex2((r.max_a - mx) * kLog2e); r.max_a = mx; }
+    if (my > r.max_b) {
+        const float sc = ex2((r.max_b - my) * kLog2e);
+        r.sum_b *= sc; r.wsum *= sc; r.max_b = my;
+    }
+    const float ma2 = r.max_a * kLog2e, mb2 = r.max_b * kLog2e;
+    float sa = 0.f, sb = 0.f, ws = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        sa += ex2(fmaf(x[i], kLog2e, -ma2));  // NaN logits make the sums NaN (they never become the maximum)
+        const float e = ex2(fmaf(y[i], kLog2e, -mb2));
+        sb += e;
+        ws = fmaf(e, y[i] - x[i], ws);
+    }
+    r.sum_a += sa; r.sum_b += sb; r.wsum += ws;
+}
+
 __device__ __forceinline__ void acc_merge(RowAcc& r, const RowAcc& o) {
     const float ma = fmaxf(r.max_a, o.max_a);
     r.sum_a = r.sum_a * (r.max_a == -INFINITY ? 0.f : __expf(r.max_a - ma)) +
@@ -79,9 +118,7 @@ kl_div_fwd_kernel(const T* __restrict__ student, const T* __restrict__ teacher, 
             float a[8], b[8];
             Vec8<T>::load(s + c * 8, a);
             Vec8<T>::load(t + c * 8, b);
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-                acc_add(r, clamp_keep_nan(a[i], max_logit) * inv_temp, clamp_keep_nan(b[i], max_logit) * inv_temp);
+            acc_add8(r, a, b, max_logit, inv_temp);
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) acc_merge(r, acc_shfl_xor(r, o));

@@ -200,6 +200,31 @@ def mask_stats(mask, stats) -> None:
     check(lib().sf_mask_stats(_p(mask), _p(stats), rows, cols, _stream()), "sf_mask_stats")
 
 
+def mask_update_tile16(score, norm, tau, mask, stats, *, keep_k, W=None, wm=None, temperature=1.0, mask_lr=0.1, pen=0.0,
+                       penalty_mode=0, binarize_decay=0.0, hx=1.0) -> None:
+    """Fused mask update of the 'block16' mode (top keep_k of every 16 x 16 tile)."""
+    _cuda(score, norm, tau, mask, stats, W, wm)
+    if mask.dtype != torch.float32 or score.dtype != torch.float32 or stats.dtype != torch.float64:
+        raise TypeError("mask_update_tile16: mask / score float32, stats float64")
+    rows, cols = mask.shape
+    check(lib().sf_mask_update_tile16(_p(score), _p(norm), _p(tau), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
+                                      _p(wm), _p(stats), rows, cols, int(keep_k), float(temperature), float(mask_lr),
+                                      float(pen), int(penalty_mode), float(binarize_decay), float(hx), _stream()),
+          "sf_mask_update_tile16")
+
+
+def project_tile16(soft, keep_k, *, want_hard=True, W=None, wm=None, hx=1.0):
+    """Per-tile hard view (float32 0/1) and / or masked weight of a float32 soft mask."""
+    _cuda(soft, W, wm)
+    if soft.dtype != torch.float32 or soft.dim() != 2:
+        raise TypeError("project_tile16: soft must be a 2-D float32 tensor")
+    rows, cols = soft.shape
+    hard = torch.empty_like(soft) if want_hard else None
+    check(lib().sf_project_tile16(_p(soft), _p(hard), _p(W), _dt(W) if W is not None else SF_F32, _p(wm), rows, cols,
+                                  int(keep_k), float(hx), _stream()), "sf_project_tile16")
+    return hard
+
+
 def block_sums(x, bs, norm=None, want_sq=True):
     """(sum, sumsq) over every whole bs x bs block of a float32 matrix, each [rows // bs, cols // bs]."""
     _cuda(x, norm)

@@ -358,6 +358,17 @@ class SparseLinear(nn.Linear):
         """16 / 32 in the block-sparse soft-mask modes, else 0."""
         return {"block_sparse16": 16, "block_sparse32": 32}.get(self.hard_mask_type, 0)
 
+    def _tile16_keep_k(self) -> int:
+        """Entries kept per 16 x 16 tile in the 'block16' mode (legacy/sparse_modeling.py:553-555)."""
+        return max(0, min(256, int(round((1.0 - float(self.sparsity_ratio)) * 256))))
+
+    def _is_tile16(self) -> bool:
+        return self._resolved_hard_type() == "block16"
+
+    def _check_tile16(self):
+        if self.out_features % 16 or self.in_features % 16:
+            raise NotImplementedError("hard_mask_type='block16' is built for layer sizes that are multiples of 16")
+
     def _block_keep(self, block_values: torch.Tensor) -> torch.Tensor:
         """uint8 [ob, ib]: the round((1 - sparsity_ratio) * blocks) blocks with the largest value, ties
         to the lower flat index (legacy/sparse_modeling.py:621-637, 671-687)."""
@@ -429,6 +440,11 @@ class SparseLinear(nn.Linear):
             return (soft_mask > 0.5).to(dtype=soft_mask.dtype)
         if mt == "nm_2_4":
             return ops.project_nm24(soft_mask)[0]
+        if mt == "block16" and soft_mask.dim() == 2:
+            # top entries of every 16 x 16 tile (:537-574)
+            if soft_mask.shape[0] % 16 or soft_mask.shape[1] % 16:
+                raise NotImplementedError("hard_mask_type='block16' is built for sizes that are multiples of 16")
+            return ops.project_tile16(soft_mask.float().contiguous(), self._tile16_keep_k()).to(soft_mask.dtype)
         if mt in ("block_sparse16", "block_sparse32"):
             # whole blocks kept by the RMS of the soft mask over the block (:607-718)
             bs = 16 if mt == "block_sparse16" else 32
@@ -487,6 +503,13 @@ class SparseLinear(nn.Linear):
         ``invalidate_masked_weight()``."""
         if self._block_size():
             return self._masked_weight_block()
+        if self._is_tile16():
+            self._check_tile16()
+            self._buffers_ready()
+            fin = bool(getattr(self, "_hardening_finalized", False))
+            ops.project_tile16(self.mask.data, self._tile16_keep_k(), want_hard=False, W=self.weight.data, wm=self._wm,
+                               hx=1.0 if fin else float(self.hardening_x))
+            return self._wm
         self._check_2to4()
         self._buffers_ready()
         key = self._current_key()
@@ -569,7 +592,7 @@ class SparseLinear(nn.Linear):
             return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)
         if self.mode != "sparse_forward":
             raise ValueError(f"Invalid mode: {self.mode}")
-        if self._resolved_hard_type() not in ("structured", "nm_2_4", "block_sparse16", "block_sparse32"):
+        if self._resolved_hard_type() not in ("structured", "nm_2_4", "block_sparse16", "block_sparse32", "block16"):
             raise NotImplementedError(f"hard mask type {self._resolved_hard_type()!r} is outside the kernel paths")
         hx = float(getattr(self, "hardening_x", 1.0))
         finalized = bool(getattr(self, "_hardening_finalized", False))
@@ -807,9 +830,9 @@ class SparseLinear(nn.Linear):
         """Gate / projection combinations the 2:4 kernels cover."""
         if self.mask_type not in ("structured", "unstructured"):
             raise ValueError(f"Invalid mask_type: {self.mask_type}")
-        if self._block_size():
+        if self._block_size() or self._is_tile16():
             if self.mask_type != "unstructured":
-                raise NotImplementedError("block-sparse hard masks are built for mask_type='unstructured' (the block gate)")
+                raise NotImplementedError("block hard masks are built for mask_type='unstructured'")
             return
         if self._resolved_hard_type() not in ("structured", "nm_2_4"):
             raise NotImplementedError(
@@ -873,6 +896,8 @@ class SparseLinear(nn.Linear):
         self._check_mask_modes()
         if self._block_size():
             return self._update_mask_block(step, lambda_mid)
+        if self._is_tile16():
+            return self._update_mask_tile16(step, lambda_mid)
         self._check_2to4()
         if not score_ready:
             self._refresh_score()
@@ -884,6 +909,34 @@ class SparseLinear(nn.Linear):
         self._launch_mask_update(self._score, self._norm, step, pen=float(self.mask_penalty_lr) * lam,
                                  pmode=pmode if lam != 0.0 else 0, tau=self._gate_tau(step), owner=self,
                                  score_bf16=self._score_is_bf16())
+
+    def _update_mask_tile16(self, step: int, lambda_mid):
+        """update_mask with hard_mask_type='block16': the unstructured gate, the per-tile top-k (or mid)
+        penalty, binarise push, EMA, per-tile hard view, masked weight and flip count in one kernel."""
+        self._check_tile16()
+        if self._beta_structural(step) > 0.0:
+            raise NotImplementedError("beta_structural mixing is an N:M target; it is not combined with block16 masks")
+        self._buffers_ready()
+        self._refresh_score()
+        lam = 0.0 if lambda_mid is None else float(lambda_mid)
+        mode = str(getattr(self.cfg, "mask_penalty_mode", "mid") or "mid")
+        pmode = 0
+        if lam != 0.0:
+            if mode not in ("block16", "mid"):
+                raise NotImplementedError(f"mask_penalty_mode={mode!r} is not combined with block16 masks")
+            pmode = 1 if mode == "block16" else 2
+        hx_new = self._next_hardening_x(step)
+        ops.mask_update_tile16(self._score, self._norm, self._gate_tau(step), self.mask.data, self._stats,
+                               keep_k=self._tile16_keep_k(), W=self.weight.data, wm=self._wm,
+                               temperature=self._temperature(step), mask_lr=float(self.cfg.mask_lr),
+                               pen=float(self.mask_penalty_lr) * lam, penalty_mode=pmode,
+                               binarize_decay=float(getattr(self.cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new)
+        self.hardening_x = hx_new
+        self._fuse_score_next = self._predict_mask_update(step + 1)
+        self.last_mask_stats = self._stats
+        self.weight.flipped_mask = _LazyInt(self._stats, _lib.MSTAT_FLIPS)
+        self.weight.init_flipped_mask = 0
+        self.weight.mask = self.mask
 
     def _block_gate(self, step: int):
         """Per-block gate of legacy/sparse_modeling.py:1122-1157: RMS of the normalised score over each

@@ -508,6 +508,10 @@ BLOCK_CASES = {
                                             mask_binarize_decay=0.05)),
     "bs32": dict(shape=(128, 160), cfg=dict(hard_mask_type="block_sparse32", mask_penalty_mode="block_sparse32")),
     "tail": dict(shape=(72, 104), cfg=dict(hard_mask_type="block_sparse16", mask_penalty_mode="mid")),
+    # per-tile top-k (hard_mask_type block16), the second recipe of the paper's LLaMA table
+    "tile16": dict(shape=(64, 96), cfg=dict(hard_mask_type="block16", mask_penalty_mode="block16",
+                                            mask_binarize_decay=0.05)),
+    "tile16mid": dict(shape=(32, 48), cfg=dict(hard_mask_type="block16", mask_penalty_mode="mid", sparsity_ratio=0.75)),
 }
 BLOCK_BASE = dict(mask_type="unstructured", mask_metric="hessian_obd", sparsity_ratio=0.5, mask_update_period=1,
                   sparsity_warmup_steps=1, mask_lr=0.3, temp_init=0.5, temp_min=0.05, temp_decay=0.7,

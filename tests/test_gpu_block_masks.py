@@ -14,7 +14,7 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda"
 
 
-@pytest.mark.parametrize("tag", ["bs16", "bs32", "tail"])
+@pytest.mark.parametrize("tag", ["bs16", "bs32", "tail", "tile16", "tile16mid"])
 def test_block_sparse_soft_masks_follow_the_reference(tag):
     import sparseforge_b200 as sf
 
@@ -39,6 +39,8 @@ def test_block_sparse_soft_masks_follow_the_reference(tag):
         assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"{tag}_s{step}_hard"])
         with torch.no_grad():
             assert rel_err(layer(x), g[f"{tag}_s{step}_y"]) <= 1e-5
+    if cfg.hard_mask_type == "block16":
+        return
     # the blockified tensor is block-constant and keeps the ragged tail
     t = torch.rand(out_f, in_f, device=DEV)
     b = layer._blockify_tensor(t)
@@ -67,3 +69,20 @@ def test_mask_stats_block_keys():
     assert st["blk_lower_half_mean"] == pytest.approx(float(means[:40].mean()), rel=1e-6)
     assert st["blk_upper_half_mean"] == pytest.approx(float(means[40:].mean()), rel=1e-6)
     assert st["blk_separation"] == pytest.approx(float(means[40:].mean() - means[:40].mean()), rel=1e-5)
+
+
+def test_tile16_projection_ties_and_random():
+    """Per-tile top-k against a stable descending sort of each tile: random values, heavy ties and
+    the all-equal tile (the initial all-ones mask)."""
+    from oracle import sparselinear_oracle as O
+    from sparseforge_b200 import ops
+
+    torch.manual_seed(9)
+    for keep_k in (1, 64, 128, 200, 255):
+        for soft in (torch.rand(64, 96), torch.randint(0, 4, (64, 96)).float() / 4, torch.ones(32, 32),
+                     torch.randn(48, 80)):
+            want = O._tile16_topk(soft, keep_k)
+            got = ops.project_tile16(soft.to(DEV), keep_k)
+            assert torch.equal(got.cpu(), want), (keep_k, tuple(soft.shape))
+    assert int(ops.project_tile16(torch.rand(16, 16, device=DEV), 0).sum()) == 0
+    assert int(ops.project_tile16(torch.rand(16, 16, device=DEV), 256).sum()) == 256

@@ -248,7 +248,7 @@ def test_mask_stats_follow_the_reference(tag):
         if math.isnan(v):
             assert math.isnan(got), k
         else:
-            assert got == pytest.approx(v, rel=1e-6, abs=1e-12), k
+            assert got == pytest.approx(v, rel=1e-5, abs=1e-12), k  # entropy terms use fp32 logarithms
 
 
 @pytest.mark.parametrize("tag,tol", [("f32", 1e-5), ("bf16", 1e-2), ("chunks", 1e-5)])

@@ -286,6 +286,39 @@ def test_block_sparse_soft_masks(tag):
         assert rel_err(O.linear_forward(g[f"{tag}_x"], W, eff), g[f"{tag}_s{step}_y"]) <= F32_TOL
 
 
+@pytest.mark.parametrize("tag", ["tile16", "tile16mid"])
+def test_block16_tile_masks(tag):
+    """hard_mask_type='block16': unstructured gate, per-tile top-k penalty and hard view."""
+    import json
+
+    g = Golden("block_masks")
+    spec = json.loads(str(g["cases_json"]))[tag]
+    cfg = dict(json.loads(str(g["base_json"])), **spec["cfg"])
+    sr = cfg["sparsity_ratio"]
+    W, H = g[f"{tag}_W"], g[f"{tag}_H"]
+    mask, hx = torch.ones(W.shape), 1.0
+    for step in range(5):
+        T = O.temperature_at(step, cfg["temp_init"], cfg["temp_decay"], cfg["temp_min"])
+        assert math.isclose(T, g.scalar(f"{tag}_s{step}_T"), rel_tol=1e-12)
+        sparsity = sr * min(1.0, step / cfg["sparsity_warmup_steps"])
+        s = O.normalize_scores(O.importance_score(W, "hessian_obd", H=H))
+        G = O.gate_target_unstructured(s, O.tau_unstructured(s, sparsity, None), T)
+        assert rel_err(G, g[f"{tag}_s{step}_G"]) <= F32_TOL
+        if step >= cfg["sparsity_warmup_steps"]:
+            new = O.mask_update_tile16(mask, G, mask_lr=cfg["mask_lr"], sparsity_ratio=sr, lambda_mid=0.25,
+                                       pen_lr=cfg["mask_penalty_lr"], penalty_mode=cfg["mask_penalty_mode"],
+                                       binarize_decay=cfg.get("mask_binarize_decay", 0.0))
+            flips = int(((O.hard_mask_tile16(mask, sr) > 0.5) ^ (O.hard_mask_tile16(new, sr) > 0.5)).sum())
+            assert flips == g.scalar(f"{tag}_s{step}_flips")
+            mask = new
+            hx = O.hardening_x(step, cfg["mask_hardening_start"], cfg["mask_hardening_duration"])
+        assert rel_err(mask, g[f"{tag}_s{step}_mask"]) <= F32_TOL
+        hard = O.hard_mask_tile16(mask, sr)
+        assert torch.equal(hard, g[f"{tag}_s{step}_hard"])
+        eff = mask if hx >= 1.0 - 1e-6 else hx * mask + (1.0 - hx) * hard
+        assert rel_err(O.linear_forward(g[f"{tag}_x"], W, eff), g[f"{tag}_s{step}_y"]) <= F32_TOL
+
+
 def test_chain_bf16_schedule():
     g = Golden("chain_bf16")
     decay = 0.05 ** (1.0 / 9.0)
