@@ -552,6 +552,188 @@ sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     }
 }
 
+// ------------------------------------------------------------------------------------------
+// CTA pair, two weight tiles per CTA: a pair computes 512 weight rows x 224 tokens. Both sparse MMAs
+// of a K step (rows [0,256) and [256,512) of the pair tile, 128 of each in every CTA) read the SAME
+// staged activation tile, so the bytes a CTA pulls from L2 per FLOP drop from 46 KiB to 32 KiB per
+// 7.3 MFLOP: the one-tile pair kernel stalls on operand delivery (about 100 B per clock and SM
+// wanted at the sparse rate, 70-75 delivered), this one asks for about 70. Price: the two
+// accumulators fill the tensor memory (2 x 224 + metadata columns), so they are not double
+// buffered and the epilogue of a tile is not hidden behind the next tile's MMAs; eight epilogue
+// warps per CTA (two per TMEM lane quarter, one per weight tile) keep it short.
+// ------------------------------------------------------------------------------------------
+constexpr int Q_STAGES = 3;
+constexpr int Q_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
+constexpr int Q_STAGE_BYTES = 2 * SP_A_BYTES + 2 * P2_B_BOX_BYTES + 2 * SP_META_BYTES;  // 65536
+constexpr int Q_META_COL0 = 2 * P2_BN;  // 448: after the two accumulators
+constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Q_THREADS, 1)
+sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                           const __grid_constant__ CUtensorMap tmE, __nv_bfloat16* __restrict__ Y,
+                           const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status) {
+    constexpr int STAGES = Q_STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw_addr + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - raw_addr);
+    auto* tail = reinterpret_cast<SpSmemTail<STAGES>*>(base_ptr + STAGES * Q_STAGE_BYTES);
+    volatile int* abort_flag = &tail->abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t cta = ptx::cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int tiles_m = (out + 511) / 512, tiles_n = (T + P2_BN - 1) / P2_BN;
+    const int total_tiles = tiles_m * tiles_n;
+    const int num_kb = (in + SP_BK - 1) / SP_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(ptx::smem_u32(&tail->full[s]), 1);
+            ptx::mbar_init(ptx::smem_u32(&tail->empty[s]), 1);
+        }
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_full[0]), 1);
+        ptx::mbar_init(ptx::smem_u32(&tail->tmem_empty[0]), 16);  // 8 epilogue warps of each CTA
+        tail->abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(ptx::smem_u32(&tail->tmem_base), P2_TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    if (warp == 0 && lane == 0) {
+        ptx::prefetch_tensormap(&tmA);
+        ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmE);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = tail->tmem_base;
+
+    if (warp == 0) {
+        // ---------------- TMA producer (both CTAs) ----------------
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
+            const int n0 = nt * P2_BN + (int)cta * P2_BNH;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 41);
+                if (!ok) break;
+                if (lane == 0) {
+                    const uint32_t local_bar = ptx::smem_u32(&tail->full[stage]);
+                    const uint32_t leader_bar = ptx::map_to_cta(local_bar, 0);
+                    const uint32_t sa = base + stage * Q_STAGE_BYTES, sb = sa + 2 * SP_A_BYTES;
+                    const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * Q_STAGE_BYTES);
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int m0 = mt * 512 + u * 256 + (int)cta * 128;  // this CTA's rows of weight tile u
+                        ptx::tma_load_2d_pair(sa + u * SP_A_BYTES, &tmA, leader_bar, kb * (SP_BK / 2), m0);
+                        ptx::tma_load_2d_pair(sm + u * SP_META_BYTES, &tmE, leader_bar, 0, ((m0 >> 7) * num_kb + kb) * 128);
+                    }
+                    ptx::tma_load_2d_pair(sb, &tmB, leader_bar, kb * SP_BK, n0);
+                    ptx::tma_load_2d_pair(sb + P2_B_BOX_BYTES, &tmB, leader_bar, kb * SP_BK + 64, n0);
+                }
+                __syncwarp();
+                if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            }
+        }
+        if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    } else if (warp == 1) {
+        // ---------------- MMA issuer (leader CTA only) ----------------
+        if (cta == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(256, P2_BN, 0, 0, 1);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            int t = 0;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+                // both accumulators are free once the sixteen epilogue warps have drained the last tile
+                ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[0]), ((uint32_t)t & 1u) ^ 1u, abort_flag, status, 43);
+                if (!ok) break;
+                ptx::tc_fence_after();
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 42);
+                    if (!ok) break;
+                    ptx::tc_fence_after();
+                    if (lane == 0) {
+                        const uint32_t sa = base + stage * Q_STAGE_BYTES, sb = sa + 2 * SP_A_BYTES;
+                        const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const uint32_t tmem_e = tmem_base + (uint32_t)(Q_META_COL0 + 4 * (stage * 2 + u));
+                            ptx::tmem_cp_128x128b_pair(tmem_e, ptx::make_smem_desc(sm + u * SP_META_BYTES, 16, 128, 0));
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; ++u) {
+                            const uint32_t tmem_d = tmem_base + (uint32_t)(u * P2_BN);
+                            const uint32_t tmem_e = tmem_base + (uint32_t)(Q_META_COL0 + 4 * (stage * 2 + u));
+#pragma unroll
+                            for (int k = 0; k < 4; ++k) {
+                                const uint64_t adesc = ptx::make_smem_desc(sa + u * SP_A_BYTES + k * 32, 16, 1024, 2);
+                                const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * P2_B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
+                                ptx::mma_f16_ss_sp_pair(tmem_d, adesc, bdesc, tmem_e + (uint32_t)(k & ~1), idesc | (uint32_t)(k & 1),
+                                                        (kb | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                        ptx::mma_commit_pair(ptx::smem_u32(&tail->empty[stage]), (uint16_t)3);
+                    }
+                    __syncwarp();
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (!ok) break;
+                if (lane == 0) ptx::mma_commit_pair(ptx::smem_u32(&tail->tmem_full[0]), (uint16_t)3);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ---------------- epilogue (both CTAs): warp (u, q) drains 32 rows x 224 tokens of weight tile u ----------------
+        const int q = warp & 3, u = (warp - 2) >> 2;
+        const uint32_t leader_empty = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[0]), 0);
+        bool ok = true;
+        int t = 0;
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+            int mt, nt;
+            sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
+            ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[0]), (uint32_t)t & 1u, abort_flag, status, 44);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const int o = mt * 512 + u * 256 + (int)cta * 128 + q * 32 + lane;
+            const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
+            const uint32_t taddr = tmem_base + (uint32_t)(u * P2_BN) + ((uint32_t)(q * 32) << 16);
+#pragma unroll 1
+            for (int c = 0; c < P2_BN / 32; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                ptx::tmem_ld_wait();
+                if (o < out) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = nt * P2_BN + c * 32 + j;
+                        if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(leader_empty);
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc_pair(tmem_base, P2_TMEM_COLS);
+    }
+}
+
 int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows);
 
 static int launch_sparse_pair(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
@@ -569,10 +751,23 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
     SF_CHECK_CUDA(cudaGetDevice(&dev));
     if (configured_dev != dev) {
         SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES));
+        SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES));
         configured_dev = dev;
     }
-    const int64_t tiles = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
     const int64_t max_pairs = sm_count() / 2;
+    // two weight tiles per CTA when the matrix has at least two 256-row tiles and enough work units
+    // for the pairs (SF_SPARSE24_ONE_TILE=1 keeps the one-tile kernel, for A/B runs)
+    static const bool one_tile_only = [] { const char* e = getenv("SF_SPARSE24_ONE_TILE"); return e && e[0] == '1'; }();
+    const int64_t tiles2 = ((out + 511) / 512) * ((T + P2_BN - 1) / P2_BN);
+    if (!one_tile_only && out >= 512 && tiles2 >= max_pairs) {
+        const int pairs2 = (int)(tiles2 < max_pairs ? tiles2 : max_pairs);
+        sparse24_gemm_pair2_kernel<<<2 * pairs2, Q_THREADS, Q_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
+                                                                                (const __nv_bfloat16*)bias, (int)out, (int)T,
+                                                                                (int)in, status);
+        SF_CHECK_CUDA(cudaGetLastError());
+        return SF_OK;
+    }
+    const int64_t tiles = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
     const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
     sparse24_gemm_pair_kernel<<<2 * pairs, SP_THREADS, P2_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
                                                                             (const __nv_bfloat16*)bias, (int)out, (int)T,

@@ -62,6 +62,8 @@ def test_pack_meta_is_the_documented_permutation(ops):
 SPARSE_SHAPES = [
     (1, 128, 128), (16, 256, 128), (17, 384, 256), (128, 512, 384), (100, 272, 200), (1024, 1024, 512),
     (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 11008), (1024, 11008, 4096), (8192, 4096, 4096),
+    # two weight tiles per CTA: ragged token count, a weight-row count that half fills the last 512-row tile
+    (8000, 1024, 1280), (5000, 384, 768), (8192, 4096, 11008),
 ]
 
 
