@@ -755,11 +755,14 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
         configured_dev = dev;
     }
     const int64_t max_pairs = sm_count() / 2;
-    // two weight tiles per CTA when the matrix has at least two 256-row tiles and enough work units
-    // for the pairs (SF_SPARSE24_ONE_TILE=1 keeps the one-tile kernel, for A/B runs)
+    // Two weight tiles per CTA when K is long enough to amortise the epilogue that this variant
+    // cannot hide (measured at T = 8192: K = 11008 303 us against 338 us, K = 4096 127 against 126),
+    // the matrix has at least two 256-row tiles and there are enough work units for the pairs.
+    // SF_SPARSE24_ONE_TILE=1 / SF_SPARSE24_TWO_TILES=1 force either kernel for A/B runs.
     static const bool one_tile_only = [] { const char* e = getenv("SF_SPARSE24_ONE_TILE"); return e && e[0] == '1'; }();
+    static const bool two_tiles_always = [] { const char* e = getenv("SF_SPARSE24_TWO_TILES"); return e && e[0] == '1'; }();
     const int64_t tiles2 = ((out + 511) / 512) * ((T + P2_BN - 1) / P2_BN);
-    if (!one_tile_only && out >= 512 && tiles2 >= max_pairs) {
+    if (!one_tile_only && out >= 512 && tiles2 >= max_pairs && (in >= 8192 || two_tiles_always)) {
         const int pairs2 = (int)(tiles2 < max_pairs ? tiles2 : max_pairs);
         sparse24_gemm_pair2_kernel<<<2 * pairs2, Q_THREADS, Q_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
                                                                                 (const __nv_bfloat16*)bias, (int)out, (int)T,
