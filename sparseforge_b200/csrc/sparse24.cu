@@ -386,22 +386,42 @@ constexpr int P2_META_COL0 = 2 * P2_BN;       // 448
 constexpr int P2_TMEM_COLS = 512;
 constexpr int P2_SMEM_BYTES = P2_STAGES * P2_STAGE_BYTES + 1024 + 256;
 
+// Token-tile width and accumulator count of the one-tile pair kernel. 224 tokens with two
+// accumulators (epilogue hidden behind the next tile) is the general case; 256 tokens with a single
+// accumulator serves products whose tiles all fit in one wave of pairs, where there is no next tile
+// to overlap with and the wider tile means fewer, fuller work units (T = 1024 on a 4096-row
+// matrix: 16 x 4 = 64 units for 74 pairs instead of 16 x 5 = 80).
+template <int BN, int NACC>
+struct PairCfg {
+    static constexpr int BNH = BN / 2;
+    static constexpr int B_BOX_BYTES = BNH * 128;
+    static constexpr int STAGE_BYTES = SP_A_BYTES + 2 * B_BOX_BYTES + SP_META_BYTES;
+    static constexpr int STAGES = 4;
+    static constexpr int META_COL0 = NACC * BN;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + 256;
+    static_assert(NACC * BN + 4 * STAGES <= 512, "accumulators and metadata must fit the tensor memory");
+    static_assert(SMEM_BYTES <= 232448, "stages must fit the shared memory of one CTA");
+    static_assert(STAGE_BYTES % 1024 == 0 && B_BOX_BYTES % 1024 == 0, "swizzled operand tiles need 1024-byte alignment");
+};
+
+template <int BN, int NACC>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(SP_THREADS, 1)
 sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                           const __grid_constant__ CUtensorMap tmE, __nv_bfloat16* __restrict__ Y,
                           const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status) {
-    constexpr int STAGES = P2_STAGES;
+    using C = PairCfg<BN, NACC>;
+    constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - raw_addr);
-    auto* tail = reinterpret_cast<SpSmemTail<STAGES>*>(base_ptr + STAGES * P2_STAGE_BYTES);
+    auto* tail = reinterpret_cast<SpSmemTail<STAGES>*>(base_ptr + STAGES * C::STAGE_BYTES);
     volatile int* abort_flag = &tail->abort_flag;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t cta = ptx::cluster_ctarank();  // 0 = leader
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int tiles_m = (out + 255) / 256, tiles_n = (T + P2_BN - 1) / P2_BN;
+    const int tiles_m = (out + 255) / 256, tiles_n = (T + BN - 1) / BN;
     const int total_tiles = tiles_m * tiles_n;
     const int num_kb = (in + SP_BK - 1) / SP_BK;
     const int meta_tiles_m = (out + 127) / 128;  // 128-row metadata tiles per K tile column
@@ -442,19 +462,19 @@ sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
             int mt, nt;
             sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
             const int m0 = mt * 256 + (int)cta * 128;    // this CTA's weight rows
-            const int n0 = nt * P2_BN + (int)cta * P2_BNH;  // this CTA's half of the token rows
+            const int n0 = nt * BN + (int)cta * C::BNH;  // this CTA's half of the token rows
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 21);
                 if (!ok) break;
                 if (lane == 0) {
                     const uint32_t local_bar = ptx::smem_u32(&tail->full[stage]);
                     const uint32_t leader_bar = ptx::map_to_cta(local_bar, 0);
-                    const uint32_t sa = base + stage * P2_STAGE_BYTES, sb = sa + SP_A_BYTES;
-                    const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
-                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * P2_STAGE_BYTES);
+                    const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + SP_A_BYTES;
+                    const uint32_t sm = sb + 2 * C::B_BOX_BYTES;
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * C::STAGE_BYTES);
                     ptx::tma_load_2d_pair(sa, &tmA, leader_bar, kb * (SP_BK / 2), m0);
                     ptx::tma_load_2d_pair(sb, &tmB, leader_bar, kb * SP_BK, n0);
-                    ptx::tma_load_2d_pair(sb + P2_B_BOX_BYTES, &tmB, leader_bar, kb * SP_BK + 64, n0);
+                    ptx::tma_load_2d_pair(sb + C::B_BOX_BYTES, &tmB, leader_bar, kb * SP_BK + 64, n0);
                     // metadata tile (m0 / 128, kb): 128 rows of 16 bytes
                     ptx::tma_load_2d_pair(sm, &tmE, leader_bar, 0, ((m0 >> 7) * num_kb + kb) * 128);
                 }
@@ -467,31 +487,32 @@ sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
     } else if (warp == 1) {
         // ---------------- MMA issuer (leader CTA only) ----------------
         if (cta == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(256, P2_BN, 0, 0, 1);
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(256, BN, 0, 0, 1);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             int t = 0;
             for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
-                const int acc = t & 1;
-                const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+                // two accumulators alternate; with one, every tile waits for the previous one to be drained
+                const int acc = NACC == 2 ? (t & 1) : 0;
+                const uint32_t acc_phase = NACC == 2 ? ((uint32_t)(t >> 1) & 1u) : ((uint32_t)t & 1u);
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 23);
                 if (!ok) break;
                 ptx::tc_fence_after();
-                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * P2_BN);
+                const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 22);
                     if (!ok) break;
                     ptx::tc_fence_after();
                     if (lane == 0) {
-                        const uint32_t sa = base + stage * P2_STAGE_BYTES, sb = sa + SP_A_BYTES;
-                        const uint32_t sm = sb + 2 * P2_B_BOX_BYTES;
-                        const uint32_t tmem_e = tmem_base + (uint32_t)(P2_META_COL0 + 4 * stage);
+                        const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + SP_A_BYTES;
+                        const uint32_t sm = sb + 2 * C::B_BOX_BYTES;
+                        const uint32_t tmem_e = tmem_base + (uint32_t)(C::META_COL0 + 4 * stage);
                         ptx::tmem_cp_128x128b_pair(tmem_e, ptx::make_smem_desc(sm, 16, 128, 0));
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
                             const uint64_t adesc = ptx::make_smem_desc(sa + k * 32, 16, 1024, 2);
-                            const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * P2_B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
+                            const uint64_t bdesc = ptx::make_smem_desc(sb + (k >> 1) * C::B_BOX_BYTES + (k & 1) * 64, 16, 1024, 2);
                             ptx::mma_f16_ss_sp_pair(tmem_d, adesc, bdesc, tmem_e + (uint32_t)(k & ~1), idesc | (uint32_t)(k & 1),
                                                     (kb | k) != 0 ? 1u : 0u);
                         }
@@ -515,23 +536,23 @@ sparse24_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
             int mt, nt;
             sp_tile_coords(tile, tiles_m, tiles_n, mt, nt);
-            const int acc = t & 1;
-            const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
+            const int acc = NACC == 2 ? (t & 1) : 0;
+            const uint32_t acc_phase = NACC == 2 ? ((uint32_t)(t >> 1) & 1u) : ((uint32_t)t & 1u);
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 24);
             if (!ok) break;
             ptx::tc_fence_after();
             const int o = mt * 256 + (int)cta * 128 + q * 32 + lane;
             const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
-            const uint32_t taddr = tmem_base + (uint32_t)(acc * P2_BN) + ((uint32_t)(q * 32) << 16);
+            const uint32_t taddr = tmem_base + (uint32_t)(acc * BN) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c = 0; c < P2_BN / 32; ++c) {
+            for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
                 ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
                 ptx::tmem_ld_wait();
                 if (o < out) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
-                        const int tok = nt * P2_BN + c * 32 + j;
+                        const int tok = nt * BN + c * 32 + j;
                         if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
                     }
                 }
@@ -741,7 +762,12 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
     CUtensorMap tmA, tmB, tmE;
     int rc = make_bf16_tensor_map(&tmA, values, in / 2, out, in / 2, SP_BM);
     if (rc) return rc;
-    rc = make_bf16_tensor_map(&tmB, x, in, T, in, P2_BNH);
+    const int64_t max_pairs = sm_count() / 2;
+    // one wave of pairs covers the product with 256-token tiles: single accumulator, wider tile
+    const int64_t tiles_wide = ((out + 255) / 256) * ((T + 255) / 256);
+    const int64_t tiles_std = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
+    const bool wide = tiles_wide <= max_pairs && tiles_std > tiles_wide;
+    rc = make_bf16_tensor_map(&tmB, x, in, T, in, wide ? 128 : P2_BNH);
     if (rc) return rc;
     const int64_t meta_rows = sf_sparse24_meta_tc_bytes(out, in) / 16;
     rc = make_meta_tensor_map(&tmE, meta_tc, meta_rows, 128);
@@ -750,11 +776,19 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
     if (configured_dev != dev) {
-        SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P2_SMEM_BYTES));
+        SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair_kernel<P2_BN, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           PairCfg<P2_BN, 2>::SMEM_BYTES));
+        SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair_kernel<256, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           PairCfg<256, 1>::SMEM_BYTES));
         SF_CHECK_CUDA(cudaFuncSetAttribute(sparse24_gemm_pair2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Q_SMEM_BYTES));
         configured_dev = dev;
     }
-    const int64_t max_pairs = sm_count() / 2;
+    if (wide) {
+        sparse24_gemm_pair_kernel<256, 1><<<2 * (int)tiles_wide, SP_THREADS, PairCfg<256, 1>::SMEM_BYTES, st>>>(
+            tmA, tmB, tmE, (__nv_bfloat16*)y, (const __nv_bfloat16*)bias, (int)out, (int)T, (int)in, status);
+        SF_CHECK_CUDA(cudaGetLastError());
+        return SF_OK;
+    }
     // Two weight tiles per CTA when K is long enough to amortise the epilogue that this variant
     // cannot hide (measured at T = 8192: K = 11008 303 us against 338 us, K = 4096 127 against 126),
     // the matrix has at least two 256-row tiles and there are enough work units for the pairs.
@@ -772,7 +806,7 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
     }
     const int64_t tiles = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
     const int pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
-    sparse24_gemm_pair_kernel<<<2 * pairs, SP_THREADS, P2_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
+    sparse24_gemm_pair_kernel<P2_BN, 2><<<2 * pairs, SP_THREADS, P2_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
                                                                             (const __nv_bfloat16*)bias, (int)out, (int)T,
                                                                             (int)in, status);
     SF_CHECK_CUDA(cudaGetLastError());
@@ -931,6 +965,11 @@ static int sparse24_gemm_impl(const void* x, const void* values, const uint8_t* 
     // Pick the tiling that wastes fewer tile slots in its last wave; a CTA-pair tile does the same
     // work with about 1.3x less operand traffic, so it wins unless its wave fill is much worse.
     const int64_t sms = sm_count();
+    // a product that 256-row x 256-token pair tiles cover in one wave goes to the single-accumulator
+    // pair kernel (launch_sparse_pair picks it)
+    if (out >= 256 && ((out + 255) / 256) * ((T + 255) / 256) <= sms / 2 &&
+        ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN) > ((out + 255) / 256) * ((T + 255) / 256))
+        return launch_sparse_pair(x, values, meta_tc, bias, y, T, in, out, status, st);
     const int64_t t1 = ((out + SP_BM - 1) / SP_BM) * ((T + 127) / 128), s1 = sms;
     const int64_t t2 = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN), s2 = sms / 2;
     const double fill1 = (double)t1 / (double)(((t1 + s1 - 1) / s1) * s1);

@@ -62,6 +62,8 @@ def test_pack_meta_is_the_documented_permutation(ops):
 SPARSE_SHAPES = [
     (1, 128, 128), (16, 256, 128), (17, 384, 256), (128, 512, 384), (100, 272, 200), (1024, 1024, 512),
     (1, 4096, 4096), (16, 4096, 4096), (128, 4096, 11008), (1024, 11008, 4096), (8192, 4096, 4096),
+    # one wave of 256 x 256 pair tiles (single accumulator): T = 1024 on 4096 rows, ragged variants
+    (1024, 4096, 4096), (1000, 512, 1280), (520, 256, 4096),
     # two weight tiles per CTA (K >= 8192): ragged token count, a weight-row count that half fills the last 512-row tile
     (8000, 8192, 1280), (8192, 11008, 4096),
 ]
