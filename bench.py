@@ -477,9 +477,9 @@ def run_sparse24(args):
     rows_sweep = [int(r) for r in args.rows.split(",")]
     status = torch.zeros(4, dtype=torch.int32, device=dev)
 
-    def timeit(fn, iters):
-        """Device time per launch: `iters` launches captured in one CUDA graph and replayed, so that
-        the host launch path (tensor-map encoding, Python) is outside the timed region."""
+    def capture(fn, iters):
+        """`iters` launches captured in one CUDA graph, so that the host launch path (tensor-map
+        encoding, Python) is outside the timed region."""
         for _ in range(max(3, args.warmup)):
             fn()
         torch.cuda.synchronize()
@@ -489,12 +489,25 @@ def run_sparse24(args):
                 fn()
         graph.replay()
         torch.cuda.synchronize()
+        return graph
+
+    def replay_ms(graph, iters):
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
         graph.replay()
         e.record()
         torch.cuda.synchronize()
         return s.elapsed_time(e) / iters
+
+    def time_pair(fn_sparse, fn_dense, iters, rounds=3):
+        """Device time per launch of both products, replayed alternately (the clock drifts under
+        the power cap, so the two are taken in the same thermal state); the median round is kept."""
+        gs, gd = capture(fn_sparse, iters), capture(fn_dense, iters)
+        ts, td = [], []
+        for _ in range(rounds):
+            ts.append(replay_ms(gs, iters))
+            td.append(replay_ms(gd, iters))
+        return sorted(ts)[rounds // 2], sorted(td)[rounds // 2]
 
     cases = []
     for i, (name, out_f, in_f) in enumerate(shapes):
@@ -506,8 +519,8 @@ def run_sparse24(args):
         for T in rows_sweep:
             x = torch.randn(T, in_f, device=dev, generator=g).to(bf)
             xd = x if T % 8 == 0 else torch.cat([x, torch.zeros(8 - T % 8, in_f, device=dev, dtype=bf)])
-            ts = timeit(lambda: ops.sparse24_gemm(x, vals, meta_tc, status=status), args.steps)
-            td = timeit(lambda: ops.gemm_fwd(xd, wd, status=status), args.steps)
+            ts, td = time_pair(lambda: ops.sparse24_gemm(x, vals, meta_tc, status=status),
+                               lambda: ops.gemm_fwd(xd, wd, status=status), args.steps)
             flops = 2.0 * T * in_f * out_f
             bytes_s = in_f * out_f + in_f * out_f / 8 + 2.0 * T * (in_f + out_f)
             cases.append({"shape": name, "rows": T, "sparse_us": round(ts * 1e3, 1), "dense_us": round(td * 1e3, 1),
@@ -519,8 +532,8 @@ def run_sparse24(args):
     print(json.dumps({"metric": "hard-2:4 compressed GEMM, dense-equivalent TFLOP/s and speed-up over the dense masked GEMM",
                       "unit": "TFLOP/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
                       "config": {"workload": "llama2-7b-sparse24-inference", "timing": "CUDA events around a replayed CUDA graph "
-                                 "of `steps` back-to-back launches (device time; same input every launch, so "
-                                 "small cases run from L2)"},
+                                 "of `steps` back-to-back launches, sparse and dense replayed alternately, median of "
+                                 "three rounds (device time; same input every launch, so small cases run from L2)"},
                       "value": round(sum(c["sparse_tflops"] for c in big) / max(1, len(big)), 1),
                       "speedup_rows_8192": round(sum(c["speedup_vs_dense"] for c in big) / max(1, len(big)), 3),
                       "cases": cases}), flush=True)

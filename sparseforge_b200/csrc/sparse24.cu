@@ -587,7 +587,9 @@ constexpr int Q_STAGES = 3;
 constexpr int Q_THREADS = 320;  // TMA warp, MMA warp, eight epilogue warps
 constexpr int Q_STAGE_BYTES = 2 * SP_A_BYTES + 2 * P2_B_BOX_BYTES + 2 * SP_META_BYTES;  // 65536
 constexpr int Q_META_COL0 = 2 * P2_BN;  // 448: after the two accumulators
-constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256;
+constexpr int Q_EPI_ROW_BYTES = 64 + 16;                      // 32 bf16 features of one token, padded against bank conflicts
+constexpr int Q_EPI_WARP_BYTES = 32 * Q_EPI_ROW_BYTES;        // one turn buffer per epilogue warp
+constexpr int Q_SMEM_BYTES = Q_STAGES * Q_STAGE_BYTES + 1024 + 256 + 8 * Q_EPI_WARP_BYTES;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(Q_THREADS, 1)
 sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -714,8 +716,15 @@ sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         }
     } else {
         // ---------------- epilogue (both CTAs): warp (u, q) drains 32 rows x 224 tokens of weight tile u ----------------
+        // This epilogue is not hidden behind MMAs, so it is kept short: a lane owns one output
+        // feature in tensor memory, but the output is token-major, so 32 x 32 chunks are turned in a
+        // private shared-memory buffer and leave as 16-byte stores (4 per lane and chunk instead of
+        // 32 two-byte stores); the next chunk's accumulator read is in flight meanwhile, and the
+        // accumulators are handed back as soon as the last chunk has been read.
         const int q = warp & 3, u = (warp - 2) >> 2;
         const uint32_t leader_empty = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[0]), 0);
+        uint8_t* ebuf = base_ptr + STAGES * Q_STAGE_BYTES + 256 + (warp - 2) * Q_EPI_WARP_BYTES;
+        const bool vec_ok = (out & 7) == 0;
         bool ok = true;
         int t = 0;
         for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
@@ -724,25 +733,46 @@ sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[0]), (uint32_t)t & 1u, abort_flag, status, 44);
             if (!ok) break;
             ptx::tc_fence_after();
-            const int o = mt * 512 + u * 256 + (int)cta * 128 + q * 32 + lane;
+            const int o_base = mt * 512 + u * 256 + (int)cta * 128 + q * 32;
+            const int o = o_base + lane;
             const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
             const uint32_t taddr = tmem_base + (uint32_t)(u * P2_BN) + ((uint32_t)(q * 32) << 16);
+            constexpr int CHUNKS = P2_BN / 32;
+            uint32_t r[32];
+            ptx::tmem_ld_32x32b_x32(taddr, r);
+            ptx::tmem_ld_wait();
 #pragma unroll 1
-            for (int c = 0; c < P2_BN / 32; ++c) {
-                uint32_t r[32];
-                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
-                ptx::tmem_ld_wait();
-                if (o < out) {
+            for (int c = 0; c < CHUNKS; ++c) {
+                // feature-major registers -> token-major rows of 32 features (64 bytes, padded to 80)
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) {
-                        const int tok = nt * P2_BN + c * 32 + j;
-                        if (tok < T) Y[(int64_t)tok * out + o] = __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                for (int j = 0; j < 32; ++j)
+                    *reinterpret_cast<__nv_bfloat16*>(ebuf + j * Q_EPI_ROW_BYTES + lane * 2) =
+                        __float2bfloat16_rn(__uint_as_float(r[j]) + b);
+                __syncwarp();
+                if (c + 1 < CHUNKS) {
+                    ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 32), r);
+                } else {
+                    ptx::tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) ptx::mbar_arrive_cluster(leader_empty);
+                }
+                const int tok = nt * P2_BN + c * 32 + lane;
+                if (tok < T) {
+                    __nv_bfloat16* yrow = Y + (int64_t)tok * out + o_base;
+                    if (vec_ok) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (o_base + 8 * i < out)
+                                *reinterpret_cast<uint4*>(yrow + 8 * i) =
+                                    *reinterpret_cast<const uint4*>(ebuf + lane * Q_EPI_ROW_BYTES + i * 16);
+                    } else {
+                        for (int i = 0; i < 32 && o_base + i < out; ++i)
+                            yrow[i] = *reinterpret_cast<const __nv_bfloat16*>(ebuf + lane * Q_EPI_ROW_BYTES + i * 2);
                     }
                 }
+                __syncwarp();  // the buffer is rewritten by the next chunk
+                if (c + 1 < CHUNKS) ptx::tmem_ld_wait();
             }
-            ptx::tc_fence_before();
-            __syncwarp();
-            if (lane == 0) ptx::mbar_arrive_cluster(leader_empty);
         }
     }
 
@@ -789,14 +819,18 @@ static int launch_sparse_pair(const void* x, const void* values, const uint8_t* 
         SF_CHECK_CUDA(cudaGetLastError());
         return SF_OK;
     }
-    // Two weight tiles per CTA when K is long enough to amortise the epilogue that this variant
-    // cannot hide (measured at T = 8192: K = 11008 303 us against 338 us, K = 4096 127 against 126),
-    // the matrix has at least two 256-row tiles and there are enough work units for the pairs.
-    // SF_SPARSE24_ONE_TILE=1 / SF_SPARSE24_TWO_TILES=1 force either kernel for A/B runs.
-    static const bool one_tile_only = [] { const char* e = getenv("SF_SPARSE24_ONE_TILE"); return e && e[0] == '1'; }();
-    static const bool two_tiles_always = [] { const char* e = getenv("SF_SPARSE24_TWO_TILES"); return e && e[0] == '1'; }();
+    // Two weight tiles per CTA when the matrix has at least two 256-row tiles and there are enough
+    // work units for the pairs (measured at T = 8192, interleaved runs: K = 11008 301 us against
+    // 335 us for the one-tile kernel, K = 4096 123 against 127 us, the 11008-row matrix 341 against
+    // 342 us). SF_SPARSE24_ONE_TILE=1 forces the one-tile kernel for A/B runs.
+    const char* e1 = getenv("SF_SPARSE24_ONE_TILE");
+    const bool one_tile_only = e1 && e1[0] == '1';
     const int64_t tiles2 = ((out + 511) / 512) * ((T + P2_BN - 1) / P2_BN);
-    if (!one_tile_only && out >= 512 && tiles2 >= max_pairs && (in >= 8192 || two_tiles_always)) {
+    // waves of pairs each variant needs; a two-tile unit costs about 1.9 one-tile units
+    const int64_t tiles1 = ((out + 255) / 256) * ((T + P2_BN - 1) / P2_BN);
+    const double cost1 = (double)((tiles1 + max_pairs - 1) / max_pairs);
+    const double cost2 = 1.9 * (double)((tiles2 + max_pairs - 1) / max_pairs);
+    if (!one_tile_only && out >= 512 && tiles2 >= max_pairs && cost2 <= cost1) {
         const int pairs2 = (int)(tiles2 < max_pairs ? tiles2 : max_pairs);
         sparse24_gemm_pair2_kernel<<<2 * pairs2, Q_THREADS, Q_SMEM_BYTES, st>>>(tmA, tmB, tmE, (__nv_bfloat16*)y,
                                                                                 (const __nv_bfloat16*)bias, (int)out, (int)T,
