@@ -261,7 +261,8 @@ def test_paper_recipe_mask_path():
         assert torch.equal(layer._hard_mask_from_soft(layer.mask.data).cpu(), g[f"s{t}_hard"])
 
 
-@pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4), (2048, 264, 136, 4), (768, 64, 136, 2)])
+@pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4), (2048, 264, 136, 4), (768, 64, 136, 2),
+                                                 (4096, 256, 1376, 8)])
 def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
     """The all-gather and reduce-scatter epilogues with every "rank" played in turn on one GPU: the
     destinations are ordinary buffers of this GPU, so only the addressing is under test."""
