@@ -184,7 +184,7 @@ def run_ours(args):
 
                 wmax_ = max(widths)
                 buf_bytes = T * wmax_ * 2
-                arena = PeerArena(4 * buf_bytes, dev)
+                arena = PeerArena(4 * buf_bytes, dev, multicast=not args.no_multicast)
             except Exception as e:  # no peer mapping on this box: say so and use the library collectives
                 print(f"[bench] peer memory unavailable ({e}); using NCCL collectives", file=sys.stderr, flush=True)
                 collective = "nccl"
@@ -193,6 +193,7 @@ def run_ours(args):
         if int(flags) == 0 and collective == "p2p":
             arena.close()
             arena, collective = None, "nccl"
+    allgather = "none" if arena is None else "multimem" if arena.mc_base else "stores"
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     decay_t = 0.05 ** (1.0 / 9.0)
     launches = 0
@@ -256,8 +257,12 @@ def run_ours(args):
                 b = i % 2
                 y_off, s_off = b * buf_bytes, (2 + b) * buf_bytes
                 rows_t = T // world
-                timed("gemm", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
-                                                             rank * mt.rows, status=status))
+                if arena.mc_base:  # one store per piece, replicated by the NVSwitch
+                    timed("gemm", lambda: ops.gemm_fwd_multicast(x, mt.wm, arena.mc_ptr(y_off), mt.rows * world,
+                                                                 rank * mt.rows, status=status))
+                else:
+                    timed("gemm", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
+                                                                 rank * mt.rows, status=status))
                 timed("gemm", lambda: ops.gemm_dgrad_reducescatter(
                     dy, mt.wm, arena.ptrs(s_off + rank * rows_t * mt.cols * 2), rank, status=status))
                 # the barrier between ranks runs beside the weight-gradient product
@@ -371,7 +376,8 @@ def run_ours(args):
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
-                   "tokens": T, "row_sharded_over": world, "collective": collective, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
+                   "tokens": T, "row_sharded_over": world, "collective": collective,
+                   "allgather": allgather, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
         "clocks": clocks,
         "e2e": None if args.no_e2e else {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2),
                                          "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -548,6 +554,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: exchange through the GEMM epilogues and peer memory (p2p) or NCCL collectives")
+    ap.add_argument("--no-multicast", action="store_true",
+                    help="output all-gather by one store per destination instead of NVSwitch multicast stores")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")

@@ -392,12 +392,20 @@ SF_API int sf_kl_div_bwd(const void* student, const void* teacher, int dtype, co
  *   the slot [T/n, in] that rank c keeps for THIS rank's partial sums (`rank` = this rank's index:
  *   the tiles are walked owner by owner in turn, starting after it). After all ranks finished
  *   (a barrier the caller provides), the owner adds its n slots with sf_reduce_slots.
- * Both need T > 128 and bf16. Host arrays y_all / slots hold device pointers; peer pointers come from
+ * sf_masked_gemm_fwd_multicast: the same all-gather through an NVSwitch multicast object: y_mc is
+ *   the multicast address of the full output [T, out_total] (one buffer at the same offset on every
+ *   GPU, all bound to one multicast object, e.g. torch symmetric memory's multicast_ptr); each
+ *   16-byte piece leaves this GPU once (multimem.st) and the switch writes it into every GPU's
+ *   copy, this GPU's included, so the traffic is 1/(n-1) of the per-destination stores.
+ * All need T > 128 and bf16. Host arrays y_all / slots hold device pointers; peer pointers come from
  * sf_peer_open. No call waits on another GPU: ordering between ranks is the caller's barrier.
  */
 SF_API int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias, void* const* y_all,
                                  int n_dest, int64_t T, int64_t in, int64_t out_local, int64_t out_total,
                                  int64_t col_offset, float alpha, int dtype, int32_t* status, void* stream);
+SF_API int sf_masked_gemm_fwd_multicast(const void* x, const void* wm, const void* bias, void* y_mc, int64_t T,
+                                 int64_t in, int64_t out_local, int64_t out_total, int64_t col_offset,
+                                 float alpha, int dtype, int32_t* status, void* stream);
 SF_API int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks,
                                        int rank, int64_t T, int64_t in, int64_t out_local, int dtype,
                                        int32_t* status, void* stream);

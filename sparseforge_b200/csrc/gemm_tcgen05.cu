@@ -111,6 +111,9 @@ __device__ __forceinline__ void store_packed_chunk(__nv_bfloat16* dst, int col0,
 // DIST_SCATTER (input-gradient reduce-scatter): rows [c*rows_per, (c+1)*rows_per) go to ptr[c], the
 // slot GPU c keeps for this GPU's partial sums ([rows_per, ld]); the owner adds the slots up.
 // Peer pointers are plain global addresses mapped through CUDA IPC; the stores cross NVLink.
+// With `multicast` set, DIST_BROADCAST has ONE destination, the multicast address of the output
+// (the same buffer on every GPU, bound to one NVSwitch multicast object): each 16-byte piece is
+// stored once with multimem.st and replicated by the switch instead of once per destination.
 constexpr int DIST_LOCAL = 0, DIST_BROADCAST = 1, DIST_SCATTER = 2;
 constexpr int DIST_EPI_ROW_BYTES = 128 + 16;                   // 64 bf16 columns + padding against bank conflicts
 constexpr int DIST_EPI_WARP_BYTES = 32 * DIST_EPI_ROW_BYTES;   // one turn buffer per epilogue warp
@@ -124,6 +127,7 @@ struct PeerOut {
     int rows_per;
     int interleave;  // DIST_SCATTER: > 1 walks the tile rows owner by owner in turn (see interleave_rows)
     int rot;         // ... starting with the owner after this rank
+    int multicast;   // DIST_BROADCAST: ptr[0] is a multicast address
 };
 
 // Tile rows in raster order all belong to one owner for a long stretch, which would send the
@@ -520,7 +524,9 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                                 *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v[rg];
                             } else {
                                 const int64_t off = (int64_t)orow * po.ld + po.col_off + col;
-                                for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v[rg];
+                                if (po.multicast) ptx::multimem_st_v4(po.ptr[0] + off, v[rg]);
+                                else
+                                    for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v[rg];
                             }
                         }
                     }
@@ -846,22 +852,38 @@ int sf_selftest_bounded_wait(double limit_ms, int32_t* status, void* stream) {
     return SF_OK;
 }
 
-int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias, void* const* y_all, int n_dest,
-                                 int64_t T, int64_t in, int64_t out_local, int64_t out_total, int64_t col_offset,
-                                 float alpha, int dtype, int32_t* status, void* stream) {
-    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_fwd_allgather: bf16 only");
+static int fwd_exchange(const char* who, const void* x, const void* wm, const void* bias, void* const* dests, int n_dest,
+                        int multicast, int64_t T, int64_t in, int64_t out_local, int64_t out_total, int64_t col_offset,
+                        float alpha, int dtype, int32_t* status, void* stream) {
+    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "%s: bf16 only", who);
     PeerOut po;
-    int rc = fill_peers("sf_masked_gemm_fwd_allgather", y_all, n_dest, &po);
+    int rc = fill_peers(who, dests, n_dest, &po);
     if (rc) return rc;
-    rc = check_gemm_args("sf_masked_gemm_fwd_allgather", x, wm, y_all[0], T, in, out_local, dtype);
+    rc = check_gemm_args(who, x, wm, dests[0], T, in, out_local, dtype);
     if (rc) return rc;
     if (col_offset < 0 || col_offset % 8 || out_total % 8 || col_offset + out_local > out_total)
-        return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_fwd_allgather: columns [%lld, %lld) do not fit %lld (multiples of 8)",
+        return fail(SF_ERR_BAD_ARG, "%s: columns [%lld, %lld) do not fit %lld (multiples of 8)", who,
                     (long long)col_offset, (long long)(col_offset + out_local), (long long)out_total);
     po.ld = out_total;
     po.col_off = col_offset;
+    po.multicast = multicast;
     return launch_bf16<0, 0>(x, in, wm, in, nullptr, 0, bias, alpha, T, out_local, in, status, (cudaStream_t)stream,
                              DIST_BROADCAST, &po);
+}
+
+int sf_masked_gemm_fwd_allgather(const void* x, const void* wm, const void* bias, void* const* y_all, int n_dest,
+                                 int64_t T, int64_t in, int64_t out_local, int64_t out_total, int64_t col_offset,
+                                 float alpha, int dtype, int32_t* status, void* stream) {
+    return fwd_exchange("sf_masked_gemm_fwd_allgather", x, wm, bias, y_all, n_dest, 0, T, in, out_local, out_total,
+                        col_offset, alpha, dtype, status, stream);
+}
+
+int sf_masked_gemm_fwd_multicast(const void* x, const void* wm, const void* bias, void* y_mc, int64_t T, int64_t in,
+                                 int64_t out_local, int64_t out_total, int64_t col_offset, float alpha, int dtype,
+                                 int32_t* status, void* stream) {
+    void* one[1] = {y_mc};
+    return fwd_exchange("sf_masked_gemm_fwd_multicast", x, wm, bias, one, 1, 1, T, in, out_local, out_total, col_offset,
+                        alpha, dtype, status, stream);
 }
 
 int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, void* const* slots, int n_ranks, int rank,

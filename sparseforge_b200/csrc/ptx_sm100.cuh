@@ -190,6 +190,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t local_smem_addr, uint32_
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar_addr) : "memory");
 }
+// One 16-byte store to a multicast address: the NVSwitch writes it into the memory of every GPU
+// bound to the multicast object (the storing GPU included), so the data leaves this GPU once.
+__device__ __forceinline__ void multimem_st_v4(void* mc_addr, const uint4& v) {
+    asm volatile("multimem.st.weak.global.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+                 ::"l"(mc_addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
 // Tiled load whose completion bytes are counted on an mbarrier that may live in the peer CTA.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, uint32_t cluster_bar_addr,
                                                  int c0, int c1) {

@@ -453,6 +453,22 @@ def gemm_fwd_allgather(x2d, wm, dest_ptrs, out_total, col_offset, bias=None, alp
                                              _p(status), _stream()), "sf_masked_gemm_fwd_allgather")
 
 
+def gemm_fwd_multicast(x2d, wm, mc_ptr, out_total, col_offset, bias=None, alpha=1.0, status=None) -> None:
+    """The same output all-gather through an NVSwitch multicast object: ``mc_ptr`` is the multicast
+    address of the [T, out_total] bf16 output that every GPU holds at the same offset of its
+    symmetric buffer; each piece is stored once and replicated by the switch."""
+    _cuda(x2d, wm, bias, status)
+    T, k = x2d.shape
+    out_local, k2 = wm.shape
+    if k != k2:
+        raise ValueError(f"gemm_fwd_multicast: x has {k} features, weight has {k2}")
+    import ctypes
+
+    check(lib().sf_masked_gemm_fwd_multicast(_p(x2d), _p(wm), _p(bias), ctypes.c_void_p(int(mc_ptr)), T, k, out_local,
+                                             int(out_total), int(col_offset), float(alpha), _gemm_dtype(x2d, wm),
+                                             _p(status), _stream()), "sf_masked_gemm_fwd_multicast")
+
+
 def gemm_dgrad_reducescatter(dy2d, wm, slot_ptrs, rank, status=None) -> None:
     """Partial input gradient of this shard, token rows of rank c written into slot_ptrs[c] (the
     [T/n, in] slot rank c keeps for this rank). The owner sums its slots with ``reduce_slots``."""

@@ -127,7 +127,8 @@ def shard_sparse_linear(full_weight: torch.Tensor, config, bias: Optional[torch.
 
 class PeerArena:
     """One device buffer per rank that every other rank of the node can store into: the landing
-    zone of the sharded GEMM epilogues (``ops.gemm_fwd_allgather`` / ``ops.gemm_dgrad_reducescatter``).
+    zone of the sharded GEMM epilogues (``ops.gemm_fwd_allgather`` / ``ops.gemm_fwd_multicast`` /
+    ``ops.gemm_dgrad_reducescatter``).
 
     Each rank allocates ``nbytes``, exports it through CUDA IPC, and opens the buffers of the other
     ranks; ``ptrs(offset)`` then lists, rank by rank, the address of the same byte offset in every
@@ -135,17 +136,47 @@ class PeerArena:
     allocation twice. ``barrier()`` orders ranks: what a rank stored before its barrier is in the
     peers' memory once they have passed theirs."""
 
-    def __init__(self, nbytes: int, device, group=None):
-        from . import ops
-
+    def __init__(self, nbytes: int, device, group=None, multicast: bool = True):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
-        self.buf = torch.empty(int(nbytes), dtype=torch.uint8, device=device)
+        self.mc_base = 0
+        self._bases, self._ptrs, self._symm = [], [], None
+        if multicast and self._open_symmetric(int(nbytes), device):
+            pass
+        else:
+            self._open_ipc(int(nbytes), device)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def _open_symmetric(self, nbytes: int, device) -> bool:
+        """Arena in torch symmetric memory: peer addresses plus one multicast address whose stores
+        the NVSwitch replicates into every rank's arena. All ranks agree on the outcome; False
+        (nothing kept) when any of them could not map it, and the IPC arena is used instead."""
+        buf = handle = None
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            buf = symm.empty(nbytes, dtype=torch.uint8, device=torch.device(device))
+            handle = symm.rendezvous(buf, dist.group.WORLD if self.group is None else self.group)
+            ok = int(handle.multicast_ptr) != 0 and len(handle.buffer_ptrs) == self.world
+        except Exception:  # no symmetric-memory support in this build / on this node
+            ok = False
+        flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        if not int(flag.item()):
+            return False
+        self.buf, self._symm = buf, handle
+        self._ptrs = [int(p) for p in handle.buffer_ptrs]
+        self.mc_base = int(handle.multicast_ptr)
+        return True
+
+    def _open_ipc(self, nbytes: int, device) -> None:
+        from . import ops
+
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
         handle, off = ops.peer_export(self.buf)
         gathered = [None] * self.world
-        dist.all_gather_object(gathered, (handle, off), group=group)
-        self._bases, self._ptrs = [], []
+        dist.all_gather_object(gathered, (handle, off), group=self.group)
         for r, (h, o) in enumerate(gathered):
             if r == self.rank:
                 self._ptrs.append(self.buf.data_ptr())
@@ -153,7 +184,12 @@ class PeerArena:
                 base, ptr = ops.peer_open(h, o)
                 self._bases.append(base)
                 self._ptrs.append(ptr)
-        self._flag = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def mc_ptr(self, offset: int = 0) -> int:
+        """Multicast address of byte ``offset`` of every rank's arena; 0 without multicast."""
+        if offset % 16:
+            raise ValueError("PeerArena offsets must be multiples of 16 bytes")
+        return self.mc_base + int(offset) if self.mc_base else 0
 
     def ptrs(self, offset: int = 0):
         if offset % 16:
@@ -178,3 +214,4 @@ class PeerArena:
         for b in self._bases:
             ops.peer_close(b)
         self._bases = []
+        self.mc_base, self._symm, self.buf = 0, None, None

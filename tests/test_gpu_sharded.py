@@ -73,7 +73,7 @@ def _worker(rank, world, port, q):
         wfull = (torch.randn(out2, in2, generator=torch.Generator().manual_seed(6)) * 0.05).to(bf).to(dev)
         dyf = torch.randn(Tt, out2, generator=torch.Generator().manual_seed(7)).to(bf).to(dev)
         y_bytes, slot_bytes = Tt * out2 * 2, Tt * in2 * 2
-        arena = PeerArena(y_bytes + slot_bytes, dev)
+        arena = PeerArena(y_bytes + slot_bytes, dev, multicast=False)
         try:
             wl = wfull[rank * ol:(rank + 1) * ol].contiguous()
             dyl = dyf[:, rank * ol:(rank + 1) * ol].contiguous()
@@ -87,6 +87,22 @@ def _worker(rank, world, port, q):
             ok = ok and rel(dx_mine, ops.gemm_dgrad(dyf, wfull)[rank * rows:(rank + 1) * rows]) <= 1e-2
         finally:
             arena.close()
+        # and the all-gather through the NVSwitch multicast address of a symmetric arena, where the
+        # node offers one (a failure here is reported, not raised: both ranks release the arena)
+        mc = PeerArena(y_bytes, dev)
+        try:
+            if mc.mc_base:
+                mc.buf.zero_()
+                mc.barrier()
+                ops.gemm_fwd_multicast(xs, wl, mc.mc_ptr(0), out2, rank * ol)
+                mc.barrier()
+                ok = ok and rel(mc.view(0, (Tt, out2), bf), ops.gemm_fwd(xs, wfull)) <= 1e-2
+                ok = ok and len(mc.ptrs(0)) == world and mc.ptrs(0)[rank] == mc.buf.data_ptr()
+        except Exception:
+            print(f"[rank {rank}] multicast arena: {traceback.format_exc()}", flush=True)
+            ok = False
+        finally:
+            mc.close()
         flips = torch.tensor([int(sharded.shard.weight.flipped_mask)], device=dev)
         dist.all_reduce(flips)
         ok = ok and abs(int(flips) - int(full.weight.flipped_mask)) <= 2
