@@ -225,8 +225,17 @@ def run_ours(args):
             ready.record(copy_stream)
         return xs, dys, ready
 
+    # --overlap: the HBM-bound tail of a matrix (slot sum, optimizer+score, mask update) runs on a
+    # second stream beside the tensor-core products of the next matrix. tail_done[i] orders the
+    # next step's products of matrix i (they read the masked weight the tail writes) behind it.
+    overlap = args.overlap == "on" or (args.overlap == "auto" and world > 1)
+    side = torch.cuda.Stream(device=dev) if overlap else None
+    tail_done = [None] * len(mats)
+    slots_summed = [None]
+
     def step(it, timers=None, e2e=False):
         nonlocal launches
+        main = torch.cuda.current_stream()
         temp = max(0.05, decay_t ** (it % 10))
         hx = max(0.0, min(1.0, 1.0 - ((it % 10) - 1) / 9.0)) if (it % 10) >= 1 else 1.0
         pending = prefetch(0, it) if e2e else None
@@ -240,12 +249,17 @@ def run_ours(args):
             else:
                 x, dy = X[mt.cols], (dYfull[mt.rows] if world == 1 else dYshard[mt.name])
 
+            if tail_done[i] is not None:
+                main.wait_event(tail_done[i])
+
             def timed(key, fn):
                 nonlocal launches
                 if timers is None:
                     out = fn()
                 else:
-                    s, e = timers.region(key)
+                    s, e = timers.region(key.split(":")[0])
+                    if ":" in key:  # also listed under its own kind (rank 0's breakdown in `passes`)
+                        timers.pairs.setdefault(key, []).append((s, e))
                     s.record()
                     out = fn()
                     e.record()
@@ -258,46 +272,66 @@ def run_ours(args):
                 y_off, s_off = b * buf_bytes, (2 + b) * buf_bytes
                 rows_t = T // world
                 if arena.mc_base:  # one store per piece, replicated by the NVSwitch
-                    timed("gemm", lambda: ops.gemm_fwd_multicast(x, mt.wm, arena.mc_ptr(y_off), mt.rows * world,
+                    timed("gemm:fwd", lambda: ops.gemm_fwd_multicast(x, mt.wm, arena.mc_ptr(y_off), mt.rows * world,
                                                                  rank * mt.rows, status=status))
                 else:
-                    timed("gemm", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
+                    timed("gemm:fwd", lambda: ops.gemm_fwd_allgather(x, mt.wm, arena.ptrs(y_off), mt.rows * world,
                                                                  rank * mt.rows, status=status))
-                timed("gemm", lambda: ops.gemm_dgrad_reducescatter(
+                timed("gemm:dgrad", lambda: ops.gemm_dgrad_reducescatter(
                     dy, mt.wm, arena.ptrs(s_off + rank * rows_t * mt.cols * 2), rank, status=status))
-                # the barrier between ranks runs beside the weight-gradient product
+                # the barrier between ranks runs beside the weight-gradient product; a rank joins it
+                # only after it has summed the slots of the matrix before (the peers overwrite that
+                # landing buffer two matrices later, once they are past this barrier)
+                if slots_summed[0] is not None:
+                    main.wait_event(slots_summed[0])
                 arrived = arena.barrier(async_op=True)
-                dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
-                arrived.wait()
-                timed("reduce", lambda: ops.reduce_slots(arena.view(s_off, (world, rows_t, mt.cols), bf)))
+                dw = timed("gemm:wgrad", lambda: ops.gemm_wgrad(dy, x, status=status))
+                with torch.cuda.stream(side if side is not None else main):
+                    arrived.wait()
+                    timed("reduce", lambda: ops.reduce_slots(arena.view(s_off, (world, rows_t, mt.cols), bf)))
+                    if side is not None:
+                        slots_summed[0] = torch.cuda.Event()
+                        slots_summed[0].record(side)
             else:
-                y = timed("gemm", lambda: ops.gemm_fwd(x, mt.wm, status=status))
+                y = timed("gemm:fwd", lambda: ops.gemm_fwd(x, mt.wm, status=status))
                 if world > 1:
                     # the collectives run on NCCL's own stream and overlap the next products
                     yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
                     works.append(dist.all_gather_into_tensor(yg, y, async_op=True))
-                dx = timed("gemm", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
+                dx = timed("gemm:dgrad", lambda: ops.gemm_dgrad(dy, mt.wm, status=status))
                 if world > 1:
                     dxs = torch.empty(T // world, mt.cols, dtype=bf, device=dev)
                     works.append(dist.reduce_scatter_tensor(dxs, dx, async_op=True))
-                dw = timed("gemm", lambda: ops.gemm_wgrad(dy, x, status=status))
-            # the reference's order: Hutchinson sample into H, optimizer step, score of the NEW weight
-            # (one pass over the matrix), then the mask update that consumes score and its statistics
-            timed("optim", lambda: ops.adamw_masked_score(
-                mt.W, dw, mt.m, mt.v, mask=mt.mask, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
-                decay=2e-4, step=it + 1, hvp=mt.hvp, probe=mt.probe, beta_h=0.99, H=mt.H, score=None,
-                norm=mt.norm, scratch=mt.scratch, metric="hessian_obd"))
-            launches += 1  # the one-block statistics kernel behind the score
-            # the mask update forms the score again from W and H (it reads W anyway), so the optimizer
-            # pass above writes no score tensor
-            timed("mask", lambda: ops.mask_update_nm24_from_weight(mt.W, mt.H, mt.norm, mt.mask, mt.stats, mt.wm,
-                                                                   mt.meta, metric="hessian_obd", temperature=temp,
-                                                                   mask_lr=0.1, hx=hx))
+                dw = timed("gemm:wgrad", lambda: ops.gemm_wgrad(dy, x, status=status))
+            if side is not None:
+                produced = torch.cuda.Event()
+                produced.record(main)
+                dw.record_stream(side)
+            with torch.cuda.stream(side if side is not None else main):
+                if side is not None:
+                    side.wait_event(produced)
+                # the reference's order: Hutchinson sample into H, optimizer step, score of the NEW weight
+                # (one pass over the matrix), then the mask update that consumes score and its statistics
+                timed("optim", lambda: ops.adamw_masked_score(
+                    mt.W, dw, mt.m, mt.v, mask=mt.mask, lr=1e-4, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                    decay=2e-4, step=it + 1, hvp=mt.hvp, probe=mt.probe, beta_h=0.99, H=mt.H, score=None,
+                    norm=mt.norm, scratch=mt.scratch, metric="hessian_obd"))
+                launches += 1  # the one-block statistics kernel behind the score
+                # the mask update forms the score again from W and H (it reads W anyway), so the optimizer
+                # pass above writes no score tensor
+                timed("mask", lambda: ops.mask_update_nm24_from_weight(mt.W, mt.H, mt.norm, mt.mask, mt.stats, mt.wm,
+                                                                       mt.meta, metric="hessian_obd", temperature=temp,
+                                                                       mask_lr=0.1, hx=hx))
+                if side is not None:
+                    tail_done[i] = torch.cuda.Event()
+                    tail_done[i].record(side)
             for wk in works:
                 wk.wait()
             if e2e:
                 stage_free[i % 2].record()
         if e2e:
+            if side is not None:
+                main.wait_stream(side)
             step_done[it % 2].record()
             return torch.stack([mt.stats for mt in mats]).to("cpu", non_blocking=False)
         return None
@@ -319,6 +353,8 @@ def run_ours(args):
     t0.record()
     for it in range(args.steps):
         step(args.warmup + it, timers)
+    if side is not None:
+        torch.cuda.current_stream().wait_stream(side)
     t1.record()
     barrier()
     clocks = sampler.stop() if rank == 0 else None
@@ -377,7 +413,7 @@ def run_ours(args):
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "collective": collective,
-                   "allgather": allgather, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
+                   "allgather": allgather, "overlap_hbm_passes": overlap, "l2": "inputs larger than L2 (each matrix pass touches >100 MB)"},
         "clocks": clocks,
         "e2e": None if args.no_e2e else {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2),
                                          "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
@@ -394,6 +430,8 @@ def run_ours(args):
             "mask_update_gbs": gbs(BYTES_MASK, mask_ms), "hbm_peak_gbs": peaks["hbm_gbs"],
             "gemm_ms_per_step": gemm_ms / args.steps, "optim_score_ms_per_step": optim_ms / args.steps,
             "mask_ms_per_step": mask_ms / args.steps,
+            "rank0_ms_per_step": {k.split(":")[-1]: round(v / args.steps, 4) for k, v in sorted(part.items())
+                                  if ":" in k or k == "reduce"},
         },
     }
     for k in ("optim_score_gbs", "mask_update_gbs"):
@@ -556,6 +594,11 @@ def main():
                     help="N > 1: exchange through the GEMM epilogues and peer memory (p2p) or NCCL collectives")
     ap.add_argument("--no-multicast", action="store_true",
                     help="output all-gather by one store per destination instead of NVSwitch multicast stores")
+    ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],
+                    help="run each matrix's slot sum / optimizer / mask passes on a second stream beside the next "
+                         "matrix's products; auto = when the layer set is sharded (the exchange kernels wait on "
+                         "NVLink and leave HBM idle; on one GPU the chip is power-capped and the overlap gains "
+                         "0-4 %% while every kernel slows down)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")
