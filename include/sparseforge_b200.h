@@ -182,6 +182,44 @@ SF_API int sf_mask_update_nm24_from_weight(const void* W, int w_dtype, const flo
                                     void* stream);
 
 /*
+ * sf_mask_update_nm24 with freeze bands (freeze_low > 0 or freeze_high < 1 in the layer config).
+ *   replaces: the frozen-entry rule of compute_gate_target, legacy/sparse_modeling.py:1227-1229
+ *             (a frozen entry's gate is its own value), and the snap at the end of update_mask,
+ *             :1621-1642: after the update, entries <= freeze_low become 0 and, when apply_high
+ *             (the reference applies it from step 2000 on), entries >= freeze_high become 1; the
+ *             snapped entries are flagged. Projection, masked weight, metadata, flip count and
+ *             sums see the snapped mask, as the reference's do.
+ * frozen_flags: [rows, cols] fp32, 0 or 1, read and updated in place (flags only ever rise).
+ */
+SF_API int sf_mask_update_nm24_frozen(const float* score, const float* norm, const float* tau,
+                               float* frozen_flags, double freeze_low, double freeze_high, int apply_high,
+                               float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta,
+                               double* stats, int64_t rows, int64_t cols, double temperature,
+                               double mask_lr, double pen, int penalty_mode, double beta_s,
+                               double binarize_decay, double hx, int structured_exact, int score_bf16,
+                               void* stream);
+
+/*
+ * WANDA importance metric: per-input-channel activation energy and the score built from it.
+ *   replaces: SparseLinear.add_batch, legacy/sparse_modeling.py:884-898 (called from the calibration
+ *             hooks of legacy/utils.py:2045-2047), and the 'wanda' branch of compute_gate_target,
+ *             legacy/sparse_modeling.py:1071-1077, with the score statistics of :1084-1088.
+ * sf_wanda_add_batch: scaler_row[c] <- scaler_row[c] * keep, then + ||x[:, c]||_2^2 / denom, both
+ *   rounded to s_dtype as the two in-place tensor operations are. x: [rows, cols] of x_dtype (the
+ *   batch flattened to tokens), cols % 8 == 0. The caller keeps nsamples on the host and passes
+ *   keep = nsamples / (nsamples + batch + 1e-8) and denom = max(nsamples + batch, 1).
+ *   scratch: sf_wanda_scratch_floats(cols) floats; the column sums are formed in a fixed order.
+ * sf_wanda_score: score[r, c] <- |W[r, c]| * sqrt(scaler_row[c] + eps) (fp32 output; arithmetic
+ *   rounded to bf16 after every operation where both operands are bf16), norm <- (mean, population
+ *   std + 1e-6); scratch as for sf_hutch_score (scratch[0], scratch[1] = the two sums).
+ */
+SF_API int64_t sf_wanda_scratch_floats(int64_t cols);
+SF_API int sf_wanda_add_batch(const void* x, int x_dtype, int64_t rows, int64_t cols, void* scaler_row,
+                       int s_dtype, double keep, double denom, float* scratch, void* stream);
+SF_API int sf_wanda_score(const void* W, int w_dtype, const void* scaler_row, int s_dtype, int64_t rows,
+                   int64_t cols, double eps, float* score, float* norm, double* scratch, void* stream);
+
+/*
  * Joint mask update of a GLU gate / up pair: both layers are updated from ONE score, the sum of
  * their importance scores, so that the same positions are pruned in both.
  *   replaces: _update_glu_joint_mask legacy/utils.py:363-479 with _compute_joint_gate_target

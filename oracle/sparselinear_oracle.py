@@ -96,9 +96,25 @@ def hutchinson_accumulate(H: torch.Tensor, hvp: torch.Tensor, v: torch.Tensor, b
     return H.clone().mul_(beta).add_(d, alpha=1 - beta)
 
 
-def importance_score(W, metric="hessian_obd", H=None, grad_ema=None, temperature=1.0):
+def wanda_add_batch(scaler_row, nsamples, inp):
+    """SparseLinear.add_batch, legacy/sparse_modeling.py:884-898: running mean over samples of the
+    squared L2 norm of every input channel. Returns the new scaler_row and sample count."""
+    if inp.dim() == 2:
+        inp = inp.unsqueeze(0)
+    batch = inp.shape[0]
+    if inp.dim() == 3:
+        inp = inp.reshape(-1, inp.shape[-1])
+    s = scaler_row.clone().mul_(nsamples / (nsamples + batch + 1e-8))
+    nsamples += batch
+    s.add_((torch.norm(inp.t().float(), p=2, dim=1) ** 2) / max(nsamples, 1))
+    return s, nsamples
+
+
+def importance_score(W, metric="hessian_obd", H=None, grad_ema=None, temperature=1.0, scaler_row=None):
     """legacy/sparse_modeling.py:1041-1079."""
     eps = 1e-8
+    if metric == "wanda":
+        return W.abs() * torch.sqrt(scaler_row.reshape(1, -1) + eps)
     if metric == "magnitude":
         return W.abs()
     if metric == "movement":
@@ -194,6 +210,44 @@ def mask_update(mask, G, *, mask_lr, lambda_mid=0.0, pen_lr=None, penalty_mode="
 # --------------------------------------------------------------------------------------
 # block-sparse soft masks (hard_mask_type block_sparse16 / block_sparse32)
 # --------------------------------------------------------------------------------------
+def freeze_gate(G, mask, frozen):
+    """legacy/sparse_modeling.py:1227-1229: a frozen entry's gate target is its own mask value."""
+    return torch.where(frozen.bool(), mask, G)
+
+
+def freeze_bands(mask, frozen, low, high, step):
+    """Tail of update_mask, legacy/sparse_modeling.py:1621-1642: entries <= low snap to 0 at every
+    update, entries >= high snap to 1 from step 2000 on; what was snapped is flagged."""
+    mask, frozen = mask.clone(), frozen.clone()
+    f0, f1 = mask <= low, mask >= high
+    mask[f0] = 0.0
+    applied = f0.clone()
+    if step >= 2000:
+        mask[f1] = 1.0
+        applied |= f1
+    return mask, torch.maximum(frozen, applied.to(frozen.dtype))
+
+
+def harden_fraction(masks, flags, fraction=0.2, band_low=0.4, band_high=0.6):
+    """legacy/utils.py:1236-1276 on lists of masks / flags; returns (masks, flags, count)."""
+    masks, flags = [m.clone() for m in masks], [f.clone() for f in flags]
+    sels = [(~f.bool()) & (m > band_low) & (m < band_high) for m, f in zip(masks, flags)]
+    diffs = [(m[s] - 0.5).abs() for m, s in zip(masks, sels)]
+    all_diff = torch.cat(diffs) if diffs else torch.zeros(0)
+    k = int(all_diff.numel() * fraction)
+    if k <= 0:
+        return masks, flags, 0
+    thr = torch.topk(all_diff, k, largest=False).values.max()
+    count = 0
+    for m, f, s, d in zip(masks, flags, sels, diffs):
+        pick = torch.zeros_like(s)
+        pick[s] = d <= thr
+        m[pick] = (m[pick] > 0.5).to(m.dtype)
+        f[pick] = 1.0
+        count += int(pick.sum())
+    return masks, flags, count
+
+
 def _block_view(x, bs):
     rows, cols = x.shape
     ob, ib = rows // bs, cols // bs

@@ -58,6 +58,12 @@ _SIGNATURES = {
     "sf_kl_div_bwd": (c_int, [_P, _P, c_int, _P, _P, c_int64, c_int64, c_double, c_double, _P, _P]),
     "sf_masked_gemm_fwd_allgather": (c_int, [_P, _P, _P, _P, c_int, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                              c_int, _P, _P]),
+    "sf_mask_update_nm24_frozen": (c_int, [_P, _P, _P, _P, c_double, c_double, c_int, _P, _P, c_int, _P, _P, _P, c_int64,
+                                           c_int64, c_double, c_double, c_double, c_int, c_double, c_double, c_double,
+                                           c_int, c_int, _P]),
+    "sf_wanda_scratch_floats": (c_int64, [c_int64]),
+    "sf_wanda_add_batch": (c_int, [_P, c_int, c_int64, c_int64, _P, c_int, c_double, c_double, _P, _P]),
+    "sf_wanda_score": (c_int, [_P, c_int, _P, c_int, c_int64, c_int64, c_double, _P, _P, _P, _P]),
     "sf_masked_gemm_fwd_multicast": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                              c_int, _P, _P]),
     "sf_masked_gemm_dgrad_reducescatter": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),

@@ -185,6 +185,108 @@ score_sum_kernel(const float* __restrict__ a, const float* __restrict__ b, float
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// WANDA: per-input-channel activation energy and the score |W| * sqrt(scaler_row + eps)
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+constexpr int kWandaRowLanes = 8;                      // row lanes per block
+constexpr int kWandaColsPerBlock = (kThreads / kWandaRowLanes) * 8;  // 32 threads x 8 columns
+constexpr int kWandaMaxRowBlocks = 64;
+
+// partial[blockIdx.y][c] = sum over this block's rows of x[r, c]^2 (fp32, rows in a fixed order)
+template <typename TX>
+__global__ void __launch_bounds__(kThreads)
+wanda_colsumsq_kernel(const TX* __restrict__ x, int64_t rows, int64_t cols, float* __restrict__ partial) {
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    const int64_t c0 = (int64_t)blockIdx.x * kWandaColsPerBlock + tx * 8;
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    if (c0 < cols)
+        for (int64_t r = (int64_t)blockIdx.y * kWandaRowLanes + ty; r < rows; r += (int64_t)gridDim.y * kWandaRowLanes) {
+            float v[8];
+            Vec8<TX>::load(x + r * cols + c0, v);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = fmaf(v[i], v[i], acc[i]);
+        }
+    __shared__ float red[kWandaRowLanes][kWandaColsPerBlock + 8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) red[ty][tx * 8 + i] = acc[i];
+    __syncthreads();
+    const int64_t c = (int64_t)blockIdx.x * kWandaColsPerBlock + threadIdx.x;
+    if (threadIdx.x < kWandaColsPerBlock && c < cols) {
+        float s = 0.f;
+#pragma unroll
+        for (int j = 0; j < kWandaRowLanes; ++j) s += red[j][threadIdx.x];
+        partial[(int64_t)blockIdx.y * cols + c] = s;
+    }
+}
+
+// scaler_row <- round(scaler_row * keep) then round(scaler_row + norm2(x[:, c])^2 / denom), the two
+// in-place tensor operations of add_batch (the norm is a square root that is squared again).
+template <typename TS>
+__global__ void __launch_bounds__(kThreads)
+wanda_scaler_update_kernel(const float* __restrict__ partial, int row_blocks, int64_t cols, float keep, float denom,
+                           TS* __restrict__ scaler) {
+    const int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x;
+    if (c >= cols) return;
+    float s = 0.f;
+    for (int j = 0; j < row_blocks; ++j) s += partial[(int64_t)j * cols + c];
+    const float nrm = __fsqrt_rn(s);
+    const float add = __fdiv_rn(__fmul_rn(nrm, nrm), denom);
+    float cur = to_float(scaler[c]);
+    cur = Vec8<TS>::round(__fmul_rn(cur, keep));
+    cur = Vec8<TS>::round(__fadd_rn(cur, add));
+    scaler[c] = from_float<TS>(cur);
+}
+
+// score = |W| * sqrt(scaler_row + eps) in the dtypes torch would use (bf16 arithmetic rounds after
+// every operation; a bf16 weight times an fp32 scaler is an fp32 product), with partial sums.
+template <typename TW, typename TS>
+__global__ void __launch_bounds__(kThreads)
+wanda_score_kernel(const TW* __restrict__ W, const TS* __restrict__ scaler, int64_t cols, float eps,
+                   float* __restrict__ score, double* __restrict__ partials, int64_t chunks) {
+    constexpr bool kRoundProduct = sizeof(TW) == 2 && sizeof(TS) == 2;
+    double acc_s = 0.0, acc_s2 = 0.0;
+    for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
+        float w[8], sc[8], s[8];
+        Vec8<TW>::load(W + c * 8, w);
+        const int64_t col = (c * 8) % cols;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc[i] = to_float(scaler[col + i]);
+        float ps = 0.0f, ps2 = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float root = Vec8<TS>::round(__fsqrt_rn(Vec8<TS>::round(__fadd_rn(sc[i], eps))));
+            const float prod = __fmul_rn(fabsf(w[i]), root);
+            s[i] = kRoundProduct ? Vec8<TW>::round(prod) : prod;
+            ps += s[i];
+            ps2 = fmaf(s[i], s[i], ps2);
+        }
+        Vec8<float>::store(score + c * 8, s);
+        acc_s += (double)ps;
+        acc_s2 += (double)ps2;
+    }
+    __shared__ double red[2][kThreads / 32];
+    acc_s = warp_sum(acc_s);
+    acc_s2 = warp_sum(acc_s2);
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    if (lane == 0) { red[0][wid] = acc_s; red[1][wid] = acc_s2; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double sa = 0.0, sb = 0.0;
+#pragma unroll
+        for (int i = 0; i < kThreads / 32; ++i) { sa += red[0][i]; sb += red[1][i]; }
+        partials[2 * blockIdx.x] = sa;
+        partials[2 * blockIdx.x + 1] = sb;
+    }
+}
+
 // Summary of one soft mask for logging: twelve sums (count, sum m, sum m^2, entropy with the
 // reference's fp32 clamp, counts below 0.5 / 0.1 / 0.01 and above 0.9 / 0.99 / 0.5, sums of the
 // entries below and above 0.5), added to `out` with atomics.
@@ -336,6 +438,11 @@ struct MaskUpdateParams {
     const float* tau;  // unstructured gate: threshold in normalised-score units (device); null = 2:4 gate
     const float* pen_mask;  // mask the penalty pull is taken from (GLU joint update); null = the updated mask
     int metric;             // FROM_W instantiations: which score to form from W and H
+    // freeze bands: flags (fp32 0 / 1, updated in place) of entries that no longer follow the gate;
+    // entries at or below freeze_low snap to 0, entries at or above freeze_high to 1 (when enabled)
+    float* frozen;
+    float freeze_low, freeze_high;
+    int freeze_high_on;
 };
 
 __device__ __forceinline__ float effective_mask_value(float m, bool kept, const MaskUpdateParams& P) {
@@ -386,6 +493,7 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
     const bool mix = !PLAIN && P.beta_s > 0.0f;
     const bool penalty = !PLAIN && P.pen != 0.0f;
     const bool binarize = !PLAIN && P.binarize;
+    const bool freeze = !PLAIN && !FROM_W && P.frozen != nullptr;
     const uint32_t omhx_bits = P.soft_only ? 0u : __float_as_uint(P.one_minus_hx);
     const float hx = P.soft_only ? 1.0f : P.hx;
     GroupStats gs;
@@ -408,6 +516,8 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
                 else if (P.metric == SF_METRIC_MAGNITUDE) sc[i] = fabsf(w[i]);
             }
         }
+        float fz[8];
+        if (freeze) Vec8<float>::load(P.frozen + e, fz);
         uint32_t kp8 = 0, kn8 = 0;
 #pragma unroll
         for (int g = 0; g < 2; ++g) {
@@ -435,6 +545,8 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
                     gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), t);
                     if (score_bf16) gi = bf16_round_int(gi);
                 }
+                // a frozen entry's gate is its own value: the pull toward the score is switched off
+                if (freeze && fz[4 * g + i] != 0.0f) gi = mp[i];
                 G[i] = gi;
             }
             if (penalty) {
@@ -472,6 +584,13 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
             for (int i = 0; i < 4; ++i) {
                 // clamp((1-a) mask + a G, 0, 1): the clamp rides on the multiply-add
                 mn[i] = __saturatef(__fmaf_rn(P.a, G[i], __fmul_rn(mp[i], P.one_minus_a)));
+                if (freeze) {
+                    const bool low = mn[i] <= P.freeze_low;
+                    const bool high = P.freeze_high_on && mn[i] >= P.freeze_high;
+                    if (low) mn[i] = 0.0f;
+                    if (high) mn[i] = 1.0f;
+                    if (low || high) fz[4 * g + i] = fmaxf(fz[4 * g + i], 1.0f);
+                }
                 m[4 * g + i] = mn[i];
             }
             uint32_t kp[4], kn[4];
@@ -492,6 +611,7 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
         }
         gs.flips += __popc(kp8 ^ kn8);
         Vec8<float>::store(mask + e, m);
+        if (freeze) Vec8<float>::store(P.frozen + e, fz);
         if (EMIT_WM) Vec8<TW>::store_product(wm + e, wraw, eff);
         if (EMIT_META) meta[c] = (uint8_t)(nibble_of_keep_lut(kn8 & 0xFu) | (nibble_of_keep_lut(kn8 >> 4) << 4));
     }
@@ -855,14 +975,24 @@ static MaskUpdateParams make_mask_params(double temperature, double mask_lr, dou
     P.tau = nullptr;
     P.pen_mask = nullptr;
     P.metric = SF_METRIC_HESSIAN_OBD;
+    P.frozen = nullptr;
+    P.freeze_low = 0.0f;
+    P.freeze_high = 1.0f;
+    P.freeze_high_on = 0;
     return P;
 }
+
+struct FreezeBands {
+    float* flags = nullptr;
+    double low = 0.0, high = 1.0;
+    int high_on = 0;
+};
 
 static int mask_update_impl(const float* score, const float* norm, const float* tau, const float* pen_mask,
                             float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats,
                             int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
                             int penalty_mode, double beta_s, double binarize_decay, double hx, int structured_exact,
-                            int score_bf16, void* stream);
+                            int score_bf16, void* stream, const FreezeBands& fb = FreezeBands());
 
 int sf_mask_update_nm24(const float* score, const float* norm, const float* tau, float* mask, const void* W,
                         int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
@@ -884,6 +1014,24 @@ int sf_mask_update_nm24_joint(const float* score, const float* norm, const float
                             mask_lr, pen, penalty_mode, beta_s, binarize_decay, hx, structured_exact, score_bf16, stream);
 }
 
+int sf_mask_update_nm24_frozen(const float* score, const float* norm, const float* tau, float* frozen_flags,
+                               double freeze_low, double freeze_high, int apply_high, float* mask, const void* W,
+                               int w_dtype, void* wm, uint8_t* meta, double* stats, int64_t rows, int64_t cols,
+                               double temperature, double mask_lr, double pen, int penalty_mode, double beta_s,
+                               double binarize_decay, double hx, int structured_exact, int score_bf16, void* stream) {
+    SF_CHECK_ARG(frozen_flags != nullptr, "sf_mask_update_nm24_frozen: frozen_flags must be non-null");
+    if (!aligned16(frozen_flags))
+        return fail(SF_ERR_ALIGNMENT, "sf_mask_update_nm24_frozen: frozen_flags must be 16-byte aligned");
+    FreezeBands fb;
+    fb.flags = frozen_flags;
+    fb.low = freeze_low;
+    fb.high = freeze_high;
+    fb.high_on = apply_high ? 1 : 0;
+    return mask_update_impl(score, norm, tau, nullptr, mask, W, w_dtype, wm, meta, stats, rows, cols, temperature,
+                            mask_lr, pen, penalty_mode, beta_s, binarize_decay, hx, structured_exact, score_bf16, stream,
+                            fb);
+}
+
 int sf_score_sum(const float* a, const float* b, float* out, float* norm, double* scratch, int64_t n, void* stream) {
     SF_CHECK_ARG(a && b && out && norm && scratch, "sf_score_sum: a, b, out, norm, scratch must be non-null");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_score_sum: n=%lld must be a positive multiple of 8", (long long)n);
@@ -894,6 +1042,71 @@ int sf_score_sum(const float* a, const float* b, float* out, float* norm, double
     int grid = grid_one_wave((const void*)score_sum_kernel, chunks);
     if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;
     score_sum_kernel<<<grid, kThreads, 0, st>>>(a, b, out, scratch, chunks);
+    SF_CHECK_CUDA(cudaGetLastError());
+    score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int64_t sf_wanda_scratch_floats(int64_t cols) { return cols > 0 ? cols * kWandaMaxRowBlocks : 0; }
+
+int sf_wanda_add_batch(const void* x, int x_dtype, int64_t rows, int64_t cols, void* scaler_row, int s_dtype,
+                       double keep, double denom, float* scratch, void* stream) {
+    SF_CHECK_ARG(x && scaler_row && scratch, "sf_wanda_add_batch: x, scaler_row, scratch must be non-null");
+    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0, "sf_wanda_add_batch: rows=%lld, cols=%lld (cols a multiple of 8)",
+                 (long long)rows, (long long)cols);
+    SF_CHECK_ARG((x_dtype == SF_F32 || x_dtype == SF_BF16) && (s_dtype == SF_F32 || s_dtype == SF_BF16),
+                 "sf_wanda_add_batch: dtypes must be SF_F32 or SF_BF16");
+    SF_CHECK_ARG(denom > 0.0, "sf_wanda_add_batch: denom must be positive");
+    if (!aligned16(x)) return fail(SF_ERR_ALIGNMENT, "sf_wanda_add_batch: x must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int col_blocks = (int)((cols + kWandaColsPerBlock - 1) / kWandaColsPerBlock);
+    int64_t row_blocks = (4 * (int64_t)sm_count() + col_blocks - 1) / col_blocks;
+    const int64_t by_rows = (rows + kWandaRowLanes - 1) / kWandaRowLanes;
+    if (row_blocks > by_rows) row_blocks = by_rows;
+    if (row_blocks > kWandaMaxRowBlocks) row_blocks = kWandaMaxRowBlocks;
+    if (row_blocks < 1) row_blocks = 1;
+    const dim3 grid((unsigned)col_blocks, (unsigned)row_blocks);
+    if (x_dtype == SF_BF16)
+        wanda_colsumsq_kernel<__nv_bfloat16><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)x, rows, cols, scratch);
+    else
+        wanda_colsumsq_kernel<float><<<grid, kThreads, 0, st>>>((const float*)x, rows, cols, scratch);
+    SF_CHECK_CUDA(cudaGetLastError());
+    const int ub = (int)((cols + kThreads - 1) / kThreads);
+    if (s_dtype == SF_BF16)
+        wanda_scaler_update_kernel<__nv_bfloat16><<<ub, kThreads, 0, st>>>(scratch, (int)row_blocks, cols, (float)keep,
+                                                                            (float)denom, (__nv_bfloat16*)scaler_row);
+    else
+        wanda_scaler_update_kernel<float><<<ub, kThreads, 0, st>>>(scratch, (int)row_blocks, cols, (float)keep,
+                                                                    (float)denom, (float*)scaler_row);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_wanda_score(const void* W, int w_dtype, const void* scaler_row, int s_dtype, int64_t rows, int64_t cols,
+                   double eps, float* score, float* norm, double* scratch, void* stream) {
+    SF_CHECK_ARG(W && scaler_row && score && norm && scratch,
+                 "sf_wanda_score: W, scaler_row, score, norm, scratch must be non-null");
+    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % 8 == 0, "sf_wanda_score: cols=%lld must be a positive multiple of 8",
+                 (long long)cols);
+    SF_CHECK_ARG((w_dtype == SF_F32 || w_dtype == SF_BF16) && (s_dtype == SF_F32 || s_dtype == SF_BF16),
+                 "sf_wanda_score: dtypes must be SF_F32 or SF_BF16");
+    if (!(aligned16(W) && aligned16(score))) return fail(SF_ERR_ALIGNMENT, "sf_wanda_score: W and score must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int64_t n = rows * cols, chunks = n / 8;
+    int grid = 0;
+#define SF_LAUNCH_WS(TW, TS)                                                                                     \
+    do {                                                                                                         \
+        auto kern = wanda_score_kernel<TW, TS>;                                                                  \
+        grid = grid_one_wave((const void*)kern, chunks);                                                         \
+        if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;                                                  \
+        kern<<<grid, kThreads, 0, st>>>((const TW*)W, (const TS*)scaler_row, cols, (float)eps, score, scratch, chunks); \
+    } while (0)
+    if (w_dtype == SF_BF16 && s_dtype == SF_BF16) SF_LAUNCH_WS(__nv_bfloat16, __nv_bfloat16);
+    else if (w_dtype == SF_BF16) SF_LAUNCH_WS(__nv_bfloat16, float);
+    else if (s_dtype == SF_BF16) SF_LAUNCH_WS(float, __nv_bfloat16);
+    else SF_LAUNCH_WS(float, float);
+#undef SF_LAUNCH_WS
     SF_CHECK_CUDA(cudaGetLastError());
     score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
     SF_CHECK_CUDA(cudaGetLastError());
@@ -943,7 +1156,7 @@ static int mask_update_impl(const float* score, const float* norm, const float* 
                             float* mask, const void* W, int w_dtype, void* wm, uint8_t* meta, double* stats,
                             int64_t rows, int64_t cols, double temperature, double mask_lr, double pen,
                             int penalty_mode, double beta_s, double binarize_decay, double hx, int structured_exact,
-                            int score_bf16, void* stream) {
+                            int score_bf16, void* stream, const FreezeBands& fb) {
     SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm24: score, norm, mask, stats must be non-null");
     SF_CHECK_ARG(rows > 0 && cols > 0, "sf_mask_update_nm24: rows=%lld cols=%lld must be positive",
                  (long long)rows, (long long)cols);
@@ -960,9 +1173,14 @@ static int mask_update_impl(const float* score, const float* norm, const float* 
                                           hx, structured_exact, score_bf16);
     P.tau = tau;
     P.pen_mask = pen_mask;
+    P.frozen = fb.flags;
+    P.freeze_low = (float)fb.low;
+    P.freeze_high = (float)fb.high;
+    P.freeze_high_on = fb.high_on;
     const int64_t chunks = rows * cols / 8;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
-    const bool plain = !score_bf16 && !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0;
+    const bool plain = !score_bf16 && !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0 &&
+                       fb.flags == nullptr;
 #define SF_MU_K(TW, EW, EM, PL)                                                                  \
     do {                                                                                         \
         auto kern = mask_update_nm24_kernel<TW, EW, EM, PL>;                                     \

@@ -95,10 +95,42 @@ def score_sum(a, b, out, norm, scratch) -> None:
     check(lib().sf_score_sum(_p(a), _p(b), _p(out), _p(norm), _p(scratch), a.numel(), _stream()), "sf_score_sum")
 
 
+_WANDA_SCRATCH = {}
+
+
+def wanda_add_batch(x2d, scaler_row, keep: float, denom: float) -> None:
+    """scaler_row <- scaler_row * keep + ||x[:, c]||^2 / denom in place (WANDA calibration energy of
+    the input channels, legacy/sparse_modeling.py:884-898); x2d is [tokens, in_features]."""
+    _cuda(x2d, scaler_row)
+    if x2d.dim() != 2 or scaler_row.dim() != 1 or scaler_row.numel() != x2d.shape[1]:
+        raise ValueError("wanda_add_batch: x must be [tokens, in] and scaler_row [in]")
+    if not (x2d.is_contiguous() and scaler_row.is_contiguous()):
+        raise ValueError("wanda_add_batch: contiguous tensors expected")
+    cols = x2d.shape[1]
+    key = (x2d.device, cols)
+    scratch = _WANDA_SCRATCH.get(key)
+    if scratch is None:
+        scratch = torch.empty(int(lib().sf_wanda_scratch_floats(cols)), dtype=torch.float32, device=x2d.device)
+        _WANDA_SCRATCH[key] = scratch
+    check(lib().sf_wanda_add_batch(_p(x2d), _dt(x2d), x2d.shape[0], cols, _p(scaler_row), _dt(scaler_row), float(keep),
+                                   float(denom), _p(scratch), _stream()), "sf_wanda_add_batch")
+
+
+def wanda_score(W, scaler_row, score, norm, scratch, eps: float = 1e-8) -> None:
+    """score <- |W| * sqrt(scaler_row + eps) (fp32) with norm <- (mean, std + 1e-6)
+    (legacy/sparse_modeling.py:1071-1088)."""
+    _cuda(W, scaler_row, score, norm, scratch)
+    if W.dim() != 2 or scaler_row.numel() != W.shape[1] or score.dtype != torch.float32 or score.numel() != W.numel():
+        raise ValueError("wanda_score: W [out, in], scaler_row [in], score float32 of W's size expected")
+    check(lib().sf_wanda_score(_p(W), _dt(W), _p(scaler_row), _dt(scaler_row), W.shape[0], W.shape[1], float(eps),
+                               _p(score), _p(norm), _p(scratch), _stream()), "sf_wanda_score")
+
+
 def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, meta=None, temperature=1.0, mask_lr=0.1,
                      pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
-                     structured_exact=False, score_bf16=False, pen_mask=None) -> None:
-    _cuda(score, norm, mask, stats, W, wm, meta, tau, pen_mask)
+                     structured_exact=False, score_bf16=False, pen_mask=None, frozen=None, freeze_low=0.0,
+                     freeze_high=1.0, freeze_apply_high=False) -> None:
+    _cuda(score, norm, mask, stats, W, wm, meta, tau, pen_mask, frozen)
     if pen_mask is not None and (pen_mask.dtype != torch.float32 or pen_mask.shape != mask.shape):
         raise TypeError("mask_update_nm24: pen_mask must be a float32 tensor of the mask's shape")
     if tau is not None and tau.dtype != torch.float32:
@@ -110,6 +142,19 @@ def mask_update_nm24(score, norm, mask, stats, *, tau=None, W=None, wm=None, met
     if wm is not None and (W is None or wm.dtype != W.dtype):
         raise TypeError("mask_update_nm24: wm needs W of the same dtype")
     rows, cols = mask.shape
+    if frozen is not None:
+        if pen_mask is not None:
+            raise ValueError("mask_update_nm24: freeze bands and a joint penalty mask are not combined")
+        if frozen.dtype != torch.float32 or frozen.shape != mask.shape:
+            raise TypeError("mask_update_nm24: frozen must be a float32 tensor of the mask's shape")
+        check(lib().sf_mask_update_nm24_frozen(_p(score), _p(norm), _p(tau), _p(frozen), float(freeze_low),
+                                               float(freeze_high), int(bool(freeze_apply_high)), _p(mask), _p(W),
+                                               _dt(W) if W is not None else SF_F32, _p(wm), _p(meta), _p(stats), rows,
+                                               cols, float(temperature), float(mask_lr), float(pen), int(penalty_mode),
+                                               float(beta_s), float(binarize_decay), float(hx),
+                                               int(bool(structured_exact)), int(bool(score_bf16)), _stream()),
+              "sf_mask_update_nm24_frozen")
+        return
     if pen_mask is not None:
         check(lib().sf_mask_update_nm24_joint(_p(score), _p(norm), _p(tau), _p(pen_mask), _p(mask), _p(W),
                                               _dt(W) if W is not None else SF_F32, _p(wm), _p(meta), _p(stats), rows,

@@ -241,7 +241,7 @@ def _effective_mask_tensor(mask32, hx, finalized):
 # ----------------------------------------------------------------------------------------
 # SparseLinear
 # ----------------------------------------------------------------------------------------
-_SUPPORTED_METRICS = ("magnitude", "movement", "hessian_obd", "hessian_ratio", "hessian")
+_SUPPORTED_METRICS = ("magnitude", "movement", "hessian_obd", "hessian_ratio", "hessian", "wanda")
 
 
 class SparseLinear(nn.Linear):
@@ -282,13 +282,16 @@ class SparseLinear(nn.Linear):
             self.hessian_diag = frozen((1,))
             self._hessian_diag_placeholder = True
         if cfg.change_mask and (cfg.freeze_low > 0.0 or cfg.freeze_high < 1.0):
-            raise NotImplementedError("freeze_low / freeze_high bands are not part of the 2:4 kernel path")
-        self.frozen_mask_flags = frozen((1,), dtype=self.weight.dtype)
-        self._frozen_mask_flags_placeholder = True
+            # fp32 like the mask: the update kernel reads and raises the flags in the same pass
+            self.frozen_mask_flags = frozen((out_features, in_features), 0.0)
+        else:
+            self.frozen_mask_flags = frozen((1,), dtype=self.weight.dtype)
+            self._frozen_mask_flags_placeholder = True
         if cfg.mask_metric == "wanda":
-            raise NotImplementedError("mask_metric='wanda' (calibration scaler) is not part of the 2:4 kernel path")
-        self.scaler_row = frozen((1,), dtype=self.weight.dtype)
-        self._scaler_row_placeholder = True
+            self.scaler_row = frozen((in_features,), 0.0, dtype=self.weight.dtype)
+        else:
+            self.scaler_row = frozen((1,), dtype=self.weight.dtype)
+            self._scaler_row_placeholder = True
         self.nsamples = 0
 
         self.weight.mask = self.mask
@@ -401,12 +404,29 @@ class SparseLinear(nn.Linear):
     def initialize(self):
         """legacy/sparse_modeling.py:410-439."""
         self.mask.fill_(1.0)
+        if not self._is_placeholder("frozen_mask_flags"):
+            self.frozen_mask_flags.zero_()
         if not self._is_placeholder("grad_ema"):
             self.grad_ema.zero_()
         if not self._is_placeholder("hessian_diag"):
             self.hessian_diag.fill_(1.0 if self.mask_metric == "hessian_obd" else 0.0)
         self.sync_weight()
         self.invalidate_masked_weight()
+
+    @torch.no_grad()
+    def add_batch(self, inp, out=None):
+        """WANDA calibration (legacy/sparse_modeling.py:884-898): folds the squared L2 norm of every
+        input channel over this batch into ``scaler_row`` as a running mean over samples."""
+        if self._is_placeholder("scaler_row"):
+            return
+        if inp.dim() == 2:
+            inp = inp.unsqueeze(0)
+        batch = inp.shape[0]
+        x2d = inp.reshape(-1, inp.shape[-1]).contiguous()
+        keep = self.nsamples / (self.nsamples + batch + 1e-8)
+        self.nsamples += batch
+        ops.wanda_add_batch(x2d, self.scaler_row.data, keep, max(self.nsamples, 1))
+        self._score_key = None  # the kernel wrote scaler_row behind autograd's version counter
 
     @torch.no_grad()
     def sync_weight(self):
@@ -670,6 +690,11 @@ class SparseLinear(nn.Linear):
             ops.hutch_accumulate(self.hessian_diag.data, hvp.contiguous(), v.contiguous(),
                                  beta=float(self.cfg.beta if beta is None else beta))
             return
+        if self.mask_metric in ("wanda", "movement"):
+            # metrics that do not read H: the sample goes into H, the score is formed when it is wanted
+            ops.hutch_accumulate(self.hessian_diag.data, hvp.contiguous(), v.contiguous(),
+                                 beta=float(self.cfg.beta if beta is None else beta))
+            return
         ops.hutch_score(self.weight.data, self.hessian_diag.data, self._score, self._norm, self._scratch,
                         hvp=hvp.contiguous(), v=v.contiguous(), beta=float(self.cfg.beta if beta is None else beta),
                         metric=self.mask_metric if self.mask_metric in _SUPPORTED_METRICS else "hessian_obd")
@@ -738,6 +763,10 @@ class SparseLinear(nn.Linear):
         self._score_key = None
         metric, H = self._resolved_metric()
         aux = None
+        if metric == "wanda":
+            ops.wanda_score(self.weight.data, self.scaler_row.data, self._score, self._norm, self._scratch)
+            self._combine_shard_norm()
+            return
         if metric == "movement":
             if self._is_placeholder("grad_ema"):
                 metric = "magnitude"
@@ -756,6 +785,8 @@ class SparseLinear(nn.Linear):
         H = None if self._is_placeholder("hessian_diag") else self.hessian_diag.data
         if H is None and metric in ("hessian_obd", "hessian_ratio", "hessian"):
             metric = "magnitude"
+        if metric == "wanda" and self._is_placeholder("scaler_row"):
+            metric = "magnitude"
         return metric, H
 
     def _score_state(self):
@@ -769,7 +800,7 @@ class SparseLinear(nn.Linear):
         if not (self.fuse_score_with_optimizer and self._fuse_score_next and self.change_mask):
             return None
         metric, H = self._resolved_metric()
-        if metric == "movement" or self.mode != "sparse_forward":
+        if metric in ("movement", "wanda") or self.mode != "sparse_forward":
             return None
         self._check_2to4()
         self._buffers_ready()
@@ -824,6 +855,9 @@ class SparseLinear(nn.Linear):
                              beta_s=self._beta_structural(step),
                              structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
                              score_bf16=self._score_is_bf16())
+        if not self._is_placeholder("frozen_mask_flags"):
+            # a frozen entry's gate is its own value (legacy/sparse_modeling.py:1227-1229)
+            G = torch.where(self.frozen_mask_flags.data != 0, self.mask.data, G)
         return G
 
     def _check_mask_modes(self):
@@ -914,6 +948,8 @@ class SparseLinear(nn.Linear):
         """update_mask with hard_mask_type='block16': the unstructured gate, the per-tile top-k (or mid)
         penalty, binarise push, EMA, per-tile hard view, masked weight and flip count in one kernel."""
         self._check_tile16()
+        if not self._is_placeholder("frozen_mask_flags"):
+            raise NotImplementedError("freeze bands are built for the 2:4 mask update, not for block16 masks")
         if self._beta_structural(step) > 0.0:
             raise NotImplementedError("beta_structural mixing is an N:M target; it is not combined with block16 masks")
         self._buffers_ready()
@@ -957,6 +993,8 @@ class SparseLinear(nn.Linear):
         bs = self._block_size()
         if self.out_features < bs or self.in_features < bs or self.in_features % 4 != 0:
             raise NotImplementedError("block-sparse masks need at least one whole block and in_features % 4 == 0")
+        if not self._is_placeholder("frozen_mask_flags"):
+            raise NotImplementedError("freeze bands are built for the 2:4 mask update, not for block masks")
         if self._beta_structural(step) > 0.0:
             raise NotImplementedError("beta_structural mixing is an N:M target; it is not combined with block masks")
         self._buffers_ready()
@@ -1000,12 +1038,20 @@ class SparseLinear(nn.Linear):
         GLU pair updated jointly)."""
         cfg = owner.cfg
         hx_new = owner._next_hardening_x(step)
+        bands = {}
+        if not self._is_placeholder("frozen_mask_flags"):
+            if owner is not self or pen_mask is not None:
+                raise NotImplementedError("freeze bands are not combined with the GLU joint mask update")
+            # the low band snaps at every update, the high band from step 2000 on
+            # (legacy/sparse_modeling.py:1621-1642)
+            bands = dict(frozen=self.frozen_mask_flags.data, freeze_low=float(self.cfg.freeze_low),
+                         freeze_high=float(self.cfg.freeze_high), freeze_apply_high=step >= 2000)
         ops.mask_update_nm24(score, norm, self.mask.data, self._stats, tau=tau, W=self.weight.data, wm=self._wm,
                              meta=self._meta, temperature=owner._temperature(step), mask_lr=float(cfg.mask_lr),
                              pen=pen, penalty_mode=pmode, beta_s=owner._beta_structural(step),
                              binarize_decay=float(getattr(cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
                              structured_exact=bool(getattr(cfg, "structured_exact", False)),
-                             score_bf16=score_bf16, pen_mask=pen_mask)
+                             score_bf16=score_bf16, pen_mask=pen_mask, **bands)
         self.hardening_x = hx_new
         self._fuse_score_next = self._predict_mask_update(step + 1)
         self.last_mask_stats = self._stats

@@ -84,6 +84,41 @@ def update_mask_penalty_lr(model, step: int, max_steps: int, penalty_lr_min: flo
     return cur
 
 
+@torch.no_grad()
+def harden_fraction(model, fraction: float = 0.2, band_low: float = 0.4, band_high: float = 0.6) -> int:
+    """legacy/utils.py:1236-1276: rounds the `fraction` of not-yet-frozen mask entries inside
+    (band_low, band_high) that lie closest to 0.5, over all layers together, to 0 / 1 and freezes them.
+    A rarely used maintenance step (the threshold is one order statistic over all layers), done
+    with tensor operations on the device; layers without freeze bands have no flags and are skipped
+    (the reference fails on them)."""
+    raw = get_raw_model(model)
+    cands = []
+    for m in _sparse_modules(raw):
+        if m._is_placeholder("frozen_mask_flags"):
+            continue
+        sel = (m.frozen_mask_flags.data == 0) & (m.mask.data > band_low) & (m.mask.data < band_high)
+        if bool(sel.any()):
+            cands.append((m, sel, (m.mask.data[sel] - 0.5).abs()))
+    if not cands:
+        return 0
+    all_diff = torch.cat([c[2] for c in cands])
+    k = int(all_diff.numel() * fraction)
+    if k <= 0:
+        return 0
+    thr = torch.topk(all_diff, k, largest=False).values.max()
+    hardened = 0
+    for m, sel, diff in cands:
+        pick = torch.zeros_like(sel)
+        pick[sel] = diff <= thr
+        n = int(pick.sum().item())
+        if n:
+            m.mask.data[pick] = (m.mask.data[pick] > 0.5).to(m.mask.dtype)
+            m.frozen_mask_flags.data[pick] = 1.0
+            m.invalidate_masked_weight()
+            hardened += n
+    return hardened
+
+
 def all_ranks_ok(ok: bool, device=None) -> bool:
     """True only if every rank passes True (the ok-flag the reference all-reduces with MIN after
     steps that may fail on one rank only, legacy/main_llama.py:637-651, 771-788). A rank that caught

@@ -34,8 +34,8 @@ _TopK = collections.namedtuple("topk", ["values", "indices"])
 
 
 def stable_topk(x, k, dim=-1, largest=True, sorted=True):  # noqa: A002
-    assert largest
-    s = torch.sort(x, dim=dim, descending=True, stable=True)
+    # the k smallest are only used through their values (harden_fraction's threshold), where ties do not matter
+    s = torch.sort(x, dim=dim, descending=bool(largest), stable=True)
     sl = [slice(None)] * x.dim()
     sl[dim] = slice(0, k)
     return _TopK(s.values[tuple(sl)], s.indices[tuple(sl)])
@@ -518,6 +518,76 @@ BLOCK_BASE = dict(mask_type="unstructured", mask_metric="hessian_obd", sparsity_
                   mask_hardening_start=2, mask_hardening_duration=2, mask_penalty_lr=0.2, tau_sample_size=1 << 30)
 
 
+def case_wanda():
+    """WANDA metric: add_batch folds the activation energy of three batches (3-D, 3-D, 2-D input)
+    into scaler_row (legacy/sparse_modeling.py:884-898); the score |W| * sqrt(scaler_row + eps)
+    (:1071-1077) then drives two mask updates."""
+    d = {}
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        torch.manual_seed(21)
+        out_f, in_f = 24, 64
+        W = torch.randn(out_f, in_f) * 0.02
+        layer = make_layer(out_f, in_f, W, dtype, mask_type="structured", mask_metric="wanda", mask_update_period=1,
+                           sparsity_warmup_steps=0, mask_lr=0.2, mask_penalty_mode="structured_topn",
+                           mask_hardening_start=2, mask_hardening_duration=8)
+        put(d, f"{tag}_W", layer.weight.data)
+        batches = [torch.randn(3, 10, in_f), torch.randn(2, 7, in_f) * 2.0, torch.randn(5, in_f) * 0.5]
+        for i, x in enumerate(batches):
+            x = x.to(dtype)
+            put(d, f"{tag}_x{i}", x)
+            layer.add_batch(x, None)
+            put(d, f"{tag}_scaler{i}", layer.scaler_row.data)
+            put(d, f"{tag}_nsamples{i}", int(layer.nsamples))
+        layer.mask.data = torch.rand(out_f, in_f)
+        put(d, f"{tag}_mask0", layer.mask.data)
+        for j, step in enumerate((3, 4)):
+            put(d, f"{tag}_G{j}", layer.compute_gate_target(step))
+            put(d, f"{tag}_T{j}", layer._temperature(step))
+            layer.update_mask(step, lambda_mid=0.3)
+            put(d, f"{tag}_mask{j + 1}", layer.mask.data)
+            put(d, f"{tag}_flips{j}", int(layer.weight.flipped_mask))
+            put(d, f"{tag}_hx{j}", float(layer.hardening_x))
+    save("wanda", d)
+
+
+def case_freeze():
+    """Freeze bands (freeze_low / freeze_high): frozen entries keep their own value as gate target
+    (legacy/sparse_modeling.py:1227-1229), the snap and the flags at the end of update_mask
+    (:1621-1642) before and after step 2000, and harden_fraction over two layers (legacy/utils.py:1236-1276)."""
+    d = {}
+    torch.manual_seed(33)
+    out_f, in_f = 32, 64
+    W = torch.randn(out_f, in_f) * 0.02
+    layer = make_layer(out_f, in_f, W, torch.float32, mask_type="structured", mask_metric="hessian_obd",
+                       mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.3, mask_penalty_mode="structured_topn",
+                       mask_hardening_start=2, mask_hardening_duration=8, temp_init=0.3, temp_min=0.3,
+                       freeze_low=0.08, freeze_high=0.93)
+    layer.hessian_diag.data = torch.rand(out_f, in_f) + 0.1
+    layer.mask.data = torch.rand(out_f, in_f)
+    put(d, "W", W); put(d, "H", layer.hessian_diag.data); put(d, "mask0", layer.mask.data)
+    steps = [5, 6, 7, 2000, 2001, 2002]
+    d["steps"] = np.asarray(steps)
+    for j, step in enumerate(steps):
+        put(d, f"s{j}_G", layer.compute_gate_target(step))
+        put(d, f"s{j}_T", layer._temperature(step))
+        layer.update_mask(step, lambda_mid=0.4)
+        put(d, f"s{j}_mask", layer.mask.data); put(d, f"s{j}_flags", layer.frozen_mask_flags.data.float())
+        put(d, f"s{j}_flips", int(layer.weight.flipped_mask)); put(d, f"s{j}_hx", float(layer.hardening_x))
+    # harden_fraction over two layers
+    other = make_layer(16, 32, torch.randn(16, 32) * 0.02, torch.float32, mask_type="structured",
+                       mask_metric="hessian_obd", freeze_low=0.08, freeze_high=0.93)
+    other.mask.data = torch.rand(16, 32)
+    other.frozen_mask_flags.data = (torch.rand(16, 32) < 0.1).float()
+    model = torch.nn.Sequential(layer, other)
+    put(d, "hf_mask_a0", layer.mask.data); put(d, "hf_flags_a0", layer.frozen_mask_flags.data.float())
+    put(d, "hf_mask_b0", other.mask.data); put(d, "hf_flags_b0", other.frozen_mask_flags.data.float())
+    n = ref_utils.harden_fraction(model, fraction=0.3, band_low=0.35, band_high=0.7)
+    put(d, "hf_count", int(n))
+    put(d, "hf_mask_a1", layer.mask.data); put(d, "hf_flags_a1", layer.frozen_mask_flags.data.float())
+    put(d, "hf_mask_b1", other.mask.data); put(d, "hf_flags_b1", other.frozen_mask_flags.data.float())
+    save("freeze", d)
+
+
 def case_block_masks():
     """Block-sparse soft masks (hard_mask_type block_sparse16 / 32): block gate, block penalty, EMA,
     blockified mask, block hard view, masked forward (legacy/sparse_modeling.py:461-508, 607-718,
@@ -548,6 +618,12 @@ def case_block_masks():
 
 
 if __name__ == "__main__":
+    # `make_golden.py wanda ...` regenerates only the named single-function cases
+    only = [a for a in sys.argv[1:] if not a.startswith("-")]
+    if only:
+        for name in only:
+            globals()["case_" + name]()
+        raise SystemExit(0)
     base = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
                 sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99)
     # scaled-down copy of the fp32 GPT-2-MLP case (temperature 1, no hardening before the update)
@@ -571,6 +647,8 @@ if __name__ == "__main__":
     case_kl_loss()
     case_slorb()
     case_block_masks()
+    case_wanda()
+    case_freeze()
     case_penalty()
     case_ties()
     case_adamw()

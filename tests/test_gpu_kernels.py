@@ -407,3 +407,115 @@ def test_ragged_sizes_against_oracle(ops, shape):
                                eps=1e-8, weight_decay=0.1, mask=mask0, decay=1e-3)
     assert rel_err(p, wp) <= F32_TOL and rel_err(m, wm_) <= F32_TOL and rel_err(vv, wv) <= F32_TOL
     assert rel_err(wm2, O.masked_weight(wp, O.effective_mask(mask0, 0.25))) <= F32_TOL
+
+
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_wanda_metric_follows_the_reference(ops, tag, tol):
+    """SparseLinear with mask_metric='wanda' against the trajectory recorded from the reference
+    (tests/golden/wanda.npz): add_batch over three batches, two mask updates."""
+    import sparseforge_b200 as sf
+
+    g = Golden("wanda")
+    W = g[f"{tag}_W"]
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="wanda", mask_update_period=1, sparsity_warmup_steps=0,
+                                mask_lr=0.2, mask_penalty_mode="structured_topn", mask_hardening_start=2,
+                                mask_hardening_duration=8)
+    layer = sf.SparseLinear(W.shape[1], W.shape[0], sparselinear_config=cfg, bias=False).to(DEV).to(W.dtype)
+    layer.initialize()
+    layer.mask.data = layer.mask.data.float()
+    layer.weight.data.copy_(W.to(DEV))
+    assert tuple(layer.scaler_row.shape) == (W.shape[1],) and not layer._is_placeholder("scaler_row")
+    for i in range(3):
+        layer.add_batch(g[f"{tag}_x{i}"].to(DEV), None)
+        assert layer.nsamples == g.scalar(f"{tag}_nsamples{i}")
+        assert rel_err(layer.scaler_row.data.float(), g[f"{tag}_scaler{i}"].float()) <= (1e-2 if tag == "bf16" else 1e-5)
+    # the fixture's scaler from here on, so that a last-bit difference in a bf16 sum does not move the scores
+    layer.scaler_row.data.copy_(g[f"{tag}_scaler2"].to(DEV))
+    layer.mask.data.copy_(g[f"{tag}_mask0"].to(DEV))
+    layer.invalidate_masked_weight()
+    for j, step in enumerate((3, 4)):
+        assert rel_err(layer.compute_gate_target(step).float(), g[f"{tag}_G{j}"].float()) <= tol
+        prev = layer.mask.data.clone().cpu()
+        layer.update_mask(step, lambda_mid=0.3)
+        assert rel_err(layer.mask.data, g[f"{tag}_mask{j + 1}"]) <= tol, (tag, j)
+        assert layer.hardening_x == pytest.approx(g.scalar(f"{tag}_hx{j}"))
+        assert int(layer.weight.flipped_mask) == O.flip_count(prev, layer.mask.data.cpu())
+        if torch.equal(O.hard_mask_from_soft(layer.mask.data.cpu()), O.hard_mask_from_soft(g[f"{tag}_mask{j + 1}"])):
+            assert int(layer.weight.flipped_mask) == g.scalar(f"{tag}_flips{j}")
+        layer.mask.data.copy_(g[f"{tag}_mask{j + 1}"].to(DEV))
+        layer.invalidate_masked_weight()
+
+
+def test_wanda_kernels_at_layer_size(ops):
+    """Column energy and score at a LLaMA-sized matrix against torch on the device (fp32 sums in
+    another order: 1e-5), bf16 activations and weights."""
+    torch.manual_seed(31)
+    T, out_f, in_f = 4096, 1024, 11008
+    x = torch.randn(T, in_f, device=DEV).to(torch.bfloat16)
+    scaler = torch.rand(in_f, device=DEV)
+    want = scaler * 0.25 + (x.float() ** 2).sum(0) / 7.0
+    ops.wanda_add_batch(x, scaler, 0.25, 7.0)
+    assert rel_err(scaler, want) <= 1e-5
+    W = (torch.randn(out_f, in_f, device=DEV) * 0.02).to(torch.bfloat16)
+    score = torch.empty(out_f, in_f, device=DEV)
+    norm = torch.empty(2, device=DEV)
+    scratch = ops.hutch_score_scratch(DEV)
+    ops.wanda_score(W, scaler, score, norm, scratch)
+    ref = W.abs().float() * torch.sqrt(scaler.reshape(1, -1) + 1e-8)
+    assert rel_err(score, ref) <= 1e-6
+    assert float(norm[0]) == pytest.approx(float(ref.mean()), rel=1e-5)
+    assert float(norm[1]) == pytest.approx(float(ref.std(unbiased=False)) + 1e-6, rel=1e-4)
+
+
+def test_freeze_bands_follow_the_reference(ops):
+    """SparseLinear with freeze_low / freeze_high against the trajectory recorded from the reference
+    (tests/golden/freeze.npz): six updates across step 2000, then harden_fraction over two layers.
+    Entries whose pre-snap value lies within 1e-5 of a band edge may snap differently (the kernel's
+    sigmoid is not ATen's to the last bit) and are left out of the comparison."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("freeze")
+    W = g["W"]
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", mask_update_period=1,
+                                sparsity_warmup_steps=0, mask_lr=0.3, mask_penalty_mode="structured_topn",
+                                mask_hardening_start=2, mask_hardening_duration=8, temp_init=0.3, temp_min=0.3,
+                                freeze_low=0.08, freeze_high=0.93)
+    layer = sf.SparseLinear(W.shape[1], W.shape[0], sparselinear_config=cfg, bias=False).to(DEV)
+    layer.initialize()
+    assert tuple(layer.frozen_mask_flags.shape) == tuple(W.shape) and not layer._is_placeholder("frozen_mask_flags")
+    layer.weight.data.copy_(W.to(DEV))
+    layer.hessian_diag.data.copy_(g["H"].to(DEV))
+    layer.mask.data.copy_(g["mask0"].to(DEV))
+    layer.invalidate_masked_weight()
+    prev = g["mask0"]
+    for j, step in enumerate(int(s) for s in g["steps"]):
+        assert layer._temperature(step) == pytest.approx(g.scalar(f"s{j}_T"), rel=1e-12)
+        assert rel_err(layer.compute_gate_target(step), g[f"s{j}_G"]) <= F32_TOL
+        layer.update_mask(step, lambda_mid=0.4)
+        pre = O.mask_update(prev, g[f"s{j}_G"], mask_lr=0.3, lambda_mid=0.4, pen_lr=0.3, penalty_mode="structured_topn")
+        sure = ((pre - 0.08).abs() > 1e-5) & ((pre - 0.93).abs() > 1e-5)
+        assert int((~sure).sum()) <= 4
+        got, flags = layer.mask.data.cpu(), layer.frozen_mask_flags.data.cpu()
+        assert rel_err(got[sure], g[f"s{j}_mask"][sure]) <= F32_TOL, j
+        assert torch.equal(flags[sure], g[f"s{j}_flags"][sure]), j
+        assert layer.hardening_x == pytest.approx(g.scalar(f"s{j}_hx"))
+        assert int(layer.weight.flipped_mask) == O.flip_count(prev, got)
+        # masked weight and metadata were formed from the snapped mask
+        hx = layer.hardening_x
+        want_wm = O.masked_weight(W, O.effective_mask(got, hx))
+        assert rel_err(layer._wm.cpu(), want_wm) <= F32_TOL
+        assert torch.equal(unpack_meta(layer._meta, W.shape[1]), O.hard_mask_from_soft(got))
+        prev = g[f"s{j}_mask"]
+        layer.mask.data.copy_(prev.to(DEV))
+        layer.frozen_mask_flags.data.copy_(g[f"s{j}_flags"].to(DEV))
+        layer.invalidate_masked_weight()
+    other = sf.SparseLinear(32, 16, sparselinear_config=sf.SparseLinearConfig(
+        mask_type="structured", mask_metric="hessian_obd", freeze_low=0.08, freeze_high=0.93), bias=False).to(DEV)
+    layer.mask.data.copy_(g["hf_mask_a0"].to(DEV)); layer.frozen_mask_flags.data.copy_(g["hf_flags_a0"].to(DEV))
+    other.mask.data.copy_(g["hf_mask_b0"].to(DEV)); other.frozen_mask_flags.data.copy_(g["hf_flags_b0"].to(DEV))
+    n = U.harden_fraction(torch.nn.Sequential(layer, other), fraction=0.3, band_low=0.35, band_high=0.7)
+    assert n == g.scalar("hf_count")
+    assert torch.equal(layer.mask.data.cpu(), g["hf_mask_a1"]) and torch.equal(other.mask.data.cpu(), g["hf_mask_b1"])
+    assert torch.equal(layer.frozen_mask_flags.data.cpu(), g["hf_flags_a1"])
+    assert torch.equal(other.frozen_mask_flags.data.cpu(), g["hf_flags_b1"])

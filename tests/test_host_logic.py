@@ -104,10 +104,10 @@ def test_host_schedules_match_reference_formulas():
 def test_unsupported_configurations_raise():
     import sparseforge_b200 as sf
 
-    with pytest.raises(NotImplementedError):
-        sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(mask_metric="wanda"))
-    with pytest.raises(NotImplementedError):
-        sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(freeze_low=0.1))
+    wanda = sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(mask_metric="wanda"))
+    assert tuple(wanda.scaler_row.shape) == (16,) and not wanda._is_placeholder("scaler_row") and wanda.nsamples == 0
+    bands = sf.SparseLinear(16, 8, sparselinear_config=sf.SparseLinearConfig(freeze_low=0.1))
+    assert tuple(bands.frozen_mask_flags.shape) == (8, 16) and not bands._is_placeholder("frozen_mask_flags")
     slorb = sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(SLoRB=True, SLoRB_k=16))
     assert tuple(slorb.x_proj.shape) == (4, 64) and tuple(slorb.SLoRB_Weight.shape) == (8, 4)
     assert list(slorb.state_dict().keys())[-2:] == ["x_proj", "SLoRB_Weight"]

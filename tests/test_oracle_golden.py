@@ -251,6 +251,52 @@ def test_slorb_bypass():
         assert rel_err(s_w.grad, g[f"{tag}_dS"]) <= F32_TOL
 
 
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_wanda_metric(tag, tol):
+    """add_batch over three batches, then the score |W| sqrt(scaler_row + eps) through two mask updates."""
+    g = Golden("wanda")
+    W = g[f"{tag}_W"]
+    scaler, n = torch.zeros(W.shape[1], dtype=W.dtype), 0
+    for i in range(3):
+        scaler, n = O.wanda_add_batch(scaler, n, g[f"{tag}_x{i}"])
+        assert n == g.scalar(f"{tag}_nsamples{i}")
+        assert rel_err(scaler.float(), g[f"{tag}_scaler{i}"].float()) <= (0.0 if tag == "bf16" else 1e-6)
+    mask = g[f"{tag}_mask0"]
+    for j in range(2):
+        s = O.normalize_scores(O.importance_score(W, "wanda", scaler_row=scaler))
+        G = O.gate_target_structured(s, g.scalar(f"{tag}_T{j}"))
+        assert rel_err(G.float(), g[f"{tag}_G{j}"].float()) <= tol
+        new_mask = O.mask_update(mask, g[f"{tag}_G{j}"], mask_lr=0.2, lambda_mid=0.3, pen_lr=0.2,
+                                 penalty_mode="structured_topn")
+        assert rel_err(new_mask, g[f"{tag}_mask{j + 1}"]) <= F32_TOL
+        assert O.flip_count(mask, g[f"{tag}_mask{j + 1}"]) == g.scalar(f"{tag}_flips{j}")
+        mask = g[f"{tag}_mask{j + 1}"].clone()
+
+
+def test_freeze_bands_and_harden_fraction():
+    """Frozen entries keep their own value as gate target; the low band snaps at every update, the
+    high band from step 2000 on; harden_fraction rounds the entries nearest 0.5 over two layers."""
+    g = Golden("freeze")
+    W, H = g["W"], g["H"]
+    mask, flags = g["mask0"], torch.zeros(W.shape)
+    raw = O.importance_score(W, "hessian_obd", H=H)
+    for j, step in enumerate(int(s) for s in g["steps"]):
+        G = O.freeze_gate(O.gate_target_structured(O.normalize_scores(raw), g.scalar(f"s{j}_T")), mask, flags)
+        assert rel_err(G, g[f"s{j}_G"]) <= F32_TOL
+        new = O.mask_update(mask, g[f"s{j}_G"], mask_lr=0.3, lambda_mid=0.4, pen_lr=0.3, penalty_mode="structured_topn")
+        new, flags = O.freeze_bands(new, flags, 0.08, 0.93, step)
+        assert rel_err(new, g[f"s{j}_mask"]) <= F32_TOL
+        assert torch.equal(flags, g[f"s{j}_flags"])
+        assert O.flip_count(mask, g[f"s{j}_mask"]) == g.scalar(f"s{j}_flips")
+        mask = g[f"s{j}_mask"].clone()
+    assert int(flags.sum()) > 200 and int((mask == 1).sum()) > 100  # the fixture does freeze on both sides
+    masks, fl, n = O.harden_fraction([g["hf_mask_a0"], g["hf_mask_b0"]], [g["hf_flags_a0"], g["hf_flags_b0"]],
+                                     fraction=0.3, band_low=0.35, band_high=0.7)
+    assert n == g.scalar("hf_count")
+    assert torch.equal(masks[0], g["hf_mask_a1"]) and torch.equal(masks[1], g["hf_mask_b1"])
+    assert torch.equal(fl[0], g["hf_flags_a1"]) and torch.equal(fl[1], g["hf_flags_b1"])
+
+
 @pytest.mark.parametrize("tag", ["bs16", "bs32", "tail"])
 def test_block_sparse_soft_masks(tag):
     import json
