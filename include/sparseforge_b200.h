@@ -282,6 +282,15 @@ SF_API int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, v
                     int64_t cols, void* stream);
 
 /*
+ * The AMSGrad variant (amsgrad=True, legacy/adamw.py:126-128, 142-156): v_max <- max(v_max, v) after
+ * v is updated, and the denominator is sqrt(v_max)/sqrt(bc2) + eps. v_max has dtype w_dtype.
+ */
+SF_API int sf_adamw_masked_amsgrad(void* p, const void* g, const float* mask, void* m, void* v, void* v_max,
+                            int w_dtype, int64_t n, double lr, double beta1, double beta2, double eps,
+                            double weight_decay, double decay, double bc1, double bc2, double adaptive_l1,
+                            void* stream);
+
+/*
  * The same AdamW step, followed in the same pass by the importance score of the UPDATED weight.
  *   replaces: AdamW.step legacy/adamw.py:65-176 followed by SparseLinear.update_mask's score
  *             refresh, legacy/sparse_modeling.py:1041-1088 (the training loop steps the optimizer,

@@ -527,9 +527,10 @@ def clip_grad_norm(grads, max_norm):
     return [g * coef for g in grads], float(total)
 
 
-def adamw_step(p, g, m, v, *, step, lr, betas, eps, weight_decay, mask=None, decay=0.0, adaptive_l1=0.0):
+def adamw_step(p, g, m, v, *, step, lr, betas, eps, weight_decay, mask=None, decay=0.0, adaptive_l1=0.0, v_max=None):
     """legacy/adamw.py:79-174 for one tensor. `step` is the 1-based step number after the
-    increment at :146. Returns (p, m, v) as new tensors."""
+    increment at :146. Returns (p, m, v) as new tensors; with `v_max` (amsgrad=True, :142-156)
+    the denominator uses the running maximum of v and (p, m, v, v_max) is returned."""
     p, m, v = p.clone(), m.clone(), v.clone()
     beta1, beta2 = betas
     p.mul_(1 - lr * weight_decay)
@@ -540,11 +541,15 @@ def adamw_step(p, g, m, v, *, step, lr, betas, eps, weight_decay, mask=None, dec
     bc2 = 1 - beta2 ** step
     m.mul_(beta1).add_(grad, alpha=1 - beta1)
     v.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
-    denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
+    if v_max is not None:
+        v_max = torch.max(v_max, v)
+        denom = (v_max.sqrt() / math.sqrt(bc2)).add_(eps)
+    else:
+        denom = (v.sqrt() / math.sqrt(bc2)).add_(eps)
     p.addcdiv_(m, denom, value=-(lr / bc1))
     if adaptive_l1 > 0.0 and p.dim() >= 2 and mask is not None:
         p.add_(adaptive_l1 * torch.sign(p) / denom, alpha=-lr)
-    return p, m, v
+    return (p, m, v) if v_max is None else (p, m, v, v_max)
 
 
 # --------------------------------------------------------------------------------------

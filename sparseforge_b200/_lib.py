@@ -38,6 +38,8 @@ _SIGNATURES = {
     "sf_effective_weight": (c_int, [_P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_int, c_double, _P]),
     "sf_adamw_masked": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_double, c_double, c_double, c_double, c_double,
                                 c_double, c_double, c_double, c_double, _P, c_double, c_int64, _P]),
+    "sf_adamw_masked_amsgrad": (c_int, [_P, _P, _P, _P, _P, _P, c_int, c_int64, c_double, c_double, c_double, c_double,
+                                        c_double, c_double, c_double, c_double, c_double, _P]),
     "sf_adamw_masked_score": (c_int, [_P, _P, _P, _P, _P, c_int, c_int64, c_double, c_double, c_double, c_double,
                                       c_double, c_double, c_double, c_double, c_double, _P, _P, c_int, c_double,
                                       _P, _P, _P, _P, c_int, _P]),

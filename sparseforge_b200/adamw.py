@@ -25,8 +25,6 @@ class AdamW(Optimizer):
             raise ValueError("Invalid beta parameter at index 0: {}".format(betas[0]))
         if not 0.0 <= betas[1] < 1.0:
             raise ValueError("Invalid beta parameter at index 1: {}".format(betas[1]))
-        if amsgrad:
-            raise NotImplementedError("amsgrad is not part of the fused kernel")
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay, amsgrad=amsgrad)
         self.decay = srste_decay if srste_decay is not None else 0.0
         self.adaptive_l1_decay = float(adaptive_l1_decay) if adaptive_l1_decay is not None else 0.0
@@ -74,6 +72,8 @@ class AdamW(Optimizer):
                     state["step"] = 0
                     state["exp_avg"] = torch.zeros_like(p.data)
                     state["exp_avg_sq"] = torch.zeros_like(p.data)
+                    if group["amsgrad"]:
+                        state["max_exp_avg_sq"] = torch.zeros_like(p.data)
                 state["step"] += 1
                 if p.data.numel() % 8 != 0 or p.dtype not in (torch.float32, torch.bfloat16):
                     self._small_tensor_step(p, grad, mask, state, group)
@@ -81,7 +81,9 @@ class AdamW(Optimizer):
                 owner = getattr(p, "_sf_owner", None)
                 layer = owner() if owner is not None else None
                 wm, hx = (None, 1.0)
-                fused = layer._optimizer_score_target() if (layer is not None and mask is not None) else None
+                ams = state.get("max_exp_avg_sq") if group["amsgrad"] else None
+                fused = layer._optimizer_score_target() if (layer is not None and mask is not None and ams is None) \
+                    else None
                 if fused is not None:
                     # the mask update of this step follows: write the score of the new weight here
                     # and leave the masked weight to that update
@@ -96,13 +98,14 @@ class AdamW(Optimizer):
                 if layer is not None:
                     layer._score_key = None
                 if layer is not None and mask is not None and layer.mode == "sparse_forward" \
-                        and layer.mask_type == "structured":
+                        and layer.mask_type == "structured" and ams is None:
                     wm, hx = layer._adamw_emit_target()
                 ops.adamw_masked(p.data, grad.contiguous(), state["exp_avg"], state["exp_avg_sq"],
                                  mask=None if mask is None else mask.data.contiguous(), lr=group["lr"], beta1=beta1,
                                  beta2=beta2, eps=group["eps"], weight_decay=group["weight_decay"],
                                  decay=float(self.decay), step=state["step"],
-                                 adaptive_l1=self.adaptive_l1_decay if p.data.dim() >= 2 else 0.0, wm=wm, hx=hx)
+                                 adaptive_l1=self.adaptive_l1_decay if p.data.dim() >= 2 else 0.0, wm=wm, hx=hx,
+                                 v_max=ams)
                 if wm is not None:
                     layer._adamw_emitted()
         return loss
@@ -119,6 +122,9 @@ class AdamW(Optimizer):
         bc2 = 1 - beta2 ** state["step"]
         m.mul_(beta1).add_(grad, alpha=1 - beta1)
         v.mul_(beta2).addcmul_(grad, grad, value=1 - beta2)
+        if group["amsgrad"]:
+            torch.max(state["max_exp_avg_sq"], v, out=state["max_exp_avg_sq"])
+            v = state["max_exp_avg_sq"]
         denom = (v.sqrt() / (bc2 ** 0.5)).add_(group["eps"])
         p.data.addcdiv_(m, denom, value=-(group["lr"] / bc1))
         if self.adaptive_l1_decay > 0.0 and p.data.dim() >= 2 and mask is not None:

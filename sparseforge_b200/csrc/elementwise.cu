@@ -718,6 +718,7 @@ struct AdamParams {
     float beta1, one_minus_beta1, beta2, one_minus_beta2;
     float inv_sqrt_bc2, eps, step_size, lr, l1;
     int has_mask;
+    void* vmax;  // AMSGrad: running maximum of the second moment (weight dtype), else unused
 };
 
 template <typename TW>
@@ -730,7 +731,9 @@ struct HutchArgs {
 
 // SCORE: also writes the importance score of the updated (stored) weight and this block's partial
 // sums of score and score^2, so the mask update that follows needs no separate score pass.
-template <typename TW, bool EMIT_WM, bool SCORE>
+// AMS: the AMSGrad variant (legacy/adamw.py:142-156): the denominator uses the running maximum of the
+// stored second moment.
+template <typename TW, bool EMIT_WM, bool SCORE, bool AMS = false>
 __global__ void __launch_bounds__(kThreads)
 adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* __restrict__ mask,
                     TW* __restrict__ m, TW* __restrict__ v, TW* __restrict__ wm, int64_t chunks,
@@ -746,6 +749,8 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         Vec8<TW>::load(m + e, em);
         Vec8<TW>::load(v + e, ev);
         if (A.has_mask) Vec8<float>::load(mask + e, mk);
+        float vx[8];
+        if (AMS) Vec8<TW>::load(static_cast<const TW*>(A.vmax) + e, vx);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             // p.mul_(1 - lr*wd) rounds to the storage type; the moments and the update are carried in
@@ -757,7 +762,12 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
                 g1 = __fmaf_rn(A.decay, __fmul_rn(p1, __fsub_rn(1.0f, mk[i])), g1);
             float m1 = __fmaf_rn(A.one_minus_beta1, g1, __fmul_rn(em[i], A.beta1));
             float v1 = __fmaf_rn(A.one_minus_beta2, __fmul_rn(g1, g1), __fmul_rn(ev[i], A.beta2));
-            float denom = __fmaf_rn(fast_sqrt(v1), A.inv_sqrt_bc2, A.eps);
+            float vden = v1;
+            if (AMS) {
+                vx[i] = fmaxf(vx[i], Vec8<TW>::round(v1));
+                vden = vx[i];
+            }
+            float denom = __fmaf_rn(fast_sqrt(vden), A.inv_sqrt_bc2, A.eps);
             const float inv_denom = fast_rcp(denom);
             float p2 = __fsub_rn(p1, __fmul_rn(A.step_size, __fmul_rn(m1, inv_denom)));
             if (A.l1 > 0.0f && A.has_mask) {
@@ -769,6 +779,7 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         Vec8<TW>::store(p + e, pw);
         Vec8<TW>::store(m + e, em);
         Vec8<TW>::store(v + e, ev);
+        if (AMS) Vec8<TW>::store(static_cast<TW*>(A.vmax) + e, vx);
         if (SCORE) {
             float h[8], sc[8];
             if (metric != SF_METRIC_MAGNITUDE || hu.hvp != nullptr) Vec8<float>::load(H + e, h);
@@ -1262,7 +1273,7 @@ static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* 
                       double lr, double beta1, double beta2, double eps, double weight_decay, double decay,
                       double bc1, double bc2, double adaptive_l1, void* wm, double hx, int64_t cols,
                       float* H, float* score, float* norm, double* scratch, int metric, const void* hvp,
-                      const void* probe, int v_dtype, double beta_h, void* stream) {
+                      const void* probe, int v_dtype, double beta_h, void* stream, void* vmax = nullptr) {
     SF_CHECK_ARG(p && g && m && v, "sf_adamw_masked: p, g, m, v must be non-null");
     SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_adamw_masked: n=%lld must be a positive multiple of 8", (long long)n);
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_adamw_masked: w_dtype must be SF_F32 or SF_BF16");
@@ -1286,12 +1297,13 @@ static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* 
     A.lr = (float)lr;
     A.l1 = (float)adaptive_l1;
     A.has_mask = mask != nullptr;
+    A.vmax = vmax;
     MaskUpdateParams P = make_mask_params(1.0, 0.0, 0.0, 0, 0.0, 0.0, hx, 0, 0);
     const int64_t chunks = n / 8;
     int grid = 0;
-#define SF_AD(TW, EW, SC)                                                                        \
+#define SF_AD(TW, EW, SC, ...)                                                                   \
     do {                                                                                         \
-        auto kern = adamw_masked_kernel<TW, EW, SC>;                                             \
+        auto kern = adamw_masked_kernel<TW, EW, SC, ##__VA_ARGS__>;                              \
         grid = grid_one_wave((const void*)kern, chunks);                                         \
         if (grid > kMaxPartialBlocks) grid = kMaxPartialBlocks;                                  \
         HutchArgs<TW> hu;                                                                        \
@@ -1303,7 +1315,9 @@ static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* 
         kern<<<grid, kThreads, 0, st>>>((TW*)p, (const TW*)g, mask, (TW*)m, (TW*)v, (TW*)wm, chunks, A, P, H, score, \
                                         scratch, metric, hu);                                    \
     } while (0)
-    if (norm != nullptr) {
+    if (vmax != nullptr) {
+        if (w_dtype == SF_F32) SF_AD(float, false, false, true); else SF_AD(__nv_bfloat16, false, false, true);
+    } else if (norm != nullptr) {
         if (w_dtype == SF_F32) SF_AD(float, false, true); else SF_AD(__nv_bfloat16, false, true);
     } else if (w_dtype == SF_F32) { if (wm) SF_AD(float, true, false); else SF_AD(float, false, false); }
     else { if (wm) SF_AD(__nv_bfloat16, true, false); else SF_AD(__nv_bfloat16, false, false); }
@@ -1322,6 +1336,15 @@ int sf_adamw_masked(void* p, const void* g, const float* mask, void* m, void* v,
                     void* stream) {
     return adamw_impl(p, g, mask, m, v, w_dtype, n, lr, beta1, beta2, eps, weight_decay, decay, bc1, bc2, adaptive_l1,
                       wm, hx, cols, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.0, stream);
+}
+
+int sf_adamw_masked_amsgrad(void* p, const void* g, const float* mask, void* m, void* v, void* v_max, int w_dtype,
+                            int64_t n, double lr, double beta1, double beta2, double eps, double weight_decay,
+                            double decay, double bc1, double bc2, double adaptive_l1, void* stream) {
+    SF_CHECK_ARG(v_max != nullptr, "sf_adamw_masked_amsgrad: v_max must be non-null");
+    if (!aligned16(v_max)) return fail(SF_ERR_ALIGNMENT, "sf_adamw_masked_amsgrad: v_max must be 16-byte aligned");
+    return adamw_impl(p, g, mask, m, v, w_dtype, n, lr, beta1, beta2, eps, weight_decay, decay, bc1, bc2, adaptive_l1,
+                      nullptr, 1.0, 0, nullptr, nullptr, nullptr, nullptr, 0, nullptr, nullptr, 0, 0.0, stream, v_max);
 }
 
 int sf_adamw_masked_score(void* p, const void* g, const float* mask, void* m, void* v, int w_dtype, int64_t n,

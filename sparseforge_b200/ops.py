@@ -199,14 +199,22 @@ def effective_weight(W, mask, wm, *, meta=None, hx=1.0, finalized=False, scale=1
 
 
 def adamw_masked(p, g, m, v, *, mask=None, lr, beta1, beta2, eps, weight_decay, decay, step, adaptive_l1=0.0,
-                 wm=None, hx=1.0) -> None:
-    _cuda(p, g, m, v, mask, wm)
+                 wm=None, hx=1.0, v_max=None) -> None:
+    _cuda(p, g, m, v, mask, wm, v_max)
     if not (p.dtype == g.dtype == m.dtype == v.dtype):
         raise TypeError("adamw_masked: p, g, m, v must share a dtype")
     if mask is not None and mask.dtype != torch.float32:
         raise TypeError("adamw_masked: mask must be float32")
     bc1 = 1.0 - beta1 ** step
     bc2 = 1.0 - beta2 ** step
+    if v_max is not None:  # AMSGrad: no masked-weight output in that variant
+        if v_max.dtype != p.dtype or wm is not None:
+            raise TypeError("adamw_masked: v_max must have the weight dtype and excludes wm")
+        check(lib().sf_adamw_masked_amsgrad(_p(p), _p(g), _p(mask), _p(m), _p(v), _p(v_max), _dt(p), p.numel(), float(lr),
+                                            float(beta1), float(beta2), float(eps), float(weight_decay), float(decay),
+                                            float(bc1), float(bc2), float(adaptive_l1), _stream()),
+              "sf_adamw_masked_amsgrad")
+        return
     cols = p.shape[-1] if p.dim() >= 2 else 0
     check(lib().sf_adamw_masked(_p(p), _p(g), _p(mask), _p(m), _p(v), _dt(p), p.numel(), float(lr), float(beta1),
                                 float(beta2), float(eps), float(weight_decay), float(decay), float(bc1), float(bc2),

@@ -248,6 +248,29 @@ def case_adamw():
     save("adamw", d)
 
 
+def case_adamw_ams():
+    """AdamW with amsgrad=True (legacy/adamw.py:126-128, 142-156): gradients shrink and grow again, so
+    the running maximum of the second moment differs from the second moment itself."""
+    torch.manual_seed(6)
+    d = {}
+    scales = (0.1, 0.01, 0.05, 0.002)
+    d["scales"] = np.asarray(scales)
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        p = torch.nn.Parameter((torch.randn(32, 64) * 0.02).to(dtype))
+        p.mask = torch.rand(32, 64)
+        opt = ref_adamw.AdamW([p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=True)
+        put(d, f"{tag}_p0", p.data); put(d, f"{tag}_mask", p.mask)
+        for t, sc in enumerate(scales):
+            g = (torch.randn(32, 64) * sc).to(dtype)
+            p.grad = g.clone()
+            opt.step(decay=5e-4 * (t + 1))
+            st = opt.state[p]
+            put(d, f"{tag}_g{t}", g); put(d, f"{tag}_p{t + 1}", p.data)
+            put(d, f"{tag}_m{t + 1}", st["exp_avg"]); put(d, f"{tag}_v{t + 1}", st["exp_avg_sq"])
+            put(d, f"{tag}_vmax{t + 1}", st["max_exp_avg_sq"])
+    save("adamw_ams", d)
+
+
 def case_block_sparse():
     torch.manual_seed(3)
     out_f, in_f, T = 64, 96, 24
@@ -652,4 +675,5 @@ if __name__ == "__main__":
     case_penalty()
     case_ties()
     case_adamw()
+    case_adamw_ams()
     case_block_sparse()

@@ -251,6 +251,23 @@ def test_adamw_golden(ops, tag, tol, l1):
         assert rel_err(wm.float(), want_wm.float()) <= tol
 
 
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_adamw_amsgrad_golden(ops, tag, tol):
+    """amsgrad=True through the optimizer class against the reference's trajectory (tests/golden/adamw_ams.npz)."""
+    import sparseforge_b200 as sf
+
+    g = Golden("adamw_ams")
+    p = torch.nn.Parameter(dev(g[f"{tag}_p0"]))
+    p.mask = dev(g[f"{tag}_mask"])
+    opt = sf.AdamW([p], lr=1e-3, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, amsgrad=True)
+    for t in range(4):
+        p.grad = dev(g[f"{tag}_g{t}"]).clone()
+        opt.step(decay=5e-4 * (t + 1))
+        st = opt.state[p]
+        for got, name in ((p.data, "p"), (st["exp_avg"], "m"), (st["exp_avg_sq"], "v"), (st["max_exp_avg_sq"], "vmax")):
+            assert rel_err(got.float(), g[f"{tag}_{name}{t + 1}"].float()) <= tol, (name, t)
+
+
 def test_adamw_no_mask(ops):
     torch.manual_seed(4)
     p0, g0 = torch.randn(1024) * 0.1, torch.randn(1024) * 0.01

@@ -111,8 +111,7 @@ def test_unsupported_configurations_raise():
     slorb = sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(SLoRB=True, SLoRB_k=16))
     assert tuple(slorb.x_proj.shape) == (4, 64) and tuple(slorb.SLoRB_Weight.shape) == (8, 4)
     assert list(slorb.state_dict().keys())[-2:] == ["x_proj", "SLoRB_Weight"]
-    with pytest.raises(NotImplementedError):
-        sf.AdamW([torch.nn.Parameter(torch.zeros(2))], amsgrad=True)
+    assert sf.AdamW([torch.nn.Parameter(torch.zeros(2))], amsgrad=True).param_groups[0]["amsgrad"] is True
     with pytest.raises(ValueError):
         sf.AdamW([torch.nn.Parameter(torch.zeros(2))], lr=-1.0)
 

@@ -404,6 +404,19 @@ def test_adamw(tag, tol, l1):
         assert rel_err(v, g[f"{tag}_v{t + 1}"]) <= tol
 
 
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_adamw_amsgrad(tag, tol):
+    g = Golden("adamw_ams")
+    p = g[f"{tag}_p0"]
+    m, v, vmax = torch.zeros_like(p), torch.zeros_like(p), torch.zeros_like(p)
+    for t in range(4):
+        p, m, v, vmax = O.adamw_step(p, g[f"{tag}_g{t}"], m, v, step=t + 1, lr=1e-3, betas=(0.9, 0.95), eps=1e-8,
+                                     weight_decay=0.1, mask=g[f"{tag}_mask"], decay=5e-4 * (t + 1), v_max=vmax)
+        for got, name in ((p, "p"), (m, "m"), (v, "v"), (vmax, "vmax")):
+            assert rel_err(got.float(), g[f"{tag}_{name}{t + 1}"].float()) <= tol
+    assert not torch.equal(vmax, v)  # the maximum is doing something in this fixture
+
+
 def test_block_sparse_layout():
     g = Golden("block_sparse")
     W = g["W"]
