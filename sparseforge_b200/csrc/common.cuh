@@ -207,6 +207,20 @@ struct Vec8<float> {
         x[0] = __uint_as_float(r.a.x); x[1] = __uint_as_float(r.a.y); x[2] = __uint_as_float(r.a.z); x[3] = __uint_as_float(r.a.w);
         x[4] = __uint_as_float(r.b.x); x[5] = __uint_as_float(r.b.y); x[6] = __uint_as_float(r.b.z); x[7] = __uint_as_float(r.b.w);
     }
+    static __device__ __forceinline__ void square(const Raw& r, float (&x)[8]) {
+        unpack(r, x);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], x[i]);
+    }
+    // The storage form of 8 values, and its store.
+    static __device__ __forceinline__ Raw pack(const float (&x)[8]) {
+        return Raw{make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3])),
+                   make_uint4(__float_as_uint(x[4]), __float_as_uint(x[5]), __float_as_uint(x[6]), __float_as_uint(x[7]))};
+    }
+    static __device__ __forceinline__ void store_raw(float* p, const Raw& r) {
+        st_stream16(p, r.a);
+        st_stream16(p + 4, r.b);
+    }
     static __device__ __forceinline__ void store_product(float* p, const Raw& r, const float (&f)[8]) {
         st_stream16(p, make_uint4(__float_as_uint(__fmul_rn(__uint_as_float(r.a.x), f[0])),
                                   __float_as_uint(__fmul_rn(__uint_as_float(r.a.y), f[1])),
@@ -249,6 +263,28 @@ struct Vec8<__nv_bfloat16> {
         for (int i = 0; i < 4; ++i) {
             x[2 * i] = __uint_as_float(w[i] << 16);
             x[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ Raw pack(const float (&x)[8]) {
+        uint32_t w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        return Raw{make_uint4(w[0], w[1], w[2], w[3])};
+    }
+    static __device__ __forceinline__ void store_raw(__nv_bfloat16* p, const Raw& r) { st_stream16(p, r.a); }
+    // x <- round(raw * raw): the packed multiply rounds the exact product once, as the tensor op does
+    static __device__ __forceinline__ void square(const Raw& r, float (&x)[8]) {
+        const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&w[i]);
+            const __nv_bfloat162 sq = __hmul2(v, v);
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(&sq);
+            x[2 * i] = __uint_as_float(u << 16);
+            x[2 * i + 1] = __uint_as_float(u & 0xffff0000u);
         }
     }
     static __device__ __forceinline__ void store_product(__nv_bfloat16* p, const Raw& r, const float (&f)[8]) {

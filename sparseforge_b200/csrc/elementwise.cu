@@ -507,13 +507,18 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
         if (EMIT_WM || FROM_W) wraw = Vec8<TW>::load_raw(W + e);
         if (FROM_W) {
             float w[8];
-            Vec8<TW>::unpack(wraw, w);
+            if (P.metric == SF_METRIC_HESSIAN_OBD) {
+                Vec8<TW>::square(wraw, w);  // round(w * w) in the weight dtype
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const float h = sc[i];
-                if (P.metric == SF_METRIC_HESSIAN_OBD) sc[i] = __fmul_rn(__fadd_rn(h, 1e-8f), Vec8<TW>::round(__fmul_rn(w[i], w[i])));
-                else if (P.metric == SF_METRIC_HESSIAN_RATIO) sc[i] = __fdiv_rn(fabsf(w[i]), __fsqrt_rn(__fadd_rn(h, 1e-8f)));
-                else if (P.metric == SF_METRIC_MAGNITUDE) sc[i] = fabsf(w[i]);
+                for (int i = 0; i < 8; ++i) sc[i] = __fmul_rn(__fadd_rn(sc[i], 1e-8f), w[i]);
+            } else {
+                Vec8<TW>::unpack(wraw, w);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float h = sc[i];
+                    if (P.metric == SF_METRIC_HESSIAN_RATIO) sc[i] = __fdiv_rn(fabsf(w[i]), __fsqrt_rn(__fadd_rn(h, 1e-8f)));
+                    else if (P.metric == SF_METRIC_MAGNITUDE) sc[i] = fabsf(w[i]);
+                }
             }
         }
         float fz[8];
@@ -776,7 +781,8 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
             }
             pw[i] = p2; em[i] = m1; ev[i] = v1;
         }
-        Vec8<TW>::store(p + e, pw);
+        const typename Vec8<TW>::Raw praw = Vec8<TW>::pack(pw);  // the weight as stored
+        Vec8<TW>::store_raw(p + e, praw);
         Vec8<TW>::store(m + e, em);
         Vec8<TW>::store(v + e, ev);
         if (AMS) Vec8<TW>::store(static_cast<TW*>(A.vmax) + e, vx);
@@ -796,14 +802,15 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
                 Vec8<float>::store(H + e, h);
             }
             float ps = 0.0f, ps2 = 0.0f;
+            float ws[8];  // the stored weight, or for the OBD score its square rounded to the weight dtype
+            if (metric == SF_METRIC_HESSIAN_OBD) Vec8<TW>::square(praw, ws); else Vec8<TW>::unpack(praw, ws);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                const float w = Vec8<TW>::round(pw[i]);  // the weight as stored
                 float sv;
-                if (metric == SF_METRIC_HESSIAN_OBD) sv = __fmul_rn(__fadd_rn(h[i], 1e-8f), Vec8<TW>::round(__fmul_rn(w, w)));
-                else if (metric == SF_METRIC_HESSIAN_RATIO) sv = __fdiv_rn(fabsf(w), __fsqrt_rn(__fadd_rn(h[i], 1e-8f)));
+                if (metric == SF_METRIC_HESSIAN_OBD) sv = __fmul_rn(__fadd_rn(h[i], 1e-8f), ws[i]);
+                else if (metric == SF_METRIC_HESSIAN_RATIO) sv = __fdiv_rn(fabsf(ws[i]), __fsqrt_rn(__fadd_rn(h[i], 1e-8f)));
                 else if (metric == SF_METRIC_HESSIAN) sv = h[i];
-                else sv = fabsf(w);
+                else sv = fabsf(ws[i]);
                 sc[i] = sv;
                 ps += sv;
                 ps2 = fmaf(sv, sv, ps2);
