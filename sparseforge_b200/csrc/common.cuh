@@ -212,6 +212,7 @@ struct Vec8<float> {
 #pragma unroll
         for (int i = 0; i < 8; ++i) x[i] = __fmul_rn(x[i], x[i]);
     }
+    static __device__ __forceinline__ void round8(float (&)[8]) {}
     // The storage form of 8 values, and its store.
     static __device__ __forceinline__ Raw pack(const float (&x)[8]) {
         return Raw{make_uint4(__float_as_uint(x[0]), __float_as_uint(x[1]), __float_as_uint(x[2]), __float_as_uint(x[3])),
@@ -275,6 +276,16 @@ struct Vec8<__nv_bfloat16> {
         return Raw{make_uint4(w[0], w[1], w[2], w[3])};
     }
     static __device__ __forceinline__ void store_raw(__nv_bfloat16* p, const Raw& r) { st_stream16(p, r.a); }
+    // Rounds eight values to the storage type and back, two per conversion.
+    static __device__ __forceinline__ void round8(float (&x)[8]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+            const uint32_t u = *reinterpret_cast<const uint32_t*>(&h);
+            x[2 * i] = __uint_as_float(u << 16);
+            x[2 * i + 1] = __uint_as_float(u & 0xffff0000u);
+        }
+    }
     // x <- round(raw * raw): the packed multiply rounds the exact product once, as the tensor op does
     static __device__ __forceinline__ void square(const Raw& r, float (&x)[8]) {
         const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
@@ -383,6 +394,15 @@ struct Span8<int8_t> {
 // Eight +-1 probe signs held as int8 in one 8-byte load (only the sign bit is read).
 template <>
 struct Vec8<int8_t> {
+    // The sign bit of each of 8 values (+1 / -1 probes), moved to the float sign position.
+    static __device__ __forceinline__ void load_signs(const int8_t* p, uint32_t (&sb)[8]) {
+        const uint2 r = __ldcs(reinterpret_cast<const uint2*>(p));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            sb[i] = (r.x << (24 - 8 * i)) & 0x80000000u;
+            sb[4 + i] = (r.y << (24 - 8 * i)) & 0x80000000u;
+        }
+    }
     static __device__ __forceinline__ void load(const int8_t* p, float (&x)[8]) {
         const uint2 r = __ldcs(reinterpret_cast<const uint2*>(p));
 #pragma unroll

@@ -756,12 +756,16 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         if (A.has_mask) Vec8<float>::load(mask + e, mk);
         float vx[8];
         if (AMS) Vec8<TW>::load(static_cast<const TW*>(A.vmax) + e, vx);
+        // p.mul_(1 - lr*wd) rounds to the storage type; the moments and the update are carried in
+        // fp32 and rounded once when stored (the reference rounds after every in-place op, which
+        // differs by at most one storage ulp)
+        float pd[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pd[i] = __fmul_rn(pw[i], A.c_wd);
+        Vec8<TW>::round8(pd);
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            // p.mul_(1 - lr*wd) rounds to the storage type; the moments and the update are carried in
-            // fp32 and rounded once when stored (the reference rounds after every in-place op, which
-            // differs by at most one storage ulp)
-            float p1 = Vec8<TW>::round(__fmul_rn(pw[i], A.c_wd));
+            const float p1 = pd[i];
             float g1 = gr[i];
             if (A.has_mask)
                 g1 = __fmaf_rn(A.decay, __fmul_rn(p1, __fsub_rn(1.0f, mk[i])), g1);
@@ -791,14 +795,24 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
             if (metric != SF_METRIC_MAGNITUDE || hu.hvp != nullptr) Vec8<float>::load(H + e, h);
             if (hu.hvp != nullptr) {
                 // the Hutchinson sample of this step is folded into H before the score reads it
-                float hv[8], sg[8];
+                float hv[8];
                 Vec8<TW>::load(hu.hvp + e, hv);
-                if (hu.probe_i8) Vec8<int8_t>::load(hu.probe_i8 + e, sg); else Vec8<TW>::load(hu.probe_w + e, sg);
+                if (hu.probe_i8) {
+                    // a +1 / -1 probe only flips the sign: the product is exact in the weight dtype
+                    uint32_t sb[8];
+                    Vec8<int8_t>::load_signs(hu.probe_i8 + e, sb);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float d = fmaxf(Vec8<TW>::round(__fmul_rn(hv[i], sg[i])), 0.0f);
-                    h[i] = __fmaf_rn(hu.one_minus_beta, d, __fmul_rn(h[i], hu.beta));
+                    for (int i = 0; i < 8; ++i) hv[i] = __uint_as_float(__float_as_uint(hv[i]) ^ sb[i]);
+                } else {
+                    float sg[8];
+                    Vec8<TW>::load(hu.probe_w + e, sg);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) hv[i] = __fmul_rn(hv[i], sg[i]);
+                    Vec8<TW>::round8(hv);
                 }
+#pragma unroll
+                for (int i = 0; i < 8; ++i)
+                    h[i] = __fmaf_rn(hu.one_minus_beta, fmaxf(hv[i], 0.0f), __fmul_rn(h[i], hu.beta));
                 Vec8<float>::store(H + e, h);
             }
             float ps = 0.0f, ps2 = 0.0f;
