@@ -181,6 +181,20 @@ __device__ __forceinline__ void st_stream8(void* p, uint2 v) {
 }
 
 // 8 consecutive elements of a float / bf16 tensor <-> 8 floats.
+// 32-byte streaming accesses (eight fp32 at once, sm_100): one memory instruction where the 16-byte
+// form needs two. The address must be 32-byte aligned.
+__device__ __forceinline__ void ld_stream32(const float* p, float (&x)[8]) {
+    asm volatile("ld.global.cs.v8.f32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=f"(x[0]), "=f"(x[1]), "=f"(x[2]), "=f"(x[3]), "=f"(x[4]), "=f"(x[5]), "=f"(x[6]), "=f"(x[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_stream32(float* p, const float (&x)[8]) {
+    asm volatile("st.global.cs.v8.f32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "f"(x[0]), "f"(x[1]), "f"(x[2]), "f"(x[3]), "f"(x[4]), "f"(x[5]), "f"(x[6]), "f"(x[7])
+                 : "memory");
+}
+__host__ __device__ inline bool aligned32(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 31u) == 0; }
+
 template <typename T>
 struct Vec8;
 template <>

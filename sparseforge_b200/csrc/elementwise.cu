@@ -478,7 +478,8 @@ __device__ __forceinline__ void block_reduce_stats(const GroupStats& g, double* 
 // (the tempering recipe of the benchmark); the general instantiation tests those at run time.
 // FROM_W: the score is not read but formed again from the weight and the Hessian diagonal with the
 // arithmetic of the score kernels (so it equals what they would have written); `score` then holds H.
-template <typename TW, bool EMIT_WM, bool EMIT_META, bool PLAIN, bool FROM_W = false>
+// WIDE: the fp32 tensors are 32-byte aligned and are moved with 32-byte accesses.
+template <typename TW, bool EMIT_WM, bool EMIT_META, bool PLAIN, bool FROM_W = false, bool WIDE = false>
 __global__ void __launch_bounds__(kThreads)
 mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict__ norm,
                         float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm,
@@ -502,8 +503,10 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
         const int64_t e = c * 8;
         float sc[8], m[8], eff[8];
         typename Vec8<TW>::Raw wraw;
-        if (!FROM_W || P.metric != SF_METRIC_MAGNITUDE) Vec8<float>::load(score + e, sc);
-        Vec8<float>::load(mask + e, m);
+        if (!FROM_W || P.metric != SF_METRIC_MAGNITUDE) {
+            if (WIDE) ld_stream32(score + e, sc); else Vec8<float>::load(score + e, sc);
+        }
+        if (WIDE) ld_stream32(mask + e, m); else Vec8<float>::load(mask + e, m);
         if (EMIT_WM || FROM_W) wraw = Vec8<TW>::load_raw(W + e);
         if (FROM_W) {
             float w[8];
@@ -615,7 +618,7 @@ mask_update_nm24_kernel(const float* __restrict__ score, const float* __restrict
             }
         }
         gs.flips += __popc(kp8 ^ kn8);
-        Vec8<float>::store(mask + e, m);
+        if (WIDE) st_stream32(mask + e, m); else Vec8<float>::store(mask + e, m);
         if (freeze) Vec8<float>::store(P.frozen + e, fz);
         if (EMIT_WM) Vec8<TW>::store_product(wm + e, wraw, eff);
         if (EMIT_META) meta[c] = (uint8_t)(nibble_of_keep_lut(kn8 & 0xFu) | (nibble_of_keep_lut(kn8 >> 4) << 4));
@@ -738,7 +741,7 @@ struct HutchArgs {
 // sums of score and score^2, so the mask update that follows needs no separate score pass.
 // AMS: the AMSGrad variant (legacy/adamw.py:142-156): the denominator uses the running maximum of the
 // stored second moment.
-template <typename TW, bool EMIT_WM, bool SCORE, bool AMS = false>
+template <typename TW, bool EMIT_WM, bool SCORE, bool AMS = false, bool WIDE = false>
 __global__ void __launch_bounds__(kThreads)
 adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* __restrict__ mask,
                     TW* __restrict__ m, TW* __restrict__ v, TW* __restrict__ wm, int64_t chunks,
@@ -753,7 +756,9 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         Vec8<TW>::load(g + e, gr);
         Vec8<TW>::load(m + e, em);
         Vec8<TW>::load(v + e, ev);
-        if (A.has_mask) Vec8<float>::load(mask + e, mk);
+        if (A.has_mask) {
+            if (WIDE) ld_stream32(mask + e, mk); else Vec8<float>::load(mask + e, mk);
+        }
         float vx[8];
         if (AMS) Vec8<TW>::load(static_cast<const TW*>(A.vmax) + e, vx);
         // p.mul_(1 - lr*wd) rounds to the storage type; the moments and the update are carried in
@@ -792,7 +797,9 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
         if (AMS) Vec8<TW>::store(static_cast<TW*>(A.vmax) + e, vx);
         if (SCORE) {
             float h[8], sc[8];
-            if (metric != SF_METRIC_MAGNITUDE || hu.hvp != nullptr) Vec8<float>::load(H + e, h);
+            if (metric != SF_METRIC_MAGNITUDE || hu.hvp != nullptr) {
+                if (WIDE) ld_stream32(H + e, h); else Vec8<float>::load(H + e, h);
+            }
             if (hu.hvp != nullptr) {
                 // the Hutchinson sample of this step is folded into H before the score reads it
                 float hv[8];
@@ -813,7 +820,7 @@ adamw_masked_kernel(TW* __restrict__ p, const TW* __restrict__ g, const float* _
 #pragma unroll
                 for (int i = 0; i < 8; ++i)
                     h[i] = __fmaf_rn(hu.one_minus_beta, fmaxf(hv[i], 0.0f), __fmul_rn(h[i], hu.beta));
-                Vec8<float>::store(H + e, h);
+                if (WIDE) st_stream32(H + e, h); else Vec8<float>::store(H + e, h);
             }
             float ps = 0.0f, ps2 = 0.0f;
             float ws[8];  // the stored weight, or for the OBD score its square rounded to the weight dtype
@@ -1171,14 +1178,17 @@ int sf_mask_update_nm24_from_weight(const void* W, int w_dtype, const float* H, 
     const int64_t chunks = rows * cols / 8;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
     const bool plain = !structured_exact && !(beta_s > 0.0) && pen == 0.0 && binarize_decay == 0.0;
-#define SF_MUW(TW, PL)                                                                           \
+    const bool wide = aligned32(mask) && aligned32(H);
+#define SF_MUW(TW, PL, WD)                                                                       \
     do {                                                                                         \
-        auto kern = mask_update_nm24_kernel<TW, true, true, PL, true>;                           \
+        auto kern = mask_update_nm24_kernel<TW, true, true, PL, true, WD>;                       \
         kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                     \
             H, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);                       \
     } while (0)
-    if (w_dtype == SF_F32) { if (plain) SF_MUW(float, true); else SF_MUW(float, false); }
-    else { if (plain) SF_MUW(__nv_bfloat16, true); else SF_MUW(__nv_bfloat16, false); }
+#define SF_MUW_W(TW, PL) do { if (wide) SF_MUW(TW, PL, true); else SF_MUW(TW, PL, false); } while (0)
+    if (w_dtype == SF_F32) { if (plain) SF_MUW_W(float, true); else SF_MUW_W(float, false); }
+    else { if (plain) SF_MUW_W(__nv_bfloat16, true); else SF_MUW_W(__nv_bfloat16, false); }
+#undef SF_MUW_W
 #undef SF_MUW
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
@@ -1339,7 +1349,10 @@ static int adamw_impl(void* p, const void* g, const float* mask, void* m, void* 
     if (vmax != nullptr) {
         if (w_dtype == SF_F32) SF_AD(float, false, false, true); else SF_AD(__nv_bfloat16, false, false, true);
     } else if (norm != nullptr) {
-        if (w_dtype == SF_F32) SF_AD(float, false, true); else SF_AD(__nv_bfloat16, false, true);
+        // the fp32 mask and Hessian move in 32-byte accesses where their addresses allow it
+        const bool wide = (mask == nullptr || aligned32(mask)) && (H == nullptr || aligned32(H)) && score == nullptr;
+        if (w_dtype == SF_F32) { if (wide) SF_AD(float, false, true, false, true); else SF_AD(float, false, true); }
+        else { if (wide) SF_AD(__nv_bfloat16, false, true, false, true); else SF_AD(__nv_bfloat16, false, true); }
     } else if (w_dtype == SF_F32) { if (wm) SF_AD(float, true, false); else SF_AD(float, false, false); }
     else { if (wm) SF_AD(__nv_bfloat16, true, false); else SF_AD(__nv_bfloat16, false, false); }
 #undef SF_AD
