@@ -1233,15 +1233,31 @@ static int mask_update_impl(const float* score, const float* norm, const float* 
     do {                                                                                         \
         if (plain) SF_MU_K(TW, EW, EM, true); else SF_MU_K(TW, EW, EM, false);                   \
     } while (0)
+    // the layer path (masked weight and metadata wanted, no freeze flags): 32-byte fp32 accesses where aligned
+    const bool wide = wm && meta && fb.flags == nullptr && aligned32(score) && aligned32(mask);
+#define SF_MU_WIDE(TW)                                                                           \
+    do {                                                                                         \
+        if (plain) {                                                                             \
+            auto kern = mask_update_nm24_kernel<TW, true, true, true, false, true>;              \
+            kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                 \
+                score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);               \
+        } else {                                                                                 \
+            auto kern = mask_update_nm24_kernel<TW, true, true, false, false, true>;             \
+            kern<<<grid_one_wave((const void*)kern, chunks), kThreads, 0, st>>>(                 \
+                score, norm, mask, (const TW*)W, (TW*)wm, meta, stats, chunks, P);               \
+        }                                                                                        \
+    } while (0)
 #define SF_MU_T(TW)                                       \
     do {                                                  \
-        if (wm && meta) SF_MU(TW, true, true);            \
+        if (wide) SF_MU_WIDE(TW);                         \
+        else if (wm && meta) SF_MU(TW, true, true);       \
         else if (wm) SF_MU(TW, true, false);              \
         else if (meta) SF_MU(TW, false, true);            \
         else SF_MU(TW, false, false);                     \
     } while (0)
     if (w_dtype == SF_F32) SF_MU_T(float); else SF_MU_T(__nv_bfloat16);
 #undef SF_MU_T
+#undef SF_MU_WIDE
 #undef SF_MU_K
 #undef SF_MU
     SF_CHECK_CUDA(cudaGetLastError());
