@@ -3,7 +3,6 @@ partial input gradients and combining the score sums must reproduce the unsharde
 import os
 import socket
 
-import pytest
 import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
