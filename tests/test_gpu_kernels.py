@@ -360,6 +360,47 @@ def test_mask_update_from_weight_equals_update_from_score(ops, dtype, metric, ex
         assert torch.equal(x, y)
 
 
+def test_passes_agree_for_16_and_32_byte_aligned_tensors(ops):
+    """The optimizer+score and mask-update passes move the fp32 mask and Hessian with 32-byte accesses
+    when their addresses allow it and with 16-byte accesses otherwise: same results either way."""
+    torch.manual_seed(23)
+    rows, cols = 64, 264
+    n = rows * cols
+    W0 = (torch.randn(rows, cols) * 0.05).to(torch.bfloat16)
+    g0 = (torch.randn(rows, cols) * 0.01).to(torch.bfloat16)
+    hvp = (torch.randn(rows, cols) * 0.1).to(torch.bfloat16)
+    sign = (torch.randint(0, 2, (rows, cols)) * 2 - 1).to(torch.int8)
+    H0, mask0 = torch.rand(rows, cols) * 1e-2, torch.rand(rows, cols)
+
+    def fp32(t, shift):  # a copy that starts `shift` floats into a 32-byte aligned buffer
+        buf = torch.empty(n + 8, device=DEV)
+        view = buf[shift:shift + n].view(rows, cols)
+        view.copy_(t)
+        assert view.data_ptr() % 32 == (4 * shift) % 32
+        return view
+
+    def run(shift):
+        p, m, v = dev(W0), torch.zeros(rows, cols, dtype=torch.bfloat16, device=DEV), torch.zeros(rows, cols, dtype=torch.bfloat16, device=DEV)
+        H, mask = fp32(H0, shift), fp32(mask0, shift)
+        norm, scr = torch.empty(2, device=DEV), ops.hutch_score_scratch(DEV)
+        stats = torch.zeros(8, dtype=torch.float64, device=DEV)
+        wm, meta = torch.empty_like(p), torch.zeros(rows, cols // 8, dtype=torch.uint8, device=DEV)
+        ops.adamw_masked_score(p, dev(g0), m, v, mask=mask, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                               decay=2e-4, step=2, hvp=dev(hvp), probe=dev(sign), beta_h=0.98, H=H, score=None, norm=norm,
+                               scratch=scr, metric="hessian_obd")
+        ops.mask_update_nm24_from_weight(p, H, norm, mask, stats, wm, meta, metric="hessian_obd", temperature=0.4,
+                                         mask_lr=0.2, hx=0.6)
+        score = torch.empty(rows, cols, device=DEV)
+        ops.hutch_score(p, H, score, norm, scr, metric="hessian_obd")
+        mask2, stats2 = mask.clone() if shift == 0 else fp32(mask, shift), torch.zeros(8, dtype=torch.float64, device=DEV)
+        ops.mask_update_nm24(fp32(score, shift), norm, mask2, stats2, W=p, wm=wm.clone(), meta=meta.clone(),
+                             temperature=0.3, mask_lr=0.2, hx=0.6, pen=0.02, penalty_mode=1)
+        return [t.clone() for t in (p, m, v, H, mask, wm, meta, stats, norm, mask2, stats2)]
+
+    for a, b in zip(run(0), run(4)):
+        assert torch.equal(a, b)
+
+
 # ---------------------------------------------------------------------------------------
 # argument checks: bad calls are refused on the host, nothing is launched
 # ---------------------------------------------------------------------------------------
