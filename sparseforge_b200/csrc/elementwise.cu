@@ -109,11 +109,16 @@ hutch_score_kernel(const TW* __restrict__ hvp, const TV* __restrict__ v, float* 
             for (int i = 0; i < 8; ++i)
                 s[i] = Vec8<TW>::round(__fdiv_rn(fabsf(Vec8<TW>::round(__fmul_rn(w[i], g[i]))), aux_scalar));
         } else {
+            if (METRIC == SF_METRIC_HESSIAN_OBD) {
+                // round(w * w) in the weight dtype, two per conversion
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w[i] = __fmul_rn(w[i], w[i]);
+                Vec8<TW>::round8(w);
+            }
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 if (METRIC == SF_METRIC_HESSIAN_OBD) {
-                    float w2 = Vec8<TW>::round(__fmul_rn(w[i], w[i]));
-                    s[i] = __fmul_rn(__fadd_rn(h[i], eps), w2);
+                    s[i] = __fmul_rn(__fadd_rn(h[i], eps), w[i]);
                 } else if (METRIC == SF_METRIC_HESSIAN_RATIO) {
                     s[i] = __fdiv_rn(fabsf(w[i]), __fsqrt_rn(__fadd_rn(h[i], eps)));
                 } else if (METRIC == SF_METRIC_HESSIAN) {
