@@ -640,6 +640,76 @@ def case_block_masks():
     save("block_masks", d)
 
 
+C1_ROWS = dict(w_rows=64, y_rows=32, dx_rows=64)
+
+
+def c1_inputs():
+    """The fp32 GPT-2-small MLP case: W [3072, 768] ~ N(0, 0.02), X [8, 1024, 768] ~ N(0, 1),
+    dY [8, 1024, 3072] ~ N(0, 1) drawn in that order from the CPU generator seeded with 0."""
+    torch.manual_seed(0)
+    W = torch.randn(3072, 768) * 0.02
+    X = torch.randn(8, 1024, 768)
+    dY = torch.randn(8, 1024, 3072)
+    return W, X, dY
+
+
+def c1_sample_rows(n_rows, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.sort(torch.randperm(n_rows, generator=g)[:count]).values
+
+
+def case_c1():
+    """The whole fp32 chain at its full size: four Hutchinson probes, one mask update at step 0, the hard
+    2:4 projection, then a masked forward / backward with the hard mask (hardening_x = 0). The inputs
+    are regenerated from the seed at test time (fingerprints stored); the hard mask is stored as packed
+    bits, the float tensors as full-tensor sums plus a sample of rows."""
+    W, X, dY = c1_inputs()
+    out_f, in_f = W.shape
+    T = X.shape[0] * X.shape[1]
+    d = {}
+    for name, t in (("W", W), ("X", X), ("dY", dY)):
+        put(d, f"fp_{name}", torch.stack([t.double().sum(), (t.double() ** 2).sum(), t.flatten()[12345].double()]))
+    layer = make_layer(out_f, in_f, W, torch.float32, mask_type="structured", mask_metric="hessian_obd", N=2, M=4,
+                       temp_init=1.0, mask_update_period=1, sparsity_warmup_steps=0)
+    rows_w = c1_sample_rows(out_f, C1_ROWS["w_rows"], 11)
+    rows_y = c1_sample_rows(T, C1_ROWS["y_rows"], 12)
+    rows_x = c1_sample_rows(T, C1_ROWS["dx_rows"], 13)
+    put(d, "rows_w", rows_w); put(d, "rows_y", rows_y); put(d, "rows_x", rows_x)
+
+    def summary(name, t, rows):
+        t2 = t.detach().reshape(-1, t.shape[-1])
+        put(d, f"{name}_sum", torch.stack([t2.double().sum(), (t2.double() ** 2).sum(), t2.double().abs().max()]))
+        put(d, f"{name}_rows", t2[rows])
+
+    for i in range(4):
+        v = rademacher((out_f, in_f), 1 + i, torch.float32)
+        dd = {}
+        hutchinson_once(layer, X, dY, v, dd, str(i))
+        summary(f"hvp_{i}", torch.from_numpy(dd[f"hvp_{i}"]), rows_w)
+        summary(f"H_{i}", layer.hessian_diag.data, rows_w)
+    put(d, "T0", layer._temperature(0))
+    raw = (layer.hessian_diag.data + 1e-8) * (layer.weight.data * layer.weight.data)
+    summary("score_raw", raw, rows_w)
+    put(d, "score_mean_std", torch.stack([raw.float().mean(), raw.float().std(unbiased=False) + 1e-6]))
+    summary("G", layer.compute_gate_target(0), rows_w)
+    ref_utils.calculate_model_mask(layer, step=0, lambda_mid=0.0)
+    summary("mask", layer.mask.data, rows_w)
+    put(d, "flips", int(layer.weight.flipped_mask))
+    put(d, "hx_after_update", float(layer.hardening_x))
+    hard = layer._hard_mask_from_soft(layer.mask.data)
+    d["hard_bits"] = np.packbits(hard.numpy().astype(np.uint8), axis=1)
+    # near-ties of the soft mask: groups whose 2nd and 3rd largest values are closer than 1e-5 relative
+    srt = torch.sort(layer.mask.data.view(out_f, in_f // 4, 4), dim=-1, descending=True).values
+    put(d, "near_tie_groups", int(((srt[..., 1] - srt[..., 2]).abs() <= 1e-5 * srt[..., 1].abs()).sum()))
+    layer.hardening_x = 0.0
+    Xr = X.clone().requires_grad_(True)
+    layer.weight.grad = None
+    Y = layer(Xr)
+    Y.backward(dY)
+    summary("Y", Y, rows_y); summary("dX", Xr.grad, rows_x); summary("dW", layer.weight.grad, rows_w)
+    save("c1", d)
+
+
 if __name__ == "__main__":
     # `make_golden.py wanda ...` regenerates only the named single-function cases
     only = [a for a in sys.argv[1:] if not a.startswith("-")]
@@ -670,6 +740,7 @@ if __name__ == "__main__":
     case_kl_loss()
     case_slorb()
     case_block_masks()
+    case_c1()
     case_wanda()
     case_freeze()
     case_penalty()

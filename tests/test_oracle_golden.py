@@ -457,3 +457,47 @@ def test_c_oracle_matches_reference_fixtures_and_python_oracle():
     hard, meta = nm24_c.project(big.numpy())
     assert np.array_equal(hard, O.hard_mask_from_soft(big).numpy())
     assert np.array_equal(meta, O.meta_from_hard(O.hard_mask_from_soft(big)).numpy())
+
+
+def test_c1_full_size_chain():
+    """The fp32 GPT-2-small MLP case at its full size ([3072, 768] weight, 8192 tokens): the oracle's
+    whole chain (four Hutchinson probes through its own double backward, score, gate, mask update,
+    projection, masked forward / backward) against the reference's recorded run (tests/golden/c1.npz)."""
+    import numpy as np
+
+    from tests import baseline_cases as B
+
+    g = Golden("c1")
+    W, X, dY = B.c1_inputs()
+    for name, t in (("W", W), ("X", X), ("dY", dY)):
+        assert torch.allclose(B.fingerprint(t), g[f"fp_{name}"], rtol=1e-12, atol=0), f"seeded input {name} differs"
+    res = B.c1_oracle(W, X, dY)
+    rows_w, rows_y, rows_x = g["rows_w"], g["rows_y"], g["rows_x"]
+
+    def check(name, t, rows, rtol, atol_scale):
+        t2 = t.reshape(-1, t.shape[-1])
+        want = g[f"{name}_rows"]
+        B.assert_elementwise(t2[rows], want, rtol, atol_scale * B.rms(want), name)
+        s = g[f"{name}_sum"]
+        assert abs(float(t2.double().sum()) - float(s[0])) <= 1e-4 * float(s[1]) ** 0.5 * t2.numel() ** 0.5 + 1e-9, name
+        assert abs(float((t2.double() ** 2).sum()) - float(s[1])) <= 1e-4 * float(s[1]), name
+
+    # second-order products of fp32 GEMMs: the summation order inside the host BLAS is the only difference
+    for i in range(4):
+        check(f"hvp_{i}", res["hvp"][i], rows_w, 1e-4, 1e-4)
+        check(f"H_{i}", res["H"][i], rows_w, 1e-5, 1e-7)
+    check("score_raw", res["score_raw"], rows_w, 1e-5, 1e-7)
+    assert torch.allclose(res["score_mean_std"], g["score_mean_std"], rtol=1e-5, atol=0)
+    check("G", res["G"], rows_w, 1e-5, 1e-7)
+    check("mask", res["mask"], rows_w, 1e-5, 1e-7)
+    want_hard = torch.from_numpy(np.unpackbits(g["hard_bits"].numpy(), axis=1)[:, : W.shape[1]].astype(np.float32))
+    diff, groups = B.hard_mismatch(res["hard"], want_hard)
+    ties = B.near_tie_groups(res["mask"], 1e-5)
+    assert bool((groups & ~ties).sum() == 0), "a hard-mask group differs outside the near-ties of the soft mask"
+    assert diff <= 2 * int(ties.sum())
+    # given the same soft mask the projection is exact: flips follow from it
+    if diff == 0:
+        assert res["flips"] == g.scalar("flips")
+    check("Y", res["Y"], rows_y, 1e-5, 1e-5)
+    check("dX", res["dX"], rows_x, 1e-5, 1e-5)
+    check("dW", res["dW"], rows_w, 1e-5, 1e-5)
