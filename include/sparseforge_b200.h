@@ -92,6 +92,18 @@ SF_API int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H,
 SF_API int sf_score_norm_from_sums(const double* sums, double n, float* norm, void* stream);
 
 /*
+ * Gradient EMA and g^2 Hessian proxy of SparseLinear.update_grad_hessian_ema
+ * (legacy/sparse_modeling.py:901-922) in one pass over the gradient:
+ *   grad_ema <- b * grad_ema + (1 - b) * g                      (g, grad_ema in `dtype`)
+ *   H        <- b * H + (1 - b) * round_dtype(g * g)            (H fp32; skipped when H is NULL)
+ * with ATen's rounding points (mul_ rounds to the tensor dtype, add_ with alpha is one fused step).
+ * n is a multiple of 8, every buffer 16-byte aligned. The early return of the reference for
+ * layers without a grad_ema tensor (every metric but `movement`) is the caller's.
+ */
+SF_API int sf_grad_hessian_ema(const void* g, void* grad_ema, int dtype, float* H, int64_t n, double beta,
+                               void* stream);
+
+/*
  * sf_hutch_score without a scratch argument: the partial sums go to an array that is part
  * of the library image. This entry point has no counterpart in the reference. It is for
  * callers that are not allowed to allocate device memory at the point where they need the
@@ -103,10 +115,12 @@ SF_API int sf_score_norm_from_sums(const double* sums, double n, float* norm, vo
  *
  * Limits and rules:
  *  - The array is 4096 doubles (32 KiB), resident on every GPU that loads the library until
- *    the process ends. It holds the partial sums of at most 2048 thread blocks of 32768
- *    elements, so n may not exceed SF_HUTCH_SCORE_STATIC_MAX_N (67,108,864 elements; the
- *    largest LLaMA-2-7B matrix has 45,088,768). A larger n returns SF_ERR_UNSUPPORTED and
- *    launches nothing; use sf_hutch_score with your own scratch then.
+ *    the process ends: two partial sums for each of at most 2048 thread blocks. The grid is
+ *    capped at 2048 blocks that stride over the input, so the array is large enough for any
+ *    n; the limit SF_HUTCH_SCORE_STATIC_MAX_N (67,108,864 elements; the largest LLaMA-2-7B
+ *    matrix has 45,088,768) is a fixed bound of this entry point, chosen so that what it
+ *    accepts is stated and tested, not a capacity of the array. A larger n returns
+ *    SF_ERR_UNSUPPORTED and launches nothing; use sf_hutch_score with your own scratch then.
  *  - The first call on each device looks up the array's device address (once per device,
  *    with that device current). Make that first call outside any CUDA stream capture.
  *  - All calls on one device share the array. It still holds the previous call's partial

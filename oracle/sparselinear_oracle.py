@@ -96,6 +96,16 @@ def hutchinson_accumulate(H: torch.Tensor, hvp: torch.Tensor, v: torch.Tensor, b
     return H.clone().mul_(beta).add_(d, alpha=1 - beta)
 
 
+def grad_hessian_ema(grad_ema, H, g, beta):
+    """SparseLinear.update_grad_hessian_ema, legacy/sparse_modeling.py:901-922: the gradient EMA (kept
+    for the movement metric) and, when the layer holds a Hessian tensor, the g^2 proxy folded into it.
+    Returns (grad_ema, H) as new tensors; H may be None."""
+    b = float(beta)
+    e = grad_ema.clone().mul_(b).add_(g, alpha=1 - b)
+    Hn = None if H is None else H.clone().mul_(b).add_(g * g, alpha=1 - b)
+    return e, Hn
+
+
 def wanda_add_batch(scaler_row, nsamples, inp):
     """SparseLinear.add_batch, legacy/sparse_modeling.py:884-898: running mean over samples of the
     squared L2 norm of every input channel. Returns the new scaler_row and sample count."""

@@ -25,6 +25,7 @@ _SIGNATURES = {
     "sf_hutch_score_scratch_doubles": (c_int64, [c_int64]),
     "sf_hutch_score": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_double, _P, _P, _P, c_int64, c_double, c_int, _P]),
     "sf_score_norm_from_sums": (c_int, [_P, c_double, _P, _P]),
+    "sf_grad_hessian_ema": (c_int, [_P, _P, c_int, _P, c_int64, c_double, _P]),
     "sf_hutch_score_static_max_n": (c_int64, []),
     "sf_hutch_score_static": (c_int, [_P, _P, c_int, _P, _P, c_int, _P, c_double, _P, _P, c_int64, c_double, c_int, _P]),
     "sf_mask_update_nm24": (c_int, [_P, _P, _P, _P, _P, c_int, _P, _P, _P, c_int64, c_int64, c_double, c_double, c_double,

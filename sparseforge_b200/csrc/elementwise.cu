@@ -426,6 +426,35 @@ static int launch_hutch_score(int metric, const void* hvp, const void* v, float*
 }
 
 // ---------------------------------------------------------------------------------------
+// Gradient EMA (movement metric) and the g^2 Hessian proxy in one pass over the gradient:
+//   grad_ema.mul_(b).add_(g, alpha = 1 - b)           in the weight dtype
+//   H.mul_(b).add_(g * g, alpha = 1 - b)              H fp32, g * g rounded to the gradient dtype
+// ---------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void __launch_bounds__(kThreads)
+grad_hessian_ema_kernel(const TW* __restrict__ g, TW* __restrict__ grad_ema, float* __restrict__ H, int64_t n,
+                        float beta, float one_minus_beta) {
+    SF_SPAN_LOOP(span, n) {
+        const SpanPos pos = span_pos(span, threadIdx.x & 31, n);
+        float gv[8], e[8];
+        Span8<TW>::load(g, pos, gv);
+        Span8<TW>::load(grad_ema, pos, e);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+            e[i] = __fmaf_rn(one_minus_beta, gv[i], Vec8<TW>::round(__fmul_rn(e[i], beta)));
+        Span8<TW>::store(grad_ema, pos, e);
+        if (H != nullptr) {
+            float h[8];
+            Span8<float>::load(H, pos, h);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                h[i] = __fmaf_rn(one_minus_beta, Vec8<TW>::round(__fmul_rn(gv[i], gv[i])), __fmul_rn(h[i], beta));
+            Span8<float>::store(H, pos, h);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
 // 2:4 soft-mask update + projection + masked weight + metadata + stats
 // ---------------------------------------------------------------------------------------
 struct MaskUpdateParams {
@@ -985,6 +1014,26 @@ int sf_hutch_score(const void* hvp, const void* v, int v_dtype, float* H, const 
     SF_CHECK_CUDA(cudaGetLastError());
     if (score == nullptr) return SF_OK;
     score_norm_finalize_kernel<<<1, kThreads, 0, st>>>(scratch, grid, (double)n, norm);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+int sf_grad_hessian_ema(const void* g, void* grad_ema, int dtype, float* H, int64_t n, double beta, void* stream) {
+    SF_CHECK_ARG(g != nullptr && grad_ema != nullptr, "sf_grad_hessian_ema: g and grad_ema must be non-null");
+    SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_grad_hessian_ema: n=%lld must be a positive multiple of 8", (long long)n);
+    SF_CHECK_ARG(dtype == SF_F32 || dtype == SF_BF16, "sf_grad_hessian_ema: dtype must be SF_F32 or SF_BF16");
+    if (!(aligned16(g) && aligned16(grad_ema) && aligned16(H)))
+        return fail(SF_ERR_ALIGNMENT, "sf_grad_hessian_ema: buffers must be 16-byte aligned");
+    cudaStream_t st = (cudaStream_t)stream;
+    const float b = (float)beta, omb = (float)(1.0 - beta);
+    if (dtype == SF_F32) {
+        auto kern = grad_hessian_ema_kernel<float>;
+        kern<<<grid_one_wave((const void*)kern, n / 8), kThreads, 0, st>>>((const float*)g, (float*)grad_ema, H, n, b, omb);
+    } else {
+        auto kern = grad_hessian_ema_kernel<__nv_bfloat16>;
+        kern<<<grid_one_wave((const void*)kern, n / 8), kThreads, 0, st>>>((const __nv_bfloat16*)g, (__nv_bfloat16*)grad_ema,
+                                                                          H, n, b, omb);
+    }
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }

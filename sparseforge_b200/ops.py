@@ -70,6 +70,18 @@ def hutch_accumulate(H, hvp, v, *, beta=0.99) -> None:
                                hvp.numel(), float(beta), _lib.METRICS["hessian_obd"], _stream()), "sf_hutch_score")
 
 
+def grad_hessian_ema(g, grad_ema, H=None, *, beta=0.99) -> None:
+    """grad_ema <- beta grad_ema + (1-beta) g and, with H, H <- beta H + (1-beta) g^2, in one pass
+    (legacy/sparse_modeling.py:901-922)."""
+    _cuda(g, grad_ema, H)
+    if g.dtype != grad_ema.dtype or g.numel() != grad_ema.numel():
+        raise TypeError("grad_hessian_ema: g and grad_ema must share dtype and size")
+    if H is not None and (H.dtype != torch.float32 or H.numel() != g.numel()):
+        raise TypeError("grad_hessian_ema: H must be float32 with g's size")
+    check(lib().sf_grad_hessian_ema(_p(g), _p(grad_ema), _dt(g), _p(H), g.numel(), float(beta), _stream()),
+          "sf_grad_hessian_ema")
+
+
 def mask_update_nm24_from_weight(W, H, norm, mask, stats, wm, meta, *, metric="hessian_obd", tau=None, temperature=1.0,
                                  mask_lr=0.1, pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0,
                                  hx=1.0, structured_exact=False) -> None:

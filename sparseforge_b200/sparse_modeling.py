@@ -606,7 +606,11 @@ class SparseLinear(nn.Linear):
     def forward(self, x):
         """legacy/sparse_modeling.py:737-796."""
         if self.mode == "sparse24_forward":
-            return self._sparse24_forward(x)
+            out = self._sparse24_forward(x)
+            if self.SLoRB and hasattr(self, "x_proj"):
+                # the low-rank bypass stays on at inference (legacy/eval_wiki_ppl.py:560-575, 623)
+                out = out + self._slorb(x)
+            return out
         if self.mode == "dense_forward" or self.mask_type == "none":
             ones = torch.ones_like(self.mask.data)
             return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)
@@ -670,9 +674,14 @@ class SparseLinear(nn.Linear):
                 return
             g = g.view_as(self.grad_ema)
         b = float(self.cfg.beta)
-        self.grad_ema.mul_(b).add_(g, alpha=1 - b)
-        if update_hessian_with_grad2 and not self._is_placeholder("hessian_diag"):
-            self.hessian_diag.mul_(b).add_((g * g).float(), alpha=1 - b)
+        with_h = update_hessian_with_grad2 and not self._is_placeholder("hessian_diag") and self.hessian_diag.shape == g.shape
+        if g.numel() % 8 == 0 and g.dtype == self.grad_ema.dtype and g.is_contiguous():
+            ops.grad_hessian_ema(g, self.grad_ema.data, self.hessian_diag.data if with_h else None, beta=b)
+        else:  # sizes the 8-wide kernel does not take (never a SparseLinear weight with in_features % 8 == 0)
+            self.grad_ema.mul_(b).add_(g.to(self.grad_ema.dtype), alpha=1 - b)
+            if with_h:
+                self.hessian_diag.mul_(b).add_((g * g).float(), alpha=1 - b)
+        self._score_key = None  # the kernel wrote grad_ema / H behind autograd's version counters
 
     def update_importance_ema(self):
         pass
@@ -767,25 +776,31 @@ class SparseLinear(nn.Linear):
             ops.wanda_score(self.weight.data, self.scaler_row.data, self._score, self._norm, self._scratch)
             self._combine_shard_norm()
             return
+        aux_scalar = float(self.cfg.temperature)
         if metric == "movement":
-            if self._is_placeholder("grad_ema"):
-                metric = "magnitude"
-            else:
-                aux = self.grad_ema.data
+            aux = self.grad_ema.data
+        elif metric == "weight_sq":
+            # W * W in the weight dtype: the movement formula |W * aux| / 1 with aux = W
+            metric, aux, aux_scalar = "movement", self.weight.data, 1.0
         ops.hutch_score(self.weight.data, H, self._score, self._norm, self._scratch, aux=aux,
-                        aux_scalar=float(self.cfg.temperature), metric=metric)
+                        aux_scalar=aux_scalar, metric=metric)
         self._combine_shard_norm()
 
     def _resolved_metric(self):
-        """(metric, H) the score is computed with: metrics that lack their tensor fall back to the
-        magnitude, as the reference does (legacy/sparse_modeling.py:1041-1079)."""
+        """(metric, H) the score is computed with. A metric that lacks its tensor falls back as the
+        reference does (legacy/sparse_modeling.py:1041-1079): to |W|, except ``hessian_obd`` without a
+        Hessian tensor, which scores W * W ("weight_sq")."""
         metric = self.mask_metric
         if metric not in _SUPPORTED_METRICS:
             metric = "magnitude"
         H = None if self._is_placeholder("hessian_diag") else self.hessian_diag.data
-        if H is None and metric in ("hessian_obd", "hessian_ratio", "hessian"):
+        if H is None and metric == "hessian_obd":
+            metric = "weight_sq"
+        elif H is None and metric in ("hessian_ratio", "hessian"):
             metric = "magnitude"
         if metric == "wanda" and self._is_placeholder("scaler_row"):
+            metric = "magnitude"
+        if metric == "movement" and self._is_placeholder("grad_ema"):
             metric = "magnitude"
         return metric, H
 
@@ -800,7 +815,7 @@ class SparseLinear(nn.Linear):
         if not (self.fuse_score_with_optimizer and self._fuse_score_next and self.change_mask):
             return None
         metric, H = self._resolved_metric()
-        if metric in ("movement", "wanda") or self.mode != "sparse_forward":
+        if metric in ("movement", "wanda", "weight_sq") or self.mode != "sparse_forward":
             return None
         self._check_2to4()
         self._buffers_ready()
@@ -830,7 +845,7 @@ class SparseLinear(nn.Linear):
 
     def _score_is_bf16(self) -> bool:
         # the reference's score has dtype promote(weight, hessian): bf16 only when no fp32 Hessian enters
-        return self.weight.dtype == torch.bfloat16 and self.mask_metric in ("magnitude", "movement")
+        return self.weight.dtype == torch.bfloat16 and self._resolved_metric()[0] in ("magnitude", "movement", "weight_sq")
 
     @torch.no_grad()
     def compute_gate_target(self, step: int) -> torch.Tensor:

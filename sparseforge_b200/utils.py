@@ -3,8 +3,8 @@
 Host-side mirror of the functions the reference training loop imports from ``legacy/utils.py``
 (``legacy/main_llama.py:32-50``) that belong to the SparseLinear hot path. Each walks the model's
 ``SparseLinear`` modules and calls their kernels; layer-wide scalars stay on the device until the
-caller reads them. Evaluation, calibration and logging helpers of that file are not part of this
-path.
+caller reads them. The perplexity evaluators of that file are outside this path: their names
+exist here so that the training script's import list resolves, and raise when called.
 """
 from __future__ import annotations
 
@@ -480,3 +480,49 @@ def optimize_sparse_model_for_inference(model, use_slorb: bool = False, compress
         m.invalidate_masked_weight()
         optimized += 1
     return model
+
+
+@torch.no_grad()
+def add_calibration(model, nsamples=128, device="cuda", calib_source="c4", synthetic_cache_path=None, dataloader=None):
+    """WANDA calibration driver (legacy/utils.py:1989-2060): ``scaler_row`` of every SparseLinear
+    starts at one, then ``nsamples`` calibration batches run through the model while a forward hook
+    on each layer folds its input into ``scaler_row`` (``SparseLinear.add_batch``).
+
+    The reference reads its batches from a pickled C4 (or synthetic) calibration set beside the
+    script and walks ``model.transformer.h`` layer by layer; that data set is not part of this
+    package. Pass ``dataloader``: an iterable whose items are the model's positional input (a tensor)
+    or a tuple / list of positional inputs; the first ``nsamples`` items are used, each in one
+    forward pass of the whole model. Without it the call raises."""
+    raw = get_raw_model(model)
+    mods = [m for m in _sparse_modules(raw) if not m._is_placeholder("scaler_row")]
+    if dataloader is None:
+        raise FileNotFoundError(
+            f"add_calibration(calib_source={calib_source!r}): the pickled calibration set of the reference "
+            "(data/c4_dataset/calibration_dataset.pkl, legacy/utils.py:2034) is not shipped with this package; "
+            "pass dataloader=<iterable of model inputs>")
+    for m in mods:
+        m.scaler_row.data.fill_(1.0)
+        m._score_key = None
+    handles = [m.register_forward_hook(lambda mod, inp, out: mod.add_batch(inp[0].data, out.data)) for m in mods]
+    try:
+        for j, batch in enumerate(dataloader):
+            if j >= int(nsamples):
+                break
+            args = batch if isinstance(batch, (tuple, list)) else (batch,)
+            raw(*[a.to(device) if torch.is_tensor(a) else a for a in args])
+    finally:
+        for h in handles:
+            h.remove()
+
+
+def eval_ppl(model, bs=2, device="cuda:0", block_size=1024, model_name_or_path=None):
+    """Name kept for ``from utils import eval_ppl`` (legacy/main_llama.py:32-50). WikiText-2 perplexity
+    evaluation (legacy/utils.py:1284-1530) needs the data set and a tokenizer and is outside this package."""
+    raise NotImplementedError("eval_ppl: perplexity evaluation (legacy/utils.py:1284-1530) is outside this package; "
+                              "it covers the SparseLinear hot path only")
+
+
+def eval_ppl_distributed(model, bs=2, device="cuda:0", block_size=1024, model_name_or_path=None, ptdtype=None):
+    """Name kept for ``from utils import eval_ppl_distributed``; see ``eval_ppl``."""
+    raise NotImplementedError("eval_ppl_distributed: perplexity evaluation (legacy/utils.py:1533-1980) is outside "
+                              "this package; it covers the SparseLinear hot path only")

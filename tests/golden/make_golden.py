@@ -710,6 +710,47 @@ def case_c1():
     save("c1", d)
 
 
+def case_movement():
+    """mask_metric='movement': update_grad_hessian_ema (legacy/sparse_modeling.py:901-922) fed by real
+    backward passes, AdamW, and mask updates scored by |W * grad_ema| / temperature. A second layer is
+    built with ``enable_hutchinson`` set on its config so that the g^2 branch into hessian_diag runs."""
+    d = {}
+    for tag, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        torch.manual_seed(41)
+        out_f, in_f = 48, 64
+        W = torch.randn(out_f, in_f) * 0.05
+        kw = dict(mask_type="structured", mask_metric="movement", N=2, M=4, mask_update_period=1, sparsity_warmup_steps=0,
+                  mask_lr=0.2, beta=0.9, temperature=0.7, temp_init=1.0, temp_decay=0.8, mask_hardening_start=2,
+                  mask_hardening_duration=4)
+        cfg = ref_sm.SparseLinearConfig(**kw)
+        cfg.enable_hutchinson = True  # hessian_diag becomes a full tensor, fed by g^2
+        layer = ref_sm.SparseLinear(in_f, out_f, sparselinear_config=cfg, bias=False).to(dtype)
+        layer.weight.data.copy_(W.to(dtype))
+        layer.initialize()
+        layer.mask.data = layer.mask.data.float()
+        layer.hessian_diag.data = layer.hessian_diag.data.float()
+        layer.sync_weight()
+        opt = ref_adamw.AdamW([layer.weight], lr=1e-3, betas=(0.9, 0.95), weight_decay=0.1)
+        put(d, f"{tag}_W0", layer.weight.data)
+        X = torch.randn(3, 10, in_f).to(dtype)
+        put(d, f"{tag}_X", X)
+        for t in range(3):
+            dY = torch.randn(3, 10, out_f).to(dtype)
+            put(d, f"{tag}_dY{t}", dY)
+            layer.weight.grad = None
+            layer(X).backward(dY)
+            put(d, f"{tag}_g{t}", layer.weight.grad)
+            ref_utils.update_model_grad_ema(layer, update_hessian_with_grad2=True)
+            put(d, f"{tag}_ema{t}", layer.grad_ema.data); put(d, f"{tag}_H{t}", layer.hessian_diag.data)
+            opt.step(decay=1e-4)
+            put(d, f"{tag}_W{t + 1}", layer.weight.data)
+            put(d, f"{tag}_G{t}", layer.compute_gate_target(t))
+            ref_utils.calculate_model_mask(layer, step=t, lambda_mid=0.0)
+            put(d, f"{tag}_mask{t + 1}", layer.mask.data); put(d, f"{tag}_hx{t}", float(layer.hardening_x))
+            put(d, f"{tag}_flips{t}", int(layer.weight.flipped_mask))
+    save("movement", d)
+
+
 if __name__ == "__main__":
     # `make_golden.py wanda ...` regenerates only the named single-function cases
     only = [a for a in sys.argv[1:] if not a.startswith("-")]
@@ -741,6 +782,7 @@ if __name__ == "__main__":
     case_slorb()
     case_block_masks()
     case_c1()
+    case_movement()
     case_wanda()
     case_freeze()
     case_penalty()

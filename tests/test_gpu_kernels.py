@@ -504,6 +504,53 @@ def test_wanda_metric_follows_the_reference(ops, tag, tol):
         layer.invalidate_masked_weight()
 
 
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_movement_metric_and_grad_ema_follow_the_reference(ops, tag, tol):
+    """update_model_grad_ema (one fused pass: gradient EMA + g^2 into H) and the movement score against
+    the reference's trajectory (tests/golden/movement.npz)."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    g = Golden("movement")
+    W0 = g[f"{tag}_W0"]
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="movement", N=2, M=4, mask_update_period=1,
+                                sparsity_warmup_steps=0, mask_lr=0.2, beta=0.9, temperature=0.7, temp_init=1.0,
+                                temp_decay=0.8, mask_hardening_start=2, mask_hardening_duration=4)
+    cfg.enable_hutchinson = True
+    layer = sf.SparseLinear(W0.shape[1], W0.shape[0], sparselinear_config=cfg, bias=False).to(DEV).to(W0.dtype)
+    layer.weight.data.copy_(W0.to(DEV))
+    layer.initialize()
+    assert not layer._is_placeholder("grad_ema") and not layer._is_placeholder("hessian_diag")
+    for t in range(3):
+        layer.weight.grad = dev(g[f"{tag}_g{t}"])
+        U.update_model_grad_ema(layer, update_hessian_with_grad2=True)
+        assert rel_err(layer.grad_ema.data.float(), g[f"{tag}_ema{t}"].float()) <= tol
+        assert rel_err(layer.hessian_diag.data, g[f"{tag}_H{t}"]) <= (F32_TOL if tag == "f32" else tol)
+        if tag == "f32":
+            assert torch.equal(layer.grad_ema.data.cpu(), g[f"{tag}_ema{t}"])  # same roundings as ATen
+        layer.grad_ema.data.copy_(g[f"{tag}_ema{t}"].to(DEV))
+        layer.weight.data.copy_(g[f"{tag}_W{t + 1}"].to(DEV))
+        layer.invalidate_masked_weight()
+        assert rel_err(layer.compute_gate_target(t).float(), g[f"{tag}_G{t}"].float()) <= tol
+        prev = layer.mask.data.clone().cpu()
+        U.calculate_model_mask(layer, step=t, lambda_mid=0.0)
+        assert rel_err(layer.mask.data, g[f"{tag}_mask{t + 1}"]) <= tol
+        assert layer.hardening_x == pytest.approx(g.scalar(f"{tag}_hx{t}"))
+        assert int(layer.weight.flipped_mask) == O.flip_count(prev, layer.mask.data.cpu())
+        layer.mask.data.copy_(g[f"{tag}_mask{t + 1}"].to(DEV))
+        layer.invalidate_masked_weight()
+    # a layer without a Hessian tensor only keeps the gradient EMA; other metrics return early
+    plain = sf.SparseLinear(64, 48, sparselinear_config=sf.SparseLinearConfig(mask_metric="movement"), bias=False).to(DEV)
+    plain.weight.grad = torch.ones_like(plain.weight)
+    plain.update_grad_hessian_ema()
+    assert float(plain.grad_ema.data.min()) == pytest.approx(0.01)
+    obd = sf.SparseLinear(64, 48, sparselinear_config=sf.SparseLinearConfig(mask_metric="hessian_obd"), bias=False).to(DEV)
+    obd.initialize()
+    obd.weight.grad = torch.ones_like(obd.weight)
+    obd.update_grad_hessian_ema()
+    assert float(obd.hessian_diag.data.min()) == 1.0  # the reference's early return: H keeps its initial value
+
+
 def test_wanda_kernels_at_layer_size(ops):
     """Column energy and score at a LLaMA-sized matrix against torch on the device (fp32 sums in
     another order: 1e-5), bf16 activations and weights."""

@@ -12,6 +12,7 @@ import pytest
 import torch
 
 from golden_io import Golden, rel_err
+from oracle import sparselinear_oracle as O
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
@@ -312,6 +313,57 @@ def test_slorb_bypass_follows_the_reference(tag, trainable):
         assert rel_err(layer.x_proj.grad, g[f"{tag}_dP"]) <= 1e-5
     else:
         assert layer.x_proj.grad is None
+
+
+def test_slorb_survives_compressed_inference():
+    """A layer with the low-rank bypass that is compressed to hard 2:4 keeps the bypass: its output
+    equals the masked dense path (binary mask) plus the bypass term (legacy/eval_wiki_ppl.py:560-575, 623
+    keeps such layers in sparse_forward because the bypass is needed at inference)."""
+    import sparseforge_b200 as sf
+
+    torch.manual_seed(17)
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, SLoRB=True, SLoRB_k=16,
+                                SLoRB_init_type="mean")
+    layer = sf.SparseLinear(256, 128, sparselinear_config=cfg, bias=True).to(DEV).to(torch.bfloat16)
+    layer.initialize()
+    layer.mask.data.copy_(torch.rand(128, 256, device=DEV))
+    layer.init_SLoRB()
+    assert float(layer.SLoRB_Weight.data.abs().max()) > 0
+    x = torch.randn(3, 40, 256, device=DEV).to(torch.bfloat16)
+    hard = layer._hard_mask_from_soft(layer.mask.data)
+    with torch.no_grad():
+        dense = torch.nn.functional.linear(x.float(), layer.weight.data.float() * hard, layer.bias.data.float())
+        bypass = (x.float() @ layer.x_proj.data.float().t()) @ layer.SLoRB_Weight.data.float().t()
+        layer.eval()
+        layer.compress_for_inference()
+        assert layer.mode == "sparse24_forward"
+        y = layer(x)
+    assert float(bypass.abs().max()) > 0.01 * float(dense.abs().max())  # the term is not negligible here
+    assert rel_err(y.float(), dense + bypass) <= 1e-2
+    assert rel_err(y.float(), dense) > 1e-2
+
+
+def test_add_calibration_runs_the_hooks():
+    """utils.add_calibration with a caller-supplied loader (legacy/utils.py:1989-2060): scaler_row starts
+    at one and every batch is folded in through SparseLinear.add_batch, as calling add_batch by hand does."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    torch.manual_seed(19)
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="wanda")
+    model = torch.nn.Sequential(sf.SparseLinear(64, 32, sparselinear_config=cfg, bias=False),
+                                sf.SparseLinear(32, 16, sparselinear_config=cfg, bias=False)).to(DEV)
+    for m in model:
+        m.initialize()
+    batches = [torch.randn(2, 5, 64) for _ in range(4)]
+    U.add_calibration(model, nsamples=3, device=DEV, dataloader=batches)
+    first = model[0]
+    assert first.nsamples == 6
+    want, ns = torch.ones(64), 0
+    for b in batches[:3]:
+        want, ns = O.wanda_add_batch(want, ns, b)
+    assert rel_err(first.scaler_row.data, want) <= 1e-5
+    assert model[1].nsamples == 6 and float(model[1].scaler_row.data.min()) > 0
 
 
 def test_score_fusion_with_the_optimizer_changes_nothing():

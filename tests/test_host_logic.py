@@ -145,3 +145,26 @@ def test_get_raw_model_unwraps():
     assert U.get_raw_model(Box(core, "student")) is core
     assert U.get_raw_model(Box(Box(core, "student"), "module")) is core
     assert math.isclose(U.update_mask_penalty_lr(core, 5, 10, 0.0, 1.0, "linear"), 0.5)
+
+
+def test_every_name_the_training_script_imports_exists():
+    """``from utils import (...)`` of legacy/main_llama.py:32-50 must resolve against this package, and so
+    must its imports from sparse_modeling and adamw; the evaluators raise a clear error when called."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import adamw, sparse_modeling
+    from sparseforge_b200 import utils as U
+
+    for name in ("calculate_model_mask", "calculate_flip_rate", "set_model_mode", "initialize_model", "add_calibration",
+                 "eval_ppl", "eval_ppl_distributed", "sync_weight", "update_model_grad_ema", "update_hessian_hutchinson",
+                 "mid_penalty", "harden_fraction", "log_mask_stats", "get_raw_model", "sparsity_penalty",
+                 "nm_2_4_tile_stats", "update_mask_penalty_lr"):
+        assert callable(getattr(U, name)), name
+    for name in ("Distill_Model", "SparseLinearConfig", "SparseLinear", "STE", "SRSTE", "FusedMaskedLinearSTE"):
+        assert hasattr(sparse_modeling, name), name
+    assert adamw.AdamW is sf.AdamW
+    with pytest.raises(NotImplementedError, match="outside this package"):
+        U.eval_ppl(torch.nn.Linear(2, 2))
+    with pytest.raises(NotImplementedError, match="outside this package"):
+        U.eval_ppl_distributed(torch.nn.Linear(2, 2))
+    with pytest.raises(FileNotFoundError, match="dataloader"):
+        U.add_calibration(torch.nn.Linear(2, 2))

@@ -501,3 +501,24 @@ def test_c1_full_size_chain():
     check("Y", res["Y"], rows_y, 1e-5, 1e-5)
     check("dX", res["dX"], rows_x, 1e-5, 1e-5)
     check("dW", res["dW"], rows_w, 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("tag,tol", [("f32", F32_TOL), ("bf16", BF16_TOL)])
+def test_movement_metric_and_grad_ema(tag, tol):
+    """Gradient EMA + g^2 Hessian proxy and the movement score against the reference's run
+    (tests/golden/movement.npz): the same ATen ops, so the EMA tensors are bit-identical."""
+    g = Golden("movement")
+    W0 = g[f"{tag}_W0"]
+    ema, H = torch.zeros_like(W0), torch.zeros(W0.shape)
+    mask = torch.ones(W0.shape)
+    for t in range(3):
+        ema, H = O.grad_hessian_ema(ema, H, g[f"{tag}_g{t}"], 0.9)
+        assert torch.equal(ema, g[f"{tag}_ema{t}"])
+        assert torch.equal(H, g[f"{tag}_H{t}"])
+        raw = O.importance_score(g[f"{tag}_W{t + 1}"], "movement", grad_ema=ema, temperature=0.7)
+        G = O.gate_target_structured(O.normalize_scores(raw), O.temperature_at(t, 1.0, 0.8, 0.05))
+        assert rel_err(G.float(), g[f"{tag}_G{t}"].float()) <= tol
+        new_mask = O.mask_update(mask, g[f"{tag}_G{t}"].float(), mask_lr=0.2)
+        assert rel_err(new_mask, g[f"{tag}_mask{t + 1}"]) <= F32_TOL
+        assert O.flip_count(mask, g[f"{tag}_mask{t + 1}"]) == g.scalar(f"{tag}_flips{t}")
+        mask = g[f"{tag}_mask{t + 1}"].clone()
