@@ -127,3 +127,40 @@ def check(rc: int, what: str = "") -> None:
     if rc != 0:
         msg = lib().sf_last_error_string()
         raise RuntimeError(f"sparseforge_b200 {what} failed ({rc}): {msg.decode() if msg else ''}")
+
+
+class PreparedCall:
+    """One library call whose arguments were converted to ctypes once.
+
+    A training step issues the same calls on the same buffers thousands of times; converting two dozen
+    Python numbers per call costs more host time than the launch itself. ``prepare(name, *values)``
+    wraps every value in the ctypes type of the symbol's signature. A value that is already a ctypes
+    instance is kept as is: such a *cell* (``ctypes.c_double()``, ``ctypes.c_void_p()``, ...) can be
+    given a new ``.value`` between calls (step count, temperature, an input pointer). Calling the
+    object issues the call and raises ``RuntimeError`` with the library's message on a non-zero code.
+    The caller keeps the tensors behind the pointers alive."""
+
+    __slots__ = ("name", "fn", "args")
+
+    def __init__(self, name, fn, args):
+        self.name, self.fn, self.args = name, fn, args
+
+    def __call__(self):
+        rc = self.fn(*self.args)
+        if rc != 0:
+            check(rc, self.name)
+
+
+def prepare(name: str, *values) -> PreparedCall:
+    res, argtypes = _SIGNATURES[name]
+    if len(values) != len(argtypes):
+        raise TypeError(f"{name}: {len(argtypes)} arguments expected, got {len(values)}")
+    args = []
+    for v, t in zip(values, argtypes):
+        if isinstance(v, ctypes._SimpleCData) or isinstance(v, ctypes.Array):
+            args.append(v)
+        elif v is None:
+            args.append(t())  # a null pointer
+        else:
+            args.append(t(v))
+    return PreparedCall(name, getattr(lib(), name), tuple(args))

@@ -20,6 +20,7 @@
 
 #include <cstdlib>
 #include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "ptx_sm100.cuh"
@@ -643,10 +644,50 @@ static EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Encoded tensor maps are kept in a small process-wide table keyed by what they were encoded from
+// (address, extents, leading dimension, box, kind): a training step launches the same products on the
+// same buffers over and over, and a lookup is cheaper than the driver call. The table owns nothing: an
+// entry is only a function of its key, so a buffer that was freed and reallocated at the same address
+// with the same shape gets an identical map. It is emptied when it reaches kMapCacheMax entries.
+struct MapKey {
+    const void* ptr;
+    int64_t inner, outer, ld;
+    int box, kind;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && inner == o.inner && outer == o.outer && ld == o.ld && box == o.box && kind == o.kind;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (uint64_t)k.inner * 0xC2B2AE3D27D4EB4Full + (uint64_t)k.outer * 0x165667B19E3779F9ull;
+        h ^= ((uint64_t)k.ld << 20) ^ ((uint64_t)k.box << 8) ^ (uint64_t)k.kind;
+        return (size_t)(h ^ (h >> 29));
+    }
+};
+constexpr size_t kMapCacheMax = 2048;
+static std::mutex g_map_mu;
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_map_cache;
+
+static bool map_cache_get(const MapKey& k, CUtensorMap* out) {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    auto it = g_map_cache.find(k);
+    if (it == g_map_cache.end()) return false;
+    *out = it->second;
+    return true;
+}
+static void map_cache_put(const MapKey& k, const CUtensorMap& m) {
+    std::lock_guard<std::mutex> lock(g_map_mu);
+    if (g_map_cache.size() >= kMapCacheMax) g_map_cache.clear();
+    g_map_cache[k] = m;
+}
+
 // Tensor map over a row-major bf16 matrix [outer, inner] with a 128-byte-swizzled box of
 // 64 inner elements x box_outer rows.
 int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64_t outer, int64_t ld,
                          int box_outer) {
+    const MapKey key{ptr, inner, outer, ld, box_outer, 0};
+    if (map_cache_get(key, map)) return SF_OK;
     if (int rc = ensure_context()) return rc;
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -658,12 +699,15 @@ int make_bf16_tensor_map(CUtensorMap* map, const void* ptr, int64_t inner, int64
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    map_cache_put(key, *map);
     return SF_OK;
 }
 
 // Tensor map over a byte matrix [rows, 16] (rows of 16 bytes, no swizzle) with a box of box_rows rows:
 // the tensor-core ordered 2:4 metadata, one 2048-byte tile = 128 such rows.
 int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int box_rows) {
+    const MapKey key{ptr, 16, rows, 16, box_rows, 1};
+    if (map_cache_get(key, map)) return SF_OK;
     if (int rc = ensure_context()) return rc;
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
@@ -675,6 +719,7 @@ int make_meta_tensor_map(CUtensorMap* map, const void* ptr, int64_t rows, int bo
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return fail(SF_ERR_CUDA, "cuTensorMapEncodeTiled (metadata) failed with CUresult %d", (int)r);
+    map_cache_put(key, *map);
     return SF_OK;
 }
 

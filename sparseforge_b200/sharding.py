@@ -197,7 +197,9 @@ class PeerArena:
         return [p + int(offset) for p in self._ptrs]
 
     def view(self, offset: int, shape, dtype) -> torch.Tensor:
-        n = int(torch.tensor(shape).prod()) * torch.empty((), dtype=dtype).element_size()
+        n = torch.empty((), dtype=dtype).element_size()
+        for d in shape:
+            n *= int(d)
         return self.buf[offset:offset + n].view(dtype).view(*shape)
 
     def barrier(self, async_op: bool = False):
@@ -207,11 +209,17 @@ class PeerArena:
         return dist.all_reduce(self._flag, group=self.group, async_op=async_op)
 
     def close(self):
+        """Unmaps the peers' buffers and drops this rank's own. Every rank must call it, with none of
+        its kernels in flight; the buffers are released even if the synchronisation in here fails, so
+        that a rank never exits while its memory is still bound to the multicast object."""
         from . import ops
 
-        torch.cuda.synchronize()
-        dist.barrier(group=self.group)
-        for b in self._bases:
-            ops.peer_close(b)
-        self._bases = []
-        self.mc_base, self._symm, self.buf = 0, None, None
+        try:
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group)
+        finally:
+            bases, self._bases = self._bases, []
+            self.mc_base, self._symm, self.buf = 0, None, None
+            for b in bases:
+                ops.peer_close(b)
+            torch.cuda.synchronize()

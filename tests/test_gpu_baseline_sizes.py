@@ -10,8 +10,11 @@ Bars. Integer outputs (hard masks, 2:4 metadata, flip counts) are exact function
 they are compared bit for bit on the same soft mask, and where the soft masks themselves differ in
 the last bits the number of differing hard entries is printed and must stay inside the groups whose
 2nd / 3rd soft values are closer than the float tolerance. Floats: every entry within
-rtol |reference| + atol with rtol 1e-5 (fp32) / 1e-2 (bf16); atol is stated at each check, as a
-fraction of the tensor's RMS.
+rtol |reference| + atol with rtol 1e-5 (fp32) / 1e-2 (bf16). atol is stated at each check as a fraction
+of the tensor's RMS: next to nothing for fp32 element-wise results, 1e-5 of the RMS for fp32 GEMM
+outputs (sums with cancellation), and 1e-2 of the RMS for tensors STORED in bf16, whose entries come
+out of a sum of two rounded terms (ATen rounds beta * m and the decayed gradient to bf16 before adding
+them; an entry where the two nearly cancel carries the rounding of the larger term).
 """
 import numpy as np
 import pytest
@@ -166,11 +169,11 @@ def test_c2_bench_pair_two_steps(shift):
                                norm=norm, scratch=scratch, metric="hessian_obd")
         B.assert_elementwise(H, want["H"], F32, 1e-12, f"step {it}: H")
         # bf16 state: one unit in the last place is 2^-8 = 0.4 % of the value
-        B.assert_elementwise(W.float(), want["W"].float(), BF16, 1e-3 * B.rms(want["W"].float()), f"step {it}: W")
-        B.assert_elementwise(m.float(), want["m"].float(), BF16, 1e-3 * B.rms(want["m"].float()), f"step {it}: exp_avg")
-        B.assert_elementwise(v.float(), want["v"].float(), BF16, 1e-3 * B.rms(want["v"].float()), f"step {it}: exp_avg_sq")
-        frac_exact = float((W.cpu() == want["W"]).float().mean())
-        print(f"[parity] step {it}: {100 * frac_exact:.3f} % of the bf16 weights equal the oracle's bit for bit")
+        B.assert_elementwise(W.float(), want["W"].float(), BF16, BF16 * B.rms(want["W"].float()), f"step {it}: W")
+        B.assert_elementwise(m.float(), want["m"].float(), BF16, BF16 * B.rms(want["m"].float()), f"step {it}: exp_avg")
+        B.assert_elementwise(v.float(), want["v"].float(), BF16, BF16 * B.rms(want["v"].float()), f"step {it}: exp_avg_sq")
+        n_w_diff = int((W.cpu() != want["W"]).sum())
+        print(f"[parity] step {it}: {n_w_diff} of {W.numel()} bf16 weights differ from the oracle's (by one unit in the last place)")
         # the score statistics belong to the weight the kernel itself produced: compare with the oracle's
         # statistics of that weight
         mu, sigma = O.score_norm_stats(O.importance_score(W.cpu(), "hessian_obd", H=H.cpu()))
@@ -196,17 +199,18 @@ def test_c2_bench_pair_two_steps(shift):
         total_diff += report_hard(f"bf16 q-projection step {it}", hard_own, O.hard_mask_from_soft(want_mask), want_mask,
                                   F32, 1e-7)
         want_wm = O.masked_weight(W.cpu(), O.effective_mask(mask_cpu, want["hx"]))
-        B.assert_elementwise(wm.float(), want_wm.float(), BF16, 1e-3 * B.rms(want_wm.float()), f"step {it}: masked weight")
+        B.assert_elementwise(wm.float(), want_wm.float(), BF16, BF16 * B.rms(want_wm.float()), f"step {it}: masked weight")
         ms = O.mask_stats(mask_cpu)
         assert abs(float(stats[_lib.MSTAT_SUM_M]) - ms["sum_m"]) <= 1e-6 * ms["sum_m"]
         assert abs(float(stats[_lib.MSTAT_SUM_M1M]) - ms["sum_m1m"]) <= 1e-6 * ms["sum_m1m"]
         assert float(stats[_lib.MSTAT_COUNT_LT_HALF]) == ms["count_lt_half"]
         # the oracle's free-running chain (its own W after its own AdamW): a weight that rounds to the
-        # neighbouring bf16 value moves that entry's score by 0.8 %, so a few entries differ visibly
+        # neighbouring bf16 value moves that entry's score by 0.8 % and, through the group threshold, the
+        # gate of the four entries of its group; nothing else may differ
         within, _ = B.elementwise_violations(mask, want["mask"], F32, 1e-7)
         print(f"[parity] step {it}: {within} of {mask.numel()} soft-mask entries differ from the free-running oracle "
               f"chain by more than 1e-5 (largest difference {float((mask.cpu() - want['mask']).abs().max()):.3g})")
-        assert within <= 1e-3 * mask.numel()
+        assert within <= 4 * n_w_diff
         # next step: both sides continue from the kernel's state
         st = {"W": W.cpu().clone(), "m": m.cpu().clone(), "v": v.cpu().clone(), "mask": mask_cpu.clone(), "H": H.cpu().clone()}
     print(f"[parity] bf16 q-projection, two steps: {total_diff} hard-mask entries differ in total")

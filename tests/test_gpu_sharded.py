@@ -87,22 +87,6 @@ def _worker(rank, world, port, q):
             ok = ok and rel(dx_mine, ops.gemm_dgrad(dyf, wfull)[rank * rows:(rank + 1) * rows]) <= 1e-2
         finally:
             arena.close()
-        # and the all-gather through the NVSwitch multicast address of a symmetric arena, where the
-        # node offers one (a failure here is reported, not raised: both ranks release the arena)
-        mc = PeerArena(y_bytes, dev)
-        try:
-            if mc.mc_base:
-                mc.buf.zero_()
-                mc.barrier()
-                ops.gemm_fwd_multicast(xs, wl, mc.mc_ptr(0), out2, rank * ol)
-                mc.barrier()
-                ok = ok and rel(mc.view(0, (Tt, out2), bf), ops.gemm_fwd(xs, wfull)) <= 1e-2
-                ok = ok and len(mc.ptrs(0)) == world and mc.ptrs(0)[rank] == mc.buf.data_ptr()
-        except Exception:
-            print(f"[rank {rank}] multicast arena: {traceback.format_exc()}", flush=True)
-            ok = False
-        finally:
-            mc.close()
         flips = torch.tensor([int(sharded.shard.weight.flipped_mask)], device=dev)
         dist.all_reduce(flips)
         ok = ok and abs(int(flips) - int(full.weight.flipped_mask)) <= 2
@@ -120,6 +104,83 @@ def _worker(rank, world, port, q):
         os._exit(1)  # leave without waiting on the peer
     finally:
         dist.destroy_process_group()
+
+
+def _multicast_worker(rank, world, port, q):
+    """The output all-gather through the NVSwitch multicast address of a symmetric-memory arena
+    (``multimem.st`` in the forward epilogue), in a process of its own. Whatever happens, a rank first
+    drops its symmetric buffer (``PeerArena.close`` releases it even when its own synchronisation
+    fails) and then leaves through a normal return: no rank exits while its memory is still bound to
+    the multicast object."""
+    import datetime
+    import traceback
+
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev, timeout=datetime.timedelta(seconds=60))
+    result, mc = "not run", None
+    try:
+        from sparseforge_b200 import ops
+        from sparseforge_b200.sharding import PeerArena
+
+        bf = torch.bfloat16
+        Tt, in2, out2 = 512, 256, 512
+        ol = out2 // world
+        xs = torch.randn(Tt, in2, generator=torch.Generator().manual_seed(5)).to(bf).to(dev)
+        wfull = (torch.randn(out2, in2, generator=torch.Generator().manual_seed(6)) * 0.05).to(bf).to(dev)
+        wl = wfull[rank * ol:(rank + 1) * ol].contiguous()
+        mc = PeerArena(Tt * out2 * 2, dev)
+        if not mc.mc_base:
+            result = "no multicast"  # the node offers no multicast object: the IPC arena is tested elsewhere
+        else:
+            mc.buf.zero_()
+            mc.barrier()
+            ops.gemm_fwd_multicast(xs, wl, mc.mc_ptr(0), out2, rank * ol)
+            mc.barrier()
+            got, want = mc.view(0, (Tt, out2), bf), ops.gemm_fwd(xs, wfull)
+            err = float((got.double() - want.double()).abs().max()) / float(want.double().abs().max())
+            same = len(mc.ptrs(0)) == world and mc.ptrs(0)[rank] == mc.buf.data_ptr()
+            result = True if (err <= 1e-2 and same) else f"multicast all-gather differs: {err}"
+            del got
+    except Exception:
+        result = traceback.format_exc()
+    finally:
+        try:
+            if mc is not None:
+                mc.close()
+        except Exception:
+            result = f"close failed after: {result}"
+    q.put((rank, result))
+    q.close()
+    q.join_thread()
+    try:
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_multicast_allgather_on_two_gpus():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_multicast_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=200)  # beyond the 60 s collective timeout, so that a failing rank has released its arena
+    for p in procs:
+        if p.is_alive():  # bounded: stop exactly the children this test started
+            p.kill()
+    results = {}
+    while not q.empty():
+        r, v = q.get(timeout=10)
+        results[r] = v
+    assert results in ({0: True, 1: True}, {0: "no multicast", 1: "no multicast"}), results
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
