@@ -194,6 +194,7 @@ def run_ours(args):
                           dYfull[mt.rows_total][:, rank * mt.rows:(rank + 1) * mt.rows].contiguous())
 
     main = torch.cuda.Stream(device=dev)   # tensor-core products
+    wgs = torch.cuda.Stream(device=dev)    # weight-gradient products, when they run beside the exchange kernels
     side = torch.cuda.Stream(device=dev)   # HBM-bound tail of a matrix (optimizer + score, mask update)
     xchg = torch.cuda.Stream(device=dev)   # rank barrier and slot sums of the exchange
     copy_stream = torch.cuda.Stream(device=dev)
@@ -232,6 +233,14 @@ def run_ours(args):
                 arena.close()
             arena, collective = None, "nccl"
     allgather = "none" if arena is None else "multimem" if arena.mc_base else "stores"
+    # From four GPUs on, the forward and input-gradient kernels wait on NVLink while the tensor cores idle:
+    # the weight-gradient product (no NVLink traffic) runs beside them on its own stream, each side limited
+    # to its share of the SMs. --wgrad-ctas sets the share of the weight gradient (0 = one stream).
+    wg_ctas = args.wgrad_ctas if args.wgrad_ctas >= 0 else ({4: 48, 8: 32}.get(world, 0) if arena is not None else 0)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    wg_ctas = max(0, min(wg_ctas, sms - 32)) // 2 * 2
+    ops.gemm_configure_stream(main, max_ctas=(sms - wg_ctas) if wg_ctas else 0)
+    ops.gemm_configure_stream(wgs, max_ctas=wg_ctas)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     rows_t = T // world
 
@@ -277,6 +286,8 @@ def run_ours(args):
             mt.reduce = [prepare("sf_reduce_slots", arena.buf.data_ptr() + s_off[(p, mt.index)], P(dxs[mt.index]), world,
                                  rows_t * mt.cols, BF, xchg.cuda_stream) for p in range(N_PARITY)]
         mt.wgrad = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status), ms)
+        mt.wgrad_beside = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status),
+                                  wgs.cuda_stream)
         # the reference's order: Hutchinson sample into H, optimizer step, score statistics of the NEW weight
         # (one pass over the matrix); the mask update forms the score again from W and H (it reads W anyway),
         # so the optimizer pass writes no score tensor
@@ -343,8 +354,11 @@ def run_ours(args):
                 x, dy = X[mt.cols], dYres[mt.name]
             mt.x_ptr.value, mt.dy_ptr.value = x.data_ptr(), dy.data_ptr()
             mt.bc1.value, mt.bc2.value, mt.temp.value, mt.hx.value = bc1, bc2, temp, hx
+            beside = wg_ctas > 0 and overlap and not e2e
             if overlap and tail_recorded[i]:
                 main.wait_event(tail_done[i])  # this step's products read the masked weight the last tail wrote
+                if beside:
+                    wgs.wait_event(tail_done[i])  # ... and the last tail read the weight gradient
 
             def timed(key, call, stream):
                 nonlocal launches
@@ -377,10 +391,15 @@ def run_ours(args):
                     with torch.cuda.stream(main):
                         dxo = torch.empty(rows_t, mt.cols, dtype=bf, device=dev)
                         nccl_work.append(dist.reduce_scatter_tensor(dxo, mt.dx, async_op=True))
-            timed("gemm:wgrad", mt.wgrad, main)
-            if overlap:
-                produced[i].record(main)
-                side.wait_event(produced[i])
+            if beside:
+                timed("gemm:wgrad", mt.wgrad_beside, wgs)
+                produced[i].record(wgs)
+                tail_stream.wait_event(produced[i])
+            else:
+                timed("gemm:wgrad", mt.wgrad, main)
+                if overlap:
+                    produced[i].record(main)
+                    side.wait_event(produced[i])
             timed("optim", mt.optim, tail_stream)
             launches += 1  # the one-block statistics kernel behind the score
             timed("mask", mt.mask_update, tail_stream)
@@ -413,6 +432,7 @@ def run_ours(args):
     def join_streams():
         main.wait_stream(side)
         main.wait_stream(xchg)
+        main.wait_stream(wgs)
 
     def barrier():
         if world > 1:
@@ -567,7 +587,8 @@ def run_ours(args):
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "collective": collective,
-                   "allgather": allgather, "overlap_hbm_passes": overlap,
+                   "allgather": allgather, "overlap_hbm_passes": overlap, "wgrad_beside_exchange_ctas": wg_ctas,
+                   "last_wave_cut_into_column_ranges": os.environ.get("SF_GEMM_TAIL_CUT", "1") != "0",
                    "rank_barriers_per_step": 0 if world == 1 else (1 if arena is not None else 0),
                    "l2": "inputs larger than L2 (each matrix pass touches >100 MB)",
                    "e2e_reads_back": "mask statistics (448 B); outputs and input gradients stay on the device"},
@@ -899,6 +920,9 @@ def main():
                          "NVLink and leave HBM idle; on one GPU the chip is power-capped and the overlap gains "
                          "0-4 %% while every kernel slows down)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    ap.add_argument("--wgrad-ctas", type=int, default=-1,
+                    help="thread blocks of the weight-gradient product when it runs on its own stream beside the forward "
+                         "and input-gradient kernels of the same matrix (0 = on the main stream; -1 = 48 at 4 GPUs, 32 at 8)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")
     ap.add_argument("--workload", default="tempering", choices=["tempering", "sparse24", "bsr16"],

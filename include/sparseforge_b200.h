@@ -414,6 +414,14 @@ SF_API int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t
                          int64_t out, int dtype, int32_t* status, void* stream);
 
 /*
+ * Per-stream setting of the bf16 tensor-core products above (and of the sharded variants below): an
+ * upper bound on the thread blocks of one launch on that stream (0 = all SMs, and forgets the stream),
+ * so that two products on two streams can share the chip. No counterpart in the reference, whose
+ * products are cuBLAS calls.
+ */
+SF_API int sf_masked_gemm_configure_stream(void* stream, int max_ctas);
+
+/*
  * Bias gradient: db[out] = sum_t dy[t, out].
  *   replaces: grad_out_2d.sum(dim=0), legacy/sparse_modeling.py:127-129.
  * db is fp32 and is overwritten.

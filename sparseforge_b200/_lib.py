@@ -56,6 +56,7 @@ _SIGNATURES = {
     "sf_masked_gemm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_float, c_int, _P, _P]),
     "sf_masked_gemm_dgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_wgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_masked_gemm_configure_stream": (c_int, [_P, c_int]),
     "sf_bias_grad": (c_int, [_P, c_int, _P, c_int64, c_int64, _P]),
     "sf_kl_div_fwd": (c_int, [_P, _P, c_int, c_int64, c_int64, c_double, c_double, _P, _P, _P]),
     "sf_kl_div_bwd": (c_int, [_P, _P, c_int, _P, _P, c_int64, c_int64, c_double, c_double, _P, _P]),

@@ -140,6 +140,35 @@ __device__ __forceinline__ int interleave_rows(int tm, int tiles_m, int G, int r
     return owner * (tiles_m / G) + tm / G;
 }
 
+// Work list of the CTA-pair kernel. Items below `full_items` are whole 256 x 256 output tiles, handed out
+// round robin. The tiles of the last, partly filled wave ("tail tiles") are cut into `parts` column
+// ranges of 256 / parts columns, one item each, so that every pair works during that wave too: a pair
+// then runs MMAs of shape 256 x (256 / parts) x 16 on the same A rows and a narrower slice of B. Every
+// output element is still the sum over K in the same order, so results do not depend on the cut.
+struct TailPlan {
+    int full_items;
+    int parts;  // 1 or 2 (the kernel also takes 4 with a K-major B operand)
+    int n_items;
+};
+struct WorkItem {
+    int tile;   // output tile in raster order
+    int col0;   // first column of the item inside the tile
+    int width;  // columns of the item: BN / parts for a tail item
+};
+__device__ __forceinline__ WorkItem work_item(int item, const TailPlan& tp) {
+    WorkItem w;
+    if (item < tp.full_items) {
+        w.tile = item; w.col0 = 0; w.width = 256;
+        return w;
+    }
+    const int u = item - tp.full_items;
+    const int t = u / tp.parts;
+    w.width = 256 / tp.parts;
+    w.col0 = (u - t * tp.parts) * w.width;
+    w.tile = tp.full_items + t;
+    return w;
+}
+
 struct GemmSmemTail {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
@@ -316,8 +345,55 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
 // released in both CTAs by multicast commits, `tmem_empty` of the leader collects the eight
 // epilogue warps of the pair.
 // ---------------------------------------------------------------------------------------
+// 64 columns of 32 rows (a thread holds one row, ra / rb its two 32-column halves) are packed to bf16
+// and turned in the warp's shared buffer: afterwards lane (rsub = lane / 8, piece = lane % 8) holds in
+// v[rg] the 16-byte piece `piece` of row rg * 4 + rsub, so that a warp store covers four rows x 128
+// contiguous bytes.
+__device__ __forceinline__ void dist_turn_chunk(uint8_t* ebuf, int lane, const uint32_t (&ra)[32], const uint32_t (&rb)[32],
+                                                int col0, float alpha, const __nv_bfloat16* __restrict__ bias, int N,
+                                                uint4 (&v)[8]) {
+    const int piece = lane & 7, rsub = lane >> 3;
+    uint4 pk[4];
+    pack_row_chunk(ra, col0, alpha, bias, N, pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + j * 16) = pk[j];
+    pack_row_chunk(rb, col0 + 32, alpha, bias, N, pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + (4 + j) * 16) = pk[j];
+    __syncwarp();
+#pragma unroll
+    for (int rg = 0; rg < 8; ++rg)
+        v[rg] = *reinterpret_cast<const uint4*>(ebuf + (rg * 4 + rsub) * DIST_EPI_ROW_BYTES + piece * 16);
+    __syncwarp();  // ebuf may be overwritten by the next chunk
+}
+
+// Stores the turned chunk (rows row0 ... row0 + 31, columns col0 ... col0 + 63 of the product) to where
+// the sharded epilogue sends it.
+template <int DIST>
+__device__ __forceinline__ void dist_store_chunk(const PeerOut& po, const uint4 (&v)[8], int lane, int row0, int col0, int M,
+                                                 int N) {
+    const int piece = lane & 7, rsub = lane >> 3;
+    const int col = col0 + piece * 8;
+#pragma unroll
+    for (int rg = 0; rg < 8; ++rg) {
+        const int orow = row0 + rg * 4 + rsub;
+        if (orow < M && col < N) {
+            if (DIST == DIST_SCATTER) {
+                const int owner = min(orow / po.rows_per, po.count - 1);
+                *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v[rg];
+            } else {
+                const int64_t off = (int64_t)orow * po.ld + po.col_off + col;
+                if (po.multicast) ptx::multimem_st_v4(po.ptr[0] + off, v[rg]);
+                else
+                    for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v[rg];
+            }
+        }
+    }
+}
+
 constexpr int PAIR_STAGES = 6;
-constexpr int PAIR_BNH = BN / 2;                       // B rows loaded by each CTA
+constexpr int PAIR_BNH = BN / 2;                       // B rows loaded by each CTA for a whole tile
+constexpr int PAIR_B_BOX = 32;                         // rows of one TMA box of a K-major B operand
 constexpr int PAIR_B_BYTES = PAIR_BNH * BK * 2;        // 16 KiB
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
@@ -335,7 +411,8 @@ template <int A_MN, int B_MN, int DIST = DIST_LOCAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
-                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po) {
+                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po,
+                      const __grid_constant__ TailPlan tp) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -380,12 +457,15 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        for (int item = pair; item < tp.n_items && ok; item += num_pairs) {
+            const WorkItem w = work_item(item, tp);
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(w.tile, tiles_m, tiles_n, tm, tn);
             if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
-            const int m0 = tm * 2 * BM + (int)cta * BM;       // this CTA's rows of A / D
-            const int n0 = tn * BN + (int)cta * PAIR_BNH;     // this CTA's half of the B rows
+            const int bn_cta = w.width / 2;                              // B rows this CTA loads
+            const int m0 = tm * 2 * BM + (int)cta * BM;                  // this CTA's rows of A / D
+            const int n0 = tn * BN + w.col0 + (int)cta * bn_cta;         // this CTA's half of the item's B rows
+            const uint32_t stage_tx = 2u * (uint32_t)(A_STAGE_BYTES + bn_cta * BK * 2);
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 31);
                 if (!ok) break;
@@ -394,7 +474,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     const uint32_t bar = ptx::map_to_cta(local_bar, 0);
                     const uint32_t sa = base + stage * PAIR_STAGE_BYTES, sb = sa + A_STAGE_BYTES;
                     const int k0 = kb * BK;
-                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * PAIR_STAGE_BYTES);
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, stage_tx);
                     if (A_MN) {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j) ptx::tma_load_2d_pair(sa + j * MN_BOX_BYTES, &tmA, bar, m0 + 64 * j, k0);
@@ -402,10 +482,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         ptx::tma_load_2d_pair(sa, &tmA, bar, k0, m0);
                     }
                     if (B_MN) {
-#pragma unroll
-                        for (int j = 0; j < PAIR_BNH / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
+                        // boxes of 64 (N) x 64 (K)
+                        for (int j = 0; j < bn_cta / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
                     } else {
-                        ptx::tma_load_2d_pair(sb, &tmB, bar, k0, n0);
+                        // boxes of 32 rows x 64 (K): 4 KiB each, whole swizzle atoms
+                        for (int j = 0; j < bn_cta / PAIR_B_BOX; ++j)
+                            ptx::tma_load_2d_pair(sb + j * (PAIR_B_BOX * BK * 2), &tmB, bar, k0, n0 + PAIR_B_BOX * j);
                     }
                 }
                 __syncwarp();
@@ -415,12 +497,16 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     } else if (warp == 1) {
         if (cta == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
+            constexpr uint32_t idesc256 = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
+            constexpr uint32_t idesc128 = ptx::make_idesc_bf16(2 * BM, BN / 2, A_MN, B_MN, 0);
+            constexpr uint32_t idesc64 = ptx::make_idesc_bf16(2 * BM, BN / 4, A_MN, B_MN, 0);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             int t = 0;
-            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+            for (int item = pair; item < tp.n_items && ok; item += num_pairs, ++t) {
+                const WorkItem w = work_item(item, tp);
+                const uint32_t idesc = w.width == 256 ? idesc256 : (w.width == 128 ? idesc128 : idesc64);
                 const int acc = t & 1;
                 const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 33);
@@ -457,11 +543,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t leader_empty1 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[1]), 0);
         bool ok = true;
         int t = 0;
-        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
+        for (int item = pair; item < tp.n_items && ok; item += num_pairs, ++t) {
+            const WorkItem w = work_item(item, tp);
             int tm, tn;
-            tile_coords(tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(w.tile, tiles_m, tiles_n, tm, tn);
             if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
-            const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN;
+            const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN + w.col0;
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 34);
@@ -472,7 +559,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (DIST == DIST_LOCAL) {
                 __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
 #pragma unroll 1
-                for (int c = 0; c < BN / 32; ++c) {
+                for (int c = 0; c < w.width / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
                     ptx::tmem_ld_wait();
@@ -483,7 +570,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 // shared memory first: a thread holds one row, a warp store then covers four rows
                 // x 128 contiguous bytes (8 lanes x 16 B per row) in every destination.
                 uint8_t* ebuf = base_ptr + PAIR_STAGES * PAIR_STAGE_BYTES + 256 + (warp - 2) * DIST_EPI_WARP_BYTES;
-                const int piece = lane & 7, rsub = lane >> 3;
                 // The accumulator reads of the next 64 columns are in flight while the stores of
                 // this chunk are issued; the accumulator is handed back to the MMA warp as soon as
                 // its last column has been read, before the last stores go out.
@@ -491,23 +577,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 ptx::tmem_ld_32x32b_x32(taddr, ra);
                 ptx::tmem_ld_32x32b_x32(taddr + 32u, rb);
                 ptx::tmem_ld_wait();
+                const int chunks = w.width / 64;
 #pragma unroll 1
-                for (int c = 0; c < BN / 64; ++c) {
-                    uint4 pk[4], v[8];
-                    pack_row_chunk(ra, n0 + c * 64, alpha, bias, N, pk);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + j * 16) = pk[j];
-                    pack_row_chunk(rb, n0 + c * 64 + 32, alpha, bias, N, pk);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *reinterpret_cast<uint4*>(ebuf + lane * DIST_EPI_ROW_BYTES + (4 + j) * 16) = pk[j];
-                    __syncwarp();
-#pragma unroll
-                    for (int rg = 0; rg < 8; ++rg)
-                        v[rg] = *reinterpret_cast<const uint4*>(ebuf + (rg * 4 + rsub) * DIST_EPI_ROW_BYTES + piece * 16);
-                    __syncwarp();  // ebuf may be overwritten by the next chunk
-                    if (c + 1 < BN / 64) {
+                for (int c = 0; c < chunks; ++c) {
+                    uint4 v[8];
+                    dist_turn_chunk(ebuf, lane, ra, rb, n0 + c * 64, alpha, bias, N, v);
+                    if (c + 1 < chunks) {
                         ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 64), ra);
                         ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 64 + 32), rb);
                     } else {
@@ -515,23 +590,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         __syncwarp();
                         if (lane == 0) ptx::mbar_arrive_cluster(acc ? leader_empty1 : leader_empty0);
                     }
-                    const int col = n0 + c * 64 + piece * 8;
-#pragma unroll
-                    for (int rg = 0; rg < 8; ++rg) {
-                        const int orow = m0 + q * 32 + rg * 4 + rsub;
-                        if (orow < M && col < N) {
-                            if (DIST == DIST_SCATTER) {
-                                const int owner = min(orow / po.rows_per, po.count - 1);
-                                *reinterpret_cast<uint4*>(po.ptr[owner] + (int64_t)(orow - owner * po.rows_per) * po.ld + col) = v[rg];
-                            } else {
-                                const int64_t off = (int64_t)orow * po.ld + po.col_off + col;
-                                if (po.multicast) ptx::multimem_st_v4(po.ptr[0] + off, v[rg]);
-                                else
-                                    for (int d = 0; d < po.count; ++d) *reinterpret_cast<uint4*>(po.ptr[d] + off) = v[rg];
-                            }
-                        }
-                    }
-                    if (c + 1 < BN / 64) ptx::tmem_ld_wait();
+                    dist_store_chunk<DIST>(po, v, lane, m0 + q * 32, n0 + c * 64, M, N);
+                    if (c + 1 < chunks) ptx::tmem_ld_wait();
                 }
             }
             if (DIST == DIST_LOCAL) {
@@ -735,6 +795,42 @@ static bool use_pair_kernel() {
     return v;
 }
 
+// Per-stream setting of the tensor-core products, registered by the caller with
+// sf_masked_gemm_configure_stream: a limit on the CTAs a launch may occupy, so that two products on two
+// streams can share the chip.
+static std::mutex g_cfg_mu;
+static std::unordered_map<void*, int> g_stream_max_ctas;
+
+static int stream_max_ctas(cudaStream_t st) {
+    std::lock_guard<std::mutex> lock(g_cfg_mu);
+    auto it = g_stream_max_ctas.find((void*)st);
+    return it == g_stream_max_ctas.end() ? 0 : it->second;
+}
+
+// Cutting the tiles of the last wave into column ranges is on unless SF_GEMM_TAIL_CUT=0 (A/B measurements).
+static bool tail_cut_enabled() {
+    static const bool v = [] {
+        const char* e = getenv("SF_GEMM_TAIL_CUT");
+        return !(e && e[0] == '0');
+    }();
+    return v;
+}
+
+// Whether the tiles of the last wave are cut into two column ranges of 128. A narrower MMA reads more
+// operand bytes per FLOP, and a wave that leaves SMs idle runs at a higher clock under the power cap, so
+// the cut is made only where it halves the wave: when at most half of the pairs would have a tile.
+// (Four ranges of 64 columns were measured slower than no cut at all and are not used.)
+static TailPlan plan_tail(int64_t ptiles, int pairs) {
+    TailPlan tp{(int)ptiles, 1, (int)ptiles};
+    if (pairs <= 0 || !tail_cut_enabled()) return tp;
+    const int rem = (int)(ptiles % pairs);
+    if (rem == 0 || 2 * rem > pairs) return tp;
+    tp.full_items = (int)(ptiles - rem);
+    tp.parts = 2;
+    tp.n_items = tp.full_items + rem * 2;
+    return tp;
+}
+
 template <int A_MN, int B_MN>
 static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldD,
                        const void* bias, float alpha, int64_t M, int64_t N, int64_t K, int32_t* status,
@@ -746,7 +842,7 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (rc) return rc;
     const bool pair = M > BM && use_pair_kernel();
     if (B_MN) rc = make_bf16_tensor_map(&tmB, B, N, K, ldb, 64);
-    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_BNH : BN);
+    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_B_BOX : BN);
     if (rc) return rc;
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
@@ -754,8 +850,11 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
         return fail(SF_ERR_UNSUPPORTED, "the sharded epilogue needs more than %d rows and the CTA-pair kernel", BM);
     if (pair) {
         const int64_t ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-        const int64_t max_pairs = sm_count() / 2;
-        const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
+        const int limit = stream_max_ctas(st);
+        int64_t max_pairs = sm_count() / 2;
+        if (limit >= 2 && limit / 2 < max_pairs) max_pairs = limit / 2;
+        const TailPlan tp = plan_tail(ptiles, (int)max_pairs);
+        const int pairs = (int)(tp.n_items < max_pairs ? tp.n_items : max_pairs);
         const PeerOut none = {};
 #define SF_LAUNCH_PAIR(DISTV, SLOT)                                                                              \
     do {                                                                                                         \
@@ -768,7 +867,7 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
         }                                                                                                        \
         pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD,                        \
                                                              (const __nv_bfloat16*)bias, alpha, (int)M, (int)N,  \
-                                                             (int)K, status, peers ? *peers : none);             \
+                                                             (int)K, status, peers ? *peers : none, tp);         \
     } while (0)
         if (dist == DIST_BROADCAST) SF_LAUNCH_PAIR(DIST_BROADCAST, 1);
         else if (dist == DIST_SCATTER) SF_LAUNCH_PAIR(DIST_SCATTER, 2);
@@ -853,6 +952,14 @@ int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int
     if (dtype == SF_F32)
         return launch_f32((const float*)dy, 1, out, (const float*)x, 1, in, (float*)dw, in, nullptr, 1.0f, out, in, T, st);
     return launch_bf16<1, 1>(dy, out, x, in, dw, in, nullptr, 1.0f, out, in, T, status, st);
+}
+
+int sf_masked_gemm_configure_stream(void* stream, int max_ctas) {
+    SF_CHECK_ARG(max_ctas >= 0, "sf_masked_gemm_configure_stream: max_ctas must be >= 0 (0 = no limit)");
+    std::lock_guard<std::mutex> lock(g_cfg_mu);
+    if (max_ctas == 0) g_stream_max_ctas.erase(stream);
+    else g_stream_max_ctas[stream] = max_ctas;
+    return SF_OK;
 }
 
 // The bounded wait every pipeline role of the GEMM kernels uses, exercised on a barrier that nobody

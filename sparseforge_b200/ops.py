@@ -369,6 +369,14 @@ def _gemm_dtype(*ts) -> int:
     return _dt(ts[0])
 
 
+def gemm_configure_stream(stream=None, *, max_ctas=0) -> None:
+    """Bounds the thread blocks of every bf16 tensor-core product launched on ``stream`` (the current
+    stream by default) to ``max_ctas``, so that two products on two streams can share the GPU; 0 lifts
+    the bound (``sf_masked_gemm_configure_stream``)."""
+    st = torch.cuda.current_stream() if stream is None else stream
+    check(lib().sf_masked_gemm_configure_stream(st.cuda_stream, int(max_ctas)), "sf_masked_gemm_configure_stream")
+
+
 def gemm_fwd(x2d, wm, bias=None, alpha=1.0, status=None):
     """y[T,out] = alpha * x2d[T,in] @ wm[out,in]^T (+ bias)."""
     _cuda(x2d, wm, bias, status)

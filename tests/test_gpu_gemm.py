@@ -67,6 +67,48 @@ def test_bf16_products(ops, T, k, n):
     assert rel_err(dw, rdw) <= BF16_TOL
 
 
+@pytest.mark.parametrize("T,k,n", [
+    (8192, 4096, 512),       # weight gradient of a 512-row shard: 32 tiles for 74 CTA pairs
+    (8192, 4096, 4096),      # 256 tiles: 3 full waves and 34 tail tiles
+    (2048, 1024, 4096),      # forward with 128 tiles (54 tail tiles: four column ranges each)
+    (1024, 4096, 520),       # ragged N: the last tile holds 8 columns
+    (8192, 4096, 1376),      # gate / up shard of an 8-way split
+    (1000, 264, 1064),       # ragged in every dimension
+])
+def test_bf16_products_with_the_last_wave_cut_into_column_ranges(ops, T, k, n, monkeypatch):
+    """The tiles of a launch's last, partly filled wave are cut into two or four column ranges so that
+    every SM works during that wave. Every output element is still summed over K in the same order, so
+    the results do not depend on the cut: launches limited to 2 and to 46 thread blocks (other tail waves,
+    other cuts) give the same bits, and all meet the fp64 products at the usual tolerance."""
+    torch.manual_seed(T + k + n + 1)
+    bf = torch.bfloat16
+    x = torch.randn(T, k, device=DEV).to(bf)
+    w = (torch.randn(n, k, device=DEV) * 0.02).to(bf)
+    dy = torch.randn(T, n, device=DEV).to(bf)
+    b = torch.randn(n, device=DEV).to(bf)
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+
+    def run():
+        return (ops.gemm_fwd(x, w, bias=b, alpha=0.75, status=status), ops.gemm_dgrad(dy, w, status=status),
+                ops.gemm_wgrad(dy, x, status=status))
+
+    try:
+        full = run()
+        # other CTA limits give other tail waves (other cuts, or none): the products may not change
+        ops.gemm_configure_stream(max_ctas=2)
+        one_pair = run()
+        ops.gemm_configure_stream(max_ctas=46)
+        some = run()
+    finally:
+        ops.gemm_configure_stream(max_ctas=0)
+    torch.cuda.synchronize()
+    check_status(status)
+    want = (0.75 * (x.float() @ w.float().t()) + b.float(), dy.float() @ w.float(), dy.float().t() @ x.float())
+    for got, a, c, ref in zip(full, one_pair, some, want):
+        assert rel_err(got, ref) <= BF16_TOL
+        assert torch.equal(got, a) and torch.equal(got, c)
+
+
 def test_bf16_bias_and_scale(ops):
     torch.manual_seed(0)
     x = torch.randn(200, 128, device=DEV).to(torch.bfloat16)
@@ -262,7 +304,7 @@ def test_paper_recipe_mask_path():
 
 
 @pytest.mark.parametrize("T,in_f,out_local,G", [(512, 192, 256, 2), (1024, 328, 136, 4), (2048, 264, 136, 4), (768, 64, 136, 2),
-                                                 (4096, 256, 1376, 8)])
+                                                 (4096, 256, 1376, 8), (1024, 4096, 512, 2), (1024, 512, 4096, 2)])
 def test_sharded_epilogues_on_one_gpu(ops, T, in_f, out_local, G):
     """The all-gather and reduce-scatter epilogues with every "rank" played in turn on one GPU: the
     destinations are ordinary buffers of this GPU, so only the addressing is under test."""
