@@ -194,6 +194,7 @@ def run_ours(args):
                           dYfull[mt.rows_total][:, rank * mt.rows:(rank + 1) * mt.rows].contiguous())
 
     main = torch.cuda.Stream(device=dev)   # tensor-core products
+    dgs = torch.cuda.Stream(device=dev)    # input-gradient products, when they have a stream of their own
     wgs = torch.cuda.Stream(device=dev)    # weight-gradient products, when they run beside the exchange kernels
     side = torch.cuda.Stream(device=dev)   # HBM-bound tail of a matrix (optimizer + score, mask update)
     xchg = torch.cuda.Stream(device=dev)   # rank barrier and slot sums of the exchange
@@ -233,19 +234,25 @@ def run_ours(args):
                 arena.close()
             arena, collective = None, "nccl"
     allgather = "none" if arena is None else "multimem" if arena.mc_base else "stores"
-    # From four GPUs on, the forward and input-gradient kernels wait on NVLink while the tensor cores idle:
-    # the weight-gradient product (no NVLink traffic) runs beside them on its own stream, each side limited
-    # to its share of the SMs. --wgrad-ctas sets the share of the weight gradient (0 = one stream).
-    wg_ctas = args.wgrad_ctas if args.wgrad_ctas >= 0 else ({4: 48, 8: 32}.get(world, 0) if arena is not None else 0)
+    # From four GPUs on, the forward and input-gradient kernels wait on NVLink while the tensor cores idle.
+    # The three products of a matrix are independent of one another, so each can have its own stream and a
+    # share of the SMs: --gemm-ctas f,d,w gives the thread blocks of forward, input gradient and weight
+    # gradient; a product with 0 runs on the forward's stream. Default: one stream up to two GPUs.
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    wg_ctas = max(0, min(wg_ctas, sms - 32)) // 2 * 2
-    ops.gemm_configure_stream(main, max_ctas=(sms - wg_ctas) if wg_ctas else 0)
-    ops.gemm_configure_stream(wgs, max_ctas=wg_ctas)
+    shares = args.gemm_ctas or ({4: "100,0,48", 8: "116,0,32"}.get(world, "0,0,0") if arena is not None else "0,0,0")
+    f_ctas, d_ctas, w_ctas = [max(0, int(v)) // 2 * 2 for v in shares.split(",")]
+    if not overlap:
+        d_ctas = w_ctas = 0
+    ops.gemm_configure_stream(main, max_ctas=f_ctas)
+    ops.gemm_configure_stream(dgs, max_ctas=d_ctas)
+    ops.gemm_configure_stream(wgs, max_ctas=w_ctas)
+    s_fwd, s_dgrad, s_wgrad = main, (dgs if d_ctas else main), (wgs if w_ctas else main)
     status = torch.zeros(4, dtype=torch.int32, device=dev)
     rows_t = T // world
 
     # ---- prepared calls -------------------------------------------------------------------------
     ms, ss = main.cuda_stream, tail_stream.cuda_stream
+    ds, ws_ = s_dgrad.cuda_stream, s_wgrad.cuda_stream
     # N = 1: one output buffer per shape (stream order keeps its uses apart); with library collectives every
     # matrix has its own, because a collective may still read the buffer when the next product starts
     own = world > 1 and arena is None
@@ -268,7 +275,7 @@ def run_ours(args):
             mt.fwd = prepare("sf_masked_gemm_fwd", mt.x_ptr, P(mt.wm), None, P(mt.y), T, mt.cols, mt.rows, 1.0, BF,
                              P(status), ms)
             mt.dgrad = prepare("sf_masked_gemm_dgrad", mt.dy_ptr, P(mt.wm), P(mt.dx), T, mt.cols, mt.rows, BF,
-                               P(status), ms)
+                               P(status), ds)
         else:
             if arena.mc_base:
                 mt.fwd = prepare("sf_masked_gemm_fwd_multicast", mt.x_ptr, P(mt.wm), None, y_cells[mt.index], T, mt.cols,
@@ -282,12 +289,10 @@ def run_ours(args):
                 slot_arrays[(p, mt.index)] = (ctypes.c_void_p * world)(
                     *arena.ptrs(s_off[(p, mt.index)] + rank * rows_t * mt.cols * 2))
             mt.dgrad = [prepare("sf_masked_gemm_dgrad_reducescatter", mt.dy_ptr, P(mt.wm), slot_arrays[(p, mt.index)], world,
-                                rank, T, mt.cols, mt.rows, BF, P(status), ms) for p in range(N_PARITY)]
+                                rank, T, mt.cols, mt.rows, BF, P(status), ds) for p in range(N_PARITY)]
             mt.reduce = [prepare("sf_reduce_slots", arena.buf.data_ptr() + s_off[(p, mt.index)], P(dxs[mt.index]), world,
                                  rows_t * mt.cols, BF, xchg.cuda_stream) for p in range(N_PARITY)]
-        mt.wgrad = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status), ms)
-        mt.wgrad_beside = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status),
-                                  wgs.cuda_stream)
+        mt.wgrad = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status), ws_)
         # the reference's order: Hutchinson sample into H, optimizer step, score statistics of the NEW weight
         # (one pass over the matrix); the mask update forms the score again from W and H (it reads W anyway),
         # so the optimizer pass writes no score tensor
@@ -326,10 +331,13 @@ def run_ours(args):
         return xs, dys, ready
 
     # events reused every step
-    produced = [torch.cuda.Event() for _ in mats]
+    prod_streams = list(dict.fromkeys([s_fwd, s_dgrad, s_wgrad]))
+    done_f = [torch.cuda.Event() for _ in mats]
+    done_d = [torch.cuda.Event() for _ in mats]
+    done_w = [torch.cuda.Event() for _ in mats]
     tail_done = [torch.cuda.Event() for _ in mats]
     tail_recorded = [False] * len(mats)
-    gemms_done = torch.cuda.Event()
+    stores_done = [torch.cuda.Event() for _ in prod_streams]
     barrier_done = [torch.cuda.Event() for _ in range(N_PARITY)]
     nccl_work = []
 
@@ -341,7 +349,8 @@ def run_ours(args):
         if arena is not None and it >= N_PARITY:
             # the landing buffers of this parity were last read by the slot sums of step it - 3; every
             # rank has finished those before it joined the barrier of step it - 2
-            main.wait_event(barrier_done[(it - 2) % N_PARITY])
+            for st in prod_streams:
+                st.wait_event(barrier_done[(it - 2) % N_PARITY])
         pending = prefetch(0, it) if e2e else None
         for i, mt in enumerate(mats):
             if e2e:
@@ -349,16 +358,17 @@ def run_ours(args):
                 # previous matrix computes; the next matrix's copy is queued before this one's kernels
                 x, dy, ready = pending
                 pending = prefetch(i + 1, it) if i + 1 < len(mats) else None
-                main.wait_event(ready)
+                for st in prod_streams:
+                    st.wait_event(ready)
             else:
                 x, dy = X[mt.cols], dYres[mt.name]
             mt.x_ptr.value, mt.dy_ptr.value = x.data_ptr(), dy.data_ptr()
             mt.bc1.value, mt.bc2.value, mt.temp.value, mt.hx.value = bc1, bc2, temp, hx
-            beside = wg_ctas > 0 and overlap and not e2e
             if overlap and tail_recorded[i]:
-                main.wait_event(tail_done[i])  # this step's products read the masked weight the last tail wrote
-                if beside:
-                    wgs.wait_event(tail_done[i])  # ... and the last tail read the weight gradient
+                # this step's products read the masked weight the last tail wrote, and overwrite the weight
+                # gradient it read
+                for st in prod_streams:
+                    st.wait_event(tail_done[i])
 
             def timed(key, call, stream):
                 nonlocal launches
@@ -373,33 +383,37 @@ def run_ours(args):
                     e.record(stream)
                 launches += 1
 
+            # the weight gradient first: it has the fewest thread blocks and then holds its SMs from the start
+            if s_wgrad is not main:
+                timed("gemm:wgrad", mt.wgrad, s_wgrad)
             if arena is not None:
                 if arena.mc_base:
                     y_cells[mt.index].value = arena.mc_ptr(y_off[(par, mt.index)])
-                    timed("gemm:fwd", mt.fwd, main)
+                    timed("gemm:fwd", mt.fwd, s_fwd)
                 else:
-                    timed("gemm:fwd", mt.fwd[par], main)
-                timed("gemm:dgrad", mt.dgrad[par], main)
+                    timed("gemm:fwd", mt.fwd[par], s_fwd)
+                timed("gemm:dgrad", mt.dgrad[par], s_dgrad)
             else:
-                timed("gemm:fwd", mt.fwd, main)
+                timed("gemm:fwd", mt.fwd, s_fwd)
                 if world > 1:  # library collectives on NCCL's own stream, beside the next products
                     with torch.cuda.stream(main):
                         yg = torch.empty(world, T, mt.rows, dtype=bf, device=dev)
                         nccl_work.append(dist.all_gather_into_tensor(yg, mt.y, async_op=True))
-                timed("gemm:dgrad", mt.dgrad, main)
+                timed("gemm:dgrad", mt.dgrad, s_dgrad)
                 if world > 1:
                     with torch.cuda.stream(main):
                         dxo = torch.empty(rows_t, mt.cols, dtype=bf, device=dev)
                         nccl_work.append(dist.reduce_scatter_tensor(dxo, mt.dx, async_op=True))
-            if beside:
-                timed("gemm:wgrad", mt.wgrad_beside, wgs)
-                produced[i].record(wgs)
-                tail_stream.wait_event(produced[i])
-            else:
-                timed("gemm:wgrad", mt.wgrad, main)
-                if overlap:
-                    produced[i].record(main)
-                    side.wait_event(produced[i])
+            if s_wgrad is main:
+                timed("gemm:wgrad", mt.wgrad, s_wgrad)
+            if overlap:
+                # the tail rewrites the masked weight (read by forward and input gradient) and reads the weight
+                # gradient: it starts when all three products of the matrix are done
+                done_f[i].record(s_fwd)
+                done_d[i].record(s_dgrad)
+                done_w[i].record(s_wgrad)
+                for ev in (done_f[i], done_d[i], done_w[i]):
+                    side.wait_event(ev)
             timed("optim", mt.optim, tail_stream)
             launches += 1  # the one-block statistics kernel behind the score
             timed("mask", mt.mask_update, tail_stream)
@@ -407,10 +421,14 @@ def run_ours(args):
                 tail_done[i].record(side)
                 tail_recorded[i] = True
             if e2e:
+                for st in prod_streams:
+                    if st is not main:
+                        main.wait_stream(st)
                 stage_free[i % 2].record(main)
         if arena is not None:
-            gemms_done.record(main)
-            xchg.wait_event(gemms_done)
+            for ev, st in zip(stores_done, prod_streams):
+                ev.record(st)
+                xchg.wait_event(ev)
             with torch.cuda.stream(xchg):
                 arena.barrier(async_op=True).wait()  # the exchange stream waits; the host does not
                 barrier_done[par].record(xchg)
@@ -421,18 +439,15 @@ def run_ours(args):
                 wk.wait()
         nccl_work.clear()
         if e2e:
-            if overlap:
-                main.wait_stream(side)
-            main.wait_stream(xchg)
+            join_streams()
             step_done[it % 2].record(main)
             with torch.cuda.stream(main):
                 return torch.stack([mt.stats for mt in mats]).to("cpu", non_blocking=False)
         return None
 
     def join_streams():
-        main.wait_stream(side)
-        main.wait_stream(xchg)
-        main.wait_stream(wgs)
+        for st in (side, xchg, dgs, wgs):
+            main.wait_stream(st)
 
     def barrier():
         if world > 1:
@@ -491,7 +506,7 @@ def run_ours(args):
             mt.x_ptr.value, mt.dy_ptr.value = x.data_ptr(), dy.data_ptr()
             arena.view(y_off[(par, mt.index)], (T, mt.rows_total), bf).zero_()
             arena.view(s_off[(par, mt.index)], (world, rows_t, mt.cols), bf).zero_()
-            main.synchronize()
+            torch.cuda.synchronize()
             dist.barrier()
             if arena.mc_base:
                 y_cells[mt.index].value = arena.mc_ptr(y_off[(par, mt.index)])
@@ -499,7 +514,7 @@ def run_ours(args):
             else:
                 mt.fwd[par]()
             mt.dgrad[par]()
-            main.synchronize()
+            torch.cuda.synchronize()
             dist.barrier()
             dx_mine = ops.reduce_slots(arena.view(s_off[(par, mt.index)], (world, rows_t, mt.cols), bf))
             y_all = arena.view(y_off[(par, mt.index)], (T, mt.rows_total), bf)
@@ -587,7 +602,7 @@ def run_ours(args):
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "collective": collective,
-                   "allgather": allgather, "overlap_hbm_passes": overlap, "wgrad_beside_exchange_ctas": wg_ctas,
+                   "allgather": allgather, "overlap_hbm_passes": overlap, "gemm_ctas_fwd_dgrad_wgrad": [f_ctas, d_ctas, w_ctas],
                    "last_wave_cut_into_column_ranges": os.environ.get("SF_GEMM_TAIL_CUT", "1") != "0",
                    "rank_barriers_per_step": 0 if world == 1 else (1 if arena is not None else 0),
                    "l2": "inputs larger than L2 (each matrix pass touches >100 MB)",
@@ -629,6 +644,10 @@ def run_ours(args):
                                      "max_rel_err_vs_unsharded": exchange_err}
     if world == 1 and not args.only:
         if not args.no_extras:
+            torch.cuda.synchronize()
+            out["passes"]["module_ms_per_step"] = round(module_path_ms(dev), 3)
+            out["passes"]["module_path"] = ("SparseLinear x 7 + utils.update_hessian_hutchinson (real double backward) + "
+                                            "AdamW.step(decay=) + utils.calculate_model_mask, 3 steps after 2 warm-up")
             out["sparse24"] = sparse24_cases(dev, rows_sweep=(1, 16, 128, 1024, 8192), iters=10, status=status)
             out["bsr16"] = bsr16_cases(dev, status=status)
         if not args.no_cpu_baseline:
@@ -636,6 +655,76 @@ def run_ours(args):
     print(json.dumps(out), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------
+# the module path: the same layer set driven through SparseLinear, the real Hutchinson step and AdamW
+# ---------------------------------------------------------------------------------------------
+def module_path_ms(dev, steps=3, warmup=2, shapes=SHAPES):
+    """One tempering step of the layer set through the package's module interface, in the order of the
+    reference's training loop (legacy/main_llama.py:1997-2211): forward of every SparseLinear, a loss with
+    curvature (sum gelu(y) * dy / T per layer), utils.update_hessian_hutchinson (the real double backward:
+    three more GEMM-shaped products per layer and a differentiable backward), loss.backward(),
+    AdamW.step(decay=), utils.calculate_model_mask. Returns milliseconds per step (CUDA events)."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import utils as U
+
+    bf = torch.bfloat16
+    T = T_TOKENS
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1,
+                                sparsity_warmup_steps=0, mask_lr=0.1, beta=0.99, temp_init=1.0, temp_min=0.05,
+                                temp_decay=0.05 ** (1.0 / 9.0), mask_hardening_start=1, mask_hardening_duration=9)
+    g = torch.Generator(device=dev).manual_seed(11)
+    layers = torch.nn.ModuleList()
+    for _, rows, cols in shapes:
+        layer = sf.SparseLinear(cols, rows, sparselinear_config=cfg, bias=False).to(dev).to(bf)
+        layer.weight.data.copy_((torch.randn(rows, cols, device=dev, generator=g) * 0.02).to(bf))
+        layer.initialize()
+        layers.append(layer)
+    opt = sf.AdamW([m.weight for m in layers], lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    widths = sorted({c for _, _, c in shapes})
+    X = {w: torch.randn(4, T // 4, w, device=dev, generator=g).to(bf) for w in widths}
+    dY = [torch.randn(4, T // 4, r, device=dev, generator=g).to(bf) for _, r, _ in shapes]
+
+    def one(it):
+        loss = None
+        for layer, dy in zip(layers, dY):
+            y = layer(X[layer.in_features])
+            term = (torch.nn.functional.gelu(y) * dy).float().sum() / T
+            loss = term if loss is None else loss + term
+        U.update_hessian_hutchinson(layers, loss)
+        loss.backward()
+        opt.step(decay=2e-4)
+        opt.zero_grad(set_to_none=True)
+        U.calculate_model_mask(layers, step=it % 10, lambda_mid=0.0)
+
+    for it in range(warmup):
+        one(it)
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for it in range(steps):
+        one(warmup + it)
+    e.record()
+    torch.cuda.synchronize()
+    ms = s.elapsed_time(e) / steps
+    del layers, opt, X, dY
+    torch.cuda.empty_cache()
+    return ms
+
+
+def run_module(args):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shapes = [s for s in SHAPES if (not args.only or s[0] in args.only.split(","))]
+    ms = module_path_ms(dev, steps=max(1, min(args.steps, 10)), warmup=2, shapes=shapes)
+    flops = sum(layer_flops(T_TOKENS, r, c) for _, r, c in shapes)
+    print(json.dumps({"metric": METRIC + ", module path with the real Hutchinson double backward", "unit": UNIT, "n_gpus": 1,
+                      "value": round(flops / (ms * 1e-3) / 1e12, 2), "ms_per_step": round(ms, 3), "dtype": "bf16",
+                      "data": "synthetic", "config": {"workload": "llama2-7b-layerset-tempering (module path)",
+                                                      "note": "value counts the forward + backward FLOPs of the training "
+                                                              "products only (6 T in out), as the headline does; the double "
+                                                              "backward runs about as many again"}}), flush=True)
 
 
 # ---------------------------------------------------------------------------------------------
@@ -920,12 +1009,14 @@ def main():
                          "NVLink and leave HBM idle; on one GPU the chip is power-capped and the overlap gains "
                          "0-4 %% while every kernel slows down)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
-    ap.add_argument("--wgrad-ctas", type=int, default=-1,
-                    help="thread blocks of the weight-gradient product when it runs on its own stream beside the forward "
-                         "and input-gradient kernels of the same matrix (0 = on the main stream; -1 = 48 at 4 GPUs, 32 at 8)")
+    ap.add_argument("--gemm-ctas", default="",
+                    help="f,d,w: thread blocks of the forward, input-gradient and weight-gradient products of a matrix; a "
+                         "product with a non-zero d or w runs on a stream of its own beside the forward (default: one "
+                         "stream up to two GPUs; 100,0,48 at four and 116,0,32 at eight, where the forward and input "
+                         "gradient wait on NVLink)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")
-    ap.add_argument("--workload", default="tempering", choices=["tempering", "sparse24", "bsr16"],
+    ap.add_argument("--workload", default="tempering", choices=["tempering", "sparse24", "bsr16", "module"],
                     help="tempering = the headline layer-set step; sparse24 = compressed inference GEMM sweep; "
                          "bsr16 = block-sparse-16 products")
     ap.add_argument("--rows", default="1,16,128,1024,8192", help="activation rows of the sparse24 sweep")
@@ -934,6 +1025,8 @@ def main():
         return run_sparse24(args)
     if args.workload == "bsr16":
         return run_bsr16(args)
+    if args.workload == "module":
+        return run_module(args)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         run_reference(args)
