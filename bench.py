@@ -239,7 +239,7 @@ def run_ours(args):
     # share of the SMs: --gemm-ctas f,d,w gives the thread blocks of forward, input gradient and weight
     # gradient; a product with 0 runs on the forward's stream. Default: one stream up to two GPUs.
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    shares = args.gemm_ctas or ({4: "100,0,48", 8: "116,0,32"}.get(world, "0,0,0") if arena is not None else "0,0,0")
+    shares = args.gemm_ctas or ({4: "100,0,48", 8: "100,0,48"}.get(world, "0,0,0") if arena is not None else "0,0,0")
     f_ctas, d_ctas, w_ctas = [max(0, int(v)) // 2 * 2 for v in shares.split(",")]
     if not overlap:
         d_ctas = w_ctas = 0
@@ -834,20 +834,25 @@ def bsr16_cases(dev, status, T=16384, density=0.5, iters=4):
         ws = torch.empty(out_f, in_f, dtype=bf, device=dev)
         useful = 2.0 * T * in_f * out_f * (col_idx.numel() / (ob * ib))
         row = {"shape": name, "tokens": T, "blocks_kept": int(col_idx.numel()), "density": round(col_idx.numel() / (ob * ib), 4)}
+        gws = torch.empty_like(ws)
+        ops.bsr16_fwd(x, blocks, row_ptr, col_idx, out_f, workspace=ws, status=status)  # leaves the scattered weight in ws
         for kind, fs, fd in (
-                ("fwd", lambda j: ops.bsr16_fwd(x, blocks, row_ptr, col_idx, out_f, workspace=ws, status=status),
+                ("fwd", lambda j: ops.bsr16_fwd(x, blocks, row_ptr, col_idx, out_f, workspace=ws, status=status, dense_ready=True),
                  lambda j: ops.gemm_fwd(x, wd, status=status)),
-                ("dgrad", lambda j: ops.bsr16_dgrad(dy, blocks, row_ptr, col_idx, in_f, workspace=ws, status=status),
+                ("fwd_with_scatter", lambda j: ops.bsr16_fwd(x, blocks, row_ptr, col_idx, out_f, workspace=ws, status=status),
+                 lambda j: ops.gemm_fwd(x, wd, status=status)),
+                ("dgrad", lambda j: ops.bsr16_dgrad(dy, blocks, row_ptr, col_idx, in_f, workspace=ws, status=status, dense_ready=True),
                  lambda j: ops.gemm_dgrad(dy, wd, status=status)),
-                ("wgrad", lambda j: ops.bsr16_wgrad(dy, x, row_ptr, col_idx, workspace=ws, status=status),
+                ("wgrad", lambda j: ops.bsr16_wgrad(dy, x, row_ptr, col_idx, workspace=gws, status=status),
                  lambda j: ops.gemm_wgrad(dy, x, status=status))):
             ts, td = time_pair(fs, fd, iters)
             row[kind] = {"us": round(ts * 1e3, 1), "dense_us": round(td * 1e3, 1), "speedup_vs_dense": round(td / ts, 3),
                          "useful_tflops": round(useful / ts / 1e9, 1), "dense_equiv_tflops": round(2.0 * T * in_f * out_f / ts / 1e9, 1)}
         cases.append(row)
-        del W, mask, wd, x, dy, ws, blocks
+        del W, mask, wd, x, dy, ws, gws, blocks
     return {"workload": "llama2-7b-mlp-block-sparse-16", "timing": f"CUDA graph of {iters} launches, block-sparse and dense "
-            "replayed alternately, median of three rounds", "cases": cases}
+            "replayed alternately, median of three rounds; fwd / dgrad with the scattered weight kept from the call before "
+            "(a layer whose blocks did not change), fwd_with_scatter rebuilds it", "cases": cases}
 
 
 def run_sparse24(args):
@@ -1012,8 +1017,8 @@ def main():
     ap.add_argument("--gemm-ctas", default="",
                     help="f,d,w: thread blocks of the forward, input-gradient and weight-gradient products of a matrix; a "
                          "product with a non-zero d or w runs on a stream of its own beside the forward (default: one "
-                         "stream up to two GPUs; 100,0,48 at four and 116,0,32 at eight, where the forward and input "
-                         "gradient wait on NVLink)")
+                         "stream up to two GPUs; 100,0,48 from four GPUs on, where the forward and input gradient wait "
+                         "on NVLink)")
     ap.add_argument("--only", default="", help="comma-separated matrix names (q,k,v,o,gate,up,down): a reduced "
                                                "workload for profiler captures; the JSON line then names it")
     ap.add_argument("--workload", default="tempering", choices=["tempering", "sparse24", "bsr16", "module"],

@@ -498,6 +498,17 @@ SF_API int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_
  */
 SF_API int sf_selftest_bounded_wait(double limit_ms, int32_t* status, void* stream);
 
+/*
+ * Issue-rate probe of the tensor cores (no counterpart in the reference): `ctas` thread blocks each
+ * issue `iters` tcgen05.mma of shape 128 x n x 16 (bf16, fp32 accumulation) back to back, the A
+ * operand read from shared memory (a_from_tmem = 0) or from tensor memory (1), and wait for them with a
+ * bounded wait; cycles[0] (device, one int64) receives the slowest block's SM cycles for the batch, so
+ * cycles[0] / iters is the cost of one MMA at that width. It is the measurement behind the choice to run
+ * block-sparse-16 products on the dense tiles: a 16-wide MMA costs as many cycles as a 64-wide one.
+ */
+SF_API int sf_selftest_mma_issue_rate(int n, int a_from_tmem, int iters, int ctas, long long* cycles,
+                                      int32_t* status, void* stream);
+
 SF_API int sf_peer_handle_bytes(void);
 SF_API int sf_peer_export(const void* ptr, void* handle, int64_t* offset);
 SF_API int sf_peer_open(const void* handle, int64_t offset, void** base, void** ptr);

@@ -38,20 +38,21 @@ def get_sparsity_info(block_row_indices: torch.Tensor, num_block_cols: int) -> d
 
 class _BlockSparseFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x2d, blocks, row_ptr, col_idx, bias, out_f, workspace):
+    def forward(ctx, x2d, blocks, row_ptr, col_idx, bias, out_f, workspace, grad_workspace, dense_ready):
         ctx.save_for_backward(x2d, blocks, row_ptr, col_idx)
-        ctx.workspace, ctx.has_bias = workspace, bias is not None
-        return ops.bsr16_fwd(x2d, blocks, row_ptr, col_idx, out_f, bias=bias, workspace=workspace)
+        ctx.workspace, ctx.grad_workspace, ctx.has_bias = workspace, grad_workspace, bias is not None
+        return ops.bsr16_fwd(x2d, blocks, row_ptr, col_idx, out_f, bias=bias, workspace=workspace, dense_ready=dense_ready)
 
     @staticmethod
     def backward(ctx, gy):
         x2d, blocks, row_ptr, col_idx = ctx.saved_tensors
         gy = gy.contiguous()
-        gx = ops.bsr16_dgrad(gy, blocks, row_ptr, col_idx, x2d.shape[1], workspace=ctx.workspace) \
+        # the forward left the scattered weight in the workspace; the weight gradient has a workspace of its own
+        gx = ops.bsr16_dgrad(gy, blocks, row_ptr, col_idx, x2d.shape[1], workspace=ctx.workspace, dense_ready=True) \
             if ctx.needs_input_grad[0] else None
-        gb = ops.bsr16_wgrad(gy, x2d, row_ptr, col_idx, workspace=ctx.workspace) if ctx.needs_input_grad[1] else None
+        gb = ops.bsr16_wgrad(gy, x2d, row_ptr, col_idx, workspace=ctx.grad_workspace) if ctx.needs_input_grad[1] else None
         gbias = ops.bias_grad(gy).to(gy.dtype) if (ctx.has_bias and ctx.needs_input_grad[4]) else None
-        return gx, gb, None, None, gbias, None, None
+        return gx, gb, None, None, gbias, None, None, None, None
 
 
 class BlockSparseLinear(nn.Module):
@@ -70,6 +71,12 @@ class BlockSparseLinear(nn.Module):
             self.bias = None
         self.sparsity_info = get_sparsity_info(block_row_indices, in_features // block_size)
         self._workspace = None
+        self._workspace_key = None
+        self._grad_workspace = None
+
+    def invalidate_workspace(self):
+        """Call after editing ``sparse_blocks`` through ``.data`` (an edit the version counter does not see)."""
+        self._workspace_key = None
 
     @classmethod
     def from_dense(cls, weight, mask, bias=None, block_size: int = 16):
@@ -88,9 +95,19 @@ class BlockSparseLinear(nn.Module):
         x2d = x.reshape(-1, self.in_features).to(self.sparse_blocks.dtype).contiguous()
         if self._workspace is None or self._workspace.device != x2d.device or self._workspace.dtype != x2d.dtype:
             self._workspace = torch.empty((self.out_features, self.in_features), dtype=x2d.dtype, device=x2d.device)
+            self._workspace_key = None
+        # the scattered weight is kept between calls and rebuilt only when the blocks have changed
+        key = (self.sparse_blocks.data_ptr(), self.sparse_blocks._version, self.block_col_indices.data_ptr())
+        ready = self._workspace_key == key
+        self._workspace_key = key
+        grad_ws = None
+        if torch.is_grad_enabled() and self.sparse_blocks.requires_grad:
+            if self._grad_workspace is None or self._grad_workspace.device != x2d.device:
+                self._grad_workspace = torch.empty_like(self._workspace)
+            grad_ws = self._grad_workspace
         bias = None if self.bias is None else self.bias.to(x2d.dtype)
         y = _BlockSparseFn.apply(x2d, self.sparse_blocks, self.block_row_indices, self.block_col_indices, bias,
-                                 self.out_features, self._workspace)
+                                 self.out_features, self._workspace, grad_ws, ready)
         return y.view(*shape[:-1], self.out_features)
 
     def extra_repr(self) -> str:

@@ -147,7 +147,7 @@ __device__ __forceinline__ int interleave_rows(int tm, int tiles_m, int G, int r
 // output element is still the sum over K in the same order, so results do not depend on the cut.
 struct TailPlan {
     int full_items;
-    int parts;  // 1 or 2 (the kernel also takes 4 with a K-major B operand)
+    int parts;  // 1 or 2
     int n_items;
 };
 struct WorkItem {
@@ -393,7 +393,6 @@ __device__ __forceinline__ void dist_store_chunk(const PeerOut& po, const uint4 
 
 constexpr int PAIR_STAGES = 6;
 constexpr int PAIR_BNH = BN / 2;                       // B rows loaded by each CTA for a whole tile
-constexpr int PAIR_B_BOX = 32;                         // rows of one TMA box of a K-major B operand
 constexpr int PAIR_B_BYTES = PAIR_BNH * BK * 2;        // 16 KiB
 constexpr int PAIR_STAGE_BYTES = A_STAGE_BYTES + PAIR_B_BYTES;
 constexpr int PAIR_SMEM_BYTES = PAIR_STAGES * PAIR_STAGE_BYTES + 1024 + 256;
@@ -410,6 +409,7 @@ struct PairSmemTail {
 template <int A_MN, int B_MN, int DIST = DIST_LOCAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                      const __grid_constant__ CUtensorMap tmBh,
                       __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
                       float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po,
                       const __grid_constant__ TailPlan tp) {
@@ -446,6 +446,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
+        ptx::prefetch_tensormap(&tmBh);
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -485,9 +486,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         // boxes of 64 (N) x 64 (K)
                         for (int j = 0; j < bn_cta / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
                     } else {
-                        // boxes of 32 rows x 64 (K): 4 KiB each, whole swizzle atoms
-                        for (int j = 0; j < bn_cta / PAIR_B_BOX; ++j)
-                            ptx::tma_load_2d_pair(sb + j * (PAIR_B_BOX * BK * 2), &tmB, bar, k0, n0 + PAIR_B_BOX * j);
+                        // one box: 128 rows x 64 (K) for a whole tile, 64 rows (the second tensor map) for a column range
+                        ptx::tma_load_2d_pair(sb, bn_cta == PAIR_BNH ? &tmB : &tmBh, bar, k0, n0);
                     }
                 }
                 __syncwarp();
@@ -499,14 +499,13 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (cta == 0) {
             constexpr uint32_t idesc256 = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
             constexpr uint32_t idesc128 = ptx::make_idesc_bf16(2 * BM, BN / 2, A_MN, B_MN, 0);
-            constexpr uint32_t idesc64 = ptx::make_idesc_bf16(2 * BM, BN / 4, A_MN, B_MN, 0);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             int t = 0;
             for (int item = pair; item < tp.n_items && ok; item += num_pairs, ++t) {
                 const WorkItem w = work_item(item, tp);
-                const uint32_t idesc = w.width == 256 ? idesc256 : (w.width == 128 ? idesc128 : idesc64);
+                const uint32_t idesc = w.width == 256 ? idesc256 : idesc128;
                 const int acc = t & 1;
                 const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 33);
@@ -842,8 +841,13 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (rc) return rc;
     const bool pair = M > BM && use_pair_kernel();
     if (B_MN) rc = make_bf16_tensor_map(&tmB, B, N, K, ldb, 64);
-    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_B_BOX : BN);
+    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_BNH : BN);
     if (rc) return rc;
+    CUtensorMap tmBh = tmB;  // K-major B of a column range of a tail tile: 64 rows per CTA
+    if (pair && !B_MN) {
+        rc = make_bf16_tensor_map(&tmBh, B, K, N, ldb, PAIR_BNH / 2);
+        if (rc) return rc;
+    }
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
     if (dist != DIST_LOCAL && !pair)
@@ -865,7 +869,7 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
             SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));    \
             pair_dev[SLOT] = dev;                                                                                \
         }                                                                                                        \
-        pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD,                        \
+        pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, tmBh, (__nv_bfloat16*)D, ldD,                  \
                                                              (const __nv_bfloat16*)bias, alpha, (int)M, (int)N,  \
                                                              (int)K, status, peers ? *peers : none, tp);         \
     } while (0)
@@ -978,6 +982,107 @@ __global__ void bounded_wait_selftest_kernel(long long limit_cycles, int32_t* st
     // two waiters: the first to run out sets the abort flag, the other leaves through it
     if (threadIdx.x == 0 || threadIdx.x == 32) ptx::mbar_wait_limit(ptx::smem_u32(&bar), 0, af, status, code, limit_cycles);
     __syncthreads();
+}
+
+// Issue-rate probe of the tensor cores: one CTA per SM issues `iters` MMAs of shape 128 x N x 16 (bf16,
+// fp32 accumulation) back to back from one thread, with precomputed descriptors and four accumulators in
+// turn, the A operand read from shared memory or from tensor memory, then commits once and waits (bounded).
+// The slowest CTA's cycle count goes to cycles[0]. Operand contents do not matter for the rate.
+__global__ void __launch_bounds__(128, 1)
+mma_issue_rate_kernel(int n, int a_from_tmem, int iters, long long* cycles, int32_t* status) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = ptx::smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t* bp = smem_raw + (base - raw);
+    constexpr int OPERAND_BYTES = 16384 + 32768;  // A tile 128 x 64, B tile 256 x 64
+    uint64_t* bar = reinterpret_cast<uint64_t*>(bp + OPERAND_BYTES);
+    uint32_t* tbase = reinterpret_cast<uint32_t*>(bp + OPERAND_BYTES + 64);
+    volatile int* abort_flag = reinterpret_cast<int*>(bp + OPERAND_BYTES + 128);
+    for (int i = threadIdx.x; i < OPERAND_BYTES / 4; i += blockDim.x) reinterpret_cast<uint32_t*>(bp)[i] = 0x3c003c00u;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_u32(bar), 1);
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+    }
+    const int warp = threadIdx.x >> 5;
+    if (warp == 0) {
+        ptx::tmem_alloc(ptx::smem_u32(tbase), 512);
+        ptx::tmem_relinquish();
+    }
+    ptx::fence_proxy_async();
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tm = *tbase;
+    if (threadIdx.x == 32) {
+        const uint32_t idesc = ptx::make_idesc_bf16(128, n, 0, 0, 0);
+        uint64_t ad[4], bd[4];
+        for (int k = 0; k < 4; ++k) {
+            ad[k] = ptx::make_smem_desc(base + k * 32, 16, 1024, 2);
+            bd[k] = ptx::make_smem_desc(base + 16384 + k * 32, 16, 1024, 2);
+        }
+        const uint32_t step = n <= 64 ? (uint32_t)n : 0u;  // four accumulators where they fit in 256 columns
+        const uint32_t ta = tm + 384u;
+        long long best = 1LL << 62;
+        for (int rep = 0; rep < 3; ++rep) {
+            const long long t0 = clock64();
+            // sixteen MMAs per trip, so that the loop itself does not bound the rate
+            if (a_from_tmem) {
+                for (int i = 0; i < iters; i += 16) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t acc = (i | u) ? 1u : 0u;
+                        ptx::mma_f16_ts(tm, ta, bd[0], idesc, acc);
+                        ptx::mma_f16_ts(tm + step, ta + 8u, bd[1], idesc, acc);
+                        ptx::mma_f16_ts(tm + 2 * step, ta + 16u, bd[2], idesc, acc);
+                        ptx::mma_f16_ts(tm + 3 * step, ta + 24u, bd[3], idesc, acc);
+                    }
+                }
+            } else {
+                for (int i = 0; i < iters; i += 16) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const uint32_t acc = (i | u) ? 1u : 0u;
+                        ptx::mma_f16_ss(tm, ad[0], bd[0], idesc, acc);
+                        ptx::mma_f16_ss(tm + step, ad[1], bd[1], idesc, acc);
+                        ptx::mma_f16_ss(tm + 2 * step, ad[2], bd[2], idesc, acc);
+                        ptx::mma_f16_ss(tm + 3 * step, ad[3], bd[3], idesc, acc);
+                    }
+                }
+            }
+            ptx::mma_commit(ptx::smem_u32(bar));
+            if (!ptx::mbar_wait(ptx::smem_u32(bar), (uint32_t)(rep & 1), abort_flag, status, 98)) break;
+            const long long t1 = clock64();
+            if (t1 - t0 < best) best = t1 - t0;
+        }
+        atomicMax(reinterpret_cast<unsigned long long*>(cycles), (unsigned long long)best);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tm, 512);
+    }
+}
+
+int sf_selftest_mma_issue_rate(int n, int a_from_tmem, int iters, int ctas, long long* cycles, int32_t* status, void* stream) {
+    SF_CHECK_ARG(cycles != nullptr && status != nullptr, "sf_selftest_mma_issue_rate: cycles and status must be non-null");
+    SF_CHECK_ARG(n >= 16 && n <= 256 && n % 16 == 0, "sf_selftest_mma_issue_rate: n must be a multiple of 16 in [16, 256]");
+    SF_CHECK_ARG(iters >= 16 && iters <= (1 << 20) && iters % 16 == 0, "sf_selftest_mma_issue_rate: iters must be a multiple of 16 in [16, 2^20]");
+    SF_CHECK_ARG(ctas >= 1 && ctas <= 1024, "sf_selftest_mma_issue_rate: ctas must be in [1, 1024]");
+    constexpr int SMEM = 16384 + 32768 + 1024 + 256;
+    static thread_local int configured_dev = -1;
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    if (configured_dev != dev) {
+        SF_CHECK_CUDA(cudaFuncSetAttribute(mma_issue_rate_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        configured_dev = dev;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    SF_CHECK_CUDA(cudaMemsetAsync(cycles, 0, sizeof(long long), st));
+    mma_issue_rate_kernel<<<ctas, 128, SMEM, st>>>(n, a_from_tmem, iters, cycles, status);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
 }
 
 static int fill_peers(const char* who, void* const* ptrs, int n_peers, PeerOut* po) {

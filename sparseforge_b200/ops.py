@@ -425,6 +425,19 @@ def gemm_wgrad(dy2d, x2d, status=None):
     return dw
 
 
+def mma_issue_cycles(n: int, *, a_from_tmem: bool = False, iters: int = 4096, ctas: int = 1, device=None) -> float:
+    """SM cycles per ``tcgen05.mma`` of shape 128 x n x 16 (bf16) when one thread issues ``iters`` of them
+    back to back (``sf_selftest_mma_issue_rate``); ``ctas`` blocks run at once, the slowest counts."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    cycles = torch.zeros(1, dtype=torch.int64, device=dev)
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    check(lib().sf_selftest_mma_issue_rate(int(n), int(bool(a_from_tmem)), int(iters), int(ctas), _p(cycles), _p(status),
+                                           _stream()), "sf_selftest_mma_issue_rate")
+    if int(status.item()) != 0:
+        raise RuntimeError(f"mma_issue_cycles: the wait for the MMAs ran out (code {int(status)})")
+    return float(cycles.item()) / iters
+
+
 def bias_grad(dy2d):
     _cuda(dy2d)
     T, out = dy2d.shape
@@ -626,20 +639,28 @@ def _bsr_ws(workspace, out, k, like):
     return workspace
 
 
-def bsr16_fwd(x2d, blocks, row_ptr, col_idx, out, bias=None, workspace=None, status=None):
+def bsr16_fwd(x2d, blocks, row_ptr, col_idx, out, bias=None, workspace=None, status=None, dense_ready=False):
+    """y = x . W^T for a block-CSR weight. The kept blocks are scattered into ``workspace`` ([out, in], the
+    weight dtype) and the product runs on the dense tensor-core tiles; ``dense_ready=True`` says that
+    ``workspace`` still holds the scattered weight of these very blocks (a layer whose blocks have not
+    changed since its last call), and skips the scatter."""
     _cuda(x2d, blocks, row_ptr, col_idx, bias, workspace, status)
     T, k = x2d.shape
     ws = _bsr_ws(workspace, out, k, x2d)
+    if dense_ready and workspace is not None:
+        return gemm_fwd(x2d, ws, bias=bias, status=status)
     y = torch.empty((T, out), dtype=x2d.dtype, device=x2d.device)
     check(lib().sf_bsr16_fwd(_p(x2d), _p(blocks), _p(row_ptr), _p(col_idx), _p(bias), _p(y), _p(ws), T, k, out,
                              _gemm_dtype(x2d, blocks), _p(status), _stream()), "sf_bsr16_fwd")
     return y
 
 
-def bsr16_dgrad(dy2d, blocks, row_ptr, col_idx, k, workspace=None, status=None):
+def bsr16_dgrad(dy2d, blocks, row_ptr, col_idx, k, workspace=None, status=None, dense_ready=False):
     _cuda(dy2d, blocks, row_ptr, col_idx, workspace, status)
     T, out = dy2d.shape
     ws = _bsr_ws(workspace, out, k, dy2d)
+    if dense_ready and workspace is not None:
+        return gemm_dgrad(dy2d, ws, status=status)
     dx = torch.empty((T, k), dtype=dy2d.dtype, device=dy2d.device)
     check(lib().sf_bsr16_dgrad(_p(dy2d), _p(blocks), _p(row_ptr), _p(col_idx), _p(dx), _p(ws), T, k, out,
                                _gemm_dtype(dy2d, blocks), _p(status), _stream()), "sf_bsr16_dgrad")

@@ -358,3 +358,16 @@ def test_a_wait_that_runs_out_reports_and_returns(ops):
     x = torch.randn(256, 64, device=DEV).to(torch.bfloat16)
     w = torch.randn(128, 64, device=DEV).to(torch.bfloat16)
     assert rel_err(ops.gemm_fwd(x, w).float(), x.float() @ w.float().t()) <= 1e-2
+
+
+def test_mma_issue_rate_probe(ops):
+    """The probe behind the block-sparse-16 design: the cost of one 128 x N x 16 MMA does not fall below a
+    floor of a few dozen cycles, so sixteen-wide MMAs (one per 16 x 16 weight block) run far below the
+    rate of the 128- and 256-wide ones. Sanity bounds only; the figures are in profiles/."""
+    c16, c64, c128, c256 = (ops.mma_issue_cycles(n) for n in (16, 64, 128, 256))
+    assert 100 <= c256 <= 400        # 128 cycles at the full rate of 8192 FLOP per clock and SM
+    assert c128 <= 0.75 * c256
+    assert c16 >= 0.5 * c64          # narrowing below 64 columns buys (almost) nothing
+    t16 = ops.mma_issue_cycles(16, a_from_tmem=True)
+    assert t16 >= 0.5 * c64
+

@@ -201,3 +201,14 @@ def test_block_sparse_linear_module(ops):
     assert rel_err(y.reshape(48, 128), x.detach().float().reshape(48, 256) @ (W * mask).float().t()) <= BF16_TOL
     assert rel_err(x.grad.reshape(48, 256), torch.ones(48, 128, device=DEV) @ (W * mask).float()) <= BF16_TOL
     assert layer.sparse_blocks.grad.shape == layer.sparse_blocks.shape
+    # the scattered weight is kept between calls: a second call reuses it, an in-place update of the blocks
+    # (version counter) or an explicit invalidation rebuilds it
+    with torch.no_grad():
+        y2 = layer(x.detach())
+        assert layer._workspace_key is not None and torch.equal(y2, y.detach())
+        layer.sparse_blocks.mul_(2)
+        assert rel_err(layer(x.detach()).float(), 2 * y.detach().float()) <= BF16_TOL
+        layer.sparse_blocks.data.mul_(0.5)
+        layer.invalidate_workspace()
+        assert torch.equal(layer(x.detach()), y.detach())
+
