@@ -139,6 +139,23 @@ def loss_is_finite_on_all_ranks(loss: torch.Tensor) -> bool:
     return all_ranks_ok(bool(torch.isfinite(loss.detach()).all().item()), device=loss.device)
 
 
+def grad_sync_context(model, is_last_micro: bool):
+    """Gradient-accumulation control of the training loop (legacy/main_llama.py:1997-2008): inside the
+    returned context the backward pass of a micro-step that is not the last one exchanges no gradients.
+    A wrapper with ``no_sync()`` (FSDP, DistributedDataParallel) is entered for those micro-steps; a
+    DistributedDataParallel wrapper also gets ``require_backward_grad_sync`` set, as the reference does.
+    Anything else (one process) gets a null context."""
+    import contextlib
+
+    target = model.student if hasattr(model, "student") and hasattr(model.student, "no_sync") else model
+    if hasattr(target, "require_backward_grad_sync"):
+        target.require_backward_grad_sync = bool(is_last_micro)
+        return contextlib.nullcontext()
+    if (not is_last_micro) and hasattr(target, "no_sync"):
+        return target.no_sync()
+    return contextlib.nullcontext()
+
+
 def _identify_glu_pairs(sparse_modules_dict):
     """{gate name: up name} of the GLU pairs whose gate layer asks for a joint mask
     (``...mlp.gate_proj`` / ``up_proj`` and ``...mlp.w1`` / ``w3``): legacy/utils.py:313-360."""
