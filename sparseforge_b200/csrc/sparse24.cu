@@ -155,15 +155,52 @@ __device__ __forceinline__ void sp_tile_coords(int tile, int tiles_m, int tiles_
     tn = r / gm;
 }
 
+// Work of one CTA of the 1-CTA kernel. Whole-tile mode (range_kb = 0): tiles round robin, each with its
+// whole K loop. Ranged mode (few tiles, short activations): the K blocks of all tiles, numbered tile by
+// tile, are dealt out in equal runs of range_kb blocks, one run per CTA, so that every SM streams the same
+// share of the weight whatever the tile count; a run that crosses a tile boundary yields two items. A
+// tile covered by several runs is summed through the workspace: part p of the tile is the p-th run that
+// touches it, nparts their number.
+struct SpItem {
+    int mn, kb0, kb1, part, nparts;
+};
+struct SpIter {
+    int range_kb, num_kb, mn_tiles, g, g_end, tile;
+    __device__ __forceinline__ void init(int range_kb_, int num_kb_, int mn_tiles_) {
+        range_kb = range_kb_; num_kb = num_kb_; mn_tiles = mn_tiles_;
+        g = (int)blockIdx.x * range_kb;
+        g_end = min(g + range_kb, mn_tiles * num_kb);
+        tile = (int)blockIdx.x;
+    }
+    __device__ __forceinline__ bool next(SpItem& it) {
+        if (range_kb > 0) {
+            if (g >= g_end) return false;
+            const int t = g / num_kb;
+            it.mn = t;
+            it.kb0 = g - t * num_kb;
+            it.kb1 = min(num_kb, it.kb0 + (g_end - g));
+            const int first = (t * num_kb) / range_kb, last = ((t + 1) * num_kb - 1) / range_kb;
+            it.part = (int)blockIdx.x - first;
+            it.nparts = last - first + 1;
+            g += it.kb1 - it.kb0;
+            return true;
+        }
+        if (tile >= mn_tiles) return false;
+        it.mn = tile; it.kb0 = 0; it.kb1 = num_kb; it.part = 0; it.nparts = 1;
+        tile += (int)gridDim.x;
+        return true;
+    }
+};
+
 template <int BN>
 __global__ void __launch_bounds__(SP_THREADS, 1)
 sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                      const uint8_t* __restrict__ meta_tc, __nv_bfloat16* __restrict__ Y,
                      const __nv_bfloat16* __restrict__ bias, int out, int T, int in, int32_t* status,
-                     int splits, float* __restrict__ ws, int* __restrict__ counters) {
-    // splits > 1: a work unit is one K range of a tile. Unit s stores its fp32 partial sums into
-    // ws[s][T][out]; the unit that draws the last ticket of the tile adds the partial sums in the
-    // order s = 0, 1, ... (a fixed order, whoever arrives last), writes Y and resets the ticket.
+                     int range_kb, float* __restrict__ ws, int* __restrict__ counters) {
+    // An item that is one of several parts of a tile stores its fp32 partial sums into ws[part][out][BN];
+    // the part that draws the last ticket of the tile adds the partial sums in the order part = 0, 1, ...
+    // (a fixed order, whoever arrives last), writes Y and resets the ticket.
     using C = SpCfg<BN>;
     constexpr int STAGES = C::STAGES;
     extern __shared__ uint8_t smem_raw[];
@@ -176,9 +213,7 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_m = (out + SP_BM - 1) / SP_BM, tiles_n = (T + BN - 1) / BN;
     const int mn_tiles = tiles_m * tiles_n;
-    const int total_tiles = mn_tiles * splits;  // unit u: tile u % mn_tiles, K range u / mn_tiles
     const int num_kb = (in + SP_BK - 1) / SP_BK;
-    const int kb_per = (num_kb + splits - 1) / splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -209,11 +244,13 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        SpIter iter;
+        iter.init(range_kb, num_kb, mn_tiles);
+        SpItem it;
+        while (ok && iter.next(it)) {
             int mt, nt;
-            sp_tile_coords(tile % mn_tiles, tiles_m, tiles_n, mt, nt);
-            const int kb0 = (tile / mn_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
-            for (int kb = kb0; kb < kb1; ++kb) {
+            sp_tile_coords(it.mn, tiles_m, tiles_n, mt, nt);
+            for (int kb = it.kb0; kb < it.kb1; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 11);
                 if (!ok) break;
                 if (lane == 0) {
@@ -237,14 +274,17 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         uint32_t phase = 0;
         bool ok = true;
         int t = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        SpIter iter;
+        iter.init(range_kb, num_kb, mn_tiles);
+        SpItem it;
+        for (; ok && iter.next(it); ++t) {
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 13);
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t tmem_d = tmem_base + (uint32_t)(acc * BN);
-            const int kb0 = (tile / mn_tiles) * kb_per, kb1 = min(num_kb, kb0 + kb_per);
+            const int kb0 = it.kb0, kb1 = it.kb1;
             for (int kb = kb0; kb < kb1; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->full[stage]), phase, abort_flag, status, 12);
                 if (!ok) break;
@@ -275,9 +315,13 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
         const int q = warp & 3;
         bool ok = true;
         int t = 0;
-        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        SpIter iter;
+        iter.init(range_kb, num_kb, mn_tiles);
+        SpItem it;
+        for (; ok && iter.next(it); ++t) {
             int mt, nt;
-            const int mn = tile % mn_tiles;
+            const int mn = it.mn;
+            const int splits = it.nparts;
             sp_tile_coords(mn, tiles_m, tiles_n, mt, nt);
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
@@ -296,8 +340,8 @@ sparse24_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_const
                 ptx::tmem_ld_wait();
                 if (o < out) {
                     if (splits > 1) {
-                        // partial sums of unit s: ws[s][o][0..BN), a contiguous run per thread
-                        float4* dst = reinterpret_cast<float4*>(&ws[((int64_t)(tile / mn_tiles) * out + o) * BN + c * CH]);
+                        // partial sums of part p: ws[p][o][0..BN), a contiguous run per thread
+                        float4* dst = reinterpret_cast<float4*>(&ws[((int64_t)it.part * out + o) * BN + c * CH]);
 #pragma unroll
                         for (int j = 0; j < CH / 4; ++j)
                             __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
@@ -853,22 +897,32 @@ constexpr int SP_MAX_SPLITS = 8;
 constexpr int64_t SP_TICKET_BYTES = 64 * 1024;
 static int64_t sp_ticket_bytes(int64_t) { return SP_TICKET_BYTES; }
 
-// Split-K factor for a product with few tiles: as many K ranges as fit in one wave of CTAs, at
-// least four K blocks each (measured on 4096-row matrices: 12.7 -> 8.6 us at 16 rows, K = 4096;
-// 38 -> 13 us at 16 rows and 44 -> 35 us at 128 rows, K = 11008; 17.5 -> 31 us at 128 rows, K = 4096). A matrix that already fills more than half of the SMs is not split
-// (it streams its weights at several TB/s as it is).
-static int choose_splits(int64_t tiles, int64_t num_kb, int64_t T) {
-    // beyond 32 rows the final sum over the partial results costs more than a short K loop saves
-    if (T > 32 && num_kb < 64) return 1;
-    int64_t s = sm_count() / (tiles > 0 ? tiles : 1);
-    if (s > SP_MAX_SPLITS) s = SP_MAX_SPLITS;
-    if (s > num_kb / 4) s = num_kb / 4;
-    return s < 2 ? 1 : (int)s;
+// K blocks per CTA for a product with fewer tiles than SMs and at most 128 activation rows: the K blocks of
+// all tiles are dealt out in equal runs, one per SM, at least four blocks each (a run shorter than that
+// does not cover the latency of its first loads), and long enough that no tile is cut into more than
+// SP_MAX_SPLITS parts. 0 = whole tiles. Measured on 4096-row matrices with uniform K ranges per tile: 12.7 ->
+// 8.6 us at 16 rows, K = 4096; 38 -> 13 us at 16 rows and 44 -> 35 us at 128 rows, K = 11008; beyond 32 rows
+// with a short K the final sum over the partial results costs more than it saves (17.5 -> 31 us at 128 rows).
+static int choose_range_kb(int64_t tiles, int64_t num_kb, int64_t T) {
+    if (T > 32 && num_kb < 64) return 0;
+    const int64_t sms = sm_count();
+    // a matrix whose tiles already fill more than half of the SMs streams its weights at over 3 TB/s as it is;
+    // measured at 16 rows on the 11008-row matrix (86 tiles): 15.3 us whole tiles, 16.2 us in balanced runs
+    // (the round trip of the partial sums costs more than the idle SMs), against 18.7 -> 15.9 us on the
+    // 4096 x 11008 matrix (32 tiles)
+    if (2 * tiles > sms) return 0;
+    const int64_t total = tiles * num_kb;
+    int64_t ctas = total / 4 < sms ? total / 4 : sms;
+    if (ctas <= tiles) return 0;
+    int64_t L = (total + ctas - 1) / ctas;
+    const int64_t min_l = (num_kb + SP_MAX_SPLITS - 2) / (SP_MAX_SPLITS - 1);  // at most SP_MAX_SPLITS parts per tile
+    if (L < min_l) L = min_l;
+    return L >= num_kb ? 0 : (int)L;
 }
 
 template <int BN>
 static int launch_sparse(const void* x, const void* values, const uint8_t* meta_tc, const void* bias, void* y,
-                         int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st, int splits = 1,
+                         int64_t T, int64_t in, int64_t out, int32_t* status, cudaStream_t st, int range_kb = 0,
                          float* ws = nullptr, int* counters = nullptr) {
     using C = SpCfg<BN>;
     CUtensorMap tmA, tmB;
@@ -884,10 +938,14 @@ static int launch_sparse(const void* x, const void* values, const uint8_t* meta_
         SF_CHECK_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
         configured_dev = dev;
     }
-    const int64_t tiles = ((out + SP_BM - 1) / SP_BM) * ((T + BN - 1) / BN) * splits;
-    const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    const int64_t tiles = ((out + SP_BM - 1) / SP_BM) * ((T + BN - 1) / BN);
+    int grid = (int)(tiles < sm_count() ? tiles : sm_count());
+    if (range_kb > 0) {
+        const int64_t total_kb = tiles * ((in + SP_BK - 1) / SP_BK);
+        grid = (int)((total_kb + range_kb - 1) / range_kb);  // one run of range_kb K blocks per CTA
+    }
     kern<<<grid, SP_THREADS, C::SMEM_BYTES, st>>>(tmA, tmB, meta_tc, (__nv_bfloat16*)y, (const __nv_bfloat16*)bias,
-                                                  (int)out, (int)T, (int)in, status, splits, ws, counters);
+                                                  (int)out, (int)T, (int)in, status, range_kb, ws, counters);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
@@ -984,17 +1042,25 @@ static int sparse24_gemm_impl(const void* x, const void* values, const uint8_t* 
     cudaStream_t st = (cudaStream_t)stream;
     if (T <= 128) {
         const int64_t tiles_m = (out + SP_BM - 1) / SP_BM, num_kb = (in + SP_BK - 1) / SP_BK;
-        int S = 1;
-        if (workspace != nullptr) S = splits > 0 ? splits : choose_splits(tiles_m, num_kb, T);
-        if (S > num_kb) S = (int)num_kb;
-        // every unit needs at least one K block: (S - 1) * ceil(num_kb / S) < num_kb
-        while (S > 1 && (int64_t)(S - 1) * ((num_kb + S - 1) / S) >= num_kb) --S;
-        int* cnt = S > 1 ? (int*)workspace : nullptr;
-        float* ws = S > 1 ? (float*)((char*)workspace + sp_ticket_bytes(out)) : nullptr;
-        if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
-        if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
-        if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
-        return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st, S, ws, cnt);
+        // splits = 0: runs of K blocks balanced over the SMs; splits = N > 1: N equal K ranges per tile (the same
+        // machinery with a run length of ceil(num_kb / N)); splits = 1 or no workspace: whole tiles
+        int L = 0;
+        if (workspace != nullptr) {
+            if (splits == 0) L = choose_range_kb(tiles_m, num_kb, T);
+            else if (splits > 1) {
+                int64_t S = splits < num_kb ? splits : num_kb;
+                const int64_t min_l = (num_kb + SP_MAX_SPLITS - 2) / (SP_MAX_SPLITS - 1);
+                L = (int)((num_kb + S - 1) / S);
+                if (L < min_l) L = (int)min_l;
+                if (L >= num_kb) L = 0;
+            }
+        }
+        int* cnt = L > 0 ? (int*)workspace : nullptr;
+        float* ws = L > 0 ? (float*)((char*)workspace + sp_ticket_bytes(out)) : nullptr;
+        if (T <= 16) return launch_sparse<16>(x, values, meta_tc, bias, y, T, in, out, status, st, L, ws, cnt);
+        if (T <= 32) return launch_sparse<32>(x, values, meta_tc, bias, y, T, in, out, status, st, L, ws, cnt);
+        if (T <= 64) return launch_sparse<64>(x, values, meta_tc, bias, y, T, in, out, status, st, L, ws, cnt);
+        return launch_sparse<128>(x, values, meta_tc, bias, y, T, in, out, status, st, L, ws, cnt);
     }
     // Pick the tiling that wastes fewer tile slots in its last wave; a CTA-pair tile does the same
     // work with about 1.3x less operand traffic, so it wins unless its wave fill is much worse.

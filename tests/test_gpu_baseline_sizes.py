@@ -214,3 +214,58 @@ def test_c2_bench_pair_two_steps(shift):
         # next step: both sides continue from the kernel's state
         st = {"W": W.cpu().clone(), "m": m.cpu().clone(), "v": v.cpu().clone(), "mask": mask_cpu.clone(), "H": H.cpu().clone()}
     print(f"[parity] bf16 q-projection, two steps: {total_diff} hard-mask entries differ in total")
+
+
+def test_c2_three_pass_path_one_step():
+    """The same q-shaped step through the three separate passes the module path uses when the score is not
+    folded into the optimizer: Hutchinson accumulate + score (`sf_hutch_score`), mask-aware AdamW that also
+    emits the masked weight (`sf_adamw_masked`), score of the new weight, mask update from the score tensor
+    (`sf_mask_update_nm24`). Against the oracle, entry by entry, at the size the benchmark runs."""
+    from sparseforge_b200 import _lib, ops
+
+    rows = cols = 4096
+    hp = B.C2_HYPER
+    it = 5
+    st = B.c2_state(rows, cols, seed=101)
+    inp = B.c2_step_inputs(rows, cols, it, seed=101)
+    temp, hx = B.c2_schedule(it)
+    dev = lambda t: t.to(DEV).contiguous()  # noqa: E731
+    W, m, v, H, mask = dev(st["W"]), dev(st["m"]), dev(st["v"]), dev(st["H"]), dev(st["mask"])
+    score = torch.empty(rows, cols, device=DEV)
+    norm, scratch = torch.zeros(2, device=DEV), ops.hutch_score_scratch(DEV)
+    # pass 1: H <- EMA of clamp(hvp * v, 0); score of the CURRENT weight
+    ops.hutch_score(W, H, score, norm, scratch, hvp=dev(inp["hvp"]), v=dev(inp["probe"]), beta=hp["beta_h"])
+    want_H = O.hutchinson_accumulate(st["H"], inp["hvp"], inp["probe"].to(inp["hvp"].dtype), hp["beta_h"])
+    B.assert_elementwise(H, want_H, F32, 1e-12, "H")
+    want_score = O.importance_score(st["W"], "hessian_obd", H=want_H)
+    B.assert_elementwise(score, want_score, F32, 1e-9 * B.rms(want_score), "score of the current weight")
+    mu, sigma = O.score_norm_stats(want_score)
+    assert torch.allclose(norm.cpu(), torch.stack([mu, sigma]), rtol=F32, atol=0)
+    # pass 2: AdamW with the mask term, masked weight emitted at the step's hardening factor
+    wm = torch.empty_like(W)
+    ops.adamw_masked(W, dev(inp["g"]), m, v, mask=mask, lr=hp["lr"], beta1=hp["beta1"], beta2=hp["beta2"], eps=hp["eps"],
+                     weight_decay=hp["weight_decay"], decay=hp["decay"], step=it + 1, wm=wm, hx=hx)
+    wW, wm_, wv = O.adamw_step(st["W"], inp["g"], st["m"], st["v"], step=it + 1, lr=hp["lr"], betas=(hp["beta1"], hp["beta2"]),
+                               eps=hp["eps"], weight_decay=hp["weight_decay"], mask=st["mask"], decay=hp["decay"])
+    for name, got, want in (("W", W, wW), ("exp_avg", m, wm_), ("exp_avg_sq", v, wv)):
+        B.assert_elementwise(got.float(), want.float(), BF16, BF16 * B.rms(want.float()), name)
+    want_wm = O.masked_weight(W.cpu(), O.effective_mask(st["mask"], hx))
+    B.assert_elementwise(wm.float(), want_wm.float(), BF16, BF16 * B.rms(want_wm.float()), "masked weight from the optimizer pass")
+    # pass 3: score of the NEW weight, then the mask update from the score tensor
+    ops.hutch_score(W, H, score, norm, scratch)
+    raw = O.importance_score(W.cpu(), "hessian_obd", H=H.cpu())
+    B.assert_elementwise(score, raw, F32, 1e-9 * B.rms(raw), "score of the new weight")
+    G = O.gate_target_structured(O.normalize_scores(raw), temp)
+    want_mask = O.mask_update(st["mask"], G, mask_lr=hp["mask_lr"])
+    stats = torch.zeros(8, dtype=torch.float64, device=DEV)
+    meta = torch.zeros(rows, cols // 8, dtype=torch.uint8, device=DEV)
+    ops.mask_update_nm24(score, norm, mask, stats, W=W, wm=wm, meta=meta, temperature=temp, mask_lr=hp["mask_lr"], hx=hx)
+    B.assert_elementwise(mask, want_mask, F32, 1e-7, "soft mask")
+    mask_cpu = mask.cpu()
+    hard_own = O.hard_mask_from_soft(mask_cpu)
+    assert torch.equal(meta.cpu(), O.meta_from_hard(hard_own))
+    assert int(stats[_lib.MSTAT_FLIPS]) == O.flip_count(st["mask"], mask_cpu)
+    report_hard("bf16 q-projection, three-pass path", hard_own, O.hard_mask_from_soft(want_mask), want_mask, F32, 1e-7)
+    want_wm = O.masked_weight(W.cpu(), O.effective_mask(mask_cpu, hx))
+    B.assert_elementwise(wm.float(), want_wm.float(), BF16, BF16 * B.rms(want_wm.float()), "masked weight from the mask update")
+
