@@ -168,3 +168,35 @@ def test_every_name_the_training_script_imports_exists():
         U.eval_ppl_distributed(torch.nn.Linear(2, 2))
     with pytest.raises(FileNotFoundError, match="dataloader"):
         U.add_calibration(torch.nn.Linear(2, 2))
+
+
+def test_prepared_calls_convert_once_and_read_cells_at_call_time():
+    """``_lib.prepare`` wraps the arguments of a library call in ctypes once; a ctypes instance among them is a
+    cell whose current value is read at every call; a non-zero return code raises with the library's message."""
+    import ctypes
+
+    from sparseforge_b200 import _lib
+
+    with pytest.raises(TypeError, match="arguments expected"):
+        _lib.prepare("sf_masked_gemm_configure_stream", None)
+    limit = ctypes.c_int(-1)
+    call = _lib.prepare("sf_masked_gemm_configure_stream", None, limit)
+    with pytest.raises(RuntimeError, match="max_ctas must be >= 0"):
+        call()
+    limit.value = 0  # the same prepared call, the cell changed: now valid (forgets the stream)
+    call()
+    rows = ctypes.c_int64(4)
+    bad = _lib.prepare("sf_project_nm24", None, 0, 8, None, 0, 8, None, rows, 8, None)
+    with pytest.raises(RuntimeError, match="soft must be non-null"):
+        bad()
+
+
+def test_bench_schedules_and_host_threads():
+    import bench
+
+    temps = [bench.schedule(it)[0] for it in range(10)]
+    assert temps[0] == 1.0 and temps[9] == pytest.approx(0.05) and all(a > b for a, b in zip(temps, temps[1:]))
+    assert bench.schedule(0)[1] == 1.0 and bench.schedule(1)[1] == 1.0 and bench.schedule(10)[1] == 1.0
+    assert bench.schedule(5)[1] == pytest.approx(1.0 - 4 / 9)
+    assert 1 <= bench.host_threads() <= (os.cpu_count() or 1)
+    assert bench.layer_flops(8192, 4096, 4096) == pytest.approx(824.63e9, rel=1e-4)
