@@ -603,7 +603,6 @@ def run_ours(args):
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "collective": collective,
                    "allgather": allgather, "overlap_hbm_passes": overlap, "gemm_ctas_fwd_dgrad_wgrad": [f_ctas, d_ctas, w_ctas],
-                   "last_wave_cut_into_column_ranges": os.environ.get("SF_GEMM_TAIL_CUT", "1") != "0",
                    "rank_barriers_per_step": 0 if world == 1 else (1 if arena is not None else 0),
                    "l2": "inputs larger than L2 (each matrix pass touches >100 MB)",
                    "e2e_reads_back": "mask statistics (448 B); outputs and input gradients stay on the device"},

@@ -140,35 +140,6 @@ __device__ __forceinline__ int interleave_rows(int tm, int tiles_m, int G, int r
     return owner * (tiles_m / G) + tm / G;
 }
 
-// Work list of the CTA-pair kernel. Items below `full_items` are whole 256 x 256 output tiles, handed out
-// round robin. The tiles of the last, partly filled wave ("tail tiles") are cut into `parts` column
-// ranges of 256 / parts columns, one item each, so that every pair works during that wave too: a pair
-// then runs MMAs of shape 256 x (256 / parts) x 16 on the same A rows and a narrower slice of B. Every
-// output element is still the sum over K in the same order, so results do not depend on the cut.
-struct TailPlan {
-    int full_items;
-    int parts;  // 1 or 2
-    int n_items;
-};
-struct WorkItem {
-    int tile;   // output tile in raster order
-    int col0;   // first column of the item inside the tile
-    int width;  // columns of the item: BN / parts for a tail item
-};
-__device__ __forceinline__ WorkItem work_item(int item, const TailPlan& tp) {
-    WorkItem w;
-    if (item < tp.full_items) {
-        w.tile = item; w.col0 = 0; w.width = 256;
-        return w;
-    }
-    const int u = item - tp.full_items;
-    const int t = u / tp.parts;
-    w.width = 256 / tp.parts;
-    w.col0 = (u - t * tp.parts) * w.width;
-    w.tile = tp.full_items + t;
-    return w;
-}
-
 struct GemmSmemTail {
     uint64_t full[STAGES];
     uint64_t empty[STAGES];
@@ -409,10 +380,9 @@ struct PairSmemTail {
 template <int A_MN, int B_MN, int DIST = DIST_LOCAL>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                      const __grid_constant__ CUtensorMap tmBh,
                       __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
-                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po,
-                      const __grid_constant__ TailPlan tp) {
+                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po) {
+
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
     const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -446,7 +416,6 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
-        ptx::prefetch_tensormap(&tmBh);
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -458,15 +427,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         int stage = 0;
         uint32_t phase = 0;
         bool ok = true;
-        for (int item = pair; item < tp.n_items && ok; item += num_pairs) {
-            const WorkItem w = work_item(item, tp);
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
             int tm, tn;
-            tile_coords(w.tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
             if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
-            const int bn_cta = w.width / 2;                              // B rows this CTA loads
-            const int m0 = tm * 2 * BM + (int)cta * BM;                  // this CTA's rows of A / D
-            const int n0 = tn * BN + w.col0 + (int)cta * bn_cta;         // this CTA's half of the item's B rows
-            const uint32_t stage_tx = 2u * (uint32_t)(A_STAGE_BYTES + bn_cta * BK * 2);
+            const int m0 = tm * 2 * BM + (int)cta * BM;       // this CTA's rows of A / D
+            const int n0 = tn * BN + (int)cta * PAIR_BNH;     // this CTA's half of the B rows
             for (int kb = 0; kb < num_kb; ++kb) {
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->empty[stage]), phase ^ 1u, abort_flag, status, 31);
                 if (!ok) break;
@@ -475,7 +441,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     const uint32_t bar = ptx::map_to_cta(local_bar, 0);
                     const uint32_t sa = base + stage * PAIR_STAGE_BYTES, sb = sa + A_STAGE_BYTES;
                     const int k0 = kb * BK;
-                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, stage_tx);
+                    if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * PAIR_STAGE_BYTES);
                     if (A_MN) {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j) ptx::tma_load_2d_pair(sa + j * MN_BOX_BYTES, &tmA, bar, m0 + 64 * j, k0);
@@ -483,11 +449,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                         ptx::tma_load_2d_pair(sa, &tmA, bar, k0, m0);
                     }
                     if (B_MN) {
-                        // boxes of 64 (N) x 64 (K)
-                        for (int j = 0; j < bn_cta / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
+#pragma unroll
+                        for (int j = 0; j < PAIR_BNH / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
                     } else {
-                        // one box: 128 rows x 64 (K) for a whole tile, 64 rows (the second tensor map) for a column range
-                        ptx::tma_load_2d_pair(sb, bn_cta == PAIR_BNH ? &tmB : &tmBh, bar, k0, n0);
+                        ptx::tma_load_2d_pair(sb, &tmB, bar, k0, n0);
                     }
                 }
                 __syncwarp();
@@ -497,15 +462,12 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (!ok) for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     } else if (warp == 1) {
         if (cta == 0) {
-            constexpr uint32_t idesc256 = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
-            constexpr uint32_t idesc128 = ptx::make_idesc_bf16(2 * BM, BN / 2, A_MN, B_MN, 0);
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(2 * BM, BN, A_MN, B_MN, 0);
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
             int t = 0;
-            for (int item = pair; item < tp.n_items && ok; item += num_pairs, ++t) {
-                const WorkItem w = work_item(item, tp);
-                const uint32_t idesc = w.width == 256 ? idesc256 : idesc128;
+            for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
                 const int acc = t & 1;
                 const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
                 ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_empty[acc]), acc_phase ^ 1u, abort_flag, status, 33);
@@ -542,12 +504,11 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t leader_empty1 = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[1]), 0);
         bool ok = true;
         int t = 0;
-        for (int item = pair; item < tp.n_items && ok; item += num_pairs, ++t) {
-            const WorkItem w = work_item(item, tp);
+        for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++t) {
             int tm, tn;
-            tile_coords(w.tile, tiles_m, tiles_n, tm, tn);
+            tile_coords(tile, tiles_m, tiles_n, tm, tn);
             if (DIST == DIST_SCATTER && po.interleave > 1) tm = interleave_rows(tm, tiles_m, po.interleave, po.rot);
-            const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN + w.col0;
+            const int m0 = tm * 2 * BM + (int)cta * BM, n0 = tn * BN;
             const int acc = t & 1;
             const uint32_t acc_phase = (uint32_t)(t >> 1) & 1u;
             ok = ptx::mbar_wait(ptx::smem_u32(&tail->tmem_full[acc]), acc_phase, abort_flag, status, 34);
@@ -558,7 +519,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             if (DIST == DIST_LOCAL) {
                 __nv_bfloat16* drow = D + (int64_t)row * ldD + n0;
 #pragma unroll 1
-                for (int c = 0; c < w.width / 32; ++c) {
+                for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
                     ptx::tmem_ld_wait();
@@ -576,7 +537,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                 ptx::tmem_ld_32x32b_x32(taddr, ra);
                 ptx::tmem_ld_32x32b_x32(taddr + 32u, rb);
                 ptx::tmem_ld_wait();
-                const int chunks = w.width / 64;
+                constexpr int chunks = BN / 64;
 #pragma unroll 1
                 for (int c = 0; c < chunks; ++c) {
                     uint4 v[8];
@@ -806,30 +767,6 @@ static int stream_max_ctas(cudaStream_t st) {
     return it == g_stream_max_ctas.end() ? 0 : it->second;
 }
 
-// Cutting the tiles of the last wave into column ranges is on unless SF_GEMM_TAIL_CUT=0 (A/B measurements).
-static bool tail_cut_enabled() {
-    static const bool v = [] {
-        const char* e = getenv("SF_GEMM_TAIL_CUT");
-        return !(e && e[0] == '0');
-    }();
-    return v;
-}
-
-// Whether the tiles of the last wave are cut into two column ranges of 128. A narrower MMA reads more
-// operand bytes per FLOP, and a wave that leaves SMs idle runs at a higher clock under the power cap, so
-// the cut is made only where it halves the wave: when at most half of the pairs would have a tile.
-// (Four ranges of 64 columns were measured slower than no cut at all and are not used.)
-static TailPlan plan_tail(int64_t ptiles, int pairs) {
-    TailPlan tp{(int)ptiles, 1, (int)ptiles};
-    if (pairs <= 0 || !tail_cut_enabled()) return tp;
-    const int rem = (int)(ptiles % pairs);
-    if (rem == 0 || 2 * rem > pairs) return tp;
-    tp.full_items = (int)(ptiles - rem);
-    tp.parts = 2;
-    tp.n_items = tp.full_items + rem * 2;
-    return tp;
-}
-
 template <int A_MN, int B_MN>
 static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, void* D, int64_t ldD,
                        const void* bias, float alpha, int64_t M, int64_t N, int64_t K, int32_t* status,
@@ -841,24 +778,18 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (rc) return rc;
     const bool pair = M > BM && use_pair_kernel();
     if (B_MN) rc = make_bf16_tensor_map(&tmB, B, N, K, ldb, 64);
-    else rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_BNH : BN);
+    int64_t max_pairs = sm_count() / 2;
+    const int limit = stream_max_ctas(st);
+    if (limit >= 2 && limit / 2 < max_pairs) max_pairs = limit / 2;
+    const int64_t ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
+    if (!B_MN) rc = make_bf16_tensor_map(&tmB, B, K, N, ldb, pair ? PAIR_BNH : BN);
     if (rc) return rc;
-    CUtensorMap tmBh = tmB;  // K-major B of a column range of a tail tile: 64 rows per CTA
-    if (pair && !B_MN) {
-        rc = make_bf16_tensor_map(&tmBh, B, K, N, ldb, PAIR_BNH / 2);
-        if (rc) return rc;
-    }
     int dev = 0;
     SF_CHECK_CUDA(cudaGetDevice(&dev));
     if (dist != DIST_LOCAL && !pair)
         return fail(SF_ERR_UNSUPPORTED, "the sharded epilogue needs more than %d rows and the CTA-pair kernel", BM);
     if (pair) {
-        const int64_t ptiles = ((M + 2 * BM - 1) / (2 * BM)) * ((N + BN - 1) / BN);
-        const int limit = stream_max_ctas(st);
-        int64_t max_pairs = sm_count() / 2;
-        if (limit >= 2 && limit / 2 < max_pairs) max_pairs = limit / 2;
-        const TailPlan tp = plan_tail(ptiles, (int)max_pairs);
-        const int pairs = (int)(tp.n_items < max_pairs ? tp.n_items : max_pairs);
+        const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
         const PeerOut none = {};
 #define SF_LAUNCH_PAIR(DISTV, SLOT)                                                                              \
     do {                                                                                                         \
@@ -869,9 +800,9 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
             SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));    \
             pair_dev[SLOT] = dev;                                                                                \
         }                                                                                                        \
-        pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, tmBh, (__nv_bfloat16*)D, ldD,                  \
+        pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD,                        \
                                                              (const __nv_bfloat16*)bias, alpha, (int)M, (int)N,  \
-                                                             (int)K, status, peers ? *peers : none, tp);         \
+                                                             (int)K, status, peers ? *peers : none);             \
     } while (0)
         if (dist == DIST_BROADCAST) SF_LAUNCH_PAIR(DIST_BROADCAST, 1);
         else if (dist == DIST_SCATTER) SF_LAUNCH_PAIR(DIST_SCATTER, 2);
