@@ -358,6 +358,35 @@ SF_API int sf_block_mask_apply(float* mask, const void* W, int w_dtype, void* wm
                         int bs, const float* value, const uint8_t* keep, double hx, void* stream);
 
 /*
+ * mask_type / hard_mask_type 'structured' with a general N:M: every group of M consecutive entries
+ * along the input dimension keeps its N largest (ties to the lower column).
+ *   replaces: the structured gate legacy/sparse_modeling.py:1164-1185, beta mixing :1199-1225,
+ *             'structured_topn' penalty :1532-1566 / 'mid' :1567-1570, binarize push :1575-1590,
+ *             EMA :1593, flip count :1659-1661, _hard_mask_from_soft 'structured' :720-735 and the
+ *             effective mask / weight*mask of forward :759-771, :74-81, for N:M other than 2:4
+ *             (2:4 has sf_mask_update_nm24, which also writes the sparse tensor cores' metadata).
+ * sf_mask_update_nm: the arithmetic of sf_mask_update_nm24 with topN-of-M in place of top2-of-4:
+ *   s = (score - norm[0]) / norm[1]; G = sigmoid((s - tau_g)/(T + 1e-8)), tau_g the N-th largest s of
+ *   the group (0/1 top-N indicator when structured_exact; the global *tau when tau != NULL); beta
+ *   mixing, penalty (pulled from pen_mask when it is not NULL: the gate layer's mask in the GLU joint
+ *   update, legacy/utils.py:363-479), binarise push, EMA, hard = topN(mask), wm <- W * cast(hx mask + (1-hx) hard)
+ *   (optional). stats as SF_MSTAT_* (the TOP2 / BOT2 slots hold the sums of the kept / dropped
+ *   entries). One thread per group. M in {2, 4, 8, 16, 32}, 1 <= N < M, cols % M == 0.
+ * sf_project_nm: hard 0/1 view of a soft mask (fp32 or bf16 in and out, row strides in elements).
+ * sf_effective_weight_nm: wm <- W * cast(hx mask + (1 - hx) topN(mask)), or W * cast(mask) when
+ *   finalized != 0 or hx >= 1 - 1e-6.
+ */
+SF_API int sf_mask_update_nm(const float* score, const float* norm, const float* tau, const float* pen_mask,
+                      float* mask, const void* W, int w_dtype, void* wm, double* stats, int64_t rows, int64_t cols, int n_keep,
+                      int m_group, double temperature, double mask_lr, double pen, int penalty_mode,
+                      double beta_s, double binarize_decay, double hx, int structured_exact, int score_bf16,
+                      void* stream);
+SF_API int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, int out_dtype, int64_t ld_hard,
+                  int64_t rows, int64_t cols, int n_keep, int m_group, void* stream);
+SF_API int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* wm, int64_t rows,
+                           int64_t cols, int n_keep, int m_group, double hx, int finalized, void* stream);
+
+/*
  * hard_mask_type 'block16': inside every 16 x 16 tile the keep_k entries with the largest soft-mask
  * value are kept (ties to the lower row-major position inside the tile).
  *   replaces: _hard_mask_from_soft 'block16' legacy/sparse_modeling.py:537-574, the 'block16'

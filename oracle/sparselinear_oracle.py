@@ -431,18 +431,18 @@ def temperature_at(step, temp_init, temp_decay, temp_min, period=1):
     return float(max(float(temp_min), float(temp_init) * (float(temp_decay) ** updates)))
 
 
-def flip_count(prev_mask, new_mask, mode="structured"):
+def flip_count(prev_mask, new_mask, mode="structured", n=2, m=4):
     """legacy/sparse_modeling.py:1659-1661."""
-    hp = hard_mask_from_soft(prev_mask, mode) > 0.5
-    hn = hard_mask_from_soft(new_mask, mode) > 0.5
+    hp = hard_mask_from_soft(prev_mask, mode, n, m) > 0.5
+    hn = hard_mask_from_soft(new_mask, mode, n, m) > 0.5
     return int((hp ^ hn).sum().item())
 
 
-def effective_mask(mask, hx, mode="structured", finalized=False):
+def effective_mask(mask, hx, mode="structured", finalized=False, n=2, m=4):
     """legacy/sparse_modeling.py:745-771."""
     if hx >= 1.0 - 1e-6 or finalized:
         return mask
-    return (hx * mask) + ((1.0 - hx) * hard_mask_from_soft(mask, mode))
+    return (hx * mask) + ((1.0 - hx) * hard_mask_from_soft(mask, mode, n, m))
 
 
 def masked_weight(W, eff_mask, scale=1.0):
@@ -451,17 +451,18 @@ def masked_weight(W, eff_mask, scale=1.0):
     return w * scale if scale != 1.0 else w
 
 
-def mask_stats(mask):
+def mask_stats(mask, n=2, m=4):
     """Per-layer sums behind mid_penalty (legacy/utils.py:913), nm_2_4_tile_stats (:1028-1234, sorted
-    groups: top-2 / bottom-2 sums) and the threshold path of sparsity_penalty (:1003)."""
+    groups: top-2 / bottom-2 sums; top-n / rest of every group of m in general) and the threshold path
+    of sparsity_penalty (:1003)."""
     rows, cols = mask.shape
     m64 = mask.double()
-    g = torch.sort(m64.view(rows, cols // 4, 4), dim=-1, descending=True).values
+    g = torch.sort(m64.view(rows, cols // m, m), dim=-1, descending=True).values
     return {
         "sum_m": float(m64.sum()),
         "sum_m1m": float((m64 * (1 - m64)).sum()),
-        "sum_top2": float(g[..., :2].sum()),
-        "sum_bot2": float(g[..., 2:].sum()),
+        "sum_top2": float(g[..., :n].sum()),
+        "sum_bot2": float(g[..., n:].sum()),
         "count_lt_half": float((mask < 0.5).sum()),
     }
 

@@ -108,6 +108,8 @@ class AdamW(Optimizer):
                                  v_max=ams)
                 if wm is not None:
                     layer._adamw_emitted()
+                elif layer is not None:
+                    layer.weight._sf_wm_stale = True  # the weight moved and no masked weight was written
         return loss
 
     def _small_tensor_step(self, p, grad, mask, state, group):

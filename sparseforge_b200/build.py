@@ -18,7 +18,7 @@ OBJ_DIR = os.path.join(PKG_DIR, "build")
 LIB_DIR = os.path.join(PKG_DIR, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libsparseforge_b200.so")
 
-SOURCES = ["elementwise.cu", "gemm_tcgen05.cu", "sparse24.cu", "bsr16.cu", "peer.cu", "kl_div.cu", "block_mask.cu", "tile16_mask.cu"]
+SOURCES = ["elementwise.cu", "gemm_tcgen05.cu", "sparse24.cu", "bsr16.cu", "peer.cu", "kl_div.cu", "block_mask.cu", "tile16_mask.cu", "nm_mask.cu"]
 HEADERS = ["common.cuh", "ptx_sm100.cuh", os.path.join("..", "..", "include", "sparseforge_b200.h")]
 
 NVCC_FLAGS = [

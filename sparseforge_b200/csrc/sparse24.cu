@@ -760,11 +760,12 @@ sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
         }
     } else {
         // ---------------- epilogue (both CTAs): warp (u, q) drains 32 rows x 224 tokens of weight tile u ----------------
-        // This epilogue is not hidden behind MMAs, so it is kept short: a lane owns one output
-        // feature in tensor memory, but the output is token-major, so 32 x 32 chunks are turned in a
-        // private shared-memory buffer and leave as 16-byte stores (4 per lane and chunk instead of
-        // 32 two-byte stores); the next chunk's accumulator read is in flight meanwhile, and the
-        // accumulators are handed back as soon as the last chunk has been read.
+        // The two accumulators fill the tensor memory, so the next tile's MMAs cannot start before
+        // both are read. The read is therefore all that stays exposed: every warp pulls its 32 x 224
+        // block into registers (rounded to bf16 with the bias added, two tokens per register: 112
+        // registers), hands the accumulators back, and only then turns 32 x 32 chunks through a
+        // private shared-memory buffer into token-major 16-byte stores, while the MMAs of the next
+        // tile already run.
         const int q = warp & 3, u = (warp - 2) >> 2;
         const uint32_t leader_empty = ptx::map_to_cta(ptx::smem_u32(&tail->tmem_empty[0]), 0);
         uint8_t* ebuf = base_ptr + STAGES * Q_STAGE_BYTES + 256 + (warp - 2) * Q_EPI_WARP_BYTES;
@@ -782,24 +783,32 @@ sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
             const float b = (bias != nullptr && o < out) ? __bfloat162float(bias[o]) : 0.0f;
             const uint32_t taddr = tmem_base + (uint32_t)(u * P2_BN) + ((uint32_t)(q * 32) << 16);
             constexpr int CHUNKS = P2_BN / 32;
-            uint32_t r[32];
-            ptx::tmem_ld_32x32b_x32(taddr, r);
-            ptx::tmem_ld_wait();
-#pragma unroll 1
+            uint32_t pk[CHUNKS * 16];
+#pragma unroll
+            for (int c = 0; c < CHUNKS; ++c) {
+                uint32_t r[32];
+                ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)(c * 32), r);
+                ptx::tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(r[2 * j]) + b,
+                                                                   __uint_as_float(r[2 * j + 1]) + b);
+                    pk[c * 16 + j] = *reinterpret_cast<const uint32_t*>(&v);
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(leader_empty);
+#pragma unroll
             for (int c = 0; c < CHUNKS; ++c) {
                 // feature-major registers -> token-major rows of 32 features (64 bytes, padded to 80)
 #pragma unroll
-                for (int j = 0; j < 32; ++j)
-                    *reinterpret_cast<__nv_bfloat16*>(ebuf + j * Q_EPI_ROW_BYTES + lane * 2) =
-                        __float2bfloat16_rn(__uint_as_float(r[j]) + b);
-                __syncwarp();
-                if (c + 1 < CHUNKS) {
-                    ptx::tmem_ld_32x32b_x32(taddr + (uint32_t)((c + 1) * 32), r);
-                } else {
-                    ptx::tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) ptx::mbar_arrive_cluster(leader_empty);
+                for (int j = 0; j < 16; ++j) {
+                    const uint32_t v = pk[c * 16 + j];
+                    *reinterpret_cast<uint16_t*>(ebuf + (2 * j) * Q_EPI_ROW_BYTES + lane * 2) = (uint16_t)(v & 0xffffu);
+                    *reinterpret_cast<uint16_t*>(ebuf + (2 * j + 1) * Q_EPI_ROW_BYTES + lane * 2) = (uint16_t)(v >> 16);
                 }
+                __syncwarp();
                 const int tok = nt * P2_BN + c * 32 + lane;
                 if (tok < T) {
                     __nv_bfloat16* yrow = Y + (int64_t)tok * out + o_base;
@@ -815,7 +824,6 @@ sparse24_gemm_pair2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid
                     }
                 }
                 __syncwarp();  // the buffer is rewritten by the next chunk
-                if (c + 1 < CHUNKS) ptx::tmem_ld_wait();
             }
         }
     }

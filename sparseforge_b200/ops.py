@@ -201,6 +201,57 @@ def project_nm24(soft, *, out_dtype=None, want_hard=True, want_meta=False):
     return hard, meta
 
 
+def mask_update_nm(score, norm, mask, stats, n_keep, m_group, *, tau=None, W=None, wm=None, temperature=1.0, mask_lr=0.1,
+                   pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
+                   structured_exact=False, score_bf16=False, pen_mask=None) -> None:
+    """``mask_update_nm24`` for a general N:M (M in 2, 4, 8, 16, 32); no metadata output."""
+    _cuda(score, norm, mask, stats, W, wm, tau, pen_mask)
+    if mask.dim() != 2:
+        raise ValueError("mask_update_nm: mask must be 2-D [out, in]")
+    if pen_mask is not None and (pen_mask.dtype != torch.float32 or pen_mask.shape != mask.shape):
+        raise TypeError("mask_update_nm: pen_mask must be a float32 tensor of the mask's shape")
+    if mask.dtype != torch.float32 or score.dtype != torch.float32 or stats.dtype != torch.float64:
+        raise TypeError("mask_update_nm: mask/score float32, stats float64")
+    if tau is not None and tau.dtype != torch.float32:
+        raise TypeError("mask_update_nm: tau must be a float32 device scalar")
+    if wm is not None and (W is None or wm.dtype != W.dtype):
+        raise TypeError("mask_update_nm: wm needs W of the same dtype")
+    rows, cols = mask.shape
+    check(lib().sf_mask_update_nm(_p(score), _p(norm), _p(tau), _p(pen_mask), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
+                                  _p(wm), _p(stats), rows, cols, int(n_keep), int(m_group), float(temperature),
+                                  float(mask_lr), float(pen), int(penalty_mode), float(beta_s), float(binarize_decay),
+                                  float(hx), int(bool(structured_exact)), int(bool(score_bf16)), _stream()),
+          "sf_mask_update_nm")
+
+
+def project_nm(soft, n_keep, m_group, *, out_dtype=None):
+    """Hard top-N-of-M projection of a 2-D soft mask along its last dimension (0/1 tensor)."""
+    if soft.dim() != 2:
+        raise ValueError("project_nm: soft must be 2-D")
+    if not soft.is_cuda:
+        raise RuntimeError("sparseforge_b200: tensors must live on a CUDA device (there is no CPU path)")
+    if soft.stride(1) != 1 and soft.numel() > 0:
+        soft = soft.contiguous()
+    rows, cols = soft.shape
+    out_dtype = out_dtype or soft.dtype
+    hard = torch.empty((rows, cols), dtype=out_dtype, device=soft.device)
+    if rows == 0 or cols == 0:
+        return hard
+    check(lib().sf_project_nm(_p(soft), _dt(soft), soft.stride(0), _p(hard), _DT[out_dtype], cols, rows, cols,
+                              int(n_keep), int(m_group), _stream()), "sf_project_nm")
+    return hard
+
+
+def effective_weight_nm(W, mask, wm, n_keep, m_group, *, hx=1.0, finalized=False) -> None:
+    """wm <- W * cast(hx mask + (1 - hx) topN-of-M(mask)) for a general N:M."""
+    _cuda(W, mask, wm)
+    if mask.dtype != torch.float32:
+        raise TypeError("effective_weight_nm: mask must be float32")
+    rows, cols = W.shape
+    check(lib().sf_effective_weight_nm(_p(W), _dt(W), _p(mask), _p(wm), rows, cols, int(n_keep), int(m_group), float(hx),
+                                       int(bool(finalized)), _stream()), "sf_effective_weight_nm")
+
+
 def effective_weight(W, mask, wm, *, meta=None, hx=1.0, finalized=False, scale=1.0) -> None:
     _cuda(W, mask, wm, meta)
     if mask.dtype != torch.float32:

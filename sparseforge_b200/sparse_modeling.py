@@ -130,21 +130,27 @@ class _MaskedWeight(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, weight, mask, hx, finalized, wm_cached):
+    def forward(ctx, weight, mask, hx, finalized, wm_cached, proj=None):
         ctx.save_for_backward(mask)
-        ctx.hx, ctx.finalized = hx, finalized
+        ctx.hx, ctx.finalized, ctx.proj = hx, finalized, proj
         if wm_cached is not None:
             return wm_cached.view_as(wm_cached)
         wm = torch.empty_like(weight)
-        ops.effective_weight(weight.detach().contiguous(), mask, wm, hx=hx, finalized=finalized)
+        if proj is not None:
+            proj(weight.detach().contiguous(), wm)
+        else:
+            ops.effective_weight(weight.detach().contiguous(), mask, wm, hx=hx, finalized=finalized)
         return wm
 
     @staticmethod
     def backward(ctx, g):
         (mask,) = ctx.saved_tensors
         out = torch.empty_like(g)
-        ops.effective_weight(g.contiguous(), mask, out, hx=ctx.hx, finalized=ctx.finalized)
-        return out, None, None, None, None
+        if ctx.proj is not None:
+            ctx.proj(g.contiguous(), out)
+        else:
+            ops.effective_weight(g.contiguous(), mask, out, hx=ctx.hx, finalized=ctx.finalized)
+        return out, None, None, None, None, None
 
 
 class STE(torch.autograd.Function):
@@ -190,7 +196,7 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight, bias, mask, decay, scale_factor=1.0, wm_cached=None, hx=1.0, finalized=True):
+    def forward(ctx, x, weight, bias, mask, decay, scale_factor=1.0, wm_cached=None, hx=1.0, finalized=True, proj=None):
         if not x.is_cuda:
             raise RuntimeError("FusedMaskedLinearSTE: tensors must live on a CUDA device (there is no CPU path)")
         cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else weight.dtype
@@ -207,6 +213,7 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
         ctx.has_bias = bias is not None
         ctx.decay = float(decay)
         ctx.hx, ctx.finalized = float(hx), bool(finalized)
+        ctx.proj = proj  # writes src * cast(M_eff) for hard views other than 2:4 (a layer's bound method)
         ctx.wm = wm if wm.dtype == cd else None
         return y2.view(*x.shape[:-1], weight.shape[0])
 
@@ -218,7 +225,7 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
         x2 = x.reshape(-1, x.shape[-1]).to(cd)
         grad_x = grad_w = grad_b = None
         if ctx.needs_input_grad[0]:
-            w = _MaskedWeight.apply(weight.to(cd), mask32, ctx.hx, ctx.finalized, ctx.wm)
+            w = _MaskedWeight.apply(weight.to(cd), mask32, ctx.hx, ctx.finalized, ctx.wm, ctx.proj)
             grad_x = _MatmulNN.apply(gy, w).view_as(x)
         if ctx.needs_input_grad[1]:
             grad_w = _MatmulTN.apply(gy, x2)
@@ -227,7 +234,7 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
                 grad_w = grad_w + ctx.decay * weight.to(cd) * eff_lt
         if ctx.has_bias and ctx.needs_input_grad[2]:
             grad_b = gy.sum(dim=0) if torch.is_grad_enabled() else ops.bias_grad(gy.contiguous()).to(cd)
-        return grad_x, grad_w, grad_b, None, None, None, None, None, None
+        return grad_x, grad_w, grad_b, None, None, None, None, None, None, None
 
 
 def _effective_mask_tensor(mask32, hx, finalized):
@@ -394,11 +401,30 @@ class SparseLinear(nn.Linear):
             self._wm = torch.empty_like(self.weight.data)
             self._wm_key = None
 
+    def _general_nm(self) -> bool:
+        """True when the layer's groups are not 2:4: the one-thread-per-group N:M kernels then take
+        the place of the 2:4 ones (no sparse tensor-core metadata, no fused optimizer output)."""
+        return (int(self.N), int(self.M)) != (2, 4)
+
     def _check_2to4(self):
-        if int(self.N) != 2 or int(self.M) != 4:
-            raise NotImplementedError(f"N:M = {self.N}:{self.M}: only 2:4 is implemented")
-        if self.in_features % 8 != 0:
-            raise ValueError(f"in_features ({self.in_features}) must be a multiple of 8 for the 2:4 kernels")
+        """Sizes and modes the N:M kernels (2:4 or general) accept."""
+        n, m = int(self.N), int(self.M)
+        if not self._general_nm():
+            if self.in_features % 8 != 0:
+                raise ValueError(f"in_features ({self.in_features}) must be a multiple of 8 for the 2:4 kernels")
+            return
+        if self._resolved_hard_type() != "structured":
+            raise NotImplementedError(
+                f"N:M = {n}:{m} with hard_mask_type={self._resolved_hard_type()!r}: gate groups and hard view must agree "
+                "(use hard_mask_type='structured' or 'match' with mask_type='structured')")
+        if m not in (2, 4, 8, 16, 32) or not 1 <= n < m:
+            raise NotImplementedError(f"N:M = {n}:{m}: M must be 2, 4, 8, 16 or 32 and 1 <= N < M")
+        if self.in_features % m != 0:
+            raise ValueError(f"in_features ({self.in_features}) must be divisible by M ({m}).")
+
+    def _check_strict_2to4(self, what: str):
+        if self._general_nm():
+            raise NotImplementedError(f"{what} needs 2:4 groups (the layer has N:M = {self.N}:{self.M})")
 
     @torch.no_grad()
     def initialize(self):
@@ -477,11 +503,16 @@ class SparseLinear(nn.Linear):
             return hard.to(soft_mask.dtype)
         if mt != "structured":
             raise ValueError(f"Invalid hard mask_type: {mt}")
-        if int(self.N) != 2 or int(self.M) != 4:
-            raise NotImplementedError(f"N:M = {self.N}:{self.M}: only 2:4 is implemented")
-        if soft_mask.shape[1] % 4 != 0:
+        n, m = int(self.N), int(self.M)
+        if soft_mask.shape[1] % m != 0:
             raise ValueError(f"in_features ({soft_mask.shape[1]}) must be divisible by M ({self.M}).")
-        return ops.project_nm24(soft_mask)[0]
+        if (n, m) == (2, 4):
+            return ops.project_nm24(soft_mask)[0]
+        if m not in (2, 4, 8, 16, 32) or not 1 <= n < m:
+            raise NotImplementedError(f"N:M = {n}:{m}: M must be 2, 4, 8, 16 or 32 and 1 <= N < M")
+        if soft_mask.dtype not in (torch.float32, torch.bfloat16):
+            return ops.project_nm(soft_mask.float(), n, m).to(soft_mask.dtype)
+        return ops.project_nm(soft_mask, n, m)
 
     @torch.no_grad()
     def metadata(self) -> torch.Tensor:
@@ -501,6 +532,8 @@ class SparseLinear(nn.Linear):
     def _adamw_emit_target(self):
         """(wm buffer, hx) the AdamW kernel should write the new masked weight with."""
         self._check_2to4()
+        if self._general_nm():
+            return None, 1.0  # the optimizer kernel ranks groups of four; masked_weight() rebuilds the product
         self._buffers_ready()
         fin = bool(getattr(self, "_hardening_finalized", False))
         return self._wm, (1.0 if fin else float(self.hardening_x))
@@ -535,11 +568,37 @@ class SparseLinear(nn.Linear):
         key = self._current_key()
         managed = getattr(self.weight, "_sf_managed", False)  # set by this package's AdamW
         if (not managed) or self._wm_key != key or getattr(self.weight, "_sf_wm_stale", True):
-            ops.effective_weight(self.weight.data, self.mask.data, self._wm, meta=self._meta,
-                                 hx=float(self.hardening_x), finalized=key[5])
+            if self._general_nm():
+                ops.effective_weight_nm(self.weight.data, self.mask.data, self._wm, int(self.N), int(self.M),
+                                        hx=float(self.hardening_x), finalized=key[5])
+            else:
+                ops.effective_weight(self.weight.data, self.mask.data, self._wm, meta=self._meta,
+                                     hx=float(self.hardening_x), finalized=key[5])
             self._wm_key = key
             self.weight._sf_wm_stale = False
         return self._wm
+
+    @torch.no_grad()
+    def _apply_effective_mask(self, src: torch.Tensor, dst: torch.Tensor) -> None:
+        """dst <- src * cast(M_eff) with the layer's current mask, hardening and hard view; the
+        backward of the masked weight (second-order products pass through it) for the hard views
+        other than 2:4."""
+        hx = float(self.hardening_x)
+        fin = bool(getattr(self, "_hardening_finalized", False))
+        bs = self._block_size()
+        if bs:
+            keep = torch.ones((self.out_features // bs, self.in_features // bs), dtype=torch.uint8, device=src.device)
+            if not fin and hx < 1.0 - 1e-6:
+                _, sq = ops.block_sums(self.mask.data, bs)
+                keep = self._block_keep(torch.sqrt(sq / float(bs * bs)))
+            ops.block_mask_apply(self.mask.data, bs, keep, W=src, wm=dst, hx=1.0 if fin else hx)
+        elif self._is_tile16():
+            ops.project_tile16(self.mask.data, self._tile16_keep_k(), want_hard=False, W=src, wm=dst,
+                               hx=1.0 if fin else hx)
+        elif self._general_nm():
+            ops.effective_weight_nm(src, self.mask.data, dst, int(self.N), int(self.M), hx=hx, finalized=fin)
+        else:
+            ops.effective_weight(src, self.mask.data, dst, hx=hx, finalized=fin)
 
     @torch.no_grad()
     def _masked_weight_block(self) -> torch.Tensor:
@@ -578,6 +637,7 @@ class SparseLinear(nn.Linear):
         The reference's inference bake-in multiplies the hard mask into a dense weight and runs a
         dense GEMM (legacy/eval_wiki_ppl.py:548-651); this is the same function with half the
         weight bytes and half the tensor-core work. Forward only; the dense weight is kept."""
+        self._check_strict_2to4("compress_for_inference (the sparse tensor cores' format)")
         self._check_2to4()
         if self.weight.dtype != torch.bfloat16:
             raise TypeError("compress_for_inference: the sparse tensor-core GEMM is bfloat16 only")
@@ -624,7 +684,9 @@ class SparseLinear(nn.Linear):
         if getattr(self.cfg, "weight_scaling", False) and hx < 1.0 - 1e-6:
             scale = 1.0 + (1.0 - hx) * (self._compute_weight_scale_factor() - 1.0)
         wm = self.masked_weight()
-        out = FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized)
+        other_view = self._block_size() or self._is_tile16() or self._general_nm()
+        out = FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized,
+                                         self._apply_effective_mask if other_view else None)
         if self.SLoRB and hasattr(self, "x_proj"):
             out = out + self._slorb(x)
         return out
@@ -865,11 +927,14 @@ class SparseLinear(nn.Linear):
         self._refresh_score()
         G = torch.zeros_like(self.mask.data)
         stats = torch.zeros(_lib.MSTAT_COUNT, dtype=torch.float64, device=G.device)
-        ops.mask_update_nm24(self._score, self._norm, G, stats, tau=self._gate_tau(step),
-                             temperature=self._temperature(step), mask_lr=1.0,
-                             beta_s=self._beta_structural(step),
-                             structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
-                             score_bf16=self._score_is_bf16())
+        gate_args = dict(tau=self._gate_tau(step), temperature=self._temperature(step), mask_lr=1.0,
+                         beta_s=self._beta_structural(step),
+                         structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
+                         score_bf16=self._score_is_bf16())
+        if self._general_nm():
+            ops.mask_update_nm(self._score, self._norm, G, stats, int(self.N), int(self.M), **gate_args)
+        else:
+            ops.mask_update_nm24(self._score, self._norm, G, stats, **gate_args)
         if not self._is_placeholder("frozen_mask_flags"):
             # a frozen entry's gate is its own value (legacy/sparse_modeling.py:1227-1229)
             G = torch.where(self.frozen_mask_flags.data != 0, self.mask.data, G)
@@ -1061,12 +1126,18 @@ class SparseLinear(nn.Linear):
             # (legacy/sparse_modeling.py:1621-1642)
             bands = dict(frozen=self.frozen_mask_flags.data, freeze_low=float(self.cfg.freeze_low),
                          freeze_high=float(self.cfg.freeze_high), freeze_apply_high=step >= 2000)
-        ops.mask_update_nm24(score, norm, self.mask.data, self._stats, tau=tau, W=self.weight.data, wm=self._wm,
-                             meta=self._meta, temperature=owner._temperature(step), mask_lr=float(cfg.mask_lr),
-                             pen=pen, penalty_mode=pmode, beta_s=owner._beta_structural(step),
-                             binarize_decay=float(getattr(cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
-                             structured_exact=bool(getattr(cfg, "structured_exact", False)),
-                             score_bf16=score_bf16, pen_mask=pen_mask, **bands)
+        common = dict(tau=tau, W=self.weight.data, wm=self._wm, temperature=owner._temperature(step),
+                      mask_lr=float(cfg.mask_lr), pen=pen, penalty_mode=pmode, beta_s=owner._beta_structural(step),
+                      binarize_decay=float(getattr(cfg, "mask_binarize_decay", 0.0) or 0.0), hx=hx_new,
+                      structured_exact=bool(getattr(cfg, "structured_exact", False)), score_bf16=score_bf16)
+        if self._general_nm():
+            if bands:
+                raise NotImplementedError(f"freeze bands are built for 2:4 groups (the layer has N:M = {self.N}:{self.M})")
+            ops.mask_update_nm(score, norm, self.mask.data, self._stats, int(self.N), int(self.M), pen_mask=pen_mask,
+                               **common)
+        else:
+            ops.mask_update_nm24(score, norm, self.mask.data, self._stats, meta=self._meta, pen_mask=pen_mask,
+                                 **common, **bands)
         self.hardening_x = hx_new
         self._fuse_score_next = self._predict_mask_update(step + 1)
         self.last_mask_stats = self._stats

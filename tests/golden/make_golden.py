@@ -751,6 +751,57 @@ def case_movement():
     save("movement", d)
 
 
+def case_nm():
+    """mask_type='structured' with N:M other than 2:4 (legacy/sparse_modeling.py:720-735, :1164-1225,
+    :1532-1570): gate, penalty pulls, beta mixing, exact gate, EMA, hard view, flip count, and a masked
+    forward / backward with hardening active. The previous masks are rounded to two decimals so that
+    groups hold exact ties."""
+    torch.manual_seed(53)
+    out_f, in_f = 48, 128
+    d = {}
+    variants = [
+        ("4of8_topn", 4, 8, torch.float32, "hessian_obd", dict(mask_penalty_mode="structured_topn"), 0.6),
+        ("1of4_mid", 1, 4, torch.float32, "hessian_obd", dict(mask_penalty_mode="mid"), 0.8),
+        ("3of4_bin", 3, 4, torch.float32, "hessian_ratio", dict(mask_penalty_mode="structured_topn", mask_binarize_decay=0.05), 0.3),
+        ("1of2_plain", 1, 2, torch.float32, "hessian_obd", dict(), 0.0),
+        ("8of16_beta", 8, 16, torch.float32, "hessian_obd",
+         dict(mask_penalty_mode="mid", beta_structural_start=0, beta_structural_end=10), 0.2),
+        ("8of32_exact", 8, 32, torch.float32, "hessian_obd", dict(structured_exact=True), 0.0),
+        ("2of8_bf16", 2, 8, torch.bfloat16, "hessian_obd", dict(mask_penalty_mode="structured_topn"), 0.5),
+        ("4of8_bf16_mag", 4, 8, torch.bfloat16, "magnitude", dict(), 0.0),
+    ]
+    d["variants"] = np.asarray([v[0] for v in variants])
+    for tag, n, m, dtype, metric, kw, lam in variants:
+        W = torch.randn(out_f, in_f) * 0.02
+        layer = make_layer(out_f, in_f, W, dtype, mask_type="structured", mask_metric=metric, N=n, M=m,
+                           mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.2, mask_penalty_lr=0.15,
+                           mask_hardening_start=2, mask_hardening_duration=8, **kw)
+        layer.mask.data = (torch.rand(out_f, in_f) * 100).round() / 100
+        if metric != "magnitude":
+            layer.hessian_diag.data = torch.rand(out_f, in_f) + 0.1
+        step = 4
+        put(d, f"{tag}_N", n); put(d, f"{tag}_M", m); put(d, f"{tag}_metric", metric)
+        put(d, f"{tag}_W", layer.weight.data); put(d, f"{tag}_mask0", layer.mask.data)
+        if metric != "magnitude":
+            put(d, f"{tag}_H", layer.hessian_diag.data)
+        put(d, f"{tag}_lambda", lam); put(d, f"{tag}_step", step)
+        put(d, f"{tag}_T", layer._temperature(step)); put(d, f"{tag}_beta_s", layer._beta_structural(step))
+        put(d, f"{tag}_hard0", layer._hard_mask_from_soft(layer.mask.data))
+        put(d, f"{tag}_G", layer.compute_gate_target(step))
+        layer.update_mask(step, lambda_mid=lam)
+        put(d, f"{tag}_mask1", layer.mask.data); put(d, f"{tag}_hx", float(layer.hardening_x))
+        put(d, f"{tag}_flips", int(layer.weight.flipped_mask))
+        put(d, f"{tag}_hard1", layer._hard_mask_from_soft(layer.mask.data))
+        X = torch.randn(2, 12, in_f).to(dtype).requires_grad_(True)
+        dY = torch.randn(2, 12, out_f).to(dtype)
+        layer.weight.grad = None
+        Y = layer(X)
+        Y.backward(dY)
+        put(d, f"{tag}_X", X); put(d, f"{tag}_dY", dY); put(d, f"{tag}_Y", Y); put(d, f"{tag}_dX", X.grad)
+        put(d, f"{tag}_dW", layer.weight.grad)
+    save("nm_general", d)
+
+
 if __name__ == "__main__":
     # `make_golden.py wanda ...` regenerates only the named single-function cases
     only = [a for a in sys.argv[1:] if not a.startswith("-")]

@@ -390,6 +390,45 @@ def test_penalty_variants():
         assert math.isclose(O.hardening_x(g.scalar(f"{tag}_step"), 2, 8), g.scalar(f"{tag}_hx"), rel_tol=1e-12)
 
 
+NM_MODES = {"4of8_topn": "structured_topn", "1of4_mid": "mid", "3of4_bin": "structured_topn", "1of2_plain": "mid",
+            "8of16_beta": "mid", "8of32_exact": "mid", "2of8_bf16": "structured_topn", "4of8_bf16_mag": "mid"}
+
+
+def test_general_nm_variants():
+    """N:M other than 2:4: gate, penalties, EMA, hard view, flip count and the masked forward /
+    backward of the reference, replayed by the oracle."""
+    g = Golden("nm_general")
+    for tag in g["variants"]:
+        n, m, metric = int(g.scalar(f"{tag}_N")), int(g.scalar(f"{tag}_M")), str(g[f"{tag}_metric"])
+        W, mask0 = g[f"{tag}_W"], g[f"{tag}_mask0"]
+        bf16 = W.dtype == torch.bfloat16
+        tol = BF16_TOL if bf16 else F32_TOL
+        H = g[f"{tag}_H"] if metric != "magnitude" else None
+        assert torch.equal(O.hard_mask_from_soft(mask0, "structured", n, m), g[f"{tag}_hard0"]), tag
+        s = O.normalize_scores(O.importance_score(W, metric, H=H))
+        G = O.gate_target_structured(s, g.scalar(f"{tag}_T"), exact=tag.endswith("exact"), beta_s=g.scalar(f"{tag}_beta_s"),
+                                     n=n, m=m)
+        assert G.dtype == g[f"{tag}_G"].dtype
+        assert rel_err(G.float(), g[f"{tag}_G"].float()) <= tol, tag
+        new = O.mask_update(mask0, g[f"{tag}_G"], mask_lr=0.2, lambda_mid=g.scalar(f"{tag}_lambda"), pen_lr=0.15,
+                            penalty_mode=NM_MODES[tag], binarize_decay=0.05 if tag == "3of4_bin" else 0.0, n=n, m=m)
+        assert rel_err(new, g[f"{tag}_mask1"]) <= tol, tag
+        hard1 = O.hard_mask_from_soft(g[f"{tag}_mask1"], "structured", n, m)
+        assert torch.equal(hard1, g[f"{tag}_hard1"]), tag
+        assert int(hard1.sum()) == hard1.numel() * n // m
+        assert O.flip_count(mask0, g[f"{tag}_mask1"], "structured", n, m) == g.scalar(f"{tag}_flips"), tag
+        hx = g.scalar(f"{tag}_hx")
+        assert math.isclose(O.hardening_x(g.scalar(f"{tag}_step"), 2, 8), hx, rel_tol=1e-12)
+        assert 0.0 < hx < 1.0  # the forward below mixes the soft mask with the hard view
+        eff = O.effective_mask(g[f"{tag}_mask1"], hx, "structured", False, n, m)
+        X, dY = g[f"{tag}_X"], g[f"{tag}_dY"]
+        Y = O.linear_forward(X, W, eff)
+        assert rel_err(Y.float(), g[f"{tag}_Y"].float()) <= tol, tag
+        dX, dW, _ = O.linear_backward(X, W, eff, dY)
+        assert rel_err(dX.float(), g[f"{tag}_dX"].float()) <= tol, tag
+        assert rel_err(dW.float(), g[f"{tag}_dW"].float()) <= tol, tag
+
+
 @pytest.mark.parametrize("tag,tol,l1", [("f32", F32_TOL, 0.0), ("bf16", BF16_TOL, 0.0), ("l1", F32_TOL, 0.02)])
 def test_adamw(tag, tol, l1):
     g = Golden("adamw")
