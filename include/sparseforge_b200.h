@@ -437,6 +437,18 @@ SF_API int sf_mask_sample_hist(const float* mask, const int64_t* idx, int64_t ta
 SF_API int sf_masked_gemm_fwd(const void* x, const void* wm, const void* bias, void* y, int64_t T,
                        int64_t in, int64_t out, float alpha, int dtype, int32_t* status,
                        void* stream);
+/*
+ * Forward product with the low-rank bypass (SLoRB) inside the same launch:
+ *   y[T,out] = x[T,in] . wm[out,in]^T + z[T,rank] . sw[out,rank]^T (+ bias[out])
+ *   replaces: `out += (x x_proj^T) SLoRB_Weight^T` after the masked product,
+ *             legacy/sparse_modeling.py:790-794, with z = x x_proj^T from sf_masked_gemm_fwd.
+ * The K loop runs on over the second operand pair into the same accumulator, so the bypass costs
+ * rank / in of the main product's time and no pass over y. bf16 only; more than 128 rows; rank a
+ * multiple of 8 (a last K block that is not full is zero-filled by the loads).
+ */
+SF_API int sf_masked_gemm_fwd_lowrank(const void* x, const void* wm, const void* z, const void* sw,
+                               const void* bias, void* y, int64_t T, int64_t in, int64_t out,
+                               int64_t rank, int dtype, int32_t* status, void* stream);
 SF_API int sf_masked_gemm_dgrad(const void* dy, const void* wm, void* dx, int64_t T, int64_t in,
                          int64_t out, int dtype, int32_t* status, void* stream);
 SF_API int sf_masked_gemm_wgrad(const void* dy, const void* x, void* dw, int64_t T, int64_t in,

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "sf_mask_summary": (c_int, [_P, c_int64, c_double, _P, _P]),
     "sf_mask_sample_hist": (c_int, [_P, _P, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_fwd": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_float, c_int, _P, _P]),
+    "sf_masked_gemm_fwd_lowrank": (c_int, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_dgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_wgrad": (c_int, [_P, _P, _P, c_int64, c_int64, c_int64, c_int, _P, _P]),
     "sf_masked_gemm_configure_stream": (c_int, [_P, c_int]),

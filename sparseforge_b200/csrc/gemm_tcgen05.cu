@@ -131,6 +131,13 @@ struct PeerOut {
     int multicast;   // DIST_BROADCAST: ptr[0] is a multicast address
 };
 
+// A second operand pair whose product lands in the same accumulator: D = A.B^T + A2.B2^T. The K loop
+// simply runs on over the second pair's K blocks (a low-rank bypass next to the main product).
+struct SecondOperands {
+    CUtensorMap a, b;
+    int k;
+};
+
 // Tile rows in raster order all belong to one owner for a long stretch, which would send the
 // kernel's whole NVLink traffic in one burst (and every rank to the same GPU at once). Walking
 // them owner by owner in turn, each rank starting at another owner, spreads the stores evenly
@@ -377,11 +384,13 @@ struct PairSmemTail {
     int abort_flag;
 };
 
-template <int A_MN, int B_MN, int DIST = DIST_LOCAL>
+template <int A_MN, int B_MN, int DIST = DIST_LOCAL, int DUAL = 0>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                       __nv_bfloat16* __restrict__ D, int64_t ldD, const __nv_bfloat16* __restrict__ bias,
-                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po) {
+                      float alpha, int M, int N, int K, int32_t* status, const __grid_constant__ PeerOut po,
+                      const __grid_constant__ SecondOperands second) {
+    static_assert(!DUAL || (A_MN == 0 && B_MN == 0 && DIST == DIST_LOCAL), "second operand pair: K-contiguous, local output");
 
     extern __shared__ uint8_t smem_raw[];
     const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -395,7 +404,8 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
     const int tiles_m = (M + 2 * BM - 1) / (2 * BM), tiles_n = (N + BN - 1) / BN;
     const int total_tiles = tiles_m * tiles_n;
-    const int num_kb = (K + BK - 1) / BK;
+    const int num_kb1 = (K + BK - 1) / BK;
+    const int num_kb = num_kb1 + (DUAL ? (second.k + BK - 1) / BK : 0);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_STAGES; ++s) {
@@ -416,6 +426,10 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     if (warp == 0 && lane == 0) {
         ptx::prefetch_tensormap(&tmA);
         ptx::prefetch_tensormap(&tmB);
+        if (DUAL) {
+            ptx::prefetch_tensormap(&second.a);
+            ptx::prefetch_tensormap(&second.b);
+        }
     }
     ptx::tc_fence_before();
     __syncthreads();
@@ -440,19 +454,20 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
                     const uint32_t local_bar = ptx::smem_u32(&tail->full[stage]);
                     const uint32_t bar = ptx::map_to_cta(local_bar, 0);
                     const uint32_t sa = base + stage * PAIR_STAGE_BYTES, sb = sa + A_STAGE_BYTES;
-                    const int k0 = kb * BK;
+                    const bool two = DUAL && kb >= num_kb1;  // the second pair's K blocks (zero-filled past its K)
+                    const int k0 = (two ? kb - num_kb1 : kb) * BK;
                     if (cta == 0) ptx::mbar_arrive_expect_tx(local_bar, 2 * PAIR_STAGE_BYTES);
                     if (A_MN) {
 #pragma unroll
                         for (int j = 0; j < BM / 64; ++j) ptx::tma_load_2d_pair(sa + j * MN_BOX_BYTES, &tmA, bar, m0 + 64 * j, k0);
                     } else {
-                        ptx::tma_load_2d_pair(sa, &tmA, bar, k0, m0);
+                        ptx::tma_load_2d_pair(sa, two ? &second.a : &tmA, bar, k0, m0);
                     }
                     if (B_MN) {
 #pragma unroll
                         for (int j = 0; j < PAIR_BNH / 64; ++j) ptx::tma_load_2d_pair(sb + j * MN_BOX_BYTES, &tmB, bar, n0 + 64 * j, k0);
                     } else {
-                        ptx::tma_load_2d_pair(sb, &tmB, bar, k0, n0);
+                        ptx::tma_load_2d_pair(sb, two ? &second.b : &tmB, bar, k0, n0);
                     }
                 }
                 __syncwarp();
@@ -791,6 +806,7 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     if (pair) {
         const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
         const PeerOut none = {};
+        const SecondOperands no_second = {};
 #define SF_LAUNCH_PAIR(DISTV, SLOT)                                                                              \
     do {                                                                                                         \
         auto pk = gemm_bf16_pair_kernel<A_MN, B_MN, DISTV>;                                                      \
@@ -802,7 +818,7 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
         }                                                                                                        \
         pk<<<2 * pairs, GEMM_THREADS, smem_bytes, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD,                        \
                                                              (const __nv_bfloat16*)bias, alpha, (int)M, (int)N,  \
-                                                             (int)K, status, peers ? *peers : none);             \
+                                                             (int)K, status, peers ? *peers : none, no_second);  \
     } while (0)
         if (dist == DIST_BROADCAST) SF_LAUNCH_PAIR(DIST_BROADCAST, 1);
         else if (dist == DIST_SCATTER) SF_LAUNCH_PAIR(DIST_SCATTER, 2);
@@ -821,6 +837,40 @@ static int launch_bf16(const void* A, int64_t lda, const void* B, int64_t ldb, v
     const int grid = (int)(tiles < sm_count() ? tiles : sm_count());
     kern<<<grid, GEMM_THREADS, GEMM_SMEM_BYTES, st>>>(tmA, tmB, (__nv_bfloat16*)D, ldD, (const __nv_bfloat16*)bias,
                                                       alpha, (int)M, (int)N, (int)K, status);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+// y[T, out] = x[T, in] . wm[out, in]^T + z[T, rank] . sw[out, rank]^T (+ bias): one launch of the pair kernel
+// whose K loop runs over both operand pairs.
+static int launch_bf16_dual(const void* x, const void* wm, const void* z, const void* sw, const void* bias, void* y,
+                            int64_t T, int64_t in, int64_t out, int64_t rank, int32_t* status, cudaStream_t st) {
+    if (T <= BM || !use_pair_kernel())
+        return fail(SF_ERR_UNSUPPORTED, "the two-pair product needs more than %d rows and the CTA-pair kernel", BM);
+    CUtensorMap tmA, tmB;
+    SecondOperands second;
+    int rc = make_bf16_tensor_map(&tmA, x, in, T, in, BM);
+    if (!rc) rc = make_bf16_tensor_map(&tmB, wm, in, out, in, PAIR_BNH);
+    if (!rc) rc = make_bf16_tensor_map(&second.a, z, rank, T, rank, BM);
+    if (!rc) rc = make_bf16_tensor_map(&second.b, sw, rank, out, rank, PAIR_BNH);
+    if (rc) return rc;
+    second.k = (int)rank;
+    int64_t max_pairs = sm_count() / 2;
+    const int limit = stream_max_ctas(st);
+    if (limit >= 2 && limit / 2 < max_pairs) max_pairs = limit / 2;
+    const int64_t ptiles = ((T + 2 * BM - 1) / (2 * BM)) * ((out + BN - 1) / BN);
+    const int pairs = (int)(ptiles < max_pairs ? ptiles : max_pairs);
+    int dev = 0;
+    SF_CHECK_CUDA(cudaGetDevice(&dev));
+    auto pk = gemm_bf16_pair_kernel<0, 0, DIST_LOCAL, 1>;
+    static thread_local int dual_dev = -1;
+    if (dual_dev != dev) {
+        SF_CHECK_CUDA(cudaFuncSetAttribute(pk, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM_BYTES));
+        dual_dev = dev;
+    }
+    const PeerOut none = {};
+    pk<<<2 * pairs, GEMM_THREADS, PAIR_SMEM_BYTES, st>>>(tmA, tmB, (__nv_bfloat16*)y, out, (const __nv_bfloat16*)bias, 1.0f,
+                                                         (int)T, (int)out, (int)in, status, none, second);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
@@ -865,6 +915,18 @@ int sf_masked_gemm_fwd(const void* x, const void* wm, const void* bias, void* y,
     if (dtype == SF_F32)
         return launch_f32((const float*)x, in, 1, (const float*)wm, in, 1, (float*)y, out, (const float*)bias, alpha, T, out, in, st);
     return launch_bf16<0, 0>(x, in, wm, in, y, out, bias, alpha, T, out, in, status, st);
+}
+
+int sf_masked_gemm_fwd_lowrank(const void* x, const void* wm, const void* z, const void* sw, const void* bias, void* y,
+                               int64_t T, int64_t in, int64_t out, int64_t rank, int dtype, int32_t* status, void* stream) {
+    int rc = check_gemm_args("sf_masked_gemm_fwd_lowrank", x, wm, y, T, in, out, dtype);
+    if (rc) return rc;
+    if (!z || !sw) return fail(SF_ERR_BAD_ARG, "sf_masked_gemm_fwd_lowrank: z and sw must be non-null");
+    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_fwd_lowrank: bf16 only");
+    if (rank <= 0 || (rank % 8) || rank > 0x7fffffff)
+        return fail(SF_ERR_UNSUPPORTED, "sf_masked_gemm_fwd_lowrank: rank=%lld must be a positive multiple of 8", (long long)rank);
+    if (!aligned16(z) || !aligned16(sw)) return fail(SF_ERR_ALIGNMENT, "sf_masked_gemm_fwd_lowrank: operands must be 16-byte aligned");
+    return launch_bf16_dual(x, wm, z, sw, bias, y, T, in, out, rank, status, (cudaStream_t)stream);
 }
 
 int sf_masked_gemm_dgrad(const void* dy, const void* wm, void* dx, int64_t T, int64_t in, int64_t out, int dtype,

@@ -328,6 +328,15 @@ static int dispatch_project(int m, const void* soft, int64_t ld_soft, void* hard
     return SF_OK;
 }
 
+static int check_group(const char* who, int n_keep, int m_group, int64_t rows, int64_t cols) {
+    if (m_group < 2 || n_keep < 1 || n_keep >= m_group) return fail(SF_ERR_BAD_ARG, "%s: need 1 <= N < M (got %d:%d)", who, n_keep, m_group);
+    if (m_group != 2 && m_group != 4 && m_group != 8 && m_group != 16 && m_group != 32)
+        return fail(SF_ERR_UNSUPPORTED, "%s: M=%d is not one of 2, 4, 8, 16, 32", who, m_group);
+    if (rows <= 0 || cols <= 0 || cols % m_group != 0)
+        return fail(SF_ERR_BAD_ARG, "%s: cols=%lld must be a multiple of M=%d", who, (long long)cols, m_group);
+    return SF_OK;
+}
+
 }  // namespace sf
 
 using namespace sf;
@@ -340,10 +349,7 @@ int sf_mask_update_nm(const float* score, const float* norm, const float* tau, c
                       double mask_lr, double pen, int penalty_mode, double beta_s, double binarize_decay, double hx,
                       int structured_exact, int score_bf16, void* stream) {
     SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm: score, norm, mask, stats must be non-null");
-    SF_CHECK_ARG(m_group >= 2 && n_keep >= 1 && n_keep < m_group, "sf_mask_update_nm: need 1 <= N < M (got %d:%d)", n_keep,
-                 m_group);
-    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % m_group == 0, "sf_mask_update_nm: cols=%lld must be a multiple of M=%d",
-                 (long long)cols, m_group);
+    if (int rc = check_group("sf_mask_update_nm", n_keep, m_group, rows, cols)) return rc;
     SF_CHECK_ARG(penalty_mode >= 0 && penalty_mode <= 2, "sf_mask_update_nm: penalty_mode must be 0, 1 or 2");
     SF_CHECK_ARG((wm == nullptr) || (W != nullptr), "sf_mask_update_nm: wm requested without W");
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_mask_update_nm: w_dtype must be SF_F32 or SF_BF16");
@@ -378,9 +384,7 @@ int sf_mask_update_nm(const float* score, const float* norm, const float* tau, c
 int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, int out_dtype, int64_t ld_hard, int64_t rows,
                   int64_t cols, int n_keep, int m_group, void* stream) {
     SF_CHECK_ARG(soft && hard, "sf_project_nm: soft and hard must be non-null");
-    SF_CHECK_ARG(m_group >= 2 && n_keep >= 1 && n_keep < m_group, "sf_project_nm: need 1 <= N < M (got %d:%d)", n_keep, m_group);
-    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % m_group == 0, "sf_project_nm: cols=%lld must be a multiple of M=%d",
-                 (long long)cols, m_group);
+    if (int rc = check_group("sf_project_nm", n_keep, m_group, rows, cols)) return rc;
     SF_CHECK_ARG(ld_soft >= cols && ld_hard >= cols, "sf_project_nm: row strides must be at least cols");
     SF_CHECK_ARG((in_dtype == SF_F32 || in_dtype == SF_BF16) && (out_dtype == SF_F32 || out_dtype == SF_BF16),
                  "sf_project_nm: dtypes must be SF_F32 or SF_BF16");
@@ -397,10 +401,7 @@ int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, i
 int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* wm, int64_t rows, int64_t cols, int n_keep,
                            int m_group, double hx, int finalized, void* stream) {
     SF_CHECK_ARG(W && mask && wm, "sf_effective_weight_nm: W, mask, wm must be non-null");
-    SF_CHECK_ARG(m_group >= 2 && n_keep >= 1 && n_keep < m_group, "sf_effective_weight_nm: need 1 <= N < M (got %d:%d)", n_keep,
-                 m_group);
-    SF_CHECK_ARG(rows > 0 && cols > 0 && cols % m_group == 0, "sf_effective_weight_nm: cols=%lld must be a multiple of M=%d",
-                 (long long)cols, m_group);
+    if (int rc = check_group("sf_effective_weight_nm", n_keep, m_group, rows, cols)) return rc;
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_effective_weight_nm: w_dtype must be SF_F32 or SF_BF16");
     if (!(aligned16(W) && aligned16(mask) && aligned16(wm)))
         return fail(SF_ERR_ALIGNMENT, "sf_effective_weight_nm: tensors must be 16-byte aligned");

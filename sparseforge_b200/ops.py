@@ -444,6 +444,21 @@ def gemm_fwd(x2d, wm, bias=None, alpha=1.0, status=None):
     return y
 
 
+def gemm_fwd_lowrank(x2d, wm, z2d, sw, bias=None, status=None):
+    """y[T,out] = x2d @ wm^T + z2d @ sw^T (+ bias) in one launch (bf16, more than 128 rows)."""
+    _cuda(x2d, wm, z2d, sw, bias, status)
+    T, k = x2d.shape
+    out, k2 = wm.shape
+    if k != k2 or z2d.shape[0] != T or sw.shape != (out, z2d.shape[1]):
+        raise ValueError(f"gemm_fwd_lowrank: shapes x{tuple(x2d.shape)} wm{tuple(wm.shape)} z{tuple(z2d.shape)} "
+                         f"sw{tuple(sw.shape)} do not fit")
+    dt = _gemm_dtype(x2d, wm, z2d, sw) if bias is None else _gemm_dtype(x2d, wm, z2d, sw, bias)
+    y = torch.empty((T, out), dtype=x2d.dtype, device=x2d.device)
+    check(lib().sf_masked_gemm_fwd_lowrank(_p(x2d), _p(wm), _p(z2d), _p(sw), _p(bias), _p(y), T, k, out, z2d.shape[1], dt,
+                                           _p(status), _stream()), "sf_masked_gemm_fwd_lowrank")
+    return y
+
+
 def gemm_dgrad(dy2d, wm, status=None):
     """dx[T,in] = dy2d[T,out] @ wm[out,in]."""
     _cuda(dy2d, wm, status)

@@ -196,7 +196,8 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
     """
 
     @staticmethod
-    def forward(ctx, x, weight, bias, mask, decay, scale_factor=1.0, wm_cached=None, hx=1.0, finalized=True, proj=None):
+    def forward(ctx, x, weight, bias, mask, decay, scale_factor=1.0, wm_cached=None, hx=1.0, finalized=True, proj=None,
+                z=None, sw=None):
         if not x.is_cuda:
             raise RuntimeError("FusedMaskedLinearSTE: tensors must live on a CUDA device (there is no CPU path)")
         cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else weight.dtype
@@ -207,9 +208,19 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
         else:
             wm = wm_cached
         x2 = x.reshape(-1, x.shape[-1])
-        y2 = ops.gemm_fwd(x2.to(cd).contiguous(), wm.to(cd), None if bias is None else bias.to(cd).contiguous(),
-                          alpha=float(scale_factor))
-        ctx.save_for_backward(x, weight, mask32)
+        b_cd = None if bias is None else bias.to(cd).contiguous()
+        if z is None:
+            y2 = ops.gemm_fwd(x2.to(cd).contiguous(), wm.to(cd), b_cd, alpha=float(scale_factor))
+        else:
+            # low-rank bypass z @ sw^T (legacy/sparse_modeling.py:790-794) added to the product: inside the
+            # same launch where the kernel allows it (bf16, more than 128 rows, no output scale)
+            z2, sw_cd = z.reshape(-1, z.shape[-1]).to(cd).contiguous(), sw.to(cd).contiguous()
+            if cd == torch.bfloat16 and x2.shape[0] > 128 and float(scale_factor) == 1.0 and z2.shape[1] % 8 == 0:
+                y2 = ops.gemm_fwd_lowrank(x2.to(cd).contiguous(), wm.to(cd), z2, sw_cd, b_cd)
+            else:
+                y2 = ops.gemm_fwd(x2.to(cd).contiguous(), wm.to(cd), b_cd, alpha=float(scale_factor))
+                y2 = y2 + ops.gemm_fwd(z2, sw_cd)
+        ctx.save_for_backward(x, weight, mask32, z, sw)
         ctx.has_bias = bias is not None
         ctx.decay = float(decay)
         ctx.hx, ctx.finalized = float(hx), bool(finalized)
@@ -219,11 +230,15 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, grad_out):
-        x, weight, mask32 = ctx.saved_tensors
+        x, weight, mask32, z, sw = ctx.saved_tensors
         cd = grad_out.dtype
         gy = grad_out.reshape(-1, grad_out.shape[-1])
         x2 = x.reshape(-1, x.shape[-1]).to(cd)
-        grad_x = grad_w = grad_b = None
+        grad_x = grad_w = grad_b = grad_z = grad_sw = None
+        if z is not None and ctx.needs_input_grad[10]:
+            grad_z = _MatmulNN.apply(gy, sw.to(cd)).view_as(z).to(z.dtype)
+        if z is not None and ctx.needs_input_grad[11]:
+            grad_sw = _MatmulTN.apply(gy, z.reshape(-1, z.shape[-1]).to(cd)).to(sw.dtype)
         if ctx.needs_input_grad[0]:
             w = _MaskedWeight.apply(weight.to(cd), mask32, ctx.hx, ctx.finalized, ctx.wm, ctx.proj)
             grad_x = _MatmulNN.apply(gy, w).view_as(x)
@@ -234,7 +249,7 @@ class FusedMaskedLinearSTE(torch.autograd.Function):
                 grad_w = grad_w + ctx.decay * weight.to(cd) * eff_lt
         if ctx.has_bias and ctx.needs_input_grad[2]:
             grad_b = gy.sum(dim=0) if torch.is_grad_enabled() else ops.bias_grad(gy.contiguous()).to(cd)
-        return grad_x, grad_w, grad_b, None, None, None, None, None, None, None
+        return grad_x, grad_w, grad_b, None, None, None, None, None, None, None, grad_z, grad_sw
 
 
 def _effective_mask_tensor(mask32, hx, finalized):
@@ -685,11 +700,16 @@ class SparseLinear(nn.Linear):
             scale = 1.0 + (1.0 - hx) * (self._compute_weight_scale_factor() - 1.0)
         wm = self.masked_weight()
         other_view = self._block_size() or self._is_tile16() or self._general_nm()
-        out = FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized,
-                                         self._apply_effective_mask if other_view else None)
+        proj = self._apply_effective_mask if other_view else None
         if self.SLoRB and hasattr(self, "x_proj"):
-            out = out + self._slorb(x)
-        return out
+            # z = x x_proj^T as a product of its own (differentiable); z SLoRB_Weight^T rides in the main
+            # product's K loop
+            cd = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else self.weight.dtype
+            x2 = x.reshape(-1, x.shape[-1]).to(cd)
+            z = _MatmulNT.apply(x2, self.x_proj.to(cd))
+            return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized, proj,
+                                              z, self.SLoRB_Weight)
+        return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, self.mask, 0.0, scale, wm, hx, finalized, proj)
 
     def _slorb(self, x):
         """(x x_proj^T) SLoRB_Weight^T, legacy/sparse_modeling.py:790-794, as two products on the

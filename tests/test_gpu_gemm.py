@@ -111,6 +111,43 @@ def test_bf16_bias_and_scale(ops):
     assert rel_err(y, 1.5 * (x.double() @ w.double().t()) + b.double()) <= BF16_TOL
 
 
+@pytest.mark.parametrize("T,k,n,r,bias", [(384, 256, 512, 64, True), (1024, 4096, 4096, 64, False), (1000, 264, 1064, 40, True),
+                                          (8192, 4096, 11008, 256, False), (136, 64, 48, 8, True)])
+def test_forward_with_a_low_rank_pair(ops, T, k, n, r, bias):
+    """y = x wm^T + z sw^T (+ bias) in one launch: the second operand pair's K blocks run on in the same
+    accumulator (a rank that is not a multiple of the 64-deep K block is zero-filled)."""
+    torch.manual_seed(T + r)
+    x = torch.randn(T, k, device=DEV).to(torch.bfloat16)
+    wm = (torch.randn(n, k, device=DEV) * 0.02).to(torch.bfloat16)
+    z = torch.randn(T, r, device=DEV).to(torch.bfloat16)
+    sw = (torch.randn(n, r, device=DEV) * 0.05).to(torch.bfloat16)
+    b = torch.randn(n, device=DEV).to(torch.bfloat16) if bias else None
+    status = torch.zeros(4, dtype=torch.int32, device=DEV)
+    y = ops.gemm_fwd_lowrank(x, wm, z, sw, b, status=status)
+    assert int(status[0]) == 0
+    want = x.float() @ wm.float().t() + z.float() @ sw.float().t()
+    if bias:
+        want = want + b.float()
+    assert rel_err(y.float(), want) <= BF16_TOL
+    # the second pair matters in this case, and leaving it out is seen
+    assert rel_err(ops.gemm_fwd(x, wm, b).float(), want) > BF16_TOL
+
+
+def test_low_rank_pair_refuses_what_it_cannot_do(ops):
+    x = torch.randn(64, 64, device=DEV).to(torch.bfloat16)
+    wm = torch.randn(32, 64, device=DEV).to(torch.bfloat16)
+    z = torch.randn(64, 16, device=DEV).to(torch.bfloat16)
+    sw = torch.randn(32, 16, device=DEV).to(torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.gemm_fwd_lowrank(x, wm, z, sw)  # 64 rows: below the CTA-pair kernel's range
+    xb = torch.randn(256, 64, device=DEV).to(torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.gemm_fwd_lowrank(xb, wm, torch.randn(256, 12, device=DEV).to(torch.bfloat16),
+                             torch.randn(32, 12, device=DEV).to(torch.bfloat16))  # rank not a multiple of 8
+    with pytest.raises(RuntimeError):
+        ops.gemm_fwd_lowrank(xb.float(), wm.float(), torch.randn(256, 16, device=DEV), torch.randn(32, 16, device=DEV))
+
+
 def test_bf16_linearity_at_full_size(ops):
     """A size-independent property at the LLaMA gate/up shape: products are linear in x."""
     torch.manual_seed(1)

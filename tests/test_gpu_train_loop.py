@@ -315,6 +315,68 @@ def test_slorb_bypass_follows_the_reference(tag, trainable):
         assert layer.x_proj.grad is None
 
 
+@pytest.mark.parametrize("trainable", [False, True])
+def test_slorb_inside_the_main_product_at_layer_size(trainable):
+    """bf16, more than 128 rows: the bypass term runs inside the main product's launch. Output and all
+    gradients equal a dense fp32 autograd model of legacy/sparse_modeling.py:759-794 with the same
+    effective mask; a Hessian-vector product through the layer runs (second-order path)."""
+    import sparseforge_b200 as sf
+
+    torch.manual_seed(23)
+    cfg = sf.SparseLinearConfig(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, SLoRB=True, SLoRB_k=16,
+                                SLoRB_init_type="mean", trainable_projection=trainable)
+    layer = sf.SparseLinear(512, 384, sparselinear_config=cfg, bias=True).to(DEV).to(torch.bfloat16)
+    layer.initialize()
+    layer.mask.data.copy_(torch.rand(384, 512, device=DEV))
+    layer.init_SLoRB()
+    layer.hardening_x = 0.5
+    layer.invalidate_masked_weight()
+    x = torch.randn(4, 96, 512, device=DEV).to(torch.bfloat16).requires_grad_(True)
+    dy = torch.randn(4, 96, 384, device=DEV).to(torch.bfloat16)
+    y = layer(x)
+    y.backward(dy)
+
+    eff = O.effective_mask(layer.mask.data.cpu(), 0.5).double()
+    W = layer.weight.data.cpu().double().requires_grad_(True)
+    P = layer.x_proj.data.cpu().double().requires_grad_(True)
+    S = layer.SLoRB_Weight.data.cpu().double().requires_grad_(True)
+    xd = x.detach().cpu().double().requires_grad_(True)
+
+    class Ste(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, a, w):
+            ctx.save_for_backward(a, w)
+            return a @ (w * eff).t()
+
+        @staticmethod
+        def backward(ctx, g):
+            a, w = ctx.saved_tensors
+            return g @ (w * eff), g.reshape(-1, g.shape[-1]).t() @ a.reshape(-1, a.shape[-1])
+
+    yd = Ste.apply(xd, W) + layer.bias.data.cpu().double() + (xd @ P.t()) @ S.t()
+    yd.backward(dy.cpu().double())
+    assert rel_err(y.detach().cpu().double(), yd.detach()) <= 1e-2
+    assert rel_err(x.grad.cpu().double(), xd.grad) <= 1e-2
+    assert rel_err(layer.weight.grad.cpu().double(), W.grad) <= 1e-2
+    assert rel_err(layer.SLoRB_Weight.grad.cpu().double(), S.grad) <= 1e-2
+    if trainable:
+        assert rel_err(layer.x_proj.grad.cpu().double(), P.grad) <= 1e-2
+    else:
+        assert layer.x_proj.grad is None
+    # without the bypass the output is visibly different: the term is really inside the product
+    with torch.no_grad():
+        plain = torch.nn.functional.linear(x.detach().float(), (layer.weight.data.float() * eff.float().to(DEV)),
+                                           layer.bias.data.float())
+    assert rel_err(plain.cpu().double(), yd.detach()) > 1e-2
+    # second order: d/dW of <dL/dW, v> through a loss that is not linear in the output
+    layer.weight.grad = None
+    loss = torch.nn.functional.gelu(layer(x.detach()).float()).square().mean()
+    (g1,) = torch.autograd.grad(loss, [layer.weight], create_graph=True)
+    v = (torch.randint(0, 2, g1.shape, device=DEV).float() * 2 - 1).to(g1.dtype)
+    (hvp,) = torch.autograd.grad((g1 * v).sum(), [layer.weight])
+    assert torch.isfinite(hvp.float()).all() and float(hvp.float().abs().max()) > 0
+
+
 def test_slorb_survives_compressed_inference():
     """A layer with the low-rank bypass that is compressed to hard 2:4 keeps the bypass: its output
     equals the masked dense path (binary mask) plus the bypass term (legacy/eval_wiki_ppl.py:560-575, 623

@@ -116,6 +116,46 @@ def test_unsupported_configurations_raise():
         sf.AdamW([torch.nn.Parameter(torch.zeros(2))], lr=-1.0)
 
 
+def test_general_nm_configurations_are_checked_on_the_host():
+    """N:M other than 2:4: which group sizes the kernels take, which combinations are refused, and the
+    argument checks of the entry points (no device needed for any of it)."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200 import _lib
+
+    def layer(n, m, in_f=64, **kw):
+        return sf.SparseLinear(in_f, 8, sparselinear_config=sf.SparseLinearConfig(mask_type="structured", N=n, M=m, **kw),
+                               bias=False)
+
+    assert not layer(2, 4)._general_nm() and layer(4, 8)._general_nm() and layer(1, 4)._general_nm()
+    for n, m in ((4, 8), (1, 2), (3, 4), (5, 16), (31, 32)):
+        layer(n, m)._check_2to4()
+    for n, m in ((2, 3), (8, 8), (0, 4), (2, 64)):
+        with pytest.raises(NotImplementedError):
+            layer(n, m)._check_2to4()
+    with pytest.raises(ValueError, match="divisible by M"):
+        layer(4, 16, in_f=72)._check_2to4()
+    with pytest.raises(NotImplementedError, match="must agree"):
+        layer(4, 8, hard_mask_type="nm_2_4")._check_2to4()
+    with pytest.raises(NotImplementedError, match="2:4"):
+        layer(4, 8).compress_for_inference()
+    layer(2, 4)._check_strict_2to4("x")
+
+    lib = _lib.lib()
+    assert lib.sf_project_nm(16, 0, 96, 16, 0, 96, 4, 96, 2, 3, None) == -2  # M = 3
+    assert b"M=3" in lib.sf_last_error_string()
+    assert lib.sf_project_nm(16, 0, 64, 16, 0, 64, 4, 60, 4, 8, None) == -1  # 60 columns, M = 8
+    assert lib.sf_project_nm(None, 0, 64, 16, 0, 64, 4, 64, 4, 8, None) == -1
+    assert lib.sf_effective_weight_nm(16, 1, 16, 16, 4, 64, 8, 8, 0.5, 0, None) == -1  # N = M
+    assert lib.sf_mask_update_nm(16, 16, None, None, 16, None, 0, None, 16, 4, 64, 4, 8, 1.0, 0.1, 0.0, 3, 0.0, 0.0, 1.0, 0,
+                                 0, None) == -1  # penalty mode 3
+    assert lib.sf_mask_update_nm(16, 16, None, None, 24, None, 0, None, 16, 4, 64, 4, 8, 1.0, 0.1, 0.0, 0, 0.0, 0.0, 1.0, 0,
+                                 0, None) == -3  # mask not 16-byte aligned
+    # the low-rank forward: rank and dtype checks
+    assert lib.sf_masked_gemm_fwd_lowrank(16, 16, 16, 16, None, 16, 256, 64, 64, 12, 1, None, None) == -2
+    assert lib.sf_masked_gemm_fwd_lowrank(16, 16, None, 16, None, 16, 256, 64, 64, 16, 1, None, None) == -1
+    assert lib.sf_masked_gemm_fwd_lowrank(16, 16, 16, 16, None, 16, 256, 64, 64, 16, 0, None, None) == -2
+
+
 def test_shard_bounds():
     from sparseforge_b200.sharding import shard_bounds
 
