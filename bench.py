@@ -56,6 +56,7 @@ BYTES_OPTIM, BYTES_MASK = 29.0, 16.125
 # (mean of forward, dgrad, wgrad: 259.2 MB for 274.88 GFLOP), scaled to a launch by its FLOPs
 GEMM_TRAFFIC_PER_GFLOP = 259.2e6 / 274.88
 N_PARITY = 3  # landing buffers of the exchange: a buffer is rewritten three steps later
+PULL_DEFAULT_WORLDS = ()  # world sizes whose input gradients go through the owner-side multimem reduce by default
 
 
 def layer_flops(T, rows, cols):
@@ -234,12 +235,22 @@ def run_ours(args):
                 arena.close()
             arena, collective = None, "nccl"
     allgather = "none" if arena is None else "multimem" if arena.mc_base else "stores"
+    # Input-gradient reduce-scatter. "scatter": the dgrad epilogue stores every owner's rows into that
+    # owner's slot, the owner adds its slots. "pull": dgrad writes its whole partial into this rank's
+    # symmetric buffer at local speed; after the step's rank barrier every owner reads the sum of ITS rows
+    # through the multicast address (multimem.ld_reduce: the switch adds the copies), on the exchange
+    # stream, beside the tail of this step and the forward products of the next.
+    pull = (arena is not None and bool(arena.mc_base) and
+            (args.dgrad_exchange == "pull" or (args.dgrad_exchange == "auto" and world in PULL_DEFAULT_WORLDS)))
+    if args.dgrad_exchange == "pull" and arena is not None and not pull:
+        print("[bench] no multicast object on this node: the input gradients go through the store-based scatter",
+              file=sys.stderr, flush=True)
     # From four GPUs on, the forward and input-gradient kernels wait on NVLink while the tensor cores idle.
     # The three products of a matrix are independent of one another, so each can have its own stream and a
     # share of the SMs: --gemm-ctas f,d,w gives the thread blocks of forward, input gradient and weight
     # gradient; a product with 0 runs on the forward's stream. Default: one stream up to two GPUs.
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
-    shares = args.gemm_ctas or ({4: "100,0,48", 8: "100,0,48"}.get(world, "0,0,0") if arena is not None else "0,0,0")
+    shares = args.gemm_ctas or ({4: "100,0,48", 8: "116,0,32"}.get(world, "0,0,0") if arena is not None else "0,0,0")
     f_ctas, d_ctas, w_ctas = [max(0, int(v)) // 2 * 2 for v in shares.split(",")]
     if not overlap:
         d_ctas = w_ctas = 0
@@ -285,13 +296,20 @@ def run_ours(args):
                 mt.fwd = [prepare("sf_masked_gemm_fwd_allgather", mt.x_ptr, P(mt.wm), None, mt.fwd_arrays[p], world, T,
                                   mt.cols, mt.rows, mt.rows_total, rank * mt.rows, 1.0, BF, P(status), ms)
                           for p in range(N_PARITY)]
-            for p in range(N_PARITY):
-                slot_arrays[(p, mt.index)] = (ctypes.c_void_p * world)(
-                    *arena.ptrs(s_off[(p, mt.index)] + rank * rows_t * mt.cols * 2))
-            mt.dgrad = [prepare("sf_masked_gemm_dgrad_reducescatter", mt.dy_ptr, P(mt.wm), slot_arrays[(p, mt.index)], world,
-                                rank, T, mt.cols, mt.rows, BF, P(status), ds) for p in range(N_PARITY)]
-            mt.reduce = [prepare("sf_reduce_slots", arena.buf.data_ptr() + s_off[(p, mt.index)], P(dxs[mt.index]), world,
-                                 rows_t * mt.cols, BF, xchg.cuda_stream) for p in range(N_PARITY)]
+            if pull:
+                mt.dgrad = [prepare("sf_masked_gemm_dgrad", mt.dy_ptr, P(mt.wm), arena.buf.data_ptr() + s_off[(p, mt.index)],
+                                    T, mt.cols, mt.rows, BF, P(status), ds) for p in range(N_PARITY)]
+                mt.reduce = [prepare("sf_multimem_reduce", arena.mc_ptr(s_off[(p, mt.index)] + rank * rows_t * mt.cols * 2),
+                                     P(dxs[mt.index]), rows_t * mt.cols, BF, args.pull_ctas, xchg.cuda_stream)
+                             for p in range(N_PARITY)]
+            else:
+                for p in range(N_PARITY):
+                    slot_arrays[(p, mt.index)] = (ctypes.c_void_p * world)(
+                        *arena.ptrs(s_off[(p, mt.index)] + rank * rows_t * mt.cols * 2))
+                mt.dgrad = [prepare("sf_masked_gemm_dgrad_reducescatter", mt.dy_ptr, P(mt.wm), slot_arrays[(p, mt.index)],
+                                    world, rank, T, mt.cols, mt.rows, BF, P(status), ds) for p in range(N_PARITY)]
+                mt.reduce = [prepare("sf_reduce_slots", arena.buf.data_ptr() + s_off[(p, mt.index)], P(dxs[mt.index]), world,
+                                     rows_t * mt.cols, BF, xchg.cuda_stream) for p in range(N_PARITY)]
         mt.wgrad = prepare("sf_masked_gemm_wgrad", mt.dy_ptr, mt.x_ptr, P(mt.dw), T, mt.cols, mt.rows, BF, P(status), ws_)
         # the reference's order: Hutchinson sample into H, optimizer step, score statistics of the NEW weight
         # (one pass over the matrix); the mask update forms the score again from W and H (it reads W anyway),
@@ -516,7 +534,13 @@ def run_ours(args):
             mt.dgrad[par]()
             torch.cuda.synchronize()
             dist.barrier()
-            dx_mine = ops.reduce_slots(arena.view(s_off[(par, mt.index)], (world, rows_t, mt.cols), bf))
+            if pull:
+                dx_mine = torch.empty(rows_t, mt.cols, dtype=bf, device=dev)
+                ops.multimem_reduce(arena.mc_ptr(s_off[(par, mt.index)] + rank * rows_t * mt.cols * 2), dx_mine)
+                torch.cuda.synchronize()
+                dist.barrier()  # nobody rewrites its partial while another rank still reads it
+            else:
+                dx_mine = ops.reduce_slots(arena.view(s_off[(par, mt.index)], (world, rows_t, mt.cols), bf))
             y_all = arena.view(y_off[(par, mt.index)], (T, mt.rows_total), bf)
             wm_full = torch.empty(world * mt.rows, mt.cols, dtype=bf, device=dev)
             dist.all_gather_into_tensor(wm_full, mt.wm)
@@ -602,7 +626,8 @@ def run_ours(args):
         "config": {"workload": "llama2-7b-layerset-tempering" + (f" (reduced to {args.only})" if args.only else ""),
                    "shapes": "q,k,v,o[4096,4096] gate,up[11008,4096] down[4096,11008]",
                    "tokens": T, "row_sharded_over": world, "collective": collective,
-                   "allgather": allgather, "overlap_hbm_passes": overlap, "gemm_ctas_fwd_dgrad_wgrad": [f_ctas, d_ctas, w_ctas],
+                   "allgather": allgather, "dgrad_exchange": "none" if arena is None else ("pull" if pull else "scatter"),
+                   "overlap_hbm_passes": overlap, "gemm_ctas_fwd_dgrad_wgrad": [f_ctas, d_ctas, w_ctas],
                    "rank_barriers_per_step": 0 if world == 1 else (1 if arena is not None else 0),
                    "l2": "inputs larger than L2 (each matrix pass touches >100 MB)",
                    "e2e_reads_back": "mask statistics (448 B); outputs and input gradients stay on the device"},
@@ -634,7 +659,13 @@ def run_ours(args):
             out["passes"][k.replace("_gbs", "_frac")] = round(out["passes"][k] / peaks["hbm_gbs"], 4)
             out["passes"][k] = round(out["passes"][k], 1)
     if arena is not None:
-        recv = (world - 1) / world * sum(T * (r + c) * 2 for _, r, c in shapes)
+        # bytes that land on one GPU per step: the other ranks' output columns, and either the other ranks'
+        # partial rows of this owner (scatter) or only the sum of its rows (pull)
+        recv = (world - 1) / world * sum(T * r * 2 for _, r, _ in shapes)
+        recv += sum(T * c * 2 for _, _, c in shapes) * ((1.0 / world) if pull else (world - 1) / world)
+        out["passes"]["exchange_sent_bytes_per_gpu_per_step"] = int(
+            sum(T * r * 2 for _, r, _ in shapes) / world * (1 if allgather == "multimem" else world - 1)
+            + sum(T * c * 2 for _, _, c in shapes) * (1.0 if pull else (world - 1) / world))
         xms = kinds.get("fwd", 0.0) + kinds.get("dgrad", 0.0)
         out["config"]["exchange_checked"] = True
         out["passes"]["exchange"] = {"received_bytes_per_gpu_per_step": int(recv),
@@ -1005,6 +1036,10 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the sparse24 and bsr16 blocks of the N = 1 line")
     ap.add_argument("--collective", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: exchange through the GEMM epilogues and peer memory (p2p) or NCCL collectives")
+    ap.add_argument("--dgrad-exchange", default="auto", choices=["auto", "scatter", "pull"],
+                    help="N > 1: input-gradient reduce-scatter by stores from the dgrad epilogue (scatter) or by an "
+                         "owner-side multimem.ld_reduce of the ranks' partials after the rank barrier (pull)")
+    ap.add_argument("--pull-ctas", type=int, default=64, help="thread blocks of the owner-side multimem reduce")
     ap.add_argument("--no-multicast", action="store_true",
                     help="output all-gather by one store per destination instead of NVSwitch multicast stores")
     ap.add_argument("--overlap", default="auto", choices=["auto", "on", "off"],

@@ -523,6 +523,19 @@ SF_API int sf_masked_gemm_dgrad_reducescatter(const void* dy, const void* wm, vo
 SF_API int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_t n, int dtype, void* stream);
 
 /*
+ * Owner-side sum of the partial input gradients through an NVSwitch multicast address:
+ *   out[i] = sum over the GPUs bound to the multicast object of their copy of mc_src[i], i < n
+ * (multimem.ld_reduce, fp32 accumulation in the switch, bf16, n a multiple of 8). Every rank writes
+ * its whole partial [T, in] into its own symmetric buffer with the plain sf_masked_gemm_dgrad; after a
+ * rank barrier each owner calls this on the multicast address of ITS rows: it receives 1/N of what the
+ * store-based scatter (sf_masked_gemm_dgrad_reducescatter + sf_reduce_slots) lands on it, the product
+ * runs at its local speed, and the transfer can run beside other work (max_ctas thread blocks, 0 = 64).
+ * The order in which the switch adds the copies is not specified (fp32 accumulation, one rounding).
+ *   replaces: the reduce-scatter of FSDP / tensor-parallel backward, legacy/main_llama.py:603-621.
+ */
+SF_API int sf_multimem_reduce(const void* mc_src, void* out, int64_t n, int dtype, int max_ctas, void* stream);
+
+/*
  * Sharing a device buffer with the other processes of one node (one process per GPU) through CUDA
  * IPC. sf_peer_export fills `handle` (sf_peer_handle_bytes() bytes) and the offset of `ptr` inside
  * its allocation; the peer process passes both to sf_peer_open and gets a pointer valid on its own

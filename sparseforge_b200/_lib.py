@@ -76,6 +76,7 @@ _SIGNATURES = {
     "sf_masked_gemm_fwd_multicast": (c_int, [_P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int64, c_float,
                                              c_int, _P, _P]),
     "sf_masked_gemm_dgrad_reducescatter": (c_int, [_P, _P, _P, c_int, c_int, c_int64, c_int64, c_int64, c_int, _P, _P]),
+    "sf_multimem_reduce": (c_int, [_P, _P, c_int64, c_int, c_int, _P]),
     "sf_reduce_slots": (c_int, [_P, _P, c_int64, c_int64, c_int, _P]),
     "sf_selftest_bounded_wait": (c_int, [c_double, _P, _P]),
     "sf_selftest_mma_issue_rate": (c_int, [c_int, c_int, c_int, c_int, _P, _P, _P]),

@@ -29,11 +29,54 @@ reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__ out, int64_t ch
     }
 }
 
+// out[i] = sum over the GPUs bound to a multicast object of their copy of src[i]: one
+// multimem.ld_reduce per 16 bytes (eight bf16) makes the NVSwitch read every GPU's copy and add them
+// in fp32, so an owner receives only the sum of its rows (1/N of what a store-based scatter lands on
+// it) while every GPU's copy leaves it once. A read takes about 4 us to come back, so the rate is set by
+// the bytes in flight: eight reads per thread; the thread blocks need no shared memory and fit beside
+// the blocks of a tensor-core product.
+__global__ void __launch_bounds__(kThreads)
+multimem_reduce_bf16_kernel(const uint4* __restrict__ mc_src, uint4* __restrict__ out, int64_t chunks) {
+    const int64_t stride = (int64_t)gridDim.x * kThreads;
+    for (int64_t c0 = (int64_t)blockIdx.x * kThreads + threadIdx.x; c0 < chunks; c0 += 8 * stride) {
+        uint4 v[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t c = c0 + j * stride;
+            if (c < chunks)
+                asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[j].x), "=r"(v[j].y), "=r"(v[j].z), "=r"(v[j].w)
+                             : "l"(mc_src + c)
+                             : "memory");
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int64_t c = c0 + j * stride;
+            if (c < chunks) out[c] = v[j];
+        }
+    }
+}
+
 }  // namespace sf
 
 using namespace sf;
 
 extern "C" {
+
+int sf_multimem_reduce(const void* mc_src, void* out, int64_t n, int dtype, int max_ctas, void* stream) {
+    SF_CHECK_ARG(mc_src && out, "sf_multimem_reduce: mc_src and out must be non-null");
+    SF_CHECK_ARG(n > 0 && n % 8 == 0, "sf_multimem_reduce: n=%lld must be a positive multiple of 8", (long long)n);
+    if (dtype != SF_BF16) return fail(SF_ERR_UNSUPPORTED, "sf_multimem_reduce: bf16 only");
+    SF_CHECK_ARG(max_ctas >= 0, "sf_multimem_reduce: max_ctas must be >= 0 (0 = default)");
+    if (!aligned16(mc_src) || !aligned16(out)) return fail(SF_ERR_ALIGNMENT, "sf_multimem_reduce: buffers must be 16-byte aligned");
+    const int64_t chunks = n / 8;
+    int64_t blocks = (chunks + 8 * kThreads - 1) / (8 * kThreads);
+    const int64_t cap = max_ctas > 0 ? max_ctas : 64;
+    if (blocks > cap) blocks = cap;
+    multimem_reduce_bf16_kernel<<<(int)blocks, kThreads, 0, (cudaStream_t)stream>>>((const uint4*)mc_src, (uint4*)out, chunks);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
 
 int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_t n, int dtype, void* stream) {
     SF_CHECK_ARG(slots && out, "sf_reduce_slots: slots and out must be non-null");

@@ -644,6 +644,20 @@ def reduce_slots(slots, out=None):
     return out
 
 
+def multimem_reduce(mc_ptr: int, out, *, max_ctas=0) -> None:
+    """out[i] <- sum over the GPUs of a multicast object of their copy of the bf16 element at
+    ``mc_ptr + 2 i`` (``mc_ptr``: a multicast address, e.g. ``PeerArena.mc_ptr(offset)``)."""
+    import ctypes
+
+    _cuda(out)
+    if out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise TypeError("multimem_reduce: out must be a contiguous bfloat16 tensor")
+    if not mc_ptr:
+        raise RuntimeError("multimem_reduce: no multicast address (the node offers no multicast object)")
+    check(lib().sf_multimem_reduce(ctypes.c_void_p(int(mc_ptr)), _p(out), out.numel(), _dt(out), int(max_ctas), _stream()),
+          "sf_multimem_reduce")
+
+
 def peer_export(t: torch.Tensor):
     """(handle bytes, byte offset) that another process of this node passes to ``peer_open``."""
     import ctypes

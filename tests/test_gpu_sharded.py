@@ -146,6 +146,22 @@ def _multicast_worker(rank, world, port, q):
             same = len(mc.ptrs(0)) == world and mc.ptrs(0)[rank] == mc.buf.data_ptr()
             result = True if (err <= 1e-2 and same) else f"multicast all-gather differs: {err}"
             del got
+            # the owner-side sum of the ranks' partial input gradients through the same multicast address
+            # (multimem.ld_reduce): every rank holds a whole [T, in] partial, an owner reads the sum of its rows
+            mc.barrier()
+            parts = [(torch.randn(Tt, in2, generator=torch.Generator().manual_seed(40 + r))).to(bf) for r in range(world)]
+            mc.view(0, (Tt, in2), bf).copy_(parts[rank].to(dev))
+            torch.cuda.synchronize()
+            mc.barrier()
+            rows = Tt // world
+            mine = torch.empty(rows, in2, dtype=bf, device=dev)
+            ops.multimem_reduce(mc.mc_ptr(rank * rows * in2 * 2), mine, max_ctas=8)
+            torch.cuda.synchronize()
+            mc.barrier()
+            want_sum = sum(p.double() for p in parts)[rank * rows:(rank + 1) * rows]
+            err2 = float((mine.cpu().double() - want_sum).abs().max()) / float(want_sum.abs().max())
+            if result is True and not err2 <= 1e-2:
+                result = f"multimem reduce differs: {err2}"
     except Exception:
         result = traceback.format_exc()
     finally:
