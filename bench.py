@@ -326,6 +326,7 @@ def run_ours(args):
     stage_free = [torch.cuda.Event(), torch.cuda.Event()]
     step_done = [torch.cuda.Event(), torch.cuda.Event()]
     stage_xw = stage_dy = host_X = host_dY = None
+    x_group = None  # its own communicator, so that these all-gathers never queue behind a step's rank barrier
     first_use = {}
     for j_, mt_ in enumerate(mats):
         first_use.setdefault(mt_.cols, j_)
@@ -341,7 +342,14 @@ def run_ours(args):
             xs = stage_xw[mt.cols][p]
             if first_use[mt.cols] == j:
                 copy_stream.wait_event(step_done[p])  # the step before last has finished with this buffer
-                xs.copy_(host_X[mt.cols], non_blocking=True)
+                if x_group is None:
+                    xs.copy_(host_X[mt.cols], non_blocking=True)
+                else:
+                    # every rank needs the whole activation: each copies its T/N rows from the host and the rows
+                    # are all-gathered over NVLink, so the step's inputs cross the host links once, not N times
+                    mine = xs[rank * rows_t:(rank + 1) * rows_t]
+                    mine.copy_(host_X[mt.cols], non_blocking=True)
+                    dist.all_gather_into_tensor(xs, mine, group=x_group)
             dys = stage_dy[b][: T * mt.rows].view(T, mt.rows)
             dys.copy_(host_dY[mt.name], non_blocking=True)
             ready = torch.cuda.Event()
@@ -557,11 +565,13 @@ def run_ours(args):
         exchange_err = float(errs)
 
     # end to end: the same step fed from pinned host buffers, stats read back every step
-    h2d = sum(T * w * 2 for w in {c for _, _, c in shapes}) + sum(T * (r // world) * 2 for _, r, _ in shapes)
+    h2d = sum(T // world * w * 2 for w in {c for _, _, c in shapes}) + sum(T * (r // world) * 2 for _, r, _ in shapes)
     d2h = len(shapes) * 8 * 8
     e2e_ms = float("nan")
     if not args.no_e2e:
-        host_X = {w: X[w].cpu().pin_memory() for w in {c for _, _, c in shapes}}
+        if world > 1:
+            x_group = dist.new_group(list(range(world)), backend="nccl")
+        host_X = {w: X[w][rank * rows_t:(rank + 1) * rows_t].cpu().pin_memory() for w in {c for _, _, c in shapes}}
         host_dY = {mt.name: dYres[mt.name].cpu().pin_memory() for mt in mats}
         wmax = max(mt.rows for mt in mats)
         stage_xw = {w: [torch.empty(T, w, dtype=bf, device=dev) for _ in range(2)] for w in host_X}
@@ -630,6 +640,9 @@ def run_ours(args):
                    "overlap_hbm_passes": overlap, "gemm_ctas_fwd_dgrad_wgrad": [f_ctas, d_ctas, w_ctas],
                    "rank_barriers_per_step": 0 if world == 1 else (1 if arena is not None else 0),
                    "l2": "inputs larger than L2 (each matrix pass touches >100 MB)",
+                   "e2e_inputs": ("activations [T, in] and upstream gradient [T, out] from pinned host memory" if world == 1 else
+                                  "per rank: its T/N rows of the activations (all-gathered over NVLink afterwards) and its column "
+                                  "block of the upstream gradient, from pinned host memory"),
                    "e2e_reads_back": "mask statistics (448 B); outputs and input gradients stay on the device"},
         "clocks": clocks,
         "e2e": None if args.no_e2e else {"value": round(flops_step / (e2e_ms / args.steps * 1e-3) / 1e12, 2),

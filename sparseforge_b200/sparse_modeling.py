@@ -437,9 +437,15 @@ class SparseLinear(nn.Linear):
         if self.in_features % m != 0:
             raise ValueError(f"in_features ({self.in_features}) must be divisible by M ({m}).")
 
+    def _is_2to4_view(self) -> bool:
+        """True when the layer's hard view is top-2-of-4 along the input dimension."""
+        t = self._resolved_hard_type()
+        return t == "nm_2_4" or (t == "structured" and not self._general_nm())
+
     def _check_strict_2to4(self, what: str):
-        if self._general_nm():
-            raise NotImplementedError(f"{what} needs 2:4 groups (the layer has N:M = {self.N}:{self.M})")
+        if not self._is_2to4_view():
+            raise NotImplementedError(f"{what} needs a 2:4 hard view (the layer has N:M = {self.N}:{self.M}, "
+                                      f"hard_mask_type={self._resolved_hard_type()!r})")
 
     @torch.no_grad()
     def initialize(self):

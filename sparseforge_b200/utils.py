@@ -467,7 +467,7 @@ def optimize_sparse_model_for_inference(model, use_slorb: bool = False, compress
     multiplied into the weight once and then runs ``dense_forward`` (a layer whose finalized
     weight already carries the zeros is not multiplied twice). With ``use_slorb`` the layer stays
     in ``sparse_forward`` and only its mask is made binary, as in the reference.
-    ``compressed=True`` goes one step further than the reference: bf16 layers are stored in the
+    ``compressed=True`` goes one step further than the reference: bf16 layers with a 2:4 hard view are stored in the
     2:4 compressed form and run on the sparse tensor cores (``SparseLinear.compress_for_inference``)."""
     optimized = total = 0
     for m in _sparse_modules(get_raw_model(model)):
@@ -488,7 +488,7 @@ def optimize_sparse_model_for_inference(model, use_slorb: bool = False, compress
             else:
                 m.mask.data.copy_(hard.to(m.mask.dtype))
         if can_dense:
-            if compressed and m.weight.dtype == torch.bfloat16 and m.in_features % 16 == 0:
+            if compressed and m.weight.dtype == torch.bfloat16 and m.in_features % 16 == 0 and m._is_2to4_view():
                 m.mask.data.copy_(hard.to(m.mask.dtype))
                 m.compress_for_inference()
             else:
