@@ -11,8 +11,9 @@ and the weight gradient of a shard are local to its rank. What crosses ranks:
 
 The reference shards the same layer through FSDP flat parameters and gathers every parameter for a
 mask update (legacy/utils.py:246-251); here nothing but the three items above is exchanged.
-The collectives go through ``torch.distributed`` (NCCL on GPUs; the functions below are
-backend-agnostic and are exercised with gloo in the CPU tests).
+``RowShardedLinear`` does the exchange with ``torch.distributed`` collectives (NCCL on GPUs; backend-agnostic,
+exercised with gloo in the CPU tests, differentiable twice); ``PeerShardedLinear`` does it inside the GEMM
+epilogues through peer memory (``PeerArena``).
 """
 from __future__ import annotations
 
@@ -123,6 +124,121 @@ def shard_sparse_linear(full_weight: torch.Tensor, config, bias: Optional[torch.
             layer.bias.copy_(bias[lo:hi])
     layer.initialize()
     return RowShardedLinear(layer, group)
+
+
+class _PeerShardedFn(torch.autograd.Function):
+    """Forward and backward of ``PeerShardedLinear``: the exchange is done by the GEMM epilogues."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, mod):
+        from . import ops
+
+        shard, arena = mod.shard, mod.arena
+        x2 = x.reshape(-1, x.shape[-1]).contiguous()
+        T = x2.shape[0]
+        mod._check(x2)
+        wm = shard.masked_weight()
+        par = mod._next_parity()
+        y_off, _ = mod._offsets(par)
+        rows = shard.out_features
+        b = None if bias is None else bias.to(x2.dtype).contiguous()
+        if arena.mc_base:
+            ops.gemm_fwd_multicast(x2, wm, arena.mc_ptr(y_off), mod.out_total, arena.rank * rows, bias=b)
+        else:
+            ops.gemm_fwd_allgather(x2, wm, arena.ptrs(y_off), mod.out_total, arena.rank * rows, bias=b)
+        arena.barrier()  # every rank's columns have landed once the stream is past this
+        y = arena.view(y_off, (T, mod.out_total), x2.dtype).clone()
+        ctx.save_for_backward(x2, wm)
+        ctx.mod, ctx.par, ctx.x_shape, ctx.has_bias = mod, par, x.shape, bias is not None
+        return y.view(*x.shape[:-1], mod.out_total)
+
+    @staticmethod
+    @torch.autograd.function.once_differentiable
+    def backward(ctx, gy):
+        from . import ops
+
+        x2, wm = ctx.saved_tensors
+        mod = ctx.mod
+        arena, rows = mod.arena, mod.shard.out_features
+        world, rank = arena.world, arena.rank
+        T, in_f = x2.shape
+        dyl = gy.reshape(-1, gy.shape[-1])[:, rank * rows:(rank + 1) * rows].contiguous()
+        grad_x = grad_w = grad_b = None
+        if ctx.needs_input_grad[1]:
+            grad_w = ops.gemm_wgrad(dyl, x2)  # no mask: straight-through (legacy/sparse_modeling.py:117-125)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            grad_b = ops.bias_grad(dyl).to(dyl.dtype)
+        if ctx.needs_input_grad[0]:
+            rows_t = T // world
+            _, s_off = mod._offsets(ctx.par)
+            # rows of owner c of this shard's partial input gradient go into the slot owner c keeps for this rank
+            ops.gemm_dgrad_reducescatter(dyl, wm, arena.ptrs(s_off + rank * rows_t * in_f * 2), rank)
+            arena.barrier()
+            mine = ops.reduce_slots(arena.view(s_off, (world, rows_t, in_f), dyl.dtype))
+            full = torch.empty(T, in_f, dtype=dyl.dtype, device=dyl.device)
+            dist.all_gather_into_tensor(full, mine, group=arena.group)  # x is replicated: every rank needs all rows
+            grad_x = full.view(ctx.x_shape)
+        return grad_x, grad_w, grad_b, None
+
+
+class PeerShardedLinear(nn.Module):
+    """``RowShardedLinear`` with the exchange inside the GEMM kernels: the forward epilogue stores this
+    shard's output columns into every rank's buffer (one multicast store per piece where the arena has
+    a multicast address), the input-gradient epilogue stores every owner's token rows into that owner's
+    slot, and the owner adds its slots (``ops.gemm_fwd_multicast`` / ``gemm_fwd_allgather``,
+    ``gemm_dgrad_reducescatter``, ``reduce_slots``). One rank barrier per forward and one per backward
+    (a one-element all-reduce on the current stream); the landing buffers alternate between two copies,
+    so a buffer is rewritten only after every rank has passed a later barrier.
+
+    bf16, more than 128 tokens per call, tokens a multiple of 8 and of the world size, at most
+    ``max_tokens``. The backward is not differentiable a second time (use ``RowShardedLinear`` under a
+    Hessian-vector product). Every rank must take the same calls in the same order, and ask for the input
+    gradient on all ranks or on none."""
+
+    N_BUFFERS = 2
+
+    def __init__(self, shard: nn.Module, out_total: int, max_tokens: int, group=None, multicast: bool = True, arena=None):
+        super().__init__()
+        self.shard = shard
+        self.group = group
+        self.out_total = int(out_total)
+        self.max_tokens = int(max_tokens)
+        dev = shard.weight.device
+        self._y_bytes = self.max_tokens * self.out_total * 2
+        self._s_bytes = self.max_tokens * shard.in_features * 2
+        self.arena = arena if arena is not None else PeerArena(self.N_BUFFERS * (self._y_bytes + self._s_bytes), dev, group,
+                                                                multicast=multicast)
+        if self.arena.world * shard.out_features != self.out_total:
+            raise ValueError(f"{self.arena.world} shards of {shard.out_features} rows do not make {self.out_total}")
+        self._calls = 0
+        if hasattr(shard, "_row_shard_group"):
+            shard._row_shard_group = group
+            shard._row_sharded = True
+
+    def _next_parity(self) -> int:
+        self._calls += 1
+        return self._calls % self.N_BUFFERS
+
+    def _offsets(self, par: int):
+        base = par * (self._y_bytes + self._s_bytes)
+        return base, base + self._y_bytes
+
+    def _check(self, x2: torch.Tensor) -> None:
+        T = x2.shape[0]
+        if x2.dtype != torch.bfloat16 or self.shard.weight.dtype != torch.bfloat16:
+            raise TypeError("PeerShardedLinear: bfloat16 activations and weights (the sharded epilogues are bf16 only)")
+        if T <= 128 or T % 8 or T % self.arena.world or T > self.max_tokens:
+            raise ValueError(f"PeerShardedLinear: {T} tokens; need more than 128, a multiple of 8 and of the world size "
+                             f"({self.arena.world}), at most max_tokens={self.max_tokens}")
+
+    def forward(self, x):
+        return _PeerShardedFn.apply(x, self.shard.weight, self.shard.bias, self)
+
+    def close(self):
+        """Releases the arena (every rank, no kernel in flight)."""
+        if self.arena is not None:
+            self.arena.close()
+            self.arena = None
 
 
 class PeerArena:

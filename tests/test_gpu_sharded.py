@@ -87,6 +87,25 @@ def _worker(rank, world, port, q):
             ok = ok and rel(dx_mine, ops.gemm_dgrad(dyf, wfull)[rank * rows:(rank + 1) * rows]) <= 1e-2
         finally:
             arena.close()
+        # the module whose forward / backward run those epilogues: same output and gradients as the unsharded layer
+        from sparseforge_b200.sharding import PeerShardedLinear
+
+        peer = PeerShardedLinear(sharded.shard, out_f, max_tokens=T, multicast=False)
+        try:
+            for _ in range(3):  # the two landing buffers are both reused
+                full.weight.grad = None
+                sharded.shard.weight.grad = None
+                x1 = X.clone().requires_grad_(True)
+                x2 = X.clone().requires_grad_(True)
+                y1, y2 = full(x1), peer(x2)
+                y1.backward(dY)
+                y2.backward(dY)
+                ok = ok and rel(y2, y1) <= 1e-2 and rel(x2.grad, x1.grad) <= 1e-2
+                ok = ok and rel(sharded.shard.weight.grad, full.weight.grad[lo:hi]) <= 1e-2
+            with torch.no_grad():
+                ok = ok and rel(peer(X), full(X)) <= 1e-2
+        finally:
+            peer.close()
         flips = torch.tensor([int(sharded.shard.weight.flipped_mask)], device=dev)
         dist.all_reduce(flips)
         ok = ok and abs(int(flips) - int(full.weight.flipped_mask)) <= 2
