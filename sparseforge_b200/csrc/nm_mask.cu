@@ -3,10 +3,10 @@
 // The 2:4 case has kernels of its own (eight entries per thread, metadata for the sparse tensor
 // cores); this file covers every other N < M with M in {2, 4, 8, 16, 32}.
 //
-// One thread owns one group: it holds the M scores, the M previous mask values and the M new ones in
-// registers and ranks them with M (M - 1) comparisons (stable descending order: ties go to the
-// lower column, NaN counts as the largest value, as in a stable sort of the group). The passes are
-// bound by HBM for M <= 8 and by the comparisons above that.
+// One thread owns one group (two or four groups for M = 4, 2): it holds the scores, the previous mask values
+// and the new ones in registers and ranks every group with M (M - 1) / 2 comparisons (stable descending
+// order: ties go to the lower column). The hard projection alone also orders NaN (largest, as a stable sort
+// of the group does). The passes are bound by HBM for M <= 8 and by the comparisons above that.
 #include "common.cuh"
 
 namespace sf {
@@ -103,22 +103,42 @@ __device__ __forceinline__ uint32_t topn_keep(const float (&x)[M], int n) {
     return keep;
 }
 
-// keep bits and the n-th largest value of the group
+// The update pass ranks NaN-free values (normalised scores, gates and masks in [0, 1]), so every pair is
+// compared once: c = (x_i >= x_j) for i < j puts i before j (the lower column wins a tie); rank_i starts at
+// the number of later columns and loses one for each of them it beats, rank_j gains one. x points at the M
+// values of the group inside a register array (all indices are compile-time constants after unrolling).
 template <int M>
-__device__ __forceinline__ uint32_t topn_keep_tau(const float (&x)[M], int n, float& tau) {
+__device__ __forceinline__ void ranks_pairwise(const float* x, int (&rank)[M]) {
+#pragma unroll
+    for (int i = 0; i < M; ++i) rank[i] = M - 1 - i;
+#pragma unroll
+    for (int i = 0; i < M; ++i)
+#pragma unroll
+        for (int j = i + 1; j < M; ++j) {
+            const int c = (int)set_ge(x[i], x[j]);  // -1 when i sorts before j, else 0
+            rank[i] += c;
+            rank[j] -= c;
+        }
+}
+template <int M>
+__device__ __forceinline__ uint32_t keep_fast(const float* x, int n) {
+    int rank[M];
+    ranks_pairwise<M>(x, rank);
+    uint32_t keep = 0;
+#pragma unroll
+    for (int i = 0; i < M; ++i) keep |= (rank[i] < n ? 1u : 0u) << i;
+    return keep;
+}
+template <int M>
+__device__ __forceinline__ uint32_t keep_tau_fast(const float* x, int n, float& tau) {
+    int rank[M];
+    ranks_pairwise<M>(x, rank);
     uint32_t keep = 0;
     tau = x[0];
 #pragma unroll
     for (int i = 0; i < M; ++i) {
-        int r = 0;
-#pragma unroll
-        for (int j = 0; j < M; ++j) {
-            if (j == i) continue;
-            const bool before = j < i ? !gt_desc(x[i], x[j]) : gt_desc(x[j], x[i]);
-            r += before ? 1 : 0;
-        }
-        keep |= (r < n ? 1u : 0u) << i;
-        if (r == n - 1) tau = x[i];
+        keep |= (rank[i] < n ? 1u : 0u) << i;
+        if (rank[i] == n - 1) tau = x[i];
     }
     return keep;
 }
@@ -150,11 +170,14 @@ __device__ __forceinline__ void nm_reduce_stats(const NmStats& g, double* __rest
     }
 }
 
-template <typename TW, int M>
+// E = GPT * M consecutive entries per thread: GPT groups of M (32 bytes of each fp32 tensor per thread
+// for M <= 8, which the memory system likes better than 8 or 16).
+template <typename TW, int M, int GPT>
 __global__ void __launch_bounds__(kNmThreads)
 mask_update_nm_kernel(const float* __restrict__ score, const float* __restrict__ norm, float* __restrict__ mask,
-                      const TW* __restrict__ W, TW* __restrict__ wm, double* __restrict__ stats, int64_t groups,
+                      const TW* __restrict__ W, TW* __restrict__ wm, double* __restrict__ stats, int64_t chunks,
                       NmUpdateParams P) {
+    constexpr int E = GPT * M;
     const float mu = norm[0];
     const float inv_sigma = __fdiv_rn(1.0f, norm[1]);
     const bool unstructured = P.tau != nullptr;
@@ -163,76 +186,82 @@ mask_update_nm_kernel(const float* __restrict__ score, const float* __restrict__
     const bool mix = P.beta_s > 0.0f;
     const int n = P.n_keep;
     NmStats gs;
-    for (int64_t g = (int64_t)blockIdx.x * kNmThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kNmThreads) {
-        const int64_t e = g * M;
-        float s[M], mp[M], G[M];
-        load_run<M>(score + e, s);
-        load_run<M>(mask + e, mp);
+    for (int64_t c = (int64_t)blockIdx.x * kNmThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kNmThreads) {
+        const int64_t e = c * E;
+        float s[E], mp[E], G[E], pm[E];
+        load_run<E>(score + e, s);
+        load_run<E>(mask + e, mp);
+        if (P.pen != 0.0f && P.pen_mask != nullptr) load_run<E>(P.pen_mask + e, pm);
 #pragma unroll
-        for (int i = 0; i < M; ++i) {
+        for (int i = 0; i < E; ++i) {
             s[i] = __fmul_rn(__fsub_rn(s[i], mu), inv_sigma);
             if (P.score_bf16) s[i] = bf16_round_int(s[i]);
         }
-        float tau = tau_global;
-        uint32_t ks = 0;
-        if (!unstructured || mix) {
-            float t;
-            ks = topn_keep_tau<M>(s, n, t);
-            if (!unstructured) tau = t;
-        }
+        uint32_t kn_all = 0;
 #pragma unroll
-        for (int i = 0; i < M; ++i) {
-            const float top = ((ks >> i) & 1u) ? 1.0f : 0.0f;
-            float gi;
-            if (exact) gi = top;
-            else {
-                gi = fast_rcp(1.0f + fast_ex2(__fmul_rn(__fsub_rn(s[i], tau), P.neg_log2e_over_t)));
-                if (P.score_bf16) gi = bf16_round_int(gi);
+        for (int g = 0; g < GPT; ++g) {
+            const int o = g * M;
+            float tau = tau_global;
+            uint32_t ks = 0;
+            if (!unstructured || mix) {
+                float t;
+                ks = keep_tau_fast<M>(s + o, n, t);
+                if (!unstructured) tau = t;
             }
-            if (mix) {
-                gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), __fmul_rn(P.beta_s, top));
-                if (P.score_bf16) gi = bf16_round_int(gi);
-            }
-            G[i] = gi;
-        }
-        if (P.pen != 0.0f) {
-            float pm[M];
-            if (P.pen_mask != nullptr) load_run<M>(P.pen_mask + e, pm);
-            else {
-#pragma unroll
-                for (int i = 0; i < M; ++i) pm[i] = mp[i];
-            }
-            if (P.penalty_mode == SF_PENALTY_TOPN) {
-                const uint32_t kg = topn_keep<M>(G, n);
-#pragma unroll
-                for (int i = 0; i < M; ++i)
-                    G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, __fsub_rn(pm[i], ((kg >> i) & 1u) ? 1.0f : 0.0f)));
-            } else if (P.penalty_mode == SF_PENALTY_MID) {
-#pragma unroll
-                for (int i = 0; i < M; ++i)
-                    G[i] = __fsub_rn(G[i], __fmul_rn(P.pen, __fsub_rn(1.0f, __fmul_rn(2.0f, pm[i]))));
-            }
-#pragma unroll
-            for (int i = 0; i < M; ++i) G[i] = fminf(fmaxf(G[i], 0.0f), 1.0f);
-        }
-        if (P.binarize) {
 #pragma unroll
             for (int i = 0; i < M; ++i) {
-                if (G[i] < 0.5f) G[i] = __fmul_rn(G[i], P.bin_lo);
-                else if (G[i] > 0.5f) G[i] = __fmul_rn(G[i], P.bin_hi);
+                const float top = ((ks >> i) & 1u) ? 1.0f : 0.0f;
+                float gi;
+                if (exact) gi = top;
+                else {
+                    gi = fast_rcp(1.0f + fast_ex2(__fmul_rn(__fsub_rn(s[o + i], tau), P.neg_log2e_over_t)));
+                    if (P.score_bf16) gi = bf16_round_int(gi);
+                }
+                if (mix) {
+                    gi = __fadd_rn(__fmul_rn(P.one_minus_beta_s, gi), __fmul_rn(P.beta_s, top));
+                    if (P.score_bf16) gi = bf16_round_int(gi);
+                }
+                G[o + i] = gi;
             }
+            if (P.pen != 0.0f) {
+                if (P.penalty_mode == SF_PENALTY_TOPN) {
+                    const uint32_t kg = keep_fast<M>(G + o, n);
+#pragma unroll
+                    for (int i = 0; i < M; ++i) {
+                        const float from = P.pen_mask != nullptr ? pm[o + i] : mp[o + i];
+                        G[o + i] = __fsub_rn(G[o + i], __fmul_rn(P.pen, __fsub_rn(from, ((kg >> i) & 1u) ? 1.0f : 0.0f)));
+                    }
+                } else if (P.penalty_mode == SF_PENALTY_MID) {
+#pragma unroll
+                    for (int i = 0; i < M; ++i) {
+                        const float from = P.pen_mask != nullptr ? pm[o + i] : mp[o + i];
+                        G[o + i] = __fsub_rn(G[o + i], __fmul_rn(P.pen, __fsub_rn(1.0f, __fmul_rn(2.0f, from))));
+                    }
+                }
+#pragma unroll
+                for (int i = 0; i < M; ++i) G[o + i] = fminf(fmaxf(G[o + i], 0.0f), 1.0f);
+            }
+            if (P.binarize) {
+#pragma unroll
+                for (int i = 0; i < M; ++i) {
+                    if (G[o + i] < 0.5f) G[o + i] = __fmul_rn(G[o + i], P.bin_lo);
+                    else if (G[o + i] > 0.5f) G[o + i] = __fmul_rn(G[o + i], P.bin_hi);
+                }
+            }
+            const uint32_t kp = keep_fast<M>(mp + o, n);
+            // the new mask takes the place of the gate
+#pragma unroll
+            for (int i = 0; i < M; ++i)
+                G[o + i] = __saturatef(__fmaf_rn(P.a, G[o + i], __fmul_rn(mp[o + i], P.one_minus_a)));
+            const uint32_t kn = keep_fast<M>(G + o, n);
+            gs.flips += __popc(kp ^ kn);
+            kn_all |= kn << (o & 31);
         }
-        const uint32_t kp = topn_keep<M>(mp, n);
-        // the new mask takes the place of the gate
+        store_run<E>(mask + e, G);
 #pragma unroll
-        for (int i = 0; i < M; ++i) G[i] = __saturatef(__fmaf_rn(P.a, G[i], __fmul_rn(mp[i], P.one_minus_a)));
-        const uint32_t kn = topn_keep<M>(G, n);
-        gs.flips += __popc(kp ^ kn);
-        store_run<M>(mask + e, G);
-#pragma unroll
-        for (int i = 0; i < M; ++i) {
+        for (int i = 0; i < E; ++i) {
             const float mv = G[i];
-            const bool top = (kn >> i) & 1u;
+            const bool top = (kn_all >> i) & 1u;
             gs.sum_m += mv;
             gs.sum_m1m += __fmaf_rn(-mv, mv, mv);
             gs.sum_top += top ? mv : 0.0f;
@@ -240,18 +269,17 @@ mask_update_nm_kernel(const float* __restrict__ score, const float* __restrict__
             // hx * mask + (1 - hx) * hard, two roundings as the reference's tensor expression
             if (!P.soft_only) G[i] = __fadd_rn(__fmul_rn(P.hx, mv), top ? P.one_minus_hx : 0.0f);
         }
-        if (wm != nullptr) store_product_run<M>(wm + e, W + e, G);
+        if (wm != nullptr) store_product_run<E>(wm + e, W + e, G);
     }
     nm_reduce_stats(gs, stats);
 }
 
-// hard view of a soft mask (generic row strides), and / or the masked weight
-// W * (hx m + (1 - hx) hard) of a contiguous layer
-template <typename TI, typename TO, typename TW, int M>
+// hard 0/1 view of a soft mask (generic row strides, fp32 or bf16; NaN counts as the largest value, as
+// in a stable descending sort of the group)
+template <typename TI, typename TO, int M>
 __global__ void __launch_bounds__(kNmThreads)
-project_nm_kernel(const TI* __restrict__ soft, int64_t ld_soft, TO* __restrict__ hard, int64_t ld_hard,
-                  const TW* __restrict__ W, TW* __restrict__ wm, int64_t rows, int64_t groups_per_row, int n, float hx,
-                  float one_minus_hx, int soft_only) {
+project_nm_kernel(const TI* __restrict__ soft, int64_t ld_soft, TO* __restrict__ hard, int64_t ld_hard, int64_t rows,
+                  int64_t groups_per_row, int n) {
     const int64_t groups = rows * groups_per_row;
     for (int64_t g = (int64_t)blockIdx.x * kNmThreads + threadIdx.x; g < groups; g += (int64_t)gridDim.x * kNmThreads) {
         const int64_t r = g / groups_per_row, c = (g - r * groups_per_row) * M;
@@ -260,19 +288,30 @@ project_nm_kernel(const TI* __restrict__ soft, int64_t ld_soft, TO* __restrict__
 #pragma unroll
         for (int i = 0; i < M; ++i) m[i] = (float)src[i];
         const uint32_t k = topn_keep<M>(m, n);
-        if (hard != nullptr) {
-            TO* dst = hard + r * ld_hard + c;
+        TO* dst = hard + r * ld_hard + c;
 #pragma unroll
-            for (int i = 0; i < M; ++i) dst[i] = (TO)(((k >> i) & 1u) ? 1.0f : 0.0f);
-        }
-        if (wm != nullptr) {
-            float eff[M];
+        for (int i = 0; i < M; ++i) dst[i] = (TO)(((k >> i) & 1u) ? 1.0f : 0.0f);
+    }
+}
+
+// wm = W * cast(hx m + (1 - hx) topN(m)) of a contiguous layer (the soft mask holds no NaN)
+template <typename TW, int M, int GPT>
+__global__ void __launch_bounds__(kNmThreads)
+effective_weight_nm_kernel(const float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm, int64_t chunks,
+                           int n, float hx, float one_minus_hx, int soft_only) {
+    constexpr int E = GPT * M;
+    for (int64_t c = (int64_t)blockIdx.x * kNmThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kNmThreads) {
+        const int64_t e = c * E;
+        float m[E];
+        load_run<E>(mask + e, m);
+        if (!soft_only) {
+            uint32_t keep = 0;
 #pragma unroll
-            for (int i = 0; i < M; ++i)
-                eff[i] = soft_only ? m[i] : __fadd_rn(__fmul_rn(hx, m[i]), ((k >> i) & 1u) ? one_minus_hx : 0.0f);
-            const int64_t e = g * M;  // W, wm contiguous with ld = cols
-            store_product_run<M>(wm + e, W + e, eff);
+            for (int g = 0; g < GPT; ++g) keep |= keep_fast<M>(m + g * M, n) << ((g * M) & 31);
+#pragma unroll
+            for (int i = 0; i < E; ++i) m[i] = __fadd_rn(__fmul_rn(hx, m[i]), ((keep >> i) & 1u) ? one_minus_hx : 0.0f);
         }
+        store_product_run<E>(wm + e, W + e, m);
     }
 }
 
@@ -282,11 +321,12 @@ static int nm_grid(int64_t groups) {
     return (int)(g < cap ? (g < 1 ? 1 : g) : cap);
 }
 
-template <typename TW, int M>
+template <typename TW, int M, int GPT>
 static int launch_update(const float* score, const float* norm, float* mask, const void* W, void* wm, double* stats,
                          int64_t groups, const NmUpdateParams& P, cudaStream_t st) {
-    mask_update_nm_kernel<TW, M><<<nm_grid(groups), kNmThreads, 0, st>>>(score, norm, mask, (const TW*)W, (TW*)wm, stats,
-                                                                       groups, P);
+    const int64_t chunks = groups / GPT;
+    mask_update_nm_kernel<TW, M, GPT><<<nm_grid(chunks), kNmThreads, 0, st>>>(score, norm, mask, (const TW*)W, (TW*)wm,
+                                                                            stats, chunks, P);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
@@ -295,25 +335,28 @@ template <typename TW>
 static int dispatch_update(int m, const float* score, const float* norm, float* mask, const void* W, void* wm,
                            double* stats, int64_t groups, const NmUpdateParams& P, cudaStream_t st) {
     switch (m) {
-        case 2: return launch_update<TW, 2>(score, norm, mask, W, wm, stats, groups, P, st);
-        case 4: return launch_update<TW, 4>(score, norm, mask, W, wm, stats, groups, P, st);
-        case 8: return launch_update<TW, 8>(score, norm, mask, W, wm, stats, groups, P, st);
-        case 16: return launch_update<TW, 16>(score, norm, mask, W, wm, stats, groups, P, st);
-        case 32: return launch_update<TW, 32>(score, norm, mask, W, wm, stats, groups, P, st);
+        case 2:
+            if (groups % 4 == 0) return launch_update<TW, 2, 4>(score, norm, mask, W, wm, stats, groups, P, st);
+            return launch_update<TW, 2, 1>(score, norm, mask, W, wm, stats, groups, P, st);
+        case 4:
+            if (groups % 2 == 0) return launch_update<TW, 4, 2>(score, norm, mask, W, wm, stats, groups, P, st);
+            return launch_update<TW, 4, 1>(score, norm, mask, W, wm, stats, groups, P, st);
+        case 8: return launch_update<TW, 8, 1>(score, norm, mask, W, wm, stats, groups, P, st);
+        case 16: return launch_update<TW, 16, 1>(score, norm, mask, W, wm, stats, groups, P, st);
+        case 32: return launch_update<TW, 32, 1>(score, norm, mask, W, wm, stats, groups, P, st);
     }
     return fail(SF_ERR_UNSUPPORTED, "N:M mask update: M=%d is not one of 2, 4, 8, 16, 32", m);
 }
 
-template <typename TI, typename TO, typename TW>
-static int dispatch_project(int m, const void* soft, int64_t ld_soft, void* hard, int64_t ld_hard, const void* W, void* wm,
-                            int64_t rows, int64_t cols, int n, double hx, int soft_only, cudaStream_t st) {
+template <typename TI, typename TO>
+static int dispatch_project(int m, const void* soft, int64_t ld_soft, void* hard, int64_t ld_hard, int64_t rows, int64_t cols,
+                            int n, cudaStream_t st) {
     const int64_t gpr = cols / m;
     const int grid = nm_grid(rows * gpr);
-#define SF_NM_PROJECT(MM)                                                                                              \
-    case MM:                                                                                                           \
-        project_nm_kernel<TI, TO, TW, MM><<<grid, kNmThreads, 0, st>>>((const TI*)soft, ld_soft, (TO*)hard, ld_hard,   \
-                                                                      (const TW*)W, (TW*)wm, rows, gpr, n, (float)hx,     \
-                                                                      (float)(1.0 - hx), soft_only);                  \
+#define SF_NM_PROJECT(MM)                                                                                               \
+    case MM:                                                                                                            \
+        project_nm_kernel<TI, TO, MM><<<grid, kNmThreads, 0, st>>>((const TI*)soft, ld_soft, (TO*)hard, ld_hard, rows,   \
+                                                                  gpr, n);                                              \
         break;
     switch (m) {
         SF_NM_PROJECT(2)
@@ -335,6 +378,33 @@ static int check_group(const char* who, int n_keep, int m_group, int64_t rows, i
     if (rows <= 0 || cols <= 0 || cols % m_group != 0)
         return fail(SF_ERR_BAD_ARG, "%s: cols=%lld must be a multiple of M=%d", who, (long long)cols, m_group);
     return SF_OK;
+}
+
+template <typename TW, int M, int GPT>
+static int launch_effective(const float* mask, const void* W, void* wm, int64_t groups, int n, double hx, int soft_only,
+                            cudaStream_t st) {
+    const int64_t chunks = groups / GPT;
+    effective_weight_nm_kernel<TW, M, GPT><<<nm_grid(chunks), kNmThreads, 0, st>>>(mask, (const TW*)W, (TW*)wm, chunks, n,
+                                                                                 (float)hx, (float)(1.0 - hx), soft_only);
+    SF_CHECK_CUDA(cudaGetLastError());
+    return SF_OK;
+}
+
+template <typename TW>
+static int dispatch_effective(int m, const float* mask, const void* W, void* wm, int64_t groups, int n, double hx,
+                              int soft_only, cudaStream_t st) {
+    switch (m) {
+        case 2:
+            if (groups % 4 == 0) return launch_effective<TW, 2, 4>(mask, W, wm, groups, n, hx, soft_only, st);
+            return launch_effective<TW, 2, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+        case 4:
+            if (groups % 2 == 0) return launch_effective<TW, 4, 2>(mask, W, wm, groups, n, hx, soft_only, st);
+            return launch_effective<TW, 4, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+        case 8: return launch_effective<TW, 8, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+        case 16: return launch_effective<TW, 16, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+        case 32: return launch_effective<TW, 32, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+    }
+    return fail(SF_ERR_UNSUPPORTED, "N:M masked weight: M=%d is not one of 2, 4, 8, 16, 32", m);
 }
 
 }  // namespace sf
@@ -390,12 +460,12 @@ int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, i
                  "sf_project_nm: dtypes must be SF_F32 or SF_BF16");
     cudaStream_t st = (cudaStream_t)stream;
     if (in_dtype == SF_F32 && out_dtype == SF_F32)
-        return dispatch_project<float, float, float>(m_group, soft, ld_soft, hard, ld_hard, nullptr, nullptr, rows, cols, n_keep, 1.0, 1, st);
+        return dispatch_project<float, float>(m_group, soft, ld_soft, hard, ld_hard, rows, cols, n_keep, st);
     if (in_dtype == SF_F32)
-        return dispatch_project<float, __nv_bfloat16, float>(m_group, soft, ld_soft, hard, ld_hard, nullptr, nullptr, rows, cols, n_keep, 1.0, 1, st);
+        return dispatch_project<float, __nv_bfloat16>(m_group, soft, ld_soft, hard, ld_hard, rows, cols, n_keep, st);
     if (out_dtype == SF_F32)
-        return dispatch_project<__nv_bfloat16, float, float>(m_group, soft, ld_soft, hard, ld_hard, nullptr, nullptr, rows, cols, n_keep, 1.0, 1, st);
-    return dispatch_project<__nv_bfloat16, __nv_bfloat16, float>(m_group, soft, ld_soft, hard, ld_hard, nullptr, nullptr, rows, cols, n_keep, 1.0, 1, st);
+        return dispatch_project<__nv_bfloat16, float>(m_group, soft, ld_soft, hard, ld_hard, rows, cols, n_keep, st);
+    return dispatch_project<__nv_bfloat16, __nv_bfloat16>(m_group, soft, ld_soft, hard, ld_hard, rows, cols, n_keep, st);
 }
 
 int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* wm, int64_t rows, int64_t cols, int n_keep,
@@ -407,10 +477,9 @@ int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* 
         return fail(SF_ERR_ALIGNMENT, "sf_effective_weight_nm: tensors must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
     const int soft_only = (finalized != 0) || hx >= 1.0 - 1e-6;
-    if (w_dtype == SF_BF16)
-        return dispatch_project<float, float, __nv_bfloat16>(m_group, mask, cols, nullptr, cols, W, wm, rows, cols, n_keep, hx,
-                                                            soft_only, st);
-    return dispatch_project<float, float, float>(m_group, mask, cols, nullptr, cols, W, wm, rows, cols, n_keep, hx, soft_only, st);
+    const int64_t groups = rows * (cols / m_group);
+    if (w_dtype == SF_BF16) return dispatch_effective<__nv_bfloat16>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, st);
+    return dispatch_effective<float>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, st);
 }
 
 }  // extern "C"
