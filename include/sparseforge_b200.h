@@ -56,6 +56,12 @@ typedef enum {
     SF_PENALTY_MID = 2   /* 'mid' (:1567-1570) */
 } sf_penalty_mode;
 
+/* Hard view of a soft mask in the general N:M entry points. */
+typedef enum {
+    SF_HARD_TOPN = 0,     /* top N of every group of M ('structured', legacy/sparse_modeling.py:720-735) */
+    SF_HARD_THRESHOLD = 1 /* mask > 0.5 ('unstructured', :526-527); N:M then only shapes beta mixing and the top-N pull */
+} sf_hard_view;
+
 SF_API int sf_version(void);
 SF_API const char* sf_last_error_string(void);
 
@@ -372,6 +378,9 @@ SF_API int sf_block_mask_apply(float* mask, const void* W, int w_dtype, void* wm
  *   update, legacy/utils.py:363-479), binarise push, EMA, hard = topN(mask), wm <- W * cast(hx mask + (1-hx) hard)
  *   (optional). stats as SF_MSTAT_* (the TOP2 / BOT2 slots hold the sums of the kept / dropped
  *   entries). One thread per group. M in {2, 4, 8, 16, 32}, 1 <= N < M, cols % M == 0.
+ * hard_view = SF_HARD_THRESHOLD makes the hard view (flip count, effective mask, kept / dropped sums)
+ *   mask > 0.5, the 'unstructured' hard mask of :526-527; the groups then only shape beta mixing and
+ *   the top-N pull, as in the reference.
  * sf_project_nm: hard 0/1 view of a soft mask (fp32 or bf16 in and out, row strides in elements).
  * sf_effective_weight_nm: wm <- W * cast(hx mask + (1 - hx) topN(mask)), or W * cast(mask) when
  *   finalized != 0 or hx >= 1 - 1e-6.
@@ -380,11 +389,12 @@ SF_API int sf_mask_update_nm(const float* score, const float* norm, const float*
                       float* mask, const void* W, int w_dtype, void* wm, double* stats, int64_t rows, int64_t cols, int n_keep,
                       int m_group, double temperature, double mask_lr, double pen, int penalty_mode,
                       double beta_s, double binarize_decay, double hx, int structured_exact, int score_bf16,
-                      void* stream);
+                      int hard_view, void* stream);
 SF_API int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, int out_dtype, int64_t ld_hard,
                   int64_t rows, int64_t cols, int n_keep, int m_group, void* stream);
 SF_API int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* wm, int64_t rows,
-                           int64_t cols, int n_keep, int m_group, double hx, int finalized, void* stream);
+                           int64_t cols, int n_keep, int m_group, double hx, int finalized, int hard_view,
+                           void* stream);
 
 /*
  * hard_mask_type 'block16': inside every 16 x 16 tile the keep_k entries with the largest soft-mask

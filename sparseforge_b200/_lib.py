@@ -46,9 +46,9 @@ _SIGNATURES = {
                                       _P, _P, _P, _P, c_int, _P]),
     "sf_mask_stats": (c_int, [_P, _P, c_int64, c_int64, _P]),
     "sf_mask_update_nm": (c_int, [_P, _P, _P, _P, _P, _P, c_int, _P, _P, c_int64, c_int64, c_int, c_int, c_double, c_double,
-                                  c_double, c_int, c_double, c_double, c_double, c_int, c_int, _P]),
+                                  c_double, c_int, c_double, c_double, c_double, c_int, c_int, c_int, _P]),
     "sf_project_nm": (c_int, [_P, c_int, c_int64, _P, c_int, c_int64, c_int64, c_int64, c_int, c_int, _P]),
-    "sf_effective_weight_nm": (c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int, c_double, c_int, _P]),
+    "sf_effective_weight_nm": (c_int, [_P, c_int, _P, _P, c_int64, c_int64, c_int, c_int, c_double, c_int, c_int, _P]),
     "sf_mask_update_tile16": (c_int, [_P, _P, _P, _P, _P, c_int, _P, _P, c_int64, c_int64, c_int, c_double, c_double, c_double,
                                       c_int, c_double, c_double, _P]),
     "sf_project_tile16": (c_int, [_P, _P, _P, c_int, _P, c_int64, c_int64, c_int, c_double, _P]),

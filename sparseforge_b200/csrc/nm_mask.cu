@@ -28,6 +28,7 @@ struct NmUpdateParams {
     int score_bf16;
     const float* tau;       // unstructured gate threshold (device scalar) or null
     const float* pen_mask;  // mask the penalty pull is taken from (GLU joint update); null = the layer's own
+    int hard_threshold;     // hard view = (mask > 0.5) instead of the top N of every group ('unstructured')
 };
 
 // M consecutive values -> floats, with the widest accesses the run allows (the run starts on a
@@ -143,6 +144,14 @@ __device__ __forceinline__ uint32_t keep_tau_fast(const float* x, int n, float& 
     return keep;
 }
 
+template <int M>
+__device__ __forceinline__ uint32_t above_half(const float* x) {
+    uint32_t keep = 0;
+#pragma unroll
+    for (int i = 0; i < M; ++i) keep |= (x[i] > 0.5f ? 1u : 0u) << i;
+    return keep;
+}
+
 struct NmStats {
     float sum_m = 0.f, sum_m1m = 0.f, sum_top = 0.f;
     int flips = 0, lt_half = 0;
@@ -248,12 +257,12 @@ mask_update_nm_kernel(const float* __restrict__ score, const float* __restrict__
                     else if (G[o + i] > 0.5f) G[o + i] = __fmul_rn(G[o + i], P.bin_hi);
                 }
             }
-            const uint32_t kp = keep_fast<M>(mp + o, n);
+            const uint32_t kp = P.hard_threshold ? above_half<M>(mp + o) : keep_fast<M>(mp + o, n);
             // the new mask takes the place of the gate
 #pragma unroll
             for (int i = 0; i < M; ++i)
                 G[o + i] = __saturatef(__fmaf_rn(P.a, G[o + i], __fmul_rn(mp[o + i], P.one_minus_a)));
-            const uint32_t kn = keep_fast<M>(G + o, n);
+            const uint32_t kn = P.hard_threshold ? above_half<M>(G + o) : keep_fast<M>(G + o, n);
             gs.flips += __popc(kp ^ kn);
             kn_all |= kn << (o & 31);
         }
@@ -298,7 +307,7 @@ project_nm_kernel(const TI* __restrict__ soft, int64_t ld_soft, TO* __restrict__
 template <typename TW, int M, int GPT>
 __global__ void __launch_bounds__(kNmThreads)
 effective_weight_nm_kernel(const float* __restrict__ mask, const TW* __restrict__ W, TW* __restrict__ wm, int64_t chunks,
-                           int n, float hx, float one_minus_hx, int soft_only) {
+                           int n, float hx, float one_minus_hx, int soft_only, int hard_threshold) {
     constexpr int E = GPT * M;
     for (int64_t c = (int64_t)blockIdx.x * kNmThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kNmThreads) {
         const int64_t e = c * E;
@@ -307,7 +316,8 @@ effective_weight_nm_kernel(const float* __restrict__ mask, const TW* __restrict_
         if (!soft_only) {
             uint32_t keep = 0;
 #pragma unroll
-            for (int g = 0; g < GPT; ++g) keep |= keep_fast<M>(m + g * M, n) << ((g * M) & 31);
+            for (int g = 0; g < GPT; ++g)
+                keep |= (hard_threshold ? above_half<M>(m + g * M) : keep_fast<M>(m + g * M, n)) << ((g * M) & 31);
 #pragma unroll
             for (int i = 0; i < E; ++i) m[i] = __fadd_rn(__fmul_rn(hx, m[i]), ((keep >> i) & 1u) ? one_minus_hx : 0.0f);
         }
@@ -382,27 +392,28 @@ static int check_group(const char* who, int n_keep, int m_group, int64_t rows, i
 
 template <typename TW, int M, int GPT>
 static int launch_effective(const float* mask, const void* W, void* wm, int64_t groups, int n, double hx, int soft_only,
-                            cudaStream_t st) {
+                            int hard_threshold, cudaStream_t st) {
     const int64_t chunks = groups / GPT;
     effective_weight_nm_kernel<TW, M, GPT><<<nm_grid(chunks), kNmThreads, 0, st>>>(mask, (const TW*)W, (TW*)wm, chunks, n,
-                                                                                 (float)hx, (float)(1.0 - hx), soft_only);
+                                                                                 (float)hx, (float)(1.0 - hx), soft_only,
+                                                                                 hard_threshold);
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
 
 template <typename TW>
 static int dispatch_effective(int m, const float* mask, const void* W, void* wm, int64_t groups, int n, double hx,
-                              int soft_only, cudaStream_t st) {
+                              int soft_only, int hard_threshold, cudaStream_t st) {
     switch (m) {
         case 2:
-            if (groups % 4 == 0) return launch_effective<TW, 2, 4>(mask, W, wm, groups, n, hx, soft_only, st);
-            return launch_effective<TW, 2, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+            if (groups % 4 == 0) return launch_effective<TW, 2, 4>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
+            return launch_effective<TW, 2, 1>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
         case 4:
-            if (groups % 2 == 0) return launch_effective<TW, 4, 2>(mask, W, wm, groups, n, hx, soft_only, st);
-            return launch_effective<TW, 4, 1>(mask, W, wm, groups, n, hx, soft_only, st);
-        case 8: return launch_effective<TW, 8, 1>(mask, W, wm, groups, n, hx, soft_only, st);
-        case 16: return launch_effective<TW, 16, 1>(mask, W, wm, groups, n, hx, soft_only, st);
-        case 32: return launch_effective<TW, 32, 1>(mask, W, wm, groups, n, hx, soft_only, st);
+            if (groups % 2 == 0) return launch_effective<TW, 4, 2>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
+            return launch_effective<TW, 4, 1>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
+        case 8: return launch_effective<TW, 8, 1>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
+        case 16: return launch_effective<TW, 16, 1>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
+        case 32: return launch_effective<TW, 32, 1>(mask, W, wm, groups, n, hx, soft_only, hard_threshold, st);
     }
     return fail(SF_ERR_UNSUPPORTED, "N:M masked weight: M=%d is not one of 2, 4, 8, 16, 32", m);
 }
@@ -417,10 +428,11 @@ int sf_mask_update_nm(const float* score, const float* norm, const float* tau, c
                       int w_dtype,
                       void* wm, double* stats, int64_t rows, int64_t cols, int n_keep, int m_group, double temperature,
                       double mask_lr, double pen, int penalty_mode, double beta_s, double binarize_decay, double hx,
-                      int structured_exact, int score_bf16, void* stream) {
+                      int structured_exact, int score_bf16, int hard_view, void* stream) {
     SF_CHECK_ARG(score && norm && mask && stats, "sf_mask_update_nm: score, norm, mask, stats must be non-null");
     if (int rc = check_group("sf_mask_update_nm", n_keep, m_group, rows, cols)) return rc;
     SF_CHECK_ARG(penalty_mode >= 0 && penalty_mode <= 2, "sf_mask_update_nm: penalty_mode must be 0, 1 or 2");
+    SF_CHECK_ARG(hard_view == SF_HARD_TOPN || hard_view == SF_HARD_THRESHOLD, "sf_mask_update_nm: hard_view must be 0 or 1");
     SF_CHECK_ARG((wm == nullptr) || (W != nullptr), "sf_mask_update_nm: wm requested without W");
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_mask_update_nm: w_dtype must be SF_F32 or SF_BF16");
     if (!(aligned16(score) && aligned16(mask) && aligned16(W) && aligned16(wm) && aligned16(pen_mask)))
@@ -445,6 +457,7 @@ int sf_mask_update_nm(const float* score, const float* norm, const float* tau, c
     P.score_bf16 = score_bf16;
     P.tau = tau;
     P.pen_mask = pen_mask;
+    P.hard_threshold = hard_view == SF_HARD_THRESHOLD;
     SF_CHECK_CUDA(cudaMemsetAsync(stats, 0, SF_MSTAT_COUNT * sizeof(double), st));
     const int64_t groups = rows * (cols / m_group);
     if (w_dtype == SF_BF16) return dispatch_update<__nv_bfloat16>(m_group, score, norm, mask, W, wm, stats, groups, P, st);
@@ -469,17 +482,19 @@ int sf_project_nm(const void* soft, int in_dtype, int64_t ld_soft, void* hard, i
 }
 
 int sf_effective_weight_nm(const void* W, int w_dtype, const float* mask, void* wm, int64_t rows, int64_t cols, int n_keep,
-                           int m_group, double hx, int finalized, void* stream) {
+                           int m_group, double hx, int finalized, int hard_view, void* stream) {
     SF_CHECK_ARG(W && mask && wm, "sf_effective_weight_nm: W, mask, wm must be non-null");
     if (int rc = check_group("sf_effective_weight_nm", n_keep, m_group, rows, cols)) return rc;
     SF_CHECK_ARG(w_dtype == SF_F32 || w_dtype == SF_BF16, "sf_effective_weight_nm: w_dtype must be SF_F32 or SF_BF16");
     if (!(aligned16(W) && aligned16(mask) && aligned16(wm)))
         return fail(SF_ERR_ALIGNMENT, "sf_effective_weight_nm: tensors must be 16-byte aligned");
     cudaStream_t st = (cudaStream_t)stream;
+    SF_CHECK_ARG(hard_view == SF_HARD_TOPN || hard_view == SF_HARD_THRESHOLD, "sf_effective_weight_nm: hard_view must be 0 or 1");
     const int soft_only = (finalized != 0) || hx >= 1.0 - 1e-6;
+    const int hard_threshold = hard_view == SF_HARD_THRESHOLD;
     const int64_t groups = rows * (cols / m_group);
-    if (w_dtype == SF_BF16) return dispatch_effective<__nv_bfloat16>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, st);
-    return dispatch_effective<float>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, st);
+    if (w_dtype == SF_BF16) return dispatch_effective<__nv_bfloat16>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, hard_threshold, st);
+    return dispatch_effective<float>(m_group, mask, W, wm, groups, n_keep, hx, soft_only, hard_threshold, st);
 }
 
 }  // extern "C"

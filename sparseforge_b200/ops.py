@@ -203,8 +203,9 @@ def project_nm24(soft, *, out_dtype=None, want_hard=True, want_meta=False):
 
 def mask_update_nm(score, norm, mask, stats, n_keep, m_group, *, tau=None, W=None, wm=None, temperature=1.0, mask_lr=0.1,
                    pen=0.0, penalty_mode=_lib.PENALTY_NONE, beta_s=0.0, binarize_decay=0.0, hx=1.0,
-                   structured_exact=False, score_bf16=False, pen_mask=None) -> None:
-    """``mask_update_nm24`` for a general N:M (M in 2, 4, 8, 16, 32); no metadata output."""
+                   structured_exact=False, score_bf16=False, pen_mask=None, threshold_view=False) -> None:
+    """``mask_update_nm24`` for a general N:M (M in 2, 4, 8, 16, 32); no metadata output. With
+    ``threshold_view`` the hard view is ``mask > 0.5`` (hard_mask_type 'unstructured')."""
     _cuda(score, norm, mask, stats, W, wm, tau, pen_mask)
     if mask.dim() != 2:
         raise ValueError("mask_update_nm: mask must be 2-D [out, in]")
@@ -220,8 +221,8 @@ def mask_update_nm(score, norm, mask, stats, n_keep, m_group, *, tau=None, W=Non
     check(lib().sf_mask_update_nm(_p(score), _p(norm), _p(tau), _p(pen_mask), _p(mask), _p(W), _dt(W) if W is not None else SF_F32,
                                   _p(wm), _p(stats), rows, cols, int(n_keep), int(m_group), float(temperature),
                                   float(mask_lr), float(pen), int(penalty_mode), float(beta_s), float(binarize_decay),
-                                  float(hx), int(bool(structured_exact)), int(bool(score_bf16)), _stream()),
-          "sf_mask_update_nm")
+                                  float(hx), int(bool(structured_exact)), int(bool(score_bf16)), int(bool(threshold_view)),
+                                  _stream()), "sf_mask_update_nm")
 
 
 def project_nm(soft, n_keep, m_group, *, out_dtype=None):
@@ -242,14 +243,14 @@ def project_nm(soft, n_keep, m_group, *, out_dtype=None):
     return hard
 
 
-def effective_weight_nm(W, mask, wm, n_keep, m_group, *, hx=1.0, finalized=False) -> None:
+def effective_weight_nm(W, mask, wm, n_keep, m_group, *, hx=1.0, finalized=False, threshold_view=False) -> None:
     """wm <- W * cast(hx mask + (1 - hx) topN-of-M(mask)) for a general N:M."""
     _cuda(W, mask, wm)
     if mask.dtype != torch.float32:
         raise TypeError("effective_weight_nm: mask must be float32")
     rows, cols = W.shape
     check(lib().sf_effective_weight_nm(_p(W), _dt(W), _p(mask), _p(wm), rows, cols, int(n_keep), int(m_group), float(hx),
-                                       int(bool(finalized)), _stream()), "sf_effective_weight_nm")
+                                       int(bool(finalized)), int(bool(threshold_view)), _stream()), "sf_effective_weight_nm")
 
 
 def effective_weight(W, mask, wm, *, meta=None, hx=1.0, finalized=False, scale=1.0) -> None:

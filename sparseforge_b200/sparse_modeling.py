@@ -416,10 +416,16 @@ class SparseLinear(nn.Linear):
             self._wm = torch.empty_like(self.weight.data)
             self._wm_key = None
 
+    def _threshold_view(self) -> bool:
+        """True when the hard view is ``mask > 0.5`` (hard_mask_type 'unstructured',
+        legacy/sparse_modeling.py:526-527)."""
+        return self._resolved_hard_type() == "unstructured"
+
     def _general_nm(self) -> bool:
-        """True when the layer's groups are not 2:4: the one-thread-per-group N:M kernels then take
-        the place of the 2:4 ones (no sparse tensor-core metadata, no fused optimizer output)."""
-        return (int(self.N), int(self.M)) != (2, 4)
+        """True when the hard view is not top-2-of-4 (other N:M, or the 0.5 threshold): the general
+        one-thread-per-group kernels then take the place of the 2:4 ones (no sparse tensor-core metadata, no
+        fused optimizer output)."""
+        return self._threshold_view() or (int(self.N), int(self.M)) != (2, 4)
 
     def _check_2to4(self):
         """Sizes and modes the N:M kernels (2:4 or general) accept."""
@@ -428,7 +434,7 @@ class SparseLinear(nn.Linear):
             if self.in_features % 8 != 0:
                 raise ValueError(f"in_features ({self.in_features}) must be a multiple of 8 for the 2:4 kernels")
             return
-        if self._resolved_hard_type() != "structured":
+        if self._resolved_hard_type() not in ("structured", "unstructured"):
             raise NotImplementedError(
                 f"N:M = {n}:{m} with hard_mask_type={self._resolved_hard_type()!r}: gate groups and hard view must agree "
                 "(use hard_mask_type='structured' or 'match' with mask_type='structured')")
@@ -591,7 +597,7 @@ class SparseLinear(nn.Linear):
         if (not managed) or self._wm_key != key or getattr(self.weight, "_sf_wm_stale", True):
             if self._general_nm():
                 ops.effective_weight_nm(self.weight.data, self.mask.data, self._wm, int(self.N), int(self.M),
-                                        hx=float(self.hardening_x), finalized=key[5])
+                                        hx=float(self.hardening_x), finalized=key[5], threshold_view=self._threshold_view())
             else:
                 ops.effective_weight(self.weight.data, self.mask.data, self._wm, meta=self._meta,
                                      hx=float(self.hardening_x), finalized=key[5])
@@ -617,7 +623,8 @@ class SparseLinear(nn.Linear):
             ops.project_tile16(self.mask.data, self._tile16_keep_k(), want_hard=False, W=src, wm=dst,
                                hx=1.0 if fin else hx)
         elif self._general_nm():
-            ops.effective_weight_nm(src, self.mask.data, dst, int(self.N), int(self.M), hx=hx, finalized=fin)
+            ops.effective_weight_nm(src, self.mask.data, dst, int(self.N), int(self.M), hx=hx, finalized=fin,
+                                    threshold_view=self._threshold_view())
         else:
             ops.effective_weight(src, self.mask.data, dst, hx=hx, finalized=fin)
 
@@ -697,7 +704,8 @@ class SparseLinear(nn.Linear):
             return FusedMaskedLinearSTE.apply(x, self.weight, self.bias, ones, 0.0, 1.0, self.weight.detach(), 1.0, True)
         if self.mode != "sparse_forward":
             raise ValueError(f"Invalid mode: {self.mode}")
-        if self._resolved_hard_type() not in ("structured", "nm_2_4", "block_sparse16", "block_sparse32", "block16"):
+        if self._resolved_hard_type() not in ("structured", "nm_2_4", "unstructured", "block_sparse16", "block_sparse32",
+                                              "block16"):
             raise NotImplementedError(f"hard mask type {self._resolved_hard_type()!r} is outside the kernel paths")
         hx = float(getattr(self, "hardening_x", 1.0))
         finalized = bool(getattr(self, "_hardening_finalized", False))
@@ -958,7 +966,8 @@ class SparseLinear(nn.Linear):
                          structured_exact=bool(getattr(self.cfg, "structured_exact", False)),
                          score_bf16=self._score_is_bf16())
         if self._general_nm():
-            ops.mask_update_nm(self._score, self._norm, G, stats, int(self.N), int(self.M), **gate_args)
+            ops.mask_update_nm(self._score, self._norm, G, stats, int(self.N), int(self.M),
+                               threshold_view=self._threshold_view(), **gate_args)
         else:
             ops.mask_update_nm24(self._score, self._norm, G, stats, **gate_args)
         if not self._is_placeholder("frozen_mask_flags"):
@@ -974,10 +983,10 @@ class SparseLinear(nn.Linear):
             if self.mask_type != "unstructured":
                 raise NotImplementedError("block hard masks are built for mask_type='unstructured'")
             return
-        if self._resolved_hard_type() not in ("structured", "nm_2_4"):
+        if self._resolved_hard_type() not in ("structured", "nm_2_4", "unstructured"):
             raise NotImplementedError(
-                f"hard mask type {self._resolved_hard_type()!r} with mask_type={self.mask_type!r} is outside the 2:4 "
-                "kernel path (use hard_mask_type='nm_2_4' or mask_type='structured')")
+                f"hard mask type {self._resolved_hard_type()!r} with mask_type={self.mask_type!r} is outside the "
+                "kernel paths")
 
     @torch.no_grad()
     def _tau_unstructured(self, scores: torch.Tensor, sparsity: float, sample_idx: Optional[torch.Tensor] = None):
@@ -1045,6 +1054,8 @@ class SparseLinear(nn.Linear):
         mode = str(getattr(self.cfg, "mask_penalty_mode", "mid") or "mid")
         if lam != 0.0 and mode not in ("mid", "structured_topn", "nm_2_4"):
             raise NotImplementedError(f"mask_penalty_mode={mode!r} is outside the 2:4 kernel path")
+        if lam != 0.0 and mode == "nm_2_4" and (int(self.N), int(self.M)) != (2, 4):
+            raise NotImplementedError(f"mask_penalty_mode='nm_2_4' pulls towards top-2-of-4; the layer's groups are {self.N}:{self.M}")
         pmode = _lib.PENALTY_MID if mode == "mid" else _lib.PENALTY_TOPN
         self._launch_mask_update(self._score, self._norm, step, pen=float(self.mask_penalty_lr) * lam,
                                  pmode=pmode if lam != 0.0 else 0, tau=self._gate_tau(step), owner=self,
@@ -1160,7 +1171,7 @@ class SparseLinear(nn.Linear):
             if bands:
                 raise NotImplementedError(f"freeze bands are built for 2:4 groups (the layer has N:M = {self.N}:{self.M})")
             ops.mask_update_nm(score, norm, self.mask.data, self._stats, int(self.N), int(self.M), pen_mask=pen_mask,
-                               **common)
+                               threshold_view=self._threshold_view(), **common)
         else:
             ops.mask_update_nm24(score, norm, self.mask.data, self._stats, meta=self._meta, pen_mask=pen_mask,
                                  **common, **bands)

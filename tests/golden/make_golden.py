@@ -802,6 +802,48 @@ def case_nm():
     save("nm_general", d)
 
 
+def case_unstructured_hard():
+    """mask_type='unstructured' with the matching hard view ``mask > 0.5`` (legacy/sparse_modeling.py:526-527):
+    quantile gate, penalty pulls, beta mixing (N:M groups only shape the pull and the mixing), EMA, flip count
+    by the threshold, and a masked forward / backward with hardening active."""
+    torch.manual_seed(59)
+    out_f, in_f = 48, 128
+    d = {}
+    variants = [
+        ("mid", torch.float32, dict(mask_penalty_mode="mid"), 0.6),
+        ("topn", torch.float32, dict(mask_penalty_mode="structured_topn"), 0.5),
+        ("beta", torch.float32, dict(mask_penalty_mode="mid", beta_structural_start=0, beta_structural_end=10), 0.2),
+        ("bin", torch.float32, dict(mask_penalty_mode="mid", mask_binarize_decay=0.05), 0.0),
+        ("bf16", torch.bfloat16, dict(mask_penalty_mode="mid"), 0.4),
+    ]
+    d["variants"] = np.asarray([v[0] for v in variants])
+    for tag, dtype, kw, lam in variants:
+        W = torch.randn(out_f, in_f) * 0.02
+        layer = make_layer(out_f, in_f, W, dtype, mask_type="unstructured", mask_metric="hessian_obd", N=2, M=4,
+                           sparsity_ratio=0.5, mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.2, mask_penalty_lr=0.15,
+                           mask_hardening_start=2, mask_hardening_duration=8, **kw)
+        layer.mask.data = torch.rand(out_f, in_f)
+        layer.hessian_diag.data = torch.rand(out_f, in_f) + 0.1
+        step = 4
+        put(d, f"{tag}_W", layer.weight.data); put(d, f"{tag}_mask0", layer.mask.data); put(d, f"{tag}_H", layer.hessian_diag.data)
+        put(d, f"{tag}_lambda", lam); put(d, f"{tag}_step", step)
+        put(d, f"{tag}_T", layer._temperature(step)); put(d, f"{tag}_beta_s", layer._beta_structural(step))
+        put(d, f"{tag}_sparsity", layer._effective_sparsity(step))
+        put(d, f"{tag}_G", layer.compute_gate_target(step))
+        layer.update_mask(step, lambda_mid=lam)
+        put(d, f"{tag}_mask1", layer.mask.data); put(d, f"{tag}_hx", float(layer.hardening_x))
+        put(d, f"{tag}_flips", int(layer.weight.flipped_mask))
+        put(d, f"{tag}_hard1", layer._hard_mask_from_soft(layer.mask.data))
+        X = torch.randn(2, 12, in_f).to(dtype).requires_grad_(True)
+        dY = torch.randn(2, 12, out_f).to(dtype)
+        layer.weight.grad = None
+        Y = layer(X)
+        Y.backward(dY)
+        put(d, f"{tag}_X", X); put(d, f"{tag}_dY", dY); put(d, f"{tag}_Y", Y); put(d, f"{tag}_dX", X.grad)
+        put(d, f"{tag}_dW", layer.weight.grad)
+    save("unstructured_hard", d)
+
+
 if __name__ == "__main__":
     # `make_golden.py wanda ...` regenerates only the named single-function cases
     only = [a for a in sys.argv[1:] if not a.startswith("-")]

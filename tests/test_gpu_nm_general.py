@@ -339,3 +339,50 @@ def test_adamw_keeps_the_masked_weight_of_a_general_layer_current():
         opt.zero_grad(set_to_none=True)
         layer.update_mask(step)
         layer.hardening_x = 0.5
+
+
+UH_KW = {"mid": dict(mask_penalty_mode="mid"), "topn": dict(mask_penalty_mode="structured_topn"),
+         "beta": dict(mask_penalty_mode="mid", beta_structural_start=0, beta_structural_end=10),
+         "bin": dict(mask_penalty_mode="mid", mask_binarize_decay=0.05), "bf16": dict(mask_penalty_mode="mid")}
+
+
+def test_unstructured_hard_view_follows_the_reference():
+    """mask_type='unstructured' with its own hard view (mask > 0.5, legacy/sparse_modeling.py:526-527):
+    gate, update, flip count, masked forward / backward of SparseLinear against the recorded reference run."""
+    import sparseforge_b200 as sf
+
+    g = Golden("unstructured_hard")
+    for tag in g["variants"]:
+        W, H, mask0 = g[f"{tag}_W"], g[f"{tag}_H"], g[f"{tag}_mask0"]
+        tol = BF16_TOL if W.dtype == torch.bfloat16 else F32_TOL
+        cfg = sf.SparseLinearConfig(mask_type="unstructured", mask_metric="hessian_obd", N=2, M=4, sparsity_ratio=0.5,
+                                    mask_update_period=1, sparsity_warmup_steps=0, mask_lr=0.2, mask_penalty_lr=0.15,
+                                    mask_hardening_start=2, mask_hardening_duration=8, **UH_KW[tag])
+        layer = sf.SparseLinear(W.shape[1], W.shape[0], sparselinear_config=cfg, bias=False).to(DEV).to(W.dtype)
+        layer.weight.data.copy_(W.to(DEV))
+        layer.initialize()
+        layer.mask.data.copy_(mask0.to(DEV))
+        layer.hessian_diag.data.copy_(H.to(DEV))
+        layer.invalidate_masked_weight()
+        assert layer._threshold_view() and layer._general_nm() and not layer._is_2to4_view()
+        step = int(g.scalar(f"{tag}_step"))
+        assert rel_err(layer.compute_gate_target(step).cpu().float(), g[f"{tag}_G"].float()) <= tol, tag
+        layer.update_mask(step, lambda_mid=g.scalar(f"{tag}_lambda"))
+        assert layer.hardening_x == pytest.approx(g.scalar(f"{tag}_hx"))
+        got = layer.mask.data.cpu()
+        assert rel_err(got, g[f"{tag}_mask1"]) <= tol, tag
+        # flips: an exact function of the masks the kernel produced; equal to the reference's unless an entry
+        # sits within rounding of 0.5
+        assert int(layer.weight.flipped_mask) == O.flip_count(mask0, got, "unstructured"), tag
+        hard = layer._hard_mask_from_soft(layer.mask.data).cpu()
+        if torch.equal(hard, g[f"{tag}_hard1"]):
+            assert int(layer.weight.flipped_mask) == g.scalar(f"{tag}_flips"), tag
+        assert (hard != g[f"{tag}_hard1"]).float().mean() <= 2e-3, tag
+        X = g[f"{tag}_X"].to(DEV).requires_grad_(True)
+        Y = layer(X)
+        Y.backward(g[f"{tag}_dY"].to(DEV))
+        assert rel_err(Y.detach().cpu().float(), g[f"{tag}_Y"].float()) <= tol, tag
+        assert rel_err(X.grad.cpu().float(), g[f"{tag}_dX"].float()) <= tol, tag
+        assert rel_err(layer.weight.grad.cpu().float(), g[f"{tag}_dW"].float()) <= tol, tag
+        with pytest.raises(NotImplementedError):
+            layer.compress_for_inference()

@@ -139,17 +139,22 @@ def test_general_nm_configurations_are_checked_on_the_host():
     with pytest.raises(NotImplementedError, match="2:4"):
         layer(4, 8).compress_for_inference()
     layer(2, 4)._check_strict_2to4("x")
+    thr = sf.SparseLinear(64, 8, sparselinear_config=sf.SparseLinearConfig(mask_type="unstructured"), bias=False)
+    assert thr._threshold_view() and thr._general_nm() and not thr._is_2to4_view()
+    thr._check_2to4()
+    thr._check_mask_modes()
 
     lib = _lib.lib()
     assert lib.sf_project_nm(16, 0, 96, 16, 0, 96, 4, 96, 2, 3, None) == -2  # M = 3
     assert b"M=3" in lib.sf_last_error_string()
     assert lib.sf_project_nm(16, 0, 64, 16, 0, 64, 4, 60, 4, 8, None) == -1  # 60 columns, M = 8
     assert lib.sf_project_nm(None, 0, 64, 16, 0, 64, 4, 64, 4, 8, None) == -1
-    assert lib.sf_effective_weight_nm(16, 1, 16, 16, 4, 64, 8, 8, 0.5, 0, None) == -1  # N = M
+    assert lib.sf_effective_weight_nm(16, 1, 16, 16, 4, 64, 8, 8, 0.5, 0, 0, None) == -1  # N = M
+    assert lib.sf_effective_weight_nm(16, 1, 16, 16, 4, 64, 4, 8, 0.5, 0, 2, None) == -1  # hard view 2
     assert lib.sf_mask_update_nm(16, 16, None, None, 16, None, 0, None, 16, 4, 64, 4, 8, 1.0, 0.1, 0.0, 3, 0.0, 0.0, 1.0, 0,
-                                 0, None) == -1  # penalty mode 3
+                                 0, 0, None) == -1  # penalty mode 3
     assert lib.sf_mask_update_nm(16, 16, None, None, 24, None, 0, None, 16, 4, 64, 4, 8, 1.0, 0.1, 0.0, 0, 0.0, 0.0, 1.0, 0,
-                                 0, None) == -3  # mask not 16-byte aligned
+                                 0, 0, None) == -3  # mask not 16-byte aligned
     # the low-rank forward: rank and dtype checks
     assert lib.sf_masked_gemm_fwd_lowrank(16, 16, 16, 16, None, 16, 256, 64, 64, 12, 1, None, None) == -2
     assert lib.sf_masked_gemm_fwd_lowrank(16, 16, None, 16, None, 16, 256, 64, 64, 16, 1, None, None) == -1

@@ -429,6 +429,35 @@ def test_general_nm_variants():
         assert rel_err(dW.float(), g[f"{tag}_dW"].float()) <= tol, tag
 
 
+UH_MODES = {"mid": "mid", "topn": "structured_topn", "beta": "mid", "bin": "mid", "bf16": "mid"}
+
+
+def test_unstructured_hard_view_variants():
+    """mask_type='unstructured' with its own hard view (mask > 0.5): quantile gate, pulls, beta mixing, EMA,
+    flip count by the threshold, masked forward / backward, replayed by the oracle."""
+    g = Golden("unstructured_hard")
+    for tag in g["variants"]:
+        W, H, mask0 = g[f"{tag}_W"], g[f"{tag}_H"], g[f"{tag}_mask0"]
+        tol = BF16_TOL if W.dtype == torch.bfloat16 else F32_TOL
+        s = O.normalize_scores(O.importance_score(W, "hessian_obd", H=H))
+        tau = O.tau_unstructured(s, g.scalar(f"{tag}_sparsity"), None)
+        G = O.gate_target_unstructured(s, tau, g.scalar(f"{tag}_T"), beta_s=g.scalar(f"{tag}_beta_s"))
+        assert rel_err(G.float(), g[f"{tag}_G"].float()) <= tol, tag
+        new = O.mask_update(mask0, g[f"{tag}_G"], mask_lr=0.2, lambda_mid=g.scalar(f"{tag}_lambda"), pen_lr=0.15,
+                            penalty_mode=UH_MODES[tag], binarize_decay=0.05 if tag == "bin" else 0.0)
+        assert rel_err(new, g[f"{tag}_mask1"]) <= tol, tag
+        assert torch.equal(O.hard_mask_from_soft(g[f"{tag}_mask1"], "unstructured"), g[f"{tag}_hard1"]), tag
+        assert O.flip_count(mask0, g[f"{tag}_mask1"], "unstructured") == g.scalar(f"{tag}_flips"), tag
+        hx = g.scalar(f"{tag}_hx")
+        assert 0.0 < hx < 1.0
+        eff = O.effective_mask(g[f"{tag}_mask1"], hx, "unstructured")
+        X, dY = g[f"{tag}_X"], g[f"{tag}_dY"]
+        assert rel_err(O.linear_forward(X, W, eff).float(), g[f"{tag}_Y"].float()) <= tol, tag
+        dX, dW, _ = O.linear_backward(X, W, eff, dY)
+        assert rel_err(dX.float(), g[f"{tag}_dX"].float()) <= tol, tag
+        assert rel_err(dW.float(), g[f"{tag}_dW"].float()) <= tol, tag
+
+
 @pytest.mark.parametrize("tag,tol,l1", [("f32", F32_TOL, 0.0), ("bf16", BF16_TOL, 0.0), ("l1", F32_TOL, 0.02)])
 def test_adamw(tag, tol, l1):
     g = Golden("adamw")
