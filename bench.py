@@ -81,25 +81,54 @@ def schedule(it):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU while the timed region runs:
+    read-only NVML queries every 10 ms from a thread, or one `nvidia-smi` query per sample where the NVML
+    binding is missing. Nothing is set."""
 
     Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index):
         self.index, self.rows, self._stop, self._t = index, [], threading.Event(), None
+        self._nvml = self._handle = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            try:
+                props = torch.cuda.get_device_properties(index)
+                bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+                self._handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus)
+            except Exception:
+                self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self._nvml = pynvml
+            self._max = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._nvml = None
+
+    def _sample_nvml(self):
+        n, h = self._nvml, self._handle
+        sm = float(n.nvmlDeviceGetClockInfo(h, n.NVML_CLOCK_SM))
+        get = getattr(n, "nvmlDeviceGetCurrentClocksEventReasons", None) or n.nvmlDeviceGetCurrentClocksThrottleReasons
+        bits = int(get(h))
+        flags = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
+        return [str(sm), str(self._max), ""] + ["Active" if bits & flags[k] else "Not Active" for k in self.NAMES]
 
     def _run(self):
         while not self._stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
-                                      str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
-                if out:
-                    self.rows.append([c.strip() for c in out.split(",")])
+                if self._nvml is not None:
+                    self.rows.append(self._sample_nvml())
+                else:
+                    out = subprocess.run(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-i",
+                                          str(self.index)], capture_output=True, text=True, timeout=5).stdout.strip()
+                    if out:
+                        self.rows.append([c.strip() for c in out.split(",")])
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(0.01 if self._nvml is not None else 0.05)
 
     def start(self):
         self._t = threading.Thread(target=self._run, daemon=True)
@@ -110,10 +139,10 @@ class ClockSampler:
         if self._t:
             self._t.join(timeout=6)
         sm = sorted(float(r[0]) for r in self.rows if r and r[0].replace(".", "").isdigit())
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, c in zip(names, r[3:7]) if c.lower().startswith("active")})
+        reasons = sorted({n for r in self.rows if len(r) >= 7 for n, c in zip(self.NAMES, r[3:7]) if c.lower().startswith("active")})
         mx = max((float(r[1]) for r in self.rows if len(r) > 1 and r[1].replace(".", "").isdigit()), default=None)
-        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm)}
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": reasons, "samples": len(sm),
+                "source": "nvml" if self._nvml is not None else "nvidia-smi"}
 
 
 # ---------------------------------------------------------------------------------------------
