@@ -379,18 +379,18 @@ def mask_update_tile16(mask, G, *, mask_lr, sparsity_ratio, lambda_mid=0.0, pen_
 
 
 def glu_joint_update(gate_score, up_score, gate_mask, up_mask, *, temperature, mask_lr, lambda_mid=0.0,
-                     pen_lr=None, penalty_mode="mid", binarize_decay=0.0, beta_s=0.0, exact=False):
+                     pen_lr=None, penalty_mode="mid", binarize_decay=0.0, beta_s=0.0, exact=False, n=2, m=4):
     """Joint update of a GLU gate / up pair, legacy/utils.py:363-479: one gate target from the
     summed raw scores (:407-412, :536-613), the penalty pull taken from the GATE layer's mask
     (:616-643; modes other than structured_topn / mid only clamp), the binarise push (:423-431),
     then the same target moves both masks (:434-435). Returns (new gate mask, new up mask)."""
     joint = gate_score + up_score
-    G = gate_target_structured(normalize_scores(joint).to(gate_mask.dtype), temperature, exact=exact, beta_s=beta_s)
+    G = gate_target_structured(normalize_scores(joint).to(gate_mask.dtype), temperature, exact=exact, beta_s=beta_s, n=n, m=m)
     a = float(mask_lr)
     pen_lr = a if pen_lr is None else float(pen_lr)
     if float(lambda_mid) != 0.0:
         if penalty_mode == "structured_topn":
-            G = G - (pen_lr * float(lambda_mid)) * (gate_mask.to(G.dtype) - topn_indicator(G, 2, 4, dtype=G.dtype))
+            G = G - (pen_lr * float(lambda_mid)) * (gate_mask.to(G.dtype) - topn_indicator(G, n, m, dtype=G.dtype))
         elif penalty_mode == "mid":
             G = G - (pen_lr * float(lambda_mid)) * (1.0 - 2.0 * gate_mask).to(G.dtype)
         G = G.clamp(0.0, 1.0)

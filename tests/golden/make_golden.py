@@ -408,6 +408,7 @@ GLU_VARIANTS = {
                  beta_structural_end=4),
     "mid": dict(mask_penalty_mode="mid"),
     "nm24": dict(mask_penalty_mode="nm_2_4"),
+    "topn48": dict(N=4, M=8, mask_penalty_mode="structured_topn", beta_structural_start=0, beta_structural_end=4),
 }
 GLU_BASE = dict(mask_type="structured", mask_metric="hessian_obd", N=2, M=4, mask_update_period=1, sparsity_warmup_steps=0,
                 mask_lr=0.25, temp_init=0.8, temp_min=0.05, temp_decay=0.7, mask_hardening_start=1,

@@ -176,7 +176,7 @@ class TinyGLU(torch.nn.Module):
         self.mlp = self.block.mlp
 
 
-@pytest.mark.parametrize("tag", ["topn", "mid", "nm24"])
+@pytest.mark.parametrize("tag", ["topn", "mid", "nm24", "topn48"])
 def test_glu_joint_mask_follows_the_reference(tag):
     """calculate_model_mask with glu_joint_mask: gate_proj / up_proj get one update from the summed
     score (penalty pull from the gate layer's mask), down_proj its own (legacy/utils.py:183-479)."""

@@ -193,15 +193,18 @@ def test_glu_joint_mask_update():
             beta_s = O.beta_structural(step, cfg.get("beta_structural_start", 0), cfg.get("beta_structural_end", 0))
             bd = cfg.get("mask_binarize_decay", 0.0)
             sc = {n: O.importance_score(W[n], "hessian_obd", H=H[n]) for n in W}
+            N, M = int(cfg["N"]), int(cfg["M"])
             new_gate, new_up = O.glu_joint_update(sc["gate"], sc["up"], mask["gate"], mask["up"], temperature=T,
                                                   mask_lr=cfg["mask_lr"], lambda_mid=lam, pen_lr=cfg["mask_penalty_lr"],
-                                                  penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd, beta_s=beta_s)
-            G = O.gate_target_structured(O.normalize_scores(sc["down"]), T, beta_s=beta_s)
+                                                  penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd, beta_s=beta_s,
+                                                  n=N, m=M)
+            G = O.gate_target_structured(O.normalize_scores(sc["down"]), T, beta_s=beta_s, n=N, m=M)
             new_down = O.mask_update(mask["down"], G, mask_lr=cfg["mask_lr"], lambda_mid=lam, pen_lr=cfg["mask_penalty_lr"],
-                                     penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd)
+                                     penalty_mode=cfg["mask_penalty_mode"], binarize_decay=bd, n=N, m=M)
             for n, new in (("gate", new_gate), ("up", new_up), ("down", new_down)):
                 assert rel_err(new, g[f"{tag}_s{step}_{n}_mask"]) <= F32_TOL, (tag, step, n)
-                assert O.flip_count(mask[n], g[f"{tag}_s{step}_{n}_mask"]) == g.scalar(f"{tag}_s{step}_{n}_flips")
+                assert O.flip_count(mask[n], g[f"{tag}_s{step}_{n}_mask"], "structured", N, M) == \
+                    g.scalar(f"{tag}_s{step}_{n}_flips")
                 mask[n] = g[f"{tag}_s{step}_{n}_mask"].clone()
                 hx = O.hardening_x(step, cfg["mask_hardening_start"], cfg["mask_hardening_duration"])
                 assert math.isclose(hx, g.scalar(f"{tag}_s{step}_{n}_hx"), abs_tol=1e-12)
