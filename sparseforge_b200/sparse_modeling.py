@@ -545,6 +545,7 @@ class SparseLinear(nn.Linear):
     def metadata(self) -> torch.Tensor:
         """Packed 2:4 metadata of top2(mask) ([out, in/8] uint8), as left by the last mask update
         or masked-weight refresh."""
+        self._check_strict_2to4("metadata()")
         self.masked_weight()
         return self._meta
 
