@@ -14,16 +14,30 @@ namespace sf {
 constexpr int kThreads = 256;
 
 // out[i] = sum_g slots[g][i], accumulated in fp32 in rank order (deterministic), 8 elements per thread.
-template <typename T>
+// GT > 0: the slot count is a compile-time constant, so all GT loads of a chunk are in flight together.
+template <typename T, int GT>
 __global__ void __launch_bounds__(kThreads)
 reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__ out, int64_t chunks, int64_t slot_stride, int G) {
     for (int64_t c = (int64_t)blockIdx.x * kThreads + threadIdx.x; c < chunks; c += (int64_t)gridDim.x * kThreads) {
-        float acc[8], x[8];
-        Vec8<T>::load(slots + c * 8, acc);
-        for (int g = 1; g < G; ++g) {
-            Vec8<T>::load(slots + g * slot_stride + c * 8, x);
+        float acc[8];
+        if (GT > 0) {
+            float x[GT > 0 ? GT : 1][8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] += x[i];
+            for (int g = 0; g < GT; ++g) Vec8<T>::load(slots + g * slot_stride + c * 8, x[g]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) acc[i] = x[0][i];
+#pragma unroll
+            for (int g = 1; g < GT; ++g)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += x[g][i];
+        } else {
+            float x[8];
+            Vec8<T>::load(slots + c * 8, acc);
+            for (int g = 1; g < G; ++g) {
+                Vec8<T>::load(slots + g * slot_stride + c * 8, x);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] += x[i];
+            }
         }
         Vec8<T>::store(out + c * 8, acc);
     }
@@ -88,11 +102,18 @@ int sf_reduce_slots(const void* slots, void* out, int64_t n_slots, int64_t n, in
     int64_t blocks = (chunks + kThreads - 1) / kThreads;
     if (blocks > 148 * 8) blocks = 148 * 8;
     cudaStream_t st = (cudaStream_t)stream;
-    if (dtype == SF_F32)
-        reduce_slots_kernel<float><<<(int)blocks, kThreads, 0, st>>>((const float*)slots, (float*)out, chunks, n, (int)n_slots);
-    else
-        reduce_slots_kernel<__nv_bfloat16><<<(int)blocks, kThreads, 0, st>>>((const __nv_bfloat16*)slots, (__nv_bfloat16*)out,
-                                                                             chunks, n, (int)n_slots);
+#define SF_REDUCE(TT, GT) reduce_slots_kernel<TT, GT><<<(int)blocks, kThreads, 0, st>>>((const TT*)slots, (TT*)out, chunks, n, (int)n_slots)
+    if (dtype == SF_F32) {
+        SF_REDUCE(float, 0);
+    } else {
+        switch (n_slots) {
+            case 2: SF_REDUCE(__nv_bfloat16, 2); break;
+            case 4: SF_REDUCE(__nv_bfloat16, 4); break;
+            case 8: SF_REDUCE(__nv_bfloat16, 8); break;
+            default: SF_REDUCE(__nv_bfloat16, 0);
+        }
+    }
+#undef SF_REDUCE
     SF_CHECK_CUDA(cudaGetLastError());
     return SF_OK;
 }
