@@ -32,16 +32,17 @@ struct NmUpdateParams {
 };
 
 // M consecutive values -> floats, with the widest accesses the run allows (the run starts on a
-// multiple of its own size, the tensors on 16 bytes).
+// multiple of its own size, the tensors on 16 bytes). Every tensor is read and written once per pass:
+// streaming (evict-first) accesses.
 template <int M>
 __device__ __forceinline__ void load_run(const float* __restrict__ p, float (&x)[M]) {
     if constexpr (M == 2) {
-        const float2 t = *reinterpret_cast<const float2*>(p);
+        const float2 t = __ldcs(reinterpret_cast<const float2*>(p));
         x[0] = t.x; x[1] = t.y;
     } else {
 #pragma unroll
         for (int i = 0; i < M / 4; ++i) {
-            const float4 t = *reinterpret_cast<const float4*>(p + 4 * i);
+            const float4 t = __ldcs(reinterpret_cast<const float4*>(p + 4 * i));
             x[4 * i] = t.x; x[4 * i + 1] = t.y; x[4 * i + 2] = t.z; x[4 * i + 3] = t.w;
         }
     }
@@ -49,19 +50,39 @@ __device__ __forceinline__ void load_run(const float* __restrict__ p, float (&x)
 template <int M>
 __device__ __forceinline__ void store_run(float* __restrict__ p, const float (&x)[M]) {
     if constexpr (M == 2) {
-        *reinterpret_cast<float2*>(p) = make_float2(x[0], x[1]);
+        __stcs(reinterpret_cast<float2*>(p), make_float2(x[0], x[1]));
     } else {
 #pragma unroll
         for (int i = 0; i < M / 4; ++i)
-            *reinterpret_cast<float4*>(p + 4 * i) = make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]);
+            __stcs(reinterpret_cast<float4*>(p + 4 * i), make_float4(x[4 * i], x[4 * i + 1], x[4 * i + 2], x[4 * i + 3]));
+    }
+}
+// M bf16 values as M / 2 packed pairs
+template <int M>
+__device__ __forceinline__ void load_pairs(const __nv_bfloat16* __restrict__ p, uint32_t (&w)[M / 2]) {
+    if constexpr (M == 2) {
+        w[0] = __ldcs(reinterpret_cast<const uint32_t*>(p));
+    } else if constexpr (M == 4) {
+        const uint2 t = __ldcs(reinterpret_cast<const uint2*>(p));
+        w[0] = t.x; w[1] = t.y;
+    } else {
+#pragma unroll
+        for (int i = 0; i < M / 8; ++i) {
+            const uint4 t = __ldcs(reinterpret_cast<const uint4*>(p + 8 * i));
+            w[4 * i] = t.x; w[4 * i + 1] = t.y; w[4 * i + 2] = t.z; w[4 * i + 3] = t.w;
+        }
     }
 }
 template <int M>
-__device__ __forceinline__ void load_run(const __nv_bfloat16* __restrict__ p, float (&x)[M]) {
+__device__ __forceinline__ void store_pairs(__nv_bfloat16* __restrict__ p, const uint32_t (&w)[M / 2]) {
+    if constexpr (M == 2) {
+        __stcs(reinterpret_cast<uint32_t*>(p), w[0]);
+    } else if constexpr (M == 4) {
+        __stcs(reinterpret_cast<uint2*>(p), make_uint2(w[0], w[1]));
+    } else {
 #pragma unroll
-    for (int i = 0; i < M / 2; ++i) {
-        const float2 t = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p + 2 * i));
-        x[2 * i] = t.x; x[2 * i + 1] = t.y;
+        for (int i = 0; i < M / 8; ++i)
+            __stcs(reinterpret_cast<uint4*>(p + 8 * i), make_uint4(w[4 * i], w[4 * i + 1], w[4 * i + 2], w[4 * i + 3]));
     }
 }
 // wm = W * cast(eff): the product is rounded once, in the weight's type, as `weight * mask` is in
@@ -77,12 +98,15 @@ __device__ __forceinline__ void store_product_run(float* __restrict__ wm, const 
 template <int M>
 __device__ __forceinline__ void store_product_run(__nv_bfloat16* __restrict__ wm, const __nv_bfloat16* __restrict__ W,
                                                   const float (&eff)[M]) {
+    uint32_t w[M / 2];
+    load_pairs<M>(W, w);
 #pragma unroll
     for (int i = 0; i < M / 2; ++i) {
-        const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(W + 2 * i);
         const __nv_bfloat162 e = __floats2bfloat162_rn(eff[2 * i], eff[2 * i + 1]);
-        *reinterpret_cast<__nv_bfloat162*>(wm + 2 * i) = __hmul2(w, e);
+        const __nv_bfloat162 r = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]), e);
+        w[i] = *reinterpret_cast<const uint32_t*>(&r);
     }
+    store_pairs<M>(wm, w);
 }
 
 // bit i set = entry i is among the n largest of the group (stable descending order)
