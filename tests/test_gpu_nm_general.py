@@ -161,6 +161,41 @@ def test_layer_size_against_the_oracle(ops, n, m):
     assert rel_err(wm.cpu().float(), want_wm.float()) <= BF16_TOL
 
 
+@pytest.mark.parametrize("rows,cols,n,m", [(3, 12, 1, 4), (5, 6, 1, 2), (7, 20, 3, 4), (3, 24, 5, 8), (1, 2, 1, 2)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_group_counts_that_do_not_fill_a_thread(ops, rows, cols, n, m, dtype):
+    """Small groups are handled several per thread; a layer whose group count is not a multiple of that
+    falls back to one group per thread. Same results as the oracle either way."""
+    from sparseforge_b200 import _lib
+
+    torch.manual_seed(rows * 100 + cols)
+    W = (torch.randn(rows, cols) * 0.02).to(dtype)
+    H = torch.rand(rows, cols) + 0.2
+    mask0 = torch.rand(rows, cols)
+    # the score pass takes multiples of eight elements; these sizes come with a score made on the host
+    raw = O.importance_score(W, "hessian_obd", H=H).float()
+    mu, sigma = O.score_norm_stats(raw)
+    score, norm = dev(raw), torch.tensor([float(mu), float(sigma)], dtype=torch.float32, device=DEV)
+    mask = dev(mask0)
+    stats = torch.zeros(8, dtype=torch.float64, device=DEV)
+    wm = torch.empty_like(dev(W))
+    ops.mask_update_nm(score, norm, mask, stats, n, m, W=dev(W), wm=wm, temperature=0.4, mask_lr=0.3, pen=0.05,
+                       penalty_mode=1, hx=0.5)
+    s = O.normalize_scores(O.importance_score(W, "hessian_obd", H=H))
+    want = O.mask_update(mask0, O.gate_target_structured(s, 0.4, n=n, m=m), mask_lr=0.3, lambda_mid=1.0, pen_lr=0.05,
+                         penalty_mode="structured_topn", n=n, m=m)
+    got = mask.cpu()
+    assert rel_err(got, want) <= 1e-5
+    assert int(stats[_lib.MSTAT_FLIPS]) == O.flip_count(mask0, got, "structured", n, m)
+    tol = BF16_TOL if dtype == torch.bfloat16 else F32_TOL
+    want_wm = O.masked_weight(W, O.effective_mask(got, 0.5, "structured", False, n, m))
+    assert rel_err(wm.cpu().float(), want_wm.float()) <= tol
+    wm2 = torch.empty_like(wm)
+    ops.effective_weight_nm(dev(W), mask, wm2, n, m, hx=0.5)
+    assert torch.equal(wm2, wm)
+    assert torch.equal(ops.project_nm(mask, n, m).cpu(), O.hard_mask_from_soft(got, "structured", n, m))
+
+
 def test_projection_strides_dtypes_and_nan(ops):
     torch.manual_seed(3)
     big = torch.rand(20, 96, device=DEV)
