@@ -468,6 +468,21 @@ def case_mask_stats():
         torch.randint = _orig_randint
         d[f"{tag}_keys"] = np.asarray(list(st.keys()))
         d[f"{tag}_values"] = np.asarray([float(v) for v in st.values()], dtype=np.float64)
+        # the per-step reductions of the loop over the same masks (legacy/utils.py:875-1234): mid penalty,
+        # sparsity penalty (structured layers count (M - N) / M analytically; then with the layers switched to
+        # the threshold count of the unstructured mask type), 2:4 tile statistics
+        put(d, f"{tag}_mid_penalty", float(ref_utils.mid_penalty(model, 0.7)))
+        pen, cur = ref_utils.sparsity_penalty(model, 0.4, 2.0)
+        put(d, f"{tag}_sparsity_pen", float(pen)); put(d, f"{tag}_sparsity_cur", float(cur))
+        for m in (model.fc1, model.fc2):
+            m.mask_type = "unstructured"
+        pen, cur = ref_utils.sparsity_penalty(model, 0.4, 2.0)
+        put(d, f"{tag}_sparsity_pen_unstructured", float(pen)); put(d, f"{tag}_sparsity_cur_unstructured", float(cur))
+        for m in (model.fc1, model.fc2):
+            m.mask_type = "structured"
+        ts = ref_utils.nm_2_4_tile_stats(model)
+        d[f"{tag}_tile_keys"] = np.asarray(list(ts.keys()))
+        d[f"{tag}_tile_values"] = np.asarray([float(v) for v in ts.values()], dtype=np.float64)
     save("mask_stats", d)
 
 

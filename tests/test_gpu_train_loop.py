@@ -250,6 +250,20 @@ def test_mask_stats_follow_the_reference(tag):
             assert math.isnan(got), k
         else:
             assert got == pytest.approx(v, rel=1e-5, abs=1e-12), k  # entropy terms use fp32 logarithms
+    # the per-step reductions of the loop over the same masks (legacy/utils.py:875-1234)
+    assert float(U.mid_penalty(model, 0.7)) == pytest.approx(g.scalar(f"{tag}_mid_penalty"), rel=1e-5)
+    pen, cur = U.sparsity_penalty(model, 0.4, 2.0)
+    assert cur == g.scalar(f"{tag}_sparsity_cur") and float(pen) == pytest.approx(g.scalar(f"{tag}_sparsity_pen"), rel=1e-6)
+    for m in (model.fc1, model.fc2):
+        m.mask_type = "unstructured"
+    pen, cur = U.sparsity_penalty(model, 0.4, 2.0)
+    assert cur == pytest.approx(g.scalar(f"{tag}_sparsity_cur_unstructured"), rel=1e-12)
+    assert float(pen) == pytest.approx(g.scalar(f"{tag}_sparsity_pen_unstructured"), rel=1e-5)
+    for m in (model.fc1, model.fc2):
+        m.mask_type = "structured"
+    tiles = U.nm_2_4_tile_stats(model)
+    for k, v in zip(g[f"{tag}_tile_keys"], g[f"{tag}_tile_values"].tolist()):
+        assert tiles[str(k)] == pytest.approx(v, rel=5e-6, abs=1e-9), k  # the reference's sums are fp32
 
 
 @pytest.mark.parametrize("tag,tol", [("f32", 1e-5), ("bf16", 1e-2), ("chunks", 1e-5)])

@@ -223,6 +223,23 @@ def test_mask_log_stats():
     for tag in ("inside", "edges"):
         got = O.mask_log_stats([g[f"{tag}_fc1_mask"], g[f"{tag}_fc2_mask"]], [g[f"{tag}_idx0"], g[f"{tag}_idx1"]])
         _same_stats(got, g[f"{tag}_keys"], g[f"{tag}_values"].tolist(), 1e-12)
+        # the per-step reductions over the same masks: mid penalty, sparsity penalty, 2:4 tile statistics
+        masks = [g[f"{tag}_fc1_mask"], g[f"{tag}_fc2_mask"]]
+        assert math.isclose(float(O.mid_penalty_value(masks, 0.7)), g.scalar(f"{tag}_mid_penalty"), rel_tol=1e-6)
+        st = [O.mask_stats(m) for m in masks]
+        n = sum(m.numel() for m in masks)
+        assert g.scalar(f"{tag}_sparsity_cur") == 0.5  # structured layers: (M - N) / M by construction
+        assert math.isclose(g.scalar(f"{tag}_sparsity_pen"), 2.0 * (0.5 - 0.4) ** 2, rel_tol=1e-6)
+        cur = sum(s["count_lt_half"] for s in st) / n
+        assert math.isclose(cur, g.scalar(f"{tag}_sparsity_cur_unstructured"), rel_tol=1e-12)
+        assert math.isclose(2.0 * (cur - 0.4) ** 2, g.scalar(f"{tag}_sparsity_pen_unstructured"), rel_tol=1e-5)
+        top2 = sum(s["sum_top2"] for s in st) / (n / 4 * 2)
+        bot2 = sum(s["sum_bot2"] for s in st) / (n / 4 * 2)
+        want = dict(zip([str(k) for k in g[f"{tag}_tile_keys"]], g[f"{tag}_tile_values"].tolist()))
+        # the reference adds the sorted groups up in fp32: a few 1e-7 from the exact sums
+        assert math.isclose(top2, want["top2_avg"], rel_tol=2e-6) and math.isclose(bot2, want["bot2_avg"], rel_tol=2e-6)
+        assert math.isclose(1.0 - top2, want["top2_gap"], rel_tol=5e-6)
+        assert math.isclose((1.0 - top2) + bot2, want["total_gap"], rel_tol=5e-6)
 
 
 @pytest.mark.parametrize("tag,tol", [("f32", 1e-5), ("bf16", BF16_TOL), ("chunks", 1e-5)])
