@@ -860,6 +860,49 @@ def case_unstructured_hard():
     save("unstructured_hard", d)
 
 
+SCHEDULE_CONFIGS = {
+    "anneal": dict(temp_init=1.0, temp_min=0.05, temp_decay=0.7, mask_update_period=3, mask_hardening_start=5,
+                   mask_hardening_duration=10, sparsity_warmup_steps=20, beta_structural_start=4, beta_structural_end=12),
+    "switch": dict(temp_init=2.0, temp_min=0.1, temp_decay=0.9, mask_update_switch_step=10, mask_update_period_before=2,
+                   mask_update_period_after=5, mask_hardening_start=0, mask_hardening_duration=1, sparsity_warmup_steps=0),
+    "block": dict(mask_type="unstructured", hard_mask_type="block_sparse16", sparsity_ratio=0.6, temp_init=1.0, temp_min=0.05,
+                  temp_decay=0.8, mask_update_period=1, sparsity_warmup_steps=40, mask_hardening_start=100,
+                  mask_hardening_duration=50),
+}
+SCHEDULE_STEPS = [0, 1, 2, 3, 4, 5, 7, 8, 9, 10, 11, 12, 15, 19, 20, 21, 30, 40, 41, 100, 125, 150, 151, 1000]
+
+
+def case_schedules():
+    """Host-side schedules of a layer (legacy/sparse_modeling.py:932-985, 1603-1619) and of the loop
+    (update_mask_penalty_lr legacy/utils.py:141-180): values of the reference over a grid of steps. The
+    hardening value is read after an update_mask call at that step on a fresh layer (it is set there)."""
+    d = {"configs_json": np.asarray(json.dumps(SCHEDULE_CONFIGS)), "steps": np.asarray(SCHEDULE_STEPS)}
+    for tag, kw in SCHEDULE_CONFIGS.items():
+        rows = []
+        for step in SCHEDULE_STEPS:
+            torch.manual_seed(3)
+            cfg = ref_sm.SparseLinearConfig(**dict(dict(mask_type="structured", mask_metric="magnitude"), **kw))
+            layer = ref_sm.SparseLinear(32, 16, sparselinear_config=cfg, bias=False)
+            layer.initialize()
+            layer.mask.data = torch.rand(16, 32)
+            vals = [float(layer._temperature(step)), float(layer._mask_update_period(step)),
+                    float(layer._effective_sparsity(step)), float(layer._beta_structural(step))]
+            # force an update at this step so that the hardening schedule is evaluated there
+            layer.cfg.mask_update_period = 1
+            layer.cfg.mask_update_switch_step = None
+            layer.cfg.sparsity_warmup_steps = 0
+            layer.update_mask(step, lambda_mid=0.0)
+            vals.append(float(layer.hardening_x))
+            rows.append(vals)
+        d[f"{tag}_values"] = np.asarray(rows, dtype=np.float64)  # temperature, period, sparsity, beta, hardening_x
+    lin = ref_sm.SparseLinear(8, 8, sparselinear_config=ref_sm.SparseLinearConfig(), bias=False)
+    pl = [[float(ref_utils.update_mask_penalty_lr(lin, s, 50, 0.02, 0.3, sched)) for s in (0, 1, 10, 25, 49, 50, 80)]
+          for sched in ("constant", "linear", "cosine", "other")]
+    d["penalty_lr_steps"] = np.asarray([0, 1, 10, 25, 49, 50, 80])
+    d["penalty_lr"] = np.asarray(pl, dtype=np.float64)
+    save("schedules", d)
+
+
 if __name__ == "__main__":
     # `make_golden.py wanda ...` regenerates only the named single-function cases
     only = [a for a in sys.argv[1:] if not a.startswith("-")]

@@ -101,6 +101,34 @@ def test_host_schedules_match_reference_formulas():
     assert layer.mask.dtype == torch.float32 and layer.grad_ema.numel() == 1 and layer._is_placeholder("grad_ema")
 
 
+def test_host_schedules_follow_the_reference_over_a_grid_of_steps():
+    """Temperature, update period, effective sparsity, beta mixing and hardening of a layer, and the penalty
+    learning-rate schedule of the loop, against values recorded from the reference
+    (tests/golden/schedules.npz; legacy/sparse_modeling.py:932-985, 1603-1619, legacy/utils.py:141-180)."""
+    import json
+
+    import sparseforge_b200 as sf
+    from golden_io import Golden
+    from sparseforge_b200 import utils as U
+
+    g = Golden("schedules")
+    steps = [int(x) for x in g["steps"]]
+    for tag, kw in json.loads(str(g["configs_json"])).items():
+        cfg = sf.SparseLinearConfig(**dict(dict(mask_type="structured", mask_metric="magnitude"), **kw))
+        layer = sf.SparseLinear(32, 16, sparselinear_config=cfg, bias=False)
+        want = g[f"{tag}_values"]
+        for i, step in enumerate(steps):
+            got = [layer._temperature(step), float(layer._mask_update_period(step)), layer._effective_sparsity(step),
+                   layer._beta_structural(step), layer._next_hardening_x(step)]
+            for name, a, b in zip(("temperature", "period", "sparsity", "beta", "hardening_x"), got, want[i].tolist()):
+                assert a == pytest.approx(b, rel=1e-12, abs=1e-15), (tag, step, name)
+    lin = sf.SparseLinear(8, 8, sparselinear_config=sf.SparseLinearConfig(), bias=False)
+    for row, sched in zip(g["penalty_lr"].tolist(), ("constant", "linear", "cosine", "other")):
+        for s_, v in zip([int(x) for x in g["penalty_lr_steps"]], row):
+            assert U.update_mask_penalty_lr(lin, s_, 50, 0.02, 0.3, sched) == pytest.approx(v, rel=1e-12), (sched, s_)
+            assert lin.mask_penalty_lr == pytest.approx(v, rel=1e-12)
+
+
 def test_unsupported_configurations_raise():
     import sparseforge_b200 as sf
 
