@@ -898,6 +898,11 @@ def case_schedules():
     lin = ref_sm.SparseLinear(8, 8, sparselinear_config=ref_sm.SparseLinearConfig(), bias=False)
     pl = [[float(ref_utils.update_mask_penalty_lr(lin, s, 50, 0.02, 0.3, sched)) for s in (0, 1, 10, 25, 49, 50, 80)]
           for sched in ("constant", "linear", "cosine", "other")]
+    import dataclasses
+
+    ref_cfg = ref_sm.SparseLinearConfig()
+    d["config_defaults_json"] = np.asarray(json.dumps({f.name: getattr(ref_cfg, f.name)
+                                                       for f in dataclasses.fields(ref_sm.SparseLinearConfig)}))
     d["penalty_lr_steps"] = np.asarray([0, 1, 10, 25, 49, 50, 80])
     d["penalty_lr"] = np.asarray(pl, dtype=np.float64)
     save("schedules", d)

@@ -76,6 +76,14 @@ def test_config_fields_match_the_reference_dataclass():
     assert [f.name for f in dataclasses.fields(sf.SparseLinearConfig)] == want
     cfg = sf.SparseLinearConfig()
     assert (cfg.mask_lr, cfg.temp_decay, cfg.mask_update_period, cfg.sparsity_warmup_steps) == (0.10, 0.97, 10, 100)
+    # every field and its default, as recorded from the reference's dataclass (legacy/sparse_modeling.py:136-239)
+    import json
+
+    from golden_io import Golden
+
+    ref = json.loads(str(Golden("schedules")["config_defaults_json"]))
+    assert list(ref) == want
+    assert {f.name: getattr(cfg, f.name) for f in dataclasses.fields(sf.SparseLinearConfig)} == ref
 
 
 def test_host_schedules_match_reference_formulas():
