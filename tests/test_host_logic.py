@@ -197,6 +197,43 @@ def test_general_nm_configurations_are_checked_on_the_host():
     assert lib.sf_masked_gemm_fwd_lowrank(16, 16, 16, 16, None, 16, 256, 64, 64, 16, 0, None, None) == -2
 
 
+def test_peer_sharded_layer_buffers_and_checks_without_a_gpu():
+    """Landing-buffer bookkeeping and input checks of PeerShardedLinear with a stand-in arena."""
+    import sparseforge_b200 as sf
+    from sparseforge_b200.sharding import PeerShardedLinear
+
+    class Arena:
+        world, rank, mc_base, group = 2, 1, 0, None
+
+        def close(self):
+            self.closed = True
+
+    shard = sf.SparseLinear(64, 32, sparselinear_config=sf.SparseLinearConfig(), bias=False).to(torch.bfloat16)
+    arena = Arena()
+    layer = PeerShardedLinear(shard, out_total=64, max_tokens=512, arena=arena)
+    assert shard._row_sharded and layer.arena is arena
+    y_bytes, s_bytes = 512 * 64 * 2, 512 * 64 * 2
+    spans = []
+    for par in range(PeerShardedLinear.N_BUFFERS):
+        y_off, s_off = layer._offsets(par)
+        spans += [(y_off, y_off + y_bytes), (s_off, s_off + s_bytes)]
+        assert y_off % 16 == 0 and s_off % 16 == 0
+    spans.sort()
+    assert all(a[1] <= b[0] for a, b in zip(spans, spans[1:]))  # the four regions do not overlap
+    assert [layer._next_parity() for _ in range(4)] == [1, 0, 1, 0]
+    layer._check(torch.zeros(256, 64, dtype=torch.bfloat16))
+    for bad in (torch.zeros(128, 64, dtype=torch.bfloat16), torch.zeros(260, 64, dtype=torch.bfloat16),
+                torch.zeros(1024, 64, dtype=torch.bfloat16)):
+        with pytest.raises(ValueError):
+            layer._check(bad)
+    with pytest.raises(TypeError):
+        layer._check(torch.zeros(256, 64))
+    with pytest.raises(ValueError):
+        PeerShardedLinear(shard, out_total=96, max_tokens=512, arena=Arena())
+    layer.close()
+    assert arena.closed and layer.arena is None
+
+
 def test_shard_bounds():
     from sparseforge_b200.sharding import shard_bounds
 
