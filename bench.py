@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import argparse
 import ctypes
+import gc
 import json
 import os
 import subprocess
@@ -527,6 +528,10 @@ def run_ours(args):
     timers = Timers() if world == 1 else None
     launches = 0
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    # at N > 1 a step lasts 2-5 ms and the host is only a step or two ahead of the devices: a collector pause
+    # on one rank would stall every rank, so the collector rests while the steps are being issued
+    gc.collect()
+    gc.disable()
     t0.record(main)
     host_t0 = time.perf_counter()
     for _ in range(args.steps):
@@ -536,6 +541,7 @@ def run_ours(args):
     join_streams()
     t1.record(main)
     barrier()
+    gc.enable()
     clocks = sampler.stop() if rank == 0 else None
     total_ms = t0.elapsed_time(t1)
     launches_timed = launches
@@ -612,12 +618,15 @@ def run_ours(args):
             it_next += 1
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        gc.collect()
+        gc.disable()
         e0.record(main)
         for _ in range(args.steps):
             step(it_next, e2e=True)
             it_next += 1
         e1.record(main)
         barrier()
+        gc.enable()
         e2e_ms = e0.elapsed_time(e1)
 
     # every rank learns of a device-side wait that ran out on ANY rank, releases the arena with the
